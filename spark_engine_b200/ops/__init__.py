@@ -1,0 +1,188 @@
+"""Operator layer: one Python entry point per op; the sm_100a kernels run on a B200, plain PyTorch
+runs on CPU (fp32 plumbing and oracle tests).
+
+On a CUDA device the kernel library MUST be present: an op whose kernel is missing raises instead of
+silently running an eager fallback (set SPARK_ALLOW_TORCH_FALLBACK=1 to run the PyTorch/ATen
+baseline path on purpose, e.g. for A/B timing against the library path).
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..oracle import layers as L
+from ..quant.formats import QuantWeight
+
+_FALLBACK = os.environ.get("SPARK_ALLOW_TORCH_FALLBACK", "0") == "1"
+_cuda_ops = None
+
+
+def cuda_ops():
+    """The kernel bindings (loaded on first use on a CUDA device)."""
+    global _cuda_ops
+    if _cuda_ops is None:
+        from . import cuda as _c
+        _cuda_ops = _c
+    return _cuda_ops
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FALLBACK
+
+
+def set_fallback(on: bool):
+    """Route CUDA tensors through PyTorch/ATen ops (the library baseline) instead of the kernels."""
+    global _FALLBACK
+    _FALLBACK = on
+
+
+# ----------------------------------------------------------------------------- basic ops
+def embed(table: torch.Tensor, ids: torch.Tensor, dtype) -> torch.Tensor:
+    return table[ids].to(dtype)
+
+
+def linear(x: torch.Tensor, w) -> torch.Tensor:
+    """y = x @ W^T for a dense `[N,K]` tensor or a quantised weight object."""
+    if isinstance(w, QuantWeight):
+        if use_kernels(x):
+            return cuda_ops().quant_linear(x, w)
+        return (x.float() @ w.dequant().to(x.device).t()).to(x.dtype)
+    if use_kernels(x):
+        return cuda_ops().dense_linear(x, w)
+    return x @ w.to(x.dtype).t()
+
+
+def rmsnorm(x, w, eps):
+    if use_kernels(x):
+        return cuda_ops().rmsnorm(x, w, eps)
+    return L.rms(x.float(), w.float(), eps).to(x.dtype)
+
+
+def add_rmsnorm(delta, res, w, eps):
+    """res' = res + delta (delta may be None); returns (rmsnorm(res') * w, res')."""
+    if use_kernels(res):
+        return cuda_ops().add_rmsnorm(delta, res, w, eps)
+    if delta is not None:
+        res = res + delta
+    return L.rms(res.float(), w.float(), eps).to(res.dtype), res
+
+
+def swiglu(gu: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+    """gu = [gate | up] halves along the last axis."""
+    if use_kernels(gu):
+        return cuda_ops().swiglu(gu, limit)
+    F_ = gu.shape[-1] // 2
+    return L.swiglu(gu[..., :F_].float(), gu[..., F_:].float(), limit).to(gu.dtype)
+
+
+# ----------------------------------------------------------------------------- MoE
+def route(h, w, c):
+    """Router: returns (weights [R,k] fp32, expert ids [R,k] int64, shared gate [R,1] or None)."""
+    logits = linear(h, w["gate"]).float()
+    sg = None
+    if c.shared_gate:
+        sg = torch.sigmoid(logits[:, c.n_experts:])
+        logits = logits[:, : c.n_experts]
+    if c.router == "softmax":
+        p = torch.softmax(logits, -1)
+        sel = p
+    elif c.router == "sigmoid_bias":
+        p = torch.sigmoid(logits)
+        sel = p + w["bias"].float().to(p.device)
+    else:
+        p = torch.sqrt(F.softplus(logits))
+        sel = p + w["bias"].float().to(p.device)
+    idx = torch.sort(sel, dim=-1, descending=True, stable=True).indices[:, : c.top_k]
+    wts = torch.gather(p, 1, idx)
+    wts = wts / wts.sum(-1, keepdim=True).clamp_min(1e-20) * c.route_scale
+    return wts, idx, sg
+
+
+def moe(h, w, c):
+    """Routed experts (slot-order weighted sum) + shared expert."""
+    if use_kernels(h):
+        return cuda_ops().moe(h, w, c)
+    R = h.shape[0]
+    wts, idx, sg = route(h, w, c)
+    out = torch.zeros(R, h.shape[1], dtype=torch.float32, device=h.device)
+    hf = h.float()
+    wgu, wd = w["w_gu"], w["w_down"]
+    for slot in range(c.top_k):
+        for e in idx[:, slot].unique().tolist():
+            rows = (idx[:, slot] == e).nonzero(as_tuple=True)[0]
+            gu = hf[rows] @ _expert(wgu, e).t()
+            y = L.swiglu(gu[:, : c.ffn], gu[:, c.ffn:], c.swiglu_limit) @ _expert(wd, e).t()
+            out[rows] += wts[rows, slot].unsqueeze(1) * y
+    if "s_gu" in w:
+        gu = linear(h, w["s_gu"]).float()
+        Fs = gu.shape[1] // 2
+        sh = linear(L.swiglu(gu[:, :Fs], gu[:, Fs:], c.swiglu_limit).to(h.dtype), w["s_down"]).float()
+        out = out + (sg * sh if sg is not None else sh)
+    return out.to(h.dtype)
+
+
+def _expert(w, e):
+    if isinstance(w, QuantWeight):
+        return w.dequant_expert(e)
+    return w[e].float()
+
+
+# ----------------------------------------------------------------------------- mixers (fast paths)
+def gdn_mixer(mixer, proj, ab, plan, commit) -> Optional[torch.Tensor]:
+    if use_kernels(proj):
+        return cuda_ops().gdn_mixer(mixer, proj, ab, plan, commit)
+    return None
+
+
+def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
+    if use_kernels(proj):
+        return cuda_ops().gdn_commit(mixer, proj, ab, plan, accepted)
+    return False
+
+
+def kda_mixer(mixer, pre, lr, plan, commit) -> Optional[torch.Tensor]:
+    if use_kernels(pre):
+        return cuda_ops().kda_mixer(mixer, pre, lr, plan, commit)
+    return None
+
+
+def attn_mixer(mixer, qkv, plan, seqs) -> Optional[torch.Tensor]:
+    if use_kernels(qkv):
+        return cuda_ops().attn_mixer(mixer, qkv, plan, seqs)
+    return None
+
+
+def model_forward(model, plan, commit, want_hidden):
+    """Whole-model fast path (captured CUDA graph of the decode step); None = run layer by layer."""
+    return None
+
+
+# ----------------------------------------------------------------------------- hyper-connections
+def hc_gated_mix(X, w, eps):
+    post, mixed = L.hc_gated_mix(X.float(), {k: v.float() for k, v in w.items()}, eps)
+    return (None if post is None else post), mixed.to(X.dtype)
+
+
+def mhc_pre(X, w, iters, eps):
+    h, post, comb = L.mhc_pre(X.float(), {k: v.float() for k, v in w.items()}, iters, eps)
+    return h.to(X.dtype), post, comb
+
+
+def mhc_post(X, x, post, comb):
+    return L.mhc_post(X.float(), x.float(), post, comb).to(X.dtype)
+
+
+def ngram_embed(model, X, plan, w):
+    """Hashed n-gram rows need the token history of each sequence: the model keeps it per slot."""
+    from ..models.ngram import ngram_rows_for_plan
+    cfg = model.cfg
+    emb = ngram_rows_for_plan(model, plan)                   # [R, heads*dim] fp32 on X.device
+    key = L.rms(emb @ w["key"].float().t(), w["norm_k"].float(), cfg.norm_eps)
+    val = emb @ w["value"].float().t()
+    d = (key * L.rms(X.float(), w["norm_q"].float(), cfg.norm_eps)).sum(-1, keepdim=True) / math.sqrt(X.shape[-1])
+    gate = torch.sigmoid(torch.sign(d) * torch.sqrt(d.abs().clamp_min(cfg.norm_eps)))
+    return (X.float() + gate * val).to(X.dtype)
