@@ -1,0 +1,231 @@
+#!/usr/bin/env python
+"""Headline benchmark: aggregate decode tokens/s at 4 concurrent streams (plus 1-3 streams, prefill
+tokens/s and TTFT) of the Qwen3-Next-style hybrid MoE (48 layers, hidden 2048, 512 experts top-10,
+vocab 151936) with random-init EXL3 4 bpw weights and synthetic uniform-random prompts.
+
+  python bench.py --gpus N --steps K --warmup W
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+A step is one decode round: every live stream emits one token (greedy).  The device-timed number
+replays the captured round K times between CUDA events; the end-to-end number drives the public
+`LLMEngine.decode_round` API, which copies the round's token ids from pinned host memory to the
+device and reads the sampled ids back every step.  Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_DECODE_4STREAMS = 139.2     # Qwen3.8-Flash-Next, prose, greedy, 4 streams, 1x DGX Spark GB10 (published)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is a Rust binary + sm_121-only CUDA shim with no setup.py/pyproject.toml: "
+                       "`pip install --target baseline/_ref /root/reference` fails (not installable), no Rust toolchain offline",
+    }))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="qwen3next-style")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the named config; a reduced "
+                                                          "count is reported in `config` and is not the headline)")
+    ap.add_argument("--streams", type=int, default=4)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--format", default=None, help="dense | exl3 (default: the config's)")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from spark_engine_b200.config import EngineConfig, get_model_config
+    from spark_engine_b200.models.build import build_random_model, weight_bytes
+    from spark_engine_b200.ops import cuda as cu
+    from spark_engine_b200.serving.engine import LLMEngine
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    kw = {}
+    if args.layers:
+        kw["n_layers"] = args.layers
+    if args.format:
+        kw["weight_format"] = args.format
+    cfg = get_model_config(args.model, **kw)
+    t0 = time.time()
+    W = build_random_model(cfg, dev, seed=0)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+    S = args.streams
+    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not args.no_graphs, prefill_chunk=4096), device=dev, max_seqs=S,
+                    kv_tokens_per_seq=max(4096, 2 * args.prompt))
+    g = torch.Generator().manual_seed(1234 + rank)
+    prompts = torch.randint(0, cfg.vocab, (S, args.prompt), generator=g)
+    pinned_prompts = prompts.to(torch.int32).pin_memory()
+
+    # ---- prefill (TTFT, prefill tok/s): device-timed per stream
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cur, ttft = [], []
+    for s in range(S):
+        torch.cuda.synchronize()
+        ev0.record()
+        lg = eng.prefill(s, pinned_prompts[s].tolist())
+        cur.append(int(torch.argmax(lg)))
+        ev1.record()
+        torch.cuda.synchronize()
+        ttft.append(ev0.elapsed_time(ev1))
+    prefill_tok_s = args.prompt / (min(ttft[1:] or ttft) / 1e3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_decode(n_streams: int, steps: int, warmup: int):
+        slots = list(range(n_streams))
+        ids = [cur[s] for s in slots]
+        for _ in range(warmup):
+            ids = eng.decode_round(slots, ids)
+        # device-timed: K replays of the captured round (inputs stay in their device buffers)
+        pos0 = [eng.model.seqs[s].length for s in slots]
+        key = (tuple(slots), 1, eng._ctx_bucket(max(pos0) + 1))
+        gph = eng.graphs.get(key)
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        ev0.record()
+        if gph is not None:
+            for i in range(steps):
+                gph.replay()
+        else:
+            for i in range(steps):
+                ids = eng.decode_round(slots, ids)
+        ev1.record()
+        barrier()
+        dev_ms = ev0.elapsed_time(ev1) / steps
+        # end to end through the public API: pinned H2D of the ids + D2H of the result each step
+        barrier()
+        t_a = time.perf_counter()
+        for _ in range(steps):
+            ids = eng.decode_round(slots, ids)
+        barrier()
+        e2e_ms = (time.perf_counter() - t_a) * 1e3 / steps
+        clocks = sampler.stop()
+        for s, t in zip(slots, ids):
+            cur[s] = t
+        return dev_ms, e2e_ms, clocks
+
+    cu.reset_launch_count()
+    dev_ms, e2e_ms, clocks = timed_decode(S, args.steps, max(args.warmup, 3))
+    launches_total = cu.launch_count()
+    sweep = {}
+    if args.sweep:
+        for n in range(1, S):
+            d, e, _ = timed_decode(n, args.steps, 3)
+            sweep[str(n)] = {"decode_tok_s": n * 1e3 / d, "e2e_tok_s": n * 1e3 / e, "ms_per_step": d}
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = t.tolist()
+    st = cu.read_status(dev)
+    value = world * S * 1e3 / dev_ms
+    e2e = world * S * 1e3 / e2e_ms
+    full = (args.layers == 0 and args.model == "qwen3next-style" and cfg.weight_format == "exl3")
+    out = {
+        "metric": "aggregate decode tok/s at 4 streams" if S == 4 else f"aggregate decode tok/s at {S} streams",
+        "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / BASELINE_DECODE_4STREAMS, 3) if full and S == 4 else None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.moe.n_experts,
+                   "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
+                   "kv": cfg.kv_dtype, "global_batch": world * S, "seq_len": args.prompt, "streams_per_gpu": S,
+                   "parallelism": f"dp{world}" if world > 1 else "single", "speculation": "none (greedy)",
+                   "cache": "inputs larger than L2 (weights %.1f GB streamed every step)" % (weight_bytes(W) / 1e9),
+                   "full_config": full},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * (3 * S + 4 * S),
+                "d2h_bytes_per_step": 4 * S, "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": launches_total,
+        "prefill_tok_s": round(prefill_tok_s, 1), "ttft_ms": round(statistics.median(ttft), 2),
+        "streams_sweep": sweep, "weight_build_s": round(build_s, 1), "device_status": list(st),
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

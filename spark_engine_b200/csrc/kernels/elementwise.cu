@@ -1,0 +1,166 @@
+// Row-wise elementwise kernels: embedding gather, (add +) RMSNorm, SwiGLU, arg-max, copies.
+// Activations are bf16, the residual stream and norm weights are fp32.  One CTA per row, 16-byte
+// accesses.  Replaces engine-rs/shim/ds41_ops.cu:17-239 (rms_norm*), kda.cu:1036 (rms_rows),
+// shared_gu.cu:38-65 and the ATen row ops of the eager path.
+#include "../common/ptx.cuh"
+
+namespace spark {
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += sh[i];      // fixed order: every thread gets the same bits
+  __syncthreads();
+  return t;
+}
+
+// res[R,H] fp32 (in/out) += delta (bf16 or fp32, optional); out[R,H] bf16 = rmsnorm(res) * w.
+template <typename TD>
+__global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ res, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ out, int H, float eps, int one_plus) {
+  __shared__ float sh[32];
+  const int r = blockIdx.x;
+  float* x = res + static_cast<size_t>(r) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = x[i];
+    if (delta != nullptr) { v += static_cast<float>(delta[static_cast<size_t>(r) * H + i]); x[i] = v; }
+    ss += v * v;
+  }
+  const float tot = block_sum(ss, sh);
+  const float rs = rsqrtf(tot / H + eps);
+  if (out != nullptr)
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float g = one_plus ? 1.f + w[i] : w[i];
+      out[static_cast<size_t>(r) * H + i] = __float2bfloat16(x[i] * rs * g);
+    }
+}
+
+// x bf16 [R,H] -> out bf16 (no residual)
+__global__ void rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                    __nv_bfloat16* __restrict__ out, int H, float eps, int one_plus) {
+  __shared__ float sh[32];
+  const int r = blockIdx.x;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(r) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = __bfloat162float(xr[i]); ss += v * v; }
+  const float rs = rsqrtf(block_sum(ss, sh) / H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float g = one_plus ? 1.f + w[i] : w[i];
+    out[static_cast<size_t>(r) * H + i] = __float2bfloat16(__bfloat162float(xr[i]) * rs * g);
+  }
+}
+
+__global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int H) {
+  const int r = blockIdx.x;
+  const __nv_bfloat16* src = table + static_cast<size_t>(ids[r]) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = __bfloat162float(src[i]);
+}
+
+// gu bf16 [R, 2F] = [gate | up] -> out bf16 [R, F]
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int F, float limit) {
+  const int r = blockIdx.x;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    float g = __bfloat162float(gu[static_cast<size_t>(r) * 2 * F + i]);
+    float u = __bfloat162float(gu[static_cast<size_t>(r) * 2 * F + F + i]);
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    out[static_cast<size_t>(r) * F + i] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+  }
+}
+
+// arg-max per row, ties -> lowest index.  logits fp32 [R, V]; out ids int32 [R], optional max value.
+__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out_id, float* __restrict__ out_val) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int r = blockIdx.x;
+  const float* x = logits + static_cast<size_t>(r) * V;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = x[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (blockDim.x >> 5); ++i)
+      if (sv[i] > best || (sv[i] == best && si[i] < bi)) { best = sv[i]; bi = si[i]; }
+    out_id[r] = bi;
+    if (out_val) out_val[r] = best;
+  }
+}
+
+// out f32 [R,H] = x f32 + add (bf16 or f32): residual add without a norm (last layer).
+template <typename TD>
+__global__ void add_kernel(const TD* __restrict__ delta, float* __restrict__ res, size_t n) {
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i < n) res[i] += static_cast<float>(delta[i]);
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n) {
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i < n) y[i] = __float2bfloat16(x[i]);
+}
+
+// gather rows: out[i, :] = src[idx[i], :]  (bf16, 16-byte vectors; H % 8 == 0)
+__global__ void gather_rows_bf16_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx,
+                                        __nv_bfloat16* __restrict__ out, int H) {
+  const int r = blockIdx.x;
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(idx[r]) * H);
+  uint4* d = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+extern "C" void spark_add_rmsnorm(const void* delta, int delta_f32, float* res, const float* w, void* out, int R, int H,
+                                  float eps, int one_plus, cudaStream_t s) {
+  if (R <= 0) return;
+  int th = H >= 2048 ? 512 : 256;
+  if (delta_f32)
+    add_rmsnorm_kernel<float><<<R, th, 0, s>>>((const float*)delta, res, w, (__nv_bfloat16*)out, H, eps, one_plus);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<R, th, 0, s>>>((const __nv_bfloat16*)delta, res, w, (__nv_bfloat16*)out, H, eps, one_plus);
+}
+extern "C" void spark_rmsnorm_bf16(const void* x, const float* w, void* out, int R, int H, float eps, int one_plus,
+                                   cudaStream_t s) {
+  if (R <= 0) return;
+  rmsnorm_bf16_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)out, H, eps, one_plus);
+}
+extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s) {
+  if (R <= 0) return;
+  embed_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)table, ids, out, H);
+}
+extern "C" void spark_swiglu(const void* gu, void* out, int R, int F, float limit, cudaStream_t s) {
+  if (R <= 0) return;
+  swiglu_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, limit);
+}
+extern "C" void spark_argmax(const float* logits, int R, int V, int* out_id, float* out_val, cudaStream_t s) {
+  if (R <= 0) return;
+  argmax_kernel<<<R, 1024, 0, s>>>(logits, V, out_id, out_val);
+}
+extern "C" void spark_add(const void* delta, int delta_f32, float* res, long n, cudaStream_t s) {
+  if (n <= 0) return;
+  unsigned b = (unsigned)((n + 255) / 256);
+  if (delta_f32) add_kernel<float><<<b, 256, 0, s>>>((const float*)delta, res, (size_t)n);
+  else add_kernel<__nv_bfloat16><<<b, 256, 0, s>>>((const __nv_bfloat16*)delta, res, (size_t)n);
+}
+extern "C" void spark_f32_to_bf16(const float* x, void* y, long n, cudaStream_t s) {
+  if (n <= 0) return;
+  f32_to_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, (__nv_bfloat16*)y, (size_t)n);
+}
+extern "C" void spark_gather_rows_bf16(const void* src, const int* idx, void* out, int R, int H, cudaStream_t s) {
+  if (R <= 0) return;
+  gather_rows_bf16_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)out, H);
+}

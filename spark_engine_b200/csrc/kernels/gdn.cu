@@ -1,0 +1,142 @@
+// Gated-DeltaNet decode / verify / sequential-prefill kernel (one launch per layer):
+//   depthwise causal conv (k=4) + SiLU on q,k,v  ->  L2-norm q,k (q scaled D^-0.5)  ->  per row
+//   S <- e^g S;  v' = beta (v - S k);  S <- S + v' k^T;  o = S q   ->  RMSNorm(o) * w * sigmoid(z).
+// Grid (value head, segment); 128 threads; thread i owns state row S[h, i, :] (D floats) in registers
+// for the whole segment, so decode touches the state once.  Rows of a segment run in order with the
+// oracle's operation order; `commit` = 0 leaves state and conv tails untouched (speculative verify),
+// a later launch with the accepted row counts replays and commits (device-side counts `n_rows`).
+// Conv tails are kept per value head ([slot, 3, Hv, 3D]: that head's q, k and v channels) so that no
+// two CTAs ever write the same tail entry.
+// Reference: engine-rs/shim/qwen_gdn.cu:45-190 (conv/recur kernels), :636-816 (launch shapes).
+#include "../common/ptx.cuh"
+
+namespace spark {
+
+constexpr int GDN_CONV_K = 4;
+
+template <int D>
+__global__ void __launch_bounds__(D)
+gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk*D + 2*Hv*D]  q | k | v | z
+               const __nv_bfloat16* __restrict__ ab, int ldab,       // [R, 2*Hv]  b | a
+               const float* __restrict__ conv_w,                     // [2*Hk*D + Hv*D, 4]
+               const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ norm_w,
+               float* __restrict__ S,                                // [slots, Hv, D, D]
+               float* __restrict__ tail,                             // [slots, 3, Hv, 3*D]
+               const int* __restrict__ seg,                          // [nseg, 4] slot, r0, n, pos0
+               const int* __restrict__ n_rows,                       // optional [nseg]: rows to process
+               __nv_bfloat16* __restrict__ out, int ldo,             // [R, Hv*D]
+               int Hk, int Hv, float eps, int commit) {
+  const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x;
+  const int slot = seg[sg * 4 + 0], r0 = seg[sg * 4 + 1];
+  int n = seg[sg * 4 + 2];
+  if (n_rows != nullptr) n = min(n, n_rows[sg]);
+  if (n <= 0) return;
+  const int hk = h / (Hv / Hk);
+  const int cq = hk * D + i, ck = Hk * D + hk * D + i, cv = 2 * Hk * D + h * D + i;   // conv channels
+  const int zc = 2 * Hk * D + Hv * D + h * D + i;                                       // z column
+  __shared__ float sq[D], sk[D], red[2][D / 32];
+  __shared__ float sred[D / 32];
+
+  float s[D];
+  float* Srow = S + ((static_cast<size_t>(slot) * Hv + h) * D + i) * D;
+#pragma unroll
+  for (int j = 0; j < D; j += 4) {
+    float4 t = *reinterpret_cast<const float4*>(Srow + j);
+    s[j] = t.x; s[j + 1] = t.y; s[j + 2] = t.z; s[j + 3] = t.w;
+  }
+  // conv history (pre-activation inputs of the 3 previous positions), oldest first
+  float hq[3], hk_[3], hv[3];
+  float* tl = tail + (static_cast<size_t>(slot) * 3 * Hv + h) * 3 * D;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const float* t = tl + static_cast<size_t>(j) * Hv * 3 * D;
+    hq[j] = t[i]; hk_[j] = t[D + i]; hv[j] = t[2 * D + i];
+  }
+  const float wq[4] = {conv_w[cq * 4], conv_w[cq * 4 + 1], conv_w[cq * 4 + 2], conv_w[cq * 4 + 3]};
+  const float wk[4] = {conv_w[ck * 4], conv_w[ck * 4 + 1], conv_w[ck * 4 + 2], conv_w[ck * 4 + 3]};
+  const float wv[4] = {conv_w[cv * 4], conv_w[cv * 4 + 1], conv_w[cv * 4 + 2], conv_w[cv * 4 + 3]};
+  const float a_neg = -__expf(A_log[h]);
+  const float dtb = dt_bias[h];
+  const float nw = norm_w[i];
+  const float qscale = rsqrtf(static_cast<float>(D));
+  const int warp = i >> 5, lane = i & 31;
+
+  for (int t = 0; t < n; ++t) {
+    const __nv_bfloat16* pr = proj + static_cast<size_t>(r0 + t) * ldp;
+    const float xq = __bfloat162float(pr[cq]), xk = __bfloat162float(pr[ck]), xv = __bfloat162float(pr[cv]);
+    float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
+    float k = hk_[0] * wk[0] + hk_[1] * wk[1] + hk_[2] * wk[2] + xk * wk[3];
+    float v = hv[0] * wv[0] + hv[1] * wv[1] + hv[2] * wv[2] + xv * wv[3];
+    hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = xq;
+    hk_[0] = hk_[1]; hk_[1] = hk_[2]; hk_[2] = xk;
+    hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = xv;
+    q = q / (1.f + __expf(-q)); k = k / (1.f + __expf(-k)); v = v / (1.f + __expf(-v));
+    // L2 norms of q and k over the D channels of this head
+    float q2 = warp_sum(q * q), k2 = warp_sum(k * k);
+    if (lane == 0) { red[0][warp] = q2; red[1][warp] = k2; }
+    __syncthreads();
+    q2 = 0.f; k2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) { q2 += red[0][w]; k2 += red[1][w]; }
+    sq[i] = q * rsqrtf(q2 + eps) * qscale;
+    sk[i] = k * rsqrtf(k2 + eps);
+    __syncthreads();
+    const float bl = __bfloat162float(ab[static_cast<size_t>(r0 + t) * ldab + h]);
+    const float al = __bfloat162float(ab[static_cast<size_t>(r0 + t) * ldab + Hv + h]);
+    const float beta = 1.f / (1.f + __expf(-bl));
+    const float xa = al + dtb;
+    const float sp = xa > 20.f ? xa : log1pf(__expf(xa));          // softplus
+    const float dec = __expf(a_neg * sp);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < D; ++j) { s[j] *= dec; dot = fmaf(s[j], sk[j], dot); }
+    const float vp = beta * (v - dot);
+    float o = 0.f;
+#pragma unroll
+    for (int j = 0; j < D; ++j) { s[j] = fmaf(vp, sk[j], s[j]); o = fmaf(s[j], sq[j], o); }
+    // RMSNorm over the head's D outputs, gate with sigmoid(z)
+    float o2 = warp_sum(o * o);
+    if (lane == 0) sred[warp] = o2;
+    __syncthreads();
+    o2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) o2 += sred[w];
+    const float z = __bfloat162float(pr[zc]);
+    const float res = o * rsqrtf(o2 / D + eps) * nw / (1.f + __expf(-z));
+    out[static_cast<size_t>(r0 + t) * ldo + h * D + i] = __float2bfloat16(res);
+    __syncthreads();     // sq/sk/red reused by the next row
+  }
+  if (commit) {
+#pragma unroll
+    for (int j = 0; j < D; j += 4) *reinterpret_cast<float4*>(Srow + j) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      float* t = tl + static_cast<size_t>(j) * Hv * 3 * D;
+      t[i] = hq[j]; t[D + i] = hk_[j]; t[2 * D + i] = hv[j];
+    }
+  }
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+extern "C" int spark_gdn_seq(const void* proj, int ldp, const void* ab, int ldab, const float* conv_w,
+                             const float* A_log, const float* dt_bias, const float* norm_w, float* S, float* tail,
+                             const int* seg, const int* n_rows, int nseg, void* out, int ldo, int Hk, int Hv, int D,
+                             float eps, int commit, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  dim3 grid(Hv, nseg);
+  if (D == 128)
+    gdn_seq_kernel<128><<<grid, 128, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+                                             dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+  else if (D == 64)
+    gdn_seq_kernel<64><<<grid, 64, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+  else if (D == 32)
+    gdn_seq_kernel<32><<<grid, 32, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+  else
+    return -5;
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

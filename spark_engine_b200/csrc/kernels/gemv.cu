@@ -1,0 +1,127 @@
+// Skinny GEMV for decode / verify rows:  y[R,N] = x[R,K] W[N,K]^T with R <= 16, bf16 weights.
+// Bandwidth-bound: each warp streams two weight rows with 16-byte loads while the activation rows
+// sit in shared memory; every output is produced by ONE warp with a fixed reduction order, so a row's
+// result does not depend on how many other rows are in the batch (batch-invariant decode, as
+// engine-rs/src/forward.rs:536-544 requires) and two runs are bitwise equal.
+// The `item` dimension (blockIdx.y) turns it into the MoE decode GEMV: item i multiplies its own
+// activation row by expert pair_expert[i]'s matrix.
+// Replaces engine-rs/shim/gemv.cu:8-72, qwen_f16.cu:14-258, dataflow.cu:772 bf16w_rows.
+#include "../common/ptx.cuh"
+
+namespace spark {
+
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_COLS = 2;      // output columns per warp
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+
+// act: 0 none; 1 = input is [gate | up] (2K wide), x := swiglu(gate, up) computed while staging.
+template <int RB, typename TO>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
+                 long long expert_stride, int ldw, TO* __restrict__ y, int ldy, int rows_per_item, int N, int K,
+                 const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit) {
+  extern __shared__ __align__(16) uint8_t smem_gemv[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [RB][K]
+  const int item = blockIdx.y;
+  const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
+  const __nv_bfloat16* Wb = W + (pair_expert ? static_cast<long long>(pair_expert[item]) * expert_stride : 0);
+  const int R = rows_per_item;
+  // stage activations (zero rows beyond R)
+  for (int i = threadIdx.x; i < RB * K; i += blockDim.x) {
+    const int r = i / K, k = i - r * K;
+    float v = 0.f;
+    if (r < R) {
+      const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
+      if (act == 1) {
+        float g = __bfloat162float(xr[k]), u = __bfloat162float(xr[K + k]);
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        v = g / (1.f + __expf(-g)) * u;
+      } else {
+        v = __bfloat162float(xr[k]);
+      }
+    }
+    xs[i] = __float2bfloat16(v);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * GEMV_WARPS + warp) * GEMV_COLS;
+  if (n0 >= N) return;
+  const bool two = (n0 + 1) < N;
+  const uint4* w0 = reinterpret_cast<const uint4*>(Wb + static_cast<size_t>(n0) * ldw);
+  const uint4* w1 = reinterpret_cast<const uint4*>(Wb + static_cast<size_t>(two ? n0 + 1 : n0) * ldw);
+  float acc0[RB], acc1[RB];
+#pragma unroll
+  for (int r = 0; r < RB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+  const int KV = K >> 3;                        // 16-byte vectors per row
+#pragma unroll 2
+  for (int kv = lane; kv < KV; kv += 32) {
+    float a[8], b[8];
+    unpack8(__ldg(w0 + kv), a);
+    unpack8(__ldg(w1 + kv), b);
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      float xv[8];
+      unpack8(*reinterpret_cast<const uint4*>(xs + r * K + kv * 8), xv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { acc0[r] = fmaf(a[i], xv[i], acc0[r]); acc1[r] = fmaf(b[i], xv[i], acc1[r]); }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RB; ++r) { acc0[r] = warp_sum(acc0[r]); acc1[r] = warp_sum(acc1[r]); }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      if (r < R) {
+        TO* yr = y + static_cast<size_t>(item * rows_per_item + r) * ldy;
+        yr[n0] = static_cast<TO>(acc0[r]);
+        if (two) yr[n0 + 1] = static_cast<TO>(acc1[r]);
+      }
+    }
+  }
+}
+
+template <int RB, typename TO>
+static int launch_gemv(const void* x, int ldx, const void* W, long long es, int ldw, void* y, int ldy, int items,
+                       int rows, int N, int K, const int* pe, const int* pr, int act, float limit, cudaStream_t s) {
+  auto kern = gemv_bf16_kernel<RB, TO>;
+  const int smem = RB * K * 2;
+  if (smem > 48 * 1024) {
+    static int set_for = 0;
+    if (smem > set_for) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set_for = 200 * 1024; }
+  }
+  if (smem > 200 * 1024) return -6;
+  dim3 grid((N + GEMV_WARPS * GEMV_COLS - 1) / (GEMV_WARPS * GEMV_COLS), items);
+  kern<<<grid, GEMV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, es, ldw, (TO*)y, ldy,
+                                            rows, N, K, pe, pr, act, limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+// items x rows_per_item rows; K % 8 == 0; out_f32 selects fp32 or bf16 output.
+extern "C" int spark_gemv_bf16(const void* x, int ldx, const void* W, long long expert_stride, int ldw, void* y, int ldy,
+                               int items, int rows_per_item, int N, int K, const int* pair_expert, const int* pair_row,
+                               int act, float limit, int out_f32, cudaStream_t s) {
+  if (items <= 0 || rows_per_item <= 0) return 0;
+  if (K % 8 || rows_per_item > 16) return -5;
+#define SPARK_GEMV_CASE(RB)                                                                                          \
+  if (rows_per_item <= RB)                                                                                           \
+    return out_f32 ? launch_gemv<RB, float>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N, K,       \
+                                            pair_expert, pair_row, act, limit, s)                                    \
+                   : launch_gemv<RB, __nv_bfloat16>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N,  \
+                                                    K, pair_expert, pair_row, act, limit, s);
+  SPARK_GEMV_CASE(1)
+  SPARK_GEMV_CASE(2)
+  SPARK_GEMV_CASE(4)
+  SPARK_GEMV_CASE(8)
+  SPARK_GEMV_CASE(16)
+#undef SPARK_GEMV_CASE
+  return -5;
+}

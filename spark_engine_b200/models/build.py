@@ -1,0 +1,147 @@
+"""Random-init models generated directly on the device in the serving weight formats.
+
+Large configs (tens of billions of parameters) are never materialised in fp32: EXL3 tensors are
+random trellis words + sign/scale vectors, MXFP4 random nibbles + E8M0 scales, FP8 random e4m3 +
+block scales, everything else bf16 N(0, 0.02).  The formats follow the checkpoints the reference
+serves (EXL3: engine-rs/src/exl3.rs, qwen/load.rs:106-217; MXFP4/FP8: ds41/load.rs:116-160,331-342).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..quant import formats as Q
+
+
+class _DevInit:
+    def __init__(self, device, seed: int, fmt: str, bits: int, std: float = 0.02):
+        self.device, self.fmt, self.bits, self.std = device, fmt, bits, std
+        self.g = torch.Generator(device=device)
+        self.g.manual_seed(seed)
+        self.n = 0
+
+    def _seed(self):
+        self.n += 1
+        return 1000003 * self.n + 17
+
+    def big(self, n, k, experts=0, kind="dense"):
+        """A large projection [n, k] (or experts x [n, k]) in the model's weight format."""
+        fmt = self.fmt
+        if fmt == "exl3" and n % 128 == 0 and k % 128 == 0:
+            return Q.random_exl3(n, k, self.bits, experts, self.std, self._seed(), self.device)
+        if fmt == "mx" and k % 128 == 0 and n % 128 == 0:
+            if kind == "expert":
+                return Q.random_mxfp4(n, k, experts, self.std, self._seed(), self.device)
+            return Q.random_fp8_block(n, k, experts, self.std, self._seed(), self.device)
+        return self.mat(*(((experts,) if experts else ()) + (n, k)))
+
+    def mat(self, *shape):
+        return (torch.randn(*shape, device=self.device, generator=self.g) * self.std).to(torch.bfloat16)
+
+    def f32(self, *shape, lo=None, hi=None, val=None):
+        if val is not None:
+            return torch.full(shape, val, device=self.device, dtype=torch.float32)
+        if lo is not None:
+            return torch.rand(*shape, device=self.device, generator=self.g) * (hi - lo) + lo
+        return torch.randn(*shape, device=self.device, generator=self.g) * self.std
+
+
+def _mix(cfg: ModelConfig, it: _DevInit, kind: str) -> dict:
+    H = cfg.hidden
+    if kind == "gdn":
+        c = cfg.gdn
+        nq, nv = c.n_k_heads * c.head_dim, c.n_v_heads * c.head_dim
+        return {"in": it.big(2 * nq + 2 * nv, H), "ab": it.mat(2 * c.n_v_heads, H),
+                "conv": it.f32(2 * nq + nv, c.conv_k, lo=-0.5, hi=0.5),
+                "A_log": torch.log(it.f32(c.n_v_heads, lo=1.0, hi=8.0)), "dt_bias": it.f32(c.n_v_heads, lo=-1.0, hi=1.0),
+                "norm": it.f32(c.head_dim, val=1.0), "o": it.big(H, nv)}
+    if kind == "attn":
+        c = cfg.attn
+        nq = c.n_q_heads * c.head_dim * (2 if c.gated else 1)
+        nkv = c.n_kv_heads * c.head_dim
+        nidx = (c.idx_heads + 1) * c.idx_dim if c.sparse_topk_blocks else 0
+        w = {"qkv": it.big(nq + 2 * nkv + nidx, H), "o": it.big(H, c.n_q_heads * c.head_dim)}
+        if c.qk_norm:
+            w["q_norm"], w["k_norm"] = it.f32(c.head_dim), it.f32(c.head_dim)
+        if c.sparse_topk_blocks:
+            w["iq_norm"], w["ik_norm"] = it.f32(c.idx_dim), it.f32(c.idx_dim)
+        return w
+    if kind == "kda":
+        c = cfg.kda
+        n, r = c.n_heads * c.head_dim, c.gate_rank
+        return {"in": it.big(3 * n, H), "conv": it.f32(3 * n, c.conv_k, lo=-0.5, hi=0.5),
+                "lr_a": it.mat(2 * r + c.n_heads, H), "f_b": it.f32(n, r) * 10, "g_b": it.f32(n, r) * 10,
+                "A_log": torch.log(it.f32(c.n_heads, lo=1.0, hi=4.0)), "dt_bias": it.f32(n, lo=-1.0, hi=1.0),
+                "o_norm": it.f32(c.head_dim, val=1.0), "o": it.big(H, n)}
+    if kind == "mla":
+        c = cfg.mla
+        idx_rows = 2 * c.idx_dim + c.idx_heads
+        w = {"a": it.mat(c.q_lora + c.kv_lora + c.rope_dim + idx_rows, H),
+             "q_a_norm": it.f32(c.q_lora, val=1.0), "kv_a_norm": it.f32(c.kv_lora, val=1.0),
+             "q_b": it.mat(c.n_heads * (c.head_dim + c.rope_dim) + c.idx_heads * c.idx_dim, c.q_lora),
+             "kv_b": it.mat(c.n_heads * 2 * c.head_dim, c.kv_lora),
+             "k_ln_w": it.f32(c.idx_dim, val=1.0), "k_ln_b": it.f32(c.idx_dim, val=0.0),
+             "ape": it.f32(c.pool, c.idx_dim), "o": it.big(H, c.n_heads * c.head_dim)}
+        if c.sink:
+            w["sink"] = it.f32(c.n_heads) * 10
+        return w
+    raise ValueError(kind)
+
+
+def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool) -> dict:
+    c, H = cfg.moe, cfg.hidden
+    if dense:
+        return {"dense_gu": it.big(2 * c.dense_ffn, H), "dense_down": it.big(H, c.dense_ffn)}
+    Fs = c.shared_ffn or c.ffn * c.n_shared
+    w = {"gate": it.mat(c.n_experts + (1 if c.shared_gate else 0), H),
+         "w_gu": it.big(2 * c.ffn, H, c.n_experts, kind="expert"),
+         "w_down": it.big(H, c.ffn, c.n_experts, kind="expert")}
+    if c.router != "softmax":
+        w["bias"] = it.f32(c.n_experts)
+    if c.n_shared:
+        w["s_gu"], w["s_down"] = it.big(2 * Fs, H), it.big(H, Fs)
+    return w
+
+
+def _layer(cfg: ModelConfig, it: _DevInit, i: int, kind: str) -> dict:
+    return {"type": kind, "in_norm": it.f32(cfg.hidden, val=1.0), "post_norm": it.f32(cfg.hidden, val=1.0),
+            "mix": _mix(cfg, it, kind), "mlp": _mlp(cfg, it, i < cfg.moe.dense_layers)}
+
+
+def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0) -> dict:
+    """Nested weight dict on `device` in cfg.weight_format (dense | exl3 | mx)."""
+    it = _DevInit(device, seed, cfg.weight_format, cfg.exl3_bits)
+    W = {"embed": it.mat(cfg.vocab, cfg.hidden), "final_norm": it.f32(cfg.hidden, val=1.0),
+         "lm_head": it.mat(cfg.vocab, cfg.hidden),
+         "layers": [_layer(cfg, it, i, cfg.layer_types[i]) for i in range(cfg.n_layers)]}
+    if cfg.mtp_layers:
+        kind = "attn" if cfg.family == "hybrid" else "mla"
+        W["mtp"] = {"fc": it.mat(cfg.hidden, 2 * cfg.hidden), "norm_e": it.f32(cfg.hidden, val=1.0),
+                    "norm_h": it.f32(cfg.hidden, val=1.0), "final_norm": it.f32(cfg.hidden, val=1.0),
+                    "layers": [_layer(cfg, it, cfg.n_layers, kind) for _ in range(cfg.mtp_layers)]}
+    if cfg.ngram_layers:
+        W["ngram_table"] = it.mat(cfg.ngram_rows, cfg.ngram_dim)
+        D = cfg.ngram_dim * cfg.ngram_heads
+        for i in cfg.ngram_layers:
+            W["layers"][i]["ngram"] = {"key": it.mat(cfg.hidden, D), "value": it.mat(cfg.hidden, D),
+                                       "norm_k": it.f32(cfg.hidden, val=1.0), "norm_q": it.f32(cfg.hidden, val=1.0)}
+    return W
+
+
+def weight_bytes(W) -> int:
+    n = 0
+
+    def rec(x):
+        nonlocal n
+        if isinstance(x, dict):
+            for v in x.values():
+                rec(v)
+        elif isinstance(x, list):
+            for v in x:
+                rec(v)
+        elif isinstance(x, Q.QuantWeight):
+            n += x.nbytes()
+        elif isinstance(x, torch.Tensor):
+            n += x.numel() * x.element_size()
+    rec(W)
+    return n

@@ -55,7 +55,12 @@ class GdnMixer:
         self.nv = c.n_v_heads * c.head_dim
         self.C = 2 * self.nq + self.nv
         self.S = torch.zeros(n_slots, c.n_v_heads, c.head_dim, c.head_dim, device=device, dtype=torch.float32)
-        self.tail = torch.zeros(n_slots, c.conv_k - 1, self.C, device=device, dtype=torch.float32)
+        # kernels keep conv tails per value head ([slot, 3, Hv, 3D]) so no two CTAs share an entry
+        self.kernel_layout = ops.use_kernels(self.S)
+        if self.kernel_layout:
+            self.tail = torch.zeros(n_slots, c.conv_k - 1, c.n_v_heads, 3 * c.head_dim, device=device, dtype=torch.float32)
+        else:
+            self.tail = torch.zeros(n_slots, c.conv_k - 1, self.C, device=device, dtype=torch.float32)
         self.pending = None
 
     def reset(self, slot: int):
@@ -560,7 +565,7 @@ class Model:
             a = mix.forward(h, plan, self.seqs, commit)
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps)
             m = mlp.forward(h)
-            return X + m
+            return ops.residual_add(X, m)
         if cfg.hc_kind == "gated":
             post, h = ops.hc_gated_mix(X, lw["hc_mix"], cfg.norm_eps)
             X = X + post.unsqueeze(-1).to(X.dtype) * mix.forward(h, plan, self.seqs, commit).unsqueeze(1)
@@ -572,7 +577,7 @@ class Model:
         return ops.mhc_post(X, mlp.forward(h), post, comb)
 
     @torch.no_grad()
-    def forward(self, plan: Plan, commit: bool = True, want_hidden: bool = False):
+    def forward(self, plan: Plan, commit: bool = True, want_hidden: bool = False, graph_mode: bool = False):
         """Run all layers over the plan's rows.  Returns logits [len(plan.logit_rows), vocab].
         With commit=False no linear-attention state nor sequence length changes: call
         `commit(accepted)` afterwards."""
@@ -595,10 +600,12 @@ class Model:
             hn = ops.rmsnorm(X, W["final_norm"], cfg.norm_eps)
         self.hidden_out = X
         self._pending_plan = None if commit else plan
-        if commit:
+        if commit and not graph_mode:       # under a captured graph the engine tracks lengths itself
             for s in plan.segs:
                 self.seqs[s.slot].length = s.pos0 + s.n
-        return ops.linear(hn[plan.logit_rows], W["lm_head"]).float()
+        if plan.logit_rows.shape[0] != hn.shape[0]:
+            hn = hn[plan.logit_rows]
+        return ops.lm_head(hn, W["lm_head"])
 
     def commit(self, accepted: List[List[int]]):
         """accepted[i]: segment-local rows of segment i that become part of the sequence, a path
@@ -627,9 +634,9 @@ class Model:
             h, X = ops.add_rmsnorm(None, X, lw["in_norm"], cfg.norm_eps)
             a = mix.forward(h, plan, self.mtp_seqs(), True)
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps)
-            X = X + mlp.forward(h)
+            X = ops.residual_add(X, mlp.forward(h))
         self.mtp_hidden = X
-        return ops.linear(ops.rmsnorm(X, M["final_norm"], cfg.norm_eps)[plan.logit_rows], self.W["lm_head"]).float()
+        return ops.lm_head(ops.rmsnorm(X, M["final_norm"], cfg.norm_eps)[plan.logit_rows], self.W["lm_head"])
 
     def mtp_seqs(self):
         return self.seqs

@@ -200,3 +200,26 @@ def count_params(W) -> int:
         return t
     map_weights(W, add)
     return n
+
+
+FP32_KEYS = {"conv", "ape", "norm", "scale", "base", "f_b", "g_b"}
+
+
+def to_device(W, device, dtype=torch.bfloat16):
+    """Move a nested weight dict to `device`: matrices in `dtype`, vectors / conv taps / norm and gate
+    parameters in fp32, quantised weights as they are."""
+    from ..quant.formats import QuantWeight
+
+    def rec(node, key=None):
+        if isinstance(node, dict):
+            return {k: rec(v, k) for k, v in node.items()}
+        if isinstance(node, list):
+            return [rec(v, key) for v in node]
+        if isinstance(node, QuantWeight):
+            return node.to(device)
+        if isinstance(node, torch.Tensor):
+            if node.dim() <= 1 or key in FP32_KEYS:
+                return node.to(device=device, dtype=torch.float32).contiguous()
+            return node.to(device=device, dtype=dtype).contiguous()
+        return node
+    return rec(W)

@@ -42,7 +42,30 @@ def set_fallback(on: bool):
 
 # ----------------------------------------------------------------------------- basic ops
 def embed(table: torch.Tensor, ids: torch.Tensor, dtype) -> torch.Tensor:
+    """Token embedding rows.  On the device the residual stream is fp32 (activations bf16)."""
+    if use_kernels(table):
+        return cuda_ops().embed(table, ids.to(torch.int32))
     return table[ids].to(dtype)
+
+
+def residual_add(res: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    if use_kernels(res) and res.dtype == torch.float32 and res.dim() == 2:
+        return cuda_ops().residual_add(res, delta)
+    return res + delta.to(res.dtype)
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Greedy token per row (ties -> lowest id), int32."""
+    if use_kernels(logits):
+        return cuda_ops().argmax(logits)
+    return torch.argmax(logits, -1).to(torch.int32)
+
+
+def lm_head(h: torch.Tensor, w) -> torch.Tensor:
+    """Logits in fp32."""
+    if use_kernels(h) and not isinstance(w, QuantWeight):
+        return cuda_ops().dense_linear(h, w, out_f32=True)
+    return linear(h, w).float()
 
 
 def linear(x: torch.Tensor, w) -> torch.Tensor:

@@ -1,0 +1,528 @@
+"""ctypes bindings of libspark_kernels.so and the CUDA implementations of the ops.
+
+The kernels take raw pointers, shapes and a stream (C ABI); this module owns the glue: output
+allocation, persistent scratch (so captured CUDA graphs replay against fixed addresses), the device
+status word that bounded waits report to, and dispatch between GEMV-class (<= 16 rows) and
+GEMM-class (tcgen05) kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from typing import Optional
+
+import torch
+
+from ..quant.formats import Exl3Weight, Fp8BlockWeight, Mxfp4Weight, QuantWeight
+
+_LIB = None
+_here = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_here), "_lib", "libspark_kernels.so")
+
+vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+_SIGS = {
+    "spark_gemm_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+    "spark_gemm_bf16_swiglu": [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
+    "spark_gemm_grouped_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, f32, i32, vp, vp],
+    "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp],
+    "spark_add_rmsnorm": [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp],
+    "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
+    "spark_embed": [vp, vp, vp, i32, i32, vp],
+    "spark_swiglu": [vp, vp, i32, i32, f32, vp],
+    "spark_argmax": [vp, i32, i32, vp, vp, vp],
+    "spark_add": [vp, i32, vp, C.c_long, vp],
+    "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
+    "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
+    "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
+                        vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
+    "spark_attn_decode": [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
+                          f32, vp, vp],
+    "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp],
+    "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
+    "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp],
+    "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                        f32, i32, vp],
+    "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp],
+    "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
+}
+
+
+# kernels launched by one call of each entry point (for the launch counter)
+_KERNELS_PER_CALL = {"spark_attn_decode": 2, "spark_moe_sort": 3}
+_launches = 0
+
+
+class _Counting:
+    """Proxy over the shared library that counts kernel launches made through it."""
+
+    def __init__(self, dll):
+        self._dll = dll
+        self._fns = {}
+
+    def __getattr__(self, name):
+        fn = self._fns.get(name)
+        if fn is None:
+            raw = getattr(self._dll, name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*a, _raw=raw, _n=n):
+                global _launches
+                _launches += _n
+                return _raw(*a)
+            self._fns[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def add_launches(n: int):
+    global _launches
+    _launches += n
+
+
+def reset_launch_count():
+    global _launches
+    _launches = 0
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: run `python -m spark_engine_b200.build` (the CUDA kernels are required "
+                "on a GPU; there is no silent eager fallback)")
+        dll = C.CDLL(LIB_PATH)
+        _LIB = _Counting(dll)
+        for name, sig in _SIGS.items():
+            fn = getattr(dll, name, None)
+            if fn is not None:
+                fn.argtypes = sig
+                fn.restype = i32 if name not in ("spark_add_rmsnorm", "spark_rmsnorm_bf16", "spark_embed", "spark_swiglu",
+                                                 "spark_argmax", "spark_add", "spark_f32_to_bf16",
+                                                 "spark_gather_rows_bf16") else None
+    return _LIB
+
+
+def P(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str):
+    if rc:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+# ----------------------------------------------------------------------------- persistent buffers
+_status = {}
+_scratch = {}
+_retired = []
+
+
+def status_word(device) -> torch.Tensor:
+    """int32[4] device status: kernels whose bounded waits run out write {code, detail...} here."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def read_status(device) -> tuple:
+    st = status_word(device).tolist()
+    return tuple(st)
+
+
+def clear_status(device):
+    status_word(device).zero_()
+
+
+def scratch(name: str, numel: int, dtype, device, zero: bool = False) -> torch.Tensor:
+    """Persistent scratch keyed by name (grows, never shrinks): fixed addresses for graph replay."""
+    key = (name, dtype, str(device))
+    t = _scratch.get(key)
+    if t is None or t.numel() < numel:
+        if t is not None:
+            _retired.append(t)      # captured graphs may still point at the old buffer: keep it alive
+        t = (torch.zeros if zero else torch.empty)(max(numel, 1), dtype=dtype, device=device)
+        _scratch[key] = t
+    return t
+
+
+def scratch_bytes() -> int:
+    return sum(t.numel() * t.element_size() for t in _scratch.values())
+
+
+# ----------------------------------------------------------------------------- dense linear
+def _as_bf16(x):
+    return x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out_f32: bool = False, fmt: int = 1) -> torch.Tensor:
+    """C[M,N] = A[M,K] B[N,K]^T on tcgen05.  fmt 1 = bf16 operands, 0 = fp16 operands."""
+    M, K = a.shape
+    N = b.shape[0]
+    assert a.stride(1) == 1 and b.stride(1) == 1 and K % 8 == 0
+    c = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    rc = lib().spark_gemm_bf16(P(a), P(b), P(c), M, N, K, a.stride(0), b.stride(0), N, int(out_f32), fmt,
+                               P(status_word(a.device)), stream())
+    check(rc, "spark_gemm_bf16")
+    return c
+
+
+def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0, out_f32=False,
+              expert_stride=0, n=None, k=None):
+    rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
+    n = n if n is not None else w.shape[-2]
+    k = k if k is not None else w.shape[-1]
+    y = torch.empty(items * rows_per_item, n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    rc = lib().spark_gemv_bf16(P(x), x.stride(0), P(w), expert_stride, k, P(y), n, items, rows_per_item, n, k,
+                               P(pair_expert), P(pair_row), act, float(limit), int(out_f32), stream())
+    check(rc, "spark_gemv_bf16")
+    return y
+
+
+def dense_linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+    x = _as_bf16(x)
+    if w.dtype != torch.bfloat16:
+        raise TypeError("dense weights must be bf16 on the device")
+    R = x.shape[0]
+    if R <= 16:
+        return gemv_bf16(x.contiguous(), w, out_f32=out_f32)
+    return gemm_bf16(x.contiguous(), w, out_f32)
+
+
+# ----------------------------------------------------------------------------- EXL3
+def _pick_slices(K: int, N: int, items: int) -> int:
+    """K-slices so that the grid covers the GPU about twice; (K/128) % S == 0 and slice <= 2048."""
+    blocks = K // 128
+    best = 1
+    for s in range(1, blocks + 1):
+        if blocks % s:
+            continue
+        if K // s > 2048:
+            continue
+        best = s
+        if (N // 128) * s * items >= 296:
+            break
+    if K // best > 2048:
+        best = blocks
+    return best
+
+
+def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0,
+              out_f32=False):
+    assert w.bits == 4, "the GEMV kernel handles 4 bpw"
+    rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
+    K, N = w.k, w.n
+    S = _pick_slices(K, N, items)
+    dev = x.device
+    part = scratch("exl3_partial", items * S * 16 * N, torch.float32, dev)
+    cnt = scratch("exl3_counters", items * (N // 128), torch.int32, dev, zero=True)
+    y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+    tw = (K // 16) * (N // 16) * 32
+    es = (tw, K, N) if w.experts else (0, 0, 0)
+    rc = lib().spark_exl3_gemv(P(x), x.stride(0), P(w.trellis), P(w.suh), P(w.svh), es[0], es[1], es[2], P(y), N,
+                               int(out_f32), P(part), P(cnt), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
+                               act, float(limit), 0 if w.kind == "mul1" else 1, stream())
+    check(rc, "spark_exl3_gemv")
+    return y
+
+
+def exl3_reconstruct(w: Exl3Weight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inner codebook weights as fp16 [.., N, K] (K-major B operand)."""
+    E = w.trellis.shape[0] if w.experts else 1
+    if out is None:
+        out = torch.empty((E, w.n, w.k) if w.experts else (w.n, w.k), dtype=torch.float16, device=w.trellis.device)
+    tw = (w.k // 16) * (w.n // 16) * 64      # int16 elements per expert
+    tr = w.trellis.view(-1)
+    o = out.view(-1)
+    for e in range(E):
+        rc = lib().spark_exl3_reconstruct(tr[e * tw:].data_ptr(), o[e * w.n * w.k:].data_ptr(), w.k, w.n,
+                                          0 if w.kind == "mul1" else 1, stream())
+        check(rc, "spark_exl3_reconstruct")
+    return out
+
+
+def exl3_had_rows(x, scale, post: bool, row_expert=None, expert_stride=0):
+    R, Cn = x.shape
+    y = torch.empty(R, Cn, dtype=torch.bfloat16 if post else torch.float16, device=x.device)
+    rc = lib().spark_exl3_had_rows(P(x), x.stride(0), P(scale), P(y), Cn, R, Cn, int(post), P(row_expert), stream(),
+                                   expert_stride)
+    check(rc, "spark_exl3_had_rows")
+    return y
+
+
+def exl3_linear(x, w: Exl3Weight):
+    x = _as_bf16(x).contiguous()
+    if x.shape[0] <= 16:
+        return exl3_gemv(x, w)
+    xh = exl3_had_rows(x, w.suh, post=False)
+    wt = exl3_reconstruct(w, scratch("exl3_recon", w.n * w.k, torch.float16, x.device)[: w.n * w.k].view(w.n, w.k))
+    acc = gemm_bf16(xh, wt, out_f32=True, fmt=0)
+    return exl3_had_rows(acc, w.svh, post=True)
+
+
+def quant_linear(x, w: QuantWeight):
+    if isinstance(w, Exl3Weight):
+        return exl3_linear(x, w)
+    from . import mx
+    return mx.quant_linear(x, w)
+
+
+# ----------------------------------------------------------------------------- elementwise
+def add_rmsnorm(delta, res, w, eps, one_plus=False):
+    R, H = res.shape
+    assert res.dtype == torch.float32 and res.is_contiguous()
+    out = torch.empty(R, H, dtype=torch.bfloat16, device=res.device)
+    if delta is not None:
+        delta = delta.contiguous()
+    lib().spark_add_rmsnorm(P(delta), int(delta is not None and delta.dtype == torch.float32), P(res), P(w), P(out), R, H,
+                            float(eps), int(one_plus), stream())
+    return out, res
+
+
+def rmsnorm(x, w, eps, one_plus=False):
+    R, H = x.shape
+    out = torch.empty(R, H, dtype=torch.bfloat16, device=x.device)
+    x = x.contiguous()
+    if x.dtype == torch.float32:
+        lib().spark_add_rmsnorm(None, 0, P(x), P(w), P(out), R, H, float(eps), int(one_plus), stream())
+    else:
+        lib().spark_rmsnorm_bf16(P(x), P(w), P(out), R, H, float(eps), int(one_plus), stream())
+    return out
+
+
+def embed(table, ids32):
+    R, H = ids32.shape[0], table.shape[1]
+    out = torch.empty(R, H, dtype=torch.float32, device=table.device)
+    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream())
+    return out
+
+
+def swiglu(gu, limit=0.0):
+    R, F2 = gu.shape
+    out = torch.empty(R, F2 // 2, dtype=torch.bfloat16, device=gu.device)
+    lib().spark_swiglu(P(gu.contiguous()), P(out), R, F2 // 2, float(limit), stream())
+    return out
+
+
+def residual_add(res, delta):
+    lib().spark_add(P(delta.contiguous()), int(delta.dtype == torch.float32), P(res), res.numel(), stream())
+    return res
+
+
+def argmax(logits):
+    R, V = logits.shape
+    ids = torch.empty(R, dtype=torch.int32, device=logits.device)
+    lib().spark_argmax(P(logits.contiguous()), R, V, P(ids), None, stream())
+    return ids
+
+
+def gather_rows(src, idx32):
+    R, H = idx32.shape[0], src.shape[1]
+    out = torch.empty(R, H, dtype=torch.bfloat16, device=src.device)
+    lib().spark_gather_rows_bf16(P(src), P(idx32), P(out), R, H, stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- MoE
+ROUTER_KIND = {"softmax": 0, "sigmoid_bias": 1, "sqrt_softplus": 2}
+
+
+def moe_route(h, w, c):
+    R = h.shape[0]
+    dev = h.device
+    logits = dense_linear(h, w["gate"], out_f32=True)
+    wts = torch.empty(R, c.top_k, dtype=torch.float32, device=dev)
+    ids = torch.empty(R, c.top_k, dtype=torch.int32, device=dev)
+    prow = torch.empty(R, c.top_k, dtype=torch.int32, device=dev)
+    sg = torch.empty(R, dtype=torch.float32, device=dev) if c.shared_gate else None
+    rc = lib().spark_moe_route(P(logits), logits.stride(0), R, c.n_experts, c.top_k, ROUTER_KIND[c.router],
+                               P(w.get("bias")), float(c.route_scale), int(c.shared_gate), P(wts), P(ids), P(prow), P(sg),
+                               stream())
+    check(rc, "spark_moe_route")
+    return wts, ids, prow, sg
+
+
+def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
+    if isinstance(w, Exl3Weight):
+        return exl3_gemv(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act,
+                         limit=limit, out_f32=out_f32)
+    if isinstance(w, QuantWeight):
+        from . import mx
+        return mx.expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32)
+    E, N, K = w.shape
+    return gemv_bf16(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act,
+                     limit=limit, out_f32=out_f32, expert_stride=N * K, n=N, k=K)
+
+
+def moe_sort(ids, E):
+    Pn = ids.numel()
+    dev = ids.device
+    perm = torch.empty(Pn, dtype=torch.int32, device=dev)
+    inv = torch.empty(Pn, dtype=torch.int32, device=dev)
+    offs = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    max_tiles = (Pn + 127) // 128 + E
+    tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+    ntile = torch.empty(1, dtype=torch.int32, device=dev)
+    hist = scratch("moe_hist", ((Pn + 255) // 256) * E, torch.int32, dev)
+    rc = lib().spark_moe_sort(P(ids), Pn, E, P(perm), P(inv), P(offs), P(tiles), P(ntile), P(hist), stream())
+    check(rc, "spark_moe_sort")
+    return perm, inv, offs, tiles, ntile, max_tiles
+
+
+def grouped_gemm(a, b, tiles, ntile, max_tiles, n_experts, rows_per_expert, N, mode, limit=0.0, fmt=1):
+    """a [P, K] rows in expert order; b [E*rows_per_expert, K]; mode 0 -> fp32 [P, N]; 1 -> swiglu bf16 [P, N]."""
+    Pn, K = a.shape
+    out = torch.empty(Pn, N, dtype=torch.bfloat16 if mode == 1 else torch.float32, device=a.device)
+    rc = lib().spark_gemm_grouped_bf16(P(a), P(b), P(out), Pn, N, K, a.stride(0), K, N, n_experts, rows_per_expert,
+                                       P(tiles), P(ntile), max_tiles, mode, float(limit), fmt, P(status_word(a.device)),
+                                       stream())
+    check(rc, "spark_gemm_grouped_bf16")
+    return out
+
+
+DECODE_PAIRS_MAX = 256
+
+
+def moe(h, w, c):
+    """Routed + shared experts; returns the bf16 block output [R, H]."""
+    h = _as_bf16(h).contiguous()
+    R, H = h.shape
+    dev = h.device
+    wts, ids, prow, sg = moe_route(h, w, c)
+    Pn = R * c.top_k
+    wgu, wd = w["w_gu"], w["w_down"]
+    shared = None
+    if "s_gu" in w:
+        if R <= 16:
+            sgu = w["s_gu"]
+            if isinstance(sgu, Exl3Weight):
+                gu = exl3_gemv(h, sgu)
+                shared = exl3_gemv(gu, w["s_down"], act=1, limit=c.swiglu_limit)
+            elif isinstance(sgu, QuantWeight):
+                shared = quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
+            else:
+                gu = gemv_bf16(h, sgu)
+                shared = gemv_bf16(gu, w["s_down"], act=1, limit=c.swiglu_limit, k=w["s_down"].shape[1])
+        else:
+            shared = linear_any(swiglu(linear_any(h, w["s_gu"]), c.swiglu_limit), w["s_down"])
+    out = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
+    if Pn <= DECODE_PAIRS_MAX:
+        pe, pr = ids.view(-1), prow.view(-1)
+        gu = _expert_gemv(h, wgu, Pn, pe, pr, 0, 0.0, False)                       # [P, 2F] bf16
+        y = _expert_gemv(gu, wd, Pn, pe, None, 1, c.swiglu_limit, True)            # [P, H] fp32
+        inv = None
+    else:
+        perm, inv, offs, tiles, ntile, max_tiles = moe_sort(ids.view(-1), c.n_experts)
+        src = torch.div(perm, c.top_k, rounding_mode="floor").to(torch.int32)
+        a = gather_rows(h, src)
+        if isinstance(wgu, Exl3Weight):
+            from .exl3_moe import exl3_grouped_experts
+            y = exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c)
+        elif isinstance(wgu, QuantWeight):
+            from . import mx
+            y = mx.grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c)
+        else:
+            E, F2, K = wgu.shape
+            act = grouped_gemm(a, wgu.view(E * F2, K), tiles, ntile, max_tiles, E, F2, F2 // 2, 1, c.swiglu_limit)
+            y = grouped_gemm(act, wd.view(E * H, F2 // 2), tiles, ntile, max_tiles, E, H, H, 0)
+    rc = lib().spark_moe_combine(None, P(y), int(y.dtype == torch.float32), P(inv), P(wts), R, c.top_k, P(shared), P(sg), H,
+                                 P(out), stream())
+    check(rc, "spark_moe_combine")
+    return out
+
+
+def linear_any(x, w):
+    return quant_linear(x, w) if isinstance(w, QuantWeight) else dense_linear(x, w)
+
+
+# ----------------------------------------------------------------------------- mixers
+def _plan_dev(plan, device):
+    if not plan.dev:
+        from ..models.plan import plan_device_arrays
+        plan.dev = plan_device_arrays(plan, device)
+    return plan.dev
+
+
+def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None):
+    if plan.is_tree:
+        raise NotImplementedError("tree verify of gated-DeltaNet layers runs on the chain kernel only")
+    c = mixer.c
+    d = _plan_dev(plan, proj.device)
+    R = proj.shape[0]
+    out = torch.empty(R, c.n_v_heads * c.head_dim, dtype=torch.bfloat16, device=proj.device)
+    w = mixer.w
+    rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
+                             P(w["norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows), len(plan.segs), P(out),
+                             out.stride(0), c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit),
+                             stream())
+    check(rc, "spark_gdn_seq")
+    return out
+
+
+def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
+    n_rows = torch.tensor([len(a) for a in accepted], dtype=torch.int32, device=proj.device)
+    gdn_mixer(mixer, proj, ab, plan, True, n_rows)
+    return True
+
+
+def kda_mixer(mixer, pre, lr, plan, commit):
+    return None      # KDA runs the generic path (projections on the kernels, recurrence in ATen) for now
+
+
+ATT_TS = 256
+
+
+def attn_mixer(mixer, qkv, plan, seqs):
+    if plan.is_tree:
+        raise NotImplementedError("tree-verify attention mask kernel")
+    c = mixer.c
+    dev = qkv.device
+    d = _plan_dev(plan, dev)
+    R = qkv.shape[0]
+    if "row_kv" not in d:
+        kvb = torch.tensor([seqs[s.slot].kv_base for s in plan.segs for _ in range(s.n)], dtype=torch.int64)
+        d["row_kv"] = kvb.to(dev)
+        d["max_ctx"] = max(s.pos0 + s.n for s in plan.segs)
+        for s in plan.segs:
+            assert s.pos0 + s.n <= seqs[s.slot].kv_cap, "sequence capacity exceeded"
+    w = mixer.w
+    sparse = c.sparse_topk_blocks > 0
+    qbuf = torch.empty(R, c.n_q_heads, c.head_dim, dtype=torch.bfloat16, device=dev)
+    qi = torch.empty(R, c.idx_heads, c.idx_dim, dtype=torch.float32, device=dev) if sparse else None
+    rc = lib().spark_attn_prep(P(qkv), qkv.stride(0), R, c.n_q_heads, c.n_kv_heads, c.head_dim, c.rope_dim, int(c.gated),
+                               int(c.qk_norm), c.idx_heads if sparse else 0, c.idx_dim if sparse else 0, c.block,
+                               int(mixer.fp8), float(mixer.cfg.norm_eps), P(w.get("q_norm")), P(w.get("k_norm")),
+                               P(w.get("iq_norm")), P(w.get("ik_norm")), P(mixer.inv), P(d["pos32"]), P(d["row_kv"]),
+                               P(d["row_j"]), P(qbuf), P(mixer.k), P(mixer.v), P(getattr(mixer, "ks", None)),
+                               P(getattr(mixer, "vs", None)), P(qi), P(getattr(mixer, "ik_raw", None)),
+                               P(getattr(mixer, "ik_pool", None)), stream())
+    check(rc, "spark_attn_prep")
+    sel = sel_n = None
+    sel_ld = 0
+    max_ctx = d["max_ctx"]
+    if sparse and max_ctx > c.sparse_topk_blocks * c.block:
+        from . import sparse as sp
+        sel, sel_n = sp.select_blocks(mixer, qi, plan, d)
+        sel_ld = sel.shape[1]
+        max_ctx = sel_ld
+    nsplit = (max_ctx + ATT_TS - 1) // ATT_TS
+    part_o = scratch("attn_part_o", R * c.n_q_heads * nsplit * c.head_dim, torch.float32, dev)
+    part_ml = scratch("attn_part_ml", R * c.n_q_heads * nsplit * 2, torch.float32, dev)
+    out = torch.empty(R, c.n_q_heads * c.head_dim, dtype=torch.bfloat16, device=dev)
+    rc = lib().spark_attn_decode(P(qbuf), P(mixer.k), P(mixer.v), P(getattr(mixer, "ks", None)),
+                                 P(getattr(mixer, "vs", None)), int(mixer.fp8), P(d["pos32"]), P(d["row_kv"]), P(sel),
+                                 P(sel_n), sel_ld, P(part_o), P(part_ml), nsplit, P(qkv), qkv.stride(0), int(c.gated), R,
+                                 c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), P(out), stream())
+    check(rc, "spark_attn_decode")
+    return out

@@ -1,0 +1,201 @@
+"""LLMEngine: the public inference API (prefill / batched decode rounds / generate).
+
+One engine per GPU rank.  Decode rounds run from captured CUDA graphs: a graph is keyed by the row
+layout (rows per sequence x sequences) and the attention split bucket, its inputs (token ids,
+positions, segment table, KV bases) live in fixed device buffers refreshed by ONE pinned host->device
+copy per round, and the sampled token ids come back with one device->host read.  The reference does
+the same per round (engine-rs/src/spec_probe.rs:314-331 `replay_checked`: upload token ids,
+graph.replay(); qwen/graph.rs:538-845 batched graphs keyed by the store set and widths).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..config import EngineConfig, ModelConfig
+from ..models.model import Model
+from ..models.plan import Plan, Segment, make_plan, plan_device_arrays
+
+
+@dataclass
+class GenStats:
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    rounds: int = 0
+    tokens: int = 0
+    drafted_tokens: int = 0
+    accepted_drafts: int = 0
+
+
+class _DecodeGraph:
+    """Captured forward over a fixed row layout; refreshed through a packed int32 staging buffer."""
+
+    def __init__(self, engine: "LLMEngine", slots: Sequence[int], rows_per_seq: int, ctx_bucket: int):
+        self.engine, self.slots, self.k = engine, list(slots), rows_per_seq
+        m = engine.model
+        dev = m.device
+        n = len(slots)
+        R = n * rows_per_seq
+        self.R = R
+        # packed host staging: ids[R] pos[R] row_pos0[R] seg[n*4]  + row_kv handled as int64 separately
+        self.host = torch.zeros(3 * R + 4 * n, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(3 * R + 4 * n, dtype=torch.int32, device=dev)
+        self.row_kv = torch.zeros(R, dtype=torch.int64, device=dev)
+        self.out_host = torch.zeros(R, dtype=torch.int32).pin_memory()
+        segs = [Segment(s, i * rows_per_seq, rows_per_seq, 0) for i, s in enumerate(self.slots)]
+        self.plan = Plan(ids=torch.zeros(R, dtype=torch.long, device=dev), pos=torch.zeros(R, dtype=torch.long, device=dev),
+                         segs=segs, logit_rows=torch.arange(R, device=dev))
+        d = {"ids32": self.dev[:R], "pos32": self.dev[R:2 * R], "row_pos0": self.dev[2 * R:3 * R],
+             "seg": self.dev[3 * R:].view(n, 4), "row_kv": self.row_kv, "max_ctx": ctx_bucket,
+             "row_slot": torch.tensor([s for s in self.slots for _ in range(rows_per_seq)], dtype=torch.int32, device=dev),
+             "row_j": torch.tensor(list(range(rows_per_seq)) * n, dtype=torch.int32, device=dev),
+             "row_r0": torch.tensor([i * rows_per_seq for i in range(n) for _ in range(rows_per_seq)], dtype=torch.int32,
+                                    device=dev)}
+        self.plan.dev = d
+        self.graph = None
+        self.out_ids = None
+        self.logits = None
+        self.hidden = None
+
+    def stage(self, ids: List[List[int]], pos0: List[int]):
+        R, n, k = self.R, len(self.slots), self.k
+        h = self.host
+        m = self.engine.model
+        for i, s in enumerate(self.slots):
+            for j in range(k):
+                r = i * k + j
+                h[r] = ids[i][j]
+                h[R + r] = pos0[i] + j
+                h[2 * R + r] = pos0[i]
+            h[3 * R + 4 * i + 0] = s
+            h[3 * R + 4 * i + 1] = i * k
+            h[3 * R + 4 * i + 2] = k
+            h[3 * R + 4 * i + 3] = pos0[i]
+            self.plan.segs[i].pos0 = pos0[i]
+        self.dev.copy_(h, non_blocking=True)
+
+    def set_kv(self):
+        m = self.engine.model
+        kv = torch.tensor([m.seqs[s].kv_base for s in self.slots for _ in range(self.k)], dtype=torch.int64)
+        self.row_kv.copy_(kv)
+
+    def run(self, commit: bool):
+        m = self.engine.model
+        if self.graph is None:
+            self.set_kv()
+            # eager warm-up sizes every persistent scratch buffer, then capture
+            from ..ops import cuda as cu
+            n0 = cu.launch_count()
+            self._body(commit)
+            self.launches = cu.launch_count() - n0
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body(commit)
+            cu.add_launches(-self.launches)       # the capture pass launched nothing
+            self.graph = g
+        self.replay()
+        self.out_host.copy_(self.out_ids, non_blocking=True)
+
+    def replay(self):
+        from ..ops import cuda as cu
+        self.graph.replay()
+        cu.add_launches(self.launches)
+
+    def _body(self, commit: bool):
+        m = self.engine.model
+        self.plan.ids = self.plan.dev["ids32"]
+        logits = m.forward(self.plan, commit=commit, graph_mode=True)
+        self.logits = logits
+        self.hidden = m.hidden_out
+        self.out_ids = ops.argmax(logits)
+
+
+class LLMEngine:
+    def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cuda",
+                 max_seqs: int = 4, kv_tokens_per_seq: int = 4096):
+        self.cfg, self.ecfg = cfg, ecfg or EngineConfig()
+        dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
+        self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=max_seqs,
+                           kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq)
+        self.device = self.model.device
+        self.graphs: Dict[tuple, _DecodeGraph] = {}
+        self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda"
+        self.stats = GenStats()
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, slot: int, ids: Sequence[int], chunk: Optional[int] = None) -> torch.Tensor:
+        """Chunked prefill of a fresh sequence; returns the logits of the last prompt token."""
+        chunk = chunk or self.ecfg.prefill_chunk
+        m = self.model
+        m.reset_slot(slot)
+        last = None
+        for c0 in range(0, len(ids), chunk):
+            toks = list(ids[c0: c0 + chunk])
+            plan = make_plan([(slot, toks, c0)], device=self.device, all_logits=False)
+            last = m.forward(plan)
+        return last[0]
+
+    # ------------------------------------------------------------------ decode
+    def _ctx_bucket(self, max_ctx: int) -> int:
+        b = 256
+        while b < max_ctx:
+            b *= 2
+        return b
+
+    @torch.no_grad()
+    def decode_round(self, slots: Sequence[int], ids: Sequence[int]) -> List[int]:
+        """One greedy token for each listed sequence (rows batched in one forward)."""
+        m = self.model
+        pos0 = [m.seqs[s].length for s in slots]
+        if not self.use_graphs:
+            plan = make_plan([(s, [t], p) for s, t, p in zip(slots, ids, pos0)], device=self.device)
+            logits = m.forward(plan)
+            return ops.argmax(logits).tolist()
+        key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + 1))
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _DecodeGraph(self, slots, 1, key[2])
+        g.stage([[t] for t in ids], pos0)
+        g.run(commit=True)
+        torch.cuda.current_stream().synchronize()
+        for s, p in zip(slots, pos0):
+            m.seqs[s].length = p + 1
+        return g.out_host.tolist()
+
+    @torch.no_grad()
+    def generate(self, prompts: List[Sequence[int]], max_new: int, stop_ids: Sequence[int] = ()) -> List[List[int]]:
+        """Greedy generation for up to `max_seqs` prompts at once (public API used by the bench)."""
+        n = len(prompts)
+        assert n <= self.model.n_slots
+        outs: List[List[int]] = [[] for _ in range(n)]
+        t0 = time.perf_counter()
+        cur = []
+        for s, p in enumerate(prompts):
+            cur.append(int(torch.argmax(self.prefill(s, p))))
+            outs[s].append(cur[-1])
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        live = list(range(n))
+        for _ in range(max_new - 1):
+            nxt = self.decode_round(live, [cur[s] for s in live])
+            for s, t in zip(live, nxt):
+                cur[s] = t
+                outs[s].append(t)
+            self.stats.rounds += 1
+            live = [s for s in live if cur[s] not in stop_ids]
+            if not live:
+                break
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        self.stats.prefill_ms += (t1 - t0) * 1e3
+        self.stats.decode_ms += (t2 - t1) * 1e3
+        self.stats.tokens += sum(len(o) for o in outs)
+        return outs

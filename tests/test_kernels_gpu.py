@@ -1,0 +1,184 @@
+"""Every CUDA kernel against a plain PyTorch fp32 reference of the same op (small shapes), plus
+run-twice bitwise determinism where the kernel promises it."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from spark_engine_b200 import ops
+from spark_engine_b200.config import MoeConfig
+from spark_engine_b200.quant import formats as Q
+
+DEV = "cuda"
+
+
+def cu():
+    return ops.cuda_ops()
+
+
+def _status_ok():
+    st = cu().read_status(torch.device(DEV))
+    assert st[0] == 0, f"device status {st}"
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+# ------------------------------------------------------------------------------ tcgen05 GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (300, 520, 1000), (1, 256, 512), (257, 96, 72),
+                                   (1024, 2048, 2048)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_gemm_tcgen05_matches_fp32_matmul(M, N, K, out_f32):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    b = torch.randn(N, K, device=DEV, generator=g).bfloat16()
+    c = cu().gemm_bf16(a, b, out_f32=out_f32)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = a.float() @ b.float().t()
+    assert rel_err(c, ref) < (2e-5 if out_f32 else 6e-3)
+    c2 = cu().gemm_bf16(a, b, out_f32=out_f32)
+    assert torch.equal(c, c2)
+
+
+def test_gemm_tcgen05_fp16_operands():
+    g = torch.Generator(device=DEV).manual_seed(2)
+    a = torch.randn(200, 256, device=DEV, generator=g).half()
+    b = torch.randn(384, 256, device=DEV, generator=g).half()
+    c = cu().gemm_bf16(a, b, out_f32=True, fmt=0)
+    _status_ok()
+    assert rel_err(c, a.float() @ b.float().t()) < 2e-5
+
+
+def test_gemm_swiglu_epilogue():
+    g = torch.Generator(device=DEV).manual_seed(3)
+    M, F, K = 200, 256, 512
+    a = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    b = (torch.randn(2 * F, K, device=DEV, generator=g) * 0.1).bfloat16()
+    out = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    rc = cu().lib().spark_gemm_bf16_swiglu(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, F, K, K, K, F, 0.0,
+                                           cu().status_word(a.device).data_ptr(), cu().stream())
+    assert rc == 0
+    gu = a.float() @ b.float().t()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    _status_ok()
+    assert rel_err(out, ref) < 8e-3
+
+
+# ------------------------------------------------------------------------------ GEMV
+@pytest.mark.parametrize("R", [1, 3, 8, 16])
+@pytest.mark.parametrize("N,K", [(64, 256), (513, 2048), (2048, 4096)])
+def test_gemv_bf16(R, N, K):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(R, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    y = cu().gemv_bf16(x, w, out_f32=True)
+    ref = x.float() @ w.float().t()
+    assert rel_err(y, ref) < 1e-5
+    # batch invariance: row 0 alone gives the same bits
+    y1 = cu().gemv_bf16(x[:1].contiguous(), w, out_f32=True)
+    assert torch.equal(y1[0], y[0])
+
+
+def test_gemv_pairs_with_swiglu_staging():
+    g = torch.Generator(device=DEV).manual_seed(5)
+    E, F, H, Pn = 6, 128, 256, 10
+    wd = (torch.randn(E, H, F, device=DEV, generator=g) * 0.05).bfloat16()
+    gu = torch.randn(Pn, 2 * F, device=DEV, generator=g).bfloat16()
+    pe = torch.randint(0, E, (Pn,), device=DEV, generator=g).int()
+    y = cu().gemv_bf16(gu, wd, items=Pn, rows_per_item=1, pair_expert=pe, act=1, out_f32=True, expert_stride=H * F, n=H, k=F)
+    act = (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).bfloat16().float()
+    ref = torch.stack([act[i] @ wd[pe[i]].float().t() for i in range(Pn)])
+    assert rel_err(y, ref) < 1e-4
+
+
+# ------------------------------------------------------------------------------ elementwise
+def test_add_rmsnorm_and_friends():
+    g = torch.Generator(device=DEV).manual_seed(6)
+    R, H = 5, 2048
+    res = torch.randn(R, H, device=DEV, generator=g)
+    delta = torch.randn(R, H, device=DEV, generator=g).bfloat16()
+    w = torch.rand(H, device=DEV, generator=g) + 0.5
+    ref_res = res + delta.float()
+    ref = ref_res * torch.rsqrt(ref_res.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    out, res2 = cu().add_rmsnorm(delta, res.clone(), w, 1e-6)
+    assert torch.allclose(res2, ref_res, atol=1e-6)
+    assert rel_err(out, ref) < 4e-3
+    sw = cu().swiglu(delta, 0.0)
+    F = H // 2
+    assert rel_err(sw, torch.nn.functional.silu(delta[:, :F].float()) * delta[:, F:].float()) < 5e-3
+    logits = torch.randn(4, 4099, device=DEV, generator=g)
+    logits[1, 7] = logits[1, 4000] = 100.0      # tie -> lowest index
+    ids = cu().argmax(logits)
+    assert ids.tolist() == [int(torch.argmax(logits[0])), 7, int(torch.argmax(logits[2])), int(torch.argmax(logits[3]))]
+
+
+def test_moe_route_kinds_match_reference():
+    g = torch.Generator(device=DEV).manual_seed(7)
+    for kind, E, k in (("softmax", 512, 10), ("sigmoid_bias", 288, 8), ("sqrt_softplus", 384, 6)):
+        c = MoeConfig(n_experts=E, top_k=k, router=kind, route_scale=2.5 if kind != "softmax" else 1.0,
+                      shared_gate=(kind == "softmax"))
+        H = 256
+        w = {"gate": (torch.randn(E + (1 if c.shared_gate else 0), H, device=DEV, generator=g) * 0.1).bfloat16(),
+             "bias": torch.randn(E, device=DEV, generator=g) * 0.01}
+        h = torch.randn(7, H, device=DEV, generator=g).bfloat16()
+        wts, ids, prow, sg = cu().moe_route(h, w, c)
+        ops.set_fallback(True)
+        rw, ri, rsg = ops.route(h, w, c)
+        ops.set_fallback(False)
+        assert torch.equal(ids.long().sort(-1).values, ri.sort(-1).values), kind
+        order = torch.argsort(ids.long(), -1)
+        rorder = torch.argsort(ri, -1)
+        assert torch.allclose(torch.gather(wts, 1, order), torch.gather(rw, 1, rorder), rtol=2e-3, atol=1e-5), kind
+        if sg is not None:
+            assert torch.allclose(sg, rsg[:, 0], rtol=2e-3, atol=1e-4)
+
+
+# ------------------------------------------------------------------------------ EXL3
+@pytest.mark.parametrize("kind", ["mul1", "mcg"])
+def test_exl3_reconstruct_is_bit_exact(kind):
+    w = Q.random_exl3(256, 384, bits=4, seed=3, kind=kind)
+    ref = Q.exl3_inner(w.trellis, kind)                     # [K, N]
+    got = cu().exl3_reconstruct(w.to(DEV)).float().cpu()    # [N, K]
+    assert torch.equal(got, ref.t())
+
+
+@pytest.mark.parametrize("R", [1, 4, 16])
+@pytest.mark.parametrize("N,K", [(256, 512), (1024, 2048), (2048, 512)])
+def test_exl3_gemv_matches_dequant_matmul(R, N, K):
+    w = Q.random_exl3(N, K, bits=4, seed=5, std=0.05)
+    g = torch.Generator(device=DEV).manual_seed(8)
+    x = torch.randn(R, K, device=DEV, generator=g).bfloat16()
+    y = cu().exl3_gemv(x, w.to(DEV), out_f32=True)
+    ref = x.float().cpu() @ w.dequant().t()
+    assert rel_err(y.cpu(), ref) < 3e-3
+    y2 = cu().exl3_gemv(x, w.to(DEV), out_f32=True)
+    assert torch.equal(y, y2)
+    y1 = cu().exl3_gemv(x[:1].contiguous(), w.to(DEV), out_f32=True)
+    assert torch.equal(y1[0], y[0])                           # batch-invariant
+
+
+def test_exl3_gemm_path_matches_dequant_matmul():
+    N, K, M = 512, 1024, 200
+    w = Q.random_exl3(N, K, bits=4, seed=6, std=0.05)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    y = cu().exl3_linear(x, w.to(DEV))
+    _status_ok()
+    ref = x.float().cpu() @ w.dequant().t()
+    assert rel_err(y.cpu(), ref) < 8e-3
+
+
+def test_exl3_moe_pairs():
+    E, F, H = 8, 128, 256
+    wgu = Q.random_exl3(2 * F, H, bits=4, experts=E, seed=10, std=0.05)
+    g = torch.Generator(device=DEV).manual_seed(10)
+    x = torch.randn(3, H, device=DEV, generator=g).bfloat16()
+    pe = torch.tensor([1, 5, 5, 0, 7, 2], dtype=torch.int32, device=DEV)
+    pr = torch.tensor([0, 0, 1, 1, 2, 2], dtype=torch.int32, device=DEV)
+    y = cu().exl3_gemv(x, wgu.to(DEV), items=6, rows_per_item=1, pair_expert=pe, pair_row=pr, out_f32=True)
+    ref = torch.stack([x[pr[i]].float().cpu() @ wgu.dequant_expert(int(pe[i])).t() for i in range(6)])
+    assert rel_err(y.cpu(), ref) < 3e-3
