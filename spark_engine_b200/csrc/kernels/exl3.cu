@@ -206,13 +206,18 @@ exl3_gemv_kernel(Exl3GemvArgs a) {
 
 // inner -> fp16 Wt[N, K] (K contiguous).  One warp per tile.
 template <int CB>
-__global__ void exl3_reconstruct_kernel(const uint32_t* __restrict__ trellis, __half* __restrict__ Wt, int K, int N) {
+__global__ void exl3_reconstruct_kernel(const uint32_t* __restrict__ trellis, __half* __restrict__ Wt, int K, int N,
+                                        int E) {
   const int KT = K >> 4, NT = N >> 4;
-  const long long tile = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (tile >= static_cast<long long>(KT) * NT) return;
+  const long long per = static_cast<long long>(KT) * NT;
+  long long tile = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (tile >= per * E) return;
   const int lane = threadIdx.x & 31;
-  const int kt = static_cast<int>(tile / NT), nt = static_cast<int>(tile % NT);
   const uint32_t cur = __ldg(trellis + tile * 32 + lane);
+  const long long e = tile / per;
+  tile -= e * per;
+  Wt += e * static_cast<long long>(N) * K;
+  const int kt = static_cast<int>(tile / NT), nt = static_cast<int>(tile % NT);
   const uint32_t prev = __shfl_sync(0xffffffffu, cur, (lane + 31) & 31);
   uint32_t w[4];
   exl3_decode8_b4<CB>(cur, prev, w);
@@ -285,11 +290,12 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int spark_exl3_reconstruct(const void* trellis, void* Wt, int K, int N, int codebook, cudaStream_t s) {
-  const long long tiles = (long long)(K >> 4) * (N >> 4);
+// E stacked tensors (experts) in one launch: trellis [E][K/16][N/16][32 words] -> Wt [E][N][K].
+extern "C" int spark_exl3_reconstruct(const void* trellis, void* Wt, int K, int N, int codebook, cudaStream_t s, int E) {
+  const long long tiles = (long long)(K >> 4) * (N >> 4) * E;
   const unsigned blocks = (unsigned)((tiles * 32 + 255) / 256);
-  if (codebook == 0) exl3_reconstruct_kernel<0><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N);
-  else exl3_reconstruct_kernel<1><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N);
+  if (codebook == 0) exl3_reconstruct_kernel<0><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
+  else exl3_reconstruct_kernel<1><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -45,7 +45,7 @@ _SIGS = {
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp],
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                         f32, i32, vp],
-    "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp],
+    "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
 }
 
@@ -242,13 +242,8 @@ def exl3_reconstruct(w: Exl3Weight, out: Optional[torch.Tensor] = None) -> torch
     E = w.trellis.shape[0] if w.experts else 1
     if out is None:
         out = torch.empty((E, w.n, w.k) if w.experts else (w.n, w.k), dtype=torch.float16, device=w.trellis.device)
-    tw = (w.k // 16) * (w.n // 16) * 64      # int16 elements per expert
-    tr = w.trellis.view(-1)
-    o = out.view(-1)
-    for e in range(E):
-        rc = lib().spark_exl3_reconstruct(tr[e * tw:].data_ptr(), o[e * w.n * w.k:].data_ptr(), w.k, w.n,
-                                          0 if w.kind == "mul1" else 1, stream())
-        check(rc, "spark_exl3_reconstruct")
+    rc = lib().spark_exl3_reconstruct(P(w.trellis), P(out), w.k, w.n, 0 if w.kind == "mul1" else 1, stream(), E)
+    check(rc, "spark_exl3_reconstruct")
     return out
 
 

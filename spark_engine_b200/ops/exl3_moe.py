@@ -1,0 +1,30 @@
+"""Prefill-size MoE over EXL3 experts: dequant to the tcgen05 grouped GEMM.
+
+Rows arrive in expert order.  Per projection: input Hadamard with the row's expert sign/scale vector
+(fp16), all experts' trellises reconstructed to fp16 K-major matrices in one launch, grouped tcgen05
+GEMM over the <=128-row tile list, output Hadamard with the expert's output vector.  The reference
+runs this with mma.sync grouped kernels that decode B tiles in the mainloop
+(engine-rs/shim/moe_exl3.cuh:521-1233).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import cuda as cu
+
+
+def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
+    dev = a.device
+    E = wgu.trellis.shape[0]
+    H, F2 = wgu.k, wgu.n
+    F = F2 // 2
+    row_expert = ids.view(-1)[perm.long()].to(torch.int32).contiguous()
+    xh = cu.exl3_had_rows(a, wgu.suh, post=False, row_expert=row_expert, expert_stride=H)
+    wt = cu.exl3_reconstruct(wgu, cu.scratch("exl3_recon_gu", E * F2 * H, torch.float16, dev)[: E * F2 * H].view(E, F2, H))
+    acc = cu.grouped_gemm(xh, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2, 0, fmt=0)
+    gu = cu.exl3_had_rows(acc, wgu.svh, post=True, row_expert=row_expert, expert_stride=F2)
+    act = cu.swiglu(gu, c.swiglu_limit)
+    xh2 = cu.exl3_had_rows(act, wd.suh, post=False, row_expert=row_expert, expert_stride=F)
+    wt2 = cu.exl3_reconstruct(wd, cu.scratch("exl3_recon_d", E * H * F, torch.float16, dev)[: E * H * F].view(E, H, F))
+    acc2 = cu.grouped_gemm(xh2, wt2.view(E * H, F), tiles, ntile, max_tiles, E, H, H, 0, fmt=0)
+    return cu.exl3_had_rows(acc2, wd.svh, post=True, row_expert=row_expert, expert_stride=H)

@@ -89,9 +89,11 @@ class _DecodeGraph:
             self.set_kv()
             # eager warm-up sizes every persistent scratch buffer, then capture
             from ..ops import cuda as cu
+            # (warm-up runs without commit: linear-attention state is written exactly once, by the replay)
             n0 = cu.launch_count()
-            self._body(commit)
+            self._body(False)
             self.launches = cu.launch_count() - n0
+            m._pending_plan = None
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):

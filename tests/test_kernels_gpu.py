@@ -126,9 +126,10 @@ def test_moe_route_kinds_match_reference():
              "bias": torch.randn(E, device=DEV, generator=g) * 0.01}
         h = torch.randn(7, H, device=DEV, generator=g).bfloat16()
         wts, ids, prow, sg = cu().moe_route(h, w, c)
-        ops.set_fallback(True)
-        rw, ri, rsg = ops.route(h, w, c)
-        ops.set_fallback(False)
+        wf = {"gate": w["gate"].float(), "bias": w["bias"]}
+        rw, ri, rsg = ops.route(h.float().cpu(), {k: v.cpu() for k, v in wf.items()}, c)   # fp32 reference on CPU
+        rw, ri = rw.to(DEV), ri.to(DEV)
+        rsg = rsg.to(DEV) if rsg is not None else None
         assert torch.equal(ids.long().sort(-1).values, ri.sort(-1).values), kind
         order = torch.argsort(ids.long(), -1)
         rorder = torch.argsort(ri, -1)
