@@ -143,7 +143,7 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, AttnDims a,
 }
 
 // ------------------------------------------------------------------------------------------ decode
-constexpr int ATT_TS = 256;        // tokens per split
+constexpr int ATT_TS = 64;         // tokens per split
 constexpr int ATT_MAXREP = 8;
 
 template <bool FP8>
@@ -228,10 +228,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qbuf, const void* __restric
     float o[ATT_MAXREP];
 #pragma unroll
     for (int h = 0; h < ATT_MAXREP; ++h) o[h] = 0.f;
-    for (int i = 0; i < nt; ++i) {
-      const float v = kv_load<FP8>(vc, (static_cast<size_t>(base + stok[i]) * Hkv + hk) * D + t);
+    for (int i0 = 0; i0 < nt; i0 += 8) {
+      float v[8];
 #pragma unroll
-      for (int h = 0; h < ATT_MAXREP; ++h) if (h < rep) o[h] = fmaf(sc[h][i], v, o[h]);
+      for (int u = 0; u < 8; ++u)
+        v[u] = (i0 + u) < nt ? kv_load<FP8>(vc, (static_cast<size_t>(base + stok[i0 + u]) * Hkv + hk) * D + t) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i0 + u < nt) {
+#pragma unroll
+          for (int h = 0; h < ATT_MAXREP; ++h) if (h < rep) o[h] = fmaf(sc[h][i0 + u], v[u], o[h]);
+        }
     }
 #pragma unroll
     for (int h = 0; h < ATT_MAXREP; ++h)

@@ -72,31 +72,47 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
   }
 }
 
-// arg-max per row, ties -> lowest index.  logits fp32 [R, V]; out ids int32 [R], optional max value.
-__global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out_id, float* __restrict__ out_val) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  const int r = blockIdx.x;
+// arg-max per row, ties -> lowest index.  Two stages so that a 150K-wide vocabulary is scanned by many
+// CTAs: stage 1 grid (R, chunks) writes (value, index) packets, stage 2 (one warp per row) picks the winner.
+__device__ __forceinline__ void argmax_combine(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_part_kernel(const float* __restrict__ logits, int V, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int r = blockIdx.x, c = blockIdx.y, nc = gridDim.y;
+  const int per = (V + nc - 1) / nc;
+  const int i0 = c * per, i1 = min(V, i0 + per);
   const float* x = logits + static_cast<size_t>(r) * V;
   float best = -INFINITY; int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = x[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  for (int i = i0 + threadIdx.x; i < i1; i += 256 * 4) {
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = (i + u * 256) < i1 ? x[i + u * 256] : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) if (v[u] > best) { best = v[u]; bi = i + u * 256; }   // ascending i: first max kept
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   if (l == 0) { sv[w] = best; si[w] = bi; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < (blockDim.x >> 5); ++i)
-      if (sv[i] > best || (sv[i] == best && si[i] < bi)) { best = sv[i]; bi = si[i]; }
-    out_id[r] = bi;
-    if (out_val) out_val[r] = best;
+    for (int i = 1; i < 8; ++i) argmax_combine(best, bi, sv[i], si[i]);
+    pv[r * nc + c] = best; pi[r * nc + c] = bi;
   }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int nc,
+                                    int* __restrict__ out_id, float* __restrict__ out_val) {
+  const int r = blockIdx.x;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < nc; i += 32) argmax_combine(best, bi, pv[r * nc + i], pi[r * nc + i]);
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (threadIdx.x == 0) { out_id[r] = bi; if (out_val) out_val[r] = best; }
 }
 
 // out f32 [R,H] = x f32 + add (bf16 or f32): residual add without a norm (last layer).
@@ -146,9 +162,13 @@ extern "C" void spark_swiglu(const void* gu, void* out, int R, int F, float limi
   if (R <= 0) return;
   swiglu_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, limit);
 }
-extern "C" void spark_argmax(const float* logits, int R, int V, int* out_id, float* out_val, cudaStream_t s) {
+// part_v / part_i: scratch of R * 64 entries each.
+extern "C" void spark_argmax(const float* logits, int R, int V, int* out_id, float* out_val, float* part_v, int* part_i,
+                             cudaStream_t s) {
   if (R <= 0) return;
-  argmax_kernel<<<R, 1024, 0, s>>>(logits, V, out_id, out_val);
+  const int nc = V >= 65536 ? 64 : (V >= 4096 ? 8 : 1);
+  argmax_part_kernel<<<dim3(R, nc), 256, 0, s>>>(logits, V, part_v, part_i);
+  argmax_final_kernel<<<R, 32, 0, s>>>(part_v, part_i, nc, out_id, out_val);
 }
 extern "C" void spark_add(const void* delta, int delta_f32, float* res, long n, cudaStream_t s) {
   if (n <= 0) return;

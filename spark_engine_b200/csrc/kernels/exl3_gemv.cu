@@ -1,0 +1,197 @@
+// EXL3 GEMV for <= 16 rows (decode / verify rows, MoE (row, expert) pairs):
+//   y = had128( had128(x * suh) @ inner ) * svh
+// One launch: input Hadamard, trellis decode, product, output Hadamard.  Grid (N/128, S, items) with a
+// thread-block cluster of S CTAs along the K-slices of one 128-column strip: every CTA streams the
+// 128-byte tiles of its slice (all loads of a warp are issued before the first decode, so one DRAM
+// round trip covers 16 tiles), decodes 8 weights per lane straight into m16n8k16 B fragments and
+// multiplies with the <= 16 activation rows; the S partial strips are then summed through distributed
+// shared memory by cluster rank 0 in slice order (no global scratch, no atomics), Hadamard-transformed
+// and scaled.  Fixed reduction order => bitwise reproducible and independent of the rows in flight.
+// M <= 16 is bandwidth / decode-ALU bound, so the warp-level MMA feeds it; GEMM-shaped EXL3 work goes
+// through exl3_reconstruct to the tcgen05 GEMM.
+// Replaces engine-rs/shim/qwen_exl3.cuh:427-626 (gemv_kernel / gemv_fused_kernel / finish_kernel) and
+// the decode half of moe_exl3.cuh:273-399.
+#include "exl3_common.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace spark {
+
+struct Exl3GemvArgs {
+  const __nv_bfloat16* x; int ldx;             // activations [rows, K] (or [rows, 2K] = [gate | up] when act == 1)
+  const uint32_t* trellis;                      // [E][K/16][N/16][32] words (4 bpw)
+  const __half* suh; const __half* svh;         // [E][K], [E][N]
+  long long t_stride, suh_stride, svh_stride;   // per expert, in elements
+  void* y; int ldy; int out_f32;                // [items*R, N]
+  const int* pair_expert; const int* pair_row;
+  int R, K, N, S, act; float limit;
+};
+
+constexpr int EXL3_MAX_KS = 2048;              // K-slice per CTA (activation slice lives in shared memory)
+
+template <int CB>
+__global__ void __launch_bounds__(256)
+exl3_gemv_kernel(Exl3GemvArgs a) {
+  extern __shared__ __align__(16) uint8_t smem_dyn[];
+  __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
+  __shared__ __align__(16) float sb[16 * 128];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int strip = blockIdx.x, slice = blockIdx.y, item = blockIdx.z;
+  const int NT = a.N >> 4;
+  const int Ks = a.K / a.S, kts = Ks >> 4;
+  const int ldh = Ks + 8;
+  const int k_begin = slice * Ks;
+  const int e = a.pair_expert ? a.pair_expert[item] : 0;
+  const int xr0 = a.pair_row ? a.pair_row[item] : item * a.R;
+  const int R = a.R;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- issue this warp's trellis loads first (they do not depend on the prologue)
+  const int nt = strip * 8 + warp;
+  const uint32_t* tw = a.trellis + e * a.t_stride + (static_cast<size_t>(slice) * kts * NT + nt) * 32 + lane;
+  uint32_t cur[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) cur[u] = (u < kts) ? __ldg(tw + static_cast<size_t>(u) * NT * 32) : 0u;
+
+  // ---- prologue: xh = had128(x * suh) / sqrt(128) for this K-slice; one warp per (row, 128-block)
+  const __half* suh = a.suh + e * a.suh_stride + k_begin;
+  const int nblk = Ks >> 7;
+  for (int job = warp; job < R * nblk; job += 8) {
+    const int r = job / nblk, b = job - r * nblk;
+    const __nv_bfloat16* xr = a.x + static_cast<size_t>(xr0 + r) * a.ldx + k_begin + b * 128 + lane * 4;
+    float v[4];
+    if (a.act == 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float gg = __bfloat162float(xr[i]), uu = __bfloat162float(xr[a.K + i]);
+        if (a.limit > 0.f) { gg = fminf(gg, a.limit); uu = fminf(fmaxf(uu, -a.limit), a.limit); }
+        v[i] = gg / (1.f + __expf(-gg)) * uu;
+      }
+    } else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(xr);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]);
+      v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+    }
+    const uint2 sraw = *reinterpret_cast<const uint2*>(suh + b * 128 + lane * 4);
+    const __half2* sp = reinterpret_cast<const __half2*>(&sraw);
+    const float2 s0 = __half22float2(sp[0]), s1 = __half22float2(sp[1]);
+    v[0] *= s0.x; v[1] *= s0.y; v[2] *= s1.x; v[3] *= s1.y;
+    fwht128_warp(v, lane);
+    __half2 h0 = __floats2half2_rn(v[0] * INV_SQRT_128, v[1] * INV_SQRT_128);
+    __half2 h1 = __floats2half2_rn(v[2] * INV_SQRT_128, v[3] * INV_SQRT_128);
+    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(xh + r * ldh + b * 128 + lane * 4) = o;
+  }
+  __syncthreads();
+
+  // ---- main loop
+  float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool lo_row = g < R, hi_row = (g + 8) < R;
+#pragma unroll 1
+  for (int kb = 0; kb < kts; kb += 16) {
+    if (kb > 0) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u) cur[u] = (kb + u < kts) ? __ldg(tw + static_cast<size_t>(kb + u) * NT * 32) : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      if (kb + u < kts) {
+        const uint32_t prev = __shfl_sync(0xffffffffu, cur[u], (lane + 31) & 31);
+        uint32_t w[4];
+        exl3_decode8_b4<CB>(cur[u], prev, w);
+        uint32_t af[4];
+        const __half* xa = xh + (kb + u) * 16 + 2 * t;
+        af[0] = lo_row ? *reinterpret_cast<const uint32_t*>(xa + g * ldh) : 0u;
+        af[1] = hi_row ? *reinterpret_cast<const uint32_t*>(xa + (g + 8) * ldh) : 0u;
+        af[2] = lo_row ? *reinterpret_cast<const uint32_t*>(xa + g * ldh + 8) : 0u;
+        af[3] = hi_row ? *reinterpret_cast<const uint32_t*>(xa + (g + 8) * ldh + 8) : 0u;
+        mma_f16_16816(d0, af, w[0], w[1]);       // columns 0..7 of the n-tile
+        mma_f16_16816(d1, af, w[2], w[3]);       // columns 8..15
+      }
+    }
+  }
+  {
+    const int c = warp * 16 + 2 * t;
+    if (lo_row) {
+      sb[g * 128 + c] = d0[0]; sb[g * 128 + c + 1] = d0[1];
+      sb[g * 128 + c + 8] = d1[0]; sb[g * 128 + c + 9] = d1[1];
+    }
+    if (hi_row) {
+      sb[(g + 8) * 128 + c] = d0[2]; sb[(g + 8) * 128 + c + 1] = d0[3];
+      sb[(g + 8) * 128 + c + 8] = d1[2]; sb[(g + 8) * 128 + c + 9] = d1[3];
+    }
+  }
+  // ---- reduce the K-slices over distributed shared memory (rank order), then y = had128(acc) * svh
+  if (a.S > 1) cluster.sync(); else __syncthreads();
+  if (slice == 0) {
+    const __half* svh = a.svh + e * a.svh_stride + strip * 128;
+    for (int r = warp; r < R; r += 8) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < a.S; ++s) {
+        const float* src = (a.S > 1) ? cluster.map_shared_rank(sb, s) : sb;
+        const float4 p = *reinterpret_cast<const float4*>(src + r * 128 + lane * 4);
+        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+      }
+      fwht128_warp(v, lane);
+      const uint2 sraw = *reinterpret_cast<const uint2*>(svh + lane * 4);
+      const __half2* sp = reinterpret_cast<const __half2*>(&sraw);
+      const float2 s0 = __half22float2(sp[0]), s1 = __half22float2(sp[1]);
+      v[0] *= INV_SQRT_128 * s0.x; v[1] *= INV_SQRT_128 * s0.y; v[2] *= INV_SQRT_128 * s1.x; v[3] *= INV_SQRT_128 * s1.y;
+      const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
+      if (a.out_f32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
+      }
+    }
+  }
+  if (a.S > 1) cluster.sync();      // peers keep their shared memory alive until rank 0 has read it
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+// rows_per_item <= 16; K, N multiples of 128; S in 1..8 with (K/128) % S == 0 and K/S <= 2048.
+// codebook: 0 mul1, 1 mcg.  ldx, ldy multiples of 4 elements.
+extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, const void* suh, const void* svh,
+                               long long t_stride_words, long long suh_stride, long long svh_stride, void* y, int ldy,
+                               int out_f32, const int* pair_expert, const int* pair_row, int items, int rows_per_item,
+                               int K, int N, int S, int act, float limit, int codebook, cudaStream_t s) {
+  if (items <= 0 || rows_per_item <= 0) return 0;
+  if (rows_per_item > 16 || (K & 127) || (N & 127) || S < 1 || S > 8 || ((K >> 7) % S) || K / S > EXL3_MAX_KS) return -5;
+  if ((ldx & 3) || (ldy & 3)) return -5;
+  Exl3GemvArgs a;
+  a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.trellis = (const uint32_t*)trellis;
+  a.suh = (const __half*)suh; a.svh = (const __half*)svh;
+  a.t_stride = t_stride_words; a.suh_stride = suh_stride; a.svh_stride = svh_stride;
+  a.y = y; a.ldy = ldy; a.out_f32 = out_f32;
+  a.pair_expert = pair_expert; a.pair_row = pair_row;
+  a.R = rows_per_item; a.K = K; a.N = N; a.S = S; a.act = act; a.limit = limit;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(N / 128, S, items);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 16 * (K / S + 8) * 2;
+  {
+    static bool done0 = false, done1 = false;
+    bool& done = codebook == 0 ? done0 : done1;
+    if (!done) {
+      if (codebook == 0) cudaFuncSetAttribute(exl3_gemv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (EXL3_MAX_KS + 8) * 2);
+      else cudaFuncSetAttribute(exl3_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (EXL3_MAX_KS + 8) * 2);
+      done = true;
+    }
+  }
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = S; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cudaError_t err = codebook == 0 ? cudaLaunchKernelEx(&cfg, exl3_gemv_kernel<0>, a)
+                                  : cudaLaunchKernelEx(&cfg, exl3_gemv_kernel<1>, a);
+  return err == cudaSuccess ? 0 : -4;
+}

@@ -31,21 +31,27 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
   const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
   const __nv_bfloat16* Wb = W + (pair_expert ? static_cast<long long>(pair_expert[item]) * expert_stride : 0);
   const int R = rows_per_item;
-  // stage activations (zero rows beyond R)
-  for (int i = threadIdx.x; i < RB * K; i += blockDim.x) {
-    const int r = i / K, k = i - r * K;
-    float v = 0.f;
-    if (r < R) {
-      const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
-      if (act == 1) {
+  // stage activations (zero rows beyond R); plain rows are copied as 16-byte vectors
+  if (act == 0) {
+    const int KV8 = K >> 3;
+    for (int i = threadIdx.x; i < RB * KV8; i += blockDim.x) {
+      const int r = i / KV8, kv = i - r * KV8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < R) v = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(xr0 + r) * ldx + kv * 8);
+      reinterpret_cast<uint4*>(xs)[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < RB * K; i += blockDim.x) {
+      const int r = i / K, k = i - r * K;
+      float v = 0.f;
+      if (r < R) {
+        const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
         float g = __bfloat162float(xr[k]), u = __bfloat162float(xr[K + k]);
         if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
         v = g / (1.f + __expf(-g)) * u;
-      } else {
-        v = __bfloat162float(xr[k]);
       }
+      xs[i] = __float2bfloat16(v);
     }
-    xs[i] = __float2bfloat16(v);
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,17 +64,30 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
 #pragma unroll
   for (int r = 0; r < RB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
   const int KV = K >> 3;                        // 16-byte vectors per row
-#pragma unroll 2
-  for (int kv = lane; kv < KV; kv += 32) {
-    float a[8], b[8];
-    unpack8(__ldg(w0 + kv), a);
-    unpack8(__ldg(w1 + kv), b);
+  constexpr int BATCH = 8;                      // loads in flight per lane and column
+  for (int kv0 = lane; kv0 < KV; kv0 += 32 * BATCH) {
+    uint4 ra[BATCH], rb[BATCH];
 #pragma unroll
-    for (int r = 0; r < RB; ++r) {
-      float xv[8];
-      unpack8(*reinterpret_cast<const uint4*>(xs + r * K + kv * 8), xv);
+    for (int u = 0; u < BATCH; ++u) {
+      const int kv = kv0 + 32 * u;
+      ra[u] = kv < KV ? __ldg(w0 + kv) : make_uint4(0u, 0u, 0u, 0u);
+      rb[u] = kv < KV ? __ldg(w1 + kv) : make_uint4(0u, 0u, 0u, 0u);
+    }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { acc0[r] = fmaf(a[i], xv[i], acc0[r]); acc1[r] = fmaf(b[i], xv[i], acc1[r]); }
+    for (int u = 0; u < BATCH; ++u) {
+      const int kv = kv0 + 32 * u;
+      if (kv < KV) {
+        float a[8], b[8];
+        unpack8(ra[u], a);
+        unpack8(rb[u], b);
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+          float xv[8];
+          unpack8(*reinterpret_cast<const uint4*>(xs + r * K + kv * 8), xv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { acc0[r] = fmaf(a[i], xv[i], acc0[r]); acc1[r] = fmaf(b[i], xv[i], acc1[r]); }
+        }
+      }
     }
   }
 #pragma unroll

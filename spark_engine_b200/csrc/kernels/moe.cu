@@ -196,8 +196,9 @@ __global__ void moe_combine_kernel(float* __restrict__ res, const TY* __restrict
                                    const float* __restrict__ wts, int top_k, const __nv_bfloat16* __restrict__ shared,
                                    const float* __restrict__ sg, int H, __nv_bfloat16* __restrict__ out_bf16) {
   const int r = blockIdx.x;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int k = 0; k < top_k; ++k) {
       const int pi = r * top_k + k;
       const int row = inv_perm ? inv_perm[pi] : pi;
@@ -244,10 +245,10 @@ extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int
                                  int top_k, const void* shared, const float* sg, int H, void* out_bf16, cudaStream_t s) {
   if (R <= 0) return 0;
   if (y_f32)
-    moe_combine_kernel<float><<<R, 256, 0, s>>>(res, (const float*)y, inv_perm, wts, top_k, (const __nv_bfloat16*)shared, sg, H,
+    moe_combine_kernel<float><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const float*)y, inv_perm, wts, top_k, (const __nv_bfloat16*)shared, sg, H,
                                                 (__nv_bfloat16*)out_bf16);
   else
-    moe_combine_kernel<__nv_bfloat16><<<R, 256, 0, s>>>(res, (const __nv_bfloat16*)y, inv_perm, wts, top_k,
+    moe_combine_kernel<__nv_bfloat16><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const __nv_bfloat16*)y, inv_perm, wts, top_k,
                                                         (const __nv_bfloat16*)shared, sg, H, (__nv_bfloat16*)out_bf16);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

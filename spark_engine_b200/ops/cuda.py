@@ -31,7 +31,7 @@ _SIGS = {
     "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_embed": [vp, vp, vp, i32, i32, vp],
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
-    "spark_argmax": [vp, i32, i32, vp, vp, vp],
+    "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
@@ -43,7 +43,7 @@ _SIGS = {
     "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp],
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp],
-    "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+    "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
                         f32, i32, vp],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
@@ -51,7 +51,7 @@ _SIGS = {
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-_KERNELS_PER_CALL = {"spark_attn_decode": 2, "spark_moe_sort": 3}
+_KERNELS_PER_CALL = {"spark_attn_decode": 2, "spark_moe_sort": 3, "spark_argmax": 2}
 _launches = 0
 
 
@@ -201,20 +201,16 @@ def dense_linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> tor
 
 
 # ----------------------------------------------------------------------------- EXL3
-def _pick_slices(K: int, N: int, items: int) -> int:
-    """K-slices so that the grid covers the GPU about twice; (K/128) % S == 0 and slice <= 2048."""
+def _pick_slices(K: int) -> int:
+    """K-slices per 128-column strip = CTAs of one cluster (<= 8): aim at 256-deep slices so that one
+    batch of loads per warp covers the whole slice."""
     blocks = K // 128
     best = 1
-    for s in range(1, blocks + 1):
-        if blocks % s:
-            continue
-        if K // s > 2048:
-            continue
-        best = s
-        if (N // 128) * s * items >= 296:
-            break
-    if K // best > 2048:
-        best = blocks
+    for s in range(1, 9):
+        if blocks % s == 0 and K // s >= 128:
+            best = s
+            if K // s <= 256:
+                break
     return best
 
 
@@ -223,15 +219,13 @@ def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, p
     assert w.bits == 4, "the GEMV kernel handles 4 bpw"
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     K, N = w.k, w.n
-    S = _pick_slices(K, N, items)
+    S = _pick_slices(K)
     dev = x.device
-    part = scratch("exl3_partial", items * S * 16 * N, torch.float32, dev)
-    cnt = scratch("exl3_counters", items * (N // 128), torch.int32, dev, zero=True)
     y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
     tw = (K // 16) * (N // 16) * 32
     es = (tw, K, N) if w.experts else (0, 0, 0)
     rc = lib().spark_exl3_gemv(P(x), x.stride(0), P(w.trellis), P(w.suh), P(w.svh), es[0], es[1], es[2], P(y), N,
-                               int(out_f32), P(part), P(cnt), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
+                               int(out_f32), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
                                act, float(limit), 0 if w.kind == "mul1" else 1, stream())
     check(rc, "spark_exl3_gemv")
     return y
@@ -318,7 +312,9 @@ def residual_add(res, delta):
 def argmax(logits):
     R, V = logits.shape
     ids = torch.empty(R, dtype=torch.int32, device=logits.device)
-    lib().spark_argmax(P(logits.contiguous()), R, V, P(ids), None, stream())
+    pv = scratch("argmax_v", R * 64, torch.float32, logits.device)
+    pi = scratch("argmax_i", R * 64, torch.int32, logits.device)
+    lib().spark_argmax(P(logits.contiguous()), R, V, P(ids), None, P(pv), P(pi), stream())
     return ids
 
 
@@ -475,7 +471,7 @@ def kda_mixer(mixer, pre, lr, plan, commit):
     return None      # KDA runs the generic path (projections on the kernels, recurrence in ATen) for now
 
 
-ATT_TS = 256
+ATT_TS = 64
 
 
 def attn_mixer(mixer, qkv, plan, seqs):
