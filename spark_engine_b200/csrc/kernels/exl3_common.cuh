@@ -16,7 +16,7 @@ __device__ __forceinline__ uint32_t exl3_pair(uint32_t s0, uint32_t s1) {
   if (CB == 0) {   // mul1: fp16(1024 + bytesum) * k_inv + k_bias, fused (one rounding)
     const uint32_t a = __dp4a(s0 * EXL3_MUL1, 0x01010101u, 0x6400u);     // 0x6400 + sum == bits of fp16(1024+sum)
     const uint32_t b = __dp4a(s1 * EXL3_MUL1, 0x01010101u, 0x6400u);
-    const uint32_t packed = a | (b << 16);
+    const uint32_t packed = __byte_perm(a, b, 0x5410);
     const __half2 inv = __halves2half2(__ushort_as_half(0x1eee), __ushort_as_half(0x1eee));
     const __half2 bias = __halves2half2(__ushort_as_half(0xc931), __ushort_as_half(0xc931));
     const __half2 v = __hfma2(*reinterpret_cast<const __half2*>(&packed), inv, bias);

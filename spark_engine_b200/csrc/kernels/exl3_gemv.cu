@@ -4,9 +4,9 @@
 // thread-block cluster of S CTAs along the K-slices of one 128-column strip: every CTA streams the
 // 128-byte tiles of its slice (all loads of a warp are issued before the first decode, so one DRAM
 // round trip covers 16 tiles), decodes 8 weights per lane straight into m16n8k16 B fragments and
-// multiplies with the <= 16 activation rows; the S partial strips are then summed through distributed
-// shared memory by cluster rank 0 in slice order (no global scratch, no atomics), Hadamard-transformed
-// and scaled.  Fixed reduction order => bitwise reproducible and independent of the rows in flight.
+// multiplies with the <= 16 activation rows; every CTA then stores its partial strip into the shared
+// memory of cluster rank 0 (distributed shared memory), which sums the slices in slice order (no global
+// scratch, no atomics), applies the output Hadamard transform and scales.  Fixed reduction order => bitwise reproducible and independent of the rows in flight.
 // M <= 16 is bandwidth / decode-ALU bound, so the warp-level MMA feeds it; GEMM-shaped EXL3 work goes
 // through exl3_reconstruct to the tcgen05 GEMM.
 // Replaces engine-rs/shim/qwen_exl3.cuh:427-626 (gemv_kernel / gemv_fused_kernel / finish_kernel) and
@@ -30,17 +30,17 @@ struct Exl3GemvArgs {
 
 constexpr int EXL3_MAX_KS = 2048;              // K-slice per CTA (activation slice lives in shared memory)
 
-template <int CB>
-__global__ void __launch_bounds__(256)
+template <int CB, bool HI>       // HI: more than 8 activation rows (the upper half of the MMA tile is live)
+__global__ void __launch_bounds__(256, 6)      // 40 registers: 6 CTAs (48 warps) per SM hide the decode dependency chains
 exl3_gemv_kernel(Exl3GemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
-  __shared__ __align__(16) float sb[16 * 128];
   cg::cluster_group cluster = cg::this_cluster();
   const int strip = blockIdx.x, slice = blockIdx.y, item = blockIdx.z;
   const int NT = a.N >> 4;
   const int Ks = a.K / a.S, kts = Ks >> 4;
   const int ldh = Ks + 8;
+  float* red = reinterpret_cast<float*>(smem_dyn + 16 * ldh * 2);   // [S][R][128]: slice partials, used on rank 0
   const int k_begin = slice * Ks;
   const int e = a.pair_expert ? a.pair_expert[item] : 0;
   const int xr0 = a.pair_row ? a.pair_row[item] : item * a.R;
@@ -51,9 +51,15 @@ exl3_gemv_kernel(Exl3GemvArgs a) {
   // ---- issue this warp's trellis loads first (they do not depend on the prologue)
   const int nt = strip * 8 + warp;
   const uint32_t* tw = a.trellis + e * a.t_stride + (static_cast<size_t>(slice) * kts * NT + nt) * 32 + lane;
-  uint32_t cur[16];
+  // (kts is a multiple of 8: batches of 8 tiles, the next batch is in flight while one is decoded)
+  uint32_t cur[8], nxt[8];
+  const size_t tstep = static_cast<size_t>(NT) * 32;
 #pragma unroll
-  for (int u = 0; u < 16; ++u) cur[u] = (u < kts) ? __ldg(tw + static_cast<size_t>(u) * NT * 32) : 0u;
+  for (int u = 0; u < 8; ++u) cur[u] = __ldg(tw + u * tstep);
+  if (kts > 8) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) nxt[u] = __ldg(tw + (8 + u) * tstep);
+  }
 
   // ---- prologue: xh = had128(x * suh) / sqrt(128) for this K-slice; one warp per (row, 128-block)
   const __half* suh = a.suh + e * a.suh_stride + k_begin;
@@ -85,72 +91,80 @@ exl3_gemv_kernel(Exl3GemvArgs a) {
     uint2 o; o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
     *reinterpret_cast<uint2*>(xh + r * ldh + b * 128 + lane * 4) = o;
   }
+  if (R < 16) {            // the zero row read by lanes without an activation row
+    for (int i = threadIdx.x; i < (Ks >> 1); i += blockDim.x) reinterpret_cast<uint32_t*>(xh + R * ldh)[i] = 0u;
+  }
   __syncthreads();
 
-  // ---- main loop
+  // ---- main loop.  Lanes whose activation row does not exist read a zeroed row, so the loop has no selects.
   float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
   const bool lo_row = g < R, hi_row = (g + 8) < R;
+  const __half* row_lo = xh + (lo_row ? g : R) * ldh + 2 * t;
+  const __half* row_hi = xh + (hi_row ? g + 8 : R) * ldh + 2 * t;
 #pragma unroll 1
-  for (int kb = 0; kb < kts; kb += 16) {
-    if (kb > 0) {
+  for (int kb = 0; kb < kts; kb += 8) {
 #pragma unroll
-      for (int u = 0; u < 16; ++u) cur[u] = (kb + u < kts) ? __ldg(tw + static_cast<size_t>(kb + u) * NT * 32) : 0u;
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t prev = __shfl_sync(0xffffffffu, cur[u], (lane + 31) & 31);
+      uint32_t w[4];
+      exl3_decode8_b4<CB>(cur[u], prev, w);
+      uint32_t af[4];
+      af[0] = *reinterpret_cast<const uint32_t*>(row_lo + (kb + u) * 16);
+      af[2] = *reinterpret_cast<const uint32_t*>(row_lo + (kb + u) * 16 + 8);
+      if (HI) {
+        af[1] = *reinterpret_cast<const uint32_t*>(row_hi + (kb + u) * 16);
+        af[3] = *reinterpret_cast<const uint32_t*>(row_hi + (kb + u) * 16 + 8);
+      } else {
+        af[1] = 0u; af[3] = 0u;
+      }
+      mma_f16_16816(d0, af, w[0], w[1]);       // columns 0..7 of the n-tile
+      mma_f16_16816(d1, af, w[2], w[3]);       // columns 8..15
     }
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      if (kb + u < kts) {
-        const uint32_t prev = __shfl_sync(0xffffffffu, cur[u], (lane + 31) & 31);
-        uint32_t w[4];
-        exl3_decode8_b4<CB>(cur[u], prev, w);
-        uint32_t af[4];
-        const __half* xa = xh + (kb + u) * 16 + 2 * t;
-        af[0] = lo_row ? *reinterpret_cast<const uint32_t*>(xa + g * ldh) : 0u;
-        af[1] = hi_row ? *reinterpret_cast<const uint32_t*>(xa + (g + 8) * ldh) : 0u;
-        af[2] = lo_row ? *reinterpret_cast<const uint32_t*>(xa + g * ldh + 8) : 0u;
-        af[3] = hi_row ? *reinterpret_cast<const uint32_t*>(xa + (g + 8) * ldh + 8) : 0u;
-        mma_f16_16816(d0, af, w[0], w[1]);       // columns 0..7 of the n-tile
-        mma_f16_16816(d1, af, w[2], w[3]);       // columns 8..15
-      }
+    for (int u = 0; u < 8; ++u) cur[u] = nxt[u];
+    if (kb + 16 < kts) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) nxt[u] = __ldg(tw + (kb + 16 + u) * tstep);
     }
   }
+  // ---- every CTA pushes its partial strip into the shared memory of cluster rank 0 (plain remote stores,
+  //      no round trip), one cluster barrier, then rank 0 sums the slices in rank order:
+  //      y = had128(sum) * svh.
   {
+    float* dst = (a.S > 1 ? cluster.map_shared_rank(red, 0) : red) + static_cast<size_t>(slice) * R * 128;
     const int c = warp * 16 + 2 * t;
     if (lo_row) {
-      sb[g * 128 + c] = d0[0]; sb[g * 128 + c + 1] = d0[1];
-      sb[g * 128 + c + 8] = d1[0]; sb[g * 128 + c + 9] = d1[1];
+      *reinterpret_cast<float2*>(dst + g * 128 + c) = make_float2(d0[0], d0[1]);
+      *reinterpret_cast<float2*>(dst + g * 128 + c + 8) = make_float2(d1[0], d1[1]);
     }
     if (hi_row) {
-      sb[(g + 8) * 128 + c] = d0[2]; sb[(g + 8) * 128 + c + 1] = d0[3];
-      sb[(g + 8) * 128 + c + 8] = d1[2]; sb[(g + 8) * 128 + c + 9] = d1[3];
+      *reinterpret_cast<float2*>(dst + (g + 8) * 128 + c) = make_float2(d0[2], d0[3]);
+      *reinterpret_cast<float2*>(dst + (g + 8) * 128 + c + 8) = make_float2(d1[2], d1[3]);
     }
   }
-  // ---- reduce the K-slices over distributed shared memory (rank order), then y = had128(acc) * svh
   if (a.S > 1) cluster.sync(); else __syncthreads();
-  if (slice == 0) {
-    const __half* svh = a.svh + e * a.svh_stride + strip * 128;
-    for (int r = warp; r < R; r += 8) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int s = 0; s < a.S; ++s) {
-        const float* src = (a.S > 1) ? cluster.map_shared_rank(sb, s) : sb;
-        const float4 p = *reinterpret_cast<const float4*>(src + r * 128 + lane * 4);
-        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
-      }
-      fwht128_warp(v, lane);
-      const uint2 sraw = *reinterpret_cast<const uint2*>(svh + lane * 4);
-      const __half2* sp = reinterpret_cast<const __half2*>(&sraw);
-      const float2 s0 = __half22float2(sp[0]), s1 = __half22float2(sp[1]);
-      v[0] *= INV_SQRT_128 * s0.x; v[1] *= INV_SQRT_128 * s0.y; v[2] *= INV_SQRT_128 * s1.x; v[3] *= INV_SQRT_128 * s1.y;
-      const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
-      if (a.out_f32) {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
-      } else {
-        __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
-        uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
-      }
+  if (slice != 0) return;
+  const __half* svh = a.svh + e * a.svh_stride + strip * 128;
+  for (int r = warp; r < R; r += 8) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < a.S; ++s) {
+      const float4 p = *reinterpret_cast<const float4*>(red + (static_cast<size_t>(s) * R + r) * 128 + lane * 4);
+      v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+    }
+    fwht128_warp(v, lane);
+    const uint2 sraw = *reinterpret_cast<const uint2*>(svh + lane * 4);
+    const __half2* sp = reinterpret_cast<const __half2*>(&sraw);
+    const float2 s0 = __half22float2(sp[0]), s1 = __half22float2(sp[1]);
+    v[0] *= INV_SQRT_128 * s0.x; v[1] *= INV_SQRT_128 * s0.y; v[2] *= INV_SQRT_128 * s1.x; v[3] *= INV_SQRT_128 * s1.y;
+    const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
+    if (a.out_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
+      uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
     }
   }
-  if (a.S > 1) cluster.sync();      // peers keep their shared memory alive until rank 0 has read it
 }
 
 }  // namespace spark
@@ -176,14 +190,16 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(N / 128, S, items);
   cfg.blockDim = dim3(256);
-  cfg.dynamicSmemBytes = 16 * (K / S + 8) * 2;
+  cfg.dynamicSmemBytes = 16 * (K / S + 8) * 2 + S * rows_per_item * 128 * 4;
+  const bool hi = rows_per_item > 8;
+  void (*kern)(Exl3GemvArgs) = codebook == 0 ? (hi ? exl3_gemv_kernel<0, true> : exl3_gemv_kernel<0, false>)
+                                             : (hi ? exl3_gemv_kernel<1, true> : exl3_gemv_kernel<1, false>);
   {
-    static bool done0 = false, done1 = false;
-    bool& done = codebook == 0 ? done0 : done1;
-    if (!done) {
-      if (codebook == 0) cudaFuncSetAttribute(exl3_gemv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (EXL3_MAX_KS + 8) * 2);
-      else cudaFuncSetAttribute(exl3_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (EXL3_MAX_KS + 8) * 2);
-      done = true;
+    static bool done[4] = {false, false, false, false};
+    const int id = (codebook ? 2 : 0) + (hi ? 1 : 0);
+    if (!done[id]) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (EXL3_MAX_KS + 8) * 2 + 8 * 16 * 128 * 4);
+      done[id] = true;
     }
   }
   cfg.stream = s;
@@ -191,7 +207,6 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = S; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  cudaError_t err = codebook == 0 ? cudaLaunchKernelEx(&cfg, exl3_gemv_kernel<0>, a)
-                                  : cudaLaunchKernelEx(&cfg, exl3_gemv_kernel<1>, a);
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, a);
   return err == cudaSuccess ? 0 : -4;
 }

@@ -205,6 +205,9 @@ def _pick_slices(K: int) -> int:
     """K-slices per 128-column strip = CTAs of one cluster (<= 8): aim at 256-deep slices so that one
     batch of loads per warp covers the whole slice."""
     blocks = K // 128
+    forced = int(os.environ.get("SPARK_EXL3_S", "0"))
+    if forced and blocks % forced == 0:
+        return forced
     best = 1
     for s in range(1, 9):
         if blocks % s == 0 and K // s >= 128:
