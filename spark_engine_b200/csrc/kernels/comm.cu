@@ -1,0 +1,286 @@
+// Peer-memory collectives over NVLink / NVSwitch (P2P loads and stores issued from ordinary CTAs).
+//
+//   arena management : cudaMalloc'd arena per rank, cudaIpc handle export / import
+//   barrier          : sequence-number barrier across ranks
+//   allreduce_rows   : one-shot all-reduce of R rows (push to every peer, rank-ordered fp32 sum), optionally
+//                      fused with residual add + RMSNorm  (decode / verify rows)
+//   rs_push / rs_finish / ag_wait : reduce-scatter by row blocks (+ residual + RMSNorm on the owned rows) and
+//                      all-gather of the result (prefill, sequence-parallel style)
+//   ag_push          : all-gather of row blocks into every peer's arena (prologue of the AG-fused GEMM)
+//   ep_dispatch / ep_combine : expert-parallel all-to-all, see ep.cu
+//
+// Sums are taken in rank order from fp32 slots, so every rank computes bit-identical results and the
+// result equals the local rank-ordered sum (the contract of the reference's RDMA transport,
+// engine-rs/shim/rdma_arn.cu:84-125,104-113).  Two slot sets alternate by sequence parity: a rank can only
+// reach sequence s+2 after every peer has finished reading set s.
+#include "../common/comm.cuh"
+
+namespace spark {
+
+// ------------------------------------------------------------------------------------------ barrier
+// flags: u32 [world] in every arena at flag_off.  Rank r writes seq into slot r of every peer, then waits
+// for all slots of its own arena.
+__global__ void comm_barrier_kernel(CommCtx c, long long flag_off, uint32_t seq) {
+  const int p = threadIdx.x;
+  if (p < c.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(c.peers[p] + flag_off) + c.rank, seq);
+    wait_flag(c, reinterpret_cast<const uint32_t*>(c.peers[c.rank] + flag_off) + p, seq, p);
+  }
+}
+
+// (ArRows, ar_rows_tail and ar_arrive_and_is_last live in comm.cuh: the fused GEMV epilogues share them)
+
+// grid = R CTAs (one row each), 256 threads.  N % 4 == 0.
+__global__ void __launch_bounds__(256)
+allreduce_rows_kernel(ArRows a) {
+  __shared__ float red[8];
+  __shared__ int last_s;
+  const int r = blockIdx.x, W = a.c.world;
+  const size_t set = static_cast<size_t>(a.seq & 1) * W * a.rows_cap * a.N;
+  for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
+    float4 v;
+    if (a.in_f32) v = ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(r) * a.N + i);
+    else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(r) * a.N + i);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+      v = make_float4(f0.x, f0.y, f1.x, f1.y);
+    }
+    for (int p = 0; p < W; ++p) {
+      float* dst = reinterpret_cast<float*>(a.c.peers[p] + a.slot_off) + set + (static_cast<size_t>(a.c.rank) * a.rows_cap + r) * a.N + i;
+      st_f4(dst, v);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a, gridDim.x) ? 1 : 0;
+  __syncthreads();
+  // every CTA finishes its own row once all flags are in
+  ar_rows_tail(a, r, gridDim.x, red);
+}
+
+// ------------------------------------------------------------------------------------------ RS / AG by rows
+struct RsAg {
+  CommCtx c;
+  long long slot_off;        // float partial slots on the OWNER: [world(src)][rows_per_rank * N]
+  long long out_off;         // gathered result rows in every arena: bf16 [M, N]
+  long long flag_rs_off, flag_ag_off;   // u32 [world] each
+  uint32_t seq;
+  int M, N, rows_per_rank;   // M = world * rows_per_rank (padded)
+  const void* in; int in_f32;            // local partial [M, N]
+  int* counter;
+  float* res;                            // fp32 residual of the OWNED rows [rows_per_rank, N] (optional)
+  const float* norm_w; float eps;
+};
+
+// push every row block to its owner (grid-stride over rows), then flag all owners
+__global__ void __launch_bounds__(256)
+rs_push_kernel(RsAg a) {
+  const int W = a.c.world;
+  for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
+    const int owner = row / a.rows_per_rank, lr = row - owner * a.rows_per_rank;
+    float* dst = reinterpret_cast<float*>(a.c.peers[owner] + a.slot_off) + (static_cast<size_t>(a.c.rank) * a.rows_per_rank + lr) * a.N;
+    for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
+      float4 v;
+      if (a.in_f32) v = ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(row) * a.N + i);
+      else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(row) * a.N + i);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+        v = make_float4(f0.x, f0.y, f1.x, f1.y);
+      }
+      st_f4(dst + i, v);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.counter = 0;
+      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_rs_off) + a.c.rank, a.seq);
+    }
+  }
+}
+
+// owner: wait all sources, rank-ordered sum (+ residual + RMSNorm) of the owned rows, push the bf16 result row
+// into every peer's gathered buffer, then flag.  grid-stride over the owned rows.
+__global__ void __launch_bounds__(256)
+rs_finish_ag_push_kernel(RsAg a) {
+  __shared__ float red[8];
+  __shared__ int ok_s;
+  const int W = a.c.world;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < W && !wait_flag(a.c, reinterpret_cast<const uint32_t*>(a.c.peers[a.c.rank] + a.flag_rs_off) + threadIdx.x, a.seq, threadIdx.x)) ok_s = 0;
+  __syncthreads();
+  if (ok_s) {
+    const float* slots = reinterpret_cast<const float*>(a.c.peers[a.c.rank] + a.slot_off);
+    for (int lr = blockIdx.x; lr < a.rows_per_rank; lr += gridDim.x) {
+      float ss = 0.f;
+      float4 keep[4];                    // N <= 256 threads * 4 * 4 = 4096 per pass; larger N loops twice
+      int ki = 0;
+      for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4, ++ki) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < W; ++p) {
+          const float4 v = ld_f4(slots + (static_cast<size_t>(p) * a.rows_per_rank + lr) * a.N + i);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (a.res) {
+          const float4 rv = ld_f4(a.res + static_cast<size_t>(lr) * a.N + i);
+          acc.x += rv.x; acc.y += rv.y; acc.z += rv.z; acc.w += rv.w;
+          st_f4(a.res + static_cast<size_t>(lr) * a.N + i, acc);
+        }
+        ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        if (ki < 4) keep[ki] = acc;
+      }
+      float rs = 1.f;
+      if (a.norm_w) {
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        __syncthreads();
+        rs = rsqrtf(tot / a.N + a.eps);
+      }
+      const int grow = a.c.rank * a.rows_per_rank + lr;
+      ki = 0;
+      for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4, ++ki) {
+        float4 v = keep[ki < 4 ? ki : 3];
+        if (a.norm_w) { const float4 g = ld_f4(a.norm_w + i); v.x *= rs * g.x; v.y *= rs * g.y; v.z *= rs * g.z; v.w *= rs * g.w; }
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+        for (int p = 0; p < W; ++p)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.c.peers[p] + a.out_off) + static_cast<size_t>(grow) * a.N + i) = o;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.counter = 0;
+      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_ag_off) + a.c.rank, a.seq);
+    }
+  }
+}
+
+__global__ void wait_flags_kernel(CommCtx c, long long flag_off, uint32_t seq) {
+  if (threadIdx.x < c.world)
+    wait_flag(c, reinterpret_cast<const uint32_t*>(c.peers[c.rank] + flag_off) + threadIdx.x, seq, threadIdx.x);
+}
+
+// ------------------------------------------------------------------------------------------ AG push
+// Copy this rank's row block x [rows, K] (bf16) into every peer's gathered buffer at row rank*rows, then flag.
+__global__ void __launch_bounds__(256)
+ag_push_kernel(CommCtx c, const __nv_bfloat16* __restrict__ x, int rows, int K, long long buf_off, long long flag_off,
+               uint32_t seq, int* counter) {
+  const int W = c.world;
+  const int KV = K >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * K);
+    for (int i = threadIdx.x; i < KV; i += blockDim.x) {
+      const uint4 v = src[i];
+      for (int p = 0; p < W; ++p)
+        reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.peers[p] + buf_off) + (static_cast<size_t>(c.rank) * rows + r) * K)[i] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *counter = 0;
+      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(c.peers[p] + flag_off) + c.rank, seq);
+    }
+  }
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+// ------------------------------------------------------------------------------------------ host API
+extern "C" void* spark_arena_alloc(long long bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
+  cudaMemset(p, 0, bytes);
+  return p;
+}
+extern "C" void spark_arena_free(void* p) { cudaFree(p); }
+extern "C" int spark_ipc_get_handle(void* p, void* out64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return -1;
+  memcpy(out64, &h, sizeof(h));
+  return 0;
+}
+extern "C" void* spark_ipc_open_handle(const void* in64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in64, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return nullptr;
+  return p;
+}
+extern "C" void spark_ipc_close(void* p) { cudaIpcCloseMemHandle(p); }
+
+struct HostCtx { void* peers[8]; int rank, world; unsigned long long wait_ns; int* status; };
+static CommCtx to_ctx(const HostCtx* h) {
+  CommCtx c;
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) c.peers[i] = static_cast<uint8_t*>(h->peers[i]);
+  c.rank = h->rank; c.world = h->world; c.wait_ns = h->wait_ns; c.status = h->status;
+  return c;
+}
+
+extern "C" int spark_comm_barrier(const HostCtx* h, long long flag_off, unsigned seq, cudaStream_t s) {
+  comm_barrier_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long long flag_off, unsigned seq, int rows_cap,
+                                    int R, int N, const void* in, int in_f32, int* counter, float* res,
+                                    const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (N % 4 || R > rows_cap) return -5;
+  ArRows a;
+  a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = seq; a.rows_cap = rows_cap; a.R = R; a.N = N;
+  a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32;
+  allreduce_rows_kernel<<<R, 256, 0, s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Reduce-scatter by row blocks (+ residual + RMSNorm on the owned rows) then all-gather of the bf16 result into
+// every arena at out_off.  M must be world * rows_per_rank.  Three launches; the last only waits.
+extern "C" int spark_rs_ag_rows(const HostCtx* h, long long slot_off, long long out_off, long long flag_rs_off,
+                                long long flag_ag_off, unsigned seq, int M, int N, int rows_per_rank, const void* in,
+                                int in_f32, int* counter, float* res, const float* norm_w, float eps, int push_only,
+                                cudaStream_t s) {
+  if (M <= 0) return 0;
+  if (N % 4 || N > 4096) return -5;
+  RsAg a;
+  a.c = to_ctx(h); a.slot_off = slot_off; a.out_off = out_off; a.flag_rs_off = flag_rs_off; a.flag_ag_off = flag_ag_off;
+  a.seq = seq; a.M = M; a.N = N; a.rows_per_rank = rows_per_rank; a.in = in; a.in_f32 = in_f32; a.counter = counter;
+  a.res = res; a.norm_w = norm_w; a.eps = eps;
+  if (push_only != 2) {
+    int grid = M < 592 ? M : 592;
+    rs_push_kernel<<<grid, 256, 0, s>>>(a);
+  }
+  if (push_only == 1) return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  int grid2 = rows_per_rank < 592 ? rows_per_rank : 592;
+  a.counter = counter + 1;
+  rs_finish_ag_push_kernel<<<grid2, 256, 0, s>>>(a);
+  wait_flags_kernel<<<1, 32, 0, s>>>(a.c, flag_ag_off, seq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int spark_ag_push(const HostCtx* h, const void* x, int rows, int K, long long buf_off, long long flag_off,
+                             unsigned seq, int* counter, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (K % 8) return -5;
+  int grid = rows < 296 ? rows : 296;
+  ag_push_kernel<<<grid, 256, 0, s>>>(to_ctx(h), (const __nv_bfloat16*)x, rows, K, buf_off, flag_off, seq, counter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int spark_wait_flags(const HostCtx* h, long long flag_off, unsigned seq, cudaStream_t s) {
+  wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -12,6 +12,7 @@
 // Replaces engine-rs/shim/qwen_exl3.cuh:427-626 (gemv_kernel / gemv_fused_kernel / finish_kernel) and
 // the decode half of moe_exl3.cuh:273-399.
 #include "exl3_common.cuh"
+#include "../common/comm.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -26,6 +27,8 @@ struct Exl3GemvArgs {
   void* y; int ldy; int out_f32;                // [items*R, N]
   const int* pair_expert; const int* pair_row;
   int R, K, N, S, act; float limit;
+  int fuse_ar;                                  // 1: row-parallel layer under TP: the epilogue pushes the strip to every
+  ArRows ar;                                    //    rank and the last CTA does all-reduce + residual + RMSNorm
 };
 
 constexpr int EXL3_MAX_KS = 2048;              // K-slice per CTA (activation slice lives in shared memory)
@@ -156,6 +159,14 @@ exl3_gemv_kernel(Exl3GemvArgs a) {
     const __half2* sp = reinterpret_cast<const __half2*>(&sraw);
     const float2 s0 = __half22float2(sp[0]), s1 = __half22float2(sp[1]);
     v[0] *= INV_SQRT_128 * s0.x; v[1] *= INV_SQRT_128 * s0.y; v[2] *= INV_SQRT_128 * s1.x; v[3] *= INV_SQRT_128 * s1.y;
+    if (a.fuse_ar) {
+      // fused all-reduce: this rank's partial strip goes straight into slot[rank] of every peer's arena
+      const size_t so = static_cast<size_t>(a.ar.seq & 1) * a.ar.c.world * a.ar.rows_cap * a.ar.N +
+                        (static_cast<size_t>(a.ar.c.rank) * a.ar.rows_cap + r) * a.ar.N + strip * 128 + lane * 4;
+      for (int p = 0; p < a.ar.c.world; ++p)
+        st_f4(reinterpret_cast<float*>(a.ar.c.peers[p] + a.ar.slot_off) + so, make_float4(v[0], v[1], v[2], v[3]));
+      continue;
+    }
     const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
     if (a.out_f32) {
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
@@ -164,6 +175,16 @@ exl3_gemv_kernel(Exl3GemvArgs a) {
       uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
       *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
     }
+  }
+  if (a.fuse_ar) {
+    // the last strip of this rank to finish raises the flags, waits (bounded) for every peer's flag and
+    // reduces all rows: sum in rank order + residual + RMSNorm
+    __shared__ int last_s;
+    __shared__ float red_s[8];
+    __syncthreads();
+    if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a.ar, gridDim.x) ? 1 : 0;
+    __syncthreads();
+    if (last_s) ar_rows_tail(a.ar, 0, 1, red_s);
   }
 }
 
@@ -176,7 +197,7 @@ using namespace spark;
 extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, const void* suh, const void* svh,
                                long long t_stride_words, long long suh_stride, long long svh_stride, void* y, int ldy,
                                int out_f32, const int* pair_expert, const int* pair_row, int items, int rows_per_item,
-                               int K, int N, int S, int act, float limit, int codebook, cudaStream_t s) {
+                               int K, int N, int S, int act, float limit, int codebook, cudaStream_t s, const void* ar_args) {
   if (items <= 0 || rows_per_item <= 0) return 0;
   if (rows_per_item > 16 || (K & 127) || (N & 127) || S < 1 || S > 8 || ((K >> 7) % S) || K / S > EXL3_MAX_KS) return -5;
   if ((ldx & 3) || (ldy & 3)) return -5;
@@ -187,6 +208,12 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   a.y = y; a.ldy = ldy; a.out_f32 = out_f32;
   a.pair_expert = pair_expert; a.pair_row = pair_row;
   a.R = rows_per_item; a.K = K; a.N = N; a.S = S; a.act = act; a.limit = limit;
+  a.fuse_ar = 0;
+  if (ar_args) {
+    if (items != 1) return -5;
+    a.fuse_ar = 1;
+    a.ar = *static_cast<const ArRows*>(ar_args);
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(N / 128, S, items);
   cfg.blockDim = dim3(256);

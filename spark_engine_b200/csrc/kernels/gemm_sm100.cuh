@@ -12,7 +12,7 @@
 // Replaces the reference's cuBLAS/ATen prefill GEMMs (engine-rs/shim/shim.cpp:253-288,1028-1106) and
 // its mma.sync grouped GEMMs (engine-rs/shim/moe_exl3.cuh:521-1233); none of those has a tcgen05 path.
 #pragma once
-#include "../common/ptx.cuh"
+#include "../common/comm.cuh"
 
 namespace spark {
 
@@ -31,6 +31,10 @@ struct GemmArgs {
   int ab_fmt;                  // operand format of A and B: 1 = bf16, 0 = fp16
   int gate_up_F;               // > 0: B rows [f0, f0+BN/2) and [F+f0, ...) form one tile (SwiGLU epilogue)
   int* status;
+  // all-gather fused into the A operand: rows [src*ag_rows, (src+1)*ag_rows) of A were pushed into the local
+  // arena by rank src; the TMA producer waits (bounded) for flag[src] >= ag_seq before the first tile of
+  // that block and visits its own block first.  ag_flags == nullptr: plain GEMM.
+  const uint32_t* ag_flags; uint32_t ag_seq; int ag_rows, ag_rank, ag_world; unsigned long long ag_wait_ns;
 };
 
 struct TileCoord {
@@ -47,6 +51,11 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& g, int t) {
     c.a_row0 = e.x; c.row_end = e.y; c.expert = e.z;
     b_base = e.z * g.b_rows_per_expert;
   } else {
+    if (g.ag_flags != nullptr) {          // rotate the m-tiles so that this rank's own row block comes first
+      const int num_m = g.num_tiles / g.num_n_tiles;
+      const int per = (g.ag_rows + GEMM_BM - 1) / GEMM_BM;
+      mt = (mt + g.ag_rank * per) % num_m;
+    }
     c.a_row0 = mt * GEMM_BM; c.row_end = g.M; c.expert = 0;
   }
   if (g.gate_up_F > 0) {
@@ -113,8 +122,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
+      uint32_t ag_seen = 0;                 // bit src set: rank src's block has arrived
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         TileCoord tc = tile_coord<BN, GROUPED>(g, t);
+        if (!GROUPED && g.ag_flags != nullptr) {
+          // a 128-row tile may straddle two source blocks when ag_rows % 128 != 0: wait for both
+          const int s0 = tc.a_row0 / g.ag_rows, s1 = min(g.ag_world - 1, (tc.a_row0 + GEMM_BM - 1) / g.ag_rows);
+          for (int src = s0; src <= s1 && ok; ++src) {
+            if (src == g.ag_rank || (ag_seen >> src) & 1u) continue;
+            CommCtx cc; cc.wait_ns = g.ag_wait_ns; cc.status = g.status;
+            if (!wait_flag(cc, g.ag_flags + src, g.ag_seq, src)) { ok = false; break; }
+            ag_seen |= 1u << src;
+            asm volatile("fence.proxy.async;" ::: "memory");   // peer's generic-proxy stores -> our TMA reads
+          }
+          if (!ok) break;
+        }
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, kb); ok = false; break;
@@ -207,11 +229,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc<TMEM_COLS>(tmem_base); }
+  if (threadIdx.x == 0) epi.cta_done(gridDim.x);
 }
 
 // ---------------------------------------------------------------- epilogues
 struct EpiStoreBf16 {
   __nv_bfloat16* C; int ldc; int N;
+  __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const { return g; }
   __device__ __forceinline__ void operator()(const TileCoord&, int row, int col, const float (&v)[32]) const {
     __nv_bfloat16* dst = C + static_cast<size_t>(row) * ldc + col;
@@ -233,6 +257,7 @@ struct EpiStoreBf16 {
 
 struct EpiStoreF32 {
   float* C; int ldc; int N;
+  __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const { return g; }
   __device__ __forceinline__ void operator()(const TileCoord&, int row, int col, const float (&v)[32]) const {
     float* dst = C + static_cast<size_t>(row) * ldc + col;
@@ -248,6 +273,7 @@ struct EpiStoreF32 {
 // SwiGLU (optionally clamped) over a [gate | up] tile pair -> bf16 [rows, F].
 struct EpiSwigluBf16 {
   __nv_bfloat16* C; int ldc; int N; float limit;
+  __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const {
     if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
     return g / (1.f + __expf(-g)) * u;
@@ -255,6 +281,36 @@ struct EpiSwigluBf16 {
   __device__ __forceinline__ void operator()(const TileCoord& tc, int row, int col, const float (&v)[32]) const {
     EpiStoreBf16 st{C, ldc, N};
     st(tc, row, col, v);
+  }
+};
+
+// Row-parallel GEMM under tensor parallelism: the fp32 partial tile goes straight to the rank that owns the
+// row block (reduce-scatter by rows over NVLink, plain P2P stores from the epilogue warps); the CTA that
+// finishes last on this rank raises the "my partials are delivered" flag on every owner.  The owners then
+// sum the slots in rank order (+ residual + RMSNorm) and all-gather the result (comm.cu rs_finish_ag_push).
+struct EpiPushRS {
+  uint8_t* peers[COMM_MAX_RANKS];
+  long long slot_off, flag_off;        // float slots [world(src)][rows_per_rank * N] on the owner; u32 flags [world]
+  int rank, world, rows_per_rank, N;
+  uint32_t seq;
+  int* counter;
+  __device__ __forceinline__ float act(float g, float u) const { return g; }
+  __device__ __forceinline__ void operator()(const TileCoord&, int row, int col, const float (&v)[32]) const {
+    const int owner = row / rows_per_rank, lr = row - owner * rows_per_rank;
+    float* dst = reinterpret_cast<float*>(peers[owner] + slot_off) + (static_cast<size_t>(rank) * rows_per_rank + lr) * N + col;
+    if (col + 32 <= N) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+      for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = v[i];
+    }
+  }
+  __device__ __forceinline__ void cta_done(int n_ctas) const {
+    __threadfence_system();
+    if (atomicAdd(counter, 1) == n_ctas - 1) {
+      *counter = 0;
+      for (int p = 0; p < world; ++p) st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + flag_off) + rank, seq);
+    }
   }
 };
 

@@ -44,7 +44,7 @@ _SIGS = {
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp],
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
-                        f32, i32, vp],
+                        f32, i32, vp, vp],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
 }
@@ -229,7 +229,7 @@ def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, p
     es = (tw, K, N) if w.experts else (0, 0, 0)
     rc = lib().spark_exl3_gemv(P(x), x.stride(0), P(w.trellis), P(w.suh), P(w.svh), es[0], es[1], es[2], P(y), N,
                                int(out_f32), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
-                               act, float(limit), 0 if w.kind == "mul1" else 1, stream())
+                               act, float(limit), 0 if w.kind == "mul1" else 1, stream(), None)
     check(rc, "spark_exl3_gemv")
     return y
 
