@@ -61,7 +61,15 @@ struct ArRows {
   float* res;                            // optional fp32 residual [R, N] (in/out): res += sum
   const float* norm_w; float eps;        // optional RMSNorm weights
   void* out; int out_f32;                // sum (no norm) or normed rows; bf16 or fp32 [R, N]
+  uint32_t* seq_ptr;                     // optional device-side sequence counter (CUDA-graph replay): the kernel
+                                         // uses *seq_ptr + 1 and the last CTA stores it back
 };
+
+// Sequence number of this launch: from the device counter when there is one (replayed graphs), else the
+// host-provided value.
+__device__ __forceinline__ uint32_t comm_seq(const uint32_t* seq_ptr, uint32_t host_seq) {
+  return seq_ptr ? *reinterpret_cast<const volatile uint32_t*>(seq_ptr) + 1u : host_seq;
+}
 
 // Shared tail: wait for every rank's flag, then rows r = first, first+stride, ...: rank-ordered sum
 // (+ residual)(+ RMSNorm).  Called by whole CTAs (blockDim.x threads).
@@ -136,6 +144,7 @@ __device__ __forceinline__ bool ar_arrive_and_is_last(const ArRows& a, int n_cta
   *a.counter = 0;
   for (int p = 0; p < a.c.world; ++p)
     st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, a.seq);
+  if (a.seq_ptr) *a.seq_ptr = a.seq;       // every CTA of this launch has read the counter before arriving
   return true;
 }
 

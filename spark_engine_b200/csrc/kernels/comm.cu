@@ -33,7 +33,9 @@ __global__ void comm_barrier_kernel(CommCtx c, long long flag_off, uint32_t seq)
 
 // grid = R CTAs (one row each), 256 threads.  N % 4 == 0.
 __global__ void __launch_bounds__(256)
-allreduce_rows_kernel(ArRows a) {
+allreduce_rows_kernel(ArRows a_in) {
+  ArRows a = a_in;
+  a.seq = comm_seq(a.seq_ptr, a.seq);
   __shared__ float red[8];
   __shared__ int last_s;
   const int r = blockIdx.x, W = a.c.world;
@@ -71,11 +73,14 @@ struct RsAg {
   int* counter;
   float* res;                            // fp32 residual of the OWNED rows [rows_per_rank, N] (optional)
   const float* norm_w; float eps;
+  uint32_t* seq_ptr;
 };
 
 // push every row block to its owner (grid-stride over rows), then flag all owners
 __global__ void __launch_bounds__(256)
-rs_push_kernel(RsAg a) {
+rs_push_kernel(RsAg a_in) {
+  RsAg a = a_in;
+  a.seq = comm_seq(a.seq_ptr, a.seq);
   const int W = a.c.world;
   for (int row = blockIdx.x; row < a.M; row += gridDim.x) {
     const int owner = row / a.rows_per_rank, lr = row - owner * a.rows_per_rank;
@@ -105,7 +110,9 @@ rs_push_kernel(RsAg a) {
 // owner: wait all sources, rank-ordered sum (+ residual + RMSNorm) of the owned rows, push the bf16 result row
 // into every peer's gathered buffer, then flag.  grid-stride over the owned rows.
 __global__ void __launch_bounds__(256)
-rs_finish_ag_push_kernel(RsAg a) {
+rs_finish_ag_push_kernel(RsAg a_in) {
+  RsAg a = a_in;
+  a.seq = comm_seq(a.seq_ptr, a.seq);
   __shared__ float red[8];
   __shared__ int ok_s;
   const int W = a.c.world;
@@ -165,16 +172,22 @@ rs_finish_ag_push_kernel(RsAg a) {
   }
 }
 
-__global__ void wait_flags_kernel(CommCtx c, long long flag_off, uint32_t seq) {
+// Waits for every rank's flag; with a device counter and `bump` it closes the sequence (stores seq back).
+__global__ void wait_flags_kernel(CommCtx c, long long flag_off, uint32_t seq, uint32_t* seq_ptr, int bump) {
+  seq = comm_seq(seq_ptr, seq);
   if (threadIdx.x < c.world)
     wait_flag(c, reinterpret_cast<const uint32_t*>(c.peers[c.rank] + flag_off) + threadIdx.x, seq, threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x == 0 && seq_ptr && bump) *seq_ptr = seq;
 }
+__global__ void seq_bump_kernel(uint32_t* seq_ptr) { *seq_ptr = *seq_ptr + 1u; }
 
 // ------------------------------------------------------------------------------------------ AG push
 // Copy this rank's row block x [rows, K] (bf16) into every peer's gathered buffer at row rank*rows, then flag.
 __global__ void __launch_bounds__(256)
 ag_push_kernel(CommCtx c, const __nv_bfloat16* __restrict__ x, int rows, int K, long long buf_off, long long flag_off,
-               uint32_t seq, int* counter) {
+               uint32_t seq, int* counter, const uint32_t* seq_ptr) {
+  seq = comm_seq(seq_ptr, seq);
   const int W = c.world;
   const int KV = K >> 3;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -237,12 +250,12 @@ extern "C" int spark_comm_barrier(const HostCtx* h, long long flag_off, unsigned
 
 extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long long flag_off, unsigned seq, int rows_cap,
                                     int R, int N, const void* in, int in_f32, int* counter, float* res,
-                                    const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s) {
+                                    const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s, void* seq_ptr) {
   if (R <= 0) return 0;
   if (N % 4 || R > rows_cap) return -5;
   ArRows a;
   a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = seq; a.rows_cap = rows_cap; a.R = R; a.N = N;
-  a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32;
+  a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32; a.seq_ptr = (uint32_t*)seq_ptr;
   allreduce_rows_kernel<<<R, 256, 0, s>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -252,13 +265,13 @@ extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long l
 extern "C" int spark_rs_ag_rows(const HostCtx* h, long long slot_off, long long out_off, long long flag_rs_off,
                                 long long flag_ag_off, unsigned seq, int M, int N, int rows_per_rank, const void* in,
                                 int in_f32, int* counter, float* res, const float* norm_w, float eps, int push_only,
-                                cudaStream_t s) {
+                                cudaStream_t s, void* seq_ptr) {
   if (M <= 0) return 0;
   if (N % 4 || N > 4096) return -5;
   RsAg a;
   a.c = to_ctx(h); a.slot_off = slot_off; a.out_off = out_off; a.flag_rs_off = flag_rs_off; a.flag_ag_off = flag_ag_off;
   a.seq = seq; a.M = M; a.N = N; a.rows_per_rank = rows_per_rank; a.in = in; a.in_f32 = in_f32; a.counter = counter;
-  a.res = res; a.norm_w = norm_w; a.eps = eps;
+  a.res = res; a.norm_w = norm_w; a.eps = eps; a.seq_ptr = (uint32_t*)seq_ptr;
   if (push_only != 2) {
     int grid = M < 592 ? M : 592;
     rs_push_kernel<<<grid, 256, 0, s>>>(a);
@@ -267,20 +280,30 @@ extern "C" int spark_rs_ag_rows(const HostCtx* h, long long slot_off, long long 
   int grid2 = rows_per_rank < 592 ? rows_per_rank : 592;
   a.counter = counter + 1;
   rs_finish_ag_push_kernel<<<grid2, 256, 0, s>>>(a);
-  wait_flags_kernel<<<1, 32, 0, s>>>(a.c, flag_ag_off, seq);
+  wait_flags_kernel<<<1, 32, 0, s>>>(a.c, flag_ag_off, seq, (uint32_t*)seq_ptr, 1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int spark_ag_push(const HostCtx* h, const void* x, int rows, int K, long long buf_off, long long flag_off,
-                             unsigned seq, int* counter, cudaStream_t s) {
+                             unsigned seq, int* counter, cudaStream_t s, const void* seq_ptr) {
   if (rows <= 0) return 0;
   if (K % 8) return -5;
   int grid = rows < 296 ? rows : 296;
-  ag_push_kernel<<<grid, 256, 0, s>>>(to_ctx(h), (const __nv_bfloat16*)x, rows, K, buf_off, flag_off, seq, counter);
+  ag_push_kernel<<<grid, 256, 0, s>>>(to_ctx(h), (const __nv_bfloat16*)x, rows, K, buf_off, flag_off, seq, counter, (const uint32_t*)seq_ptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+extern "C" int spark_seq_bump(void* seq_ptr, cudaStream_t s) {
+  seq_bump_kernel<<<1, 1, 0, s>>>((uint32_t*)seq_ptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 extern "C" int spark_wait_flags(const HostCtx* h, long long flag_off, unsigned seq, cudaStream_t s) {
-  wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq);
+  wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq, nullptr, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Wait on a flag region using the device-side sequence counter (value + 1); bump != 0 stores it back.
+extern "C" int spark_wait_flags_dev(const HostCtx* h, long long flag_off, void* seq_ptr, int bump, cudaStream_t s) {
+  wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, 0, (uint32_t*)seq_ptr, bump);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -28,6 +28,7 @@ struct EpLayout {
   long long ret_flag_off;  // u32 [world]: combine flags
   int cap;                 // rows per (src, dst) sub-slab
   int row_bytes;           // H + H/128*4 + 16
+  uint32_t* seq_ptr;       // optional device-side sequence counter (graph replay)
 };
 
 constexpr int EP_THREADS = 256;
@@ -46,6 +47,7 @@ ep_dispatch_kernel(CommCtx c, EpLayout L, uint32_t seq, const __nv_bfloat16* __r
   __shared__ int sel_id[32];
   __shared__ float sel_p[32];
   __shared__ int sel_pos[32];
+  seq = comm_seq(L.seq_ptr, seq);
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int epr = E / c.world;
 
@@ -160,6 +162,7 @@ ep_dispatch_kernel(CommCtx c, EpLayout L, uint32_t seq, const __nv_bfloat16* __r
 __global__ void __launch_bounds__(256)
 ep_recv_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, __nv_bfloat16* __restrict__ a_rows,
                int* __restrict__ expert_local, int4* __restrict__ meta_out, int* __restrict__ total) {
+  seq = comm_seq(L.seq_ptr, seq);
   __shared__ int base[COMM_MAX_RANKS + 1];
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
@@ -202,6 +205,7 @@ ep_recv_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, __nv_bfloat16* __rest
 __global__ void __launch_bounds__(256)
 ep_combine_push_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, int top_k, const __nv_bfloat16* __restrict__ y,
                        const int4* __restrict__ meta, const int* __restrict__ total, int* __restrict__ done_counter) {
+  seq = comm_seq(L.seq_ptr, seq);
   const int P = *total;
   for (int i = blockIdx.x; i < P; i += gridDim.x) {
     const int4 m = meta[i];
@@ -223,6 +227,7 @@ ep_combine_push_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, int top_k, co
 __global__ void __launch_bounds__(256)
 ep_combine_reduce_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, int top_k, const float* __restrict__ wts,
                          float* __restrict__ res, __nv_bfloat16* __restrict__ out) {
+  seq = comm_seq(L.seq_ptr, seq);
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
@@ -281,6 +286,7 @@ extern "C" int spark_ep_dispatch(const HostCtxE* h, const EpLayout* L, unsigned 
 
 // A rank with no tokens still has to raise its flags: dispatch with T == 0 goes through this.
 __global__ void ep_empty_flags_kernel(CommCtx c, EpLayout L, uint32_t seq, int which) {
+  seq = comm_seq(L.seq_ptr, seq);
   const int d = threadIdx.x;
   if (d < c.world) {
     if (which == 0) *reinterpret_cast<volatile int*>(c.peers[d] + L.count_off + c.rank * 4) = 0;

@@ -35,7 +35,9 @@ constexpr int EXL3_MAX_KS = 2048;              // K-slice per CTA (activation sl
 
 template <int CB, bool HI>       // HI: more than 8 activation rows (the upper half of the MMA tile is live)
 __global__ void __launch_bounds__(256, 6)      // 40 registers: 6 CTAs (48 warps) per SM hide the decode dependency chains
-exl3_gemv_kernel(Exl3GemvArgs a) {
+exl3_gemv_kernel(Exl3GemvArgs a_in) {
+  Exl3GemvArgs a = a_in;
+  if (a.fuse_ar) a.ar.seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
   cg::cluster_group cluster = cg::this_cluster();

@@ -135,7 +135,7 @@ extern "C" int spark_gemm_grouped_bf16(const void* A, const void* B, void* C, in
 // Row-parallel GEMM fused with the reduce-scatter of its output: C is never materialised locally; the epilogue
 // writes fp32 partial tiles into the owner rank's arena and flags the owners when this rank is done.
 // M must equal world * rows_per_rank (pad rows are computed from zero-filled A and pushed as zeros).
-struct HostPush { void* peers[8]; long long slot_off, flag_off; int rank, world, rows_per_rank; unsigned seq; int* counter; };
+struct HostPush { void* peers[8]; long long slot_off, flag_off; int rank, world, rows_per_rank; unsigned seq; int* counter; void* seq_ptr; };
 extern "C" int spark_gemm_bf16_push_rs(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int fmt,
                                        const HostPush* hp, int* status, cudaStream_t stream) {
   if (M <= 0) return 0;
@@ -151,6 +151,7 @@ extern "C" int spark_gemm_bf16_push_rs(const void* A, const void* B, int M, int 
   for (int i = 0; i < 8; ++i) epi.peers[i] = static_cast<uint8_t*>(hp->peers[i]);
   epi.slot_off = hp->slot_off; epi.flag_off = hp->flag_off; epi.rank = hp->rank; epi.world = hp->world;
   epi.rows_per_rank = hp->rows_per_rank; epi.N = N; epi.seq = hp->seq; epi.counter = hp->counter;
+  epi.seq_ptr = static_cast<const uint32_t*>(hp->seq_ptr);
   const int mt = (M + GEMM_BM - 1) / GEMM_BM;
   if (N > 128) {
     g.num_n_tiles = (N + 255) / 256; g.num_tiles = mt * g.num_n_tiles;
@@ -167,7 +168,7 @@ extern "C" int spark_gemm_bf16_push_rs(const void* A, const void* B, int M, int 
 // that block's flag arrives, the local block first.
 extern "C" int spark_gemm_bf16_ag(const void* A_gathered, const void* B, void* C, int M, int N, int K, int ldb, int ldc,
                                   int out_f32, const void* ag_flags, unsigned ag_seq, int ag_rows, int rank, int world,
-                                  unsigned long long wait_ns, int* status, cudaStream_t stream) {
+                                  unsigned long long wait_ns, int* status, cudaStream_t stream, const void* seq_ptr) {
   if (M <= 0) return 0;
   CUtensorMap tA, tB;
   int r = make_tmap_bf16(&tA, A_gathered, M, K, K, 128, 1);
@@ -177,7 +178,7 @@ extern "C" int spark_gemm_bf16_ag(const void* A_gathered, const void* B, void* C
   GemmArgs g{};
   g.M = M; g.N = N; g.K = K; g.status = status; g.ab_fmt = 1;
   g.ag_flags = static_cast<const uint32_t*>(ag_flags); g.ag_seq = ag_seq; g.ag_rows = ag_rows; g.ag_rank = rank;
-  g.ag_world = world; g.ag_wait_ns = wait_ns;
+  g.ag_world = world; g.ag_wait_ns = wait_ns; g.ag_seq_ptr = static_cast<const uint32_t*>(seq_ptr);
   const int mt = (M + GEMM_BM - 1) / GEMM_BM;
   if (N > 128) {
     g.num_n_tiles = (N + 255) / 256; g.num_tiles = mt * g.num_n_tiles;

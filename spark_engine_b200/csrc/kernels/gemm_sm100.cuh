@@ -35,6 +35,7 @@ struct GemmArgs {
   // arena by rank src; the TMA producer waits (bounded) for flag[src] >= ag_seq before the first tile of
   // that block and visits its own block first.  ag_flags == nullptr: plain GEMM.
   const uint32_t* ag_flags; uint32_t ag_seq; int ag_rows, ag_rank, ag_world; unsigned long long ag_wait_ns;
+  const uint32_t* ag_seq_ptr;
 };
 
 struct TileCoord {
@@ -123,6 +124,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
       uint32_t ag_seen = 0;                 // bit src set: rank src's block has arrived
+      const uint32_t ag_seq = comm_seq(g.ag_seq_ptr, g.ag_seq);
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         TileCoord tc = tile_coord<BN, GROUPED>(g, t);
         if (!GROUPED && g.ag_flags != nullptr) {
@@ -131,7 +133,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int src = s0; src <= s1 && ok; ++src) {
             if (src == g.ag_rank || (ag_seen >> src) & 1u) continue;
             CommCtx cc; cc.wait_ns = g.ag_wait_ns; cc.status = g.status;
-            if (!wait_flag(cc, g.ag_flags + src, g.ag_seq, src)) { ok = false; break; }
+            if (!wait_flag(cc, g.ag_flags + src, ag_seq, src)) { ok = false; break; }
             ag_seen |= 1u << src;
             asm volatile("fence.proxy.async;" ::: "memory");   // peer's generic-proxy stores -> our TMA reads
           }
@@ -294,6 +296,7 @@ struct EpiPushRS {
   int rank, world, rows_per_rank, N;
   uint32_t seq;
   int* counter;
+  const uint32_t* seq_ptr;
   __device__ __forceinline__ float act(float g, float u) const { return g; }
   __device__ __forceinline__ void operator()(const TileCoord&, int row, int col, const float (&v)[32]) const {
     const int owner = row / rows_per_rank, lr = row - owner * rows_per_rank;
@@ -309,7 +312,8 @@ struct EpiPushRS {
     __threadfence_system();
     if (atomicAdd(counter, 1) == n_ctas - 1) {
       *counter = 0;
-      for (int p = 0; p < world; ++p) st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + flag_off) + rank, seq);
+      const uint32_t sq = comm_seq(seq_ptr, seq);
+      for (int p = 0; p < world; ++p) st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + flag_off) + rank, sq);
     }
   }
 };

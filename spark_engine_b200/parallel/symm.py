@@ -30,29 +30,31 @@ class CommCtx(C.Structure):
 class ArRows(C.Structure):
     _fields_ = [("c", CommCtx), ("slot_off", i64), ("flag_off", i64), ("seq", u32), ("rows_cap", i32), ("R", i32),
                 ("N", i32), ("inp", vp), ("in_f32", i32), ("counter", vp), ("res", vp), ("norm_w", vp), ("eps", f32),
-                ("out", vp), ("out_f32", i32)]
+                ("out", vp), ("out_f32", i32), ("seq_ptr", vp)]
 
 
 class HostPush(C.Structure):
     _fields_ = [("peers", vp * 8), ("slot_off", i64), ("flag_off", i64), ("rank", i32), ("world", i32),
-                ("rows_per_rank", i32), ("seq", u32), ("counter", vp)]
+                ("rows_per_rank", i32), ("seq", u32), ("counter", vp), ("seq_ptr", vp)]
 
 
 class EpLayout(C.Structure):
     _fields_ = [("slab_off", i64), ("count_off", i64), ("flag_off", i64), ("ret_off", i64), ("ret_flag_off", i64),
-                ("cap", i32), ("row_bytes", i32)]
+                ("cap", i32), ("row_bytes", i32), ("seq_ptr", vp)]
 
 
 _SIGS = {
     "spark_arena_alloc": ([i64], vp), "spark_arena_free": ([vp], None),
     "spark_ipc_get_handle": ([vp, vp], i32), "spark_ipc_open_handle": ([vp], vp), "spark_ipc_close": ([vp], None),
     "spark_comm_barrier": ([vp, i64, u32, vp], i32),
-    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp], i32),
-    "spark_rs_ag_rows": ([vp, i64, i64, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp], i32),
-    "spark_ag_push": ([vp, vp, i32, i32, i64, i64, u32, vp, vp], i32),
+    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp], i32),
+    "spark_rs_ag_rows": ([vp, i64, i64, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp, vp], i32),
+    "spark_ag_push": ([vp, vp, i32, i32, i64, i64, u32, vp, vp, vp], i32),
+    "spark_seq_bump": ([vp, vp], i32),
     "spark_wait_flags": ([vp, i64, u32, vp], i32),
+    "spark_wait_flags_dev": ([vp, i64, vp, i32, vp], i32),
     "spark_gemm_bf16_push_rs": ([vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp], i32),
-    "spark_gemm_bf16_ag": ([vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, u32, i32, i32, i32, C.c_ulonglong, vp, vp], i32),
+    "spark_gemm_bf16_ag": ([vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, u32, i32, i32, i32, C.c_ulonglong, vp, vp, vp], i32),
     "spark_ep_row_bytes": ([i32], i32),
     "spark_ep_dispatch": ([vp, vp, u32, vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp], i32),
     "spark_ep_empty": ([vp, vp, u32, i32, vp], i32),
@@ -129,6 +131,7 @@ class Arena:
         self.seqs: Dict[str, int] = {}
         self._counters = torch.zeros(64, dtype=torch.int32, device=self.device)
         self._n_counters = 0
+        self._seq_tensors = []
         self.flag_barrier = self.region("barrier_flags", 8 * 4)
         self.barrier()
 
@@ -154,6 +157,13 @@ class Arena:
         p = self._counters[self._n_counters:].data_ptr()
         self._n_counters += 2
         return p
+
+    def seq_counter(self) -> torch.Tensor:
+        """Device-side sequence counter of one channel (kernels use value+1 and store it back, so a captured
+        graph can be replayed)."""
+        t = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._seq_tensors.append(t)
+        return t
 
     def next_seq(self, name: str) -> int:
         self.seqs[name] = self.seqs.get(name, 0) + 1
@@ -189,11 +199,13 @@ class FusedAllReduce:
         self.slot_off = arena.region(name + ".slots", 2 * W * rows_cap * N * 4)
         self.flag_off = arena.region(name + ".flags", 8 * 4)
         self.counter = arena.counter()
+        self.seq = arena.seq_counter()
 
     def _args(self, R, inp, res, norm_w, eps, out) -> ArRows:
         ar = ArRows()
         ar.c = self.a.ctx
-        ar.slot_off, ar.flag_off, ar.seq = self.slot_off, self.flag_off, self.a.next_seq(self.name)
+        ar.slot_off, ar.flag_off, ar.seq = self.slot_off, self.flag_off, 0
+        ar.seq_ptr = self.seq.data_ptr()
         ar.rows_cap, ar.R, ar.N = self.rows_cap, R, self.N
         ar.inp = cu.P(inp)
         ar.in_f32 = int(inp is not None and inp.dtype == torch.float32)
@@ -210,7 +222,7 @@ class FusedAllReduce:
         ar = self._args(R, x.contiguous(), res, norm_w, eps, out)
         rc = _lib()._dll.spark_allreduce_rows(C.byref(ar.c), ar.slot_off, ar.flag_off, ar.seq, ar.rows_cap, R, N, ar.inp,
                                               ar.in_f32, ar.counter, ar.res, ar.norm_w, ar.eps, ar.out, ar.out_f32,
-                                              cu.stream())
+                                              cu.stream(), ar.seq_ptr)
         cu.check(rc, "spark_allreduce_rows")
         return out
 
@@ -245,6 +257,7 @@ class RowParallelGemm:
         self.flag_rs = arena.region(name + ".frs", 32)
         self.flag_ag = arena.region(name + ".fag", 32)
         self.counters = torch.zeros(4, dtype=torch.int32, device=arena.device)
+        self.seq = arena.seq_counter()
 
     def __call__(self, x, w, res_owned=None, norm_w=None, eps=1e-6, fused=True) -> torch.Tensor:
         """x [M, K_shard] bf16, w [N, K_shard] bf16 -> gathered result rows [M, N] bf16 (view into the arena)."""
@@ -254,7 +267,7 @@ class RowParallelGemm:
         rpr = (M + W - 1) // W
         assert rpr <= self.rpr_cap
         Mp = rpr * W
-        seq = a.next_seq(self.name)
+        seq = 0
         lib = _lib()._dll
         if fused:
             hp = HostPush()
@@ -262,6 +275,7 @@ class RowParallelGemm:
                 hp.peers[i] = a.peer_ptrs[i]
             hp.slot_off, hp.flag_off, hp.rank, hp.world = self.slot_off, self.flag_rs, a.rank, W
             hp.rows_per_rank, hp.seq, hp.counter = rpr, seq, self.counters.data_ptr()
+            hp.seq_ptr = self.seq.data_ptr()
             rc = lib.spark_gemm_bf16_push_rs(cu.P(x), cu.P(w), Mp if Mp == M else M, self.N, K, x.stride(0), w.stride(0), 1,
                                              C.byref(hp), cu.P(cu.status_word(x.device)), cu.stream())
             cu.check(rc, "spark_gemm_bf16_push_rs")
@@ -275,7 +289,7 @@ class RowParallelGemm:
             inp = part
         rc = lib.spark_rs_ag_rows(C.byref(a.ctx), self.slot_off, self.out_off, self.flag_rs, self.flag_ag, seq, Mp,
                                   self.N, rpr, cu.P(inp), 1, self.counters[1:].data_ptr(), cu.P(res_owned), cu.P(norm_w),
-                                  float(eps), push_only, cu.stream())
+                                  float(eps), push_only, cu.stream(), self.seq.data_ptr())
         cu.check(rc, "spark_rs_ag_rows")
         return a.view(self.out_off, Mp * self.N * 2, torch.bfloat16).view(Mp, self.N)[:M]
 
@@ -290,6 +304,7 @@ class AllGatherGemm:
         self.buf_off = arena.region(name + ".gather", W * self.rpr_cap * K * 2)
         self.flag_off = arena.region(name + ".flags", 32)
         self.counter = arena.counter()
+        self.seq = arena.seq_counter()
 
     def __call__(self, x_local, w, out_f32=False) -> torch.Tensor:
         """x_local [rows, K] bf16 (this rank's row block) ; w [N_shard, K] -> [world*rows, N_shard]."""
@@ -297,17 +312,18 @@ class AllGatherGemm:
         W = a.world
         rows, K = x_local.shape
         assert K == self.K and rows <= self.rpr_cap
-        seq = a.next_seq(self.name)
+        seq = 0
         lib = _lib()._dll
         rc = lib.spark_ag_push(C.byref(a.ctx), cu.P(x_local.contiguous()), rows, K, self.buf_off, self.flag_off, seq,
-                               self.counter, cu.stream())
+                               self.counter, cu.stream(), self.seq.data_ptr())
         cu.check(rc, "spark_ag_push")
         M, N = W * rows, w.shape[0]
         out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x_local.device)
         rc = lib.spark_gemm_bf16_ag(a.base + self.buf_off, cu.P(w), cu.P(out), M, N, K, w.stride(0), N, int(out_f32),
                                     a.base + self.flag_off, seq, rows, a.rank, W, a.ctx.wait_ns,
-                                    cu.P(cu.status_word(x_local.device)), cu.stream())
+                                    cu.P(cu.status_word(x_local.device)), cu.stream(), self.seq.data_ptr())
         cu.check(rc, "spark_gemm_bf16_ag")
+        cu.check(lib.spark_seq_bump(self.seq.data_ptr(), cu.stream()), "spark_seq_bump")
         return out
 
 
@@ -329,6 +345,8 @@ class ExpertParallel:
         L.ret_off = arena.region(name + ".ret", tokens_cap * top_k * H * 2)
         L.ret_flag_off = arena.region(name + ".rflag", 32)
         L.cap, L.row_bytes = self.cap, self.row_bytes
+        self.seq_dev = arena.seq_counter()
+        L.seq_ptr = self.seq_dev.data_ptr()
         self.L = L
         dev = arena.device
         self.send_count = torch.zeros(8, dtype=torch.int32, device=dev)
@@ -343,7 +361,7 @@ class ExpertParallel:
         """x [T,H] bf16, logits [T,E] fp32 -> (wts [T,k], ids [T,k]); received rows land in self.a_rows[:total]."""
         a, lib = self.a, _lib()._dll
         T = x.shape[0]
-        self.seq = a.next_seq(self.name)
+        self.seq = 0
         wts = torch.empty(T, self.k, dtype=torch.float32, device=x.device)
         ids = torch.empty(T, self.k, dtype=torch.int32, device=x.device)
         if T == 0:
@@ -366,9 +384,10 @@ class ExpertParallel:
         cu.check(rc, "spark_ep_combine_push")
         out = torch.empty(T, self.H, dtype=torch.bfloat16, device=y.device)
         if T == 0:
-            rc = lib.spark_wait_flags(C.byref(a.ctx), self.L.ret_flag_off, self.seq, cu.stream())
+            rc = lib.spark_wait_flags_dev(C.byref(a.ctx), self.L.ret_flag_off, self.seq_dev.data_ptr(), 0, cu.stream())
         else:
             rc = lib.spark_ep_combine_reduce(C.byref(a.ctx), C.byref(self.L), self.seq, T, self.H, self.k, cu.P(wts),
                                              cu.P(res), cu.P(out), cu.stream())
         cu.check(rc, "spark_ep_combine_reduce")
+        cu.check(lib.spark_seq_bump(self.seq_dev.data_ptr(), cu.stream()), "spark_seq_bump")
         return out
