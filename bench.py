@@ -97,6 +97,8 @@ def main():
     ap.add_argument("--format", default=None, help="dense | exl3 (default: the config's)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
+    ap.add_argument("--parallel", default="tp", help="N > 1: tp = one model sharded over the GPUs (tensor + expert "
+                                                     "parallel, fused peer-memory all-reduce); dp = one replica per GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -123,13 +125,23 @@ def main():
         kw["weight_format"] = args.format
     cfg = get_model_config(args.model, **kw)
     t0 = time.time()
-    W = build_random_model(cfg, dev, seed=0)
+    tp = None
+    use_tp = world > 1 and args.parallel == "tp"
+    if use_tp:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        from spark_engine_b200.parallel import symm
+        from spark_engine_b200.parallel.tp import DeviceTP
+        arena = symm.Arena(1 << 30, wait_ms=4000.0)
+        tp = DeviceTP(arena, cfg.hidden, rows_cap=1024)
+    W = build_random_model(cfg, dev, seed=0, tp=(rank, world) if use_tp else (0, 1))
     torch.cuda.synchronize()
     build_s = time.time() - t0
+    if world > 1:
+        dist.barrier()          # ranks finish building their shards at different times
     S = args.streams
-    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not args.no_graphs, prefill_chunk=4096), device=dev, max_seqs=S,
-                    kv_tokens_per_seq=max(4096, 2 * args.prompt))
-    g = torch.Generator().manual_seed(1234 + rank)
+    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not args.no_graphs, prefill_chunk=1024 if use_tp else 4096),
+                    device=dev, max_seqs=S, kv_tokens_per_seq=max(4096, 2 * args.prompt), tp=tp)
+    g = torch.Generator().manual_seed(1234 + (0 if use_tp else rank))
     prompts = torch.randint(0, cfg.vocab, (S, args.prompt), generator=g)
     pinned_prompts = prompts.to(torch.int32).pin_memory()
 
@@ -140,10 +152,11 @@ def main():
         torch.cuda.synchronize()
         ev0.record()
         lg = eng.prefill(s, pinned_prompts[s].tolist())
-        cur.append(int(torch.argmax(lg)))
+        cur.append(int(eng.model.greedy(lg.unsqueeze(0))[0]))
         ev1.record()
         torch.cuda.synchronize()
         ttft.append(ev0.elapsed_time(ev1))
+        eng.check_device_status()      # fail fast if a bounded wait gave up
     prefill_tok_s = args.prompt / (min(ttft[1:] or ttft) / 1e3)
 
     def barrier():
@@ -198,19 +211,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = t.tolist()
     st = cu.read_status(dev)
-    value = world * S * 1e3 / dev_ms
-    e2e = world * S * 1e3 / e2e_ms
+    replicas = 1 if use_tp else world
+    value = replicas * S * 1e3 / dev_ms
+    e2e = replicas * S * 1e3 / e2e_ms
     full = (args.layers == 0 and args.model == "qwen3next-style" and cfg.weight_format == "exl3")
     out = {
         "metric": "aggregate decode tok/s at 4 streams" if S == 4 else f"aggregate decode tok/s at {S} streams",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "strong" if use_tp else "weak",
         "vs_baseline": round(value / BASELINE_DECODE_4STREAMS, 3) if full and S == 4 else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.moe.n_experts,
                    "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
-                   "kv": cfg.kv_dtype, "global_batch": world * S, "seq_len": args.prompt, "streams_per_gpu": S,
-                   "parallelism": f"dp{world}" if world > 1 else "single", "speculation": "none (greedy)",
+                   "kv": cfg.kv_dtype, "global_batch": replicas * S, "seq_len": args.prompt, "streams_per_gpu": S,
+                   "parallelism": (f"tp{world}+ep{world}" if use_tp else f"dp{world}") if world > 1 else "single", "speculation": "none (greedy)",
                    "cache": "inputs larger than L2 (weights %.1f GB streamed every step)" % (weight_bytes(W) / 1e9),
                    "full_config": full},
         "clocks": clocks,

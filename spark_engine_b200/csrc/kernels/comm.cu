@@ -248,6 +248,47 @@ extern "C" int spark_comm_barrier(const HostCtx* h, long long flag_off, unsigned
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// Many rows (prefill): two launches.  A CTA that waits for a peer's flag must never keep one of its own
+// grid's CTAs from running (the peer's flag needs ALL of that peer's CTAs to have pushed, and vice versa), so
+// the push kernel never waits and the tail kernel only waits for flags that push kernels raise.
+__global__ void __launch_bounds__(256)
+ar_push_kernel(ArRows a_in) {
+  ArRows a = a_in;
+  a.seq = comm_seq(a.seq_ptr, a.seq);
+  a.seq_ptr = nullptr;                                   // the tail kernel closes the sequence
+  const int W = a.c.world;
+  const size_t set = static_cast<size_t>(a.seq & 1) * W * a.rows_cap * a.N;
+  for (int r = blockIdx.x; r < a.R; r += gridDim.x) {
+    for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
+      float4 v;
+      if (a.in_f32) v = ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(r) * a.N + i);
+      else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(r) * a.N + i);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+        v = make_float4(f0.x, f0.y, f1.x, f1.y);
+      }
+      for (int p = 0; p < W; ++p)
+        st_f4(reinterpret_cast<float*>(a.c.peers[p] + a.slot_off) + set + (static_cast<size_t>(a.c.rank) * a.rows_cap + r) * a.N + i, v);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) ar_arrive_and_is_last(a, gridDim.x);
+}
+
+__global__ void __launch_bounds__(256)
+ar_tail_kernel(ArRows a_in, int* tail_counter) {
+  __shared__ float red[8];
+  ArRows a = a_in;
+  a.seq = comm_seq(a.seq_ptr, a.seq);
+  ar_rows_tail(a, blockIdx.x, gridDim.x, red);
+  __syncthreads();
+  if (threadIdx.x == 0 && a.seq_ptr) {                   // last CTA of the tail closes the sequence
+    __threadfence();
+    if (atomicAdd(tail_counter, 1) == static_cast<int>(gridDim.x) - 1) { *tail_counter = 0; *a.seq_ptr = a.seq; }
+  }
+}
+
 extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long long flag_off, unsigned seq, int rows_cap,
                                     int R, int N, const void* in, int in_f32, int* counter, float* res,
                                     const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s, void* seq_ptr) {
@@ -256,7 +297,12 @@ extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long l
   ArRows a;
   a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = seq; a.rows_cap = rows_cap; a.R = R; a.N = N;
   a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32; a.seq_ptr = (uint32_t*)seq_ptr;
-  allreduce_rows_kernel<<<R, 256, 0, s>>>(a);
+  if (R <= 64) {                 // all CTAs co-resident: one kernel pushes, signals, waits and reduces
+    allreduce_rows_kernel<<<R, 256, 0, s>>>(a);
+  } else {
+    ar_push_kernel<<<R < 592 ? R : 592, 256, 0, s>>>(a);
+    ar_tail_kernel<<<R < 296 ? R : 296, 256, 0, s>>>(a, counter + 1);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

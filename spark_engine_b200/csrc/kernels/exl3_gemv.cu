@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(256, 6)      // 40 registers: 6 CTAs (48 warps
 exl3_gemv_kernel(Exl3GemvArgs a_in) {
   Exl3GemvArgs a = a_in;
   if (a.fuse_ar) a.ar.seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
+  if (a.pair_expert && a.pair_expert[blockIdx.z] < 0) return;   // expert on another rank (whole cluster leaves)
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
   cg::cluster_group cluster = cg::this_cluster();

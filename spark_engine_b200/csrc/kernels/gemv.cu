@@ -28,6 +28,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
   extern __shared__ __align__(16) uint8_t smem_gemv[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [RB][K]
   const int item = blockIdx.y;
+  if (pair_expert && pair_expert[item] < 0) return;      // pair of an expert that lives on another rank
   const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
   const __nv_bfloat16* Wb = W + (pair_expert ? static_cast<long long>(pair_expert[item]) * expert_stride : 0);
   const int R = rows_per_item;

@@ -19,7 +19,7 @@ constexpr int ROUTE_MAXE_PER_THREAD = 4;     // up to 1024 experts
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const float* __restrict__ logits, int ld, int E, int top_k, int kind, const float* __restrict__ bias,
                  float scale, int shared_gate, float* __restrict__ wts, int* __restrict__ ids,
-                 int* __restrict__ pair_row, float* __restrict__ sg) {
+                 int* __restrict__ pair_row, float* __restrict__ sg, int e_lo, int e_hi) {
   __shared__ float rv[ROUTE_THREADS / 32];
   __shared__ int ri[ROUTE_THREADS / 32];
   __shared__ float bv; __shared__ int bidx;
@@ -96,7 +96,8 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int E, int top_k, int
 #pragma unroll
       for (int jj = 0; jj < ROUTE_MAXE_PER_THREAD; ++jj) if (jj == j) { bp = p[jj]; s[jj] = -INFINITY; }
       sel_p[k] = bp;
-      ids[static_cast<size_t>(r) * top_k + k] = win;
+      // expert-parallel ranks keep only their own experts [e_lo, e_hi): others become -1 (skipped downstream)
+      ids[static_cast<size_t>(r) * top_k + k] = (win >= e_lo && win < e_hi) ? win - e_lo : -1;
       if (pair_row) pair_row[static_cast<size_t>(r) * top_k + k] = r;
     }
     __syncthreads();
@@ -120,7 +121,7 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
   int* cnt = sh; int* start = sh + E;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < P; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
+  for (int i = threadIdx.x; i < P; i += blockDim.x) if (ids[i] >= 0) atomicAdd(&cnt[ids[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0, nt = 0;
@@ -135,6 +136,7 @@ moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ per
   // stable placement: pair i goes to start[e] + (number of earlier pairs with the same expert)
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
     const int e = ids[i];
+    if (e < 0) { if (inv_perm) inv_perm[i] = -1; continue; }   // not a local expert
     int rank = 0;
     for (int j = 0; j < i; ++j) rank += (ids[j] == e);     // P is small on the decode path
     perm[start[e] + rank] = i;
@@ -149,7 +151,7 @@ __global__ void moe_hist_kernel(const int* __restrict__ ids, int P, int E, int* 
   for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < P) atomicAdd(&sh[ids[i]], 1);
+  if (i < P && ids[i] >= 0) atomicAdd(&sh[ids[i]], 1);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) block_hist[static_cast<size_t>(blockIdx.x) * E + e] = sh[e];
 }
@@ -182,6 +184,7 @@ __global__ void moe_place_kernel(const int* __restrict__ ids, int P, int E, cons
   __syncthreads();
   if (i >= P) return;
   const int e = sid[threadIdx.x];
+  if (e < 0) { if (inv_perm) inv_perm[i] = -1; return; }
   int rank = 0;
   for (int j = 0; j < threadIdx.x; ++j) rank += (sid[j] == e);
   const int dst = offsets[e] + block_hist[static_cast<size_t>(blockIdx.x) * E + e] + rank;
@@ -194,13 +197,15 @@ __global__ void moe_place_kernel(const int* __restrict__ ids, int P, int E, cons
 template <typename TY>
 __global__ void moe_combine_kernel(float* __restrict__ res, const TY* __restrict__ y, const int* __restrict__ inv_perm,
                                    const float* __restrict__ wts, int top_k, const __nv_bfloat16* __restrict__ shared,
-                                   const float* __restrict__ sg, int H, __nv_bfloat16* __restrict__ out_bf16) {
+                                   const float* __restrict__ sg, int H, __nv_bfloat16* __restrict__ out_bf16,
+                                   const int* __restrict__ pair_expert) {
   const int r = blockIdx.x;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
 #pragma unroll 4
     for (int k = 0; k < top_k; ++k) {
       const int pi = r * top_k + k;
+      if (pair_expert && pair_expert[pi] < 0) continue;          // expert lives on another rank
       const int row = inv_perm ? inv_perm[pi] : pi;
       acc = fmaf(wts[pi], static_cast<float>(y[static_cast<size_t>(row) * H + i]), acc);
     }
@@ -219,10 +224,10 @@ using namespace spark;
 
 extern "C" int spark_moe_route(const float* logits, int ld, int R, int E, int top_k, int kind, const float* bias,
                                float scale, int shared_gate, float* wts, int* ids, int* pair_row, float* sg,
-                               cudaStream_t s) {
+                               cudaStream_t s, int e_lo, int e_hi) {
   if (R <= 0) return 0;
   if (E > ROUTE_THREADS * ROUTE_MAXE_PER_THREAD || top_k > 32) return -5;
-  moe_route_kernel<<<R, ROUTE_THREADS, 0, s>>>(logits, ld, E, top_k, kind, bias, scale, shared_gate, wts, ids, pair_row, sg);
+  moe_route_kernel<<<R, ROUTE_THREADS, 0, s>>>(logits, ld, E, top_k, kind, bias, scale, shared_gate, wts, ids, pair_row, sg, e_lo, e_hi);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -242,13 +247,14 @@ extern "C" int spark_moe_sort(const int* ids, int P, int E, int* perm, int* inv_
 }
 
 extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int* inv_perm, const float* wts, int R,
-                                 int top_k, const void* shared, const float* sg, int H, void* out_bf16, cudaStream_t s) {
+                                 int top_k, const void* shared, const float* sg, int H, void* out_bf16, cudaStream_t s,
+                                 const int* pair_expert) {
   if (R <= 0) return 0;
   if (y_f32)
     moe_combine_kernel<float><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const float*)y, inv_perm, wts, top_k, (const __nv_bfloat16*)shared, sg, H,
-                                                (__nv_bfloat16*)out_bf16);
+                                                (__nv_bfloat16*)out_bf16, pair_expert);
   else
     moe_combine_kernel<__nv_bfloat16><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const __nv_bfloat16*)y, inv_perm, wts, top_k,
-                                                        (const __nv_bfloat16*)shared, sg, H, (__nv_bfloat16*)out_bf16);
+                                                        (const __nv_bfloat16*)shared, sg, H, (__nv_bfloat16*)out_bf16, pair_expert);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -14,15 +14,20 @@ from ..quant import formats as Q
 
 
 class _DevInit:
-    def __init__(self, device, seed: int, fmt: str, bits: int, std: float = 0.02):
-        self.device, self.fmt, self.bits, self.std = device, fmt, bits, std
-        self.g = torch.Generator(device=device)
-        self.g.manual_seed(seed)
+    def __init__(self, device, seed: int, fmt: str, bits: int, std: float = 0.02, rank: int = 0):
+        self.device, self.fmt, self.bits, self.std, self.rank = device, fmt, bits, std, rank
+        self.g = torch.Generator(device=device)          # sharded tensors: a different stream per rank
+        self.g.manual_seed(seed + 7919 * rank)
+        self.gc = torch.Generator(device=device)         # replicated tensors: the same on every rank
+        self.gc.manual_seed(seed + 1)
         self.n = 0
 
     def _seed(self):
         self.n += 1
-        return 1000003 * self.n + 17
+        return 1000003 * self.n + 17 + 7919 * self.rank
+
+    def mat_common(self, *shape):
+        return (torch.randn(*shape, device=self.device, generator=self.gc) * self.std).to(torch.bfloat16)
 
     def big(self, n, k, experts=0, kind="dense"):
         """A large projection [n, k] (or experts x [n, k]) in the model's weight format."""
@@ -88,37 +93,47 @@ def _mix(cfg: ModelConfig, it: _DevInit, kind: str) -> dict:
     raise ValueError(kind)
 
 
-def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool) -> dict:
+def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool, tp=(0, 1)) -> dict:
     c, H = cfg.moe, cfg.hidden
     if dense:
         return {"dense_gu": it.big(2 * c.dense_ffn, H), "dense_down": it.big(H, c.dense_ffn)}
     Fs = c.shared_ffn or c.ffn * c.n_shared
-    w = {"gate": it.mat(c.n_experts + (1 if c.shared_gate else 0), H),
-         "w_gu": it.big(2 * c.ffn, H, c.n_experts, kind="expert"),
-         "w_down": it.big(H, c.ffn, c.n_experts, kind="expert")}
+    rank, world = tp
+    assert c.n_experts % world == 0
+    e_loc = c.n_experts // world
+    w = {"gate": it.mat_common(c.n_experts + (1 if c.shared_gate else 0), H),
+         "w_gu": it.big(2 * c.ffn, H, e_loc, kind="expert"),
+         "w_down": it.big(H, c.ffn, e_loc, kind="expert")}
+    if world > 1:
+        w["ep"] = (rank * e_loc, (rank + 1) * e_loc)
     if c.router != "softmax":
-        w["bias"] = it.f32(c.n_experts)
-    if c.n_shared:
+        w["bias"] = torch.zeros(c.n_experts, device=it.device)
+    if c.n_shared and rank == 0:
         w["s_gu"], w["s_down"] = it.big(2 * Fs, H), it.big(H, Fs)
     return w
 
 
-def _layer(cfg: ModelConfig, it: _DevInit, i: int, kind: str) -> dict:
+def _layer(cfg: ModelConfig, lcfg: ModelConfig, it: _DevInit, i: int, kind: str, tp=(0, 1)) -> dict:
     return {"type": kind, "in_norm": it.f32(cfg.hidden, val=1.0), "post_norm": it.f32(cfg.hidden, val=1.0),
-            "mix": _mix(cfg, it, kind), "mlp": _mlp(cfg, it, i < cfg.moe.dense_layers)}
+            "mix": _mix(lcfg, it, kind), "mlp": _mlp(cfg, it, i < cfg.moe.dense_layers, tp)}
 
 
-def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0) -> dict:
-    """Nested weight dict on `device` in cfg.weight_format (dense | exl3 | mx)."""
-    it = _DevInit(device, seed, cfg.weight_format, cfg.exl3_bits)
-    W = {"embed": it.mat(cfg.vocab, cfg.hidden), "final_norm": it.f32(cfg.hidden, val=1.0),
-         "lm_head": it.mat(cfg.vocab, cfg.hidden),
-         "layers": [_layer(cfg, it, i, cfg.layer_types[i]) for i in range(cfg.n_layers)]}
+def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0, tp=(0, 1)) -> dict:
+    """Nested weight dict on `device` in cfg.weight_format (dense | exl3 | mx).  `tp` = (rank, world): only this
+    rank's shard is generated (heads, experts by id, vocabulary rows of lm_head); replicated tensors come from a
+    generator that is seeded identically on every rank."""
+    rank, world = tp
+    from ..parallel.tp import local_config
+    lcfg = local_config(cfg, world) if world > 1 else cfg
+    it = _DevInit(device, seed, cfg.weight_format, cfg.exl3_bits, rank=rank)
+    W = {"embed": it.mat_common(cfg.vocab, cfg.hidden), "final_norm": it.f32(cfg.hidden, val=1.0),
+         "lm_head": it.mat(cfg.vocab // world, cfg.hidden),
+         "layers": [_layer(cfg, lcfg, it, i, cfg.layer_types[i], tp) for i in range(cfg.n_layers)]}
     if cfg.mtp_layers:
         kind = "attn" if cfg.family == "hybrid" else "mla"
         W["mtp"] = {"fc": it.mat(cfg.hidden, 2 * cfg.hidden), "norm_e": it.f32(cfg.hidden, val=1.0),
                     "norm_h": it.f32(cfg.hidden, val=1.0), "final_norm": it.f32(cfg.hidden, val=1.0),
-                    "layers": [_layer(cfg, it, cfg.n_layers, kind) for _ in range(cfg.mtp_layers)]}
+                    "layers": [_layer(cfg, cfg, it, cfg.n_layers, kind) for _ in range(cfg.mtp_layers)]}
     if cfg.ngram_layers:
         W["ngram_table"] = it.mat(cfg.ngram_rows, cfg.ngram_dim)
         D = cfg.ngram_dim * cfg.ngram_heads

@@ -123,7 +123,7 @@ class GdnMixer:
                 outs.append(o)
             o = torch.cat(outs, 0).to(h.dtype)
         self.pending = None if commit else (proj, ab, plan)
-        return ops.linear(o, self.w["o"])
+        return ops.row_parallel(o, self.w["o"], getattr(self, "tp", None))
 
     def commit(self, accepted: List[List[int]]):
         """Replay the accepted rows (segment-local row indices, a root-to-leaf path) into the state."""
@@ -281,7 +281,7 @@ class AttnMixer:
         qkv = ops.linear(h, self.w["qkv"])
         fast = ops.attn_mixer(self, qkv, plan, seqs)
         if fast is not None:
-            return ops.linear(fast, self.w["o"])
+            return ops.row_parallel(fast, self.w["o"], getattr(self, "tp", None))
         R = h.shape[0]
         D = c.head_dim
         qg = qkv[:, : self.nq].float().view(R, c.n_q_heads, -1)
@@ -520,8 +520,11 @@ class MoeBlock:
 # ============================================================================= the model
 class Model:
     def __init__(self, cfg: ModelConfig, W: dict, device="cpu", dtype=torch.float32, n_slots: int = 4,
-                 kv_tokens: int = 4096, slot_tokens: Optional[int] = None):
+                 kv_tokens: int = 4096, slot_tokens: Optional[int] = None, tp=None):
+        """`tp`: tensor/expert-parallel context (spark_engine_b200.parallel.tp); `W` then holds this rank's shard."""
         self.cfg, self.W, self.device, self.dtype = cfg, W, torch.device(device), dtype
+        self.tp = tp
+        self.lcfg = tp.local_config(cfg) if tp is not None else cfg      # per-rank head counts
         self.n_slots, self.kv_tokens = n_slots, kv_tokens
         per = slot_tokens or kv_tokens // n_slots
         self.seqs = [SeqInfo(i * per, per) for i in range(n_slots)]
@@ -534,15 +537,16 @@ class Model:
         for lw in lws:
             kind = lw["type"]
             if kind == "gdn":
-                mix = GdnMixer(self.cfg, lw["mix"], self.n_slots, self.device, self.dtype)
+                mix = GdnMixer(self.lcfg, lw["mix"], self.n_slots, self.device, self.dtype)
             elif kind == "kda":
-                mix = KdaMixer(self.cfg, lw["mix"], self.n_slots, self.device, self.dtype)
+                mix = KdaMixer(self.lcfg, lw["mix"], self.n_slots, self.device, self.dtype)
             elif kind == "attn":
-                mix = AttnMixer(self.cfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
+                mix = AttnMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
             elif kind == "mla":
-                mix = MlaMixer(self.cfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
+                mix = MlaMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
             else:
                 raise ValueError(kind)
+            mix.tp = self.tp
             out.append((lw, mix, MoeBlock(self.cfg, lw["mlp"])))
         return out
 
@@ -556,25 +560,33 @@ class Model:
         self.seqs[slot].kv_base, self.seqs[slot].kv_cap = base, cap
 
     # -- forward ----------------------------------------------------------------------------
-    def _block(self, lw, mix, mlp, X, plan, commit):
-        cfg = self.cfg
+    def _block(self, lw, mix, mlp, X, pend, plan, commit):
+        """One decoder block.  `pend` is the previous block's MLP output, still to be added to the residual
+        (under tensor parallelism it is this rank's partial sum): the add, the all-reduce and this block's
+        first RMSNorm happen in one fused op.  Returns (X, new pending output)."""
+        cfg, tp = self.cfg, self.tp
         if cfg.hc_kind == "none":
             if "ngram" in lw:
+                if pend is not None:
+                    _, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
+                    pend = None
                 X = ops.ngram_embed(self, X, plan, lw["ngram"])
-            h, X = ops.add_rmsnorm(None, X, lw["in_norm"], cfg.norm_eps)
+            h, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
             a = mix.forward(h, plan, self.seqs, commit)
-            h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps)
-            m = mlp.forward(h)
-            return ops.residual_add(X, m)
+            h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
+            return X, mlp.forward(h)
+        assert tp is None, "hyper-connection models run without tensor parallelism"
+        if pend is not None:
+            X = X + pend
         if cfg.hc_kind == "gated":
             post, h = ops.hc_gated_mix(X, lw["hc_mix"], cfg.norm_eps)
             X = X + post.unsqueeze(-1).to(X.dtype) * mix.forward(h, plan, self.seqs, commit).unsqueeze(1)
             post, h = ops.hc_gated_mix(X, lw["hc_mlp"], cfg.norm_eps)
-            return X + post.unsqueeze(-1).to(X.dtype) * mlp.forward(h).unsqueeze(1)
+            return X + post.unsqueeze(-1).to(X.dtype) * mlp.forward(h).unsqueeze(1), None
         h, post, comb = ops.mhc_pre(X, lw["hc_mix"], cfg.sinkhorn_iters, cfg.norm_eps)
         X = ops.mhc_post(X, mix.forward(h, plan, self.seqs, commit), post, comb)
         h, post, comb = ops.mhc_pre(X, lw["hc_mlp"], cfg.sinkhorn_iters, cfg.norm_eps)
-        return ops.mhc_post(X, mlp.forward(h), post, comb)
+        return ops.mhc_post(X, mlp.forward(h), post, comb), None
 
     @torch.no_grad()
     def forward(self, plan: Plan, commit: bool = True, want_hidden: bool = False, graph_mode: bool = False):
@@ -589,15 +601,17 @@ class Model:
         if cfg.hc_kind != "none":
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
         self._ids_for_ngram = plan
+        pend = None
         for lw, mix, mlp in self.layers:
-            X = self._block(lw, mix, mlp, X, plan, commit)
+            X, pend = self._block(lw, mix, mlp, X, pend, plan, commit)
         if cfg.hc_kind == "gated":
             _, X = ops.hc_gated_mix(X, W["hc_final"], cfg.norm_eps)
             hn = X
-        else:
-            if cfg.hc_kind == "mhc":
-                X = X.mean(1)
+        elif cfg.hc_kind == "mhc":
+            X = X.mean(1)
             hn = ops.rmsnorm(X, W["final_norm"], cfg.norm_eps)
+        else:
+            hn, X = ops.add_rmsnorm(pend, X, W["final_norm"], cfg.norm_eps, self.tp)
         self.hidden_out = X
         self._pending_plan = None if commit else plan
         if commit and not graph_mode:       # under a captured graph the engine tracks lengths itself
@@ -606,6 +620,12 @@ class Model:
         if plan.logit_rows.shape[0] != hn.shape[0]:
             hn = hn[plan.logit_rows]
         return ops.lm_head(hn, W["lm_head"])
+
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy token ids (int32) from the logits `forward` returned (vocabulary-parallel under TP)."""
+        if self.tp is not None:
+            return self.tp.greedy(logits, logits.shape[1])
+        return ops.argmax(logits)
 
     def commit(self, accepted: List[List[int]]):
         """accepted[i]: segment-local rows of segment i that become part of the sequence, a path

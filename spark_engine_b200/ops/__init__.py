@@ -85,8 +85,27 @@ def rmsnorm(x, w, eps):
     return L.rms(x.float(), w.float(), eps).to(x.dtype)
 
 
-def add_rmsnorm(delta, res, w, eps):
-    """res' = res + delta (delta may be None); returns (rmsnorm(res') * w, res')."""
+class Partial:
+    """A row-parallel product x @ W_shard^T that has not been computed yet: under tensor parallelism the
+    GEMV, the all-reduce, the residual add and the next RMSNorm run as one kernel."""
+
+    def __init__(self, x, w):
+        self.x, self.w = x, w
+
+
+def row_parallel(x, w, tp=None):
+    """Output projection of a mixer.  Without tensor parallelism: the product.  With it: this rank's partial
+    product, deferred when the fused GEMV + all-reduce kernel can take it (EXL3 weights, <= 16 rows)."""
+    if tp is not None and tp.can_fuse_gemv(x, w):
+        return Partial(x, w)
+    return linear(x, w)
+
+
+def add_rmsnorm(delta, res, w, eps, tp=None):
+    """res' = res + delta (delta may be None); returns (rmsnorm(res') * w, res').  With `tp`, delta is this
+    rank's partial sum and is all-reduced first (one fused kernel on the device)."""
+    if tp is not None and delta is not None:
+        return tp.add_rmsnorm(delta, res, w, eps)
     if use_kernels(res):
         return cuda_ops().add_rmsnorm(delta, res, w, eps)
     if delta is not None:
@@ -134,11 +153,14 @@ def moe(h, w, c):
     out = torch.zeros(R, h.shape[1], dtype=torch.float32, device=h.device)
     hf = h.float()
     wgu, wd = w["w_gu"], w["w_down"]
+    lo, hi = w.get("ep", (0, c.n_experts))       # expert-parallel rank: only its own experts, partial output
     for slot in range(c.top_k):
         for e in idx[:, slot].unique().tolist():
+            if not lo <= e < hi:
+                continue
             rows = (idx[:, slot] == e).nonzero(as_tuple=True)[0]
-            gu = hf[rows] @ _expert(wgu, e).t()
-            y = L.swiglu(gu[:, : c.ffn], gu[:, c.ffn:], c.swiglu_limit) @ _expert(wd, e).t()
+            gu = hf[rows] @ _expert(wgu, e - lo).t()
+            y = L.swiglu(gu[:, : c.ffn], gu[:, c.ffn:], c.swiglu_limit) @ _expert(wd, e - lo).t()
             out[rows] += wts[rows, slot].unsqueeze(1) * y
     if "s_gu" in w:
         gu = linear(h, w["s_gu"]).float()

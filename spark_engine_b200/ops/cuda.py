@@ -40,9 +40,9 @@ _SIGS = {
                         vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     "spark_attn_decode": [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
                           f32, vp, vp],
-    "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp],
+    "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp, i32, i32],
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
-    "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp],
+    "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp, vp],
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
                         f32, i32, vp, vp],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
@@ -332,7 +332,7 @@ def gather_rows(src, idx32):
 ROUTER_KIND = {"softmax": 0, "sigmoid_bias": 1, "sqrt_softplus": 2}
 
 
-def moe_route(h, w, c):
+def moe_route(h, w, c, e_lo=0, e_hi=None):
     R = h.shape[0]
     dev = h.device
     logits = dense_linear(h, w["gate"], out_f32=True)
@@ -342,7 +342,7 @@ def moe_route(h, w, c):
     sg = torch.empty(R, dtype=torch.float32, device=dev) if c.shared_gate else None
     rc = lib().spark_moe_route(P(logits), logits.stride(0), R, c.n_experts, c.top_k, ROUTER_KIND[c.router],
                                P(w.get("bias")), float(c.route_scale), int(c.shared_gate), P(wts), P(ids), P(prow), P(sg),
-                               stream())
+                               stream(), e_lo, c.n_experts if e_hi is None else e_hi)
     check(rc, "spark_moe_route")
     return wts, ids, prow, sg
 
@@ -362,7 +362,7 @@ def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
 def moe_sort(ids, E):
     Pn = ids.numel()
     dev = ids.device
-    perm = torch.empty(Pn, dtype=torch.int32, device=dev)
+    perm = torch.zeros(Pn, dtype=torch.int32, device=dev)      # entries past the local pairs stay valid indices
     inv = torch.empty(Pn, dtype=torch.int32, device=dev)
     offs = torch.empty(E + 1, dtype=torch.int32, device=dev)
     max_tiles = (Pn + 127) // 128 + E
@@ -389,11 +389,14 @@ DECODE_PAIRS_MAX = 256
 
 
 def moe(h, w, c):
-    """Routed + shared experts; returns the bf16 block output [R, H]."""
+    """Routed + shared experts; returns the bf16 block output [R, H].  Under expert parallelism (`w["ep"]` =
+    (first local expert, end)) only the local experts' pairs are computed and the result is this rank's partial
+    sum; the shared expert is added by the rank that holds it."""
     h = _as_bf16(h).contiguous()
     R, H = h.shape
     dev = h.device
-    wts, ids, prow, sg = moe_route(h, w, c)
+    ep = w.get("ep")
+    wts, ids, prow, sg = moe_route(h, w, c, *(ep if ep else (0, None)))
     Pn = R * c.top_k
     wgu, wd = w["w_gu"], w["w_down"]
     shared = None
@@ -417,7 +420,7 @@ def moe(h, w, c):
         y = _expert_gemv(gu, wd, Pn, pe, None, 1, c.swiglu_limit, True)            # [P, H] fp32
         inv = None
     else:
-        perm, inv, offs, tiles, ntile, max_tiles = moe_sort(ids.view(-1), c.n_experts)
+        perm, inv, offs, tiles, ntile, max_tiles = moe_sort(ids.view(-1), (ep[1] - ep[0]) if ep else c.n_experts)
         src = torch.div(perm, c.top_k, rounding_mode="floor").to(torch.int32)
         a = gather_rows(h, src)
         if isinstance(wgu, Exl3Weight):
@@ -431,7 +434,7 @@ def moe(h, w, c):
             act = grouped_gemm(a, wgu.view(E * F2, K), tiles, ntile, max_tiles, E, F2, F2 // 2, 1, c.swiglu_limit)
             y = grouped_gemm(act, wd.view(E * H, F2 // 2), tiles, ntile, max_tiles, E, H, H, 0)
     rc = lib().spark_moe_combine(None, P(y), int(y.dtype == torch.float32), P(inv), P(wts), R, c.top_k, P(shared), P(sg), H,
-                                 P(out), stream())
+                                 P(out), stream(), P(ids) if ep else None)
     check(rc, "spark_moe_combine")
     return out
 

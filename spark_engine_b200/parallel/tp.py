@@ -1,0 +1,185 @@
+"""Tensor / expert parallelism of the model across the GPUs of one box.
+
+Shard rules (reference: engine-rs/src/weights.rs:119-153,831-864, docs/features.md:59-66):
+  * linear-attention and softmax-attention mixers are split by heads (q/k/v/z projections column-parallel,
+    the output projection row-parallel); KV heads are replicated when there are fewer of them than ranks;
+  * routed experts are split by expert id (each rank owns E/world experts; activations are replicated, so no
+    dispatch is needed on this path: a rank computes the pairs of its own experts and the partial outputs
+    are summed by the same all-reduce as a row-parallel layer); the shared expert lives on rank 0;
+  * lm_head is vocabulary-parallel: each rank scores V/world rows and only (value, index) packets travel
+    (reference: head_select.rs:42-67); embeddings, norms, routers, conv taps and gates are replicated.
+Two all-reduces per layer remain (after the mixer's output projection and after the MoE); on the device each
+is fused with the residual add and the following RMSNorm, and for EXL3 decode rows also with the GEMV.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config import ModelConfig
+from .. import ops
+
+
+def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
+    c = dataclasses.replace(cfg)
+    g = cfg.gdn
+    assert g.n_k_heads % world == 0 and g.n_v_heads % world == 0 or "gdn" not in cfg.layer_types
+    c.gdn = dataclasses.replace(g, n_k_heads=max(1, g.n_k_heads // world), n_v_heads=max(1, g.n_v_heads // world))
+    a = cfg.attn
+    assert a.n_q_heads % world == 0 or "attn" not in cfg.layer_types
+    c.attn = dataclasses.replace(a, n_q_heads=max(1, a.n_q_heads // world), n_kv_heads=max(1, a.n_kv_heads // world))
+    k = cfg.kda
+    c.kda = dataclasses.replace(k, n_heads=max(1, k.n_heads // world))
+    m = cfg.mla
+    c.mla = dataclasses.replace(m, n_heads=max(1, m.n_heads // world))
+    return c
+
+
+def _rows(t, lo, hi):
+    return t[lo:hi].contiguous()
+
+
+def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
+    """This rank's shard of a dense (unquantised) weight dict laid out as in models/weights.py."""
+    out = {"embed": W["embed"], "final_norm": W["final_norm"], "layers": []}
+    V = cfg.vocab
+    assert V % world == 0
+    out["lm_head"] = _rows(W["lm_head"], rank * V // world, (rank + 1) * V // world)
+    for lw in W["layers"]:
+        kind, w = lw["type"], lw["mix"]
+        nl = {"type": kind, "in_norm": lw["in_norm"], "post_norm": lw["post_norm"]}
+        if kind == "gdn":
+            c = cfg.gdn
+            D, hk, hv = c.head_dim, c.n_k_heads // world, c.n_v_heads // world
+            nq, nv = c.n_k_heads * D, c.n_v_heads * D
+            q0, v0 = rank * hk * D, rank * hv * D
+            sel = torch.cat((torch.arange(q0, q0 + hk * D), nq + torch.arange(q0, q0 + hk * D),
+                             2 * nq + torch.arange(v0, v0 + hv * D)))
+            zsel = 2 * nq + nv + torch.arange(v0, v0 + hv * D)
+            hsel = torch.arange(rank * hv, (rank + 1) * hv)
+            nl["mix"] = {"in": w["in"][torch.cat((sel, zsel))].contiguous(),
+                         "ab": w["ab"][torch.cat((hsel, c.n_v_heads + hsel))].contiguous(),
+                         "conv": w["conv"][sel].contiguous(), "A_log": w["A_log"][hsel].contiguous(),
+                         "dt_bias": w["dt_bias"][hsel].contiguous(), "norm": w["norm"],
+                         "o": w["o"][:, v0: v0 + hv * D].contiguous()}
+        elif kind == "attn":
+            c = cfg.attn
+            D = c.head_dim
+            qw = D * (2 if c.gated else 1)
+            hq = c.n_q_heads // world
+            nq, nkv = c.n_q_heads * qw, c.n_kv_heads * D
+            if c.n_kv_heads >= world:
+                hkv = c.n_kv_heads // world
+                kv0 = rank * hkv
+            else:
+                hkv, kv0 = 1, rank * c.n_kv_heads // world
+            sel = torch.cat((torch.arange(rank * hq * qw, (rank + 1) * hq * qw),
+                             nq + torch.arange(kv0 * D, (kv0 + hkv) * D),
+                             nq + nkv + torch.arange(kv0 * D, (kv0 + hkv) * D),
+                             torch.arange(nq + 2 * nkv, w["qkv"].shape[0])))
+            nl["mix"] = dict(w)
+            nl["mix"]["qkv"] = w["qkv"][sel].contiguous()
+            nl["mix"]["o"] = w["o"][:, rank * hq * D: (rank + 1) * hq * D].contiguous()
+        else:
+            raise NotImplementedError(f"tensor-parallel shard rule for layer type {kind}")
+        m = lw["mlp"]
+        if "dense_gu" in m:
+            F = cfg.moe.dense_ffn
+            f0, f1 = rank * F // world, (rank + 1) * F // world
+            nl["mlp"] = {"dense_gu": torch.cat((m["dense_gu"][f0:f1], m["dense_gu"][F + f0: F + f1])).contiguous(),
+                         "dense_down": m["dense_down"][:, f0:f1].contiguous()}
+        else:
+            E = cfg.moe.n_experts
+            e0, e1 = rank * E // world, (rank + 1) * E // world
+            nm = {"gate": m["gate"], "w_gu": m["w_gu"][e0:e1].contiguous(), "w_down": m["w_down"][e0:e1].contiguous(),
+                  "ep": (e0, e1)}
+            if "bias" in m:
+                nm["bias"] = m["bias"]
+            if "s_gu" in m and rank == 0:
+                nm["s_gu"], nm["s_down"] = m["s_gu"], m["s_down"]
+            nl["mlp"] = nm
+        out["layers"].append(nl)
+    return out
+
+
+class TPBase:
+    def __init__(self, rank: int, world: int):
+        self.rank, self.world = rank, world
+
+    def local_config(self, cfg: ModelConfig) -> ModelConfig:
+        return local_config(cfg, self.world)
+
+    def can_fuse_gemv(self, x, w) -> bool:
+        return False
+
+    def greedy(self, logits_local: torch.Tensor, vocab_local: int) -> torch.Tensor:
+        """Global arg-max from vocabulary-parallel logits: (value, index) packets, ties -> lowest id."""
+        val, idx = logits_local.max(-1)
+        pk = torch.zeros(logits_local.shape[0], 2 * self.world, dtype=torch.float32, device=logits_local.device)
+        pk[:, 2 * self.rank] = val.float()
+        pk[:, 2 * self.rank + 1] = (idx + self.rank * vocab_local).float()
+        pk = self.allreduce(pk)
+        vals, ids = pk[:, 0::2], pk[:, 1::2]
+        best = vals.max(-1, keepdim=True).values
+        cand = torch.where(vals == best, ids, torch.full_like(ids, float("inf")))
+        return cand.min(-1).values.to(torch.int32)
+
+
+class CpuTP(TPBase):
+    """gloo ranks on CPU: the host-side logic of the sharded model without a GPU."""
+
+    def __init__(self, group=None):
+        super().__init__(dist.get_rank(group), dist.get_world_size(group))
+        self.group = group
+
+    def allreduce(self, x):
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        acc = torch.zeros_like(x, dtype=torch.float32)
+        for p in parts:                      # rank order, like the device kernels
+            acc = acc + p.float()
+        return acc.to(x.dtype)
+
+    def add_rmsnorm(self, delta, res, w, eps):
+        if isinstance(delta, ops.Partial):
+            delta = ops.linear(delta.x, delta.w)
+        res = res + self.allreduce(delta.float()).to(res.dtype)
+        from ..oracle import layers as L
+        return L.rms(res.float(), w.float(), eps).to(res.dtype), res
+
+
+class DeviceTP(TPBase):
+    """Peer-memory tensor parallelism on the GPUs of one box (fused all-reduce kernels)."""
+
+    def __init__(self, arena, hidden: int, rows_cap: int = 1024, name: str = "tp"):
+        super().__init__(arena.rank, arena.world)
+        from . import symm
+        self.arena = arena
+        self.rows_cap = rows_cap
+        self.ar = symm.FusedAllReduce(arena, name + ".ar", rows_cap, hidden)
+        self.pk = symm.FusedAllReduce(arena, name + ".packets", 64, 2 * 8)
+
+    def can_fuse_gemv(self, x, w) -> bool:
+        from ..quant.formats import Exl3Weight
+        return isinstance(w, Exl3Weight) and not w.experts and x.shape[0] <= 16 and x.is_cuda
+
+    def allreduce(self, x):
+        assert x.shape[0] <= 64 and x.shape[1] <= 16
+        pad = torch.zeros(x.shape[0], 16, dtype=torch.float32, device=x.device)
+        pad[:, : x.shape[1]] = x
+        return self.pk(pad, out_dtype=torch.float32)[:, : x.shape[1]]
+
+    def add_rmsnorm(self, delta, res, w, eps):
+        if isinstance(delta, ops.Partial):
+            h = self.ar.gemv_fused(delta.x.contiguous(), delta.w, res=res, norm_w=w, eps=eps)
+            return h, res
+        R = delta.shape[0]
+        if R <= self.rows_cap:
+            return self.ar(delta, res=res, norm_w=w, eps=eps), res
+        outs = []
+        for r0 in range(0, R, self.rows_cap):
+            outs.append(self.ar(delta[r0: r0 + self.rows_cap], res=res[r0: r0 + self.rows_cap], norm_w=w, eps=eps))
+        return torch.cat(outs), res

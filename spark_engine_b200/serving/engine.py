@@ -114,20 +114,21 @@ class _DecodeGraph:
         logits = m.forward(self.plan, commit=commit, graph_mode=True)
         self.logits = logits
         self.hidden = m.hidden_out
-        self.out_ids = ops.argmax(logits)
+        self.out_ids = m.greedy(logits)
 
 
 class LLMEngine:
     def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cuda",
-                 max_seqs: int = 4, kv_tokens_per_seq: int = 4096):
+                 max_seqs: int = 4, kv_tokens_per_seq: int = 4096, tp=None):
         self.cfg, self.ecfg = cfg, ecfg or EngineConfig()
         dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
         self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=max_seqs,
-                           kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq)
+                           kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
         self.graphs: Dict[tuple, _DecodeGraph] = {}
         self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda"
         self.stats = GenStats()
+        self._rounds_since_check = 0
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -158,7 +159,7 @@ class LLMEngine:
         if not self.use_graphs:
             plan = make_plan([(s, [t], p) for s, t, p in zip(slots, ids, pos0)], device=self.device)
             logits = m.forward(plan)
-            return ops.argmax(logits).tolist()
+            return m.greedy(logits).tolist()
         key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + 1))
         g = self.graphs.get(key)
         if g is None:
@@ -168,7 +169,21 @@ class LLMEngine:
         torch.cuda.current_stream().synchronize()
         for s, p in zip(slots, pos0):
             m.seqs[s].length = p + 1
+        self._rounds_since_check += 1
+        if self._rounds_since_check >= 64:
+            self.check_device_status()
         return g.out_host.tolist()
+
+    def check_device_status(self):
+        """Fail-stop on a device-side error: a bounded wait that ran out (a peer that never arrived, a stalled
+        pipeline) leaves its code in the status word instead of hanging the GPU; the host raises here."""
+        self._rounds_since_check = 0
+        if self.device.type != "cuda":
+            return
+        from ..ops import cuda as cu
+        st = cu.read_status(self.device)
+        if st[0] != 0:
+            raise RuntimeError(f"device status {st}: a kernel gave up waiting (code {st[0]}, detail {st[1:]})")
 
     @torch.no_grad()
     def generate(self, prompts: List[Sequence[int]], max_new: int, stop_ids: Sequence[int] = ()) -> List[List[int]]:
@@ -179,7 +194,7 @@ class LLMEngine:
         t0 = time.perf_counter()
         cur = []
         for s, p in enumerate(prompts):
-            cur.append(int(torch.argmax(self.prefill(s, p))))
+            cur.append(int(self.model.greedy(self.prefill(s, p).unsqueeze(0))[0]))
             outs[s].append(cur[-1])
         if self.device.type == "cuda":
             torch.cuda.synchronize()
