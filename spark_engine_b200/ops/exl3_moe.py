@@ -18,7 +18,9 @@ def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
     E = wgu.trellis.shape[0]
     H, F2 = wgu.k, wgu.n
     F = F2 // 2
-    row_expert = ids.view(-1)[perm.long()].to(torch.int32).contiguous()
+    # rows past this rank's pairs are filler (perm 0): their expert id may be -1 (non-local) -> clamp, they are
+    # never part of a tile and never combined
+    row_expert = ids.view(-1)[perm.long()].clamp_min(0).to(torch.int32).contiguous()
     xh = cu.exl3_had_rows(a, wgu.suh, post=False, row_expert=row_expert, expert_stride=H)
     wt = cu.exl3_reconstruct(wgu, cu.scratch("exl3_recon_gu", E * F2 * H, torch.float16, dev)[: E * F2 * H].view(E, F2, H))
     acc = cu.grouped_gemm(xh, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2, 0, fmt=0)
