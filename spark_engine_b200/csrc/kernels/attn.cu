@@ -306,3 +306,64 @@ extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* v
                                               (__nv_bfloat16*)out);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory (declared in attn_noalloc.h; this entry
+// point has no counterpart in the reference).  Same kernels as spark_attn_decode, but the split partials live
+// in a fixed array inside this library instead of a caller-provided scratch buffer.
+#include "attn_noalloc.h"
+#include <cstdio>
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_scratch[SPARK_ATTN_NOALLOC_MAX_FLOATS];
+
+// `g_noalloc_scratch` names a host-side shadow here; the device address is looked up once per device.
+static float* noalloc_scratch_for_current_device(cudaError_t* err) {
+  static std::mutex mu;
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    *err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  return ptrs[dev];
+}
+
+extern "C" int spark_attn_decode_noalloc(const void* qbuf, const void* kc, const void* vc, const float* ks,
+                                         const float* vs, int fp8, const int* pos, const long long* row_kv,
+                                         const int* sel, const int* sel_n, int sel_ld, int nsplit, const void* qkv,
+                                         int ld, int gated, int R, int Hq, int Hkv, int D, float scale, void* out,
+                                         cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (D > 256 || Hq / Hkv > ATT_MAXREP || nsplit <= 0) return -5;
+  const long long need = static_cast<long long>(R) * Hq * nsplit * (D + 2);
+  if (need > SPARK_ATTN_NOALLOC_MAX_FLOATS) {
+    fprintf(stderr, "spark_attn_decode_noalloc: rows*heads*splits*(head_dim+2) = %lld floats exceeds the built-in "
+                    "scratch of %lld floats; use spark_attn_decode with a caller-provided buffer\n",
+            need, static_cast<long long>(SPARK_ATTN_NOALLOC_MAX_FLOATS));
+    return SPARK_ATTN_NOALLOC_TOO_LARGE;
+  }
+  cudaError_t err;
+  float* scratch = noalloc_scratch_for_current_device(&err);
+  if (scratch == nullptr) {
+    fprintf(stderr, "spark_attn_decode_noalloc: scratch symbol lookup failed: %s\n", cudaGetErrorString(err));
+    return -4;
+  }
+  float* part_o = scratch;
+  float* part_ml = scratch + static_cast<size_t>(R) * Hq * nsplit * D;
+  dim3 grid(R, Hkv, nsplit);
+  if (fp8)
+    attn_decode_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
+                                                  part_o, part_ml, Hq, Hkv, D, scale);
+  else
+    attn_decode_kernel<false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
+                                                   part_o, part_ml, Hq, Hkv, D, scale);
+  attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D,
+                                              (__nv_bfloat16*)out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
