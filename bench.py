@@ -97,7 +97,7 @@ def main():
     ap.add_argument("--format", default=None, help="dense | exl3 (default: the config's)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
-    ap.add_argument("--parallel", default="tp", help="N > 1: tp = one model sharded over the GPUs (tensor + expert "
+    ap.add_argument("--parallel", default="dp", help="N > 1: tp = one model sharded over the GPUs (tensor + expert "
                                                      "parallel, fused peer-memory all-reduce); dp = one replica per GPU")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,0 +1,50 @@
+"""Block-sparse selection for the sparse-attention layers: indexer scores + exact top-k (ties -> lowest index)."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import cuda as cu
+
+vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+_bound = False
+
+
+def _dll():
+    global _bound
+    dll = cu.lib()._dll
+    if not _bound:
+        dll.spark_idx_score.argtypes = [vp, i32, i32, i32, vp, vp, vp, i32, vp, f32, vp, i32, i32, vp]
+        dll.spark_idx_score.restype = i32
+        dll.spark_topk_select.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, vp, vp]
+        dll.spark_topk_select.restype = i32
+        _bound = True
+    return dll
+
+
+def select_tokens(qi, pool, row_kv, pos32, block, topk, max_ctx, head_w=None, scale=None):
+    """qi [R,H,Dm] fp32 indexer queries; pool [*, Dm] fp32 pooled keys (block b of a sequence at row_kv/block + b).
+    Returns (sel [R, topk*block + block] int32 token indices, sel_n [R])."""
+    R, H, Dm = qi.shape
+    dev = qi.device
+    nb_max = max(1, max_ctx // block)
+    score = cu.scratch("idx_score", R * nb_max, torch.float32, dev)
+    cu.add_launches(2)
+    rc = _dll().spark_idx_score(cu.P(qi), R, H, Dm, cu.P(pool), cu.P(row_kv), cu.P(pos32), block, cu.P(head_w),
+                                float(scale if scale is not None else 1.0 / math.sqrt(Dm)), cu.P(score), nb_max, nb_max,
+                                cu.stream())
+    cu.check(rc, "spark_idx_score")
+    sel_ld = topk * block + block
+    sel = torch.empty(R, sel_ld, dtype=torch.int32, device=dev)
+    sel_n = torch.empty(R, dtype=torch.int32, device=dev)
+    rc = _dll().spark_topk_select(cu.P(score), nb_max, cu.P(pos32), R, block, topk, cu.P(sel), sel_ld, cu.P(sel_n),
+                                  cu.stream())
+    cu.check(rc, "spark_topk_select")
+    return sel, sel_n
+
+
+def select_blocks(mixer, qi, plan, d):
+    c = mixer.c
+    return select_tokens(qi, mixer.ik_pool, d["row_kv"], d["pos32"], c.block, c.sparse_topk_blocks, d["max_ctx"])
