@@ -1,0 +1,317 @@
+"""Engine serving loop (rank 0 owns the socket; under TP the other ranks replay the same steps from the op log).
+
+One iteration = one unit of work chosen by the C++ scheduler: admit a request (KV lease + prefix reuse: continue an
+idle store, restore a checkpoint from the host library or the NVMe cache, or start cold), one prefill chunk, one
+batched speculative round over all decoding sequences, or a cancellation.  Reference: engine-rs/src/
+spec_probe.rs:2407-2708, qwen/serve.rs:158-470.
+"""
+from __future__ import annotations
+
+import os
+import select
+import socket
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache.kv import KvManager
+from ..cache.prefix import CheckpointLibrary, DiskPrefixCache
+from ..config import EngineConfig, ModelConfig
+from ..models.model import Model
+from ..models.plan import make_plan
+from ..runtime import rt
+from ..spec import sampling
+from ..spec.decoder import SeqSpec, SpecDecoder
+from ..spec.lookup import LookupIndex
+from ..utils.profile import Profiler
+from . import protocol as proto
+
+
+class _Live:
+    def __init__(self, msg, now):
+        self.id = msg["id"]
+        self.msg = msg
+        self.t_arrive = now
+        self.t_admit = self.t_first = None
+        self.prefill_ms = self.decode_ms = 0.0
+        self.rounds = 0
+        self.seq: Optional[SeqSpec] = None
+        self.prefix_hit = 0
+        self.sent = 0
+
+
+class EngineServer:
+    def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cpu", tp=None):
+        self.cfg, self.ecfg = cfg, ecfg or EngineConfig()
+        e = self.ecfg
+        dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
+        per = max(256, e.kv_tokens // e.max_seqs // 256 * 256)
+        self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=e.max_seqs, kv_tokens=per * e.max_seqs,
+                           slot_tokens=per, tp=tp)
+        self.slot_tokens = per
+        self.kv = KvManager(self.model, granule=256)
+        self.sched = rt().Scheduler(e.max_seqs, per * e.max_seqs, per, e.prefill_chunk, e.max_seqs)
+        drafter = "mtp" if (e.spec == "mtp" and self.model.mtp_layers) else (lambda s, d: ([], []))
+        if e.spec == "lookup":
+            drafter = "lookup"
+        self.spec = SpecDecoder(self.model, drafter, depth=e.spec_depth if e.spec != "none" else 0,
+                                policy={"theta": "theta", "tau": "tau", "rate": "rate"}.get(e.spec_policy, "all"))
+        self.library = CheckpointLibrary(8)
+        self.disk = DiskPrefixCache(e.pcache_dir, [cfg.name, cfg.to_json(), e.numerics], e.pcache_bytes) if e.pcache_dir else None
+        self.live: Dict[int, _Live] = {}
+        self.by_slot: Dict[int, _Live] = {}
+        self.prof = Profiler(e.profile)
+        self.totals = {"prompt_tokens": 0, "generation_tokens": 0, "requests": 0, "spec_rounds": 0, "drafted_tokens": 0,
+                       "accepted_drafts": 0, "prefix_hit_tokens": 0, "disk_restores": 0}
+        self.out: List[dict] = []
+        self.shutdown = False
+
+    # ------------------------------------------------------------------------------------------ requests
+    def submit(self, msg: dict):
+        now = time.time()
+        if "cancel" in msg:
+            self.sched.cancel(int(msg["cancel"]))
+            return
+        if msg.get("shutdown"):
+            self.shutdown = True
+            return
+        if msg.get("stats"):
+            self.out.append({"id": msg.get("id"), "stats": self.stats()})
+            return
+        err = proto.validate_request(msg, self.cfg.vocab, self.slot_tokens)
+        if err:
+            self.out.append({"id": msg.get("id"), "error": err})
+            return
+        R = rt().Request()
+        R.id, R.prompt, R.max_new = int(msg["id"]), list(msg["prompt_ids"]), int(msg.get("max_new", 256))
+        R.stop = list(msg.get("stop_token_ids", []))
+        R.temperature, R.seed, R.t_arrive = float(msg.get("temperature", 0.0)), int(msg.get("seed", 0)), now
+        self.live[R.id] = _Live(msg, now)
+        self.sched.submit(R)
+        self.out.append({"id": R.id, "queued": True})
+
+    def stats(self) -> dict:
+        d = dict(self.sched.stats())
+        d.update(self.kv.stats())
+        d.update(self.totals)
+        if self.disk:
+            d["pcache"] = self.disk.stats()
+        d["sections_ms"] = self.prof.table()
+        return d
+
+    # ------------------------------------------------------------------------------------------ steps
+    def step(self) -> bool:
+        """Run one unit of work.  Returns False when idle."""
+        K = rt().Step.Kind
+        disk_tokens = 0
+        st = self.sched.next(disk_tokens)
+        if st.kind == K.Idle:
+            return False
+        if st.kind == K.Admit:
+            self._admit(st.admit)
+        elif st.kind == K.Prefill:
+            self._prefill(st.slot, st.chunk_begin, st.chunk_end)
+        elif st.kind == K.Decode:
+            self._decode(list(st.decode_slots))
+        elif st.kind == K.Cancel:
+            self._finish(st.slot, "cancelled")
+        return True
+
+    def _admit(self, plan):
+        lv = self.live.get(plan.request_id)
+        if plan.slot < 0:
+            self.sched.on_admitted(plan)
+            if lv:
+                self.out.append({"id": lv.id, "error": "request does not fit the KV budget"})
+                self.live.pop(lv.id, None)
+            return
+        m, msg = self.model, lv.msg
+        prompt = msg["prompt_ids"]
+        need = len(prompt) + int(msg.get("max_new", 256))
+        reuse = 0
+        RK = rt().ReuseKind
+        if plan.kind == RK.ContinueStore and plan.slot in self.kv.lease and self.kv.grow(plan.slot, need):
+            reuse = min(plan.reuse_tokens, m.seqs[plan.slot].length)
+            self.kv.pool.pin(self.kv.lease[plan.slot], True)
+        else:
+            if not self.kv.assign(plan.slot, need):
+                self.sched.on_admitted(plan)
+                self.out.append({"id": lv.id, "error": "KV pool exhausted"})
+                self.sched.on_finished(plan.slot)
+                self.live.pop(lv.id, None)
+                return
+            m.reset_slot(plan.slot)
+            hit = self.library.longest_prefix(prompt)
+            if hit is not None:
+                m.restore(plan.slot, hit[1])
+                reuse = hit[1]["length"]
+            elif self.disk is not None:
+                t, key = self.disk.lookup(prompt)
+                snap = self.disk.load(key) if t else None
+                if snap is not None:
+                    m.restore(plan.slot, snap)
+                    reuse = snap["length"]
+                    self.totals["disk_restores"] += 1
+        # the scheduler's plan carries its own estimate; the executor reports what was really reused
+        reuse = min(reuse, len(prompt) - 1)
+        m.seqs[plan.slot].length = reuse
+        self.sched.on_admitted(plan)
+        self.sched.on_prefilled(plan.slot, reuse)
+        lv.t_admit = time.time()
+        lv.prefix_hit = reuse
+        self.totals["prefix_hit_tokens"] += reuse
+        self.by_slot[plan.slot] = lv
+        lv.seq = SeqSpec(plan.slot, -1, temperature=float(msg.get("temperature", 0.0)), seed=int(msg.get("seed", 0)))
+        lv.seq.lookup = LookupIndex(self.spec.lookup_n)
+        lv.seq.lookup.extend(prompt[:reuse])
+
+    def _prefill(self, slot: int, c0: int, c1: int):
+        lv, m = self.by_slot[slot], self.model
+        prompt = lv.msg["prompt_ids"]
+        t0 = time.time()
+        with self.prof.section("prefill"):
+            toks = prompt[c0:c1]
+            logits = m.forward(make_plan([(slot, toks, c0)], device=m.device, all_logits=False))[0]
+            hid = m.hidden_out
+            if m.mtp_layers:
+                nxt = prompt[c0 + 1: c1 + 1]
+                if nxt:
+                    m.mtp_forward(make_plan([(slot, nxt, c0)], device=m.device, all_logits=False), hid[: len(nxt)])
+        lv.seq.lookup.extend(toks)
+        lv.prefill_ms += (time.time() - t0) * 1e3
+        self.sched.on_prefilled(slot, c1)
+        if c1 == len(prompt):
+            s = lv.seq
+            first = sampling.sample(logits, s.temperature, s.seed, len(prompt))
+            s.last_token, s.hidden = first, hid[-1].clone()
+            s.pending_mtp = [(hid[-1].clone(), first)]
+            s.generated = [first]
+            s.lookup.extend([first])
+            lv.t_first = time.time()
+            self.totals["prompt_tokens"] += len(prompt)
+            boundary = len(prompt) // 256 * 256
+            if self.disk is not None and boundary and boundary == len(prompt):
+                self.disk.save(prompt, m.snapshot(slot))
+            self._emit(lv, [first])
+
+    def _emit(self, lv: _Live, toks: List[int]):
+        msg = lv.msg
+        stop = set(msg.get("stop_token_ids", []))
+        max_new = int(msg.get("max_new", 256))
+        self.out.append({"id": lv.id, "delta": toks})
+        lv.sent += len(toks)
+        self.totals["generation_tokens"] += len(toks)
+        done = lv.sent >= max_new or (toks and toks[-1] in stop)
+        self.sched.on_tokens(lv.seq.slot, toks, False)
+        if done:
+            self._finish(lv.seq.slot, "stop" if (toks and toks[-1] in stop) else "length")
+
+    def _decode(self, slots: List[int]):
+        lvs = [self.by_slot[s] for s in slots]
+        t0 = time.time()
+        budgets = [int(lv.msg.get("max_new", 256)) - lv.sent for lv in lvs]
+        stops = set()
+        for lv in lvs:
+            stops.update(lv.msg.get("stop_token_ids", []))
+        with self.prof.section("spec.round"):
+            outs = self.spec.round([lv.seq for lv in lvs], budgets, stop=tuple(stops))
+        dt = (time.time() - t0) * 1e3
+        self.totals["spec_rounds"] += 1
+        for lv, out in zip(lvs, outs):
+            lv.decode_ms += dt
+            lv.rounds += 1
+            own_stop = set(lv.msg.get("stop_token_ids", []))
+            cut = []
+            for t in out:
+                cut.append(t)
+                if t in own_stop:
+                    break
+            self._emit(lv, cut)
+
+    def _finish(self, slot: int, reason: str):
+        lv = self.by_slot.pop(slot, None)
+        if lv is None:
+            self.sched.on_finished(slot)
+            return
+        s = lv.seq
+        self.totals["requests"] += 1
+        self.totals["drafted_tokens"] += s.drafted
+        self.totals["accepted_drafts"] += s.accepted
+        gen = s.generated[: lv.sent]
+        self.out.append({"id": lv.id, "done": True, "token_ids": gen, "finish_reason": reason,
+                         "queue_ms": round(((lv.t_admit or time.time()) - lv.t_arrive) * 1e3, 3),
+                         "prefill_ms": round(lv.prefill_ms, 3), "decode_ms": round(lv.decode_ms, 3),
+                         "ttft_ms": round(((lv.t_first or time.time()) - lv.t_arrive) * 1e3, 3),
+                         "prefix_hit_tokens": lv.prefix_hit, "rounds": lv.rounds, "accepted_drafts": s.accepted,
+                         "drafted_tokens": s.drafted})
+        # keep the finished store for prefix reuse: history = prompt + generated tokens that are in the state
+        m = self.model
+        L = m.seqs[slot].length
+        if reason != "cancelled" and 0 < L <= 8192:
+            self.library.save((lv.msg["prompt_ids"] + gen)[:L], m.snapshot(slot))
+        self.kv.idle(slot)
+        self.sched.on_finished(slot)
+        self.live.pop(lv.id, None)
+
+    # ------------------------------------------------------------------------------------------ socket loop
+    def serve_forever(self, path: str, idle_sleep: float = 0.002, ready_cb=None):
+        if os.path.exists(path):
+            os.unlink(path)
+        srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        srv.bind(path)
+        srv.listen(4)
+        srv.setblocking(False)
+        conns: Dict[socket.socket, proto.LineBuffer] = {}
+        owner: Dict[int, socket.socket] = {}
+        print("[serve] rank0 ready", flush=True)
+        if ready_cb:
+            ready_cb()
+        while not self.shutdown:
+            rl, _, _ = select.select([srv] + list(conns), [], [], 0)
+            for s in rl:
+                if s is srv:
+                    c, _ = srv.accept()
+                    c.setblocking(False)
+                    conns[c] = proto.LineBuffer()
+                    continue
+                try:
+                    data = s.recv(1 << 16)
+                except BlockingIOError:
+                    continue
+                except ConnectionError:
+                    data = b""
+                if not data:                          # front end gone: cancel everything it owns
+                    for rid, c in list(owner.items()):
+                        if c is s:
+                            self.sched.cancel(rid)
+                            owner.pop(rid, None)
+                    conns.pop(s, None)
+                    s.close()
+                    continue
+                for msg in conns[s].feed(data):
+                    if "id" in msg and "prompt_ids" in msg:
+                        owner[int(msg["id"])] = s
+                    if msg.get("stats"):
+                        owner[msg.get("id", -1)] = s
+                    self.submit(msg)
+            busy = self.step()
+            for msg in self.out:
+                c = owner.get(msg.get("id", -1))
+                if c is None and conns:
+                    c = next(iter(conns))
+                if c is not None and c in conns:
+                    try:
+                        c.sendall(proto.encode(msg))
+                    except (BlockingIOError, ConnectionError):
+                        pass
+                if msg.get("done") or msg.get("error"):
+                    owner.pop(msg.get("id", -1), None)
+            self.out = []
+            if not busy:
+                time.sleep(idle_sleep)
+        for c in conns:
+            c.close()
+        srv.close()
+        if os.path.exists(path):
+            os.unlink(path)
