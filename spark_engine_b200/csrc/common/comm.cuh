@@ -73,19 +73,19 @@ __device__ __forceinline__ uint32_t comm_seq(const uint32_t* seq_ptr, uint32_t h
 
 // Shared tail: wait for every rank's flag, then rows r = first, first+stride, ...: rank-ordered sum
 // (+ residual)(+ RMSNorm).  Called by whole CTAs (blockDim.x threads).
-__device__ __forceinline__ void ar_rows_tail(const ArRows& a, int first_row, int row_stride, float* red_smem) {
+__device__ __forceinline__ void ar_rows_tail(const ArRows& a, uint32_t seq, int first_row, int row_stride, float* red_smem) {
   const int W = a.c.world;
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (threadIdx.x < W) {
-    if (!wait_flag(a.c, reinterpret_cast<const uint32_t*>(a.c.peers[a.c.rank] + a.flag_off) + threadIdx.x, a.seq, threadIdx.x))
+    if (!wait_flag(a.c, reinterpret_cast<const uint32_t*>(a.c.peers[a.c.rank] + a.flag_off) + threadIdx.x, seq, threadIdx.x))
       ok_s = 0;
   }
   __syncthreads();
   if (!ok_s) return;
   const float* slots = reinterpret_cast<const float*>(a.c.peers[a.c.rank] + a.slot_off) +
-                       static_cast<size_t>(a.seq & 1) * W * a.rows_cap * a.N;
+                       static_cast<size_t>(seq & 1) * W * a.rows_cap * a.N;
   for (int r = first_row; r < a.R; r += row_stride) {
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
@@ -137,14 +137,14 @@ __device__ __forceinline__ void ar_rows_tail(const ArRows& a, int first_row, int
 }
 
 // Signal "all my rows are in every peer's slot": called by one thread after the CTA's pushes are fenced.
-__device__ __forceinline__ bool ar_arrive_and_is_last(const ArRows& a, int n_ctas) {
+__device__ __forceinline__ bool ar_arrive_and_is_last(const ArRows& a, uint32_t seq, int n_ctas) {
   __threadfence_system();
   const int old = atomicAdd(a.counter, 1);
   if (old != n_ctas - 1) return false;
   *a.counter = 0;
   for (int p = 0; p < a.c.world; ++p)
-    st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, a.seq);
-  if (a.seq_ptr) *a.seq_ptr = a.seq;       // every CTA of this launch has read the counter before arriving
+    st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, seq);
+  if (a.seq_ptr) *a.seq_ptr = seq;       // every CTA of this launch has read the counter before arriving
   return true;
 }
 

@@ -55,10 +55,10 @@ allreduce_rows_kernel(ArRows a_in) {
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a, gridDim.x) ? 1 : 0;
+  if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a, a.seq, gridDim.x) ? 1 : 0;
   __syncthreads();
   // every CTA finishes its own row once all flags are in
-  ar_rows_tail(a, r, gridDim.x, red);
+  ar_rows_tail(a, a.seq, r, gridDim.x, red);
 }
 
 // ------------------------------------------------------------------------------------------ RS / AG by rows
@@ -273,7 +273,7 @@ ar_push_kernel(ArRows a_in) {
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) ar_arrive_and_is_last(a, gridDim.x);
+  if (threadIdx.x == 0) ar_arrive_and_is_last(a, a.seq, gridDim.x);
 }
 
 __global__ void __launch_bounds__(256)
@@ -281,7 +281,7 @@ ar_tail_kernel(ArRows a_in, int* tail_counter) {
   __shared__ float red[8];
   ArRows a = a_in;
   a.seq = comm_seq(a.seq_ptr, a.seq);
-  ar_rows_tail(a, blockIdx.x, gridDim.x, red);
+  ar_rows_tail(a, a.seq, blockIdx.x, gridDim.x, red);
   __syncthreads();
   if (threadIdx.x == 0 && a.seq_ptr) {                   // last CTA of the tail closes the sequence
     __threadfence();

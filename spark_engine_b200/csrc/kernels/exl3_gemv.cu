@@ -31,13 +31,28 @@ struct Exl3GemvArgs {
   ArRows ar;                                    //    rank and the last CTA does all-reduce + residual + RMSNorm
 };
 
+#ifndef SPARK_EXL3_MINB
+#define SPARK_EXL3_MINB 6   // 40 registers: 6 CTAs (48 warps) per SM; measured faster than 4 (64 regs) or 2 (94 regs)
+#endif
 constexpr int EXL3_MAX_KS = 2048;              // K-slice per CTA (activation slice lives in shared memory)
 
+// Fused all-reduce tail (rare path, kept out of line so that it costs the GEMV no registers): the last strip of
+// this rank to finish raises the flags, waits (bounded) for every peer's flag and reduces all rows: sum in rank
+// order + residual + RMSNorm.
+__device__ __noinline__ void exl3_fused_ar_tail(const Exl3GemvArgs& a) {
+  __shared__ int last_s;
+  __shared__ float red_s[8];
+  const uint32_t seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a.ar, seq, gridDim.x) ? 1 : 0;
+  __syncthreads();
+  if (last_s) ar_rows_tail(a.ar, seq, 0, 1, red_s);
+}
+
 template <int CB, bool HI>       // HI: more than 8 activation rows (the upper half of the MMA tile is live)
-__global__ void __launch_bounds__(256, 6)      // 40 registers: 6 CTAs (48 warps) per SM hide the decode dependency chains
-exl3_gemv_kernel(Exl3GemvArgs a_in) {
-  Exl3GemvArgs a = a_in;
-  if (a.fuse_ar) a.ar.seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
+__global__ void __launch_bounds__(256, SPARK_EXL3_MINB)
+exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
+  // (the argument block stays in constant memory: a local copy would put every field access on the stack)
   if (a.pair_expert && a.pair_expert[blockIdx.z] < 0) return;   // expert on another rank (whole cluster leaves)
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
@@ -164,7 +179,8 @@ exl3_gemv_kernel(Exl3GemvArgs a_in) {
     v[0] *= INV_SQRT_128 * s0.x; v[1] *= INV_SQRT_128 * s0.y; v[2] *= INV_SQRT_128 * s1.x; v[3] *= INV_SQRT_128 * s1.y;
     if (a.fuse_ar) {
       // fused all-reduce: this rank's partial strip goes straight into slot[rank] of every peer's arena
-      const size_t so = static_cast<size_t>(a.ar.seq & 1) * a.ar.c.world * a.ar.rows_cap * a.ar.N +
+      const uint32_t ar_seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
+      const size_t so = static_cast<size_t>(ar_seq & 1) * a.ar.c.world * a.ar.rows_cap * a.ar.N +
                         (static_cast<size_t>(a.ar.c.rank) * a.ar.rows_cap + r) * a.ar.N + strip * 128 + lane * 4;
       for (int p = 0; p < a.ar.c.world; ++p)
         st_f4(reinterpret_cast<float*>(a.ar.c.peers[p] + a.ar.slot_off) + so, make_float4(v[0], v[1], v[2], v[3]));
@@ -179,16 +195,7 @@ exl3_gemv_kernel(Exl3GemvArgs a_in) {
       *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
     }
   }
-  if (a.fuse_ar) {
-    // the last strip of this rank to finish raises the flags, waits (bounded) for every peer's flag and
-    // reduces all rows: sum in rank order + residual + RMSNorm
-    __shared__ int last_s;
-    __shared__ float red_s[8];
-    __syncthreads();
-    if (threadIdx.x == 0) last_s = ar_arrive_and_is_last(a.ar, gridDim.x) ? 1 : 0;
-    __syncthreads();
-    if (last_s) ar_rows_tail(a.ar, 0, 1, red_s);
-  }
+  if (a.fuse_ar) exl3_fused_ar_tail(a);
 }
 
 }  // namespace spark

@@ -18,7 +18,7 @@ from ..quant.formats import Exl3Weight, Fp8BlockWeight, Mxfp4Weight, QuantWeight
 
 _LIB = None
 _here = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_here), "_lib", "libspark_kernels.so")
+LIB_PATH = os.environ.get("SPARK_KERNEL_LIB") or os.path.join(os.path.dirname(_here), "_lib", "libspark_kernels.so")
 
 vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 
