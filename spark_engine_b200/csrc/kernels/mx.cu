@@ -1,0 +1,336 @@
+// Micro-scaled weight formats on the decode path and their converters.
+//
+//   format 0: FP8 e4m3 weights [N,K] with one fp32 scale per 128x128 block (dense projections, shared experts)
+//   format 1: MXFP4: E2M1 nibbles [N,K/2] (low nibble = even k) with one E8M0 scale per 32 along K (routed experts)
+//
+// mx_gemv_kernel: y[R<=16, N] = x[R,K] W^T for decode / verify rows and for MoE (expert,row) pairs.  The weights
+// go from global memory straight into `mma.sync.m16n8k16` B fragments: a thread loads 16 consecutive bytes of one
+// weight row and feeds them to consecutive k-steps, the activation fragment is read from shared memory with the
+// same k permutation (a contraction does not care in which order k is visited as long as A and B agree).  With
+// <= 16 rows the kernel is bound by the weight stream, so the warp-level MMA is the right tool: it removes the
+// R x FMA cost per weight that a SIMT GEMV pays.  FP8 block scales are applied to a per-iteration accumulator
+// (one iteration of a warp never crosses a 128-deep block), MXFP4 scales (powers of two) to the fp16 weight
+// pairs.  K is split over the 8 warps of a CTA in a fixed pattern and summed in warp order: run-to-run bitwise
+// equal, and a row's result does not depend on the other rows.
+// Reference kernels replaced: engine-rs/shim/ds41_mx.cu fp8_gemv_mx / up_mx / down_mx, fp8.cu, fp8ws.cu.
+//
+// mx_dequant_kernel: both formats -> bf16 [rows, K] for the tcgen05 GEMM of prefill-size batches.
+// act_quant kernels: FP8 1x128 (fp32 or power-of-two scale) and MXFP8 1x32 (E8M0) activation quantisation
+// (reference/ds41/kernel.py:59-93; engine-rs/shim/ds41_mx.cu:320-375).
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <cuda_fp16.h>
+
+#include "../common/ptx.cuh"
+
+namespace spark {
+
+constexpr int MXV_WARPS = 8;
+constexpr int MXV_COLS = 16;       // output columns per CTA (two n8 tiles, every warp covers all of them)
+
+__device__ __forceinline__ uint32_t fp8x2_to_h2(uint16_t v) {
+  __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
+  return static_cast<uint32_t>(r.x) | (static_cast<uint32_t>(r.y) << 16);
+}
+__device__ __forceinline__ uint32_t fp4x2_to_h2(uint8_t v, __half2 scale) {
+  __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(v), __NV_E2M1);
+  __half2 h = __hmul2(*reinterpret_cast<__half2*>(&r), scale);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// 2^(e-127) as fp16 (clamped to the normal range of fp16: exponents outside [-14, 15] do not occur in weights)
+__device__ __forceinline__ __half2 e8m0_h2(uint8_t e) {
+  int ex = static_cast<int>(e) - 127;
+  ex = max(-14, min(15, ex));
+  const uint16_t bits = static_cast<uint16_t>((ex + 15) << 10);
+  __half_raw hr; hr.x = bits;
+  return __half2half2(*reinterpret_cast<__half*>(&hr));
+}
+__device__ __forceinline__ float e8m0_f32(uint8_t e) { return __uint_as_float(static_cast<uint32_t>(e ? e : 0) << 23); }
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// FMT 0: W = e4m3 [N,K], scales fp32 [N/128, K/128].  FMT 1: W = nibbles [N,K/2], scales u8 [N, K/32].
+// RB = rows held in shared memory (1, 4, 8 or 16).  act 1: x is [gate | up] (2K wide), swiglu while staging.
+template <int FMT, int RB, typename TO>
+__global__ void __launch_bounds__(MXV_WARPS * 32)
+mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __restrict__ W, const void* __restrict__ scales,
+               long long w_expert_stride, long long s_expert_stride, TO* __restrict__ y, int ldy, int rows_per_item,
+               int N, int K, const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit) {
+  extern __shared__ __align__(16) uint8_t smem_mx[];
+  const int XS = K + 8;                                        // row stride in halfs: 16 bytes mod 128 -> no conflicts
+  __half* xs = reinterpret_cast<__half*>(smem_mx);              // [RB][XS]
+  float* red = reinterpret_cast<float*>(smem_mx + static_cast<size_t>(RB) * XS * 2);   // [warps][16][16]
+  const int item = blockIdx.y;
+  if (pair_expert && pair_expert[item] < 0) return;            // pair of an expert that lives on another rank
+  const int e = pair_expert ? pair_expert[item] : 0;
+  const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
+  const int R = rows_per_item;
+  for (int i = threadIdx.x; i < RB * (K >> 1); i += blockDim.x) {
+    const int r = i / (K >> 1), k = (i - r * (K >> 1)) * 2;
+    float v0 = 0.f, v1 = 0.f;
+    if (r < R) {
+      const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
+      if (act == 0) { v0 = g.x; v1 = g.y; }
+      else {
+        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + K + k));
+        float g0 = g.x, g1 = g.y, u0 = u.x, u1 = u.y;
+        if (limit > 0.f) {
+          g0 = fminf(g0, limit); g1 = fminf(g1, limit);
+          u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
+        }
+        v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
+      }
+    }
+    *reinterpret_cast<__half2*>(xs + r * XS + k) = __floats2half2_rn(v0, v1);
+  }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * MXV_COLS;
+  constexpr int KI = FMT == 0 ? 64 : 128;                      // k per warp iteration (4 threads x 16 bytes)
+  constexpr int KT = KI / 4;                                   // k per thread per iteration
+  constexpr int STEPS = KT / 4;                                // mma k-steps per iteration
+  const int iters = K / KI;
+  const size_t row_bytes = FMT == 0 ? K : (K >> 1);
+  const uint8_t* Wb = W + static_cast<size_t>(e) * w_expert_stride;
+  const uint8_t* w_lo = Wb + static_cast<size_t>(n0 + g) * row_bytes + t * 16;
+  const uint8_t* w_hi = w_lo + 8 * row_bytes;
+  const float* sc_f = nullptr;
+  const uint8_t* sc_lo = nullptr; const uint8_t* sc_hi = nullptr;
+  if (FMT == 0) sc_f = reinterpret_cast<const float*>(scales) + static_cast<size_t>(e) * s_expert_stride +
+                       static_cast<size_t>(n0 >> 7) * (K >> 7);
+  else {
+    sc_lo = reinterpret_cast<const uint8_t*>(scales) + static_cast<size_t>(e) * s_expert_stride +
+            static_cast<size_t>(n0 + g) * (K >> 5) + t;
+    sc_hi = sc_lo + 8 * (K >> 5);
+  }
+  const __half* xa = xs + (g < RB ? g : 0) * XS + t * KT;       // row g of A
+  const __half* xb = xs + ((g + 8) < RB ? (g + 8) : 0) * XS + t * KT;
+  const bool has_a = g < RB, has_b = (g + 8) < RB;
+
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  constexpr int U = 4;                                         // iterations in flight
+  for (int it0 = warp; it0 < iters; it0 += MXV_WARPS * U) {
+    uint4 wl[U], wh[U];
+    uint8_t sl[U], sh[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int it = it0 + u * MXV_WARPS;
+      if (it < iters) {
+        wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + static_cast<size_t>(it) * 64));
+        wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + static_cast<size_t>(it) * 64));
+        if (FMT == 1) { sl[u] = __ldg(sc_lo + it * 4); sh[u] = __ldg(sc_hi + it * 4); }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int it = it0 + u * MXV_WARPS;
+      if (it >= iters) break;
+      float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
+      const uint32_t* ph = reinterpret_cast<const uint32_t*>(&wh[u]);
+      __half2 hl, hh;
+      if (FMT == 1) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
+#pragma unroll
+      for (int s = 0; s < STEPS; ++s) {
+        // A: 4 consecutive k of rows g / g+8
+        uint2 av = make_uint2(0u, 0u), bv = make_uint2(0u, 0u);
+        if (has_a) av = *reinterpret_cast<const uint2*>(xa + it * KI + s * 4);
+        if (has_b) bv = *reinterpret_cast<const uint2*>(xb + it * KI + s * 4);
+        uint32_t b0l, b1l, b0h, b1h;
+        if (FMT == 0) {
+          const uint32_t vl = pl[s], vh = ph[s];
+          b0l = fp8x2_to_h2(static_cast<uint16_t>(vl & 0xffffu)); b1l = fp8x2_to_h2(static_cast<uint16_t>(vl >> 16));
+          b0h = fp8x2_to_h2(static_cast<uint16_t>(vh & 0xffffu)); b1h = fp8x2_to_h2(static_cast<uint16_t>(vh >> 16));
+        } else {
+          const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
+          b0l = fp4x2_to_h2(static_cast<uint8_t>(vl & 0xffu), hl); b1l = fp4x2_to_h2(static_cast<uint8_t>((vl >> 8) & 0xffu), hl);
+          b0h = fp4x2_to_h2(static_cast<uint8_t>(vh & 0xffu), hh); b1h = fp4x2_to_h2(static_cast<uint8_t>((vh >> 8) & 0xffu), hh);
+        }
+        mma16816(c[0], av.x, bv.x, av.y, bv.y, b0l, b1l);
+        mma16816(c[1], av.x, bv.x, av.y, bv.y, b0h, b1h);
+      }
+      float sc = 1.f;
+      if (FMT == 0) sc = __ldg(sc_f + ((it * KI) >> 7));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[0][j] = fmaf(c[0][j], sc, acc[0][j]); acc[1][j] = fmaf(c[1][j], sc, acc[1][j]); }
+    }
+  }
+  // fixed-order sum over the warps: red[warp][row][col]
+  float* rw = red + warp * 256;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    rw[g * 16 + nt * 8 + 2 * t] = acc[nt][0];
+    rw[g * 16 + nt * 8 + 2 * t + 1] = acc[nt][1];
+    rw[(g + 8) * 16 + nt * 8 + 2 * t] = acc[nt][2];
+    rw[(g + 8) * 16 + nt * 8 + 2 * t + 1] = acc[nt][3];
+  }
+  __syncthreads();
+  const int row = threadIdx.x >> 4, col = threadIdx.x & 15;
+  if (row < R && n0 + col < N) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < MXV_WARPS; ++w) v += red[w * 256 + row * 16 + col];
+    y[static_cast<size_t>(item * rows_per_item + row) * ldy + n0 + col] = static_cast<TO>(v);
+  }
+}
+
+template <int FMT, int RB, typename TO>
+static int launch_mx_gemv(const void* x, int ldx, const void* W, const void* sc, long long wes, long long ses, void* y,
+                          int ldy, int items, int rows, int N, int K, const int* pe, const int* pr, int act, float limit,
+                          cudaStream_t s) {
+  auto kern = mx_gemv_kernel<FMT, RB, TO>;
+  const int smem = RB * (K + 8) * 2 + MXV_WARPS * 256 * 4;
+  if (smem > 200 * 1024) return -6;
+  if (smem > 48 * 1024) {
+    static int set_for = 0;
+    if (!set_for) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set_for = 1; }
+  }
+  dim3 grid(N / MXV_COLS, items);
+  kern<<<grid, MXV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W, sc, wes, ses, (TO*)y, ldy, rows,
+                                          N, K, pe, pr, act, limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int FMT, typename TO>
+static int dispatch_rows(const void* x, int ldx, const void* W, const void* sc, long long wes, long long ses, void* y,
+                         int ldy, int items, int rows, int N, int K, const int* pe, const int* pr, int act, float limit,
+                         cudaStream_t s) {
+  if (rows <= 1) return launch_mx_gemv<FMT, 1, TO>(x, ldx, W, sc, wes, ses, y, ldy, items, rows, N, K, pe, pr, act, limit, s);
+  if (rows <= 4) return launch_mx_gemv<FMT, 4, TO>(x, ldx, W, sc, wes, ses, y, ldy, items, rows, N, K, pe, pr, act, limit, s);
+  if (rows <= 8) return launch_mx_gemv<FMT, 8, TO>(x, ldx, W, sc, wes, ses, y, ldy, items, rows, N, K, pe, pr, act, limit, s);
+  return launch_mx_gemv<FMT, 16, TO>(x, ldx, W, sc, wes, ses, y, ldy, items, rows, N, K, pe, pr, act, limit, s);
+}
+
+// ------------------------------------------------------------------------------------------ dequant to bf16
+// one thread = 16 consecutive k of one row; rows = experts x N flattened (scales follow the same flattening)
+template <int FMT>
+__global__ void mx_dequant_kernel(const uint8_t* __restrict__ W, const void* __restrict__ scales, __nv_bfloat16* __restrict__ out,
+                                  long long rows, int N, int K) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per_row = K >> 4;
+  if (i >= rows * per_row) return;
+  const long long r = i / per_row;
+  const int k0 = static_cast<int>(i - r * per_row) << 4;
+  float v[16];
+  if (FMT == 0) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(W + r * K + k0));
+    const long long e = r / N; const int n = static_cast<int>(r - e * N);
+    const float sc = __ldg(reinterpret_cast<const float*>(scales) + (e * (N >> 7) + (n >> 7)) * (K >> 7) + (k0 >> 7));
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(&q);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t h = fp8x2_to_h2(p[j]);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+      v[2 * j] = f.x * sc; v[2 * j + 1] = f.y * sc;
+    }
+  } else {
+    const uint2 q = __ldg(reinterpret_cast<const uint2*>(W + r * (K >> 1) + (k0 >> 1)));
+    const float sc = e8m0_f32(__ldg(reinterpret_cast<const uint8_t*>(scales) + r * (K >> 5) + (k0 >> 5)));
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&q);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(p[j]), __NV_E2M1);
+      const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+      v[2 * j] = f.x * sc; v[2 * j + 1] = f.y * sc;
+    }
+  }
+  uint4 o[2];
+  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ob[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  uint4* dst = reinterpret_cast<uint4*>(out + r * K + k0);
+  dst[0] = o[0]; dst[1] = o[1];
+}
+
+// ------------------------------------------------------------------------------------------ activation quant
+// One warp per (row, block).  BLOCK 128 -> e4m3 + fp32 scale (amax/448, clamp 1e-4; optionally rounded up to a
+// power of two); BLOCK 32 -> e4m3 + E8M0 scale byte (MXFP8: 2^ceil(log2(amax/448))).  act 1: x = [gate | up].
+template <int BLOCK, typename TI>
+__global__ void act_quant_kernel(const TI* __restrict__ x, int ldx, uint8_t* __restrict__ q, void* __restrict__ scales, int R,
+                                 int K, int pow2, int act, float limit) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nb = K / BLOCK;
+  if (warp >= R * nb) return;
+  const int r = warp / nb, b = warp - r * nb;
+  constexpr int PER = BLOCK / 32;
+  float v[PER];
+  float amax = 0.f;
+  const TI* xr = x + static_cast<size_t>(r) * ldx;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int k = b * BLOCK + lane * PER + j;
+    float a = static_cast<float>(xr[k]);
+    if (act) {
+      float u = static_cast<float>(xr[K + k]);
+      if (limit > 0.f) { a = fminf(a, limit); u = fminf(fmaxf(u, -limit), limit); }
+      a = a / (1.f + __expf(-a)) * u;
+    }
+    v[j] = a;
+    amax = fmaxf(amax, fabsf(a));
+  }
+  amax = warp_max(amax);
+  amax = fmaxf(amax, 1e-4f);
+  float sc = amax / 448.f;
+  if (BLOCK == 32 || pow2) sc = exp2f(ceilf(log2f(sc)));
+  if (lane == 0) {
+    if (BLOCK == 32) reinterpret_cast<uint8_t*>(scales)[static_cast<size_t>(r) * nb + b] =
+        static_cast<uint8_t>(__float_as_uint(sc) >> 23);
+    else reinterpret_cast<float*>(scales)[static_cast<size_t>(r) * nb + b] = sc;
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const float s = fminf(fmaxf(v[j] / sc, -448.f), 448.f);
+    q[static_cast<size_t>(r) * K + b * BLOCK + lane * PER + j] =
+        static_cast<uint8_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+// fmt 0 = FP8 128x128-block scales (fp32), 1 = MXFP4.  Strides are per expert (bytes for W, elements for scales).
+extern "C" int spark_mx_gemv(const void* x, int ldx, const void* W, const void* scales, int fmt, long long w_expert_stride,
+                             long long s_expert_stride, void* y, int ldy, int items, int rows_per_item, int N, int K,
+                             const int* pair_expert, const int* pair_row, int act, float limit, int out_f32, cudaStream_t s) {
+  if (items <= 0 || rows_per_item <= 0) return 0;
+  if (rows_per_item > 16 || N % 16 || K % 128) return -5;
+#define SPARK_MXV(FMT, TO) dispatch_rows<FMT, TO>(x, ldx, W, scales, w_expert_stride, s_expert_stride, y, ldy, items, \
+                                                  rows_per_item, N, K, pair_expert, pair_row, act, limit, s)
+  if (fmt == 0) return out_f32 ? SPARK_MXV(0, float) : SPARK_MXV(0, __nv_bfloat16);
+  if (fmt == 1) return out_f32 ? SPARK_MXV(1, float) : SPARK_MXV(1, __nv_bfloat16);
+#undef SPARK_MXV
+  return -5;
+}
+
+extern "C" int spark_mx_dequant(const void* W, const void* scales, int fmt, void* out, long long rows, int N, int K,
+                                cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (K % 128 || N % 128) return -5;
+  const long long n = rows * (K >> 4);
+  const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+  if (fmt == 0) mx_dequant_kernel<0><<<blocks, 256, 0, s>>>((const uint8_t*)W, scales, (__nv_bfloat16*)out, rows, N, K);
+  else mx_dequant_kernel<1><<<blocks, 256, 0, s>>>((const uint8_t*)W, scales, (__nv_bfloat16*)out, rows, N, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// block 128 -> fp32 scales [R, K/128]; block 32 -> E8M0 bytes [R, K/32].  x bf16 (in_f32 0) or fp32.
+extern "C" int spark_act_quant(const void* x, int ldx, int in_f32, void* q, void* scales, int R, int K, int block, int pow2,
+                               int act, float limit, cudaStream_t s) {
+  if (R <= 0) return 0;
+  if ((block != 128 && block != 32) || K % block) return -5;
+  const long long warps = static_cast<long long>(R) * (K / block);
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+#define SPARK_AQ(B, T) act_quant_kernel<B, T><<<blocks, 256, 0, s>>>((const T*)x, ldx, (uint8_t*)q, scales, R, K, pow2, act, limit)
+  if (block == 128) { if (in_f32) SPARK_AQ(128, float); else SPARK_AQ(128, __nv_bfloat16); }
+  else { if (in_f32) SPARK_AQ(32, float); else SPARK_AQ(32, __nv_bfloat16); }
+#undef SPARK_AQ
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

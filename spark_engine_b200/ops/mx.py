@@ -1,0 +1,109 @@
+"""Device ops for the micro-scaled weight formats (FP8 128x128-block dense weights, MXFP4 experts).
+
+Decode / verify rows (<= 16) and MoE (expert,row) pairs stream the packed weights through the tensor-core
+GEMV of `csrc/kernels/mx.cu`; prefill-size batches convert the weights to bf16 once per call and run the
+tcgen05 GEMM (dense) or the grouped tcgen05 GEMM over the ragged expert tile list.  Activation
+quantisers (FP8 1x128, MXFP8 1x32) are exposed for the block-scaled paths and the FP8 KV / latent stores.
+Reference: engine-rs/shim/ds41_mx.cu (fp8_gemv_mx, up_mx/down_mx, up_gemm/down_gemm, act_quant),
+fp8.cu / fp8ws.cu, engine-rs/src/ds41/load.rs:116-160.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..quant.formats import Fp8BlockWeight, Mxfp4Weight, QuantWeight
+from . import cuda as cu
+
+_vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+_SIGS = {
+    "spark_mx_gemv": [_vp, _i32, _vp, _vp, _i32, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _f32, _i32,
+                      _vp],
+    "spark_mx_dequant": [_vp, _vp, _i32, _vp, _i64, _i32, _i32, _vp],
+    "spark_act_quant": [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+}
+_bound = False
+
+
+def _lib():
+    global _bound
+    dll = cu.lib()
+    if not _bound:
+        for name, sig in _SIGS.items():
+            fn = getattr(dll._dll, name)
+            fn.argtypes, fn.restype = sig, _i32
+        _bound = True
+    return dll
+
+
+def _parts(w: QuantWeight):
+    """(packed bytes, scales, fmt, bytes per expert, scale elements per expert)"""
+    if isinstance(w, Fp8BlockWeight):
+        assert w.bn == 128 and w.bk == 128, "the device path serves 128x128 block scales"
+        q = w.q.view(torch.uint8)
+        return q, w.scales, 0, w.n * w.k, (w.n // 128) * (w.k // 128)
+    if isinstance(w, Mxfp4Weight):
+        return w.packed, w.scales, 1, w.n * w.k // 2, w.n * (w.k // 32)
+    raise TypeError(type(w))
+
+
+def gemv(x, w: QuantWeight, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0,
+         out_f32=False):
+    x = cu._as_bf16(x).contiguous()
+    q, sc, fmt, wes, ses = _parts(w)
+    rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
+    y = torch.empty(items * rows_per_item, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    rc = _lib().spark_mx_gemv(cu.P(x), x.stride(0), cu.P(q), cu.P(sc), fmt, wes, ses, cu.P(y), w.n, items, rows_per_item,
+                              w.n, w.k, cu.P(pair_expert), cu.P(pair_row), act, float(limit), int(out_f32), cu.stream())
+    cu.check(rc, "spark_mx_gemv")
+    return y
+
+
+def dequant_bf16(w: QuantWeight, out=None):
+    """All rows (all experts) of `w` as bf16 [.., N, K] on the device."""
+    q, sc, fmt, _, _ = _parts(w)
+    E = q.shape[0] if w.experts else 1
+    rows = E * w.n
+    if out is None:
+        out = torch.empty(rows * w.k, dtype=torch.bfloat16, device=q.device)
+    rc = _lib().spark_mx_dequant(cu.P(q), cu.P(sc), fmt, cu.P(out), rows, w.n, w.k, cu.stream())
+    cu.check(rc, "spark_mx_dequant")
+    return out[: rows * w.k].view(*((E,) if w.experts else ()), w.n, w.k)
+
+
+def act_quant(x, block=128, pow2=False, act=0, limit=0.0):
+    """x [R, K] (or [R, 2K] = [gate | up] with act=1) bf16/fp32 -> (e4m3 [R, K], scales): fp32 [R, K/128] for
+    block 128, E8M0 bytes [R, K/32] for block 32."""
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype in (torch.bfloat16, torch.float32)
+    R = x.shape[0]
+    K = x.shape[1] // (2 if act else 1)
+    q = torch.empty(R, K, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(R, K // block, dtype=torch.float32 if block == 128 else torch.uint8, device=x.device)
+    rc = _lib().spark_act_quant(cu.P(x), x.stride(0), int(x.dtype == torch.float32), cu.P(q), cu.P(sc), R, K, block,
+                                int(pow2), act, float(limit), cu.stream())
+    cu.check(rc, "spark_act_quant")
+    return q.view(torch.float8_e4m3fn), sc
+
+
+def quant_linear(x, w: QuantWeight):
+    x = cu._as_bf16(x).contiguous()
+    if x.shape[0] <= 16:
+        return gemv(x, w)
+    wt = dequant_bf16(w, cu.scratch("mx_deq", w.n * w.k, torch.bfloat16, x.device))
+    return cu.gemm_bf16(x, wt)
+
+
+def expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
+    return gemv(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act, limit=limit,
+                out_f32=out_f32)
+
+
+def grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
+    """Rows in expert order through gate/up (+SwiGLU epilogue) and down; returns fp32 [P, H]."""
+    E, F2, H = wgu.packed.shape[0] if isinstance(wgu, Mxfp4Weight) else wgu.q.shape[0], wgu.n, wgu.k
+    dev = a.device
+    wt = dequant_bf16(wgu, cu.scratch("mx_deq_gu", E * F2 * H, torch.bfloat16, dev))
+    act = cu.grouped_gemm(a, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2 // 2, 1, c.swiglu_limit)
+    wt2 = dequant_bf16(wd, cu.scratch("mx_deq_d", E * H * (F2 // 2), torch.bfloat16, dev))
+    return cu.grouped_gemm(act, wt2.view(E * H, F2 // 2), tiles, ntile, max_tiles, E, H, H, 0)
