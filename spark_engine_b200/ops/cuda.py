@@ -36,6 +36,8 @@ _SIGS = {
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
+                                i32, f32, vp],
     "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
                         vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     "spark_attn_decode": [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
@@ -451,6 +453,36 @@ def _plan_dev(plan, device):
     return plan.dev
 
 
+GDN_CHUNKED = os.environ.get("SPARK_GDN_CHUNKED", "1") == "1"
+GDN_CHUNK_MIN_ROWS = 64
+_KERNELS_PER_CALL["spark_gdn_chunk_prefill"] = 3
+
+
+def _gdn_chunk_prefill(mixer, proj, ab, plan, d, out):
+    """Committed segments of >= 64 rows: chunked (WY-form) gated delta rule on tensor cores, three launches."""
+    c, w, dev = mixer.c, mixer.w, proj.device
+    if "gdn_chunks" not in d:
+        chunks, first = [], []
+        for i, sg in enumerate(plan.segs):
+            first.append(len(chunks))
+            chunks += [(i, k) for k in range((sg.n + 63) // 64)]
+        d["gdn_chunks"] = torch.tensor(chunks, dtype=torch.int32).to(dev)
+        d["gdn_chunk0"] = torch.tensor(first, dtype=torch.int32).to(dev)
+    chunks, first = d["gdn_chunks"], d["gdn_chunk0"]
+    nch = chunks.shape[0]
+    dll = lib()
+    fn = dll._dll.spark_gdn_chunk_ws_floats
+    fn.restype, fn.argtypes = C.c_longlong, [i32, i32]
+    ws = scratch("gdn_chunk_ws", fn(nch, c.n_v_heads), torch.float32, dev)
+    o_raw = scratch("gdn_chunk_o", proj.shape[0] * c.n_v_heads * c.head_dim, torch.float32, dev)
+    rc = dll.spark_gdn_chunk_prefill(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]),
+                                     P(w["dt_bias"]), P(w["norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), len(plan.segs),
+                                     P(chunks), nch, P(first), P(ws), P(o_raw), P(out), out.stride(0), c.n_k_heads,
+                                     c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), stream())
+    check(rc, "spark_gdn_chunk_prefill")
+    return out
+
+
 def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None):
     if plan.is_tree:
         raise NotImplementedError("tree verify of gated-DeltaNet layers runs on the chain kernel only")
@@ -459,6 +491,9 @@ def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None):
     R = proj.shape[0]
     out = torch.empty(R, c.n_v_heads * c.head_dim, dtype=torch.bfloat16, device=proj.device)
     w = mixer.w
+    if (commit and n_rows is None and c.head_dim == 128 and GDN_CHUNKED
+            and min(s.n for s in plan.segs) >= GDN_CHUNK_MIN_ROWS):
+        return _gdn_chunk_prefill(mixer, proj, ab, plan, d, out)
     rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
                              P(w["norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows), len(plan.segs), P(out),
                              out.stride(0), c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit),
