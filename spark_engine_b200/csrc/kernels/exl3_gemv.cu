@@ -69,6 +69,9 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
 
+  // every CTA of the cluster must be running before its shared memory is written remotely: arrive now, wait
+  // right before the first remote store
+  if (a.S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   // ---- issue this warp's trellis loads first (they do not depend on the prologue)
   const int nt = strip * 8 + warp;
   const uint32_t* tw = a.trellis + e * a.t_stride + (static_cast<size_t>(slice) * kts * NT + nt) * 32 + lane;
@@ -152,6 +155,7 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
   //      no round trip), one cluster barrier, then rank 0 sums the slices in rank order:
   //      y = had128(sum) * svh.
   {
+    if (a.S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     float* dst = (a.S > 1 ? cluster.map_shared_rank(red, 0) : red) + static_cast<size_t>(slice) * R * 128;
     const int c = warp * 16 + 2 * t;
     if (lo_row) {

@@ -36,6 +36,7 @@ _SIGS = {
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
                                 i32, f32, vp],
     "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
@@ -252,6 +253,31 @@ def exl3_had_rows(x, scale, post: bool, row_expert=None, expert_stride=0):
     rc = lib().spark_exl3_had_rows(P(x), x.stride(0), P(scale), P(y), Cn, R, Cn, int(post), P(row_expert), stream(),
                                    expert_stride)
     check(rc, "spark_exl3_had_rows")
+    return y
+
+
+def _pick_mg_slices(K: int) -> int:
+    """K-slices (cluster size) of the grouped EXL3 GEMM: the smallest of 1/2/4/8 that brings the slice to <= 512."""
+    blocks = K // 128
+    target = int(os.environ.get("SPARK_MG_KS", "512"))
+    best = 1
+    for s in (1, 2, 4, 8):
+        if blocks % s == 0:
+            best = s
+            if K // s <= target:
+                break
+    return best
+
+
+def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False):
+    """Rows in expert order (fp16, input Hadamard applied) x expert trellises -> [P, N]; output Hadamard fused."""
+    Pn, K = xh.shape
+    y = torch.empty(Pn, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=xh.device)
+    t = w.trellis
+    rc = lib().spark_exl3_mgemm(P(xh), xh.stride(0), P(t), P(w.svh), (K // 16) * (w.n // 16) * 32, w.n, P(tiles),
+                                P(ntile), max_tiles, P(y), w.n, int(out_f32), K, w.n, _pick_mg_slices(K),
+                                0 if w.kind == "mul1" else 1, stream())
+    check(rc, "spark_exl3_mgemm")
     return y
 
 

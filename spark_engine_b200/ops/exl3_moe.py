@@ -1,16 +1,24 @@
 """Prefill-size MoE over EXL3 experts: dequant to the tcgen05 grouped GEMM.
 
-Rows arrive in expert order.  Per projection: input Hadamard with the row's expert sign/scale vector
-(fp16), all experts' trellises reconstructed to fp16 K-major matrices in one launch, grouped tcgen05
+Rows arrive in expert order.  Default: per projection an input Hadamard with the row's expert sign/scale
+vector (fp16), then the fused grouped kernel (`exl3_mgemm.cu`) that decodes each expert's packed trellis once
+per <= 64 rows straight into MMA fragments and applies the output Hadamard in its epilogue.  With very many rows
+per expert: all experts' trellises reconstructed to fp16 K-major matrices in one launch, grouped tcgen05
 GEMM over the <=128-row tile list, output Hadamard with the expert's output vector.  The reference
 runs this with mma.sync grouped kernels that decode B tiles in the mainloop
 (engine-rs/shim/moe_exl3.cuh:521-1233).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import cuda as cu
+
+
+EXL3_MOE_FUSED = os.environ.get("SPARK_EXL3_MOE_FUSED", "1") == "1"
+FUSED_MAX_ROWS_PER_EXPERT = 512      # beyond this the one-off reconstruction is cheaper than decoding once per 64 rows
 
 
 def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
@@ -22,6 +30,12 @@ def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
     # never part of a tile and never combined
     row_expert = ids.view(-1)[perm.long()].clamp_min(0).to(torch.int32).contiguous()
     xh = cu.exl3_had_rows(a, wgu.suh, post=False, row_expert=row_expert, expert_stride=H)
+    if EXL3_MOE_FUSED and wgu.bits == 4 and a.shape[0] <= FUSED_MAX_ROWS_PER_EXPERT * E:
+        # packed trellises straight into the MMA: decode once per <= 64 rows of an expert, output Hadamard fused
+        gu = cu.exl3_mgemm(xh, wgu, tiles, ntile, max_tiles)
+        act = cu.swiglu(gu, c.swiglu_limit)
+        xh2 = cu.exl3_had_rows(act, wd.suh, post=False, row_expert=row_expert, expert_stride=F)
+        return cu.exl3_mgemm(xh2, wd, tiles, ntile, max_tiles, out_f32=True)
     wt = cu.exl3_reconstruct(wgu, cu.scratch("exl3_recon_gu", E * F2 * H, torch.float16, dev)[: E * F2 * H].view(E, F2, H))
     acc = cu.grouped_gemm(xh, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2, 0, fmt=0)
     gu = cu.exl3_had_rows(acc, wgu.svh, post=True, row_expert=row_expert, expert_stride=F2)

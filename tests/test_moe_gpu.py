@@ -56,3 +56,29 @@ def test_moe_block(fmt, R):
     assert err < 2e-2, err
     out2 = ops.moe(h, w, c)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("H,F,R", [(2048, 256, 300), (1024, 512, 77), (4096, 128, 130)])
+def test_exl3_prefill_experts_fused_kernel_vs_reconstruct_path(H, F, R):
+    """The fused grouped EXL3 kernel (packed trellis -> MMA, clusters along K) against the reconstruct + tcgen05
+    path and the fp32 reference."""
+    from spark_engine_b200.ops import exl3_moe
+    g = torch.Generator(device=DEV).manual_seed(5)
+    c = MoeConfig(n_experts=16, top_k=4, ffn=F, router="softmax", shared_gate=True)
+    w = _weights(c, H, "exl3", g)
+    h = torch.randn(R, H, device=DEV, generator=g).bfloat16()
+    outs = []
+    for fused in (True, False):
+        exl3_moe.EXL3_MOE_FUSED = fused
+        try:
+            outs.append(ops.moe(h, w, c))
+            if fused:
+                assert torch.equal(outs[0], ops.moe(h, w, c))
+        finally:
+            exl3_moe.EXL3_MOE_FUSED = True
+    torch.cuda.synchronize()
+    ref = _ref(h, w, c)
+    for o in outs:
+        err = ((o.float().cpu() - ref).norm() / ref.norm()).item()
+        assert err < 2e-2, err
+    assert ((outs[0].float() - outs[1].float()).norm() / outs[1].float().norm()).item() < 1e-2
