@@ -36,7 +36,8 @@ _SIGS = {
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
-    "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp],
+    "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
+    "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
                                 i32, f32, vp],
     "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
@@ -256,10 +257,9 @@ def exl3_had_rows(x, scale, post: bool, row_expert=None, expert_stride=0):
     return y
 
 
-def _pick_mg_slices(K: int) -> int:
-    """K-slices (cluster size) of the grouped EXL3 GEMM: the smallest of 1/2/4/8 that brings the slice to <= 512."""
+def _pick_mg_slices(K: int, target: int) -> int:
+    """K-slices (cluster size) of the grouped EXL3 GEMM: the smallest of 1/2/4/8 that brings the slice to <= target."""
     blocks = K // 128
-    target = int(os.environ.get("SPARK_MG_KS", "512"))
     best = 1
     for s in (1, 2, 4, 8):
         if blocks % s == 0:
@@ -269,14 +269,16 @@ def _pick_mg_slices(K: int) -> int:
     return best
 
 
-def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False):
+def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False, rows_per_item=64):
     """Rows in expert order (fp16, input Hadamard applied) x expert trellises -> [P, N]; output Hadamard fused."""
     Pn, K = xh.shape
     y = torch.empty(Pn, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=xh.device)
     t = w.trellis
+    # slice depth: two (64-row items) or three (32-row items) CTAs per SM must fit their rows + reduction buffers
+    target = int(os.environ.get("SPARK_MG_KS", "512" if rows_per_item == 32 else "256"))
     rc = lib().spark_exl3_mgemm(P(xh), xh.stride(0), P(t), P(w.svh), (K // 16) * (w.n // 16) * 32, w.n, P(tiles),
-                                P(ntile), max_tiles, P(y), w.n, int(out_f32), K, w.n, _pick_mg_slices(K),
-                                0 if w.kind == "mul1" else 1, stream())
+                                P(ntile), max_tiles, P(y), w.n, int(out_f32), K, w.n, _pick_mg_slices(K, target),
+                                0 if w.kind == "mul1" else 1, rows_per_item, stream())
     check(rc, "spark_exl3_mgemm")
     return y
 
@@ -541,6 +543,10 @@ def kda_mixer(mixer, pre, lr, plan, commit):
 ATT_TS = 64
 
 
+ATTN_PREFILL_KERNEL = os.environ.get("SPARK_ATTN_PREFILL", "1") == "1"
+ATTN_PREFILL_MIN_ROWS = 32
+
+
 def attn_mixer(mixer, qkv, plan, seqs):
     if plan.is_tree:
         raise NotImplementedError("tree-verify attention mask kernel")
@@ -574,6 +580,15 @@ def attn_mixer(mixer, qkv, plan, seqs):
         sel, sel_n = sp.select_blocks(mixer, qi, plan, d)
         sel_ld = sel.shape[1]
         max_ctx = sel_ld
+    if (sel is None and not mixer.fp8 and ATTN_PREFILL_KERNEL and c.head_dim in (64, 128, 256)
+            and min(s.n for s in plan.segs) >= ATTN_PREFILL_MIN_ROWS):
+        # whole segments, dense context: flash-style tensor-core kernel (one CTA per 64 rows of a head)
+        out = torch.empty(R, c.n_q_heads * c.head_dim, dtype=torch.bfloat16, device=dev)
+        rc = lib().spark_attn_prefill(P(qbuf), P(mixer.k), P(mixer.v), P(d["row_kv"]), P(d["seg"]), len(plan.segs),
+                                      max(s.n for s in plan.segs), P(qkv), qkv.stride(0), int(c.gated), P(out),
+                                      c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), stream())
+        check(rc, "spark_attn_prefill")
+        return out
     nsplit = (max_ctx + ATT_TS - 1) // ATT_TS
     part_o = scratch("attn_part_o", R * c.n_q_heads * nsplit * c.head_dim, torch.float32, dev)
     part_ml = scratch("attn_part_ml", R * c.n_q_heads * nsplit * 2, torch.float32, dev)

@@ -18,6 +18,7 @@ from . import cuda as cu
 
 
 EXL3_MOE_FUSED = os.environ.get("SPARK_EXL3_MOE_FUSED", "1") == "1"
+SMALL_ITEM_ROWS_PER_EXPERT = int(os.environ.get("SPARK_MG_SMALL", "24"))   # average rows per expert up to which 32-row items win
 FUSED_MAX_ROWS_PER_EXPERT = 512      # beyond this the one-off reconstruction is cheaper than decoding once per 64 rows
 
 
@@ -32,10 +33,11 @@ def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
     xh = cu.exl3_had_rows(a, wgu.suh, post=False, row_expert=row_expert, expert_stride=H)
     if EXL3_MOE_FUSED and wgu.bits == 4 and a.shape[0] <= FUSED_MAX_ROWS_PER_EXPERT * E:
         # packed trellises straight into the MMA: decode once per <= 64 rows of an expert, output Hadamard fused
-        gu = cu.exl3_mgemm(xh, wgu, tiles, ntile, max_tiles)
+        rpi = 32 if a.shape[0] <= SMALL_ITEM_ROWS_PER_EXPERT * E else 64
+        gu = cu.exl3_mgemm(xh, wgu, tiles, ntile, max_tiles, rows_per_item=rpi)
         act = cu.swiglu(gu, c.swiglu_limit)
         xh2 = cu.exl3_had_rows(act, wd.suh, post=False, row_expert=row_expert, expert_stride=F)
-        return cu.exl3_mgemm(xh2, wd, tiles, ntile, max_tiles, out_f32=True)
+        return cu.exl3_mgemm(xh2, wd, tiles, ntile, max_tiles, out_f32=True, rows_per_item=rpi)
     wt = cu.exl3_reconstruct(wgu, cu.scratch("exl3_recon_gu", E * F2 * H, torch.float16, dev)[: E * F2 * H].view(E, F2, H))
     acc = cu.grouped_gemm(xh, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2, 0, fmt=0)
     gu = cu.exl3_had_rows(acc, wgu.svh, post=True, row_expert=row_expert, expert_stride=F2)
