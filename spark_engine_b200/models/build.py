@@ -137,7 +137,7 @@ def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0, tp=(0, 1)
     if cfg.ngram_layers:
         W["ngram_table"] = it.mat(cfg.ngram_rows, cfg.ngram_dim)
         D = cfg.ngram_dim * cfg.ngram_heads
-        for i in cfg.ngram_layers:
+        for i in (j for j in cfg.ngram_layers if j < cfg.n_layers):
             W["layers"][i]["ngram"] = {"key": it.mat(cfg.hidden, D), "value": it.mat(cfg.hidden, D),
                                        "norm_k": it.f32(cfg.hidden, val=1.0), "norm_q": it.f32(cfg.hidden, val=1.0)}
     return W

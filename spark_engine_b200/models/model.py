@@ -220,6 +220,9 @@ class KdaMixer:
         if self.pending is None:
             return
         pre, lr, plan = self.pending
+        if ops.kda_commit(self, pre, lr, plan, accepted):
+            self.pending = None
+            return
         for s, rows in zip(plan.segs, accepted):
             if not rows:
                 continue
@@ -469,25 +472,30 @@ class MlaMixer:
             self.pool[pb + b0: pb + b1] = (torch.softmax(gb, 1) * kb).sum(1)
 
     def _mask(self, base, L0, n, qi, hw):
+        """Visibility [n, L0+n] of each row: its top-k pools (all of them while there are <= top-k), the tokens after
+        the last complete pool, and the sliding window.  Vectorised on the device of the cache."""
         c = self.c
+        dev = qi.device
         pb = base // c.pool
-        nb = (L0 + n) // c.pool
-        score = None
+        tot = L0 + n
+        nb = tot // c.pool
+        p = L0 + torch.arange(n, device=dev)
+        vis = (p + 1) // c.pool
+        tok = torch.arange(tot, device=dev).unsqueeze(0)
+        mask = (tok >= (vis * c.pool).unsqueeze(1)) & (tok <= p.unsqueeze(1))
+        if c.window:
+            mask |= (tok >= (p + 1 - c.window).clamp_min(0).unsqueeze(1)) & (tok <= p.unsqueeze(1))
         if nb:
-            pk = self.pool[pb: pb + nb]
-            sc = F.relu(torch.einsum("thd,nd->thn", qi, pk) * c.idx_dim ** -0.5)
-            score = torch.einsum("th,thn->tn", hw, sc)
-        mask = torch.zeros(n, L0 + n, dtype=torch.bool)
-        for j in range(n):
-            p = L0 + j
-            vis = (p + 1) // c.pool
-            if vis:
-                blocks = torch.arange(vis) if vis <= c.topk_pools else L.stable_topk(score[j, :vis].cpu(), c.topk_pools)
-                tok = (blocks.unsqueeze(1) * c.pool + torch.arange(c.pool)).flatten()
-                mask[j, tok] = True
-            mask[j, vis * c.pool: p + 1] = True
-            if c.window:
-                mask[j, max(0, p + 1 - c.window): p + 1] = True
+            visible = torch.arange(nb, device=dev).unsqueeze(0) < vis.unsqueeze(1)
+            if nb <= c.topk_pools:
+                chosen = visible
+            else:
+                pk = self.pool[pb: pb + nb]
+                sc = F.relu(torch.einsum("thd,nd->thn", qi, pk) * c.idx_dim ** -0.5)
+                score = torch.einsum("th,thn->tn", hw, sc).masked_fill(~visible, float("-inf"))
+                order = torch.sort(score, dim=1, descending=True, stable=True).indices[:, : c.topk_pools]
+                chosen = torch.zeros(n, nb, dtype=torch.bool, device=dev).scatter_(1, order, True) & visible
+            mask[:, : nb * c.pool] |= chosen.repeat_interleave(c.pool, 1)
         return mask
 
     def commit(self, accepted):

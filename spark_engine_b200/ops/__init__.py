@@ -195,6 +195,12 @@ def kda_mixer(mixer, pre, lr, plan, commit) -> Optional[torch.Tensor]:
     return None
 
 
+def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
+    if use_kernels(pre) and not plan.is_tree:
+        return cuda_ops().kda_commit(mixer, pre, lr, plan, accepted)
+    return False
+
+
 def attn_mixer(mixer, qkv, plan, seqs) -> Optional[torch.Tensor]:
     if use_kernels(qkv):
         return cuda_ops().attn_mixer(mixer, qkv, plan, seqs)

@@ -36,6 +36,7 @@ _SIGS = {
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
@@ -536,8 +537,34 @@ def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
     return True
 
 
-def kda_mixer(mixer, pre, lr, plan, commit):
-    return None      # KDA runs the generic path (projections on the kernels, recurrence in ATen) for now
+def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
+    """KDA layer core on the device: the low-rank gate expansions run on the GEMV/GEMM kernels, conv + norms +
+    per-channel-decay delta rule + gated RMS output in one launch (sequential over the rows of a segment)."""
+    if plan.is_tree:
+        return None
+    c, w = mixer.c, mixer.w
+    dev = pre.device
+    d = _plan_dev(plan, dev)
+    r, n = c.gate_rank, c.n_heads * c.head_dim
+    if not hasattr(mixer, "_gate_w"):
+        mixer._gate_w = (w["f_b"].to(torch.bfloat16).contiguous(), w["g_b"].to(torch.bfloat16).contiguous())
+    pre = _as_bf16(pre)
+    lr = _as_bf16(lr)
+    g1 = dense_linear(lr[:, :r].contiguous(), mixer._gate_w[0], out_f32=True)
+    g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
+    R = pre.shape[0]
+    out = torch.empty(R, n, dtype=torch.bfloat16, device=dev)
+    rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
+                             P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows),
+                             len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream())
+    check(rc, "spark_kda_seq")
+    return out
+
+
+def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
+    n_rows = torch.tensor([len(a) for a in accepted], dtype=torch.int32, device=pre.device)
+    kda_mixer(mixer, pre, lr, plan, True, n_rows)
+    return True
 
 
 ATT_TS = 64

@@ -54,7 +54,7 @@ def rope_neox(x: torch.Tensor, pos: torch.Tensor, rot: int, theta: float, inv: O
     half = rot // 2
     if inv is None:
         inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2 / rot)
-    ang = (pos.double().unsqueeze(1) * inv.unsqueeze(0)).float()
+    ang = (pos.to(x.device).double().unsqueeze(1) * inv.to(x.device).unsqueeze(0)).float()
     shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
     cos, sin = ang.cos().view(shape), ang.sin().view(shape)
     x1, x2, rest = x[..., :half], x[..., half:rot], x[..., rot:]
