@@ -60,10 +60,19 @@ __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int& total)
   return base + inc - v;
 }
 
-// grid R, 1024 threads.  sel [R, sel_ld] token indices, sel_n [R].
+// float bits -> unsigned key with the same order (negative scores sort below positive ones, -0 == +0)
+__device__ __forceinline__ uint32_t order_key(uint32_t b) {
+  if (b == 0x80000000u) b = 0u;
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// grid R, 1024 threads.  sel [R, sel_ld] token indices, sel_n [R].  `window` > 0: the last `window` positions are
+// always visible (sliding window); selected blocks are emitted only up to the start of that range, so no token
+// appears twice.
 __global__ void __launch_bounds__(1024)
-topk_select_kernel(const float* __restrict__ score, int ld, const int* __restrict__ pos, int block, int k,
+topk_select_kernel(const float* __restrict__ score, int ld, const int* __restrict__ pos, int block, int k, int window,
                    int* __restrict__ sel, int sel_ld, int* __restrict__ sel_n) {
+  __shared__ int s_straddle;
   __shared__ int hist[256];
   __shared__ int warp_tot[32];
   __shared__ uint32_t s_prefix;
@@ -86,7 +95,7 @@ topk_select_kernel(const float* __restrict__ score, int ld, const int* __restric
     __syncthreads();
     const int shift = pass * 8;
     for (int i = t; i < vis; i += 1024) {
-      const uint32_t key = s[i];
+      const uint32_t key = order_key(s[i]);
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
     }
     __syncthreads();
@@ -102,28 +111,41 @@ topk_select_kernel(const float* __restrict__ score, int ld, const int* __restric
     __syncthreads();
   }
   const uint32_t thr = prefix;                     // k-th largest key; `need` of the keys equal to thr are taken
-  // ---- emit in ascending block order
+  // ---- emit in ascending block order; blocks that reach into the always-visible range [lo, p] are cut there
+  const int tail0 = vis * block;
+  const int lo = window > 0 ? min(max(0, p + 1 - window), tail0) : tail0;
+  const int sb = lo / block;                       // block that straddles lo (when lo is not a block boundary)
+  if (t == 0) s_straddle = 0;
+  __syncthreads();
   int n_out = 0, eq_taken = 0;
   for (int base = 0; base < vis; base += 1024) {
     const int i = base + t;
-    const uint32_t key = i < vis ? s[i] : 0u;
+    const uint32_t key = i < vis ? order_key(s[i]) : 0u;
     const int is_eq = (i < vis && key == thr) ? 1 : 0;
     int tot_eq;
     const int eq_rank = block_excl_scan(is_eq, warp_tot, tot_eq);
     const int take = (i < vis) && (key > thr || (is_eq && eq_taken + eq_rank < need));
+    const int full = take && (i + 1) * block <= lo;
+    if (take && !full && i == sb && lo > sb * block) s_straddle = 1;
     int tot_take;
-    const int o = block_excl_scan(take ? 1 : 0, warp_tot, tot_take);
-    if (take) {
+    const int o = block_excl_scan(full ? 1 : 0, warp_tot, tot_take);
+    if (full) {
       const int dst = (n_out + o) * block;
       for (int j = 0; j < block; ++j) out[dst + j] = i * block + j;
     }
     n_out += tot_take;
     eq_taken += tot_eq;
   }
-  // ---- tail tokens of the open block
-  const int tail0 = vis * block;
-  if (t <= p - tail0) out[n_out * block + t] = tail0 + t;
-  if (t == 0) sel_n[r] = n_out * block + (p - tail0 + 1);
+  __syncthreads();
+  int cnt = n_out * block;
+  if (s_straddle) {
+    const int m = lo - sb * block;
+    if (t < m) out[cnt + t] = sb * block + t;
+    cnt += m;
+  }
+  // ---- the always-visible range: window and the tokens of the open block
+  for (int i = t; i <= p - lo; i += 1024) out[cnt + i] = lo + i;
+  if (t == 0) sel_n[r] = cnt + (p - lo + 1);
 }
 
 }  // namespace spark
@@ -140,9 +162,9 @@ extern "C" int spark_idx_score(const float* qi, int R, int H, int Dm, const floa
 }
 
 extern "C" int spark_topk_select(const float* score, int ld, const int* pos, int R, int block, int k, int* sel,
-                                 int sel_ld, int* sel_n, cudaStream_t s) {
+                                 int sel_ld, int* sel_n, cudaStream_t s, int window) {
   if (R <= 0) return 0;
-  if (sel_ld < k * block + block) return -5;
-  topk_select_kernel<<<R, 1024, 0, s>>>(score, ld, pos, block, k, sel, sel_ld, sel_n);
+  if (sel_ld < k * block + block + window || window < 0) return -5;
+  topk_select_kernel<<<R, 1024, 0, s>>>(score, ld, pos, block, k, window, sel, sel_ld, sel_n);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

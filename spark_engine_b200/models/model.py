@@ -409,6 +409,9 @@ class MlaMixer:
     def forward(self, h, plan: Plan, seqs, commit: bool):
         c = self.c
         R = h.shape[0]
+        fast = ops.mla_mixer(self, h, plan, seqs)
+        if fast is not None:
+            return ops.linear(fast, self.w["o"])
         a = ops.linear(h, self.w["a"]).float()
         o0 = c.q_lora
         o1 = o0 + c.kv_lora + c.rope_dim

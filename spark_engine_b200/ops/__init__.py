@@ -201,6 +201,12 @@ def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
     return False
 
 
+def mla_mixer(mixer, h, plan, seqs) -> Optional[torch.Tensor]:
+    if use_kernels(h):
+        return cuda_ops().mla_mixer(mixer, h, plan, seqs)
+    return None
+
+
 def attn_mixer(mixer, qkv, plan, seqs) -> Optional[torch.Tensor]:
     if use_kernels(qkv):
         return cuda_ops().attn_mixer(mixer, qkv, plan, seqs)

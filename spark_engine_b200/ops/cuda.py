@@ -36,6 +36,10 @@ _SIGS = {
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_mla_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                       vp, vp],
+    "spark_mla_qrope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp],
+    "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp],
     "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
@@ -184,13 +188,19 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out_f32: bool = False, fmt: int 
 
 
 def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0, out_f32=False,
-              expert_stride=0, n=None, k=None):
+              expert_stride=0, n=None, k=None, out=None, ldx=None):
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     n = n if n is not None else w.shape[-2]
     k = k if k is not None else w.shape[-1]
-    y = torch.empty(items * rows_per_item, n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
-    rc = lib().spark_gemv_bf16(P(x), x.stride(0), P(w), expert_stride, k, P(y), n, items, rows_per_item, n, k,
-                               P(pair_expert), P(pair_row), act, float(limit), int(out_f32), stream())
+    if out is None:
+        y = torch.empty(items * rows_per_item, n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+        ldy = n
+    else:
+        y, ldy = out, out.stride(0)
+        out_f32 = out.dtype == torch.float32
+    rc = lib().spark_gemv_bf16(P(x), ldx if ldx is not None else x.stride(0), P(w), expert_stride, w.stride(-2), P(y), ldy,
+                               items, rows_per_item, n, k, P(pair_expert), P(pair_row), act, float(limit), int(out_f32),
+                               stream())
     check(rc, "spark_gemv_bf16")
     return y
 
@@ -565,6 +575,86 @@ def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
     n_rows = torch.tensor([len(a) for a in accepted], dtype=torch.int32, device=pre.device)
     kda_mixer(mixer, pre, lr, plan, True, n_rows)
     return True
+
+
+MLA_TS = 64
+MLA_KERNELS = os.environ.get("SPARK_MLA_KERNELS", "1") == "1"
+_KERNELS_PER_CALL["spark_mla_attn"] = 2
+
+
+def mla_mixer(mixer, h, plan, seqs):
+    """Latent attention on the device: returns the per-head outputs [R, H*D] (before the output projection), or None
+    (tree plans run the generic path)."""
+    if plan.is_tree or not MLA_KERNELS:
+        return None
+    c, w, cfg = mixer.c, mixer.w, mixer.cfg
+    dev = h.device
+    d = _plan_dev(plan, dev)
+    R = h.shape[0]
+    if "row_kv" not in d:
+        d["row_kv"] = torch.tensor([seqs[s.slot].kv_base for s in plan.segs for _ in range(s.n)], dtype=torch.int64).to(dev)
+        d["max_ctx"] = max(s.pos0 + s.n for s in plan.segs)
+        for s in plan.segs:
+            assert s.pos0 + s.n <= seqs[s.slot].kv_cap, "sequence capacity exceeded"
+    H, D, L, Rr = c.n_heads, c.head_dim, c.kv_lora, c.rope_dim
+    KW = L + Rr
+    if not hasattr(mixer, "_dev"):
+        half = max(Rr // 2, 1)
+        inv = (c.rope_theta ** (-torch.arange(half, dtype=torch.float64) * 2 / max(Rr, 1))).to(dev)
+        mixer._dev = {"inv": inv, "w_ukT": mixer.w_uk.transpose(1, 2).contiguous().to(torch.bfloat16),
+                      "w_uv": mixer.w_uv.contiguous().to(torch.bfloat16),
+                      "ape": w["ape"].float().contiguous()}
+    md = mixer._dev
+    a = _as_bf16(linear_any(h, w["a"])).contiguous()
+    cq = torch.empty(R, c.q_lora, dtype=torch.bfloat16, device=dev)
+    hw = torch.empty(R, c.idx_heads, dtype=torch.float32, device=dev)
+    rc = lib().spark_mla_prep(P(a), a.stride(0), R, c.q_lora, L, Rr, c.idx_dim, c.idx_heads, c.pool, float(cfg.norm_eps),
+                              P(w["q_a_norm"]), P(w["kv_a_norm"]), P(w["k_ln_w"]), P(w["k_ln_b"]), P(md["ape"]), P(md["inv"]),
+                              P(d["pos32"]), P(d["row_kv"]), P(d["row_j"]), P(cq), P(mixer.lat), P(mixer.ik), P(mixer.ig),
+                              P(mixer.pool), P(hw), stream())
+    check(rc, "spark_mla_prep")
+    qb = _as_bf16(linear_any(cq, w["q_b"]))
+    nq = H * (D + Rr)
+    q_full = torch.empty(R, H, KW, dtype=torch.bfloat16, device=dev)
+    decode = R * H <= 4096 and R <= 16
+    if decode:
+        key = ("mla_pairs", R, H)
+        if key not in md:
+            md[key] = (torch.arange(H, dtype=torch.int32, device=dev).repeat(R).contiguous(),
+                       torch.arange(R * H, dtype=torch.int32, device=dev))
+        pe, pr = md[key]
+        qn = qb[:, :nq].contiguous()
+        # absorb W_uk: one (row, head) pair per item, the head's [L, D] matrix as the "expert"
+        gemv_bf16(qn, md["w_ukT"], items=R * H, rows_per_item=1, pair_expert=pe, pair_row=pr, expert_stride=L * D, n=L, k=D,
+                  out=q_full.view(R * H, KW), ldx=D + Rr)
+    else:
+        q_full[..., :L] = torch.einsum("thd,hld->thl", qb[:, :nq].view(R, H, D + Rr)[..., :D], md["w_ukT"])
+    if Rr:
+        rc = lib().spark_mla_qrope(P(qb), qb.stride(0), R, H, D, Rr, L, P(md["inv"]), P(d["pos32"]), P(q_full), stream())
+        check(rc, "spark_mla_qrope")
+    sel = sel_n = None
+    sel_ld = 0
+    max_ctx = d["max_ctx"]
+    if max_ctx // c.pool > c.topk_pools:
+        from . import sparse as sp
+        qi = qb[:, nq:].float().view(R, c.idx_heads, c.idx_dim).contiguous()
+        sel, sel_n = sp.select_tokens(qi, mixer.pool, d["row_kv"], d["pos32"], c.pool, c.topk_pools, max_ctx, head_w=hw,
+                                      scale=c.idx_dim ** -0.5, window=c.window)
+        sel_ld = sel.shape[1]
+        max_ctx = sel_ld
+    nsplit = (max_ctx + MLA_TS - 1) // MLA_TS
+    part_o = scratch("mla_part_o", R * H * nsplit * L, torch.float32, dev)
+    part_ml = scratch("mla_part_ml", R * H * nsplit * 2, torch.float32, dev)
+    out_lat = torch.empty(R, H, L, dtype=torch.bfloat16, device=dev)
+    rc = lib().spark_mla_attn(P(q_full), P(mixer.lat), P(d["pos32"]), P(d["row_kv"]), P(sel), P(sel_n), sel_ld, P(part_o),
+                              P(part_ml), nsplit, P(w.get("sink")) if c.sink else None, R, H, L, Rr,
+                              1.0 / math.sqrt(D + Rr), P(out_lat), stream())
+    check(rc, "spark_mla_attn")
+    if decode:
+        pe, pr = md[("mla_pairs", R, H)]
+        return gemv_bf16(out_lat.view(R * H, L), md["w_uv"], items=R * H, rows_per_item=1, pair_expert=pe, pair_row=pr,
+                         expert_stride=D * L, n=D, k=L).view(R, H * D)
+    return torch.einsum("thl,hdl->thd", out_lat, md["w_uv"]).reshape(R, H * D)
 
 
 ATT_TS = 64

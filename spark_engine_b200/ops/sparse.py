@@ -18,15 +18,16 @@ def _dll():
     if not _bound:
         dll.spark_idx_score.argtypes = [vp, i32, i32, i32, vp, vp, vp, i32, vp, f32, vp, i32, i32, vp]
         dll.spark_idx_score.restype = i32
-        dll.spark_topk_select.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, vp, vp]
+        dll.spark_topk_select.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, vp, vp, i32]
         dll.spark_topk_select.restype = i32
         _bound = True
     return dll
 
 
-def select_tokens(qi, pool, row_kv, pos32, block, topk, max_ctx, head_w=None, scale=None):
+def select_tokens(qi, pool, row_kv, pos32, block, topk, max_ctx, head_w=None, scale=None, window=0):
     """qi [R,H,Dm] fp32 indexer queries; pool [*, Dm] fp32 pooled keys (block b of a sequence at row_kv/block + b).
-    Returns (sel [R, topk*block + block] int32 token indices, sel_n [R])."""
+    `window` > 0 keeps the last `window` positions
+    visible as well.  Returns (sel [R, topk*block + block + window] int32 token indices, sel_n [R])."""
     R, H, Dm = qi.shape
     dev = qi.device
     nb_max = max(1, max_ctx // block)
@@ -36,11 +37,11 @@ def select_tokens(qi, pool, row_kv, pos32, block, topk, max_ctx, head_w=None, sc
                                 float(scale if scale is not None else 1.0 / math.sqrt(Dm)), cu.P(score), nb_max, nb_max,
                                 cu.stream())
     cu.check(rc, "spark_idx_score")
-    sel_ld = topk * block + block
+    sel_ld = topk * block + block + window
     sel = torch.empty(R, sel_ld, dtype=torch.int32, device=dev)
     sel_n = torch.empty(R, dtype=torch.int32, device=dev)
     rc = _dll().spark_topk_select(cu.P(score), nb_max, cu.P(pos32), R, block, topk, cu.P(sel), sel_ld, cu.P(sel_n),
-                                  cu.stream())
+                                  cu.stream(), window)
     cu.check(rc, "spark_topk_select")
     return sel, sel_n
 

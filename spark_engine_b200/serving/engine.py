@@ -126,9 +126,9 @@ class LLMEngine:
                            kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
         self.graphs: Dict[tuple, _DecodeGraph] = {}
-        # decode rounds are captured only when every layer runs on capturable kernels: the latent-attention layers and
-        # the host-streamed n-gram tables still go through ATen ops with host-side index work
-        capturable = "mla" not in cfg.layer_types and not cfg.ngram_layers
+        # decode rounds are captured only when every layer runs on capturable kernels: the host-streamed n-gram tables
+        # go through host-side index work
+        capturable = not cfg.ngram_layers
         self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda" and capturable
         self.stats = GenStats()
         self._rounds_since_check = 0
