@@ -24,7 +24,10 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-BASELINE_DECODE_4STREAMS = 139.2     # Qwen3.8-Flash-Next, prose, greedy, 4 streams, 1x DGX Spark GB10 (published)
+# published aggregate decode tok/s at 4 streams (prose, greedy) of the reference, per model family:
+# Qwen3.8-Flash-Next on 1x DGX Spark GB10; GLM-5.3-Flash on 2x GB10 (TP2); DeepSeek-V4.1-Flash on 3x GB10 (TP3)
+BASELINE_DECODE_4STREAMS = {"qwen3next-style": 139.2, "glm-style": 82.9, "ds4-style": 124.7}
+DEFAULT_FORMAT = {"qwen3next-style": "exl3", "glm-style": "exl3", "ds4-style": "mx"}
 
 
 class ClockSampler:
@@ -214,12 +217,13 @@ def main():
     replicas = 1 if use_tp else world
     value = replicas * S * 1e3 / dev_ms
     e2e = replicas * S * 1e3 / e2e_ms
-    full = (args.layers == 0 and args.model == "qwen3next-style" and cfg.weight_format == "exl3")
+    full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS
+            and cfg.weight_format == DEFAULT_FORMAT[args.model])
     out = {
         "metric": "aggregate decode tok/s at 4 streams" if S == 4 else f"aggregate decode tok/s at {S} streams",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "strong" if use_tp else "weak",
-        "vs_baseline": round(value / BASELINE_DECODE_4STREAMS, 3) if full and S == 4 else None,
+        "vs_baseline": round(value / BASELINE_DECODE_4STREAMS[args.model], 3) if full and S == 4 else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.moe.n_experts,
                    "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
