@@ -608,7 +608,16 @@ class Model:
         fast = ops.model_forward(self, plan, commit, want_hidden)
         if fast is not None:
             return fast
-        X = ops.embed(W["embed"], plan.ids, self.dtype)
+        if plan.mm_rows:
+            # salted placeholder ids are outside the vocabulary: look up row 0 for them, then write the encoded media
+            # rows over those positions (engine-rs/src/weights.rs:536-569)
+            from ..multimodal.canvas import MM_BASE, inject_rows
+            salted = plan.ids >= MM_BASE
+            X = ops.embed(W["embed"], torch.where(salted, torch.zeros_like(plan.ids), plan.ids), self.dtype)
+            X[salted.to(X.device)] = 0
+            X = inject_rows(X, plan.ids, plan.mm_rows)
+        else:
+            X = ops.embed(W["embed"], plan.ids, self.dtype)
         if cfg.hc_kind != "none":
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
         self._ids_for_ngram = plan

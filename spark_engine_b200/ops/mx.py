@@ -14,6 +14,7 @@ import ctypes
 import torch
 
 from ..quant.formats import Fp8BlockWeight, Mxfp4Weight, QuantWeight
+from ..quant.recode import Q4Weight, Q8Weight
 from . import cuda as cu
 
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
@@ -22,6 +23,7 @@ _SIGS = {
                       _vp],
     "spark_mx_dequant": [_vp, _vp, _i32, _vp, _i64, _i32, _i32, _vp],
     "spark_act_quant": [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
 }
 _bound = False
 
@@ -86,12 +88,37 @@ def act_quant(x, block=128, pow2=False, act=0, limit=0.0):
     return q.view(torch.float8_e4m3fn), sc
 
 
+def coded_gemv(x, w, out_f32=False):
+    """<= 16 rows through the int8 / int4 re-coded copy of a dense weight."""
+    x = cu._as_bf16(x).contiguous()
+    q4 = isinstance(w, Q4Weight)
+    assert (w.group == 64) if q4 else (w.group == 128)
+    y = torch.empty(x.shape[0], w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    rc = _lib().spark_coded_gemv(cu.P(x), x.stride(0), cu.P(w.q), cu.P(w.sm if q4 else w.scales), 3 if q4 else 2, cu.P(y),
+                                 w.n, x.shape[0], w.n, w.k, int(out_f32), cu.stream())
+    cu.check(rc, "spark_coded_gemv")
+    return y
+
+
+def _resident_bf16(w: QuantWeight, device) -> torch.Tensor:
+    """bf16 expansion of a re-coded weight, made once (prefill-size batches; codings without a device kernel yet)."""
+    t = getattr(w, "_bf16", None)
+    if t is None or t.device != device:
+        t = w.dequant().to(torch.bfloat16).to(device)
+        w._bf16 = t
+    return t
+
+
 def quant_linear(x, w: QuantWeight):
     x = cu._as_bf16(x).contiguous()
-    if x.shape[0] <= 16:
-        return gemv(x, w)
-    wt = dequant_bf16(w, cu.scratch("mx_deq", w.n * w.k, torch.bfloat16, x.device))
-    return cu.gemm_bf16(x, wt)
+    if isinstance(w, (Fp8BlockWeight, Mxfp4Weight)):
+        if x.shape[0] <= 16:
+            return gemv(x, w)
+        wt = dequant_bf16(w, cu.scratch("mx_deq", w.n * w.k, torch.bfloat16, x.device))
+        return cu.gemm_bf16(x, wt)
+    if isinstance(w, (Q8Weight, Q4Weight)) and x.shape[0] <= 16 and w.n % 16 == 0:
+        return coded_gemv(x, w)
+    return cu.dense_linear(x, _resident_bf16(w, x.device))
 
 
 def expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
