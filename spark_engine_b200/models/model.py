@@ -622,8 +622,13 @@ class Model:
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
         self._ids_for_ngram = plan
         pend = None
-        for lw, mix, mlp in self.layers:
+        taps = getattr(self, "tap_layers", None)
+        if taps:
+            self.taps = {}
+        for li, (lw, mix, mlp) in enumerate(self.layers):
             X, pend = self._block(lw, mix, mlp, X, pend, plan, commit)
+            if taps and li in taps:          # residual stream after layer li (feature taps of a drafter)
+                self.taps[li] = X if pend is None else ops.residual_add(X.clone(), pend)
         if cfg.hc_kind == "gated":
             _, X = ops.hc_gated_mix(X, W["hc_final"], cfg.norm_eps)
             hn = X

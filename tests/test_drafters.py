@@ -1,0 +1,62 @@
+"""Feature-conditioned (DFlash2-style) and staged (DSpark-style) drafters: candidate paths, trees, and exactness of
+speculative decoding with them (drafts only change speed, never the tokens)."""
+import torch
+
+from spark_engine_b200.config import tiny_hybrid
+from spark_engine_b200.models.model import Model
+from spark_engine_b200.models.weights import init_weights
+from spark_engine_b200.spec import drafters as D
+from spark_engine_b200.spec.decoder import SpecDecoder
+from spark_engine_b200.spec.tree import check_topological
+
+
+def test_greedy_path_and_tree():
+    g = torch.Generator().manual_seed(0)
+    unary = torch.randn(4, 6, generator=g)
+    edges = torch.randn(3, 6, 6, generator=g)
+    path = D.greedy_path(unary, edges)
+    assert path[0] == int(unary[0].argmax())
+    for j in range(3):
+        assert path[j + 1] == int((unary[j + 1] + edges[j, path[j]]).argmax())
+    ids = torch.arange(24).view(4, 6)
+    c = D.Candidates(ids, unary, edges, path, [0.5] * 4)
+    nodes = D.to_tree(c, [3, 2, 2, 1])
+    check_topological(nodes)
+    assert len(nodes) == 8
+    spine = [n.token for n in nodes if n is nodes[0] or True][:1]
+    assert nodes[0].token == int(ids[0, path[0]]) and nodes[0].parent == -1
+    # siblings share the parent of the spine node of their depth; the spine continues from the previous spine node
+    assert nodes[1].parent == -1 and nodes[2].parent == -1 and nodes[3].parent == 0 and nodes[3].token == int(ids[1, path[1]])
+
+
+def _greedy(cfg, W, prompt, n):
+    m = Model(cfg, W, n_slots=1, kv_tokens=256)
+    return SpecDecoder(m, drafter=None, depth=0).generate([prompt], n)[0]
+
+
+def test_speculation_with_feature_and_stage_drafters_is_exact():
+    cfg = tiny_hybrid()
+    cfg.mtp_layers = 0
+    W = init_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(3)).tolist()
+    ref = _greedy(cfg, W, prompt, 20)
+    m = Model(cfg, W, n_slots=1, kv_tokens=256)
+    fd = D.FeatureDrafter(m, D.FeatureDrafterConfig(target_hidden=cfg.hidden, taps=(0, cfg.n_layers - 1), vocab=cfg.vocab,
+                                                    sub_vocab=min(512, cfg.vocab), depth=3, cand_k=8))
+    out = SpecDecoder(m, drafter=fd, depth=3).generate([prompt], 20)[0]
+    assert out == ref
+    assert fd.last is not None and fd.last.ids.shape == (3, 8)
+    m2 = Model(cfg, W, n_slots=1, kv_tokens=256)
+    sd = D.StageDrafter(D.StageDrafterConfig(hidden=cfg.hidden, vocab=cfg.vocab, threshold=0.0))
+    out2 = SpecDecoder(m2, drafter=sd, depth=4).generate([prompt], 20)[0]
+    assert out2 == ref
+
+
+def test_stage_drafter_lengths_follow_confidence():
+    sd = D.StageDrafter(D.StageDrafterConfig(threshold=0.5))
+    assert sd.draft_length([0.9, 0.9, 0.5, 0.9], 5) == 2          # 0.81 ok, 0.405 < 0.5
+    assert sd.draft_length([0.4], 5) == 0
+    assert sd.draft_length([0.99] * 5, 3) == 3
+    toks, confs = sd.propose_block(torch.randn(256, generator=torch.Generator().manual_seed(1)), 7)
+    assert len(toks) == 5 and all(0.0 <= c <= 1.0 for c in confs)
+    assert (toks, confs) == sd.propose_block(torch.randn(256, generator=torch.Generator().manual_seed(1)), 7)
