@@ -67,7 +67,7 @@ def build_runtime(force=False) -> str:
         return ""
     if force or _newer(srcs + hdrs, out):
         _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-pthread", "-I", pybind11.get_include(),
-              "-I", sysconfig.get_paths()["include"]] + srcs + ["-o", out, "-lrt"])
+              "-I", sysconfig.get_paths()["include"]] + srcs + ["-o", out, "-lrt", "-ldl"])
     return out
 
 

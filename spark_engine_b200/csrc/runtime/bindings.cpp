@@ -3,6 +3,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "devmem.h"
 #include "kv_pool.h"
 #include "memguard.h"
 #include "oplog.h"
@@ -104,5 +105,29 @@ PYBIND11_MODULE(_runtime, m) {
   m.def("drop_file_cache", &drop_file_cache);
   py::class_<MemWatch>(m, "MemWatch").def(py::init<int64_t, int, std::function<void(int64_t)>, const std::string&>(), py::arg("threshold"), py::arg("period_ms"), py::arg("on_low"), py::arg("meminfo") = "")
       .def("fired", &MemWatch::fired);
+  // device-memory plumbing (driver API resolved at run time; `fake=True` runs against host memory)
+  auto pick = [](bool fake) { return fake ? fake_driver_api() : cuda_driver_api(); };
+  m.def("cuda_driver_available", []() { return cuda_driver_api() != nullptr; });
+  m.def("fake_driver_mapped_bytes", &fake_driver_mapped_bytes);
+  py::class_<VmmRegion>(m, "VmmRegion")
+      .def(py::init([pick](int device, size_t max_bytes, bool fake) { return new VmmRegion(pick(fake), device, max_bytes); }),
+           py::arg("device"), py::arg("max_bytes"), py::arg("fake") = false)
+      .def_property_readonly("ptr", &VmmRegion::ptr).def_property_readonly("size", &VmmRegion::size)
+      .def_property_readonly("capacity", &VmmRegion::capacity).def_property_readonly("granularity", &VmmRegion::granularity)
+      .def("resize", &VmmRegion::resize);
+  py::class_<PinnedBuffer>(m, "PinnedBuffer", py::buffer_protocol())
+      .def(py::init([pick](size_t bytes, bool huge, bool fake) { return new PinnedBuffer(pick(fake), bytes, huge); }),
+           py::arg("bytes"), py::arg("huge_pages") = false, py::arg("fake") = false)
+      .def_property_readonly("registered", &PinnedBuffer::registered).def_property_readonly("size", &PinnedBuffer::size)
+      .def_property_readonly("ptr", [](const PinnedBuffer& b) { return reinterpret_cast<uint64_t>(b.data()); })
+      .def_buffer([](PinnedBuffer& b) { return py::buffer_info(b.data(), 1, py::format_descriptor<uint8_t>::format(), 1, {b.size()}, {1}); });
+  py::class_<LoadStats>(m, "LoadStats").def_readonly("bytes", &LoadStats::bytes).def_readonly("reads", &LoadStats::reads)
+      .def_readonly("copies", &LoadStats::copies).def_readonly("read_s", &LoadStats::read_s).def_readonly("total_s", &LoadStats::total_s);
+  m.def("fast_load", [pick](const std::string& path, int64_t offset, int64_t size, uint64_t dst, uint64_t stream, size_t chunk,
+                            int n_buffers, int n_threads, bool fake) {
+          py::gil_scoped_release rel;
+          return fast_load(pick(fake), path, offset, size, dst, stream, chunk, n_buffers, n_threads);
+        }, py::arg("path"), py::arg("offset"), py::arg("size"), py::arg("dst"), py::arg("stream") = 0,
+        py::arg("chunk") = 64 << 20, py::arg("n_buffers") = 3, py::arg("n_threads") = 2, py::arg("fake") = false);
   m.def("sha256_hex", [](py::bytes b) { std::string s = b; Sha256 h; h.update(s.data(), s.size()); return h.hex(); });
 }

@@ -1,0 +1,71 @@
+"""Growable device buffers (virtual memory management), pinned staging and the threaded loader.  The logic runs against
+an in-process fake of the driver API on CPU; the GPU tests use the real driver."""
+import os
+
+import pytest
+import torch
+
+from spark_engine_b200 import runtime as rt
+from spark_engine_b200.utils.devmem import GrowableDeviceBuffer, load_file_range_to
+
+
+def test_vmm_region_grows_and_shrinks_in_place_fake():
+    L = rt.rt()
+    before = L.fake_driver_mapped_bytes()
+    b = GrowableDeviceBuffer(0, 10 << 20, fake=True)
+    g = b.region.granularity
+    assert b.size == 0 and b.region.capacity >= 10 << 20
+    assert b.resize(3 * g + 1) == 4 * g
+    ptr = b.region.ptr
+    t = b.view(0, (4 * g // 4,), torch.int32)
+    t.copy_(torch.arange(t.numel(), dtype=torch.int32))
+    assert b.resize(6 * g) == 6 * g and b.region.ptr == ptr            # same address after growing
+    assert torch.equal(b.view(0, (4 * g // 4,), torch.int32), torch.arange(4 * g // 4, dtype=torch.int32))
+    assert b.resize(2 * g) == 2 * g
+    assert L.fake_driver_mapped_bytes() - before == 2 * g
+    with pytest.raises(ValueError):
+        b.view(0, (3 * g,), torch.uint8)
+    with pytest.raises(RuntimeError):
+        b.resize(11 << 20)
+    del b, t
+    assert L.fake_driver_mapped_bytes() == before
+
+
+def test_fast_load_through_staging_ring_fake(tmp_path):
+    data = torch.randint(0, 256, (5 * 1000 * 1000 + 123,), dtype=torch.uint8)
+    p = tmp_path / "blob.bin"
+    p.write_bytes(b"HEAD" + data.numpy().tobytes())
+    dst = torch.zeros_like(data)
+    st = load_file_range_to(dst, str(p), 4, chunk=1 << 20, n_buffers=3, n_threads=3)
+    assert torch.equal(dst, data) and st.bytes == data.numel() and st.copies == 5
+    with pytest.raises(RuntimeError):
+        load_file_range_to(torch.zeros(10, dtype=torch.uint8), str(tmp_path / "missing"), 0)
+    pb = rt.rt().PinnedBuffer(100000, False, True)
+    assert pb.size >= 100000 and memoryview(pb).nbytes == pb.size
+
+
+@pytest.mark.gpu
+def test_vmm_region_and_loader_on_device(tmp_path):
+    assert rt.rt().cuda_driver_available()
+    torch.zeros(1, device="cuda")                                        # primary context
+    b = GrowableDeviceBuffer(0, 64 << 20)
+    g = b.region.granularity
+    b.resize(g)
+    t = b.view(0, (g // 4,), torch.float32)
+    t.fill_(3.0)
+    ptr = b.region.ptr
+    b.resize(4 * g)
+    assert b.region.ptr == ptr and float(b.view(0, (g // 4,), torch.float32).sum()) == 3.0 * (g // 4)
+    u = b.view(3 * g, (1024,), torch.int64)
+    u.copy_(torch.arange(1024, device="cuda"))
+    assert int(u.sum()) == 1023 * 1024 // 2
+    b.resize(g)
+    torch.cuda.synchronize()
+    data = torch.randint(0, 256, (9 * 1000 * 1000 + 7,), dtype=torch.uint8)
+    p = tmp_path / "w.bin"
+    p.write_bytes(data.numpy().tobytes())
+    dst = torch.empty_like(data, device="cuda")
+    st = load_file_range_to(dst, str(p), 0, chunk=2 << 20)
+    assert torch.equal(dst.cpu(), data) and st.bytes == data.numel()
+    pb = rt.rt().PinnedBuffer(1 << 20, True, False)
+    assert pb.registered
