@@ -1,0 +1,41 @@
+"""Host n-gram table: threaded gathers through the staging ring equal plain indexing; file-backed tables."""
+import pytest
+import torch
+
+from spark_engine_b200.cache.engram import EngramTable
+
+
+def test_prefetch_equals_index_and_ring_reuse(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(5000, 48, generator=g).bfloat16()
+    et = EngramTable(table, ring_slots=3, max_rows=700, threads=3)
+    reqs = [torch.randint(0, 5000, (n,), generator=g) for n in (1, 640, 37, 700, 255)]
+    futs = []
+    for ids in reqs:                       # more requests than ring slots: consume in order, like layer after layer
+        futs.append((ids, et.prefetch(ids.view(-1, 1))))
+        if len(futs) == 2:
+            ids0, f0 = futs.pop(0)
+            assert torch.equal(EngramTable.take(f0), table[ids0])
+    for ids0, f0 in futs:
+        assert torch.equal(EngramTable.take(f0), table[ids0])
+    with pytest.raises(ValueError):
+        et.prefetch(torch.zeros(701, dtype=torch.long))
+    assert et.stats["requests"] == 5
+    et.close()
+    p = tmp_path / "t.bin"
+    p.write_bytes(table.view(torch.int16).numpy().tobytes())
+    ef = EngramTable.from_file(str(p), 5000, 48, max_rows=64)
+    ids = torch.tensor([0, 4999, 17])
+    assert torch.equal(EngramTable.take(ef.prefetch(ids)), table[ids])
+    ef.close()
+
+
+@pytest.mark.gpu
+def test_prefetch_to_device():
+    table = torch.randn(3000, 64).bfloat16()
+    et = EngramTable(table, device="cuda", ring_slots=2, max_rows=512)
+    for seed in range(4):
+        ids = torch.randint(0, 3000, (300,), generator=torch.Generator().manual_seed(seed))
+        rows = EngramTable.take(et.prefetch(ids))
+        assert rows.is_cuda and torch.equal(rows.cpu(), table[ids])
+    et.close()
