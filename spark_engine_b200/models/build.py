@@ -95,10 +95,11 @@ def _mix(cfg: ModelConfig, it: _DevInit, kind: str) -> dict:
 
 def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool, tp=(0, 1)) -> dict:
     c, H = cfg.moe, cfg.hidden
-    if dense:
-        return {"dense_gu": it.big(2 * c.dense_ffn, H), "dense_down": it.big(H, c.dense_ffn)}
-    Fs = c.shared_ffn or c.ffn * c.n_shared
     rank, world = tp
+    if dense:
+        Fd = c.dense_ffn // world            # dense MLPs are split by the intermediate dimension
+        return {"dense_gu": it.big(2 * Fd, H), "dense_down": it.big(H, Fd)}
+    Fs = c.shared_ffn or c.ffn * c.n_shared
     assert c.n_experts % world == 0
     e_loc = c.n_experts // world
     w = {"gate": it.mat_common(c.n_experts + (1 if c.shared_gate else 0), H),

@@ -44,7 +44,8 @@ def _rows(t, lo, hi):
 
 def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
     """This rank's shard of a dense (unquantised) weight dict laid out as in models/weights.py."""
-    out = {"embed": W["embed"], "final_norm": W["final_norm"], "layers": []}
+    out = {k: v for k, v in W.items() if k not in ("lm_head", "layers", "mtp")}      # replicated tensors and tables
+    out["layers"] = []
     V = cfg.vocab
     assert V % world == 0
     out["lm_head"] = _rows(W["lm_head"], rank * V // world, (rank + 1) * V // world)
@@ -83,8 +84,34 @@ def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dic
             nl["mix"] = dict(w)
             nl["mix"]["qkv"] = w["qkv"][sel].contiguous()
             nl["mix"]["o"] = w["o"][:, rank * hq * D: (rank + 1) * hq * D].contiguous()
+        elif kind == "kda":
+            c = cfg.kda
+            D, hh = c.head_dim, c.n_heads // world
+            n, r = c.n_heads * D, c.gate_rank
+            ch = torch.arange(rank * hh * D, (rank + 1) * hh * D)           # this rank's channels inside q, k or v
+            sel = torch.cat((ch, n + ch, 2 * n + ch))
+            hsel = torch.arange(rank * hh, (rank + 1) * hh)
+            nl["mix"] = {"in": w["in"][sel].contiguous(), "conv": w["conv"][sel].contiguous(),
+                         "lr_a": torch.cat((w["lr_a"][: 2 * r], w["lr_a"][2 * r + hsel])).contiguous(),
+                         "f_b": w["f_b"][ch].contiguous(), "g_b": w["g_b"][ch].contiguous(),
+                         "A_log": w["A_log"][hsel].contiguous(), "dt_bias": w["dt_bias"][ch].contiguous(),
+                         "o_norm": w["o_norm"], "o": w["o"][:, ch].contiguous()}
+        elif kind == "mla":
+            c = cfg.mla
+            hh = c.n_heads // world
+            qw = c.head_dim + c.rope_dim
+            nq = c.n_heads * qw
+            nl["mix"] = dict(w)                                              # low-rank projections, norms, indexer: replicated
+            nl["mix"]["q_b"] = torch.cat((w["q_b"][rank * hh * qw: (rank + 1) * hh * qw], w["q_b"][nq:])).contiguous()
+            nl["mix"]["kv_b"] = w["kv_b"][rank * hh * 2 * c.head_dim: (rank + 1) * hh * 2 * c.head_dim].contiguous()
+            nl["mix"]["o"] = w["o"][:, rank * hh * c.head_dim: (rank + 1) * hh * c.head_dim].contiguous()
+            if "sink" in w:
+                nl["mix"]["sink"] = w["sink"][rank * hh: (rank + 1) * hh].contiguous()
         else:
             raise NotImplementedError(f"tensor-parallel shard rule for layer type {kind}")
+        for extra in lw:                                                     # n-gram gates etc.: replicated
+            if extra not in ("type", "in_norm", "post_norm", "mix", "mlp"):
+                nl[extra] = lw[extra]
         m = lw["mlp"]
         if "dense_gu" in m:
             F = cfg.moe.dense_ffn

@@ -16,7 +16,16 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q):
+def _config(name):
+    from spark_engine_b200.config import get_model_config, scaled_down, tiny_hybrid
+    if name == "tiny":
+        return tiny_hybrid()
+    cfg = scaled_down(get_model_config(name))
+    cfg.mtp_layers = 0
+    return cfg
+
+
+def _worker(rank, world, port, q, name="tiny"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from spark_engine_b200.config import tiny_hybrid
@@ -25,7 +34,7 @@ def _worker(rank, world, port, q):
     from spark_engine_b200.models.weights import init_weights
     from spark_engine_b200.parallel.tp import CpuTP, shard_dense_weights
     torch.manual_seed(0)
-    cfg = tiny_hybrid()
+    cfg = _config(name)
     W = init_weights(cfg, seed=0)
     tp = CpuTP()
     m = Model(cfg, shard_dense_weights(W, cfg, rank, world), n_slots=1, kv_tokens=128, tp=tp)
@@ -44,22 +53,25 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_tp2_logits_match_unsharded():
-    from spark_engine_b200.config import tiny_hybrid
+import pytest
+
+
+@pytest.mark.parametrize("name", ["tiny", "glm-style", "ds4-style"])
+def test_tp2_logits_match_unsharded(name):
     from spark_engine_b200.models.model import Model
     from spark_engine_b200.models.plan import make_plan
     from spark_engine_b200.models.weights import init_weights
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, name)) for r in range(2)]
     for p in procs:
         p.start()
     logits, toks, logits2 = q.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    cfg = tiny_hybrid()
+    cfg = _config(name)
     W = init_weights(cfg, seed=0)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()

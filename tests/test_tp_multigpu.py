@@ -65,6 +65,23 @@ def _worker(rank, world, port):
     assert all(torch.equal(a, allt[0]) for a in allt), "ranks diverged"
     eng2 = LLMEngine(cfg2, W2, EngineConfig(cuda_graphs=False, prefill_chunk=64), device=dev, max_seqs=2, kv_tokens_per_seq=512, tp=tp2)
     assert eng2.generate(prompts, 10) == outs, "graph replay differs from eager under TP"
+    # ---- the other families (KDA + latent attention, compressed sparse latent attention): sharded vs single GPU
+    from spark_engine_b200.config import get_model_config, scaled_down
+    for k, name in enumerate(("glm-style", "ds4-style")):
+        cfg3 = scaled_down(get_model_config(name))
+        cfg3.mtp_layers = 0
+        W3 = init_weights(cfg3, seed=1)
+        tp3 = DeviceTP(arena, cfg3.hidden, rows_cap=64, name=f"tp3{k}")
+        ref3 = Model(cfg3, to_device(W3, dev), device=dev, dtype=torch.bfloat16, n_slots=1, kv_tokens=128)
+        m3 = Model(cfg3, to_device(shard_dense_weights(W3, cfg3, rank, world), dev), device=dev, dtype=torch.bfloat16,
+                   n_slots=1, kv_tokens=128, tp=tp3)
+        for plan_items in ([(0, ids[:36], 0)], [(0, ids[36:37], 36)]):
+            lr3 = ref3.forward(make_plan(plan_items, device=dev))
+            lt3 = m3.forward(make_plan(plan_items, device=dev))
+            parts3 = [torch.empty_like(lt3) for _ in range(world)]
+            dist.all_gather(parts3, lt3.contiguous())
+            err3 = ((torch.cat(parts3, 1) - lr3).norm() / lr3.norm()).item()
+            assert err3 < 3e-2, (name, err3)
     torch.cuda.synchronize()
     assert arena.status()[0] == 0, arena.status()
     arena.close()
