@@ -40,6 +40,8 @@ _SIGS = {
                        vp, vp],
     "spark_mla_qrope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp],
     "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp],
+    "spark_kda_chunk_prefill": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32,
+                                i32, i32, vp],
     "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
@@ -547,6 +549,10 @@ def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
     return True
 
 
+KDA_CHUNKED = os.environ.get("SPARK_KDA_CHUNKED", "1") == "1"
+_KERNELS_PER_CALL["spark_kda_chunk_prefill"] = 3
+
+
 def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
     """KDA layer core on the device: the low-rank gate expansions run on the GEMV/GEMM kernels, conv + norms +
     per-channel-decay delta rule + gated RMS output in one launch (sequential over the rows of a segment)."""
@@ -564,6 +570,29 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
     g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
     R = pre.shape[0]
     out = torch.empty(R, n, dtype=torch.bfloat16, device=dev)
+    if (commit and n_rows is None and c.head_dim == 128 and KDA_CHUNKED
+            and min(s.n for s in plan.segs) >= GDN_CHUNK_MIN_ROWS):
+        # committed segments of >= 64 rows: chunked form on tensor cores (16-row chunks, per-channel decay)
+        if "kda_chunks" not in d:
+            chunks, first = [], []
+            for i, sg in enumerate(plan.segs):
+                first.append(len(chunks))
+                chunks += [(i, k) for k in range((sg.n + 15) // 16)]
+            d["kda_chunks"] = torch.tensor(chunks, dtype=torch.int32).to(dev)
+            d["kda_chunk0"] = torch.tensor(first, dtype=torch.int32).to(dev)
+        chunks, first = d["kda_chunks"], d["kda_chunk0"]
+        nch = chunks.shape[0]
+        dll = lib()
+        fn = dll._dll.spark_kda_chunk_ws_floats
+        fn.restype, fn.argtypes = C.c_longlong, [i32, i32]
+        ws = scratch("kda_chunk_ws", fn(nch, c.n_heads), torch.float32, dev)
+        o_raw = scratch("kda_chunk_o", R * n, torch.float32, dev)
+        rc = dll.spark_kda_chunk_prefill(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]),
+                                         P(w["A_log"]), P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]),
+                                         len(plan.segs), P(chunks), nch, P(first), P(ws), P(o_raw), P(out), n, c.n_heads,
+                                         c.head_dim, stream())
+        check(rc, "spark_kda_chunk_prefill")
+        return out
     rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
                              P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows),
                              len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream())
