@@ -134,7 +134,7 @@ def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0, tp=(0, 1)
         kind = "attn" if cfg.family == "hybrid" else "mla"
         W["mtp"] = {"fc": it.mat(cfg.hidden, 2 * cfg.hidden), "norm_e": it.f32(cfg.hidden, val=1.0),
                     "norm_h": it.f32(cfg.hidden, val=1.0), "final_norm": it.f32(cfg.hidden, val=1.0),
-                    "layers": [_layer(cfg, cfg, it, cfg.n_layers, kind) for _ in range(cfg.mtp_layers)]}
+                    "layers": [_layer(cfg, lcfg, it, cfg.n_layers, kind, tp) for _ in range(cfg.mtp_layers)]}
     if cfg.ngram_layers:
         W["ngram_table"] = it.mat(cfg.ngram_rows, cfg.ngram_dim)
         D = cfg.ngram_dim * cfg.ngram_heads
