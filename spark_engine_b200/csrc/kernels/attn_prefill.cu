@@ -49,7 +49,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_pf);        // [64][LDS]
   __nv_bfloat16* Ks = Qs + PF_BM * LDS;                                  // [2][64][LDS]
   __nv_bfloat16* Vs = Ks + 2 * PF_BN * LDS;                              // [2][64][LDS]
-  const int sg = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int sg = blockIdx.z, h = blockIdx.y;
+  const int qt = gridDim.x - 1 - blockIdx.x;                 // longest row tiles (most key tiles) are scheduled first
   const int r0 = seg[sg * 4 + 1], n = seg[sg * 4 + 2], pos0 = seg[sg * 4 + 3];
   if (qt * PF_BM >= n) return;
   const int hk = h / (Hq / Hkv);

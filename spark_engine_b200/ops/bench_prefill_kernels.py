@@ -1,7 +1,7 @@
 """Microbenchmarks of the prefill-side kernels on shapes of the three model families (CUDA-event timed, L2 flushed
 between iterations): chunked gated-DeltaNet, chunked KDA, fused grouped EXL3 expert GEMM, flash-style prefill
 attention, latent attention.  `python -m spark_engine_b200.ops.bench_prefill_kernels [name ...] [--small]`;
-`--small` shrinks the shapes to a few hundred MB for profiler captures.
+`--small` shrinks the shapes to a few hundred MB and `--once` launches every kernel exactly once (profiler captures).
 """
 from __future__ import annotations
 
@@ -18,7 +18,15 @@ from ..quant import formats as Q
 DEV = "cuda"
 
 
+ONCE = False          # --once: a single launch per kernel and no A/B variant (profiler captures)
+
+
 def _time(fn, iters=5):
+    if ONCE:
+        if iters == 5:
+            fn()
+            torch.cuda.synchronize()
+        return float("nan")
     flush = torch.empty(160 << 20, dtype=torch.uint8, device=DEV)
     fn()
     torch.cuda.synchronize()
@@ -118,5 +126,6 @@ BENCHES = {"gdn": bench_gdn, "kda": bench_kda, "moe": bench_moe, "attn": bench_a
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     small = "--small" in sys.argv
+    ONCE = "--once" in sys.argv
     for name in (args or list(BENCHES)):
         BENCHES[name](small)
