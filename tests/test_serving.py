@@ -148,3 +148,18 @@ def test_front_end_text_helpers():
     assert r1 + r2 == "plan" and c1 + c2 == "answer"
     txt, calls = parse_tool_calls('ok <tool_call>{"name": "f", "arguments": {"x": 1}}</tool_call>')
     assert txt == "ok" and calls[0]["function"]["name"] == "f" and json.loads(calls[0]["function"]["arguments"]) == {"x": 1}
+
+
+def test_http_bench_script_against_a_live_front_end(tmp_path):
+    from spark_engine_b200.serving import bench_http
+    cfg, W, es, sock, th = _start(tmp_path, spec="none")
+    srv, app = serve(sock, "127.0.0.1", 0, "tiny")
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{srv.server_address[1]}"
+    res = bench_http.main(["--url", url, "--streams", "1", "2", "--max-tokens", "6", "--prefill", "40"])
+    assert [d["streams"] for d in res["decode"]] == [1, 2]
+    assert res["decode"][1]["tokens"] == 12 and res["decode"][0]["aggregate_decode_tok_s"] > 0
+    assert res["prefill"][0]["prompt_tokens"] >= 30 and res["prefill"][0]["prefill_tok_s"] > 0
+    srv.shutdown()
+    es.shutdown = True
+    th.join(10)
