@@ -12,6 +12,17 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#include <cstdio>
+
+// Status of the launches an entry point just made: 0, or -4 after printing the runtime's message (a bad launch
+// configuration, or an earlier asynchronous fault that surfaces here).
+static inline int spark_launch_rc(const char* where) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return 0;
+  fprintf(stderr, "[spark_kernels] %s: %s\n", where, cudaGetErrorString(e));
+  return -4;
+}
+
 namespace spark {
 
 // ---------------------------------------------------------------- status word

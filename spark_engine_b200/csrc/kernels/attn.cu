@@ -286,7 +286,7 @@ extern "C" int spark_attn_prep(const void* qkv, int ld, int R, int Hq, int Hkv, 
   dim3 grid(R, Hq + 2 * Hkv + idx_heads + (idx_dim > 0 ? 1 : 0));
   attn_prep_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)qkv, ld, a, q_norm, k_norm, iq_norm, ik_norm, inv_freq, pos,
                                         row_kv, row_j, (__nv_bfloat16*)qbuf, kc, vc, ks, vs, qi_buf, ik_raw, ik_pool);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* vc, const float* ks, const float* vs,
@@ -304,7 +304,7 @@ extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* v
                                                    part_o, part_ml, Hq, Hkv, D, scale);
   attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D,
                                               (__nv_bfloat16*)out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -365,5 +365,5 @@ extern "C" int spark_attn_decode_noalloc(const void* qbuf, const void* kc, const
                                                    part_o, part_ml, Hq, Hkv, D, scale);
   attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D,
                                               (__nv_bfloat16*)out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -198,7 +198,7 @@ static int launch_prefill(const void* qbuf, const void* kc, const void* vc, cons
   kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qbuf, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, row_kv, seg,
                                (const __nv_bfloat16*)qkv, ld, gated, (__nv_bfloat16*)out, Hq, Hkv,
                                scale * 1.4426950408889634f);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 }  // namespace spark

@@ -245,7 +245,7 @@ static CommCtx to_ctx(const HostCtx* h) {
 
 extern "C" int spark_comm_barrier(const HostCtx* h, long long flag_off, unsigned seq, cudaStream_t s) {
   comm_barrier_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // Many rows (prefill): two launches.  A CTA that waits for a peer's flag must never keep one of its own
@@ -303,7 +303,7 @@ extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long l
     ar_push_kernel<<<R < 592 ? R : 592, 256, 0, s>>>(a);
     ar_tail_kernel<<<R < 296 ? R : 296, 256, 0, s>>>(a, counter + 1);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // Reduce-scatter by row blocks (+ residual + RMSNorm on the owned rows) then all-gather of the bf16 result into
@@ -322,12 +322,12 @@ extern "C" int spark_rs_ag_rows(const HostCtx* h, long long slot_off, long long 
     int grid = M < 592 ? M : 592;
     rs_push_kernel<<<grid, 256, 0, s>>>(a);
   }
-  if (push_only == 1) return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  if (push_only == 1) return spark_launch_rc(__func__);
   int grid2 = rows_per_rank < 592 ? rows_per_rank : 592;
   a.counter = counter + 1;
   rs_finish_ag_push_kernel<<<grid2, 256, 0, s>>>(a);
   wait_flags_kernel<<<1, 32, 0, s>>>(a.c, flag_ag_off, seq, (uint32_t*)seq_ptr, 1);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_ag_push(const HostCtx* h, const void* x, int rows, int K, long long buf_off, long long flag_off,
@@ -336,20 +336,20 @@ extern "C" int spark_ag_push(const HostCtx* h, const void* x, int rows, int K, l
   if (K % 8) return -5;
   int grid = rows < 296 ? rows : 296;
   ag_push_kernel<<<grid, 256, 0, s>>>(to_ctx(h), (const __nv_bfloat16*)x, rows, K, buf_off, flag_off, seq, counter, (const uint32_t*)seq_ptr);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_seq_bump(void* seq_ptr, cudaStream_t s) {
   seq_bump_kernel<<<1, 1, 0, s>>>((uint32_t*)seq_ptr);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 extern "C" int spark_wait_flags(const HostCtx* h, long long flag_off, unsigned seq, cudaStream_t s) {
   wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, seq, nullptr, 0);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // Wait on a flag region using the device-side sequence counter (value + 1); bump != 0 stores it back.
 extern "C" int spark_wait_flags_dev(const HostCtx* h, long long flag_off, void* seq_ptr, int bump, cudaStream_t s) {
   wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, 0, (uint32_t*)seq_ptr, bump);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -54,10 +54,18 @@ __global__ void rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ x, const f
   }
 }
 
+// A token id outside [0, V) never reaches memory: its row is zero and the status word records {ST_BOUNDS, row, id}
+// (ids come from clients; the host also validates them, this is the last line).
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int H) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
   const int r = blockIdx.x;
-  const __nv_bfloat16* src = table + static_cast<size_t>(ids[r]) * H;
+  const int id = ids[r];
+  if (id < 0 || id >= V) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = 0.f;
+    if (threadIdx.x == 0 && status) set_status(status, ST_BOUNDS, r, id, V);
+    return;
+  }
+  const __nv_bfloat16* src = table + static_cast<size_t>(id) * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = __bfloat162float(src[i]);
 }
 
@@ -154,9 +162,9 @@ extern "C" void spark_rmsnorm_bf16(const void* x, const float* w, void* out, int
   if (R <= 0) return;
   rmsnorm_bf16_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)out, H, eps, one_plus);
 }
-extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s) {
+extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s, int V, int* status) {
   if (R <= 0) return;
-  embed_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)table, ids, out, H);
+  embed_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)table, ids, out, H, V, status);
 }
 extern "C" void spark_swiglu(const void* gu, void* out, int R, int F, float limit, cudaStream_t s) {
   if (R <= 0) return;

@@ -281,7 +281,7 @@ extern "C" int spark_ep_dispatch(const HostCtxE* h, const EpLayout* L, unsigned 
   const int smem = H + (H >> 7) * 4;
   ep_dispatch_kernel<<<T, EP_THREADS, smem, s>>>(to_ctx_e(h), *L, seq, (const __nv_bfloat16*)x, H, logits, ld, E, top_k, wts,
                                                   ids, send_count, done_counter);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // A rank with no tokens still has to raise its flags: dispatch with T == 0 goes through this.
@@ -296,14 +296,14 @@ __global__ void ep_empty_flags_kernel(CommCtx c, EpLayout L, uint32_t seq, int w
 }
 extern "C" int spark_ep_empty(const HostCtxE* h, const EpLayout* L, unsigned seq, int which, cudaStream_t s) {
   ep_empty_flags_kernel<<<1, 32, 0, s>>>(to_ctx_e(h), *L, seq, which);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_ep_recv(const HostCtxE* h, const EpLayout* L, unsigned seq, int H, void* a_rows, int* expert_local,
                              void* meta_out, int* total, int max_rows, cudaStream_t s) {
   int grid = max_rows < 1184 ? (max_rows > 0 ? max_rows : 1) : 1184;
   ep_recv_kernel<<<grid, 256, 0, s>>>(to_ctx_e(h), *L, seq, H, (__nv_bfloat16*)a_rows, expert_local, (int4*)meta_out, total);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_ep_combine_push(const HostCtxE* h, const EpLayout* L, unsigned seq, int H, int top_k, const void* y,
@@ -311,12 +311,12 @@ extern "C" int spark_ep_combine_push(const HostCtxE* h, const EpLayout* L, unsig
   int grid = max_rows < 1184 ? (max_rows > 0 ? max_rows : 1) : 1184;
   ep_combine_push_kernel<<<grid, 256, 0, s>>>(to_ctx_e(h), *L, seq, H, top_k, (const __nv_bfloat16*)y, (const int4*)meta, total,
                                               done_counter);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_ep_combine_reduce(const HostCtxE* h, const EpLayout* L, unsigned seq, int T, int H, int top_k,
                                        const float* wts, float* res, void* out, cudaStream_t s) {
   if (T <= 0) return 0;
   ep_combine_reduce_kernel<<<T, 256, 0, s>>>(to_ctx_e(h), *L, seq, H, top_k, wts, res, (__nv_bfloat16*)out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

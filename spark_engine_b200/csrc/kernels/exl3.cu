@@ -66,7 +66,7 @@ extern "C" int spark_exl3_reconstruct(const void* trellis, void* Wt, int K, int 
   const unsigned blocks = (unsigned)((tiles * 32 + 255) / 256);
   if (codebook == 0) exl3_reconstruct_kernel<0><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
   else exl3_reconstruct_kernel<1><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // pre (post = 0): x bf16 -> y fp16 = had128(x * scale);  post = 1: x fp32 -> y bf16 = had128(x) * scale.
@@ -78,5 +78,5 @@ extern "C" int spark_exl3_had_rows(const void* x, int ldx, const void* scale, vo
   dim3 grid(R, C / 128);
   if (!post) exl3_had_rows_kernel<__nv_bfloat16, __half><<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, (const __half*)scale, (__half*)y, ldy, 0, row_expert, expert_stride);
   else exl3_had_rows_kernel<float, __nv_bfloat16><<<grid, 128, 0, s>>>((const float*)x, ldx, (const __half*)scale, (__nv_bfloat16*)y, ldy, 1, row_expert, expert_stride);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

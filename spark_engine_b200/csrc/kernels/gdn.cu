@@ -138,5 +138,5 @@ extern "C" int spark_gdn_seq(const void* proj, int ldp, const void* ab, int ldab
                                            dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
   else
     return -5;
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -468,5 +468,5 @@ extern "C" int spark_gdn_chunk_prefill(const void* proj, int ldp, const void* ab
                                                                     tail, o_raw, Hv * GD, Hk, Hv);
   gdn_chunk_out_kernel<<<dim3(n_chunks, Hv), 256, 0, s>>>(o_raw, Hv * GD, (const __nv_bfloat16*)proj, ldp, norm_w, seg, chunks,
                                                           (__nv_bfloat16*)out, ldo, Hk, Hv, eps);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -53,7 +53,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const GemmArgs& 
     attr_done = true;
   }
   kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tA, tB, g, epi);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 }  // namespace spark

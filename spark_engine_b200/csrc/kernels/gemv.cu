@@ -118,7 +118,7 @@ static int launch_gemv(const void* x, int ldx, const void* W, long long es, int 
   dim3 grid((N + GEMV_WARPS * GEMV_COLS - 1) / (GEMV_WARPS * GEMV_COLS), items);
   kern<<<grid, GEMV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, es, ldw, (TO*)y, ldy,
                                             rows, N, K, pe, pr, act, limit);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 }  // namespace spark

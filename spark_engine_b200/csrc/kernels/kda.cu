@@ -131,5 +131,5 @@ extern "C" int spark_kda_seq(const void* pre, int ldp, const float* g1, const fl
   else if (D == 32) SPARK_KDA(32, 1);
   else return -5;
 #undef SPARK_KDA
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -366,5 +366,5 @@ extern "C" int spark_kda_chunk_prefill(const void* pre, int ldp, const float* g1
   kda_chunk_state_kernel<<<dim3(KD / KVS, H, nseg), 128, 0, s>>>(ws, seg, seg_chunk0, (const __nv_bfloat16*)pre, ldp, S, tail,
                                                                  o_raw, H * KD, H);
   kda_chunk_out_kernel<<<dim3(n_chunks, H), 128, 0, s>>>(o_raw, H * KD, g2, ldg, o_norm, seg, chunks, (__nv_bfloat16*)out, ldo, H);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -307,7 +307,7 @@ extern "C" int spark_mla_prep(const void* a, int lda, int R, int q_lora, int kv_
   MlaDims dm{q_lora, kv_lora, rope, idx_dim, idx_heads, pool_sz, eps};
   mla_prep_kernel<<<R, 128, 0, s>>>((const __nv_bfloat16*)a, lda, dm, q_norm, kv_norm, ln_w, ln_b, ape, inv_freq, pos, row_kv,
                                     row_j, (__nv_bfloat16*)cq, (__nv_bfloat16*)lat, ik, ig, pool, hw);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_mla_qrope(const void* qb, int ldq, int R, int H, int D, int rope, int kv_lora, const double* inv_freq,
@@ -316,7 +316,7 @@ extern "C" int spark_mla_qrope(const void* qb, int ldq, int R, int H, int D, int
   if (rope > 512) return -5;
   mla_qrope_kernel<<<dim3(R, H), (rope / 2 + 31) / 32 * 32, 0, s>>>((const __nv_bfloat16*)qb, ldq, D, rope, kv_lora, inv_freq, pos,
                                                                     (__nv_bfloat16*)q_full, H);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // part_o: fp32 [R, H, nsplit, L]; part_ml: fp32 [R, H, nsplit, 2]; out: bf16 [R, H, L].
@@ -337,5 +337,5 @@ extern "C" int spark_mla_attn(const void* q_full, const void* lat, const int* po
   kern<<<dim3(R, nsplit), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv, sel, sel_n, sel_ld,
                                           part_o, part_ml, H, KW, kv_lora, scale);
   mla_merge_kernel<<<dim3(R, H), 128, 0, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, (__nv_bfloat16*)out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

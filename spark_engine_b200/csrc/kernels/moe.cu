@@ -228,7 +228,7 @@ extern "C" int spark_moe_route(const float* logits, int ld, int R, int E, int to
   if (R <= 0) return 0;
   if (E > ROUTE_THREADS * ROUTE_MAXE_PER_THREAD || top_k > 32) return -5;
   moe_route_kernel<<<R, ROUTE_THREADS, 0, s>>>(logits, ld, E, top_k, kind, bias, scale, shared_gate, wts, ids, pair_row, sg, e_lo, e_hi);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // Scratch `block_hist` must hold ceil(P/256) * E ints when P > 2048.
@@ -243,7 +243,7 @@ extern "C" int spark_moe_sort(const int* ids, int P, int E, int* perm, int* inv_
     moe_scan_kernel<<<1, 1024, E * sizeof(int), s>>>(block_hist, nb, E, offsets, (int4*)tile_list, tile_count);
     moe_place_kernel<<<nb, 256, 256 * sizeof(int), s>>>(ids, P, E, block_hist, offsets, perm, inv_perm);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int* inv_perm, const float* wts, int R,
@@ -256,5 +256,5 @@ extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int
   else
     moe_combine_kernel<__nv_bfloat16><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const __nv_bfloat16*)y, inv_perm, wts, top_k,
                                                         (const __nv_bfloat16*)shared, sg, H, (__nv_bfloat16*)out_bf16, pair_expert);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -195,7 +195,7 @@ static int launch_mx_gemv(const void* x, int ldx, const void* W, const void* sc,
   dim3 grid(N / MXV_COLS, items);
   kern<<<grid, MXV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W, sc, wes, ses, (TO*)y, ldy, rows,
                                           N, K, pe, pr, act, limit);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 template <int FMT, typename TO>
@@ -318,7 +318,7 @@ extern "C" int spark_mx_dequant(const void* W, const void* scales, int fmt, void
   const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
   if (fmt == 0) mx_dequant_kernel<0><<<blocks, 256, 0, s>>>((const uint8_t*)W, scales, (__nv_bfloat16*)out, rows, N, K);
   else mx_dequant_kernel<1><<<blocks, 256, 0, s>>>((const uint8_t*)W, scales, (__nv_bfloat16*)out, rows, N, K);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 // block 128 -> fp32 scales [R, K/128]; block 32 -> E8M0 bytes [R, K/32].  x bf16 (in_f32 0) or fp32.
@@ -332,5 +332,5 @@ extern "C" int spark_act_quant(const void* x, int ldx, int in_f32, void* q, void
   if (block == 128) { if (in_f32) SPARK_AQ(128, float); else SPARK_AQ(128, __nv_bfloat16); }
   else { if (in_f32) SPARK_AQ(32, float); else SPARK_AQ(32, __nv_bfloat16); }
 #undef SPARK_AQ
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

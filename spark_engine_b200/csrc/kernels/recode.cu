@@ -161,7 +161,7 @@ static int launch_coded(const void* x, int ldx, const void* W, const float* sc, 
   static bool done = false;
   if (!done) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done = true; }
   kern<<<N / RCV_COLS, RCV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W, sc, (TO*)y, ldy, R, N, K);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 }  // namespace spark

@@ -158,7 +158,7 @@ extern "C" int spark_idx_score(const float* qi, int R, int H, int Dm, const floa
   if (R <= 0 || nb_max <= 0) return 0;
   if (Dm > 128) return -5;
   idx_score_kernel<<<dim3((nb_max + 7) / 8, R), 256, 0, s>>>(qi, H, Dm, pool, row_kv, pos, block, head_w, scale, score, ld);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }
 
 extern "C" int spark_topk_select(const float* score, int ld, const int* pos, int R, int block, int k, int* sel,
@@ -166,5 +166,5 @@ extern "C" int spark_topk_select(const float* score, int ld, const int* pos, int
   if (R <= 0) return 0;
   if (sel_ld < k * block + block + window || window < 0) return -5;
   topk_select_kernel<<<R, 1024, 0, s>>>(score, ld, pos, block, k, window, sel, sel_ld, sel_n);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return spark_launch_rc(__func__);
 }

@@ -29,7 +29,7 @@ _SIGS = {
     "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp],
     "spark_add_rmsnorm": [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
-    "spark_embed": [vp, vp, vp, i32, i32, vp],
+    "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp],
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
     "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
@@ -150,6 +150,10 @@ def status_word(device) -> torch.Tensor:
 def read_status(device) -> tuple:
     st = status_word(device).tolist()
     return tuple(st)
+
+
+def reset_status(device):
+    status_word(device).zero_()
 
 
 def clear_status(device):
@@ -339,7 +343,7 @@ def rmsnorm(x, w, eps, one_plus=False):
 def embed(table, ids32):
     R, H = ids32.shape[0], table.shape[1]
     out = torch.empty(R, H, dtype=torch.float32, device=table.device)
-    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream())
+    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)))
     return out
 
 

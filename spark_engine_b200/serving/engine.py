@@ -139,6 +139,10 @@ class LLMEngine:
         """Chunked prefill of a fresh sequence; returns the logits of the last prompt token."""
         chunk = chunk or self.ecfg.prefill_chunk
         m = self.model
+        vocab = self.cfg.vocab
+        for t in ids:                       # client-supplied ids never index the embedding table unchecked
+            if not 0 <= t < vocab and not (1 << 20) <= t < (1 << 24):
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab} entries")
         m.reset_slot(slot)
         last = None
         for c0 in range(0, len(ids), chunk):

@@ -315,3 +315,17 @@ def test_kda_chunked_prefill_matches_sequential_kernel(lens):
     assert torch.equal(t1, t0)
     row_err = (o1 - o0).norm(dim=1) / o0.norm(dim=1).clamp_min(1e-6)
     assert row_err.max() < 3e-2, row_err.max()
+
+
+def test_embedding_rejects_out_of_range_ids():
+    """A token id outside the table never reaches memory: zero row + status word {bounds, row, id}."""
+    table = torch.randn(100, 64, device=DEV).bfloat16()
+    ids = torch.tensor([3, 100, 7, -1, 99], dtype=torch.int32, device=DEV)
+    cu().reset_status(torch.device(DEV))
+    out = cu().embed(table, ids)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], table[3].float()) and torch.equal(out[4], table[99].float())
+    assert float(out[1].abs().sum()) == 0 and float(out[3].abs().sum()) == 0
+    st = cu().read_status(torch.device(DEV))
+    assert st[0] == 8 and st[1] in (1, 3)
+    cu().reset_status(torch.device(DEV))

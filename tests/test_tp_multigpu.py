@@ -60,7 +60,8 @@ def _worker(rank, world, port):
         ref3 = Model(cfg3, to_device(W3, dev), device=dev, dtype=torch.bfloat16, n_slots=1, kv_tokens=128)
         m3 = Model(cfg3, to_device(shard_dense_weights(W3, cfg3, rank, world), dev), device=dev, dtype=torch.bfloat16,
                    n_slots=1, kv_tokens=128, tp=tp3)
-        for plan_items in ([(0, ids[:36], 0)], [(0, ids[36:37], 36)]):
+        ids3 = [t % cfg3.vocab for t in ids]
+        for plan_items in ([(0, ids3[:36], 0)], [(0, ids3[36:37], 36)]):
             lr3 = ref3.forward(make_plan(plan_items, device=dev))
             lt3 = m3.forward(make_plan(plan_items, device=dev))
             parts3 = [torch.empty_like(lt3) for _ in range(world)]
