@@ -1,0 +1,280 @@
+// Block-scaled FP8 GEMM on tcgen05:  C[M,N] = (A . sfa)[M,K] (B . sfb)[N,K]^T with e4m3 operands and one E8M0 scale per
+// 32 elements along K for every row of A and of B (MXFP8), accumulated in fp32 in TMEM.  The scales are applied by the
+// tensor core itself (`tcgen05.mma.kind::mxf8f6f4.block_scale`): no dequantised copy of the weights ever exists.
+//
+// Same skeleton as the bf16 GEMM (persistent CTAs, warp 0 = TMA producer, warp 1 = one-thread MMA issuer, warps 2..5 =
+// epilogue, 128-byte-swizzled K-major tiles, two TMEM accumulator stages), plus the scale-factor path:
+//   * scales live in global memory in the layout the tensor core wants, one 512-byte block per (128 rows, 128 k):
+//     byte (row % 32) * 16 + (row / 32) * 4 + (k / 32) % 4  (act_quant / weight preparation write this directly);
+//   * the producer fetches the block of A and of B with a bulk copy onto the stage's full barrier;
+//   * the MMA thread copies both blocks to tensor memory (`tcgen05.cp.32x128b.warpx4`: 32 rows x 16 bytes, replicated
+//     to the four lane quadrants) and issues four K=32 MMAs per stage whose descriptors select scale byte 0..3.
+// Tile 128 x 128 x 128 bytes of K; TMEM: 2 x 128 accumulator columns + 8 scale columns per stage.
+// Every wait is bounded (status word + normal teardown).  Reference paths replaced: engine-rs/shim/ds41_mx.cu
+// fp8_gemm_mx* (warp-level block-scaled mma.sync), fp8.cu / fp8pf.cu (wmma + scale promotion).
+#include "../common/ptx.cuh"
+#include <mutex>
+
+namespace spark {
+
+constexpr int MX_BM = 128, MX_BN = 128, MX_BK = 128;       // BK in elements = bytes (fp8)
+constexpr int MX_STAGES = 5;
+constexpr int MX_ACC_STAGES = 2;
+constexpr int MX_THREADS = 192;
+constexpr int MX_A_BYTES = MX_BM * MX_BK, MX_B_BYTES = MX_BN * MX_BK, MX_SF_BYTES = 512;
+constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;
+constexpr int MX_SMEM = MX_STAGES * MX_STAGE_BYTES + 256 + 1024;
+constexpr int MX_TMEM_COLS = 512;                           // 256 accumulator + 40 scale columns, power of two
+constexpr int MX_SF_COL0 = MX_ACC_STAGES * MX_BN;
+
+struct MxGemmArgs {
+  int M, N, K;
+  const uint8_t* sfa; const uint8_t* sfb;     // [ceil(M/128)][K/128][512], [ceil(N/128)][K/128][512]
+  void* C; int ldc; int out_f32;
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 consecutive 32-bit TMEM columns, replicated over the 4 lane quadrants
+__device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// un-swizzled K-major descriptor of a 32 x 16-byte block: 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(16 >> 4) << 16;        // leading byte offset (one 16-byte column only)
+  d |= static_cast<uint64_t>(128 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= 1ull << 46;                                  // descriptor version of this architecture
+  return d;
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t tsfa,
+                                          uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
+}
+// block-scaled instruction descriptor: [4,6) B scale byte, [7,10) A format, [10,13) B format (0 = e4m3), [17,23) N>>3,
+// bit 23 scale format (1 = E8M0), [24,29) M>>4, [29,31) A scale byte, bit 31 K size (0 = 32 for 8-bit operands)
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t M, uint32_t N) {
+  return ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(MX_THREADS, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, MxGemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + MX_STAGES * MX_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + MX_STAGES;
+  uint64_t* tmem_full = empty_bar + MX_STAGES;
+  uint64_t* tmem_empty = tmem_full + MX_ACC_STAGES;
+  uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(tmem_empty + MX_ACC_STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_k = g.K / MX_BK;
+  const int mt_n = (g.M + MX_BM - 1) / MX_BM, nt_n = (g.N + MX_BN - 1) / MX_BN;
+  const int num_tiles = mt_n * nt_n;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < MX_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < MX_ACC_STAGES; ++s) { mbar_init(&tmem_full[s], 1); mbar_init(&tmem_empty[s], 4); }
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc<MX_TMEM_COLS>(tmem_base_ptr); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int mt = t / nt_n, nt = t % nt_n;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, kb); ok = false; break;
+          }
+          uint8_t* a_dst = smem + stage * MX_STAGE_BYTES;
+          uint8_t* b_dst = a_dst + MX_A_BYTES;
+          uint8_t* sfa_dst = b_dst + MX_B_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], MX_STAGE_BYTES);
+          tma_load_2d(a_dst, &tmA, &full_bar[stage], kb * MX_BK, mt * MX_BM);
+          tma_load_2d(b_dst, &tmB, &full_bar[stage], kb * MX_BK, nt * MX_BN);
+          bulk_load(sfa_dst, g.sfa + (static_cast<size_t>(mt) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
+          bulk_load(sfa_dst + MX_SF_BYTES, g.sfb + (static_cast<size_t>(nt) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES,
+                    &full_bar[stage]);
+          if (++stage == MX_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc0 = make_idesc_mx(MX_BM, MX_BN);
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          set_status(g.status, ST_TIMEOUT_TMEM_EMPTY, blockIdx.x, t, acc); break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * MX_BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            set_status(g.status, ST_TIMEOUT_MBAR_FULL, blockIdx.x, t, kb); ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * MX_STAGE_BYTES);
+          const uint64_t a_desc = make_smem_desc_sw128(a_addr);
+          const uint64_t b_desc = make_smem_desc_sw128(a_addr + MX_A_BYTES);
+          const uint32_t tsfa = tmem_base + MX_SF_COL0 + stage * 8, tsfb = tsfa + 4;
+          tmem_cp_32x128b_x4(tsfa, make_sf_desc(a_addr + MX_A_BYTES + MX_B_BYTES));
+          tmem_cp_32x128b_x4(tsfb, make_sf_desc(a_addr + MX_A_BYTES + MX_B_BYTES + MX_SF_BYTES));
+#pragma unroll
+          for (int k = 0; k < MX_BK / 32; ++k) {
+            // 32 fp8 = 32 bytes along K inside the swizzled row: +2 in the encoded address; scale byte k of the block
+            const uint32_t idesc = idesc0 | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
+            umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsfa, tsfb, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == MX_STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tmem_full[acc]);
+        if (++acc == MX_ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int mt = t / nt_n, nt = t % nt_n;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_phase))) {
+        set_status(g.status, ST_TIMEOUT_TMEM_FULL, blockIdx.x, t, acc); break;
+      }
+      tc_fence_after();
+      const int row = mt * MX_BM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + acc * MX_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < MX_BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c, r);
+        tmem_ld_wait();
+        const int col = nt * MX_BN + c;
+        if (row < g.M) {
+          if (g.out_f32) {
+            float* dst = reinterpret_cast<float*>(g.C) + static_cast<size_t>(row) * g.ldc + col;
+            for (int i = 0; i < 32 && col + i < g.N; ++i) dst[i] = __uint_as_float(r[i]);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C) + static_cast<size_t>(row) * g.ldc + col;
+            if (col + 32 <= g.N && (g.ldc & 7) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < g.N; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == MX_ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc<MX_TMEM_COLS>(tmem_base); }
+}
+
+// Scale bytes [rows, K/32] (row-major) -> the tensor core's block layout [ceil(rows/128)][K/128][512]; rows past the
+// end get exponent 0 (scale 2^-127: their products vanish and are never stored anyway).
+__global__ void mx_sf_to_blocks_kernel(const uint8_t* __restrict__ sf, uint8_t* __restrict__ out, int rows, int kblocks32) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int kb128 = kblocks32 >> 2;
+  const long long total = static_cast<long long>((rows + 127) / 128) * kb128 * 512;
+  if (i >= total) return;
+  const int within = static_cast<int>(i & 511);
+  const long long blk = i >> 9;
+  const int kt = static_cast<int>(blk % kb128);
+  const int rt = static_cast<int>(blk / kb128);
+  const int r32 = within >> 4, q = (within >> 2) & 3, kk = within & 3;
+  const int row = rt * 128 + q * 32 + r32;
+  out[i] = row < rows ? sf[static_cast<size_t>(row) * kblocks32 + kt * 4 + kk] : 0;
+}
+
+typedef CUresult (*EncodeTiledFnMx)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFnMx encode_fn_mx() {
+  static EncodeTiledFnMx fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFnMx>(p);
+  });
+  return fn;
+}
+static int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t K, uint64_t ld) {
+  EncodeTiledFnMx fn = encode_fn_mx();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld & 15)) return -2;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {MX_BK, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+}  // namespace spark
+
+using namespace spark;
+
+// A e4m3 [M,K] (row stride lda bytes), B e4m3 [N,K]; sfa / sfb in block layout (spark_mx_sf_to_blocks); K % 128 == 0.
+extern "C" int spark_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N, int K,
+                                int lda, int ldb, int ldc, int out_f32, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % MX_BK) return -5;
+  CUtensorMap tA, tB;
+  int r = make_tmap_u8(&tA, A, M, K, lda);
+  if (r) return r;
+  r = make_tmap_u8(&tB, B, N, K, ldb);
+  if (r) return r;
+  MxGemmArgs g{M, N, K, (const uint8_t*)sfa, (const uint8_t*)sfb, C, ldc, out_f32, status};
+  static bool attr_done = false;
+  if (!attr_done) { cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM); attr_done = true; }
+  static int sms = 0;
+  if (!sms) { int dev; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const int tiles = ((M + MX_BM - 1) / MX_BM) * ((N + MX_BN - 1) / MX_BN);
+  gemm_mxfp8_kernel<<<tiles < sms ? tiles : sms, MX_THREADS, MX_SMEM, stream>>>(tA, tB, g);
+  return spark_launch_rc(__func__);
+}
+
+extern "C" int spark_mx_sf_to_blocks(const void* sf, void* out, int rows, int kblocks32, cudaStream_t stream) {
+  if (rows <= 0 || kblocks32 <= 0) return 0;
+  if (kblocks32 % 4) return -5;
+  const long long total = static_cast<long long>((rows + 127) / 128) * (kblocks32 / 4) * 512;
+  mx_sf_to_blocks_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>((const uint8_t*)sf, (uint8_t*)out, rows,
+                                                                                         kblocks32);
+  return spark_launch_rc(__func__);
+}

@@ -13,7 +13,7 @@ import ctypes
 
 import torch
 
-from ..quant.formats import Fp8BlockWeight, Mxfp4Weight, QuantWeight
+from ..quant.formats import Fp8BlockWeight, Mxfp4Weight, Mxfp8Weight, QuantWeight
 from ..quant.recode import Q4Weight, Q8Weight
 from . import cuda as cu
 
@@ -23,6 +23,8 @@ _SIGS = {
                       _vp],
     "spark_mx_dequant": [_vp, _vp, _i32, _vp, _i64, _i32, _i32, _vp],
     "spark_act_quant": [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "spark_gemm_mxfp8": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp],
+    "spark_mx_sf_to_blocks": [_vp, _vp, _i32, _i32, _vp],
     "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
 }
 _bound = False
@@ -109,8 +111,36 @@ def _resident_bf16(w: QuantWeight, device) -> torch.Tensor:
     return t
 
 
+def sf_blocks(sf: torch.Tensor) -> torch.Tensor:
+    """E8M0 scale bytes [rows, K/32] -> the tensor core's block layout [ceil(rows/128), K/128, 512]."""
+    rows, kb = sf.shape
+    out = torch.empty((rows + 127) // 128, kb // 4, 512, dtype=torch.uint8, device=sf.device)
+    rc = _lib().spark_mx_sf_to_blocks(cu.P(sf.contiguous()), cu.P(out), rows, kb, cu.stream())
+    cu.check(rc, "spark_mx_sf_to_blocks")
+    return out
+
+
+def gemm_mxfp8(a_q, a_sf, w: Mxfp8Weight, out_f32=False):
+    """C = (a_q . a_sf) (w.q . w.scales)^T on the block-scaled tcgen05 path.  a_q e4m3 [M,K], a_sf u8 [M, K/32]."""
+    M, K = a_q.shape
+    assert K == w.k and K % 128 == 0
+    wb = getattr(w, "_sf_blocks", None)
+    if wb is None or wb.device != a_q.device:
+        wb = w._sf_blocks = sf_blocks(w.scales)
+    ab = sf_blocks(a_sf)
+    c = torch.empty(M, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a_q.device)
+    rc = _lib().spark_gemm_mxfp8(cu.P(a_q), cu.P(w.q), cu.P(ab), cu.P(wb), cu.P(c), M, w.n, K, a_q.stride(0), w.q.stride(0),
+                                 w.n, int(out_f32), cu.P(cu.status_word(a_q.device)), cu.stream())
+    cu.check(rc, "spark_gemm_mxfp8")
+    return c
+
+
 def quant_linear(x, w: QuantWeight):
     x = cu._as_bf16(x).contiguous()
+    if isinstance(w, Mxfp8Weight):
+        # activations are quantised to MXFP8 (1 x 32 E8M0 scales) and both operands go to the tensor core as they are
+        a_q, a_sf = act_quant(x, block=32)
+        return gemm_mxfp8(a_q, a_sf, w)
     if isinstance(w, (Fp8BlockWeight, Mxfp4Weight)):
         if x.shape[0] <= 16:
             return gemv(x, w)

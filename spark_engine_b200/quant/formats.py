@@ -297,3 +297,42 @@ def act_quant_fp8(x: torch.Tensor, block: int = 128, pow2: bool = False):
     if pow2:
         sc = torch.pow(2.0, torch.ceil(torch.log2(sc)))
     return (blk / sc.unsqueeze(-1)).to(torch.float8_e4m3fn).view(R, K), sc
+
+
+# ----------------------------------------------------------------------------------------------- MXFP8
+def quant_mxfp8(w: torch.Tensor):
+    """[..., K] fp32 -> (e4m3 [..., K], E8M0 scale bytes [..., K/32]); scale = 2^ceil(log2(amax/448)) per 32
+    (reference/ds41/kernel.py:76-93)."""
+    K = w.shape[-1]
+    blk = w.float().reshape(*w.shape[:-1], K // 32, 32)
+    amax = blk.abs().amax(-1).clamp_min(448.0 * 2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / 448.0)).clamp(-127, 127)
+    q = (blk / torch.pow(2.0, e).unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).reshape(w.shape)
+    return q, (e + 127).to(torch.uint8)
+
+
+def dequant_mxfp8(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    K = q.shape[-1]
+    return (q.float().reshape(*q.shape[:-1], K // 32, 32) * e8m0_to_float(scales).unsqueeze(-1)).reshape(q.shape)
+
+
+class Mxfp8Weight(QuantWeight):
+    """e4m3 [N,K] + E8M0 scale per 32 along K: the operand format of the block-scaled tensor-core GEMM."""
+    experts = False
+
+    def __init__(self, q, scales):
+        self.q, self.scales = q, scales
+        self.n, self.k = q.shape
+
+    @staticmethod
+    def encode(w: torch.Tensor) -> "Mxfp8Weight":
+        return Mxfp8Weight(*quant_mxfp8(w))
+
+    def dequant(self):
+        return dequant_mxfp8(self.q.cpu(), self.scales.cpu())
+
+    def to(self, device):
+        return Mxfp8Weight(self.q.to(device), self.scales.to(device))
+
+    def nbytes(self):
+        return self.q.numel() + self.scales.numel()

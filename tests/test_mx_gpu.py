@@ -133,3 +133,31 @@ def test_mx_model_matches_cpu_runner_on_the_same_weights():
     assert rel_err(lg, ref[:32]) < 4e-2
     rows = [m.forward(make_plan([(0, [ids[t]], t)], device=DEV)).float().cpu()[0] for t in range(32, 40)]   # GEMV path
     assert rel_err(torch.stack(rows), ref[32:]) < 4e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 128, 512), (256, 384, 1024), (77, 200, 256), (1000, 640, 2048)])
+def test_block_scaled_fp8_gemm_matches_dequantised_product(M, N, K):
+    """tcgen05 block-scaled MMA (scales applied by the tensor core) against the fp32 product of the dequantised
+    operands: equal up to fp32 summation order."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g) * torch.exp(torch.randn(M, 1, generator=g))          # rows of different magnitude
+    w = torch.randn(N, K, generator=g) * 0.05 * torch.exp(torch.randn(N, K // 32, generator=g).repeat_interleave(32, 1))
+    wq = Q.Mxfp8Weight.encode(w).to(DEV)
+    aq, asf = Q.quant_mxfp8(a)
+    c = mx().gemm_mxfp8(aq.to(DEV), asf.to(DEV), wq, out_f32=True)
+    torch.cuda.synchronize()
+    st = ops.cuda_ops().read_status(torch.device(DEV))
+    assert st[0] == 0, st
+    ref = Q.dequant_mxfp8(aq, asf).double() @ wq.dequant().double().t()
+    assert rel_err(c.cpu().double(), ref) < 1e-5
+    assert torch.equal(c, mx().gemm_mxfp8(aq.to(DEV), asf.to(DEV), wq, out_f32=True))
+
+
+def test_mxfp8_linear_quantises_activations_on_the_device():
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(256, 512, generator=g) * 0.05
+    wq = Q.Mxfp8Weight.encode(w).to(DEV)
+    x = torch.randn(150, 512, generator=g).bfloat16().to(DEV)
+    y = ops.linear(x, wq)
+    ref = x.float().cpu() @ wq.dequant().t()
+    assert rel_err(y.cpu(), ref) < 4e-2              # e4m3 activations: ~2^-4 relative per element, averaged over K
