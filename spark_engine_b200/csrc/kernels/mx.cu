@@ -32,6 +32,10 @@ __device__ __forceinline__ uint32_t fp8x2_to_h2(uint16_t v) {
   __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
   return static_cast<uint32_t>(r.x) | (static_cast<uint32_t>(r.y) << 16);
 }
+__device__ __forceinline__ uint32_t h2_scale(uint32_t v, __half2 scale) {
+  const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&v), scale);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ uint32_t fp4x2_to_h2(uint8_t v, __half2 scale) {
   __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(v), __NV_E2M1);
   __half2 h = __hmul2(*reinterpret_cast<__half2*>(&r), scale);
@@ -55,6 +59,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // FMT 0: W = e4m3 [N,K], scales fp32 [N/128, K/128].  FMT 1: W = nibbles [N,K/2], scales u8 [N, K/32].
+// FMT 2: W = e4m3 [N,K], scales u8 (E8M0) [N, K/32] (MXFP8).
 // RB = rows held in shared memory (1, 4, 8 or 16).  act 1: x is [gate | up] (2K wide), swiglu while staging.
 template <int FMT, int RB, typename TO>
 __global__ void __launch_bounds__(MXV_WARPS * 32)
@@ -93,11 +98,11 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * MXV_COLS;
-  constexpr int KI = FMT == 0 ? 64 : 128;                      // k per warp iteration (4 threads x 16 bytes)
+  constexpr int KI = FMT == 1 ? 128 : 64;                      // k per warp iteration (4 threads x 16 bytes)
   constexpr int KT = KI / 4;                                   // k per thread per iteration
   constexpr int STEPS = KT / 4;                                // mma k-steps per iteration
   const int iters = K / KI;
-  const size_t row_bytes = FMT == 0 ? K : (K >> 1);
+  const size_t row_bytes = FMT == 1 ? (K >> 1) : K;
   const uint8_t* Wb = W + static_cast<size_t>(e) * w_expert_stride;
   const uint8_t* w_lo = Wb + static_cast<size_t>(n0 + g) * row_bytes + t * 16;
   const uint8_t* w_hi = w_lo + 8 * row_bytes;
@@ -106,10 +111,12 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
   if (FMT == 0) sc_f = reinterpret_cast<const float*>(scales) + static_cast<size_t>(e) * s_expert_stride +
                        static_cast<size_t>(n0 >> 7) * (K >> 7);
   else {
+    // FMT 1: a lane's 16 bytes are one 32-k scale block; FMT 2: 16 k = half a block, lanes (0,1) and (2,3) share one
     sc_lo = reinterpret_cast<const uint8_t*>(scales) + static_cast<size_t>(e) * s_expert_stride +
-            static_cast<size_t>(n0 + g) * (K >> 5) + t;
+            static_cast<size_t>(n0 + g) * (K >> 5) + (FMT == 1 ? t : (t >> 1));
     sc_hi = sc_lo + 8 * (K >> 5);
   }
+  constexpr int SPI = FMT == 1 ? 4 : 2;                        // scale blocks per warp iteration
   const __half* xa = xs + (g < RB ? g : 0) * XS + t * KT;       // row g of A
   const __half* xb = xs + ((g + 8) < RB ? (g + 8) : 0) * XS + t * KT;
   const bool has_a = g < RB, has_b = (g + 8) < RB;
@@ -125,7 +132,7 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
       if (it < iters) {
         wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + static_cast<size_t>(it) * 64));
         wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + static_cast<size_t>(it) * 64));
-        if (FMT == 1) { sl[u] = __ldg(sc_lo + it * 4); sh[u] = __ldg(sc_hi + it * 4); }
+        if (FMT != 0) { sl[u] = __ldg(sc_lo + it * SPI); sh[u] = __ldg(sc_hi + it * SPI); }
       }
     }
 #pragma unroll
@@ -136,7 +143,7 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
       const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
       const uint32_t* ph = reinterpret_cast<const uint32_t*>(&wh[u]);
       __half2 hl, hh;
-      if (FMT == 1) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
+      if (FMT != 0) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
 #pragma unroll
       for (int s = 0; s < STEPS; ++s) {
         // A: 4 consecutive k of rows g / g+8
@@ -148,6 +155,10 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
           const uint32_t vl = pl[s], vh = ph[s];
           b0l = fp8x2_to_h2(static_cast<uint16_t>(vl & 0xffffu)); b1l = fp8x2_to_h2(static_cast<uint16_t>(vl >> 16));
           b0h = fp8x2_to_h2(static_cast<uint16_t>(vh & 0xffffu)); b1h = fp8x2_to_h2(static_cast<uint16_t>(vh >> 16));
+        } else if (FMT == 2) {
+          const uint32_t vl = pl[s], vh = ph[s];
+          b0l = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vl & 0xffffu)), hl); b1l = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vl >> 16)), hl);
+          b0h = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vh & 0xffffu)), hh); b1h = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vh >> 16)), hh);
         } else {
           const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
           b0l = fp4x2_to_h2(static_cast<uint8_t>(vl & 0xffu), hl); b1l = fp4x2_to_h2(static_cast<uint8_t>((vl >> 8) & 0xffu), hl);
@@ -296,7 +307,7 @@ __global__ void act_quant_kernel(const TI* __restrict__ x, int ldx, uint8_t* __r
 
 using namespace spark;
 
-// fmt 0 = FP8 128x128-block scales (fp32), 1 = MXFP4.  Strides are per expert (bytes for W, elements for scales).
+// fmt 0 = FP8 128x128-block scales (fp32), 1 = MXFP4, 2 = MXFP8 (E8M0 per 32).  Strides are per expert (bytes for W, elements for scales).
 extern "C" int spark_mx_gemv(const void* x, int ldx, const void* W, const void* scales, int fmt, long long w_expert_stride,
                              long long s_expert_stride, void* y, int ldy, int items, int rows_per_item, int N, int K,
                              const int* pair_expert, const int* pair_row, int act, float limit, int out_f32, cudaStream_t s) {
@@ -306,6 +317,7 @@ extern "C" int spark_mx_gemv(const void* x, int ldx, const void* W, const void* 
                                                   rows_per_item, N, K, pair_expert, pair_row, act, limit, s)
   if (fmt == 0) return out_f32 ? SPARK_MXV(0, float) : SPARK_MXV(0, __nv_bfloat16);
   if (fmt == 1) return out_f32 ? SPARK_MXV(1, float) : SPARK_MXV(1, __nv_bfloat16);
+  if (fmt == 2) return out_f32 ? SPARK_MXV(2, float) : SPARK_MXV(2, __nv_bfloat16);
 #undef SPARK_MXV
   return -5;
 }

@@ -37,6 +37,8 @@ class _DevInit:
         if fmt == "mx" and k % 128 == 0 and n % 128 == 0:
             if kind == "expert":
                 return Q.random_mxfp4(n, k, experts, self.std, self._seed(), self.device)
+            if experts == 0:        # dense projections: MXFP8 (E8M0 per 32), the block-scaled tensor-core operand format
+                return Q.random_mxfp8(n, k, self.std, self._seed(), self.device)
             return Q.random_fp8_block(n, k, experts, self.std, self._seed(), self.device)
         return self.mat(*(((experts,) if experts else ()) + (n, k)))
 

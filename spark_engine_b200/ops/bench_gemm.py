@@ -1,10 +1,11 @@
 """Throughput of the tcgen05 GEMM against torch.matmul (cuBLAS) on the same shapes.
 
-  python -m spark_engine_b200.ops.bench_gemm [--ncu-case]
+  python -m spark_engine_b200.ops.bench_gemm [--ncu-case] [--mx]
 
 CUDA-event timing, 3 warm-ups, operands rotated through copies larger than L2 for the small shapes.  Prints one JSON
 line per shape with TFLOP/s and the fraction of the measured bf16 peak (MEASURED_PEAKS.json when present).
-`--ncu-case` runs a single 8192x4096x4096 launch pair (the case captured under ncu)."""
+`--ncu-case` runs a single 8192x4096x4096 launch pair (the case captured under ncu).  `--mx` adds the block-scaled MXFP8
+GEMM (e4m3 operands, E8M0 scale per 32 along K, scales applied by the tensor core) on the same shapes."""
 from __future__ import annotations
 
 import json
@@ -46,6 +47,33 @@ def main():
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / iters
             res[name] = {"ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1)}
+        if "--mx" in sys.argv and K % 128 == 0:
+            from ..quant import formats as Q
+            from . import mx
+            wq = [Q.random_mxfp8(N, K, 0.02, i, dev) for i in range(ncopy)]
+            aq = [(torch.randn(M, K, device=dev) * 50).clamp(-448, 448).to(torch.float8_e4m3fn) for _ in range(ncopy)]
+            asf = torch.full((M, K // 32), 120, dtype=torch.uint8, device=dev)
+            ab = mx.sf_blocks(asf)
+            for w in wq:
+                w._sf_blocks = mx.sf_blocks(w.scales)
+            lib = mx._lib()
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+            def run_mx(i):
+                w = wq[i % ncopy]
+                lib.spark_gemm_mxfp8(cu.P(aq[i % ncopy]), cu.P(w.q), cu.P(ab), cu.P(w._sf_blocks), cu.P(out), M, N, K, K, K, N, 0,
+                                     cu.P(cu.status_word(torch.device(dev))), cu.stream())
+            iters = 1 if ncu_case else 20
+            for i in range(0 if ncu_case else 3):
+                run_mx(i)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(iters):
+                run_mx(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            res["tcgen05_mxfp8"] = {"ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1)}
         c = cu.gemm_bf16(a[0], b[0]).float()
         ref = torch.matmul(a[0], b[0].t()).float()
         print(json.dumps({"M": M, "N": N, "K": K, **res, "frac_of_measured_peak": round(res["tcgen05"]["tflops"] / peak, 3),

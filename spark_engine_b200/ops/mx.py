@@ -49,6 +49,8 @@ def _parts(w: QuantWeight):
         return q, w.scales, 0, w.n * w.k, (w.n // 128) * (w.k // 128)
     if isinstance(w, Mxfp4Weight):
         return w.packed, w.scales, 1, w.n * w.k // 2, w.n * (w.k // 32)
+    if isinstance(w, Mxfp8Weight):
+        return w.q.view(torch.uint8), w.scales, 2, w.n * w.k, w.n * (w.k // 32)
     raise TypeError(type(w))
 
 
@@ -137,6 +139,8 @@ def gemm_mxfp8(a_q, a_sf, w: Mxfp8Weight, out_f32=False):
 
 def quant_linear(x, w: QuantWeight):
     x = cu._as_bf16(x).contiguous()
+    if isinstance(w, Mxfp8Weight) and x.shape[0] <= 16:
+        return gemv(x, w)                 # decode rows: bf16 activations, weights decoded in the GEMV
     if isinstance(w, Mxfp8Weight):
         # activations are quantised to MXFP8 (1 x 32 E8M0 scales) and both operands go to the tensor core as they are
         a_q, a_sf = act_quant(x, block=32)

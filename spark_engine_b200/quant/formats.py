@@ -336,3 +336,12 @@ class Mxfp8Weight(QuantWeight):
 
     def nbytes(self):
         return self.q.numel() + self.scales.numel()
+
+
+def random_mxfp8(n, k, std=0.02, seed=0, device="cpu") -> Mxfp8Weight:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    q = (torch.randn(n, k, device=device, generator=g) * 100).clamp(-448, 448).to(torch.float8_e4m3fn)
+    e = int(round(math.log2(std / 100))) + 127
+    scales = torch.randint(e - 1, e + 1, (n, k // 32), dtype=torch.uint8, device=device, generator=g)
+    return Mxfp8Weight(q, scales)

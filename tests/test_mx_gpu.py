@@ -28,11 +28,14 @@ def _swiglu(gu, limit):
     return torch.nn.functional.silu(g) * u
 
 
-@pytest.mark.parametrize("fmt", ["fp8", "mxfp4"])
+@pytest.mark.parametrize("fmt", ["fp8", "mxfp4", "mxfp8"])
 @pytest.mark.parametrize("R", [1, 3, 4, 8, 13, 16])
 @pytest.mark.parametrize("N,K", [(256, 512), (1024, 2048)])
 def test_mx_gemv_matches_dequant_matmul(fmt, R, N, K):
-    w = (Q.random_fp8_block if fmt == "fp8" else Q.random_mxfp4)(N, K, 0, 0.02, 5, DEV)
+    if fmt == "mxfp8":
+        w = Q.random_mxfp8(N, K, 0.02, 5, DEV)
+    else:
+        w = (Q.random_fp8_block if fmt == "fp8" else Q.random_mxfp4)(N, K, 0, 0.02, 5, DEV)
     g = torch.Generator(device=DEV).manual_seed(2)
     x = torch.randn(R, K, device=DEV, generator=g).bfloat16()
     y = mx().gemv(x, w, out_f32=True)
@@ -123,16 +126,18 @@ def test_mx_model_matches_cpu_runner_on_the_same_weights():
         elif isinstance(n, QuantWeight):
             kinds.add(type(n).__name__)
     walk(W)
-    assert kinds == {"Fp8BlockWeight", "Mxfp4Weight"}
+    assert kinds == {"Mxfp8Weight", "Mxfp4Weight"}
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
     ref_m = Model(cfg, to_device(W, "cpu", torch.float32), n_slots=1, kv_tokens=128)
     ref = ref_m.forward(make_plan([(0, ids, 0)]))
     m = Model(cfg, W, device=DEV, dtype=torch.bfloat16, n_slots=1, kv_tokens=128)
     lg = m.forward(make_plan([(0, ids[:32], 0)], device=DEV)).float().cpu()          # prefill rows (GEMM path)
-    assert rel_err(lg, ref[:32]) < 4e-2
+    # prefill quantises the activations of the dense projections to MXFP8 (3 mantissa bits) for the block-scaled
+    # tensor-core GEMM, as the reference's FP8 prefill does; decode rows keep bf16 activations
+    assert rel_err(lg, ref[:32]) < 0.12, rel_err(lg, ref[:32])
     rows = [m.forward(make_plan([(0, [ids[t]], t)], device=DEV)).float().cpu()[0] for t in range(32, 40)]   # GEMV path
-    assert rel_err(torch.stack(rows), ref[32:]) < 4e-2
+    assert rel_err(torch.stack(rows), ref[32:]) < 0.12, rel_err(torch.stack(rows), ref[32:])
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 128, 512), (256, 384, 1024), (77, 200, 256), (1000, 640, 2048)])
