@@ -346,3 +346,138 @@ extern "C" int spark_act_quant(const void* x, int ldx, int in_f32, void* q, void
 #undef SPARK_AQ
   return spark_launch_rc(__func__);
 }
+
+// ------------------------------------------------------------------------------------------ grouped MXFP4 GEMM
+// Prefill-size MoE over MXFP4 experts: rows in expert order, <= 64 rows per work item (a half of a 128-row tile of
+// the MoE sort).  The packed expert weights cross HBM once (0.5 byte per weight + scales) and go straight into MMA
+// fragments, exactly like the decode GEMV, but every decoded fragment now feeds up to four 16-row tiles; the
+// activations of the item (bf16 -> fp16, optional SwiGLU of a [gate | up] input) are staged per 512-deep K chunk and
+// shared by the 8 warps of the CTA, each of which owns 16 output columns for the whole K (no cross-warp reduction:
+// one fixed summation order per output).  Grid (N/128, 2 * tiles).
+namespace spark {
+
+constexpr int MXG_KC = 512;        // K chunk staged in shared memory
+constexpr int MXG_ROWS = 64;
+
+__global__ void __launch_bounds__(256, 2)
+mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __restrict__ W, const uint8_t* __restrict__ scales,
+                long long w_expert_stride, long long s_expert_stride, const int4* __restrict__ tiles,
+                const int* __restrict__ ntile, void* __restrict__ y, int ldy, int out_f32, int N, int K, int act, float limit) {
+  const int tile = blockIdx.y >> 1, half = blockIdx.y & 1;
+  if (tile >= *ntile) return;
+  const int4 td = tiles[tile];
+  const int row0 = td.x + half * MXG_ROWS;
+  const int nrows = min(min(td.x + 128, td.y) - row0, MXG_ROWS);
+  if (nrows <= 0) return;
+  const int e = td.z;
+  constexpr int XS = MXG_KC + 8;
+  extern __shared__ __align__(16) uint8_t smem_mg[];
+  __half* xs = reinterpret_cast<__half*>(smem_mg);              // [64][XS]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int mts = (nrows + 15) >> 4;
+  const int n0 = blockIdx.x * 128 + warp * 16;
+  const size_t row_bytes = K >> 1;
+  const uint8_t* w_lo = W + static_cast<size_t>(e) * w_expert_stride + static_cast<size_t>(n0 + g) * row_bytes + t * 16;
+  const uint8_t* w_hi = w_lo + 8 * row_bytes;
+  const uint8_t* sc_lo = scales + static_cast<size_t>(e) * s_expert_stride + static_cast<size_t>(n0 + g) * (K >> 5) + t;
+  const uint8_t* sc_hi = sc_lo + 8 * (K >> 5);
+  float acc[4][2][4];
+#pragma unroll
+  for (int m = 0; m < 4; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { acc[m][0][j] = 0.f; acc[m][1][j] = 0.f; }
+  constexpr int IPC = MXG_KC / 128;                // warp iterations per chunk (128 k each)
+  for (int k0 = 0; k0 < K; k0 += MXG_KC) {
+    // this chunk's packed weights are requested before the activations are staged
+    uint4 wl[IPC], wh[IPC];
+    uint8_t sl[IPC], sh[IPC];
+#pragma unroll
+    for (int u = 0; u < IPC; ++u) {
+      const int it = (k0 >> 7) + u;
+      if (k0 + u * 128 < K) {
+        wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + static_cast<size_t>(it) * 64));
+        wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + static_cast<size_t>(it) * 64));
+        sl[u] = __ldg(sc_lo + it * 4); sh[u] = __ldg(sc_hi + it * 4);
+      }
+    }
+    __syncthreads();                                // previous chunk fully consumed
+    const int kc = min(MXG_KC, K - k0);
+    for (int i = threadIdx.x; i < mts * 16 * (kc >> 1); i += 256) {
+      const int r = i / (kc >> 1), k = (i - r * (kc >> 1)) * 2;
+      float v0 = 0.f, v1 = 0.f;
+      if (r < nrows) {
+        const __nv_bfloat16* xr = x + static_cast<size_t>(row0 + r) * ldx + k0;
+        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
+        if (act == 0) { v0 = gg.x; v1 = gg.y; }
+        else {
+          const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + K + k));
+          float g0 = gg.x, g1 = gg.y, u0 = uu.x, u1 = uu.y;
+          if (limit > 0.f) {
+            g0 = fminf(g0, limit); g1 = fminf(g1, limit);
+            u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
+          }
+          v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
+        }
+      }
+      *reinterpret_cast<__half2*>(xs + r * XS + k) = __floats2half2_rn(v0, v1);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < IPC; ++u) {
+      if (k0 + u * 128 >= K) break;
+      const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
+      const uint32_t* ph = reinterpret_cast<const uint32_t*>(&wh[u]);
+      const __half2 hl = e8m0_h2(sl[u]), hh = e8m0_h2(sh[u]);
+      const __half* xk = xs + g * XS + u * 128 + t * 32;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
+        const uint32_t b0l = fp4x2_to_h2(static_cast<uint8_t>(vl & 0xffu), hl), b1l = fp4x2_to_h2(static_cast<uint8_t>((vl >> 8) & 0xffu), hl);
+        const uint32_t b0h = fp4x2_to_h2(static_cast<uint8_t>(vh & 0xffu), hh), b1h = fp4x2_to_h2(static_cast<uint8_t>((vh >> 8) & 0xffu), hh);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          if (m < mts) {
+            const uint2 av = *reinterpret_cast<const uint2*>(xk + (m * 16) * XS + s * 4);
+            const uint2 bv = *reinterpret_cast<const uint2*>(xk + (m * 16 + 8) * XS + s * 4);
+            mma16816(acc[m][0], av.x, bv.x, av.y, bv.y, b0l, b1l);
+            mma16816(acc[m][1], av.x, bv.x, av.y, bv.y, b0h, b1h);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    if (m >= mts) break;
+#pragma unroll
+    for (int hh2 = 0; hh2 < 2; ++hh2) {
+      const int r = m * 16 + g + hh2 * 8;
+      if (r >= nrows) continue;
+      const size_t o = static_cast<size_t>(row0 + r) * ldy + n0 + 2 * t;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const float v0 = acc[m][nt][2 * hh2], v1 = acc[m][nt][2 * hh2 + 1];
+        if (out_f32) *reinterpret_cast<float2*>(reinterpret_cast<float*>(y) + o + nt * 8) = make_float2(v0, v1);
+        else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + o + nt * 8) = __floats2bfloat162_rn(v0, v1);
+      }
+    }
+  }
+}
+
+}  // namespace spark
+
+// MXFP4 experts, rows in expert order; tiles = the 128-row tile list of the MoE sort (max_tiles allocated, *ntile valid).
+// x bf16 [P, K] (act 0) or [P, 2K] = [gate | up] (act 1); y [P, N] bf16 or fp32.  N % 128 == 0, K % 128 == 0.
+extern "C" int spark_mx_mgemm(const void* x, int ldx, const void* W, const void* scales, long long w_expert_stride,
+                              long long s_expert_stride, const void* tiles, const int* ntile, int max_tiles, void* y, int ldy,
+                              int out_f32, int N, int K, int act, float limit, cudaStream_t s) {
+  if (max_tiles <= 0) return 0;
+  if (N % 128 || K % 128 || (ldx & 1) || (ldy & 1)) return -5;
+  constexpr int smem = spark::MXG_ROWS * (spark::MXG_KC + 8) * 2;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(spark::mx_mgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
+  spark::mx_mgemm_kernel<<<dim3(N / 128, 2 * max_tiles), 256, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W,
+                                                                     (const uint8_t*)scales, w_expert_stride, s_expert_stride,
+                                                                     (const int4*)tiles, ntile, y, ldy, out_f32, N, K, act, limit);
+  return spark_launch_rc(__func__);
+}

@@ -10,6 +10,7 @@ fp8.cu / fp8ws.cu, engine-rs/src/ds41/load.rs:116-160.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -25,6 +26,7 @@ _SIGS = {
     "spark_act_quant": [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "spark_gemm_mxfp8": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp],
     "spark_mx_sf_to_blocks": [_vp, _vp, _i32, _i32, _vp],
+    "spark_mx_mgemm": [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
 }
 _bound = False
@@ -160,10 +162,29 @@ def expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
                 out_f32=out_f32)
 
 
+MX_MOE_FUSED = os.environ.get("SPARK_MX_MOE_FUSED", "1") == "1"
+
+
+def mx_mgemm(x, w: Mxfp4Weight, tiles, ntile, max_tiles, act=0, limit=0.0, out_f32=False):
+    """Rows in expert order x packed MXFP4 experts -> [P, N] (fused decode, <= 64 rows per work item)."""
+    Pn = x.shape[0]
+    y = torch.empty(Pn, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    rc = _lib().spark_mx_mgemm(cu.P(x), x.stride(0), cu.P(w.packed), cu.P(w.scales), w.n * w.k // 2, w.n * (w.k // 32),
+                               cu.P(tiles), cu.P(ntile), max_tiles, cu.P(y), w.n, int(out_f32), w.n, w.k, act, float(limit),
+                               cu.stream())
+    cu.check(rc, "spark_mx_mgemm")
+    return y
+
+
 def grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
-    """Rows in expert order through gate/up (+SwiGLU epilogue) and down; returns fp32 [P, H]."""
+    """Rows in expert order through gate/up (+SwiGLU) and down; returns fp32 [P, H]."""
     E, F2, H = wgu.packed.shape[0] if isinstance(wgu, Mxfp4Weight) else wgu.q.shape[0], wgu.n, wgu.k
     dev = a.device
+    if MX_MOE_FUSED and isinstance(wgu, Mxfp4Weight) and F2 % 128 == 0 and H % 128 == 0 and a.shape[0] <= 512 * E:
+        # packed experts straight into the MMA: the weights cross HBM once, SwiGLU is applied while the down
+        # projection stages its input
+        gu = mx_mgemm(cu._as_bf16(a).contiguous(), wgu, tiles, ntile, max_tiles)
+        return mx_mgemm(gu, wd, tiles, ntile, max_tiles, act=1, limit=c.swiglu_limit, out_f32=True)
     wt = dequant_bf16(wgu, cu.scratch("mx_deq_gu", E * F2 * H, torch.bfloat16, dev))
     act = cu.grouped_gemm(a, wt.view(E * F2, H), tiles, ntile, max_tiles, E, F2, F2 // 2, 1, c.swiglu_limit)
     wt2 = dequant_bf16(wd, cu.scratch("mx_deq_d", E * H * (F2 // 2), torch.bfloat16, dev))

@@ -82,3 +82,28 @@ def test_exl3_prefill_experts_fused_kernel_vs_reconstruct_path(H, F, R):
         err = ((o.float().cpu() - ref).norm() / ref.norm()).item()
         assert err < 2e-2, err
     assert ((outs[0].float() - outs[1].float()).norm() / outs[1].float().norm()).item() < 1e-2
+
+
+@pytest.mark.parametrize("H,F,R", [(512, 256, 300), (1024, 128, 77), (256, 384, 40)])
+def test_mxfp4_prefill_experts_fused_kernel_vs_dequant_path(H, F, R):
+    """Fused grouped MXFP4 kernel (packed experts -> MMA fragments) against the dequantise + tcgen05 path and the
+    fp32 reference."""
+    from spark_engine_b200.ops import mx
+    g = torch.Generator(device=DEV).manual_seed(6)
+    c = MoeConfig(n_experts=16, top_k=4, ffn=F, router="sqrt_softplus", route_scale=1.5, swiglu_limit=10.0, n_shared=0)
+    w = {"gate": (torch.randn(16, H, device=DEV, generator=g) * 0.1).bfloat16(), "bias": torch.zeros(16, device=DEV),
+         "w_gu": Q.random_mxfp4(2 * F, H, 16, 0.05, 1, DEV), "w_down": Q.random_mxfp4(H, F, 16, 0.05, 2, DEV)}
+    h = torch.randn(R, H, device=DEV, generator=g).bfloat16()
+    outs = []
+    for fused in (True, False):
+        mx.MX_MOE_FUSED = fused
+        try:
+            outs.append(ops.moe(h, w, c))
+            if fused:
+                assert torch.equal(outs[0], ops.moe(h, w, c))
+        finally:
+            mx.MX_MOE_FUSED = True
+    ref = _ref(h, w, c)
+    for o in outs:
+        err = ((o.float().cpu() - ref).norm() / ref.norm()).item()
+        assert err < 2e-2, err
