@@ -269,27 +269,45 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   }
 }
 
-// grid (R, H); 128 threads.  Splits merged in ascending order; `sink` (per head, optional) joins the denominator.
-__global__ void __launch_bounds__(128)
+// grid R; 256 threads.  Splits merged in ascending order; `sink` (per head, optional) joins the denominator.
+// One CTA per row: the per-head weights of the splits are computed once into shared memory, then the threads sweep
+// the row's H x L outputs with 16-byte loads.
+__global__ void __launch_bounds__(256)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, const float* __restrict__ sink,
                  int H, int L, __nv_bfloat16* __restrict__ out) {
-  const int r = blockIdx.x, h = blockIdx.y;
-  const size_t pb = (static_cast<size_t>(r) * H + h) * nsplit;
-  float M = sink ? sink[h] : -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(pb + s) * 2]);
-  float l = sink ? __expf(sink[h] - M) : 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float m = part_ml[(pb + s) * 2];
-    if (m != -INFINITY) l += __expf(m - M) * part_ml[(pb + s) * 2 + 1];
-  }
-  const float inv = 1.f / l;
-  for (int d = threadIdx.x; d < L; d += 128) {
-    float o = 0.f;
+  extern __shared__ float wts[];                        // [H][nsplit]: exp(m_s - M) / l
+  const int r = blockIdx.x;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const size_t pb = (static_cast<size_t>(r) * H + h) * nsplit;
+    float M = sink ? sink[h] : -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(pb + s) * 2]);
+    float l = sink ? __expf(sink[h] - M) : 0.f;
     for (int s = 0; s < nsplit; ++s) {
       const float m = part_ml[(pb + s) * 2];
-      if (m != -INFINITY) o += __expf(m - M) * part_o[(pb + s) * L + d];
+      if (m != -INFINITY) l += __expf(m - M) * part_ml[(pb + s) * 2 + 1];
     }
-    out[(static_cast<size_t>(r) * H + h) * L + d] = __float2bfloat16(o * inv);
+    const float inv = 1.f / l;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = part_ml[(pb + s) * 2];
+      wts[h * nsplit + s] = m != -INFINITY ? __expf(m - M) * inv : 0.f;
+    }
+  }
+  __syncthreads();
+  const int L4 = L >> 2;
+  for (int i = threadIdx.x; i < H * L4; i += blockDim.x) {
+    const int h = i / L4, d = (i - h * L4) * 4;
+    const size_t pb = (static_cast<size_t>(r) * H + h) * nsplit;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < nsplit; ++s) {
+      const float w = wts[h * nsplit + s];
+      if (w != 0.f) {
+        const float4 p = *reinterpret_cast<const float4*>(part_o + (pb + s) * L + d);
+        o.x = fmaf(w, p.x, o.x); o.y = fmaf(w, p.y, o.y); o.z = fmaf(w, p.z, o.z); o.w = fmaf(w, p.w, o.w);
+      }
+    }
+    const __nv_bfloat162 b0 = __floats2bfloat162_rn(o.x, o.y), b1 = __floats2bfloat162_rn(o.z, o.w);
+    uint2 ov; ov.x = *reinterpret_cast<const uint32_t*>(&b0); ov.y = *reinterpret_cast<const uint32_t*>(&b1);
+    *reinterpret_cast<uint2*>(out + (static_cast<size_t>(r) * H + h) * L + d) = ov;
   }
 }
 
@@ -336,6 +354,7 @@ extern "C" int spark_mla_attn(const void* q_full, const void* lat, const int* po
   if (!done[id]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done[id] = true; }
   kern<<<dim3(R, nsplit), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv, sel, sel_n, sel_ld,
                                           part_o, part_ml, H, KW, kv_lora, scale);
-  mla_merge_kernel<<<dim3(R, H), 128, 0, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, (__nv_bfloat16*)out);
+  if (H * nsplit * 4 > 48 * 1024) return -6;
+  mla_merge_kernel<<<R, 256, H * nsplit * 4, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, (__nv_bfloat16*)out);
   return spark_launch_rc(__func__);
 }

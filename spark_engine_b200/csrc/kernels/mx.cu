@@ -370,7 +370,11 @@ mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __r
   const int nrows = min(min(td.x + 128, td.y) - row0, MXG_ROWS);
   if (nrows <= 0) return;
   const int e = td.z;
-  constexpr int XS = MXG_KC + 8;
+  // Activation layout in shared memory: inside every 128-k block the four lanes' 32-k runs are interleaved in groups
+  // of four elements (element k sits at ((k % 32) / 4) * 16 + (k / 32) * 4 + k % 4), so that the 8-byte fragment
+  // loads of a k-step are contiguous over the lane quad; with rows 32 bytes (mod 128) apart a warp's 32 loads
+  // cover 256 bytes in the minimum of two shared-memory wavefronts.
+  constexpr int XS = MXG_KC + 16;
   extern __shared__ __align__(16) uint8_t smem_mg[];
   __half* xs = reinterpret_cast<__half*>(smem_mg);              // [64][XS]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -419,7 +423,9 @@ mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __r
           v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
         }
       }
-      *reinterpret_cast<__half2*>(xs + r * XS + k) = __floats2half2_rn(v0, v1);
+      const int kk = k & 127;
+      *reinterpret_cast<__half2*>(xs + r * XS + (k - kk) + ((kk & 31) >> 2) * 16 + (kk >> 5) * 4 + (kk & 3)) =
+          __floats2half2_rn(v0, v1);
     }
     __syncthreads();
 #pragma unroll
@@ -428,7 +434,7 @@ mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __r
       const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
       const uint32_t* ph = reinterpret_cast<const uint32_t*>(&wh[u]);
       const __half2 hl = e8m0_h2(sl[u]), hh = e8m0_h2(sh[u]);
-      const __half* xk = xs + g * XS + u * 128 + t * 32;
+      const __half* xk = xs + g * XS + u * 128 + t * 4;
 #pragma unroll
       for (int s = 0; s < 8; ++s) {
         const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
@@ -437,8 +443,8 @@ mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __r
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           if (m < mts) {
-            const uint2 av = *reinterpret_cast<const uint2*>(xk + (m * 16) * XS + s * 4);
-            const uint2 bv = *reinterpret_cast<const uint2*>(xk + (m * 16 + 8) * XS + s * 4);
+            const uint2 av = *reinterpret_cast<const uint2*>(xk + (m * 16) * XS + s * 16);
+            const uint2 bv = *reinterpret_cast<const uint2*>(xk + (m * 16 + 8) * XS + s * 16);
             mma16816(acc[m][0], av.x, bv.x, av.y, bv.y, b0l, b1l);
             mma16816(acc[m][1], av.x, bv.x, av.y, bv.y, b0h, b1h);
           }
@@ -473,7 +479,7 @@ extern "C" int spark_mx_mgemm(const void* x, int ldx, const void* W, const void*
                               int out_f32, int N, int K, int act, float limit, cudaStream_t s) {
   if (max_tiles <= 0) return 0;
   if (N % 128 || K % 128 || (ldx & 1) || (ldy & 1)) return -5;
-  constexpr int smem = spark::MXG_ROWS * (spark::MXG_KC + 8) * 2;
+  constexpr int smem = spark::MXG_ROWS * (spark::MXG_KC + 16) * 2;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(spark::mx_mgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   spark::mx_mgemm_kernel<<<dim3(N / 128, 2 * max_tiles), 256, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W,

@@ -238,8 +238,13 @@ def ngram_embed(model, X, plan, w):
     from ..models.ngram import ngram_rows_for_plan
     cfg = model.cfg
     emb = ngram_rows_for_plan(model, plan)                   # [R, heads*dim] fp32 on X.device
-    key = L.rms(emb @ w["key"].float().t(), w["norm_k"].float(), cfg.norm_eps)
-    val = emb @ w["value"].float().t()
+    if use_kernels(X):                                       # the two projections on the GEMV / tcgen05 GEMM kernels
+        eb = emb.to(torch.bfloat16)
+        key = L.rms(linear(eb, w["key"]).float(), w["norm_k"].float(), cfg.norm_eps)
+        val = linear(eb, w["value"]).float()
+    else:
+        key = L.rms(emb @ w["key"].float().t(), w["norm_k"].float(), cfg.norm_eps)
+        val = emb @ w["value"].float().t()
     d = (key * L.rms(X.float(), w["norm_q"].float(), cfg.norm_eps)).sum(-1, keepdim=True) / math.sqrt(X.shape[-1])
     gate = torch.sigmoid(torch.sign(d) * torch.sqrt(d.abs().clamp_min(cfg.norm_eps)))
     return (X.float() + gate * val).to(X.dtype)
