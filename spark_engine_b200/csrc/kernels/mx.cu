@@ -406,26 +406,51 @@ mx_mgemm_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __r
     }
     __syncthreads();                                // previous chunk fully consumed
     const int kc = min(MXG_KC, K - k0);
-    for (int i = threadIdx.x; i < mts * 16 * (kc >> 1); i += 256) {
-      const int r = i / (kc >> 1), k = (i - r * (kc >> 1)) * 2;
-      float v0 = 0.f, v1 = 0.f;
-      if (r < nrows) {
-        const __nv_bfloat16* xr = x + static_cast<size_t>(row0 + r) * ldx + k0;
-        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
-        if (act == 0) { v0 = gg.x; v1 = gg.y; }
-        else {
-          const float2 uu = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + K + k));
-          float g0 = gg.x, g1 = gg.y, u0 = uu.x, u1 = uu.y;
-          if (limit > 0.f) {
-            g0 = fminf(g0, limit); g1 = fminf(g1, limit);
-            u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
+    // stage the chunk: 16-byte loads, four in flight per thread before any is converted (the loads come from L2 and
+    // a dependent load-convert-store chain would leave the CTA waiting on latency)
+    const int vpr = kc >> 3, total = mts * 16 * vpr;
+    for (int base = threadIdx.x; base < total; base += 256 * 4) {
+      uint4 gv[4], uv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = base + j * 256;
+        gv[j] = make_uint4(0u, 0u, 0u, 0u); uv[j] = gv[j];
+        if (i < total) {
+          const int r = i / vpr, k = (i - r * vpr) * 8;
+          if (r < nrows) {
+            const __nv_bfloat16* xr = x + static_cast<size_t>(row0 + r) * ldx + k0 + k;
+            gv[j] = *reinterpret_cast<const uint4*>(xr);
+            if (act) uv[j] = *reinterpret_cast<const uint4*>(xr + K);
           }
-          v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
         }
       }
-      const int kk = k & 127;
-      *reinterpret_cast<__half2*>(xs + r * XS + (k - kk) + ((kk & 31) >> 2) * 16 + (kk >> 5) * 4 + (kk & 3)) =
-          __floats2half2_rn(v0, v1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = base + j * 256;
+        if (i >= total) break;
+        const int r = i / vpr, k = (i - r * vpr) * 8;
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv[j]);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv[j]);
+        __half2 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float2 gg = __bfloat1622float2(gp[q]);
+          if (act) {
+            float2 uu = __bfloat1622float2(up[q]);
+            if (limit > 0.f) {
+              gg.x = fminf(gg.x, limit); gg.y = fminf(gg.y, limit);
+              uu.x = fminf(fmaxf(uu.x, -limit), limit); uu.y = fminf(fmaxf(uu.y, -limit), limit);
+            }
+            gg.x = gg.x / (1.f + __expf(-gg.x)) * uu.x; gg.y = gg.y / (1.f + __expf(-gg.y)) * uu.y;
+          }
+          h[q] = __floats2half2_rn(gg.x, gg.y);
+        }
+        // elements k..k+3 and k+4..k+7 are two consecutive 4-groups of one lane's 32-k run
+        const int kk = k & 127;
+        __half* dst = xs + r * XS + (k - kk) + ((kk & 31) >> 2) * 16 + (kk >> 5) * 4;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&h[0]), *reinterpret_cast<uint32_t*>(&h[1]));
+        *reinterpret_cast<uint2*>(dst + 16) = make_uint2(*reinterpret_cast<uint32_t*>(&h[2]), *reinterpret_cast<uint32_t*>(&h[3]));
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -478,7 +503,7 @@ extern "C" int spark_mx_mgemm(const void* x, int ldx, const void* W, const void*
                               long long s_expert_stride, const void* tiles, const int* ntile, int max_tiles, void* y, int ldy,
                               int out_f32, int N, int K, int act, float limit, cudaStream_t s) {
   if (max_tiles <= 0) return 0;
-  if (N % 128 || K % 128 || (ldx & 1) || (ldy & 1)) return -5;
+  if (N % 128 || K % 128 || (ldx & 7) || (ldy & 1)) return -5;
   constexpr int smem = spark::MXG_ROWS * (spark::MXG_KC + 16) * 2;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(spark::mx_mgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
