@@ -145,7 +145,7 @@ __device__ __forceinline__ void mla_mma(float (&c)[4], const uint32_t (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (R, nsplit); 256 threads.  HM = 16-head MMA tiles (H <= 16*HM).  KW = kv_lora + rope (multiple of 16),
+// grid (R, ceil(nsplit / spc)); 256 threads; a CTA walks `spc` consecutive splits.  HM = 16-head MMA tiles (H <= 16*HM).  KW = kv_lora + rope (multiple of 16),
 // L = kv_lora (multiple of 16).
 template <int HM>
 __global__ void __launch_bounds__(256)
@@ -154,7 +154,7 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
                   const int* __restrict__ pos, const long long* __restrict__ row_kv, const int* __restrict__ sel,
                   const int* __restrict__ sel_n, int sel_ld, float* __restrict__ part_o,   // [R, H, nsplit, L]
                   float* __restrict__ part_ml,                   // [R, H, nsplit, 2]
-                  int H, int KW, int L, float scale) {
+                  int H, int KW, int L, float scale, int nsplit, int spc) {
   extern __shared__ __align__(16) uint8_t smem_mla[];
   const int LDK = KW + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_mla);          // [HM*16][LDK]
@@ -162,9 +162,18 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   float* Ss = reinterpret_cast<float*>(Ls + MLA_TS * LDK);                  // [HM*16][65]
   __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + HM * 16 * 65);  // [HM*16][72]
   __shared__ int stok[MLA_TS];
-  const int r = blockIdx.x, sp = blockIdx.y, nsplit = gridDim.y;
+  const int r = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n_ctx = sel ? sel_n[r] : pos[r] + 1;
+  const long long base = row_kv[r];
+  const int VPR = KW >> 3;
+  // the row's queries (all heads) are staged once and serve every split this CTA walks through
+  for (int i = tid; i < HM * 16 * VPR; i += 256) {
+    const int h = i / VPR, v = i - h * VPR;
+    if (h < H) mla_cp16(Qs + h * LDK + v * 8, q_full + (static_cast<size_t>(r) * H + h) * KW + v * 8);
+    else *reinterpret_cast<uint4*>(Qs + h * LDK + v * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int sp = blockIdx.y * spc; sp < min(nsplit, (blockIdx.y + 1) * spc); ++sp) {
   const int t0 = sp * MLA_TS;
   const size_t pb = (static_cast<size_t>(r) * H) * nsplit + sp;
   if (t0 >= n_ctx) {                                           // empty split: neutral partial
@@ -172,18 +181,12 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
       part_ml[(pb + static_cast<size_t>(h) * nsplit) * 2] = -INFINITY;
       part_ml[(pb + static_cast<size_t>(h) * nsplit) * 2 + 1] = 0.f;
     }
-    return;
+    continue;
   }
   const int nt = min(MLA_TS, n_ctx - t0);
-  const long long base = row_kv[r];
+  __syncthreads();                                             // the previous split's tiles are no longer read
   if (tid < MLA_TS) stok[tid] = tid < nt ? (sel ? sel[static_cast<size_t>(r) * sel_ld + t0 + tid] : t0 + tid) : -1;
   __syncthreads();
-  const int VPR = KW >> 3;
-  for (int i = tid; i < HM * 16 * VPR; i += 256) {
-    const int h = i / VPR, v = i - h * VPR;
-    if (h < H) mla_cp16(Qs + h * LDK + v * 8, q_full + (static_cast<size_t>(r) * H + h) * KW + v * 8);
-    else *reinterpret_cast<uint4*>(Qs + h * LDK + v * 8) = make_uint4(0u, 0u, 0u, 0u);
-  }
   for (int i = tid; i < MLA_TS * VPR; i += 256) {
     const int k = i / VPR, v = i - k * VPR;
     if (stok[k] >= 0) mla_cp16(Ls + k * LDK + v * 8, lat + (base + stok[k]) * KW + v * 8);
@@ -267,6 +270,8 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
       }
     }
   }
+  }   // splits of this CTA
+  asm volatile("cp.async.wait_all;" ::: "memory");               // the query copy, if every split was empty
 }
 
 // grid R; 256 threads.  Splits merged in ascending order; `sink` (per head, optional) joins the denominator.
@@ -348,12 +353,14 @@ extern "C" int spark_mla_attn(const void* q_full, const void* lat, const int* po
   const int smem = (HM * 16 + MLA_TS) * (KW + 8) * 2 + HM * 16 * 65 * 4 + HM * 16 * 72 * 2;
   if (smem > 200 * 1024) return -6;
   void (*kern)(const __nv_bfloat16*, const __nv_bfloat16*, const int*, const long long*, const int*, const int*, int, float*,
-               float*, int, int, int, float) = HM == 1 ? mla_decode_kernel<1> : (HM == 2 ? mla_decode_kernel<2> : mla_decode_kernel<4>);
+               float*, int, int, int, float, int, int) = HM == 1 ? mla_decode_kernel<1> : (HM == 2 ? mla_decode_kernel<2> : mla_decode_kernel<4>);
   static bool done[3] = {false, false, false};
   const int id = HM == 1 ? 0 : (HM == 2 ? 1 : 2);
   if (!done[id]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done[id] = true; }
-  kern<<<dim3(R, nsplit), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv, sel, sel_n, sel_ld,
-                                          part_o, part_ml, H, KW, kv_lora, scale);
+  // few rows (decode): one split per CTA for parallelism; many rows (prefill): a CTA per row walks all its splits
+  const int spc = R >= 128 ? nsplit : (R >= 32 ? 4 : 1);
+  kern<<<dim3(R, (nsplit + spc - 1) / spc), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv,
+                                                            sel, sel_n, sel_ld, part_o, part_ml, H, KW, kv_lora, scale, nsplit, spc);
   if (H * nsplit * 4 > 48 * 1024) return -6;
   mla_merge_kernel<<<R, 256, H * nsplit * 4, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, (__nv_bfloat16*)out);
   return spark_launch_rc(__func__);
