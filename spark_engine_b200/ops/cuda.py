@@ -141,9 +141,10 @@ _retired = []
 
 def status_word(device) -> torch.Tensor:
     """int32[4] device status: kernels whose bounded waits run out write {code, detail...} here."""
-    key = str(device)
+    d = torch.device(device)
+    key = d.index if d.index is not None else torch.cuda.current_device()     # "cuda" and "cuda:0" are one word
     if key not in _status:
-        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]
 
 
