@@ -108,8 +108,7 @@ class GdnMixer:
         return q, k, v
 
     def forward(self, h, plan: Plan, seqs, commit: bool):
-        proj = ops.linear(h, self.w["in"])
-        ab = ops.linear(h, self.w["ab"])
+        proj, ab = ops.linear_pair(h, self.w["in"], self.w["ab"])
         fast = ops.gdn_mixer(self, proj, ab, plan, commit)
         if fast is not None:
             o = fast
@@ -199,8 +198,7 @@ class KdaMixer:
         return o.reshape(T, n), S, tail
 
     def forward(self, h, plan: Plan, seqs, commit: bool):
-        pre = ops.linear(h, self.w["in"])
-        lr = ops.linear(h, self.w["lr_a"])
+        pre, lr = ops.linear_pair(h, self.w["in"], self.w["lr_a"])
         fast = ops.kda_mixer(self, pre, lr, plan, commit)
         if fast is not None:
             o = fast

@@ -79,6 +79,22 @@ def linear(x: torch.Tensor, w) -> torch.Tensor:
     return x @ w.to(x.dtype).t()
 
 
+def linear_pair(x, w_a, w_b):
+    """Two independent projections of the same rows.  On the device, decode-size batches run the second one on a
+    side stream next to the first (parallel branches of the captured graph)."""
+    if use_kernels(x) and x.shape[0] <= 16 and cuda_ops().SIDE_STREAMS:
+        c = cuda_ops()
+        main = torch.cuda.current_stream()
+        side = c._side_stream(x.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            b = linear(x, w_b)
+        a = linear(x, w_a)
+        main.wait_stream(side)
+        return a, b
+    return linear(x, w_a), linear(x, w_b)
+
+
 def rmsnorm(x, w, eps):
     if use_kernels(x):
         return cuda_ops().rmsnorm(x, w, eps)

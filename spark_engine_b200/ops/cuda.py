@@ -436,6 +436,17 @@ def grouped_gemm(a, b, tiles, ntile, max_tiles, n_experts, rows_per_expert, N, m
 DECODE_PAIRS_MAX = 256
 
 
+SIDE_STREAMS = os.environ.get("SPARK_SIDE_STREAMS", "1") == "1"
+_side = {}
+
+
+def _side_stream(device) -> torch.cuda.Stream:
+    key = torch.device(device).index
+    if key not in _side:
+        _side[key] = torch.cuda.Stream(device=device)
+    return _side[key]
+
+
 def moe(h, w, c):
     """Routed + shared experts; returns the bf16 block output [R, H].  Under expert parallelism (`w["ep"]` =
     (first local expert, end)) only the local experts' pairs are computed and the result is this rank's partial
@@ -448,17 +459,25 @@ def moe(h, w, c):
     Pn = R * c.top_k
     wgu, wd = w["w_gu"], w["w_down"]
     shared = None
+    side = None
     if "s_gu" in w:
         if R <= 16:
+            # decode rows: the shared expert's two GEMVs do not depend on the router, so they run on a side stream
+            # next to the routed experts (a fork/join that a captured graph keeps as parallel branches)
             sgu = w["s_gu"]
-            if isinstance(sgu, Exl3Weight):
-                gu = exl3_gemv(h, sgu)
-                shared = exl3_gemv(gu, w["s_down"], act=1, limit=c.swiglu_limit)
-            elif isinstance(sgu, QuantWeight):
-                shared = quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
-            else:
-                gu = gemv_bf16(h, sgu)
-                shared = gemv_bf16(gu, w["s_down"], act=1, limit=c.swiglu_limit, k=w["s_down"].shape[1])
+            main = torch.cuda.current_stream()
+            side = _side_stream(dev) if SIDE_STREAMS else None
+            if side is not None:
+                side.wait_stream(main)
+            with torch.cuda.stream(side if side is not None else main):
+                if isinstance(sgu, Exl3Weight):
+                    gu_s = exl3_gemv(h, sgu)
+                    shared = exl3_gemv(gu_s, w["s_down"], act=1, limit=c.swiglu_limit)
+                elif isinstance(sgu, QuantWeight):
+                    shared = quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
+                else:
+                    gu_s = gemv_bf16(h, sgu)
+                    shared = gemv_bf16(gu_s, w["s_down"], act=1, limit=c.swiglu_limit, k=w["s_down"].shape[1])
         else:
             shared = linear_any(swiglu(linear_any(h, w["s_gu"]), c.swiglu_limit), w["s_down"])
     out = torch.empty(R, H, dtype=torch.bfloat16, device=dev)
@@ -481,6 +500,8 @@ def moe(h, w, c):
             E, F2, K = wgu.shape
             act = grouped_gemm(a, wgu.view(E * F2, K), tiles, ntile, max_tiles, E, F2, F2 // 2, 1, c.swiglu_limit)
             y = grouped_gemm(act, wd.view(E * H, F2 // 2), tiles, ntile, max_tiles, E, H, H, 0)
+    if side is not None:
+        torch.cuda.current_stream().wait_stream(side)          # join: the combine reads the shared expert's output
     rc = lib().spark_moe_combine(None, P(y), int(y.dtype == torch.float32), P(inv), P(wts), R, c.top_k, P(shared), P(sg), H,
                                  P(out), stream(), P(ids) if ep else None)
     check(rc, "spark_moe_combine")
