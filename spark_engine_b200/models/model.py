@@ -67,6 +67,28 @@ class GdnMixer:
         self.S[slot].zero_()
         self.tail[slot].zero_()
 
+    # The kernels keep the conv history per value head ([3, Hv, 3D]: that head's q, k, v channels); the generic path
+    # wants one row of all channels ([3, 2*nq + nv]).  Tree-verify rows run the generic path on the device too.
+    def _tail_get(self, slot: int) -> torch.Tensor:
+        t = self.tail[slot]
+        if not self.kernel_layout:
+            return t
+        c, D = self.c, self.c.head_dim
+        rep = c.n_v_heads // c.n_k_heads
+        qk = t[:, ::rep, : 2 * D]                                    # one value head per key head carries q and k
+        return torch.cat((qk[..., :D].reshape(3, -1), qk[..., D:].reshape(3, -1), t[..., 2 * D:].reshape(3, -1)), 1)
+
+    def _tail_set(self, slot: int, g: torch.Tensor):
+        if not self.kernel_layout:
+            self.tail[slot] = g
+            return
+        c, D = self.c, self.c.head_dim
+        rep = c.n_v_heads // c.n_k_heads
+        q = g[:, : self.nq].view(3, c.n_k_heads, D).repeat_interleave(rep, 1)
+        k = g[:, self.nq: 2 * self.nq].view(3, c.n_k_heads, D).repeat_interleave(rep, 1)
+        v = g[:, 2 * self.nq:].view(3, c.n_v_heads, D)
+        self.tail[slot] = torch.cat((q, k, v), -1)
+
     def _seg(self, proj, ab, S0, tail0, parents=None):
         """Sequential oracle math for one segment.  Returns (o_gated, S_end, tail_end) and, for
         trees, per-node states are materialised (torch path only)."""
@@ -116,9 +138,10 @@ class GdnMixer:
             outs = []
             for s in plan.segs:
                 o, S, tail = self._seg(proj[s.r0: s.r0 + s.n], ab[s.r0: s.r0 + s.n], self.S[s.slot],
-                                       self.tail[s.slot], s.parents)
+                                       self._tail_get(s.slot), s.parents)
                 if commit:
-                    self.S[s.slot], self.tail[s.slot] = S, tail
+                    self.S[s.slot] = S
+                    self._tail_set(s.slot, tail)
                 outs.append(o)
             o = torch.cat(outs, 0).to(h.dtype)
         self.pending = None if commit else (proj, ab, plan)
@@ -136,8 +159,9 @@ class GdnMixer:
             if not rows:
                 continue
             idx = torch.tensor([s.r0 + j for j in rows], device=proj.device)
-            _, S, tail = self._seg(proj[idx], ab[idx], self.S[s.slot], self.tail[s.slot])
-            self.S[s.slot], self.tail[s.slot] = S, tail
+            _, S, tail = self._seg(proj[idx], ab[idx], self.S[s.slot], self._tail_get(s.slot))
+            self.S[s.slot] = S
+            self._tail_set(s.slot, tail)
         self.pending = None
 
     def state_tensors(self):

@@ -200,7 +200,7 @@ def gdn_mixer(mixer, proj, ab, plan, commit) -> Optional[torch.Tensor]:
 
 
 def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
-    if use_kernels(proj):
+    if use_kernels(proj) and not plan.is_tree:
         return cuda_ops().gdn_commit(mixer, proj, ab, plan, accepted)
     return False
 

@@ -552,7 +552,7 @@ def _gdn_chunk_prefill(mixer, proj, ab, plan, d, out):
 
 def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None):
     if plan.is_tree:
-        raise NotImplementedError("tree verify of gated-DeltaNet layers runs on the chain kernel only")
+        return None          # tree rows: per-node states through the generic path (every node forks its parent's state)
     c = mixer.c
     d = _plan_dev(plan, proj.device)
     R = proj.shape[0]
@@ -721,7 +721,7 @@ ATTN_PREFILL_MIN_ROWS = 32
 
 def attn_mixer(mixer, qkv, plan, seqs):
     if plan.is_tree:
-        raise NotImplementedError("tree-verify attention mask kernel")
+        return None          # ancestor-masked rows run the generic path
     c = mixer.c
     dev = qkv.device
     d = _plan_dev(plan, dev)

@@ -192,6 +192,50 @@ class SpecDecoder:
         self.rounds += 1
         return emitted
 
+    @torch.no_grad()
+    def round_tree(self, seqs: List[SeqSpec], trees: List[List[Node]], budgets: Optional[List[int]] = None,
+                   stop: Sequence[int] = ()) -> List[List[int]]:
+        """One speculative round with a verification TREE per sequence (nodes in topological order, parent -1 = the
+        last sampled token): every node is one extra row that sees the committed context plus its own ancestors; the
+        accept walk follows the target's samples through the tree and the accepted root-to-leaf path is committed
+        (linear-attention states replayed along the path, KV rows compacted).  Reference: engine-rs/src/speculative.rs,
+        spec_probe.rs:254-460 (tree topologies), mla_latent.rs:472-773."""
+        m = self.m
+        items, parents = [], []
+        for s, nodes in zip(seqs, trees):
+            L = m.seqs[s.slot].length
+            items.append((s.slot, [s.last_token] + [n.token for n in nodes], L))
+            parents.append([-1] + [n.parent + 1 for n in nodes])
+        plan = make_plan(items, device=m.device, parents=parents)
+        logits = m.forward(plan, commit=False)
+        hidden = m.hidden_out
+        emitted, accepted_rows = [], []
+        for i, (s, nodes) in enumerate(zip(seqs, trees)):
+            seg = plan.segs[i]
+            depth = [0] * seg.n
+            for j in range(1, seg.n):
+                depth[j] = depth[seg.parents[j]] + 1
+            preds = [sampling.sample(logits[seg.r0 + j], s.temperature, s.seed, seg.pos0 + 1 + depth[j]) for j in range(seg.n)]
+            budget = budgets[i] if budgets is not None else None
+            path, out, _ = accept(nodes, preds[0], preds[1:], budget=budget, stop=stop)
+            rows = [0] + [n + 1 for n in path]
+            rows = rows[: len(out)] if len(out) <= len(path) else rows
+            accepted_rows.append(rows)
+            s.drafted += len(nodes)
+            s.accepted += len(path)
+            emitted.append(out)
+        m.commit(accepted_rows)
+        for i, (s, out) in enumerate(zip(seqs, emitted)):
+            seg, rows = plan.segs[i], accepted_rows[i]
+            s.pending_mtp = [(hidden[seg.r0 + r].clone(), out[j]) for j, r in enumerate(rows) if j < len(out)]
+            s.last_token = out[-1]
+            s.hidden = hidden[seg.r0 + rows[-1]].clone()
+            s.generated.extend(out)
+            if s.lookup is not None:
+                s.lookup.extend(out)
+        self.rounds += 1
+        return emitted
+
     def generate(self, prompts: List[Sequence[int]], max_new: int, stop: Sequence[int] = (), temperature: float = 0.0,
                  seed: int = 0) -> List[List[int]]:
         seqs = [self.start(i, p, temperature, seed) for i, p in enumerate(prompts)]

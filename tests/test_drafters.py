@@ -60,3 +60,37 @@ def test_stage_drafter_lengths_follow_confidence():
     toks, confs = sd.propose_block(torch.randn(256, generator=torch.Generator().manual_seed(1)), 7)
     assert len(toks) == 5 and all(0.0 <= c <= 1.0 for c in confs)
     assert (toks, confs) == sd.propose_block(torch.randn(256, generator=torch.Generator().manual_seed(1)), 7)
+
+
+def test_tree_verification_rounds_are_exact():
+    """Rounds that verify a candidate TREE (feature drafter: spine + siblings) emit exactly the greedy tokens; the
+    accepted path is committed through linear-attention replay and KV compaction."""
+    cfg = tiny_hybrid()
+    cfg.mtp_layers = 0
+    W = init_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = _greedy(cfg, W, prompt, 16)
+    m = Model(cfg, W, n_slots=1, kv_tokens=256)
+    fd = D.FeatureDrafter(m, D.FeatureDrafterConfig(target_hidden=cfg.hidden, taps=(0, cfg.n_layers - 1), vocab=cfg.vocab,
+                                                    sub_vocab=min(512, cfg.vocab), depth=3, cand_k=8))
+    dec = SpecDecoder(m, drafter=None, depth=0)
+    seq = dec.start(0, prompt)
+    out = list(seq.generated)
+    # mix the drafter's tree with a tree that contains the true continuation, so that deep acceptances occur too
+    rnd = 0
+    while len(out) < 16:
+        cand = fd.candidates(seq)
+        nodes = D.to_tree(cand, [3, 2, 2])
+        if rnd % 2 == 1:
+            k = len(out)
+            true_next = ref[k: k + 2]
+            nodes = [D.Node(-1, (true_next[0] + 1) % cfg.vocab), D.Node(-1, true_next[0])]
+            if len(true_next) > 1:
+                nodes += [D.Node(1, true_next[1]), D.Node(1, (true_next[1] + 7) % cfg.vocab)]
+        emitted = dec.round_tree([seq], [nodes], budgets=[16 - len(out)])[0]
+        assert 1 <= len(emitted) <= len(nodes) + 1
+        if rnd % 2 == 1 and len(true_next) > 1 and 16 - len(out) >= 3:
+            assert len(emitted) == 3                         # root sample + both true nodes accepted
+        out += emitted
+        rnd += 1
+    assert out == ref

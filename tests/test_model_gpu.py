@@ -150,3 +150,28 @@ def test_other_families_on_device_match_cpu_runner(preset):
     assert torch.isfinite(got).all()
     err = (got - ref).norm() / ref.norm()
     assert err < 5e-2, err
+
+
+def test_tree_verification_on_device_is_exact():
+    """Tree-verify rounds on the device (ancestor-masked rows through the generic path, kernels for everything else)
+    emit the greedy tokens and leave the state where plain decoding would."""
+    from spark_engine_b200.spec.decoder import SpecDecoder
+    from spark_engine_b200.spec.tree import Node
+    cfg, W, Wr, prompts = _setup()
+    cfg.mtp_layers = 0
+    Wd = to_device(W, "cuda")
+    prompt = prompts[0, :24].tolist()
+    mg = Model(cfg, Wd, device="cuda", dtype=torch.bfloat16, n_slots=1, kv_tokens=256)
+    ref = SpecDecoder(mg, drafter=None, depth=0).generate([prompt], 14)[0]
+    m = Model(cfg, Wd, device="cuda", dtype=torch.bfloat16, n_slots=1, kv_tokens=256)
+    dec = SpecDecoder(m, drafter=None, depth=0)
+    seq = dec.start(0, prompt)
+    out = list(seq.generated)
+    while len(out) < 14:
+        k = len(out)
+        nxt = ref[k: k + 2]
+        nodes = [Node(-1, (nxt[0] + 3) % cfg.vocab), Node(-1, nxt[0])]
+        if len(nxt) > 1:
+            nodes += [Node(1, (nxt[1] + 5) % cfg.vocab), Node(1, nxt[1]), Node(0, 7)]
+        out += dec.round_tree([seq], [nodes], budgets=[14 - len(out)])[0]
+    assert out == ref
