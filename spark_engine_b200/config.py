@@ -236,6 +236,7 @@ class EngineConfig:
     spec_policy: str = "theta"           # tau | theta | rate | cost
     comm: str = "fused"                  # fused (peer-memory kernels) | nccl (baseline)
     comm_wait_ms: float = 1000.0         # bound of every device-side wait
+    step_deadline_s: float = 0.0         # > 0: a watchdog aborts the process when one engine step runs longer
     pcache_dir: Optional[str] = None
     pcache_bytes: int = 64 << 30
     socket: str = "/tmp/spark-b200.sock"

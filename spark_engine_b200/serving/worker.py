@@ -66,6 +66,10 @@ class EngineServer:
                        "accepted_drafts": 0, "prefix_hit_tokens": 0, "disk_restores": 0}
         self.out: List[dict] = []
         self.shutdown = False
+        self.watchdog = None
+        if e.step_deadline_s > 0:                 # fail-stop on a stuck step: the process is aborted, never the device
+            from ..parallel.faults import StepWatchdog
+            self.watchdog = StepWatchdog(e.step_deadline_s)
 
     # ------------------------------------------------------------------------------------------ requests
     def submit(self, msg: dict):
@@ -108,6 +112,14 @@ class EngineServer:
         st = self.sched.next(disk_tokens)
         if st.kind == K.Idle:
             return False
+        if self.watchdog is not None:
+            with self.watchdog.step(str(st.kind)):
+                self._run_step(st, K)
+        else:
+            self._run_step(st, K)
+        return True
+
+    def _run_step(self, st, K):
         if st.kind == K.Admit:
             self._admit(st.admit)
         elif st.kind == K.Prefill:
@@ -116,7 +128,6 @@ class EngineServer:
             self._decode(list(st.decode_slots))
         elif st.kind == K.Cancel:
             self._finish(st.slot, "cancelled")
-        return True
 
     def _admit(self, plan):
         lv = self.live.get(plan.request_id)
