@@ -79,7 +79,8 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + alignment slack
+  static constexpr int XPOSE_BYTES = 4 * 32 * 33 * 4;                     // per-epilogue-warp transpose tile (coalesced pushes)
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + XPOSE_BYTES + 1024;   // + alignment slack
 };
 
 // Epilogue functor contract:
@@ -218,7 +219,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (row < tc.row_end) epi(tc, row, tc.out_col0 + c, v);
+          if constexpr (Epi::kWarpTile) {
+            // remote stores want whole 128-byte lines: transpose the warp's 32 x 32 block through shared memory so
+            // that the 32 lanes write 32 consecutive floats of one row per instruction
+            float* xp = reinterpret_cast<float*>(smem + STAGES * S::STAGE_BYTES + S::BAR_BYTES) + quarter * 32 * 33;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) xp[lane * 33 + i] = v[i];
+            __syncwarp();
+            epi.warp_tile(tc, tc.a_row0 + quarter * 32, tc.out_col0 + c, xp, lane);
+            __syncwarp();
+          } else {
+            if (row < tc.row_end) epi(tc, row, tc.out_col0 + c, v);
+          }
         }
       }
       tc_fence_before();
@@ -236,6 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // ---------------------------------------------------------------- epilogues
 struct EpiStoreBf16 {
+  static constexpr bool kWarpTile = false;
   __nv_bfloat16* C; int ldc; int N;
   __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const { return g; }
@@ -258,6 +271,7 @@ struct EpiStoreBf16 {
 };
 
 struct EpiStoreF32 {
+  static constexpr bool kWarpTile = false;
   float* C; int ldc; int N;
   __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const { return g; }
@@ -274,6 +288,7 @@ struct EpiStoreF32 {
 
 // SwiGLU (optionally clamped) over a [gate | up] tile pair -> bf16 [rows, F].
 struct EpiSwigluBf16 {
+  static constexpr bool kWarpTile = false;
   __nv_bfloat16* C; int ldc; int N; float limit;
   __device__ __forceinline__ void cta_done(int) const {}
   __device__ __forceinline__ float act(float g, float u) const {
@@ -291,6 +306,7 @@ struct EpiSwigluBf16 {
 // finishes last on this rank raises the "my partials are delivered" flag on every owner.  The owners then
 // sum the slots in rank order (+ residual + RMSNorm) and all-gather the result (comm.cu rs_finish_ag_push).
 struct EpiPushRS {
+  static constexpr bool kWarpTile = true;
   uint8_t* peers[COMM_MAX_RANKS];
   long long slot_off, flag_off;        // float slots [world(src)][rows_per_rank * N] on the owner; u32 flags [world]
   int rank, world, rows_per_rank, N;
@@ -306,6 +322,18 @@ struct EpiPushRS {
       for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     } else {
       for (int i = 0; i < 32 && col + i < N; ++i) dst[i] = v[i];
+    }
+  }
+  // xp: the warp's 32 x 32 block, row-major with stride 33; rows row0..row0+31, columns col..col+31
+  __device__ __forceinline__ void warp_tile(const TileCoord& tc, int row0, int col, const float* xp, int lane) const {
+    if (col + lane >= N) return;
+#pragma unroll 4
+    for (int r = 0; r < 32; ++r) {
+      const int row = row0 + r;
+      if (row >= tc.row_end) break;
+      const int owner = row / rows_per_rank, lr = row - owner * rows_per_rank;
+      float* dst = reinterpret_cast<float*>(peers[owner] + slot_off) + (static_cast<size_t>(rank) * rows_per_rank + lr) * N + col;
+      dst[lane] = xp[r * 33 + lane];
     }
   }
   __device__ __forceinline__ void cta_done(int n_ctas) const {
