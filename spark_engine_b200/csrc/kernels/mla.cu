@@ -274,15 +274,18 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   asm volatile("cp.async.wait_all;" ::: "memory");               // the query copy, if every split was empty
 }
 
-// grid R; 256 threads.  Splits merged in ascending order; `sink` (per head, optional) joins the denominator.
-// One CTA per row: the per-head weights of the splits are computed once into shared memory, then the threads sweep
-// the row's H x L outputs with 16-byte loads.
+// grid (R, ceil(H / hpc)); 256 threads.  Splits merged in ascending order; `sink` (per head, optional) joins the
+// denominator.  A CTA owns `hpc` heads of one row: the per-head weights of the splits are computed once into shared
+// memory, then the threads sweep the hpc x L outputs with 16-byte loads.  The launcher picks hpc so that a decode
+// round of a few rows still fills the SMs (one head per CTA), while a prefill chunk keeps one CTA per row.
 __global__ void __launch_bounds__(256)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit, const float* __restrict__ sink,
-                 int H, int L, __nv_bfloat16* __restrict__ out) {
-  extern __shared__ float wts[];                        // [H][nsplit]: exp(m_s - M) / l
-  const int r = blockIdx.x;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+                 int H, int L, int hpc, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float wts[];                        // [hpc][nsplit]: exp(m_s - M) / l
+  const int r = blockIdx.x, h0 = blockIdx.y * hpc;
+  const int nh = min(hpc, H - h0);
+  for (int hl = threadIdx.x; hl < nh; hl += blockDim.x) {
+    const int h = h0 + hl;
     const size_t pb = (static_cast<size_t>(r) * H + h) * nsplit;
     float M = sink ? sink[h] : -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(pb + s) * 2]);
@@ -294,17 +297,17 @@ mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
     const float inv = 1.f / l;
     for (int s = 0; s < nsplit; ++s) {
       const float m = part_ml[(pb + s) * 2];
-      wts[h * nsplit + s] = m != -INFINITY ? __expf(m - M) * inv : 0.f;
+      wts[hl * nsplit + s] = m != -INFINITY ? __expf(m - M) * inv : 0.f;
     }
   }
   __syncthreads();
   const int L4 = L >> 2;
-  for (int i = threadIdx.x; i < H * L4; i += blockDim.x) {
-    const int h = i / L4, d = (i - h * L4) * 4;
+  for (int i = threadIdx.x; i < nh * L4; i += blockDim.x) {
+    const int hl = i / L4, d = (i - hl * L4) * 4, h = h0 + hl;
     const size_t pb = (static_cast<size_t>(r) * H + h) * nsplit;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < nsplit; ++s) {
-      const float w = wts[h * nsplit + s];
+      const float w = wts[hl * nsplit + s];
       if (w != 0.f) {
         const float4 p = *reinterpret_cast<const float4*>(part_o + (pb + s) * L + d);
         o.x = fmaf(w, p.x, o.x); o.y = fmaf(w, p.y, o.y); o.z = fmaf(w, p.z, o.z); o.w = fmaf(w, p.w, o.w);
@@ -362,6 +365,11 @@ extern "C" int spark_mla_attn(const void* q_full, const void* lat, const int* po
   kern<<<dim3(R, (nsplit + spc - 1) / spc), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv,
                                                             sel, sel_n, sel_ld, part_o, part_ml, H, KW, kv_lora, scale, nsplit, spc);
   if (H * nsplit * 4 > 48 * 1024) return -6;
-  mla_merge_kernel<<<R, 256, H * nsplit * 4, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, (__nv_bfloat16*)out);
+  int hpc = H;                                          // heads per merge CTA: enough CTAs for two per SM when rows are few
+  while (hpc > 1 && R * ((H + hpc - 1) / hpc) < 296) hpc = (hpc + 1) / 2;
+  const int L4 = kv_lora >> 2;
+  const int mthreads = hpc * L4 >= 256 ? 256 : ((hpc * L4 + 31) / 32 * 32);
+  mla_merge_kernel<<<dim3(R, (H + hpc - 1) / hpc), mthreads, hpc * nsplit * 4, s>>>(part_o, part_ml, nsplit, sink, H, kv_lora, hpc,
+                                                                                  (__nv_bfloat16*)out);
   return spark_launch_rc(__func__);
 }

@@ -62,14 +62,15 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 // FMT 2: W = e4m3 [N,K], scales u8 (E8M0) [N, K/32] (MXFP8).
 // RB = rows held in shared memory (1, 4, 8 or 16).  act 1: x is [gate | up] (2K wide), swiglu while staging.
 template <int FMT, int RB, typename TO>
-__global__ void __launch_bounds__(MXV_WARPS * 32)
+__global__ void __launch_bounds__(MXV_WARPS * 32, 2)
 mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __restrict__ W, const void* __restrict__ scales,
                long long w_expert_stride, long long s_expert_stride, TO* __restrict__ y, int ldy, int rows_per_item,
-               int N, int K, const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit) {
+               int N, int K, const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit,
+               int cgroups) {
   extern __shared__ __align__(16) uint8_t smem_mx[];
   const int XS = K + 8;                                        // row stride in halfs: 16 bytes mod 128 -> no conflicts
   __half* xs = reinterpret_cast<__half*>(smem_mx);              // [RB][XS]
-  float* red = reinterpret_cast<float*>(smem_mx + static_cast<size_t>(RB) * XS * 2);   // [warps][16][16]
+  float* red = reinterpret_cast<float*>(smem_mx + static_cast<size_t>(RB) * XS * 2);   // [2][warps][16][16]
   const int item = blockIdx.y;
   if (pair_expert && pair_expert[item] < 0) return;            // pair of an expert that lives on another rank
   const int e = pair_expert ? pair_expert[item] : 0;
@@ -97,7 +98,7 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
   __syncthreads();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * MXV_COLS;
+  const int n0 = blockIdx.x * MXV_COLS * cgroups;
   constexpr int KI = FMT == 1 ? 128 : 64;                      // k per warp iteration (4 threads x 16 bytes)
   constexpr int KT = KI / 4;                                   // k per thread per iteration
   constexpr int STEPS = KT / 4;                                // mma k-steps per iteration
@@ -108,8 +109,7 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
   const uint8_t* w_hi = w_lo + 8 * row_bytes;
   const float* sc_f = nullptr;
   const uint8_t* sc_lo = nullptr; const uint8_t* sc_hi = nullptr;
-  if (FMT == 0) sc_f = reinterpret_cast<const float*>(scales) + static_cast<size_t>(e) * s_expert_stride +
-                       static_cast<size_t>(n0 >> 7) * (K >> 7);
+  if (FMT == 0) sc_f = reinterpret_cast<const float*>(scales) + static_cast<size_t>(e) * s_expert_stride;
   else {
     // FMT 1: a lane's 16 bytes are one 32-k scale block; FMT 2: 16 k = half a block, lanes (0,1) and (2,3) share one
     sc_lo = reinterpret_cast<const uint8_t*>(scales) + static_cast<size_t>(e) * s_expert_stride +
@@ -121,23 +121,38 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
   const __half* xb = xs + ((g + 8) < RB ? (g + 8) : 0) * XS + t * KT;
   const bool has_a = g < RB, has_b = (g + 8) < RB;
 
+  // A CTA walks `cgroups` groups of 16 output columns with the staged rows kept in shared memory.  The weight loads
+  // of batch b+1 (the next U k-slices of this warp, or the first ones of the next column group) are issued before
+  // the MMAs of batch b, so the memory pipe stays full across the per-group reductions.
   float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  constexpr int U = 4;                                         // iterations in flight
-  for (int it0 = warp; it0 < iters; it0 += MXV_WARPS * U) {
-    uint4 wl[U], wh[U];
-    uint8_t sl[U], sh[U];
+  constexpr int U = 4;                                         // k-slices per batch
+  const int nb = (iters + MXV_WARPS * U - 1) / (MXV_WARPS * U);      // batches per column group
+  const int total = cgroups * nb;
+  uint4 wl0[U], wh0[U], wl1[U], wh1[U];
+  uint8_t sl0[U], sh0[U], sl1[U], sh1[U];
+
+  auto load = [&](uint4 (&wl)[U], uint4 (&wh)[U], uint8_t (&sl)[U], uint8_t (&sh)[U], int bi) {
+    if (bi >= total) return;
+    const int cg = bi / nb, kb = bi - cg * nb;
+    const size_t goff = static_cast<size_t>(cg) * MXV_COLS * row_bytes;
+    const size_t soff = static_cast<size_t>(cg) * MXV_COLS * (K >> 5);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int it = it0 + u * MXV_WARPS;
+      const int it = warp + (kb * U + u) * MXV_WARPS;
       if (it < iters) {
-        wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + static_cast<size_t>(it) * 64));
-        wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + static_cast<size_t>(it) * 64));
-        if (FMT != 0) { sl[u] = __ldg(sc_lo + it * SPI); sh[u] = __ldg(sc_hi + it * SPI); }
+        wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + goff + static_cast<size_t>(it) * 64));
+        wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + goff + static_cast<size_t>(it) * 64));
+        if (FMT != 0) { sl[u] = __ldg(sc_lo + soff + it * SPI); sh[u] = __ldg(sc_hi + soff + it * SPI); }
       }
     }
+  };
+
+  auto compute = [&](const uint4 (&wl)[U], const uint4 (&wh)[U], const uint8_t (&sl)[U], const uint8_t (&sh)[U], int bi) {
+    const int cg = bi / nb, kb = bi - cg * nb;
+    const int nc = n0 + cg * MXV_COLS;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int it = it0 + u * MXV_WARPS;
+      const int it = warp + (kb * U + u) * MXV_WARPS;
       if (it >= iters) break;
       float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
@@ -168,27 +183,40 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
         mma16816(c[1], av.x, bv.x, av.y, bv.y, b0h, b1h);
       }
       float sc = 1.f;
-      if (FMT == 0) sc = __ldg(sc_f + ((it * KI) >> 7));
+      if (FMT == 0) sc = __ldg(sc_f + static_cast<size_t>(nc >> 7) * (K >> 7) + ((it * KI) >> 7));
 #pragma unroll
       for (int j = 0; j < 4; ++j) { acc[0][j] = fmaf(c[0][j], sc, acc[0][j]); acc[1][j] = fmaf(c[1][j], sc, acc[1][j]); }
     }
-  }
-  // fixed-order sum over the warps: red[warp][row][col]
-  float* rw = red + warp * 256;
+    if (kb == nb - 1) {
+      // fixed-order sum over the warps: red[parity][warp][row][col]; the parity buffer lets the next group's
+      // partials land while slow threads still read this group's
+      float* rb = red + (cg & 1) * (MXV_WARPS * 256);
+      float* rw = rb + warp * 256;
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    rw[g * 16 + nt * 8 + 2 * t] = acc[nt][0];
-    rw[g * 16 + nt * 8 + 2 * t + 1] = acc[nt][1];
-    rw[(g + 8) * 16 + nt * 8 + 2 * t] = acc[nt][2];
-    rw[(g + 8) * 16 + nt * 8 + 2 * t + 1] = acc[nt][3];
-  }
-  __syncthreads();
-  const int row = threadIdx.x >> 4, col = threadIdx.x & 15;
-  if (row < R && n0 + col < N) {
-    float v = 0.f;
+      for (int nt = 0; nt < 2; ++nt) {
+        rw[g * 16 + nt * 8 + 2 * t] = acc[nt][0];
+        rw[g * 16 + nt * 8 + 2 * t + 1] = acc[nt][1];
+        rw[(g + 8) * 16 + nt * 8 + 2 * t] = acc[nt][2];
+        rw[(g + 8) * 16 + nt * 8 + 2 * t + 1] = acc[nt][3];
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      }
+      __syncthreads();
+      const int row = threadIdx.x >> 4, col = threadIdx.x & 15;
+      if (row < R && nc + col < N) {
+        float v = 0.f;
 #pragma unroll
-    for (int w = 0; w < MXV_WARPS; ++w) v += red[w * 256 + row * 16 + col];
-    y[static_cast<size_t>(item * rows_per_item + row) * ldy + n0 + col] = static_cast<TO>(v);
+        for (int w = 0; w < MXV_WARPS; ++w) v += rb[w * 256 + row * 16 + col];
+        y[static_cast<size_t>(item * rows_per_item + row) * ldy + nc + col] = static_cast<TO>(v);
+      }
+    }
+  };
+
+  load(wl0, wh0, sl0, sh0, 0);
+  for (int bi = 0; bi < total; bi += 2) {
+    load(wl1, wh1, sl1, sh1, bi + 1);
+    compute(wl0, wh0, sl0, sh0, bi);
+    load(wl0, wh0, sl0, sh0, bi + 2);
+    if (bi + 1 < total) compute(wl1, wh1, sl1, sh1, bi + 1);
   }
 }
 
@@ -197,15 +225,20 @@ static int launch_mx_gemv(const void* x, int ldx, const void* W, const void* sc,
                           int ldy, int items, int rows, int N, int K, const int* pe, const int* pr, int act, float limit,
                           cudaStream_t s) {
   auto kern = mx_gemv_kernel<FMT, RB, TO>;
-  const int smem = RB * (K + 8) * 2 + MXV_WARPS * 256 * 4;
+  const int smem = RB * (K + 8) * 2 + 2 * MXV_WARPS * 256 * 4;
   if (smem > 200 * 1024) return -6;
+  // column groups per CTA: as many as keep four CTAs per SM's worth of work in the grid
+  const int ngroups = N / MXV_COLS;
+  int cgroups = 1;
+  for (int c = 4; c > 1; c >>= 1)
+    if (ngroups % c == 0 && static_cast<long long>(ngroups / c) * items >= 592) { cgroups = c; break; }
   if (smem > 48 * 1024) {
     static int set_for = 0;
     if (!set_for) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set_for = 1; }
   }
-  dim3 grid(N / MXV_COLS, items);
+  dim3 grid(ngroups / cgroups, items);
   kern<<<grid, MXV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W, sc, wes, ses, (TO*)y, ldy, rows,
-                                          N, K, pe, pr, act, limit);
+                                          N, K, pe, pr, act, limit, cgroups);
   return spark_launch_rc(__func__);
 }
 

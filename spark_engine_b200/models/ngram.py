@@ -12,10 +12,39 @@ import torch
 from ..oracle import layers as L
 
 
+def chain_row_ids(model, slot: int, pos0: int, new_ids) -> list:
+    """Table rows of `new_ids` appended to the history of `slot` at `pos0`, in plain integer arithmetic (a decode
+    round hashes one or a few positions per sequence: no tensor ops on the host).  Updates the history.  Equals
+    `oracle.layers.ngram_ids` on the whole sequence, restricted to the new positions."""
+    cfg = model.cfg
+    heads = cfg.ngram_heads
+    head_rows = model.W["ngram_table"].shape[0] // heads
+    hist = getattr(model, "id_history", None)
+    if hist is None:
+        hist = model.id_history = {}
+    past = hist.get(slot, torch.empty(0, dtype=torch.long))[:pos0]
+    tail = [-1, -1] + past[-2:].tolist()
+    m0, m1, m2 = (L._wrap64(v) for v in L.NGRAM_MULT)
+    half = heads // 2
+    out = []
+    for t in new_ids:
+        t = int(t)
+        bi = L._wrap64(t * m0) ^ L._wrap64(tail[-1] * m1)
+        tri = bi ^ L._wrap64(tail[-2] * m2)
+        rb, rt = bi % head_rows, tri % head_rows
+        out.append([(rb if h < half else rt) + h * head_rows for h in range(heads)])
+        tail.append(t)
+    hist[slot] = torch.cat((past, torch.tensor([int(t) for t in new_ids], dtype=torch.long)))
+    return out
+
+
 def ngram_rows_for_plan(model, plan) -> torch.Tensor:
     cfg = model.cfg
     table = model.W["ngram_table"]
     head_rows = table.shape[0] // cfg.ngram_heads
+    staged = (getattr(plan, "dev", None) or {}).get("ngram_rows")
+    if staged is not None:             # captured decode: the host staged the row ids, the gather runs on the device
+        return table[staged].flatten(1).float()
     hist = getattr(model, "id_history", None)
     if hist is None:
         hist = model.id_history = {}

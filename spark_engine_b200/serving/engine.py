@@ -55,6 +55,11 @@ class _DecodeGraph:
              "row_j": torch.tensor(list(range(rows_per_seq)) * n, dtype=torch.int32, device=dev),
              "row_r0": torch.tensor([i * rows_per_seq for i in range(n) for _ in range(rows_per_seq)], dtype=torch.int32,
                                     device=dev)}
+        # hashed n-gram layers: the row ids of each position come from the token history, which lives on the host
+        self.ng_host = None
+        if engine.cfg.ngram_layers:
+            self.ng_host = torch.zeros(R, engine.cfg.ngram_heads, dtype=torch.int64).pin_memory()
+            d["ngram_rows"] = torch.zeros(R, engine.cfg.ngram_heads, dtype=torch.int64, device=dev)
         self.plan.dev = d
         self.graph = None
         self.out_ids = None
@@ -77,6 +82,11 @@ class _DecodeGraph:
             h[3 * R + 4 * i + 3] = pos0[i]
             self.plan.segs[i].pos0 = pos0[i]
         self.dev.copy_(h, non_blocking=True)
+        if self.ng_host is not None:
+            from ..models.ngram import chain_row_ids
+            for i, s in enumerate(self.slots):
+                self.ng_host[i * k:(i + 1) * k] = torch.tensor(chain_row_ids(m, s, pos0[i], ids[i]), dtype=torch.int64)
+            self.plan.dev["ngram_rows"].copy_(self.ng_host, non_blocking=True)
 
     def set_kv(self):
         m = self.engine.model
@@ -126,9 +136,10 @@ class LLMEngine:
                            kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
         self.graphs: Dict[tuple, _DecodeGraph] = {}
-        # decode rounds are captured only when every layer runs on capturable kernels: the host-streamed n-gram tables
-        # go through host-side index work
-        capturable = not cfg.ngram_layers
+        # decode rounds are captured when every layer runs on capturable kernels: hashed n-gram layers qualify when
+        # their table is resident on the device (row ids are staged by the host, the gather is captured); a
+        # host-streamed table goes through host-side gathers and runs eagerly
+        capturable = not cfg.ngram_layers or self.model.W["ngram_table"].device.type == "cuda"
         self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda" and capturable
         self.stats = GenStats()
         self._rounds_since_check = 0

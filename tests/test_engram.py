@@ -39,3 +39,24 @@ def test_prefetch_to_device():
         rows = EngramTable.take(et.prefetch(ids))
         assert rows.is_cuda and torch.equal(rows.cpu(), table[ids])
     et.close()
+
+
+def test_integer_chain_row_ids_equal_the_tensor_hash():
+    """The decode path hashes the new positions in plain integers against the per-slot id history; same rows as
+    the whole-sequence tensor hash, whatever the split into rounds."""
+    from types import SimpleNamespace
+    from spark_engine_b200.models.ngram import chain_row_ids
+    from spark_engine_b200.oracle import layers as L
+    m = SimpleNamespace(cfg=SimpleNamespace(ngram_heads=16), W={"ngram_table": torch.zeros(4096, 8)}, id_history={})
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 150000, (40,), generator=g)
+    ref = L.ngram_ids(ids, 16, 256)
+    got, p = [], 0
+    for k in (3, 1, 1, 5, 1, 2, 27):
+        got += chain_row_ids(m, 0, p, ids[p:p + k].tolist())
+        p += k
+    assert torch.equal(torch.tensor(got), ref)
+    # a round that rewinds (rejected drafts) re-hashes from the kept prefix
+    again = chain_row_ids(m, 0, 12, ids[12:15].tolist())
+    assert torch.equal(torch.tensor(again), ref[12:15])
+    assert m.id_history[0].tolist() == ids[:15].tolist()

@@ -152,6 +152,22 @@ def test_other_families_on_device_match_cpu_runner(preset):
     assert err < 5e-2, err
 
 
+@pytest.mark.parametrize("preset", ["glm-style", "ds4-style"])
+def test_other_families_graph_replay_equals_eager(preset):
+    """Captured decode rounds of the other families (the DS-style hashed n-gram rows are staged by the host and
+    gathered inside the graph) emit the tokens of the eager rounds."""
+    from spark_engine_b200.config import EngineConfig, get_model_config, scaled_down
+    cfg = scaled_down(get_model_config(preset))
+    cfg.mtp_layers = 0
+    Wd = to_device(init_weights(cfg, seed=2), "cuda")
+    g = torch.Generator().manual_seed(6)
+    p = torch.randint(0, cfg.vocab, (2, 40), generator=g).tolist()
+    e1 = LLMEngine(cfg, Wd, EngineConfig(cuda_graphs=True), max_seqs=2, kv_tokens_per_seq=256)
+    e2 = LLMEngine(cfg, Wd, EngineConfig(cuda_graphs=False), max_seqs=2, kv_tokens_per_seq=256)
+    assert e1.use_graphs and not e2.use_graphs
+    assert e1.generate(p, 12) == e2.generate(p, 12)
+
+
 def test_tree_verification_on_device_is_exact():
     """Tree-verify rounds on the device (ancestor-masked rows through the generic path, kernels for everything else)
     emit the greedy tokens and leave the state where plain decoding would."""
