@@ -47,8 +47,11 @@ __device__ __forceinline__ void set_status(int* status, int code, int a = 0, int
 }
 
 #ifndef SPARK_WAIT_POLLS
-#define SPARK_WAIT_POLLS (1u << 22)   // bounded polls per mbarrier wait (each try_wait suspends briefly)
+#define SPARK_WAIT_POLLS (1u << 22)   // hard cap on polls per mbarrier wait
 #endif
+#ifndef SPARK_WAIT_NS
+#define SPARK_WAIT_NS 2000000000ull   // wall-clock limit of one mbarrier wait: a try_wait may suspend the thread for an
+#endif                                // implementation-defined time, so the poll count alone does not bound the wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -93,9 +96,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false when the limit ran out (caller records status and leaves its loop).
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 0; i < SPARK_WAIT_POLLS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u && global_timer_ns() - t0 > SPARK_WAIT_NS) return false;
   }
   return false;
 }

@@ -20,8 +20,14 @@
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
 #include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdlib>
 
 #include "../common/ptx.cuh"
+
+#ifndef SPARK_FP4_CVT
+#define SPARK_FP4_CVT 0            // 1: E2M1 through the hardware conversion instruction, 0: integer-pipe decode
+#endif
 
 namespace spark {
 
@@ -41,9 +47,29 @@ __device__ __forceinline__ uint32_t fp4x2_to_h2(uint8_t v, __half2 scale) {
   __half2 h = __hmul2(*reinterpret_cast<__half2*>(&r), scale);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// Eight E2M1 nibbles of one 32-bit word -> four half2 on the integer pipe (the conversion instruction runs on the
+// transcendental unit and caps a memory-bound decode kernel at a fraction of HBM bandwidth).  A nibble s|ee|m shifted
+// so that ee|m lands on fp16 bits 11..9 reads as the E2M1 value times 2^-14, subnormal 0.5 included; the 2^14 goes
+// into the block scale.  Nibbles i and i+4 sit 16 bits apart, so one shift places both halves of pair i:
+// h[i] = (nibble i, nibble i+4).  The staged activations use the matching order within every 8 k.
+__device__ __forceinline__ void fp4x8_to_h2x4(uint32_t w, __half2 scale14, uint32_t (&h)[4]) {
+  h[0] = h2_scale(((w << 9) & 0x0E000E00u) | ((w << 12) & 0x80008000u), scale14);
+  h[1] = h2_scale(((w << 5) & 0x0E000E00u) | ((w << 8) & 0x80008000u), scale14);
+  h[2] = h2_scale(((w << 1) & 0x0E000E00u) | ((w << 4) & 0x80008000u), scale14);
+  h[3] = h2_scale(((w >> 3) & 0x0E000E00u) | (w & 0x80008000u), scale14);
+}
 // 2^(e-127) as fp16 (clamped to the normal range of fp16: exponents outside [-14, 15] do not occur in weights)
 __device__ __forceinline__ __half2 e8m0_h2(uint8_t e) {
   int ex = static_cast<int>(e) - 127;
+  ex = max(-14, min(15, ex));
+  const uint16_t bits = static_cast<uint16_t>((ex + 15) << 10);
+  __half_raw hr; hr.x = bits;
+  return __half2half2(*reinterpret_cast<__half*>(&hr));
+}
+// 2^(e-127+14) as fp16 for the shift-decoded E2M1 values: block scales from 2^-28 to 2 are exact, which covers
+// weights (a scale above 2 would mean weight magnitudes above 12)
+__device__ __forceinline__ __half2 e8m0_h2_x14(uint8_t e) {
+  int ex = static_cast<int>(e) - 127 + 14;
   ex = max(-14, min(15, ex));
   const uint16_t bits = static_cast<uint16_t>((ex + 15) << 10);
   __half_raw hr; hr.x = bits;
@@ -66,7 +92,7 @@ __global__ void __launch_bounds__(MXV_WARPS * 32, 2)
 mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __restrict__ W, const void* __restrict__ scales,
                long long w_expert_stride, long long s_expert_stride, TO* __restrict__ y, int ldy, int rows_per_item,
                int N, int K, const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit,
-               int cgroups) {
+               int cgroups, int xvec) {
   extern __shared__ __align__(16) uint8_t smem_mx[];
   const int XS = K + 8;                                        // row stride in halfs: 16 bytes mod 128 -> no conflicts
   __half* xs = reinterpret_cast<__half*>(smem_mx);              // [RB][XS]
@@ -76,27 +102,6 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
   const int e = pair_expert ? pair_expert[item] : 0;
   const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
   const int R = rows_per_item;
-  for (int i = threadIdx.x; i < RB * (K >> 1); i += blockDim.x) {
-    const int r = i / (K >> 1), k = (i - r * (K >> 1)) * 2;
-    float v0 = 0.f, v1 = 0.f;
-    if (r < R) {
-      const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
-      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
-      if (act == 0) { v0 = g.x; v1 = g.y; }
-      else {
-        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + K + k));
-        float g0 = g.x, g1 = g.y, u0 = u.x, u1 = u.y;
-        if (limit > 0.f) {
-          g0 = fminf(g0, limit); g1 = fminf(g1, limit);
-          u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
-        }
-        v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
-      }
-    }
-    *reinterpret_cast<__half2*>(xs + r * XS + k) = __floats2half2_rn(v0, v1);
-  }
-  __syncthreads();
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * MXV_COLS * cgroups;
   constexpr int KI = FMT == 1 ? 128 : 64;                      // k per warp iteration (4 threads x 16 bytes)
@@ -138,7 +143,7 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
     const size_t soff = static_cast<size_t>(cg) * MXV_COLS * (K >> 5);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int it = warp + (kb * U + u) * MXV_WARPS;
+      const int it = (kb * MXV_WARPS + warp) * U + u;          // U adjacent k-slices: 64 * U contiguous bytes per row
       if (it < iters) {
         wl[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + goff + static_cast<size_t>(it) * 64));
         wh[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + goff + static_cast<size_t>(it) * 64));
@@ -152,16 +157,22 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
     const int nc = n0 + cg * MXV_COLS;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int it = warp + (kb * U + u) * MXV_WARPS;
+      const int it = (kb * MXV_WARPS + warp) * U + u;          // U adjacent k-slices: 64 * U contiguous bytes per row
       if (it >= iters) break;
       float c[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const uint32_t* pl = reinterpret_cast<const uint32_t*>(&wl[u]);
       const uint32_t* ph = reinterpret_cast<const uint32_t*>(&wh[u]);
       __half2 hl, hh;
-      if (FMT != 0) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
+      if (FMT == 2) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
+#if SPARK_FP4_CVT
+      if (FMT == 1) { hl = e8m0_h2(sl[u]); hh = e8m0_h2(sh[u]); }
+#else
+      if (FMT == 1) { hl = e8m0_h2_x14(sl[u]); hh = e8m0_h2_x14(sh[u]); }
+#endif
+      uint32_t dl[4], dh[4];
 #pragma unroll
       for (int s = 0; s < STEPS; ++s) {
-        // A: 4 consecutive k of rows g / g+8
+        // A: 4 staged k of rows g / g+8
         uint2 av = make_uint2(0u, 0u), bv = make_uint2(0u, 0u);
         if (has_a) av = *reinterpret_cast<const uint2*>(xa + it * KI + s * 4);
         if (has_b) bv = *reinterpret_cast<const uint2*>(xb + it * KI + s * 4);
@@ -175,9 +186,16 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
           b0l = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vl & 0xffffu)), hl); b1l = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vl >> 16)), hl);
           b0h = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vh & 0xffffu)), hh); b1h = h2_scale(fp8x2_to_h2(static_cast<uint16_t>(vh >> 16)), hh);
         } else {
+#if SPARK_FP4_CVT
           const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
           b0l = fp4x2_to_h2(static_cast<uint8_t>(vl & 0xffu), hl); b1l = fp4x2_to_h2(static_cast<uint8_t>((vl >> 8) & 0xffu), hl);
           b0h = fp4x2_to_h2(static_cast<uint8_t>(vh & 0xffu), hh); b1h = fp4x2_to_h2(static_cast<uint8_t>((vh >> 8) & 0xffu), hh);
+#else
+          // one 32-bit word feeds two steps: pairs (0,4),(1,5) then (2,6),(3,7) of its 8 k
+          if ((s & 1) == 0) { fp4x8_to_h2x4(pl[s >> 1], hl, dl); fp4x8_to_h2x4(ph[s >> 1], hh, dh); }
+          b0l = dl[(s & 1) * 2]; b1l = dl[(s & 1) * 2 + 1];
+          b0h = dh[(s & 1) * 2]; b1h = dh[(s & 1) * 2 + 1];
+#endif
         }
         mma16816(c[0], av.x, bv.x, av.y, bv.y, b0l, b1l);
         mma16816(c[1], av.x, bv.x, av.y, bv.y, b0h, b1h);
@@ -211,7 +229,85 @@ mx_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __re
     }
   };
 
-  load(wl0, wh0, sl0, sh0, 0);
+  load(wl0, wh0, sl0, sh0, 0);            // the first weights are in flight while the rows are staged
+  if (xvec) {
+    // 16-byte loads, four in flight per thread: the rows are staged in about one memory latency
+    const int K8 = K >> 3, chunks = RB * K8;
+    constexpr int SU = 4;
+    for (int i0 = threadIdx.x; i0 < chunks; i0 += blockDim.x * SU) {
+      uint4 gq[SU], uq[SU];
+#pragma unroll
+      for (int u = 0; u < SU; ++u) {
+        const int i = i0 + u * blockDim.x;
+        gq[u] = make_uint4(0u, 0u, 0u, 0u); uq[u] = gq[u];
+        if (i < chunks) {
+          const int r = i / K8, k = (i - r * K8) * 8;
+          if (r < R) {
+            const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
+            gq[u] = *reinterpret_cast<const uint4*>(xr + k);
+            if (act != 0) uq[u] = *reinterpret_cast<const uint4*>(xr + K + k);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SU; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= chunks) break;
+        const int r = i / K8, k = (i - r * K8) * 8;
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gq[u]);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uq[u]);
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = __bfloat1622float2(gp[j]);
+          float v0 = g.x, v1 = g.y;
+          if (act != 0) {
+            const float2 uu = __bfloat1622float2(up[j]);
+            float g0 = g.x, g1 = g.y, u0 = uu.x, u1 = uu.y;
+            if (limit > 0.f) {
+              g0 = fminf(g0, limit); g1 = fminf(g1, limit);
+              u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
+            }
+            v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
+          }
+          const __half2 h = __floats2half2_rn(v0, v1);
+          op[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        if (FMT == 1 && !SPARK_FP4_CVT) o = make_uint4(__byte_perm(o.x, o.z, 0x5410), __byte_perm(o.x, o.z, 0x7632),     // k order 0 4 1 5 2 6 3 7
+                                     __byte_perm(o.y, o.w, 0x5410), __byte_perm(o.y, o.w, 0x7632));
+        *reinterpret_cast<uint4*>(xs + r * XS + k) = o;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < RB * (K >> 1); i += blockDim.x) {
+      const int r = i / (K >> 1), k = (i - r * (K >> 1)) * 2;
+      float v0 = 0.f, v1 = 0.f;
+      if (r < R) {
+        const __nv_bfloat16* xr = x + static_cast<size_t>(xr0 + r) * ldx;
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
+        if (act == 0) { v0 = g.x; v1 = g.y; }
+        else {
+          const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + K + k));
+          float g0 = g.x, g1 = g.y, u0 = u.x, u1 = u.y;
+          if (limit > 0.f) {
+            g0 = fminf(g0, limit); g1 = fminf(g1, limit);
+            u0 = fminf(fmaxf(u0, -limit), limit); u1 = fminf(fmaxf(u1, -limit), limit);
+          }
+          v0 = g0 / (1.f + __expf(-g0)) * u0; v1 = g1 / (1.f + __expf(-g1)) * u1;
+        }
+      }
+      if (FMT == 1 && !SPARK_FP4_CVT) {                   // k order 0 4 1 5 2 6 3 7 within every 8 (matches fp4x8_to_h2x4)
+        __half* q = xs + r * XS + (k & ~7);
+        q[(k & 3) * 2 + ((k & 7) >> 2)] = __float2half_rn(v0);
+        q[((k + 1) & 3) * 2 + (((k + 1) & 7) >> 2)] = __float2half_rn(v1);
+      } else {
+        *reinterpret_cast<__half2*>(xs + r * XS + k) = __floats2half2_rn(v0, v1);
+      }
+    }
+  }
+  __syncthreads();
+
   for (int bi = 0; bi < total; bi += 2) {
     load(wl1, wh1, sl1, sh1, bi + 1);
     compute(wl0, wh0, sl0, sh0, bi);
@@ -230,7 +326,9 @@ static int launch_mx_gemv(const void* x, int ldx, const void* W, const void* sc,
   // column groups per CTA: as many as keep four CTAs per SM's worth of work in the grid
   const int ngroups = N / MXV_COLS;
   int cgroups = 1;
-  for (int c = 4; c > 1; c >>= 1)
+  static const bool xvec_ok = [] { const char* e = getenv("SPARK_MXV_XVEC"); return !e || atoi(e) != 0; }();
+  static const int cg_max = [] { const char* e = getenv("SPARK_MXV_CG"); return e ? atoi(e) : 4; }();   // tuning knob
+  for (int c = cg_max; c > 1; c >>= 1)
     if (ngroups % c == 0 && static_cast<long long>(ngroups / c) * items >= 592) { cgroups = c; break; }
   if (smem > 48 * 1024) {
     static int set_for = 0;
@@ -238,7 +336,8 @@ static int launch_mx_gemv(const void* x, int ldx, const void* W, const void* sc,
   }
   dim3 grid(ngroups / cgroups, items);
   kern<<<grid, MXV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)W, sc, wes, ses, (TO*)y, ldy, rows,
-                                          N, K, pe, pr, act, limit, cgroups);
+                                          N, K, pe, pr, act, limit, cgroups,
+                                          xvec_ok && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx & 7) == 0 ? 1 : 0);
   return spark_launch_rc(__func__);
 }
 

@@ -27,6 +27,9 @@ _SIGS = {
     "spark_gemm_mxfp8": [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp],
     "spark_mx_sf_to_blocks": [_vp, _vp, _i32, _i32, _vp],
     "spark_mx_mgemm": [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
+    "spark_mx4_items": [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp],
+    "spark_mx_sf_tile_blocks": [_vp, _vp, _vp, _i32, _i32, _vp, _vp],
+    "spark_moe_mxfp4": [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp, _vp],
     "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
 }
 _bound = False
@@ -60,6 +63,11 @@ def gemv(x, w: QuantWeight, items=1, rows_per_item=None, pair_expert=None, pair_
          out_f32=False):
     x = cu._as_bf16(x).contiguous()
     q, sc, fmt, wes, ses = _parts(w)
+    if fmt == 1 and not getattr(w, "_scale_range_ok", False) and not torch.cuda.is_current_stream_capturing():
+        # the decode kernel folds 2^14 into the fp16 block scale: scales up to 2 (E8M0 byte 128) are exact
+        if int(sc.max()) > 128:
+            raise ValueError("MXFP4 block scale above 2: outside the range of the decode kernel")
+        w._scale_range_ok = True
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     y = torch.empty(items * rows_per_item, w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     rc = _lib().spark_mx_gemv(cu.P(x), x.stride(0), cu.P(q), cu.P(sc), fmt, wes, ses, cu.P(y), w.n, items, rows_per_item,
@@ -139,6 +147,37 @@ def gemm_mxfp8(a_q, a_sf, w: Mxfp8Weight, out_f32=False):
     return c
 
 
+MX_MOE_TC = os.environ.get("SPARK_MX_MOE_TC", "0") == "1"
+
+
+def moe_mxfp4_tc(x, w: Mxfp4Weight, out_rows, max_items, tiles=None, ntile=None, pair_expert=None, pair_row=None,
+                 act=0, limit=0.0, out_f32=False):
+    """Grouped expert GEMM on the block-scaled tcgen05 path: MXFP8 activations (quantised here, SwiGLU of a
+    [gate | up] input first when act=1) x packed MXFP4 experts, the nibbles expanded by TMA on the way to shared
+    memory.  Work items come from the expert-sorted tile list (prefill) or from (token, expert) pairs (decode)."""
+    dev = x.device
+    E, N, K = w.packed.shape[0], w.n, w.k
+    a_q, a_sf = act_quant(x, block=32, act=act, limit=limit)
+    items = torch.empty(max_items, 4, dtype=torch.int32, device=dev)
+    n_items = torch.empty(1, dtype=torch.int32, device=dev)
+    mode = 0 if tiles is not None else 1
+    rc = _lib().spark_mx4_items(mode, cu.P(tiles), cu.P(ntile), cu.P(pair_expert), cu.P(pair_row),
+                                0 if mode == 0 else max_items, max_items, cu.P(items), cu.P(n_items), cu.stream())
+    cu.check(rc, "spark_mx4_items")
+    sfa = torch.empty(max_items, K // 128, 512, dtype=torch.uint8, device=dev)
+    rc = _lib().spark_mx_sf_tile_blocks(cu.P(a_sf), cu.P(items), cu.P(n_items), max_items, K // 32, cu.P(sfa), cu.stream())
+    cu.check(rc, "spark_mx_sf_tile_blocks")
+    wb = getattr(w, "_sf_blocks", None)
+    if wb is None or wb.device != dev:
+        wb = w._sf_blocks = sf_blocks(w.scales.reshape(E * N, K // 32))
+    c = torch.empty(out_rows, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+    rc = _lib().spark_moe_mxfp4(cu.P(a_q), a_q.stride(0), a_q.shape[0], cu.P(w.packed), cu.P(sfa), cu.P(wb), cu.P(items),
+                                cu.P(n_items), max_items, E, N, K, cu.P(c), N, int(out_f32),
+                                cu.P(cu.status_word(dev)), cu.stream())
+    cu.check(rc, "spark_moe_mxfp4")
+    return c
+
+
 def quant_linear(x, w: QuantWeight):
     x = cu._as_bf16(x).contiguous()
     if isinstance(w, Mxfp8Weight) and x.shape[0] <= 16:
@@ -157,7 +196,14 @@ def quant_linear(x, w: QuantWeight):
     return cu.dense_linear(x, _resident_bf16(w, x.device))
 
 
+MX_DECODE_TC = os.environ.get("SPARK_MX_DECODE_TC", "0") == "1"
+
+
 def expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
+    if MX_DECODE_TC and isinstance(w, Mxfp4Weight) and w.n % 128 == 0 and w.k % 128 == 0:
+        # decode pairs on the block-scaled tensor-core path (activations quantised to MXFP8)
+        return moe_mxfp4_tc(cu._as_bf16(x).contiguous(), w, pairs, pairs, pair_expert=pair_expert, pair_row=pair_row,
+                            act=act, limit=limit, out_f32=out_f32)
     return gemv(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act, limit=limit,
                 out_f32=out_f32)
 
@@ -180,6 +226,11 @@ def grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):
     """Rows in expert order through gate/up (+SwiGLU) and down; returns fp32 [P, H]."""
     E, F2, H = wgu.packed.shape[0] if isinstance(wgu, Mxfp4Weight) else wgu.q.shape[0], wgu.n, wgu.k
     dev = a.device
+    if MX_MOE_TC and isinstance(wgu, Mxfp4Weight) and F2 % 256 == 0 and H % 128 == 0:
+        # block-scaled tensor-core path: MXFP8 activations x packed MXFP4 experts, no decoded copy of the weights
+        Pn = a.shape[0]
+        gu = moe_mxfp4_tc(cu._as_bf16(a).contiguous(), wgu, Pn, max_tiles, tiles=tiles, ntile=ntile)
+        return moe_mxfp4_tc(gu, wd, Pn, max_tiles, tiles=tiles, ntile=ntile, act=1, limit=c.swiglu_limit, out_f32=True)
     if MX_MOE_FUSED and isinstance(wgu, Mxfp4Weight) and F2 % 128 == 0 and H % 128 == 0 and a.shape[0] <= 512 * E:
         # packed experts straight into the MMA: the weights cross HBM once, SwiGLU is applied while the down
         # projection stages its input

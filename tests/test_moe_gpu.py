@@ -95,15 +95,64 @@ def test_mxfp4_prefill_experts_fused_kernel_vs_dequant_path(H, F, R):
          "w_gu": Q.random_mxfp4(2 * F, H, 16, 0.05, 1, DEV), "w_down": Q.random_mxfp4(H, F, 16, 0.05, 2, DEV)}
     h = torch.randn(R, H, device=DEV, generator=g).bfloat16()
     outs = []
-    for fused in (True, False):
-        mx.MX_MOE_FUSED = fused
-        try:
+    mx.MX_MOE_TC = False
+    try:
+        for fused in (True, False):
+            mx.MX_MOE_FUSED = fused
             outs.append(ops.moe(h, w, c))
             if fused:
                 assert torch.equal(outs[0], ops.moe(h, w, c))
-        finally:
-            mx.MX_MOE_FUSED = True
+    finally:
+        mx.MX_MOE_FUSED = True
+        mx.MX_MOE_TC = True
     ref = _ref(h, w, c)
     for o in outs:
         err = ((o.float().cpu() - ref).norm() / ref.norm()).item()
         assert err < 2e-2, err
+    # block-scaled tensor-core path: same experts, activations quantised to MXFP8 on the way in
+    tc = ops.moe(h, w, c)
+    assert torch.equal(tc, ops.moe(h, w, c))
+    err = ((tc.float().cpu() - ref).norm() / ref.norm()).item()
+    assert err < 6e-2, err
+    assert ops.cuda_ops().read_status(torch.device(DEV))[0] == 0
+
+
+@pytest.mark.parametrize("mode", ["tiles", "pairs"])
+@pytest.mark.parametrize("N,K", [(256, 128), (512, 1024), (128, 4096)])
+def test_grouped_mxfp4_tensor_core_gemm_matches_dequantised_product(mode, N, K):
+    """tcgen05 block-scaled grouped GEMM (MXFP8 activations x packed MXFP4 experts, scales applied by the tensor
+    core) against the fp32 product of the dequantised operands, for expert-sorted tiles and for (token, expert)
+    pairs."""
+    from spark_engine_b200.ops import mx
+    E = 6
+    w = Q.random_mxfp4(N, K, E, 0.05, 3, DEV)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    if mode == "tiles":
+        counts = [150, 0, 3, 17, 128, 40]                    # rows per expert, in expert order
+        P = sum(counts)
+        x = (torch.randn(P, K, device=DEV, generator=g) * torch.exp(torch.randn(P, 1, device=DEV, generator=g))).bfloat16()
+        tl, r0 = [], 0
+        for e, n in enumerate(counts):
+            for a in range(r0, r0 + n, 128):
+                tl.append([a, r0 + n, e, 0])
+            r0 += n
+        max_items = len(tl) + 3
+        tiles = torch.tensor(tl + [[0, 0, 0, 0]] * 3, dtype=torch.int32, device=DEV)
+        ntile = torch.tensor([len(tl)], dtype=torch.int32, device=DEV)
+        y = mx.moe_mxfp4_tc(x, w, P, max_items, tiles=tiles, ntile=ntile, out_f32=True)
+        rows = [(p, p, e) for e, n in enumerate(counts) for p in range(sum(counts[:e]), sum(counts[:e]) + n)]
+    else:
+        T, P = 4, 10
+        x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+        pe = torch.tensor([0, 5, 2, -1, 3, 3, 1, 4, -1, 0], dtype=torch.int32, device=DEV)
+        pr = torch.tensor([0, 0, 1, 1, 2, 3, 3, 2, 0, 1], dtype=torch.int32, device=DEV)
+        y = mx.moe_mxfp4_tc(x, w, P, P, pair_expert=pe, pair_row=pr, out_f32=True)
+        rows = [(p, int(pr[p]), int(pe[p])) for p in range(P) if int(pe[p]) >= 0]
+    torch.cuda.synchronize()
+    assert ops.cuda_ops().read_status(torch.device(DEV))[0] == 0
+    aq, asf = mx.act_quant(x, block=32)
+    xd = Q.dequant_mxfp8(aq.cpu(), asf.cpu()).double()
+    for out_row, a_row, e in rows:
+        ref = xd[a_row] @ w.dequant_expert(e).double().t()
+        err = ((y[out_row].cpu().double() - ref).norm() / ref.norm().clamp_min(1e-12)).item()
+        assert err < 1e-5, (out_row, a_row, e, err)
