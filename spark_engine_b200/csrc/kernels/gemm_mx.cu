@@ -13,7 +13,6 @@
 // Every wait is bounded (status word + normal teardown).  Reference paths replaced: engine-rs/shim/ds41_mx.cu
 // fp8_gemm_mx* (warp-level block-scaled mma.sync), fp8.cu / fp8pf.cu (wmma + scale promotion).
 #include "../common/ptx.cuh"
-#include <cstdlib>
 #include <mutex>
 
 namespace spark {
@@ -222,17 +221,34 @@ struct Mx4Args {
   const uint8_t* sfw;         // [E * N/128][K/128][512]
   void* C; int ldc; int out_f32;
   int* status;
-  uint32_t w_tx_bytes;        // bytes one weight tile adds to the stage barrier's transaction count
+  uint32_t w_tx_bytes;        // bytes one weight tile adds to the stage barrier's transaction count (packed size)
 };
 
+// SMALL: every item has <= 16 rows.  The activation box is 2 KB, so a stage shrinks to 19 KB and ten stages fit:
+// twice the weight bytes in flight per SM, which is what a GEMV-shaped problem is bound by.  The MMA still reads a
+// 128-row A tile; with the A regions packed first in shared memory, rows 16..127 of a stage's tile alias the
+// following A and B regions (allocated memory with arbitrary contents: those accumulator rows are never stored).
+template <bool SMALL>
+struct Mx4Cfg {
+  static constexpr int STAGES = SMALL ? 10 : MX_STAGES;
+  static constexpr int A_REGION = SMALL ? 16 * MX_BK : MX_A_BYTES;
+  static constexpr int B_OFF = STAGES * A_REGION;
+  static constexpr int SF_OFF = B_OFF + STAGES * MX_B_BYTES;
+  static constexpr int BAR_OFF = SF_OFF + STAGES * 2 * MX_SF_BYTES;
+  static constexpr int SMEM = BAR_OFF + 256 + 1024;
+};
+
+template <bool SMALL>
 __global__ void __launch_bounds__(MX_THREADS, 1)
 moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA16,
                  const __grid_constant__ CUtensorMap tmW, Mx4Args g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + MX_STAGES * MX_STAGE_BYTES);
-  uint64_t* empty_bar = full_bar + MX_STAGES;
-  uint64_t* tmem_full = empty_bar + MX_STAGES;
+  using Cfg = Mx4Cfg<SMALL>;
+  constexpr int STAGES = Cfg::STAGES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + MX_ACC_STAGES;
   uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(tmem_empty + MX_ACC_STAGES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -245,7 +261,7 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmA16);
     tma_prefetch_desc(&tmW);
-    for (int s = 0; s < MX_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < MX_ACC_STAGES; ++s) { mbar_init(&tmem_full[s], 1); mbar_init(&tmem_empty[s], 4); }
     fence_barrier_init();
   }
@@ -262,22 +278,23 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int it = t / nt_n, nt = t - it * nt_n;
         const int4 item = g.items[it];
         if (item.z < 0 || item.y <= 0) continue;                 // expert of another rank / empty item
-        const bool small = item.y <= 16;
+        if (SMALL && item.y > 16) { set_status(g.status, ST_BOUNDS, blockIdx.x, t, item.y); break; }
+        const bool small = SMALL || item.y <= 16;
         const uint32_t a_bytes = small ? 16 * MX_BK : MX_A_BYTES;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, kb); ok = false; break;
           }
-          uint8_t* a_dst = smem + stage * MX_STAGE_BYTES;
-          uint8_t* b_dst = a_dst + MX_A_BYTES;
-          uint8_t* sfa_dst = b_dst + MX_B_BYTES;
+          uint8_t* a_dst = smem + stage * Cfg::A_REGION;
+          uint8_t* b_dst = smem + Cfg::B_OFF + stage * MX_B_BYTES;
+          uint8_t* sfa_dst = smem + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], a_bytes + g.w_tx_bytes + 2 * MX_SF_BYTES);
           tma_load_2d(a_dst, small ? &tmA16 : &tmA, &full_bar[stage], kb * MX_BK, item.x);
           tma_load_2d(b_dst, &tmW, &full_bar[stage], kb * MX_BK, item.z * g.N + nt * MX_BN);
           bulk_load(sfa_dst, g.sfa + (static_cast<size_t>(it) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
           bulk_load(sfa_dst + MX_SF_BYTES,
                     g.sfw + (static_cast<size_t>(item.z * nt_n + nt) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
-          if (++stage == MX_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -298,19 +315,20 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             set_status(g.status, ST_TIMEOUT_MBAR_FULL, blockIdx.x, t, kb); ok = false; break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * MX_STAGE_BYTES);
-          const uint64_t a_desc = make_smem_desc_sw128(a_addr);
-          const uint64_t b_desc = make_smem_desc_sw128(a_addr + MX_A_BYTES);
+          const uint32_t s0 = smem_u32(smem);
+          const uint64_t a_desc = make_smem_desc_sw128(s0 + stage * Cfg::A_REGION);
+          const uint64_t b_desc = make_smem_desc_sw128(s0 + Cfg::B_OFF + stage * MX_B_BYTES);
+          const uint32_t sf_addr = s0 + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;
           const uint32_t tsfa = tmem_base + MX_SF_COL0 + stage * 8, tsfb = tsfa + 4;
-          tmem_cp_32x128b_x4(tsfa, make_sf_desc(a_addr + MX_A_BYTES + MX_B_BYTES));
-          tmem_cp_32x128b_x4(tsfb, make_sf_desc(a_addr + MX_A_BYTES + MX_B_BYTES + MX_SF_BYTES));
+          tmem_cp_32x128b_x4(tsfa, make_sf_desc(sf_addr));
+          tmem_cp_32x128b_x4(tsfb, make_sf_desc(sf_addr + MX_SF_BYTES));
 #pragma unroll
           for (int k = 0; k < MX_BK / 32; ++k) {
             const uint32_t idesc = idesc0 | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
             umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsfa, tsfb, (kb | k) != 0);
           }
           umma_commit(&empty_bar[stage]);
-          if (++stage == MX_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);
@@ -498,10 +516,10 @@ extern "C" int spark_mx_sf_tile_blocks(const void* sf, const void* items, const 
 
 // A e4m3 [rows_a, K] (row stride lda bytes); W packed e2m1 [E * N, K / 2]; sfa item-local blocks
 // (spark_mx_sf_tile_blocks), sfw blocks of the flattened [E * N, K / 32] scales (spark_mx_sf_to_blocks);
-// C [*, ldc] bf16 or fp32.  N % 128 == 0, K % 128 == 0.
+// C [*, ldc] bf16 or fp32.  N % 128 == 0, K % 128 == 0.  small != 0: every item has <= 16 rows (ten-stage variant).
 extern "C" int spark_moe_mxfp4(const void* A, int lda, int rows_a, const void* W, const void* sfa, const void* sfw,
                                const void* items, const int* n_items, int max_items, int E, int N, int K, void* C, int ldc,
-                               int out_f32, int* status, cudaStream_t stream) {
+                               int out_f32, int small, int* status, cudaStream_t stream) {
   if (max_items <= 0 || rows_a <= 0) return 0;
   if (K % MX_BK || N % MX_BN || (ldc & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -5;
   CUtensorMap tA, tA16, tW;
@@ -511,14 +529,21 @@ extern "C" int spark_moe_mxfp4(const void* A, int lda, int rows_a, const void* W
   if (r) return r;
   r = make_tmap_u4(&tW, W, static_cast<uint64_t>(E) * N, K);
   if (r) return r - 10;
-  static const uint32_t w_tx = [] { const char* e = getenv("SPARK_MX4_WTX"); return e ? (uint32_t)atoi(e) : (uint32_t)MX_B_BYTES; }();
+  // a 16U4_ALIGN16B copy completes the barrier with the packed bytes it read (64 per row), not the 128 it writes
+  const uint32_t w_tx = MX_B_BYTES / 2;
   Mx4Args g{(const int4*)items, n_items, max_items, N, K, (const uint8_t*)sfa, (const uint8_t*)sfw, C, ldc, out_f32, status, w_tx};
   static bool attr_done = false;
-  if (!attr_done) { cudaFuncSetAttribute(moe_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM); attr_done = true; }
+  if (!attr_done) {
+    cudaFuncSetAttribute(moe_mxfp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Cfg<false>::SMEM);
+    cudaFuncSetAttribute(moe_mxfp4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Cfg<true>::SMEM);
+    attr_done = true;
+  }
   static int sms = 0;
   if (!sms) { int dev; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   const long long tiles = static_cast<long long>(max_items) * (N / MX_BN);
-  moe_mxfp4_kernel<<<tiles < sms ? static_cast<int>(tiles) : sms, MX_THREADS, MX_SMEM, stream>>>(tA, tA16, tW, g);
+  const int grid = tiles < sms ? static_cast<int>(tiles) : sms;
+  if (small) moe_mxfp4_kernel<true><<<grid, MX_THREADS, Mx4Cfg<true>::SMEM, stream>>>(tA, tA16, tW, g);
+  else moe_mxfp4_kernel<false><<<grid, MX_THREADS, Mx4Cfg<false>::SMEM, stream>>>(tA, tA16, tW, g);
   return spark_launch_rc(__func__);
 }
 

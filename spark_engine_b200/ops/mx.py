@@ -29,7 +29,7 @@ _SIGS = {
     "spark_mx_mgemm": [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "spark_mx4_items": [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp],
     "spark_mx_sf_tile_blocks": [_vp, _vp, _vp, _i32, _i32, _vp, _vp],
-    "spark_moe_mxfp4": [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp, _vp],
+    "spark_moe_mxfp4": [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _vp],
     "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
 }
 _bound = False
@@ -147,7 +147,7 @@ def gemm_mxfp8(a_q, a_sf, w: Mxfp8Weight, out_f32=False):
     return c
 
 
-MX_MOE_TC = os.environ.get("SPARK_MX_MOE_TC", "0") == "1"
+MX_MOE_TC = os.environ.get("SPARK_MX_MOE_TC", "1") == "1"
 
 
 def moe_mxfp4_tc(x, w: Mxfp4Weight, out_rows, max_items, tiles=None, ntile=None, pair_expert=None, pair_row=None,
@@ -172,7 +172,7 @@ def moe_mxfp4_tc(x, w: Mxfp4Weight, out_rows, max_items, tiles=None, ntile=None,
         wb = w._sf_blocks = sf_blocks(w.scales.reshape(E * N, K // 32))
     c = torch.empty(out_rows, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
     rc = _lib().spark_moe_mxfp4(cu.P(a_q), a_q.stride(0), a_q.shape[0], cu.P(w.packed), cu.P(sfa), cu.P(wb), cu.P(items),
-                                cu.P(n_items), max_items, E, N, K, cu.P(c), N, int(out_f32),
+                                cu.P(n_items), max_items, E, N, K, cu.P(c), N, int(out_f32), int(mode == 1),
                                 cu.P(cu.status_word(dev)), cu.stream())
     cu.check(rc, "spark_moe_mxfp4")
     return c
@@ -196,7 +196,7 @@ def quant_linear(x, w: QuantWeight):
     return cu.dense_linear(x, _resident_bf16(w, x.device))
 
 
-MX_DECODE_TC = os.environ.get("SPARK_MX_DECODE_TC", "0") == "1"
+MX_DECODE_TC = os.environ.get("SPARK_MX_DECODE_TC", "1") == "1"
 
 
 def expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):

@@ -95,7 +95,7 @@ def test_mxfp4_prefill_experts_fused_kernel_vs_dequant_path(H, F, R):
          "w_gu": Q.random_mxfp4(2 * F, H, 16, 0.05, 1, DEV), "w_down": Q.random_mxfp4(H, F, 16, 0.05, 2, DEV)}
     h = torch.randn(R, H, device=DEV, generator=g).bfloat16()
     outs = []
-    mx.MX_MOE_TC = False
+    mx.MX_MOE_TC = mx.MX_DECODE_TC = False           # bf16-activation paths first
     try:
         for fused in (True, False):
             mx.MX_MOE_FUSED = fused
@@ -104,7 +104,7 @@ def test_mxfp4_prefill_experts_fused_kernel_vs_dequant_path(H, F, R):
                 assert torch.equal(outs[0], ops.moe(h, w, c))
     finally:
         mx.MX_MOE_FUSED = True
-        mx.MX_MOE_TC = True
+        mx.MX_MOE_TC = mx.MX_DECODE_TC = True
     ref = _ref(h, w, c)
     for o in outs:
         err = ((o.float().cpu() - ref).norm() / ref.norm()).item()
