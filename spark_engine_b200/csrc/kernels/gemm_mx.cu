@@ -13,6 +13,7 @@
 // Every wait is bounded (status word + normal teardown).  Reference paths replaced: engine-rs/shim/ds41_mx.cu
 // fp8_gemm_mx* (warp-level block-scaled mma.sync), fp8.cu / fp8pf.cu (wmma + scale promotion).
 #include "../common/ptx.cuh"
+#include <cstdlib>
 #include <mutex>
 
 namespace spark {
@@ -21,6 +22,7 @@ constexpr int MX_BM = 128, MX_BN = 128, MX_BK = 128;       // BK in elements = b
 constexpr int MX_STAGES = 5;
 constexpr int MX_ACC_STAGES = 2;
 constexpr int MX_THREADS = 192;
+constexpr int MX4_THREADS = 224;       // grouped MXFP4 kernel: + one warp that fetches the scale blocks
 constexpr int MX_A_BYTES = MX_BM * MX_BK, MX_B_BYTES = MX_BN * MX_BK, MX_SF_BYTES = 512;
 constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;
 constexpr int MX_SMEM = MX_STAGES * MX_STAGE_BYTES + 256 + 1024;
@@ -222,12 +224,13 @@ struct Mx4Args {
   void* C; int ldc; int out_f32;
   int* status;
   uint32_t w_tx_bytes;        // bytes one weight tile adds to the stage barrier's transaction count (packed size)
+  int burst;                  // k-blocks whose tile loads are issued together (1 .. stages / 2)
 };
 
-// SMALL: every item has <= 16 rows.  The activation box is 2 KB, so a stage shrinks to 19 KB and ten stages fit:
-// twice the weight bytes in flight per SM, which is what a GEMV-shaped problem is bound by.  The MMA still reads a
-// 128-row A tile; with the A regions packed first in shared memory, rows 16..127 of a stage's tile alias the
-// following A and B regions (allocated memory with arbitrary contents: those accumulator rows are never stored).
+// SMALL: every item has <= 16 rows (decode pairs).  The operands are swapped: the weight tile is the 128-row M
+// operand, the 16-row activation box the N operand, so the accumulator is [128 weight rows, 16 activation rows] and
+// the tensor pipe does an eighth of the work per weight byte.  A stage is 19 KB (2 KB activations, 16 KB weights,
+// two scale blocks) and ten stages fit.
 template <bool SMALL>
 struct Mx4Cfg {
   static constexpr int STAGES = SMALL ? 10 : MX_STAGES;
@@ -239,7 +242,7 @@ struct Mx4Cfg {
 };
 
 template <bool SMALL>
-__global__ void __launch_bounds__(MX_THREADS, 1)
+__global__ void __launch_bounds__(MX4_THREADS, 1)
 moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA16,
                  const __grid_constant__ CUtensorMap tmW, Mx4Args g) {
   extern __shared__ uint8_t smem_raw[];
@@ -261,7 +264,7 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmA16);
     tma_prefetch_desc(&tmW);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }    // two producers
     for (int s = 0; s < MX_ACC_STAGES; ++s) { mbar_init(&tmem_full[s], 1); mbar_init(&tmem_empty[s], 4); }
     fence_barrier_init();
   }
@@ -281,30 +284,66 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (SMALL && item.y > 16) { set_status(g.status, ST_BOUNDS, blockIdx.x, t, item.y); break; }
         const bool small = SMALL || item.y <= 16;
         const uint32_t a_bytes = small ? 16 * MX_BK : MX_A_BYTES;
+        // the tile loads can go out in bursts of `burst` k-blocks (adjacent 64-byte row pieces requested together);
+        // measured neutral on B200, so the default is 1
+        for (int kb0 = 0; kb0 < num_k && ok; kb0 += g.burst) {
+          const int nb = min(g.burst, num_k - kb0);
+          int st = stage; uint32_t ph = phase;
+          for (int j = 0; j < nb; ++j) {
+            if (!mbar_wait(&empty_bar[st], ph ^ 1)) {
+              set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, kb0 + j); ok = false; break;
+            }
+            if (++st == STAGES) { st = 0; ph ^= 1; }
+          }
+          if (!ok) break;
+          for (int j = 0; j < nb; ++j) {
+            const int kb = kb0 + j;
+            uint8_t* a_dst = smem + stage * Cfg::A_REGION;
+            uint8_t* b_dst = smem + Cfg::B_OFF + stage * MX_B_BYTES;
+            mbar_arrive_expect_tx(&full_bar[stage], a_bytes + g.w_tx_bytes);
+            tma_load_2d(a_dst, small ? &tmA16 : &tmA, &full_bar[stage], kb * MX_BK, item.x);
+            tma_load_2d(b_dst, &tmW, &full_bar[stage], kb * MX_BK, item.z * g.N + nt * MX_BN);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // second producer: the two scale blocks of every stage, so that the tile loads and the scale copies are issued
+    // by different threads
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int it = t / nt_n, nt = t - it * nt_n;
+        const int4 item = g.items[it];
+        if (item.z < 0 || item.y <= 0) continue;
+        if (SMALL && item.y > 16) break;
+        const uint8_t* sa = g.sfa + static_cast<size_t>(it) * num_k * MX_SF_BYTES;
+        const uint8_t* sw = g.sfw + static_cast<size_t>(item.z * nt_n + nt) * num_k * MX_SF_BYTES;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, kb); ok = false; break;
+            set_status(g.status, ST_TIMEOUT_MBAR_EMPTY, blockIdx.x, t, -kb - 1); ok = false; break;
           }
-          uint8_t* a_dst = smem + stage * Cfg::A_REGION;
-          uint8_t* b_dst = smem + Cfg::B_OFF + stage * MX_B_BYTES;
-          uint8_t* sfa_dst = smem + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], a_bytes + g.w_tx_bytes + 2 * MX_SF_BYTES);
-          tma_load_2d(a_dst, small ? &tmA16 : &tmA, &full_bar[stage], kb * MX_BK, item.x);
-          tma_load_2d(b_dst, &tmW, &full_bar[stage], kb * MX_BK, item.z * g.N + nt * MX_BN);
-          bulk_load(sfa_dst, g.sfa + (static_cast<size_t>(it) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
-          bulk_load(sfa_dst + MX_SF_BYTES,
-                    g.sfw + (static_cast<size_t>(item.z * nt_n + nt) * num_k + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
+          uint8_t* sf_dst = smem + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], 2 * MX_SF_BYTES);
+          bulk_load(sf_dst, sa + static_cast<size_t>(kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
+          bulk_load(sf_dst + MX_SF_BYTES, sw + static_cast<size_t>(kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc0 = make_idesc_mx(MX_BM, MX_BN) | (5u << 10);       // B format e2m1
+      // 128-row tiles: D[activation rows, weight rows], weights are operand B (format e2m1 in bits [10,13)).
+      // SMALL: operands swapped, D[weight rows, 16 activation rows]: the MMA is 128 x 16 x 32 instead of
+      // 128 x 128 x 32, an eighth of the tensor-pipe time per weight byte, which is what lets the decode shape run at
+      // memory speed (with the 128-wide form the tensor pipe, padded 1 row -> 128, was the limit at 0.4 us per stage).
+      const uint32_t idesc0 = SMALL ? (make_idesc_mx(MX_BN, 16) | (5u << 7)) : (make_idesc_mx(MX_BM, MX_BN) | (5u << 10));
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int4 item = g.items[t / nt_n];
         if (item.z < 0 || item.y <= 0) continue;
+        if (SMALL && item.y > 16) break;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) {
           set_status(g.status, ST_TIMEOUT_TMEM_EMPTY, blockIdx.x, t, acc); break;
         }
@@ -316,12 +355,13 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tc_fence_after();
           const uint32_t s0 = smem_u32(smem);
-          const uint64_t a_desc = make_smem_desc_sw128(s0 + stage * Cfg::A_REGION);
-          const uint64_t b_desc = make_smem_desc_sw128(s0 + Cfg::B_OFF + stage * MX_B_BYTES);
-          const uint32_t sf_addr = s0 + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;
+          const uint64_t x_desc = make_smem_desc_sw128(s0 + stage * Cfg::A_REGION);            // activations
+          const uint64_t w_desc = make_smem_desc_sw128(s0 + Cfg::B_OFF + stage * MX_B_BYTES);  // weights
+          const uint64_t a_desc = SMALL ? w_desc : x_desc, b_desc = SMALL ? x_desc : w_desc;
+          const uint32_t sf_addr = s0 + Cfg::SF_OFF + stage * 2 * MX_SF_BYTES;                 // [activations | weights]
           const uint32_t tsfa = tmem_base + MX_SF_COL0 + stage * 8, tsfb = tsfa + 4;
-          tmem_cp_32x128b_x4(tsfa, make_sf_desc(sf_addr));
-          tmem_cp_32x128b_x4(tsfb, make_sf_desc(sf_addr + MX_SF_BYTES));
+          tmem_cp_32x128b_x4(tsfa, make_sf_desc(sf_addr + (SMALL ? MX_SF_BYTES : 0)));
+          tmem_cp_32x128b_x4(tsfb, make_sf_desc(sf_addr + (SMALL ? 0 : MX_SF_BYTES)));
 #pragma unroll
           for (int k = 0; k < MX_BK / 32; ++k) {
             const uint32_t idesc = idesc0 | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
@@ -348,6 +388,21 @@ moe_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int r = quarter * 32 + lane;
       const uint32_t t_addr = tmem_base + acc * MX_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (SMALL) {
+        // lane = weight row (output column), TMEM column j = activation row j of the item
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr, v);
+        tmem_ld_wait();
+        const int col = nt * MX_BN + r;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j < item.y) {
+            const size_t o = (static_cast<size_t>(item.w) + j) * g.ldc + col;
+            if (g.out_f32) reinterpret_cast<float*>(g.C)[o] = __uint_as_float(v[j]);
+            else reinterpret_cast<__nv_bfloat16*>(g.C)[o] = __float2bfloat16(__uint_as_float(v[j]));
+          }
+        }
+      } else
       // a warp whose 32 rows all lie past the item's rows has nothing to read
       if (quarter * 32 < item.y) {
 #pragma unroll 1
@@ -531,7 +586,13 @@ extern "C" int spark_moe_mxfp4(const void* A, int lda, int rows_a, const void* W
   if (r) return r - 10;
   // a 16U4_ALIGN16B copy completes the barrier with the packed bytes it read (64 per row), not the 128 it writes
   const uint32_t w_tx = MX_B_BYTES / 2;
-  Mx4Args g{(const int4*)items, n_items, max_items, N, K, (const uint8_t*)sfa, (const uint8_t*)sfw, C, ldc, out_f32, status, w_tx};
+  static const int burst_env = [] { const char* e = getenv("SPARK_MX4_BURST"); return e ? atoi(e) : 0; }();   // tuning knob
+  int burst = burst_env > 0 ? burst_env : 1;
+  const int max_burst = (small ? Mx4Cfg<true>::STAGES : Mx4Cfg<false>::STAGES) / 2;
+  if (burst > max_burst) burst = max_burst;
+  if (burst < 1) burst = 1;
+  Mx4Args g{(const int4*)items, n_items, max_items, N, K, (const uint8_t*)sfa, (const uint8_t*)sfw, C, ldc, out_f32, status, w_tx,
+            burst};
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(moe_mxfp4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Cfg<false>::SMEM);
@@ -542,8 +603,8 @@ extern "C" int spark_moe_mxfp4(const void* A, int lda, int rows_a, const void* W
   if (!sms) { int dev; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   const long long tiles = static_cast<long long>(max_items) * (N / MX_BN);
   const int grid = tiles < sms ? static_cast<int>(tiles) : sms;
-  if (small) moe_mxfp4_kernel<true><<<grid, MX_THREADS, Mx4Cfg<true>::SMEM, stream>>>(tA, tA16, tW, g);
-  else moe_mxfp4_kernel<false><<<grid, MX_THREADS, Mx4Cfg<false>::SMEM, stream>>>(tA, tA16, tW, g);
+  if (small) moe_mxfp4_kernel<true><<<grid, MX4_THREADS, Mx4Cfg<true>::SMEM, stream>>>(tA, tA16, tW, g);
+  else moe_mxfp4_kernel<false><<<grid, MX4_THREADS, Mx4Cfg<false>::SMEM, stream>>>(tA, tA16, tW, g);
   return spark_launch_rc(__func__);
 }
 

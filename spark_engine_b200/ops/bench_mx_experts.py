@@ -5,7 +5,9 @@
 Decode: `pairs` (token, expert) pairs with distinct experts through the GEMV (gate/up, then SwiGLU + down) and,
 with --tc, through the block-scaled tensor-core kernel.  Prefill: `tokens` x top-6 rows in expert order through
 the fused grouped kernel and the tensor-core kernel.  CUDA-event timed, median of the iterations, L2 flushed by a
-256 MB write before every timed launch.  One JSON line per measurement.
+256 MB write before every timed launch.  One JSON line per measurement.  The tensor-core calls are four launches
+(activation quantiser, work items, scale blocks, GEMM): time them with --graph, without it the host launch path of the
+small decode case is what the events see.
 """
 from __future__ import annotations
 
@@ -23,6 +25,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tc", action="store_true", help="also time the block-scaled tcgen05 path")
     ap.add_argument("--once", action="store_true", help="one launch of each kernel, no timing (profiler runs)")
+    ap.add_argument("--graph", action="store_true", help="time each call as a captured CUDA graph (as the decode "
+                    "rounds run it): removes the host launch path of multi-kernel calls from the measurement")
     a = ap.parse_args()
     from . import cuda as cu
     from . import mx
@@ -43,6 +47,13 @@ def main():
             torch.cuda.synchronize()
             return float("nan")
         for _ in range(3):
+            fn()
+        if a.graph:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            fn = gr.replay
             fn()
         ts = []
         for _ in range(a.iters):
