@@ -81,7 +81,7 @@ def reference_arm(args):
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference is a Rust binary + sm_121-only CUDA shim with no setup.py/pyproject.toml: "
-                       "`pip install --target baseline/_ref /root/reference` fails (not installable), no Rust toolchain offline",
+                       "`pip install --target baseline/_ref <reference checkout>` fails (not installable), no Rust toolchain offline",
     }))
     return 0
 

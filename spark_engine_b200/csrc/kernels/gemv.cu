@@ -24,12 +24,18 @@ template <int RB, typename TO>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                  long long expert_stride, int ldw, TO* __restrict__ y, int ldy, int rows_per_item, int N, int K,
-                 const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit) {
+                 const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit,
+                 long long x_item_stride, long long y_item_stride) {
   extern __shared__ __align__(16) uint8_t smem_gemv[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [RB][K]
   const int item = blockIdx.y;
   if (pair_expert && pair_expert[item] < 0) return;      // pair of an expert that lives on another rank
-  const int xr0 = pair_row ? pair_row[item] : item * rows_per_item;
+  // strided items (either stride non-zero): item i reads rows x + i * x_item_stride + r * ldx and writes rows
+  // y + i * y_item_stride + r * ldy, e.g. the per-head slices of a [rows, heads, dim] tensor
+  const bool strided = (x_item_stride | y_item_stride) != 0;
+  if (strided) { x += item * x_item_stride; y += item * y_item_stride; }
+  const int xr0 = strided ? 0 : (pair_row ? pair_row[item] : item * rows_per_item);
+  const int yr0 = strided ? 0 : item * rows_per_item;
   const __nv_bfloat16* Wb = W + (pair_expert ? static_cast<long long>(pair_expert[item]) * expert_stride : 0);
   const int R = rows_per_item;
   // stage activations (zero rows beyond R); plain rows are copied as 16-byte vectors
@@ -97,7 +103,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
       if (r < R) {
-        TO* yr = y + static_cast<size_t>(item * rows_per_item + r) * ldy;
+        TO* yr = y + static_cast<size_t>(yr0 + r) * ldy;
         yr[n0] = static_cast<TO>(acc0[r]);
         if (two) yr[n0 + 1] = static_cast<TO>(acc1[r]);
       }
@@ -107,7 +113,8 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
 
 template <int RB, typename TO>
 static int launch_gemv(const void* x, int ldx, const void* W, long long es, int ldw, void* y, int ldy, int items,
-                       int rows, int N, int K, const int* pe, const int* pr, int act, float limit, cudaStream_t s) {
+                       int rows, int N, int K, const int* pe, const int* pr, int act, float limit, cudaStream_t s,
+                       long long xis = 0, long long yis = 0) {
   auto kern = gemv_bf16_kernel<RB, TO>;
   const int smem = RB * K * 2;
   if (smem > 48 * 1024) {
@@ -117,7 +124,7 @@ static int launch_gemv(const void* x, int ldx, const void* W, long long es, int 
   if (smem > 200 * 1024) return -6;
   dim3 grid((N + GEMV_WARPS * GEMV_COLS - 1) / (GEMV_WARPS * GEMV_COLS), items);
   kern<<<grid, GEMV_WARPS * 32, smem, s>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, es, ldw, (TO*)y, ldy,
-                                            rows, N, K, pe, pr, act, limit);
+                                            rows, N, K, pe, pr, act, limit, xis, yis);
   return spark_launch_rc(__func__);
 }
 
@@ -143,5 +150,29 @@ extern "C" int spark_gemv_bf16(const void* x, int ldx, const void* W, long long 
   SPARK_GEMV_CASE(8)
   SPARK_GEMV_CASE(16)
 #undef SPARK_GEMV_CASE
+  return -5;
+}
+
+// Strided items: item i multiplies rows x + i * x_item_stride + r * ldx (r < rows_per_item) by expert
+// pair_expert[i] (or W itself) and writes y + i * y_item_stride + r * ldy.  Used for per-head projections of
+// [rows, heads, dim] tensors: every head's matrix is streamed once for all rows.  Strides in elements; the item
+// offsets must keep x 16-byte aligned.
+extern "C" int spark_gemv_bf16_items(const void* x, int ldx, long long x_item_stride, const void* W, long long expert_stride,
+                                     int ldw, void* y, int ldy, long long y_item_stride, int items, int rows_per_item, int N,
+                                     int K, const int* pair_expert, int out_f32, cudaStream_t s) {
+  if (items <= 0 || rows_per_item <= 0) return 0;
+  if (K % 8 || rows_per_item > 16 || (x_item_stride & 7) || (ldx & 7) || (x_item_stride | y_item_stride) == 0) return -5;
+#define SPARK_GEMV_ITEMS(RB)                                                                                         \
+  if (rows_per_item <= RB)                                                                                           \
+    return out_f32 ? launch_gemv<RB, float>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N, K,       \
+                                            pair_expert, nullptr, 0, 0.f, s, x_item_stride, y_item_stride)           \
+                   : launch_gemv<RB, __nv_bfloat16>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N,  \
+                                                    K, pair_expert, nullptr, 0, 0.f, s, x_item_stride, y_item_stride);
+  SPARK_GEMV_ITEMS(1)
+  SPARK_GEMV_ITEMS(2)
+  SPARK_GEMV_ITEMS(4)
+  SPARK_GEMV_ITEMS(8)
+  SPARK_GEMV_ITEMS(16)
+#undef SPARK_GEMV_ITEMS
   return -5;
 }

@@ -27,6 +27,7 @@ _SIGS = {
     "spark_gemm_bf16_swiglu": [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
     "spark_gemm_grouped_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, f32, i32, vp, vp],
     "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp],
+    "spark_gemv_bf16_items": [vp, i32, i64, vp, i64, i32, vp, i32, i64, i32, i32, i32, i32, vp, i32, vp],
     "spark_add_rmsnorm": [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp],
@@ -209,6 +210,16 @@ def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None
                                items, rows_per_item, n, k, P(pair_expert), P(pair_row), act, float(limit), int(out_f32),
                                stream())
     check(rc, "spark_gemv_bf16")
+    return y
+
+
+def gemv_bf16_items(x, ldx, x_item_stride, w, expert_stride, ldw, y, ldy, y_item_stride, items, rows_per_item, n, k,
+                    pair_expert):
+    """Per-item GEMV over strided slices: item i multiplies rows x[i * x_item_stride + r * ldx] (r < rows_per_item) by
+    matrix pair_expert[i] of `w` and writes y[i * y_item_stride + r * ldy].  Strides in elements."""
+    rc = lib().spark_gemv_bf16_items(P(x), ldx, x_item_stride, P(w), expert_stride, ldw, P(y), ldy, y_item_stride, items,
+                                     rows_per_item, n, k, P(pair_expert), int(y.dtype == torch.float32), stream())
+    check(rc, "spark_gemv_bf16_items")
     return y
 
 
@@ -673,15 +684,13 @@ def mla_mixer(mixer, h, plan, seqs):
     q_full = torch.empty(R, H, KW, dtype=torch.bfloat16, device=dev)
     decode = R * H <= 4096 and R <= 16
     if decode:
-        key = ("mla_pairs", R, H)
+        key = ("mla_heads", H)
         if key not in md:
-            md[key] = (torch.arange(H, dtype=torch.int32, device=dev).repeat(R).contiguous(),
-                       torch.arange(R * H, dtype=torch.int32, device=dev))
-        pe, pr = md[key]
+            md[key] = torch.arange(H, dtype=torch.int32, device=dev)
+        heads = md[key]
         qn = qb[:, :nq].contiguous()
-        # absorb W_uk: one (row, head) pair per item, the head's [L, D] matrix as the "expert"
-        gemv_bf16(qn, md["w_ukT"], items=R * H, rows_per_item=1, pair_expert=pe, pair_row=pr, expert_stride=L * D, n=L, k=D,
-                  out=q_full.view(R * H, KW), ldx=D + Rr)
+        # absorb W_uk: one item per head over all rows (the head's [L, D] matrix is streamed once for the round)
+        gemv_bf16_items(qn, H * (D + Rr), D + Rr, md["w_ukT"], L * D, D, q_full, H * KW, KW, H, R, L, D, heads)
     else:
         q_full[..., :L] = torch.einsum("thd,hld->thl", qb[:, :nq].view(R, H, D + Rr)[..., :D], md["w_ukT"])
     if Rr:
@@ -706,9 +715,8 @@ def mla_mixer(mixer, h, plan, seqs):
                               1.0 / math.sqrt(D + Rr), P(out_lat), stream())
     check(rc, "spark_mla_attn")
     if decode:
-        pe, pr = md[("mla_pairs", R, H)]
-        return gemv_bf16(out_lat.view(R * H, L), md["w_uv"], items=R * H, rows_per_item=1, pair_expert=pe, pair_row=pr,
-                         expert_stride=D * L, n=D, k=L).view(R, H * D)
+        out = torch.empty(R, H * D, dtype=torch.bfloat16, device=dev)
+        return gemv_bf16_items(out_lat, H * L, L, md["w_uv"], D * L, L, out, H * D, D, H, R, D, L, md[("mla_heads", H)])
     return torch.einsum("thl,hdl->thd", out_lat, md["w_uv"]).reshape(R, H * D)
 
 
