@@ -488,6 +488,39 @@ __global__ void mx_sf_tile_blocks_kernel(const uint8_t* __restrict__ sf, const i
   }
 }
 
+// Work items and their activation scale blocks in one launch (one block per item): the decode path runs this twice
+// per MoE layer, and a launch saved there is worth more than the few redundant loads.
+__global__ void mx4_prep_kernel(int mode, const int4* __restrict__ tiles, const int* __restrict__ ntile,
+                                const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int pairs,
+                                int max_items, const uint8_t* __restrict__ sf, int kblocks32, int4* __restrict__ items,
+                                int* __restrict__ n_items, uint8_t* __restrict__ out) {
+  const int i = blockIdx.x;
+  const int n = mode == 0 ? min(*ntile, max_items) : min(pairs, max_items);
+  int4 item = make_int4(0, 0, -1, 0);
+  if (i < n) {
+    if (mode == 0) {
+      const int4 td = tiles[i];
+      item = make_int4(td.x, min(128, td.y - td.x), td.z, td.x);
+    } else {
+      item = make_int4(pair_row ? pair_row[i] : i, 1, pair_expert[i], i);
+    }
+  }
+  if (threadIdx.x == 0) {
+    items[i] = item;
+    if (i == 0) *n_items = n;
+  }
+  if (i >= n) return;
+  const int kb128 = kblocks32 >> 2;
+  for (int j = threadIdx.x; j < kb128 * 512; j += blockDim.x) {
+    const int kt = j >> 9, within = j & 511;
+    const int r32 = within >> 4, q = (within >> 2) & 3, kk = within & 3;
+    const int r = q * 32 + r32;
+    uint8_t v = 0;
+    if (item.z >= 0 && r < item.y) v = sf[static_cast<size_t>(item.x + r) * kblocks32 + kt * 4 + kk];
+    out[(static_cast<size_t>(i) * kb128 + kt) * 512 + within] = v;
+  }
+}
+
 // Scale bytes [rows, K/32] (row-major) -> the tensor core's block layout [ceil(rows/128)][K/128][512]; rows past the
 // end get exponent 0 (scale 2^-127: their products vanish and are never stored anyway).
 __global__ void mx_sf_to_blocks_kernel(const uint8_t* __restrict__ sf, uint8_t* __restrict__ out, int rows, int kblocks32) {
@@ -566,6 +599,16 @@ extern "C" int spark_mx_sf_tile_blocks(const void* sf, const void* items, const 
   if (kblocks32 % 4) return -5;
   mx_sf_tile_blocks_kernel<<<max_items, 256, 0, stream>>>((const uint8_t*)sf, (const int4*)items, n_items, max_items, kblocks32,
                                                          (uint8_t*)out);
+  return spark_launch_rc(__func__);
+}
+
+extern "C" int spark_mx4_prep(int mode, const void* tiles, const int* ntile, const int* pair_expert, const int* pair_row,
+                              int pairs, int max_items, const void* sf, int kblocks32, void* items, int* n_items, void* out,
+                              cudaStream_t stream) {
+  if (max_items <= 0 || kblocks32 <= 0) return 0;
+  if (kblocks32 % 4) return -5;
+  mx4_prep_kernel<<<max_items, 256, 0, stream>>>(mode, (const int4*)tiles, ntile, pair_expert, pair_row, pairs, max_items,
+                                                 (const uint8_t*)sf, kblocks32, (int4*)items, n_items, (uint8_t*)out);
   return spark_launch_rc(__func__);
 }
 

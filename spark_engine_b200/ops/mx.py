@@ -28,6 +28,7 @@ _SIGS = {
     "spark_mx_sf_to_blocks": [_vp, _vp, _i32, _i32, _vp],
     "spark_mx_mgemm": [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp],
     "spark_mx4_items": [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp],
+    "spark_mx4_prep": [_i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp],
     "spark_mx_sf_tile_blocks": [_vp, _vp, _vp, _i32, _i32, _vp, _vp],
     "spark_moe_mxfp4": [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _vp],
     "spark_coded_gemv": [_vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
@@ -161,12 +162,11 @@ def moe_mxfp4_tc(x, w: Mxfp4Weight, out_rows, max_items, tiles=None, ntile=None,
     items = torch.empty(max_items, 4, dtype=torch.int32, device=dev)
     n_items = torch.empty(1, dtype=torch.int32, device=dev)
     mode = 0 if tiles is not None else 1
-    rc = _lib().spark_mx4_items(mode, cu.P(tiles), cu.P(ntile), cu.P(pair_expert), cu.P(pair_row),
-                                0 if mode == 0 else max_items, max_items, cu.P(items), cu.P(n_items), cu.stream())
-    cu.check(rc, "spark_mx4_items")
     sfa = torch.empty(max_items, K // 128, 512, dtype=torch.uint8, device=dev)
-    rc = _lib().spark_mx_sf_tile_blocks(cu.P(a_sf), cu.P(items), cu.P(n_items), max_items, K // 32, cu.P(sfa), cu.stream())
-    cu.check(rc, "spark_mx_sf_tile_blocks")
+    rc = _lib().spark_mx4_prep(mode, cu.P(tiles), cu.P(ntile), cu.P(pair_expert), cu.P(pair_row),
+                               0 if mode == 0 else max_items, max_items, cu.P(a_sf), K // 32, cu.P(items), cu.P(n_items),
+                               cu.P(sfa), cu.stream())
+    cu.check(rc, "spark_mx4_prep")
     wb = getattr(w, "_sf_blocks", None)
     if wb is None or wb.device != dev:
         wb = w._sf_blocks = sf_blocks(w.scales.reshape(E * N, K // 32))
