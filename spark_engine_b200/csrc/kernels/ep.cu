@@ -27,11 +27,15 @@ struct EpLayout {
   long long ret_off;       // return buffer on the home rank: bf16 [T_cap * top_k][H]
   long long ret_flag_off;  // u32 [world]: combine flags
   int cap;                 // rows per (src, dst) sub-slab
-  int row_bytes;           // H + H/128*4 + 16
+  int row_bytes;           // H + ep_scale_bytes(H) + 16
   uint32_t* seq_ptr;       // optional device-side sequence counter (graph replay)
 };
 
 constexpr int EP_THREADS = 256;
+
+// Bytes of the per-row scale area (one fp32 per 128 elements), padded to 16 bytes so that the metadata that follows
+// and the 16-byte row copies stay aligned for every H that is a multiple of 128.
+__host__ __device__ constexpr int ep_scale_bytes(int H) { return (((H >> 7) * 4) + 15) & ~15; }
 
 // grid T, 256 threads; H % 2048 == 0 is not required: thread handles 8 consecutive elements per pass.
 __global__ void __launch_bounds__(EP_THREADS)
@@ -130,7 +134,7 @@ ep_dispatch_kernel(CommCtx c, EpLayout L, uint32_t seq, const __nv_bfloat16* __r
   }
   __syncthreads();
   // ---- scatter to the owners
-  const int payload16 = (H + (H >> 7) * 4) >> 4;            // 16-byte vectors of fp8 row + scales
+  const int payload16 = (H + ep_scale_bytes(H)) >> 4;            // 16-byte vectors of fp8 row + scales
   for (int k = 0; k < top_k; ++k) {
     const int e = sel_id[k], dst = e / epr, pos = sel_pos[k];
     if (pos >= L.cap) { if (tid == 0) set_status(c.status, ST_BOUNDS, dst, pos, L.cap); continue; }
@@ -138,7 +142,7 @@ ep_dispatch_kernel(CommCtx c, EpLayout L, uint32_t seq, const __nv_bfloat16* __r
     for (int i = tid; i < payload16; i += EP_THREADS) reinterpret_cast<uint4*>(row)[i] = reinterpret_cast<const uint4*>(sm)[i];
     if (tid == 0) {
       int4 meta; meta.x = t; meta.y = k; meta.z = e - dst * epr; meta.w = __float_as_int(sel_p[k]);
-      *reinterpret_cast<int4*>(row + H + (H >> 7) * 4) = meta;
+      *reinterpret_cast<int4*>(row + H + ep_scale_bytes(H)) = meta;
     }
   }
   __syncthreads();
@@ -194,7 +198,7 @@ ep_recv_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, __nv_bfloat16* __rest
       *reinterpret_cast<uint4*>(a_rows + static_cast<size_t>(i) * H + b) = *reinterpret_cast<uint4*>(o);
     }
     if (threadIdx.x == 0) {
-      const int4 m = *reinterpret_cast<const int4*>(row + H + (H >> 7) * 4);
+      const int4 m = *reinterpret_cast<const int4*>(row + H + ep_scale_bytes(H));
       expert_local[i] = m.z;
       meta_out[i] = make_int4(src, m.x, m.y, m.w);
     }
@@ -271,14 +275,14 @@ static CommCtx to_ctx_e(const HostCtxE* h) {
   return c;
 }
 
-extern "C" int spark_ep_row_bytes(int H) { return H + (H >> 7) * 4 + 16; }
+extern "C" int spark_ep_row_bytes(int H) { return H + ep_scale_bytes(H) + 16; }
 
 extern "C" int spark_ep_dispatch(const HostCtxE* h, const EpLayout* L, unsigned seq, const void* x, int T, int H,
                                  const float* logits, int ld, int E, int top_k, float* wts, int* ids, int* send_count,
                                  int* done_counter, cudaStream_t s) {
   if (T <= 0) return 0;
-  if (H % 128 || E > 1024 || top_k > 32 || E % h->world) return -5;
-  const int smem = H + (H >> 7) * 4;
+  if (H % 128 || E > 1024 || top_k > 32 || E % h->world || L->row_bytes != H + ep_scale_bytes(H) + 16) return -5;
+  const int smem = H + ep_scale_bytes(H);
   ep_dispatch_kernel<<<T, EP_THREADS, smem, s>>>(to_ctx_e(h), *L, seq, (const __nv_bfloat16*)x, H, logits, ld, E, top_k, wts,
                                                   ids, send_count, done_counter);
   return spark_launch_rc(__func__);

@@ -42,6 +42,16 @@ struct Cur {
     while (p < e && *p != ',' && *p != '}' && *p != ']') ++p;
   }
 };
+// bits per element of the dtypes the format defines (0 = unknown: size not checked)
+int dtype_bits(const std::string& d) {
+  if (d == "F64" || d == "I64" || d == "U64") return 64;
+  if (d == "F32" || d == "I32" || d == "U32") return 32;
+  if (d == "F16" || d == "BF16" || d == "I16" || d == "U16") return 16;
+  if (d == "I8" || d == "U8" || d == "BOOL" || d == "F8_E4M3" || d == "F8_E5M2" || d == "F8_E8M0") return 8;
+  if (d == "F4" || d == "F4_E2M1") return 4;
+  return 0;
+}
+
 }  // namespace
 
 SafeTensors::SafeTensors(const std::string& path) : path_(path) {
@@ -75,6 +85,18 @@ SafeTensors::SafeTensors(const std::string& path) : path_(path) {
       c.eat(',');
     }
     c.eat(',');
+    // a truncated or crafted file must not make data() / read_into() reach past the mapping
+    const int64_t payload = static_cast<int64_t>(size_) - static_cast<int64_t>(data_off_);
+    if (ti.begin < 0 || ti.end < ti.begin || ti.end > payload)
+      throw std::runtime_error("safetensors: data_offsets of " + name + " are outside the file");
+    int64_t numel = 1;
+    for (int64_t d : ti.shape) {
+      if (d < 0) throw std::runtime_error("safetensors: negative dimension in " + name);
+      numel *= d;
+    }
+    const int bits = dtype_bits(ti.dtype);
+    if (bits > 0 && (numel * bits + 7) / 8 != ti.end - ti.begin)
+      throw std::runtime_error("safetensors: byte count of " + name + " does not match its shape and dtype");
     tensors_[name] = ti;
   }
 }

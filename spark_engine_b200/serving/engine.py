@@ -174,6 +174,7 @@ class LLMEngine:
         """One greedy token for each listed sequence (rows batched in one forward)."""
         m = self.model
         pos0 = [m.seqs[s].length for s in slots]
+        self._check_capacity(slots, pos0, 1)
         if not self.use_graphs:
             plan = make_plan([(s, [t], p) for s, t, p in zip(slots, ids, pos0)], device=self.device)
             logits = m.forward(plan)
@@ -191,6 +192,16 @@ class LLMEngine:
         if self._rounds_since_check >= 64:
             self.check_device_status()
         return g.out_host.tolist()
+
+    def _check_capacity(self, slots: Sequence[int], pos0: Sequence[int], rows_per_seq: int):
+        """Host-side guard of the KV regions: a round that would write a row past a slot's region is refused before
+        anything is staged or replayed (a captured round carries fixed KV bases, so the kernels cannot check it)."""
+        m = self.model
+        for s, p in zip(slots, pos0):
+            cap = m.seqs[s].kv_cap
+            if p + rows_per_seq > cap:
+                raise RuntimeError(f"sequence in slot {s} is at {p} tokens: {rows_per_seq} more row(s) exceed its "
+                                   f"KV region of {cap} tokens")
 
     def check_device_status(self):
         """Fail-stop on a device-side error: a bounded wait that ran out (a peer that never arrived, a stalled

@@ -275,6 +275,7 @@ class EngineServer:
         srv.setblocking(False)
         conns: Dict[socket.socket, proto.LineBuffer] = {}
         owner: Dict[int, socket.socket] = {}
+        outbuf: Dict[socket.socket, bytearray] = {}      # bytes accepted for a connection but not yet sent
         print("[serve] rank0 ready", flush=True)
         if ready_cb:
             ready_cb()
@@ -312,14 +313,31 @@ class EngineServer:
                 if c is None and conns:
                     c = next(iter(conns))
                 if c is not None and c in conns:
-                    try:
-                        c.sendall(proto.encode(msg))
-                    except (BlockingIOError, ConnectionError):
-                        pass
+                    outbuf.setdefault(c, bytearray()).extend(proto.encode(msg))
                 if msg.get("done") or msg.get("error"):
                     owner.pop(msg.get("id", -1), None)
             self.out = []
-            if not busy:
+            # non-blocking sockets may take only part of a line: keep the rest and send it when the socket drains, so
+            # the line protocol to the front end is never cut in the middle of a message
+            for c in list(outbuf):
+                buf = outbuf[c]
+                if c not in conns:
+                    outbuf.pop(c, None)
+                    continue
+                try:
+                    while buf:
+                        n = c.send(buf)
+                        if n <= 0:
+                            break
+                        del buf[:n]
+                except BlockingIOError:
+                    pass
+                except (ConnectionError, OSError):
+                    outbuf.pop(c, None)
+                    continue
+                if not buf:
+                    outbuf.pop(c, None)
+            if not busy and not outbuf:
                 time.sleep(idle_sleep)
         for c in conns:
             c.close()

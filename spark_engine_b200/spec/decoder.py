@@ -141,11 +141,12 @@ class SpecDecoder:
     def round(self, seqs: List[SeqSpec], budgets: Optional[List[int]] = None, stop: Sequence[int] = ()) -> List[List[int]]:
         """One speculative round over all given sequences.  Returns the tokens emitted per sequence."""
         m = self.m
-        drafts = []
+        drafts, draft_confs = [], []
         for s in seqs:
             d, c = self._draft(s, self.depth)
             k = self._choose(s, c, len(seqs), sum(1 + len(x) for x in drafts))
             drafts.append(d[:k])
+            draft_confs.append(list(c[:k]))
         items = []
         for s, d in zip(seqs, drafts):
             L = m.seqs[s.slot].length
@@ -168,8 +169,10 @@ class SpecDecoder:
             if len(out) <= n:                              # budget or stop cut inside the accepted prefix
                 rows = list(range(len(out)))
             accepted_rows.append(rows)
+            # online calibration of the cells the rate policy reads: (depth, the drafter's own confidence)
+            cj = draft_confs[i]
             for j, tok in enumerate(d):
-                s.table.observe(j, 0.5, j < n)
+                s.table.observe(j, cj[j] if j < len(cj) else 0.5, j < n)
             s.drafted += len(d)
             s.accepted += n
             emitted.append(out)

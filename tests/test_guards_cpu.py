@@ -1,0 +1,82 @@
+"""Host-side guards that keep bad inputs away from the device (all run on CPU)."""
+import ctypes
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from spark_engine_b200.config import tiny_hybrid
+from spark_engine_b200.models.weights import init_weights
+from spark_engine_b200.runtime import rt
+from spark_engine_b200.serving.engine import LLMEngine
+from spark_engine_b200.spec.decoder import SeqSpec, SpecDecoder
+
+
+def test_decode_round_refuses_a_row_past_the_kv_region():
+    cfg = tiny_hybrid()
+    eng = LLMEngine(cfg, init_weights(cfg, seed=0), device="cpu", max_seqs=2, kv_tokens_per_seq=8)
+    ids = list(range(1, 8))
+    first = int(eng.model.greedy(eng.prefill(0, ids).unsqueeze(0))[0])
+    nxt = eng.decode_round([0], [first])          # position 7 is the last row that fits
+    with pytest.raises(RuntimeError, match="KV region"):
+        eng.decode_round([0], nxt)
+    assert eng.model.seqs[0].length == 8           # nothing was written by the refused round
+    with pytest.raises(RuntimeError, match="KV region"):
+        eng.generate([list(range(1, 7))], max_new=8)
+
+
+def test_ep_row_layout_is_16_byte_aligned_for_every_hidden_size():
+    from spark_engine_b200.ops import cuda as cu
+    if not os.path.exists(cu.LIB_PATH):
+        pytest.skip("kernel library not built")
+    try:
+        dll = ctypes.CDLL(cu.LIB_PATH)
+    except OSError:
+        pytest.skip("CUDA runtime library not loadable here")
+    dll.spark_ep_row_bytes.argtypes, dll.spark_ep_row_bytes.restype = [ctypes.c_int], ctypes.c_int
+    for H in (128, 256, 384, 512, 1024, 2048, 4096, 5120):
+        rb = dll.spark_ep_row_bytes(H)
+        assert rb % 16 == 0 and rb >= H + 4 * (H // 128) + 16
+        assert (rb - 16 - H) % 16 == 0            # metadata offset = H + padded scale area
+
+
+def _write_st(path, header: dict, payload: bytes):
+    h = json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + payload)
+
+
+def test_safetensors_rejects_offsets_outside_the_file(tmp_path):
+    good = tmp_path / "good.safetensors"
+    _write_st(good, {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]}}, b"\0" * 16)
+    st = rt().SafeTensors(str(good))
+    assert st.names() == ["a"]
+    cases = {
+        "past_end": {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 32]}},
+        "reversed": {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [16, 0]}},
+        "size_mismatch": {"a": {"dtype": "F32", "shape": [3, 2], "data_offsets": [0, 16]}},
+    }
+    for name, hdr in cases.items():
+        p = tmp_path / f"{name}.safetensors"
+        _write_st(p, hdr, b"\0" * 16)
+        with pytest.raises(Exception):
+            rt().SafeTensors(str(p))
+
+
+def test_online_calibration_reaches_the_cells_the_rate_policy_reads():
+    cfg = tiny_hybrid()
+    from spark_engine_b200.models.model import Model
+    m = Model(cfg, init_weights(cfg, seed=0), n_slots=1, kv_tokens=256)
+    conf = 0.83
+
+    def drafter(seq, depth):                      # always wrong, always confident
+        return [(seq.last_token + 1 + j) % cfg.vocab for j in range(depth)], [conf] * depth
+    dec = SpecDecoder(m, drafter=drafter, depth=3, policy="all")
+    s = dec.start(0, list(range(5, 25)))
+    before = [s.table.prob(j, conf) for j in range(3)]
+    for _ in range(6):
+        dec.round([s])
+    after = [s.table.prob(j, conf) for j in range(3)]
+    assert all(a < b for a, b in zip(after, before)), (before, after)
