@@ -6,10 +6,18 @@ vocab 151936) with random-init EXL3 4 bpw weights and synthetic uniform-random p
   python bench.py --gpus N --steps K --warmup W
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
 
-A step is one decode round: every live stream emits one token (greedy).  The device-timed number
-replays the captured round K times between CUDA events; the end-to-end number drives the public
-`LLMEngine.decode_round` API, which copies the round's token ids from pinned host memory to the
-device and reads the sampled ids back every step.  Rank 0 prints ONE JSON line.
+A step is one decode round: every live stream emits one token (greedy).  Two numbers are measured:
+
+  value  device-timed (CUDA events): K consecutive decode steps of the captured round with the sampled ids
+         fed back on the device (`LLMEngine.decode_steps`): every step is a real decode step (new token ids,
+         positions and KV rows advance), only the host round trip between steps is left out;
+  e2e    wall clock through the public per-step API (`LLMEngine.decode_round`): every step copies its token
+         ids and positions from pinned host memory to the device and reads the sampled ids back.
+
+With N > 1 the default is ONE model sharded over the N GPUs (tensor + expert parallel, `--parallel tp`, strong
+scaling); `--parallel dp` runs one replica per GPU (weak scaling, no collective).  Rank 0 prints ONE JSON line.
+`--impl aten` runs the same model code through PyTorch/ATen ops instead of the kernels (a library baseline,
+reported as such); `--impl reference` reports why the reference itself cannot run here.
 """
 from __future__ import annotations
 
@@ -42,7 +50,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -91,16 +99,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--impl", default="ours", help="ours | aten (same model code on PyTorch/ATen ops) | reference")
     ap.add_argument("--model", default="qwen3next-style")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the named config; a reduced "
                                                           "count is reported in `config` and is not the headline)")
     ap.add_argument("--streams", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=1024)
-    ap.add_argument("--format", default=None, help="dense | exl3 (default: the config's)")
+    ap.add_argument("--format", default=None, help="dense | exl3 | mx (default: the config's)")
+    ap.add_argument("--kv", default=None, help="bf16 | fp8 (default: the config's)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
-    ap.add_argument("--parallel", default="dp", help="N > 1: tp = one model sharded over the GPUs (tensor + expert "
+    ap.add_argument("--parallel", default="tp", help="N > 1: tp = one model sharded over the GPUs (tensor + expert "
                                                      "parallel, fused peer-memory all-reduce); dp = one replica per GPU")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -108,8 +117,9 @@ def main():
 
     import torch
     import torch.distributed as dist
+    from spark_engine_b200 import ops
     from spark_engine_b200.config import EngineConfig, get_model_config
-    from spark_engine_b200.models.build import build_random_model, weight_bytes
+    from spark_engine_b200.models.build import build_random_model, decode_step_bytes, weight_bytes
     from spark_engine_b200.ops import cuda as cu
     from spark_engine_b200.serving.engine import LLMEngine
 
@@ -119,6 +129,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     kw = {}
@@ -127,22 +138,38 @@ def main():
     if args.format:
         kw["weight_format"] = args.format
     cfg = get_model_config(args.model, **kw)
+    if args.kv:
+        cfg.kv_dtype = args.kv
+    aten = args.impl == "aten"
+    if aten and cfg.weight_format != "dense":
+        # the ATen path has no kernels for the packed formats: it would dequantise every matrix on the host per call
+        if rank == 0:
+            print(json.dumps({"impl": "aten", "unavailable": f"the ATen baseline runs bf16 weights only (--format dense, "
+                              f"reduced --layers to fit): {cfg.weight_format} weights need this repo's kernels"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     t0 = time.time()
     tp = None
     use_tp = world > 1 and args.parallel == "tp"
     if use_tp:
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        from spark_engine_b200.parallel import symm
-        from spark_engine_b200.parallel.tp import DeviceTP
-        arena = symm.Arena(1 << 30, wait_ms=4000.0)
-        tp = DeviceTP(arena, cfg.hidden, rows_cap=1024)
+        if aten:
+            from spark_engine_b200.parallel.tp import NcclTP
+            tp = NcclTP()
+        else:
+            from spark_engine_b200.parallel import symm
+            from spark_engine_b200.parallel.tp import DeviceTP
+            arena = symm.Arena(1 << 30, wait_ms=4000.0)
+            tp = DeviceTP(arena, cfg.hidden, rows_cap=1024)
     W = build_random_model(cfg, dev, seed=0, tp=(rank, world) if use_tp else (0, 1))
     torch.cuda.synchronize()
     build_s = time.time() - t0
     if world > 1:
         dist.barrier()          # ranks finish building their shards at different times
+    if aten:
+        ops.set_fallback(True)
     S = args.streams
-    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not args.no_graphs, prefill_chunk=1024 if use_tp else 4096),
+    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not (args.no_graphs or aten), prefill_chunk=1024 if use_tp else 4096),
                     device=dev, max_seqs=S, kv_tokens_per_seq=max(4096, 2 * args.prompt), tp=tp)
     g = torch.Generator().manual_seed(1234 + (0 if use_tp else rank))
     prompts = torch.randint(0, cfg.vocab, (S, args.prompt), generator=g)
@@ -170,26 +197,22 @@ def main():
     def timed_decode(n_streams: int, steps: int, warmup: int):
         slots = list(range(n_streams))
         ids = [cur[s] for s in slots]
-        for _ in range(warmup):
+        for _ in range(max(warmup - 2, 1)):
             ids = eng.decode_round(slots, ids)
-        # device-timed: K replays of the captured round (inputs stay in their device buffers)
-        pos0 = [eng.model.seqs[s].length for s in slots]
-        key = (tuple(slots), 1, eng._ctx_bucket(max(pos0) + 1))
-        gph = eng.graphs.get(key)
+        ids = eng.decode_steps(slots, ids, 2)[-1]              # warms the device-fed variant of the round as well
         barrier()
         sampler = ClockSampler(local)
         sampler.start()
+        n0 = cu.launch_count()
+        # device-timed: K real decode steps, sampled ids fed back on the device
         ev0.record()
-        if gph is not None:
-            for i in range(steps):
-                gph.replay()
-        else:
-            for i in range(steps):
-                ids = eng.decode_round(slots, ids)
+        toks = eng.decode_steps(slots, ids, steps)
         ev1.record()
         barrier()
         dev_ms = ev0.elapsed_time(ev1) / steps
-        # end to end through the public API: pinned H2D of the ids + D2H of the result each step
+        launches = cu.launch_count() - n0
+        ids = toks[-1]
+        # end to end through the public per-step API: pinned H2D of ids + positions, D2H of the result, every step
         barrier()
         t_a = time.perf_counter()
         for _ in range(steps):
@@ -199,16 +222,14 @@ def main():
         clocks = sampler.stop()
         for s, t in zip(slots, ids):
             cur[s] = t
-        return dev_ms, e2e_ms, clocks
+        return dev_ms, e2e_ms, clocks, launches
 
-    cu.reset_launch_count()
-    dev_ms, e2e_ms, clocks = timed_decode(S, args.steps, max(args.warmup, 3))
-    launches_total = cu.launch_count()
+    dev_ms, e2e_ms, clocks, launches_total = timed_decode(S, args.steps, max(args.warmup, 3))
     sweep = {}
     if args.sweep:
         for n in range(1, S):
-            d, e, _ = timed_decode(n, args.steps, 3)
-            sweep[str(n)] = {"decode_tok_s": n * 1e3 / d, "e2e_tok_s": n * 1e3 / e, "ms_per_step": d}
+            d, e, _, _ = timed_decode(n, args.steps, 3)
+            sweep[str(n)] = {"decode_tok_s": round(n * 1e3 / d, 1), "e2e_tok_s": round(n * 1e3 / e, 1), "ms_per_step": round(d, 4)}
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -219,18 +240,34 @@ def main():
     e2e = replicas * S * 1e3 / e2e_ms
     full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS
             and cfg.weight_format == DEFAULT_FORMAT[args.model])
+    # what a step streams: the weights a round of S rows touches on this rank (not the whole model)
+    step_bytes = decode_step_bytes(W, cfg, S)
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    kv_t = next((mix.k if hasattr(mix, "k") else mix.lat for _, mix, _ in eng.model.layers if hasattr(mix, "k") or hasattr(mix, "lat")), None)
+    kv_label = {torch.bfloat16: "bf16", torch.float8_e4m3fn: "fp8", torch.float32: "fp32"}.get(kv_t.dtype, str(kv_t.dtype)) \
+        if kv_t is not None else "none"
     out = {
         "metric": "aggregate decode tok/s at 4 streams" if S == 4 else f"aggregate decode tok/s at {S} streams",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "strong" if use_tp else "weak",
-        "vs_baseline": round(value / BASELINE_DECODE_4STREAMS[args.model], 3) if full and S == 4 else None,
+        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "strong" if use_tp or world == 1 else "weak",
+        "vs_baseline": round(value / BASELINE_DECODE_4STREAMS[args.model], 3) if full and S == 4 and not aten else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.moe.n_experts,
                    "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
-                   "kv": cfg.kv_dtype, "global_batch": replicas * S, "seq_len": args.prompt, "streams_per_gpu": S,
+                   "kv": kv_label, "global_batch": replicas * S, "seq_len": args.prompt, "streams_per_gpu": S,
                    "parallelism": (f"tp{world}+ep{world}" if use_tp else f"dp{world}") if world > 1 else "single", "speculation": "none (greedy)",
-                   "cache": "inputs larger than L2 (weights %.1f GB streamed every step)" % (weight_bytes(W) / 1e9),
+                   "cache": "inputs larger than L2: a step streams %.2f GB of weights per GPU (of %.1f GB resident)"
+                            % (step_bytes / 1e9, weight_bytes(W) / 1e9),
                    "full_config": full},
+        "step_weight_bytes": step_bytes,
+        "hbm_fraction": round(step_bytes / (dev_ms * 1e-3) / (hbm_gbs * 1e9), 4),
+        "hbm_fraction_of": "measured copy bandwidth %.0f GB/s" % hbm_gbs if peaks else "fallback 6650 GB/s",
         "clocks": clocks,
         "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * (3 * S + 4 * S),
                 "d2h_bytes_per_step": 4 * S, "ms_per_step": round(e2e_ms, 4)},
@@ -238,6 +275,9 @@ def main():
         "prefill_tok_s": round(prefill_tok_s, 1), "ttft_ms": round(statistics.median(ttft), 2),
         "streams_sweep": sweep, "weight_build_s": round(build_s, 1), "device_status": list(st),
     }
+    if aten:
+        out["impl"] = "aten"
+        out["note"] = "library baseline: this repo's model code on PyTorch/ATen ops (+ NCCL), not the reference"
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -223,7 +223,12 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
 
 // ---------------------------------------------------------------- misc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#ifdef SPARK_PDL_NO_EARLY_TRIGGER
+// A/B build: dependents launch only when this grid completes (the launch latency is still hidden)
+__device__ __forceinline__ void pdl_trigger() {}
+#else
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

@@ -10,7 +10,7 @@
 // All reductions have a fixed order (no float atomics): run-to-run bitwise equal, and a row's result is
 // independent of the other rows in the batch.
 // Reference: engine-rs/shim/qwen_qsa.cu:69-178 (prep/pool), :215-882 (attn_* / attn_combine).
-#include "../common/ptx.cuh"
+#include "../common/decode.cuh"
 #include <cuda_fp8.h>
 
 namespace spark {
@@ -36,6 +36,8 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, AttnDims a,
                  float* __restrict__ ik_raw, float* __restrict__ ik_pool) {
   __shared__ float red[4];
   __shared__ float vals[256];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, job = blockIdx.y, t = threadIdx.x;
   const int qw = a.D * (a.gated ? 2 : 1);
   const int nq = a.Hq * qw, nkv = a.Hkv * a.D;
@@ -164,6 +166,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qbuf, const void* __restric
   __shared__ float sc[ATT_MAXREP][ATT_TS];
   __shared__ float sq[ATT_MAXREP][256];
   __shared__ int stok[ATT_TS];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
   const int rep = Hq / Hkv;
   const int n_ctx = sel ? sel_n[r] : pos[r] + 1;
@@ -250,6 +254,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qbuf, const void* __restric
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit,
                                   const __nv_bfloat16* __restrict__ qkv, int ld, int gated, int Hq, int D,
                                   __nv_bfloat16* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const size_t pb = (static_cast<size_t>(r) * Hq + h) * nsplit;
   float M = -INFINITY;
@@ -284,9 +290,10 @@ extern "C" int spark_attn_prep(const void* qkv, int ld, int R, int Hq, int Hkv, 
   if (D > 256 || idx_dim > 256) return -5;
   AttnDims a{Hq, Hkv, D, rope_dim, gated, qk_norm, idx_heads, idx_dim, block, fp8, eps};
   dim3 grid(R, Hq + 2 * Hkv + idx_heads + (idx_dim > 0 ? 1 : 0));
-  attn_prep_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)qkv, ld, a, q_norm, k_norm, iq_norm, ik_norm, inv_freq, pos,
-                                        row_kv, row_j, (__nv_bfloat16*)qbuf, kc, vc, ks, vs, qi_buf, ik_raw, ik_pool);
-  return spark_launch_rc(__func__);
+  const cudaError_t err = spark_launch_pdl(attn_prep_kernel, grid, dim3(128), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qkv, ld, a,
+                                           q_norm, k_norm, iq_norm, ik_norm, inv_freq, pos, row_kv, row_j, (__nv_bfloat16*)qbuf,
+                                           kc, vc, ks, vs, qi_buf, ik_raw, ik_pool);
+  return err == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* vc, const float* ks, const float* vs,
@@ -296,15 +303,17 @@ extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* v
   if (R <= 0) return 0;
   if (D > 256 || Hq / Hkv > ATT_MAXREP) return -5;
   dim3 grid(R, Hkv, nsplit);
+  cudaError_t err;
   if (fp8)
-    attn_decode_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
-                                                  part_o, part_ml, Hq, Hkv, D, scale);
+    err = spark_launch_pdl(attn_decode_kernel<true>, grid, dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qbuf, kc, vc, ks, vs,
+                           pos, row_kv, sel, sel_n, sel_ld, part_o, part_ml, Hq, Hkv, D, scale);
   else
-    attn_decode_kernel<false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
-                                                   part_o, part_ml, Hq, Hkv, D, scale);
-  attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D,
-                                              (__nv_bfloat16*)out);
-  return spark_launch_rc(__func__);
+    err = spark_launch_pdl(attn_decode_kernel<false>, grid, dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qbuf, kc, vc, ks, vs,
+                           pos, row_kv, sel, sel_n, sel_ld, part_o, part_ml, Hq, Hkv, D, scale);
+  if (err != cudaSuccess) return -4;
+  err = spark_launch_pdl(attn_merge_kernel, dim3(R, Hq), dim3(D), 0, s, dim3(1, 1, 1), (const float*)part_o, (const float*)part_ml,
+                         nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D, (__nv_bfloat16*)out);
+  return err == cudaSuccess ? 0 : -4;
 }
 
 // ---------------------------------------------------------------------------------------------------------

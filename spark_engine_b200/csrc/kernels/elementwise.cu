@@ -2,7 +2,7 @@
 // Activations are bf16, the residual stream and norm weights are fp32.  One CTA per row, 16-byte
 // accesses.  Replaces engine-rs/shim/ds41_ops.cu:17-239 (rms_norm*), kda.cu:1036 (rms_rows),
 // shared_gu.cu:38-65 and the ATen row ops of the eager path.
-#include "../common/ptx.cuh"
+#include "../common/decode.cuh"
 
 namespace spark {
 
@@ -22,6 +22,8 @@ template <typename TD>
 __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ res, const float* __restrict__ w,
                                    __nv_bfloat16* __restrict__ out, int H, float eps, int one_plus) {
   __shared__ float sh[32];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   float* x = res + static_cast<size_t>(r) * H;
   float ss = 0.f;
@@ -56,17 +58,65 @@ __global__ void rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ x, const f
 
 // A token id outside [0, V) never reaches memory: its row is zero and the status word records {ST_BOUNDS, row, id}
 // (ids come from clients; the host also validates them, this is the last line).
+// With `ssq` (H % 128 == 0) it also leaves the strip partial sums of squares of the row: the first block's deferred
+// RMSNorm reads them (decode.cuh).
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ status, float* __restrict__ ssq,
+                             int ssq_ld) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int id = ids[r];
-  if (id < 0 || id >= V) {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = 0.f;
-    if (threadIdx.x == 0 && status) set_status(status, ST_BOUNDS, r, id, V);
+  const bool bad = id < 0 || id >= V;
+  if (bad && threadIdx.x == 0 && status) set_status(status, ST_BOUNDS, r, id, V);
+  const __nv_bfloat16* src = table + static_cast<size_t>(bad ? 0 : id) * H;
+  if (ssq == nullptr) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      out[static_cast<size_t>(r) * H + i] = bad ? 0.f : __bfloat162float(src[i]);
     return;
   }
-  const __nv_bfloat16* src = table + static_cast<size_t>(id) * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = __bfloat162float(src[i]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int strip = warp; strip * 128 < H; strip += nw) {
+    const int col = strip * 128 + lane * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!bad) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src + col);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+      v = make_float4(f0.x, f0.y, f1.x, f1.y);
+    }
+    *reinterpret_cast<float4*>(out + static_cast<size_t>(r) * H + col) = v;
+    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    if (lane == 0) ssq[static_cast<size_t>(strip) * ssq_ld + r] = ss;
+  }
+}
+
+// Strip partial sums of squares of existing fp32 rows (entry into the deferred-norm chain from a path that updated
+// the residual without leaving them).  grid R, one warp per strip.
+__global__ void row_ssq_kernel(const float* __restrict__ res, int H, float* __restrict__ ssq, int ssq_ld) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int strip = warp; strip * 128 < H; strip += nw) {
+    const float4 v = *reinterpret_cast<const float4*>(res + static_cast<size_t>(r) * H + strip * 128 + lane * 4);
+    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    if (lane == 0) ssq[static_cast<size_t>(strip) * ssq_ld + r] = ss;
+  }
+}
+
+// End of a device-fed decode round (one row per sequence): the sampled ids become the next round's input ids and
+// every position advances by one, so a captured round can be replayed without the host in between.
+// dev = packed plan [ids R | pos R | row_pos0 R | seg n*4] with R == n.
+__global__ void decode_advance_kernel(int* __restrict__ dev, const int* __restrict__ out_ids, int n) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = threadIdx.x;
+  if (i < n) {
+    dev[i] = out_ids[i];
+    dev[n + i] += 1;
+    dev[2 * n + i] += 1;
+    dev[3 * n + 4 * i + 3] += 1;
+  }
 }
 
 // gu bf16 [R, 2F] = [gate | up] -> out bf16 [R, F]
@@ -90,6 +140,8 @@ __global__ void __launch_bounds__(256)
 argmax_part_kernel(const float* __restrict__ logits, int V, float* __restrict__ pv, int* __restrict__ pi) {
   __shared__ float sv[8];
   __shared__ int si[8];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, c = blockIdx.y, nc = gridDim.y;
   const int per = (V + nc - 1) / nc;
   const int i0 = c * per, i1 = min(V, i0 + per);
@@ -115,6 +167,8 @@ argmax_part_kernel(const float* __restrict__ logits, int V, float* __restrict__ 
 
 __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int nc,
                                     int* __restrict__ out_id, float* __restrict__ out_val) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   float best = -INFINITY; int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < nc; i += 32) argmax_combine(best, bi, pv[r * nc + i], pi[r * nc + i]);
@@ -153,18 +207,35 @@ extern "C" void spark_add_rmsnorm(const void* delta, int delta_f32, float* res, 
   if (R <= 0) return;
   int th = H >= 2048 ? 512 : 256;
   if (delta_f32)
-    add_rmsnorm_kernel<float><<<R, th, 0, s>>>((const float*)delta, res, w, (__nv_bfloat16*)out, H, eps, one_plus);
+    spark_launch_pdl(add_rmsnorm_kernel<float>, dim3(R), dim3(th), 0, s, dim3(1, 1, 1), (const float*)delta, res, w,
+                     (__nv_bfloat16*)out, H, eps, one_plus);
   else
-    add_rmsnorm_kernel<__nv_bfloat16><<<R, th, 0, s>>>((const __nv_bfloat16*)delta, res, w, (__nv_bfloat16*)out, H, eps, one_plus);
+    spark_launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(R), dim3(th), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)delta, res, w,
+                     (__nv_bfloat16*)out, H, eps, one_plus);
 }
 extern "C" void spark_rmsnorm_bf16(const void* x, const float* w, void* out, int R, int H, float eps, int one_plus,
                                    cudaStream_t s) {
   if (R <= 0) return;
   rmsnorm_bf16_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)out, H, eps, one_plus);
 }
-extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s, int V, int* status) {
+extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s, int V, int* status,
+                            float* ssq, int ssq_ld) {
   if (R <= 0) return;
-  embed_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)table, ids, out, H, V, status);
+  if (H % 128) ssq = nullptr;
+  spark_launch_pdl(embed_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)table, ids, out, H, V, status,
+                   ssq, ssq_ld);
+}
+extern "C" int spark_row_ssq(const float* res, int R, int H, float* ssq, int ssq_ld, cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (H % 128) return -5;
+  const cudaError_t e = spark_launch_pdl(row_ssq_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), res, H, ssq, ssq_ld);
+  return e == cudaSuccess ? 0 : -4;
+}
+extern "C" int spark_decode_advance(int* dev, const int* out_ids, int n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (n > 1024) return -5;
+  const cudaError_t e = spark_launch_pdl(decode_advance_kernel, dim3(1), dim3(((n + 31) / 32) * 32), 0, s, dim3(1, 1, 1), dev, out_ids, n);
+  return e == cudaSuccess ? 0 : -4;
 }
 extern "C" void spark_swiglu(const void* gu, void* out, int R, int F, float limit, cudaStream_t s) {
   if (R <= 0) return;
@@ -175,8 +246,9 @@ extern "C" void spark_argmax(const float* logits, int R, int V, int* out_id, flo
                              cudaStream_t s) {
   if (R <= 0) return;
   const int nc = V >= 65536 ? 64 : (V >= 4096 ? 8 : 1);
-  argmax_part_kernel<<<dim3(R, nc), 256, 0, s>>>(logits, V, part_v, part_i);
-  argmax_final_kernel<<<R, 32, 0, s>>>(part_v, part_i, nc, out_id, out_val);
+  spark_launch_pdl(argmax_part_kernel, dim3(R, nc), dim3(256), 0, s, dim3(1, 1, 1), logits, V, part_v, part_i);
+  spark_launch_pdl(argmax_final_kernel, dim3(R), dim3(32), 0, s, dim3(1, 1, 1), (const float*)part_v, (const int*)part_i, nc, out_id,
+                   out_val);
 }
 extern "C" void spark_add(const void* delta, int delta_f32, float* res, long n, cudaStream_t s) {
   if (n <= 0) return;

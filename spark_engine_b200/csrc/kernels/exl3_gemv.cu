@@ -13,6 +13,7 @@
 // the decode half of moe_exl3.cuh:273-399.
 #include "exl3_common.cuh"
 #include "../common/comm.cuh"
+#include "../common/decode.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -29,7 +30,10 @@ struct Exl3GemvArgs {
   int R, K, N, S, act; float limit;
   int fuse_ar;                                  // 1: row-parallel layer under TP: the epilogue pushes the strip to every
   ArRows ar;                                    //    rank and the last CTA does all-reduce + residual + RMSNorm
-};
+  NormIn nin;                                   // nin.res != nullptr: rows = rmsnorm(residual) rebuilt while staging
+  ResOut rout;                                  // rout.res != nullptr: residual += y, strip sums of squares (items == 1)
+  int pairs_early;                              // pair tables were written at least two launches back: they may be read
+};                                              // (and the weight loads issued) before the dependency wait
 
 #ifndef SPARK_EXL3_MINB
 #define SPARK_EXL3_MINB 6   // 40 registers: 6 CTAs (48 warps) per SM; measured faster than 4 (64 regs) or 2 (94 regs)
@@ -53,7 +57,13 @@ template <int CB, bool HI>       // HI: more than 8 activation rows (the upper h
 __global__ void __launch_bounds__(256, SPARK_EXL3_MINB)
 exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
   // (the argument block stays in constant memory: a local copy would put every field access on the stack)
-  if (a.pair_expert && a.pair_expert[blockIdx.z] < 0) return;   // expert on another rank (whole cluster leaves)
+  // Weight loads depend on no earlier launch; everything else is read after the dependency wait.
+  const bool early = a.pair_expert == nullptr || a.pairs_early;
+  if (!early) pdl_wait();
+  if (a.pair_expert && a.pair_expert[blockIdx.z] < 0) {         // expert on another rank (whole cluster leaves)
+    if (early) pdl_wait();
+    return;
+  }
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   __half* xh = reinterpret_cast<__half*>(smem_dyn);          // [16][Ks + 8]
   cg::cluster_group cluster = cg::this_cluster();
@@ -85,6 +95,8 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
     for (int u = 0; u < 8; ++u) nxt[u] = __ldg(tw + (8 + u) * tstep);
   }
 
+  if (early) pdl_wait();
+  pdl_trigger();
   // ---- prologue: xh = had128(x * suh) / sqrt(128) for this K-slice; one warp per (row, 128-block)
   const __half* suh = a.suh + e * a.suh_stride + k_begin;
   const int nblk = Ks >> 7;
@@ -92,7 +104,9 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
     const int r = job / nblk, b = job - r * nblk;
     const __nv_bfloat16* xr = a.x + static_cast<size_t>(xr0 + r) * a.ldx + k_begin + b * 128 + lane * 4;
     float v[4];
-    if (a.act == 1) {
+    if (a.nin.res != nullptr) {
+      norm_row4(a.nin, xr0 + r, k_begin + b * 128 + lane * 4, lane, v);
+    } else if (a.act == 1) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float gg = __bfloat162float(xr[i]), uu = __bfloat162float(xr[a.K + i]);
@@ -190,6 +204,16 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
         st_f4(reinterpret_cast<float*>(a.ar.c.peers[p] + a.ar.slot_off) + so, make_float4(v[0], v[1], v[2], v[3]));
       continue;
     }
+    if (a.rout.res != nullptr) {
+      // residual update in place (this CTA owns the strip's columns) + the strip's share of the row's sum of squares
+      float* rp = a.rout.res + static_cast<size_t>(xr0 + r) * a.N + strip * 128 + lane * 4;
+      float4 o4 = *reinterpret_cast<const float4*>(rp);
+      o4.x += v[0]; o4.y += v[1]; o4.z += v[2]; o4.w += v[3];
+      *reinterpret_cast<float4*>(rp) = o4;
+      const float ss = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w);
+      if (lane == 0) a.rout.ssq[static_cast<size_t>(strip) * a.rout.ssq_ld + xr0 + r] = ss;
+      continue;
+    }
     const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
     if (a.out_f32) {
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
@@ -211,7 +235,8 @@ using namespace spark;
 extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, const void* suh, const void* svh,
                                long long t_stride_words, long long suh_stride, long long svh_stride, void* y, int ldy,
                                int out_f32, const int* pair_expert, const int* pair_row, int items, int rows_per_item,
-                               int K, int N, int S, int act, float limit, int codebook, cudaStream_t s, const void* ar_args) {
+                               int K, int N, int S, int act, float limit, int codebook, cudaStream_t s, const void* ar_args,
+                               const void* norm_in, const void* res_out, int pairs_early) {
   if (items <= 0 || rows_per_item <= 0) return 0;
   if (rows_per_item > 16 || (K & 127) || (N & 127) || S < 1 || S > 8 || ((K >> 7) % S) || K / S > EXL3_MAX_KS) return -5;
   if ((ldx & 3) || (ldy & 3)) return -5;
@@ -223,15 +248,21 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   a.pair_expert = pair_expert; a.pair_row = pair_row;
   a.R = rows_per_item; a.K = K; a.N = N; a.S = S; a.act = act; a.limit = limit;
   a.fuse_ar = 0;
+  a.nin = NormIn{}; a.rout = ResOut{}; a.pairs_early = pairs_early;
+  if (norm_in) {
+    a.nin = *static_cast<const NormIn*>(norm_in);
+    if (act == 1 || a.nin.H != K) return -5;
+  }
+  if (res_out) {
+    if (items != 1 || ar_args) return -5;
+    a.rout = *static_cast<const ResOut*>(res_out);
+  }
   if (ar_args) {
     if (items != 1) return -5;
     a.fuse_ar = 1;
     a.ar = *static_cast<const ArRows*>(ar_args);
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(N / 128, S, items);
-  cfg.blockDim = dim3(256);
-  cfg.dynamicSmemBytes = 16 * (K / S + 8) * 2 + S * rows_per_item * 128 * 4;
+  const size_t smem_bytes = 16 * (K / S + 8) * 2 + S * rows_per_item * 128 * 4;
   const bool hi = rows_per_item > 8;
   void (*kern)(Exl3GemvArgs) = codebook == 0 ? (hi ? exl3_gemv_kernel<0, true> : exl3_gemv_kernel<0, false>)
                                              : (hi ? exl3_gemv_kernel<1, true> : exl3_gemv_kernel<1, false>);
@@ -243,11 +274,6 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
       done[id] = true;
     }
   }
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = S; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
-  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, a);
+  cudaError_t err = spark_launch_pdl(kern, dim3(N / 128, S, items), dim3(256), smem_bytes, s, dim3(1, S, 1), a);
   return err == cudaSuccess ? 0 : -4;
 }

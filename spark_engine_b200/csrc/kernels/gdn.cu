@@ -8,7 +8,7 @@
 // Conv tails are kept per value head ([slot, 3, Hv, 3D]: that head's q, k and v channels) so that no
 // two CTAs ever write the same tail entry.
 // Reference: engine-rs/shim/qwen_gdn.cu:45-190 (conv/recur kernels), :636-816 (launch shapes).
-#include "../common/ptx.cuh"
+#include "../common/decode.cuh"
 
 namespace spark {
 
@@ -27,10 +27,11 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
                __nv_bfloat16* __restrict__ out, int ldo,             // [R, Hv*D]
                int Hk, int Hv, float eps, int commit) {
   const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x;
+  // The segment table, the state and the conv history were last written at least two launches back (plan staging,
+  // this layer's launch of the previous round): they are fetched before the dependency wait, so the 64 KB state of
+  // the head streams in while the input projection that precedes this kernel drains.
   const int slot = seg[sg * 4 + 0], r0 = seg[sg * 4 + 1];
   int n = seg[sg * 4 + 2];
-  if (n_rows != nullptr) n = min(n, n_rows[sg]);
-  if (n <= 0) return;
   const int hk = h / (Hv / Hk);
   const int cq = hk * D + i, ck = Hk * D + hk * D + i, cv = 2 * Hk * D + h * D + i;   // conv channels
   const int zc = 2 * Hk * D + Hv * D + h * D + i;                                       // z column
@@ -55,6 +56,10 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
   const float wq[4] = {conv_w[cq * 4], conv_w[cq * 4 + 1], conv_w[cq * 4 + 2], conv_w[cq * 4 + 3]};
   const float wk[4] = {conv_w[ck * 4], conv_w[ck * 4 + 1], conv_w[ck * 4 + 2], conv_w[ck * 4 + 3]};
   const float wv[4] = {conv_w[cv * 4], conv_w[cv * 4 + 1], conv_w[cv * 4 + 2], conv_w[cv * 4 + 3]};
+  pdl_wait();
+  pdl_trigger();
+  if (n_rows != nullptr) n = min(n, n_rows[sg]);
+  if (n <= 0) return;
   const float a_neg = -__expf(A_log[h]);
   const float dtb = dt_bias[h];
   const float nw = norm_w[i];
@@ -127,16 +132,17 @@ extern "C" int spark_gdn_seq(const void* proj, int ldp, const void* ab, int ldab
                              float eps, int commit, cudaStream_t s) {
   if (nseg <= 0) return 0;
   dim3 grid(Hv, nseg);
+  cudaError_t e = cudaSuccess;
   if (D == 128)
-    gdn_seq_kernel<128><<<grid, 128, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+    e = spark_launch_pdl(gdn_seq_kernel<128>, grid, dim3(128), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
                                              dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
   else if (D == 64)
-    gdn_seq_kernel<64><<<grid, 64, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+    e = spark_launch_pdl(gdn_seq_kernel<64>, grid, dim3(64), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
                                            dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
   else if (D == 32)
-    gdn_seq_kernel<32><<<grid, 32, 0, s>>>((const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
+    e = spark_launch_pdl(gdn_seq_kernel<32>, grid, dim3(32), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
                                            dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
   else
     return -5;
-  return spark_launch_rc(__func__);
+  return e == cudaSuccess ? 0 : -4;
 }

@@ -8,7 +8,7 @@
 //   moe_combine  : residual += sum over slots (slot order) of weight * expert output (+ gated shared).
 // Reference: engine-rs/shim/qwen_moe.cu:10-92, dataflow.cu:370-572, ds41_ops.cu:375-421 (routers);
 // moe_exl3.cuh:141-231 (count/scan/fill), :1085 (slot-order combine).
-#include "../common/ptx.cuh"
+#include "../common/decode.cuh"
 
 namespace spark {
 
@@ -108,6 +108,265 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int E, int top_k, int
     sum = fmaxf(sum, 1e-20f);
     for (int k = 0; k < top_k; ++k) wts[static_cast<size_t>(r) * top_k + k] = sel_p[k] / sum * scale;
     if (shared_gate) sg[r] = 1.f / (1.f + expf(-x[E]));
+  }
+}
+
+
+// ---------------------------------------------------------------------------------- decode router (fused)
+// One launch for <= 16 rows: router GEMV over the E (+1 shared-gate) columns, then the CTA that finishes last
+// (integer arrival counter, nobody waits) scores, picks the top-k experts of every row with one warp per row and
+// writes the pair tables the expert GEMVs read: ids / weights / source row for top_k routed slots plus an optional
+// shared-expert slot (the shared expert is stored as one more matrix of the expert stack, so it is just another
+// pair; under tensor parallelism row r's shared pair belongs to rank r % world).
+// Input rows are bf16, or the fp32 residual stream with the deferred RMSNorm (NormIn).
+// Replaces three launches (norm, GEMV, route); reference: engine-rs/shim/qwen_moe.cu:10-92, dataflow.cu:370-572.
+struct RouterArgs {
+  const __nv_bfloat16* x; int ldx;           // [R, K] (unused with nin.res)
+  NormIn nin;
+  const __nv_bfloat16* Wg; int ldw;          // [E (+1), K]
+  float* logits; int ld;                     // scratch [R, ld]
+  int R, K, E, top_k, kind;                  // kind: 0 softmax, 1 sigmoid+bias, 2 sqrt(softplus)+bias
+  const float* bias; float scale; int shared_gate;
+  int slots;                                 // top_k, or top_k + 1 when the shared expert is a pair
+  int shared_expert;                         // index of the shared expert in the local stack (slot top_k)
+  int e_lo, e_hi, rank, world;
+  float* wts; int* ids; int* pair_row;       // [R, slots]
+  float* sg;                                 // optional [R]: shared gate (when the shared expert is NOT a pair)
+  int* counter;
+};
+
+constexpr int ROUTER_RB = 16;
+
+__global__ void __launch_bounds__(256)
+moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
+  extern __shared__ __align__(16) uint8_t smem_router[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_router);     // [R][K]
+  __shared__ float rstd_s[ROUTER_RB];
+  __shared__ int last_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int R = a.R, K = a.K;
+  // the gate matrix depends on no earlier launch: its first batch of loads is in flight before the dependency wait
+  const int NE = a.E + (a.shared_gate ? 1 : 0);
+  const int n0 = (blockIdx.x * 8 + warp) * 2;
+  const bool two = n0 + 1 < NE;
+  const uint4* w0 = reinterpret_cast<const uint4*>(a.Wg + static_cast<size_t>(n0 < NE ? n0 : 0) * a.ldw);
+  const uint4* w1 = reinterpret_cast<const uint4*>(a.Wg + static_cast<size_t>(two ? n0 + 1 : (n0 < NE ? n0 : 0)) * a.ldw);
+  constexpr int BATCH = 8;                                 // weight loads in flight per lane and column
+  const int KV = K >> 3;
+  uint4 wa[BATCH], wb[BATCH];
+#pragma unroll
+  for (int u = 0; u < BATCH; ++u) {
+    const int kv = lane + 32 * u;
+    wa[u] = kv < KV ? __ldg(w0 + kv) : make_uint4(0u, 0u, 0u, 0u);
+    wb[u] = kv < KV ? __ldg(w1 + kv) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  pdl_wait();
+  pdl_trigger();
+  if (a.nin.res != nullptr) {
+    for (int r = warp; r < R; r += 8) {
+      const float v = norm_rstd(a.nin, r, lane);
+      if (lane == 0) rstd_s[r] = v;
+    }
+    __syncthreads();
+    const int KV4 = K >> 2;
+    for (int i = tid; i < R * KV4; i += 256) {
+      const int r = i / KV4, kv = i - r * KV4;
+      float v[4];
+      norm_load4(a.nin, r, kv * 4, rstd_s[r], v);
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
+      uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+      reinterpret_cast<uint2*>(xs)[i] = o;
+    }
+  } else {
+    const int KV8 = K >> 3;
+    for (int i = tid; i < R * KV8; i += 256) {
+      const int r = i / KV8, kv = i - r * KV8;
+      reinterpret_cast<uint4*>(xs)[i] = *reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(r) * a.ldx + kv * 8);
+    }
+  }
+  __syncthreads();
+  // ---- GEMV: this CTA's 16 gate columns (2 per warp), all rows; one warp per output => fixed reduction order
+  if (n0 < NE) {
+    float acc0[ROUTER_RB], acc1[ROUTER_RB];
+#pragma unroll
+    for (int r = 0; r < ROUTER_RB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+    for (int kv0 = lane; kv0 < KV; kv0 += 32 * BATCH) {
+      if (kv0 != lane) {
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+          const int kv = kv0 + 32 * u;
+          wa[u] = kv < KV ? __ldg(w0 + kv) : make_uint4(0u, 0u, 0u, 0u);
+          wb[u] = kv < KV ? __ldg(w1 + kv) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int kv = kv0 + 32 * u;
+        if (kv >= KV) break;
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&wa[u]);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&wb[u]);
+        float fa[8], fb[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t0 = __bfloat1622float2(pa[i]), t1 = __bfloat1622float2(pb[i]);
+          fa[2 * i] = t0.x; fa[2 * i + 1] = t0.y; fb[2 * i] = t1.x; fb[2 * i + 1] = t1.y;
+        }
+#pragma unroll
+        for (int r = 0; r < ROUTER_RB; ++r) {
+          if (r < R) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(r) * K + kv * 8);
+            const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = __bfloat1622float2(px[i]);
+              acc0[r] = fmaf(fa[2 * i], t.x, acc0[r]); acc0[r] = fmaf(fa[2 * i + 1], t.y, acc0[r]);
+              acc1[r] = fmaf(fb[2 * i], t.x, acc1[r]); acc1[r] = fmaf(fb[2 * i + 1], t.y, acc1[r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROUTER_RB; ++r) {
+      if (r < R) {
+        const float s0 = warp_sum(acc0[r]), s1 = warp_sum(acc1[r]);
+        if (lane == 0) {
+          a.logits[static_cast<size_t>(r) * a.ld + n0] = s0;
+          if (two) a.logits[static_cast<size_t>(r) * a.ld + n0 + 1] = s1;
+        }
+      }
+    }
+  }
+  // ---- arrival: the last CTA to get here routes every row
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(a.counter, 1);
+    last_s = old == static_cast<int>(gridDim.x) - 1;
+    if (last_s) *a.counter = 0;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  constexpr int EPL = 32;                                   // experts per lane (E <= 1024); loops stop at nj
+  const int nj = (a.E + 31) >> 5;
+  for (int r = warp; r < R; r += 8) {
+    const float* lg = a.logits + static_cast<size_t>(r) * a.ld;
+    float p[EPL], s[EPL];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const int e = lane + 32 * j;
+      p[j] = (j < nj && e < a.E) ? __ldcg(lg + e) : -INFINITY;
+      s[j] = -INFINITY;
+      mx = fmaxf(mx, p[j]);
+    }
+    if (a.kind == 0) {
+      mx = warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) if (j < nj) { p[j] = (lane + 32 * j) < a.E ? expf(p[j] - mx) : 0.f; sum += p[j]; }
+      sum = warp_sum(sum);
+      const float inv = 1.f / sum;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) if (j < nj) { p[j] = p[j] * inv; s[j] = (lane + 32 * j) < a.E ? p[j] : -INFINITY; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        if (j < nj && e < a.E) {
+          const float v = p[j];
+          p[j] = a.kind == 1 ? 1.f / (1.f + expf(-v)) : sqrtf(v > 20.f ? v : log1pf(expf(v)));
+          s[j] = p[j] + (a.bias ? a.bias[e] : 0.f);
+        } else { p[j] = 0.f; s[j] = -INFINITY; }
+      }
+    }
+    float selp = 0.f; int seli = -1;                        // lane k keeps slot k's probability and expert
+    float tot = 0.f;
+    for (int k = 0; k < a.top_k; ++k) {
+      float best = -INFINITY; int bj = 0;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }   // ascending e: first maximum kept
+      int bi = best == -INFINITY ? 0x7fffffff : lane + 32 * bj;
+      float bp = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) if (j == bj) bp = p[j];
+      float wv = best; int wi = bi; float wp = bp;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+        const float op = __shfl_xor_sync(0xffffffffu, wp, o);
+        if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; wp = op; }
+      }
+      if (wi == bi && bi != 0x7fffffff) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) if (j == bj) s[j] = -INFINITY;
+      }
+      if (lane == k) { selp = wp; seli = wi; }
+      tot += wp;                                            // slot order, identical on every lane
+    }
+    tot = fmaxf(tot, 1e-20f);
+    const size_t o = static_cast<size_t>(r) * a.slots;
+    if (lane < a.top_k) {
+      a.wts[o + lane] = selp / tot * a.scale;
+      a.ids[o + lane] = (seli >= a.e_lo && seli < a.e_hi) ? seli - a.e_lo : -1;
+      if (a.pair_row) a.pair_row[o + lane] = r;
+    }
+    if (lane == 0) {
+      const float g = a.shared_gate ? 1.f / (1.f + expf(-__ldcg(lg + a.E))) : 1.f;
+      if (a.slots > a.top_k) {
+        a.wts[o + a.top_k] = g;
+        a.ids[o + a.top_k] = (r % a.world) == a.rank ? a.shared_expert : -1;
+        if (a.pair_row) a.pair_row[o + a.top_k] = r;
+      }
+      if (a.sg) a.sg[r] = g;
+    }
+  }
+}
+
+// Decode combine: residual += sum over slots (slot order) of weight * y[pair], plus the strip partial sums of
+// squares of the new residual (deferred RMSNorm of the next block).  One warp per 128-column strip of a row.
+__global__ void __launch_bounds__(128)
+moe_combine_res_kernel(const float* __restrict__ y, const float* __restrict__ wts, const int* __restrict__ ids, int slots,
+                       int H, ResOut rout, float* __restrict__ out_f32, const __nv_bfloat16* __restrict__ shared,
+                       const float* __restrict__ sg) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int strip = blockIdx.x * 4 + warp;
+  if (strip * 128 >= H) return;
+  const int col = strip * 128 + lane * 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < slots; k0 += 4) {                  // four slots' loads in flight; summed in slot order
+    float4 v[4]; float w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int pi = r * slots + k0 + u;
+      const bool live = (k0 + u) < slots && ids[pi] >= 0;   // -1: expert (or shared pair) of another rank
+      w[u] = live ? wts[pi] : 0.f;
+      v[u] = live ? __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(pi) * H + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      acc.x = fmaf(w[u], v[u].x, acc.x); acc.y = fmaf(w[u], v[u].y, acc.y);
+      acc.z = fmaf(w[u], v[u].z, acc.z); acc.w = fmaf(w[u], v[u].w, acc.w);
+    }
+  }
+  if (shared) {                                            // shared expert computed outside the pair list
+    const uint2 raw = *reinterpret_cast<const uint2*>(shared + static_cast<size_t>(r) * H + col);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+    const float g = sg ? sg[r] : 1.f;
+    acc.x += g * f0.x; acc.y += g * f0.y; acc.z += g * f1.x; acc.w += g * f1.y;
+  }
+  if (out_f32) *reinterpret_cast<float4*>(out_f32 + static_cast<size_t>(r) * H + col) = acc;
+  if (rout.res) {
+    float* rp = rout.res + static_cast<size_t>(r) * H + col;
+    float4 o4 = *reinterpret_cast<const float4*>(rp);
+    o4.x += acc.x; o4.y += acc.y; o4.z += acc.z; o4.w += acc.w;
+    *reinterpret_cast<float4*>(rp) = o4;
+    const float ss = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w);
+    if (lane == 0) rout.ssq[static_cast<size_t>(strip) * rout.ssq_ld + r] = ss;
   }
 }
 
@@ -257,4 +516,43 @@ extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int
     moe_combine_kernel<__nv_bfloat16><<<dim3(R, (H + 255) / 256), 256, 0, s>>>(res, (const __nv_bfloat16*)y, inv_perm, wts, top_k,
                                                         (const __nv_bfloat16*)shared, sg, H, (__nv_bfloat16*)out_bf16, pair_expert);
   return spark_launch_rc(__func__);
+}
+
+// Fused decode router: see moe_router_topk_kernel.  `logits` scratch [R, ld] fp32 (ld >= E + 1), `counter` one int
+// that is zero between launches.  norm_in: NormIn* or null (then x bf16 [R, K]).
+extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* norm_in, const void* Wg, int ldw, float* logits,
+                                     int ld, int R, int K, int E, int top_k, int kind, const float* bias, float scale,
+                                     int shared_gate, int slots, int shared_expert, int e_lo, int e_hi, int rank, int world,
+                                     float* wts, int* ids, int* pair_row, float* sg, int* counter, cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (R > ROUTER_RB || E > 1024 || top_k > 32 || (K & 7) || slots < top_k || slots > top_k + 1 || ld < E + (shared_gate ? 1 : 0))
+    return -5;
+  RouterArgs a;
+  a.x = (const __nv_bfloat16*)x; a.ldx = ldx;
+  a.nin = NormIn{};
+  if (norm_in) { a.nin = *static_cast<const NormIn*>(norm_in); if (a.nin.H != K) return -5; }
+  a.Wg = (const __nv_bfloat16*)Wg; a.ldw = ldw; a.logits = logits; a.ld = ld;
+  a.R = R; a.K = K; a.E = E; a.top_k = top_k; a.kind = kind; a.bias = bias; a.scale = scale; a.shared_gate = shared_gate;
+  a.slots = slots; a.shared_expert = shared_expert; a.e_lo = e_lo; a.e_hi = e_hi; a.rank = rank; a.world = world < 1 ? 1 : world;
+  a.wts = wts; a.ids = ids; a.pair_row = pair_row; a.sg = sg; a.counter = counter;
+  const int NE = E + (shared_gate ? 1 : 0);
+  const size_t smem = static_cast<size_t>(R) * K * 2;
+  if (smem > 200 * 1024) return -6;
+  static bool attr_set = false;
+  if (!attr_set) { cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr_set = true; }
+  const cudaError_t err = spark_launch_pdl(moe_router_topk_kernel, dim3((NE + 15) / 16), dim3(256), smem, s, dim3(1, 1, 1), a);
+  return err == cudaSuccess ? 0 : -4;
+}
+
+// y fp32 [R * slots, H] in pair order.  res_out: ResOut* (residual += sum, strip sums of squares) and / or out_f32 [R, H].
+extern "C" int spark_moe_combine_res(const float* y, const float* wts, const int* ids, int R, int slots, int H,
+                                     const void* res_out, float* out_f32, const void* shared, const float* sg,
+                                     cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (H % 128) return -5;
+  ResOut ro = {};
+  if (res_out) ro = *static_cast<const ResOut*>(res_out);
+  const cudaError_t err = spark_launch_pdl(moe_combine_res_kernel, dim3((H / 128 + 3) / 4, R), dim3(128), 0, s, dim3(1, 1, 1),
+                                           y, wts, ids, slots, H, ro, out_f32, (const __nv_bfloat16*)shared, sg);
+  return err == cudaSuccess ? 0 : -4;
 }

@@ -26,6 +26,12 @@ class _DevInit:
         self.n += 1
         return 1000003 * self.n + 17 + 7919 * self.rank
 
+    def common_seeded(self) -> "_DevInit":
+        """An initialiser for a replicated tensor: its seeds depend on the call count only, not on the rank."""
+        c = _DevInit(self.device, 0, self.fmt, self.bits, self.std, rank=0)
+        c.n = 500000 + self.n
+        return c
+
     def mat_common(self, *shape):
         return (torch.randn(*shape, device=self.device, generator=self.gc) * self.std).to(torch.bfloat16)
 
@@ -104,14 +110,31 @@ def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool, tp=(0, 1)) -> dict:
     Fs = c.shared_ffn or c.ffn * c.n_shared
     assert c.n_experts % world == 0
     e_loc = c.n_experts // world
-    w = {"gate": it.mat_common(c.n_experts + (1 if c.shared_gate else 0), H),
-         "w_gu": it.big(2 * c.ffn, H, e_loc, kind="expert"),
-         "w_down": it.big(H, c.ffn, e_loc, kind="expert")}
+    # EXL3 models keep a shared expert of the routed experts' width as one more matrix of the expert stacks (index
+    # e_loc): decode treats it as one more (row, expert) pair of the grouped GEMVs, and under tensor parallelism every
+    # rank holds it and serves the rows r with r % world == rank.
+    stack_shared = bool(c.n_shared) and Fs == c.ffn and it.fmt == "exl3" and H % 128 == 0 and c.ffn % 128 == 0
+    n_stack = e_loc + (1 if stack_shared else 0)
+    w = {"gate": it.mat_common(c.n_experts + (1 if c.shared_gate else 0), H), "tp_rank": (rank, world)}
+    if stack_shared:
+        it_s = it.common_seeded()            # the shared expert is replicated: same bits on every rank
+        gu_r, dn_r = it.big(2 * c.ffn, H, e_loc, kind="expert"), it.big(H, c.ffn, e_loc, kind="expert")
+        gu_s, dn_s = it_s.big(2 * c.ffn, H, 1, kind="expert"), it_s.big(H, c.ffn, 1, kind="expert")
+        w["w_gu"] = Q.Exl3Weight(torch.cat((gu_r.trellis, gu_s.trellis)), torch.cat((gu_r.suh, gu_s.suh)),
+                                 torch.cat((gu_r.svh, gu_s.svh)), gu_r.bits, gu_r.kind)
+        w["w_down"] = Q.Exl3Weight(torch.cat((dn_r.trellis, dn_s.trellis)), torch.cat((dn_r.suh, dn_s.suh)),
+                                   torch.cat((dn_r.svh, dn_s.svh)), dn_r.bits, dn_r.kind)
+        w["shared_in_stack"] = True
+        for name, st in (("s_gu", w["w_gu"]), ("s_down", w["w_down"])):      # views for prefill-size batches
+            w[name] = Q.Exl3Weight(st.trellis[e_loc], st.suh[e_loc], st.svh[e_loc], st.bits, st.kind)
+    else:
+        w["w_gu"] = it.big(2 * c.ffn, H, e_loc, kind="expert")
+        w["w_down"] = it.big(H, c.ffn, e_loc, kind="expert")
     if world > 1:
         w["ep"] = (rank * e_loc, (rank + 1) * e_loc)
     if c.router != "softmax":
         w["bias"] = torch.zeros(c.n_experts, device=it.device)
-    if c.n_shared and rank == 0:
+    if c.n_shared and not stack_shared and rank == 0:
         w["s_gu"], w["s_down"] = it.big(2 * Fs, H), it.big(H, Fs)
     return w
 
@@ -163,3 +186,40 @@ def weight_bytes(W) -> int:
             n += x.numel() * x.element_size()
     rec(W)
     return n
+
+
+def decode_step_bytes(W, cfg: ModelConfig, rows: int) -> int:
+    """Weight bytes one decode round of `rows` rows has to read from memory: every dense / attention projection,
+    router, norm and lm_head once, and per MoE layer the matrices of the (row, expert) pairs (rows x top-k distinct
+    experts at most, plus the shared expert).  KV / state traffic is not included."""
+    def nbytes(x):
+        if isinstance(x, Q.QuantWeight):
+            return x.nbytes()
+        if isinstance(x, torch.Tensor):
+            return x.numel() * x.element_size()
+        if isinstance(x, dict):
+            return sum(nbytes(v) for v in x.values())
+        return 0
+    total = nbytes(W["lm_head"]) + nbytes(W["final_norm"]) + rows * cfg.hidden * 2
+    for lw in W["layers"]:
+        total += nbytes(lw["mix"]) + nbytes(lw["in_norm"]) + nbytes(lw["post_norm"])
+        m = lw["mlp"]
+        if "dense_gu" in m:
+            total += nbytes(m)
+            continue
+        total += nbytes(m["gate"])
+        wg = m["w_gu"]
+        if isinstance(wg, Q.Exl3Weight):
+            stack = wg.trellis.shape[0]
+        elif isinstance(wg, torch.Tensor):
+            stack = wg.shape[0]
+        else:
+            stack = wg.packed.shape[0] if hasattr(wg, "packed") else cfg.moe.n_experts
+        per_expert = (nbytes(m["w_gu"]) + nbytes(m["w_down"])) / max(stack, 1)
+        pairs = min(rows * cfg.moe.top_k, cfg.moe.n_experts)
+        total += int(per_expert * pairs)
+        if m.get("shared_in_stack"):
+            total += int(per_expert)
+        elif "s_gu" in m:
+            total += nbytes(m["s_gu"]) + nbytes(m["s_down"])
+    return int(total)

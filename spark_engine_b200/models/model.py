@@ -236,7 +236,7 @@ class KdaMixer:
                 outs.append(o)
             o = torch.cat(outs, 0).to(h.dtype)
         self.pending = None if commit else (pre, lr, plan)
-        return ops.linear(o, self.w["o"])
+        return ops.row_parallel(o, self.w["o"], getattr(self, "tp", None))
 
     def commit(self, accepted):
         if self.pending is None:
@@ -433,7 +433,7 @@ class MlaMixer:
         R = h.shape[0]
         fast = ops.mla_mixer(self, h, plan, seqs)
         if fast is not None:
-            return ops.linear(fast, self.w["o"])
+            return ops.row_parallel(fast, self.w["o"], getattr(self, "tp", None))
         a = ops.linear(h, self.w["a"]).float()
         o0 = c.q_lora
         o1 = o0 + c.kv_lora + c.rope_dim
@@ -542,12 +542,13 @@ class MoeBlock:
         self.cfg, self.c, self.w = cfg, cfg.moe, w
         self.dense = "dense_gu" in w
 
-    def forward(self, h):
+    def forward(self, h, defer: bool = False):
         c = self.c
         if self.dense:
             gu = ops.linear(h, self.w["dense_gu"])
-            return ops.linear(ops.swiglu(gu, c.swiglu_limit), self.w["dense_down"])
-        return ops.moe(h, self.w, c)
+            a = ops.swiglu(gu, c.swiglu_limit)
+            return ops.row_parallel(a, self.w["dense_down"]) if defer else ops.linear(a, self.w["dense_down"])
+        return ops.moe(h, self.w, c, defer)
 
 
 # ============================================================================= the model
@@ -599,25 +600,30 @@ class Model:
         first RMSNorm happen in one fused op.  Returns (X, new pending output)."""
         cfg, tp = self.cfg, self.tp
         if cfg.hc_kind == "none":
+            deferred = not isinstance(X, torch.Tensor)      # decode round: residual-stream object, norms deferred
             if "ngram" in lw:
                 if pend is not None:
                     _, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
                     pend = None
-                X = ops.ngram_embed(self, X, plan, lw["ngram"])
+                if deferred:
+                    X.x = ops.ngram_embed(self, X.x, plan, lw["ngram"])
+                    X.valid = False
+                else:
+                    X = ops.ngram_embed(self, X, plan, lw["ngram"])
             h, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
             a = mix.forward(h, plan, self.seqs, commit)
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
-            return X, mlp.forward(h)
+            return X, mlp.forward(h, defer=deferred)
         assert tp is None, "hyper-connection models run without tensor parallelism"
         if pend is not None:
-            X = X + pend
+            X = X + ops.to_tensor(pend)
         if cfg.hc_kind == "gated":
             post, h = ops.hc_gated_mix(X, lw["hc_mix"], cfg.norm_eps)
-            X = X + post.unsqueeze(-1).to(X.dtype) * mix.forward(h, plan, self.seqs, commit).unsqueeze(1)
+            X = X + post.unsqueeze(-1).to(X.dtype) * ops.to_tensor(mix.forward(h, plan, self.seqs, commit)).unsqueeze(1)
             post, h = ops.hc_gated_mix(X, lw["hc_mlp"], cfg.norm_eps)
             return X + post.unsqueeze(-1).to(X.dtype) * mlp.forward(h).unsqueeze(1), None
         h, post, comb = ops.mhc_pre(X, lw["hc_mix"], cfg.sinkhorn_iters, cfg.norm_eps)
-        X = ops.mhc_post(X, mix.forward(h, plan, self.seqs, commit), post, comb)
+        X = ops.mhc_post(X, ops.to_tensor(mix.forward(h, plan, self.seqs, commit)), post, comb)
         h, post, comb = ops.mhc_pre(X, lw["hc_mlp"], cfg.sinkhorn_iters, cfg.norm_eps)
         return ops.mhc_post(X, mlp.forward(h), post, comb), None
 
@@ -627,9 +633,8 @@ class Model:
         With commit=False no linear-attention state nor sequence length changes: call
         `commit(accepted)` afterwards."""
         cfg, W = self.cfg, self.W
-        fast = ops.model_forward(self, plan, commit, want_hidden)
-        if fast is not None:
-            return fast
+        # decode-size batches on the device keep the residual stream as an object whose RMSNorms stay deferred
+        resid = cfg.hc_kind == "none" and self.tp is None and plan.rows <= 16 and not plan.mm_rows
         if plan.mm_rows:
             # salted placeholder ids are outside the vocabulary: look up row 0 for them, then write the encoded media
             # rows over those positions (engine-rs/src/weights.rs:536-569)
@@ -639,7 +644,7 @@ class Model:
             X[salted.to(X.device)] = 0
             X = inject_rows(X, plan.ids, plan.mm_rows)
         else:
-            X = ops.embed(W["embed"], plan.ids, self.dtype)
+            X = ops.embed(W["embed"], plan.ids, self.dtype, resid)
         if cfg.hc_kind != "none":
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
         self._ids_for_ngram = plan
@@ -650,7 +655,7 @@ class Model:
         for li, (lw, mix, mlp) in enumerate(self.layers):
             X, pend = self._block(lw, mix, mlp, X, pend, plan, commit)
             if taps and li in taps:          # residual stream after layer li (feature taps of a drafter)
-                self.taps[li] = X if pend is None else ops.residual_add(X.clone(), pend)
+                self.taps[li] = ops.to_tensor(X) if pend is None else ops.residual_add(ops.to_tensor(X).clone(), pend)
         if cfg.hc_kind == "gated":
             _, X = ops.hc_gated_mix(X, W["hc_final"], cfg.norm_eps)
             hn = X
@@ -659,13 +664,13 @@ class Model:
             hn = ops.rmsnorm(X, W["final_norm"], cfg.norm_eps)
         else:
             hn, X = ops.add_rmsnorm(pend, X, W["final_norm"], cfg.norm_eps, self.tp)
-        self.hidden_out = X
+        self.hidden_out = ops.to_tensor(X)
         self._pending_plan = None if commit else plan
         if commit and not graph_mode:       # under a captured graph the engine tracks lengths itself
             for s in plan.segs:
                 self.seqs[s.slot].length = s.pos0 + s.n
         if plan.logit_rows.shape[0] != hn.shape[0]:
-            hn = hn[plan.logit_rows]
+            hn = ops.to_tensor(hn)[plan.logit_rows]
         return ops.lm_head(hn, W["lm_head"])
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:

@@ -26,11 +26,16 @@ _SIGS = {
     "spark_gemm_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "spark_gemm_bf16_swiglu": [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
     "spark_gemm_grouped_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, f32, i32, vp, vp],
-    "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp],
+    "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp, vp],
     "spark_gemv_bf16_items": [vp, i32, i64, vp, i64, i32, vp, i32, i64, i32, i32, i32, i32, vp, i32, vp],
     "spark_add_rmsnorm": [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
-    "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp],
+    "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp, vp, i32],
+    "spark_row_ssq": [vp, i32, i32, vp, i32, vp],
+    "spark_decode_advance": [vp, vp, i32, vp],
+    "spark_moe_router_topk": [vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, f32, i32, i32, i32, i32, i32, i32,
+                              i32, vp, vp, vp, vp, vp, vp],
+    "spark_moe_combine_res": [vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp],
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
     "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
@@ -56,7 +61,7 @@ _SIGS = {
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp, vp],
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
-                        f32, i32, vp, vp],
+                        f32, i32, vp, vp, vp, vp, i32],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
 }
@@ -178,6 +183,107 @@ def scratch_bytes() -> int:
     return sum(t.numel() * t.element_size() for t in _scratch.values())
 
 
+# ----------------------------------------------------------------------------- deferred norm (decode rounds)
+class NormInC(C.Structure):
+    _fields_ = [("res", vp), ("ssq", vp), ("w", vp), ("nparts", i32), ("ssq_ld", i32), ("H", i32), ("eps", f32),
+                ("one_plus", i32)]
+
+
+class ResOutC(C.Structure):
+    _fields_ = [("res", vp), ("ssq", vp), ("ssq_ld", i32)]
+
+
+SSQ_LD = 16          # rows per strip line of the partial sums of squares (decode rounds hold <= 16 rows)
+FUSED_DECODE = os.environ.get("SPARK_FUSED_DECODE", "1") == "1"
+
+
+class Resid:
+    """fp32 residual stream of a decode round [R <= 16, H] with, per 128-column strip and row, the partial sum of
+    squares of the current rows (`ssq`, valid when `valid`).  Kernels that finish a residual update leave the
+    partials; the consumers of the normalised rows rebuild rstd from them (csrc/common/decode.cuh)."""
+
+    def __init__(self, x: torch.Tensor, ssq: Optional[torch.Tensor] = None, valid: bool = False):
+        self.x = x
+        H = x.shape[1]
+        self.ssq = ssq if ssq is not None else torch.empty(H // 128, SSQ_LD, dtype=torch.float32, device=x.device)
+        self.valid = valid
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def res_out(self) -> ResOutC:
+        r = ResOutC()
+        r.res, r.ssq, r.ssq_ld = self.x.data_ptr(), self.ssq.data_ptr(), SSQ_LD
+        return r
+
+
+class LazyNorm:
+    """rmsnorm(residual) * w that has not been materialised: kernels with a norm prologue take it as it is,
+    everything else calls `tensor()` (one norm launch, cached)."""
+
+    def __init__(self, resid: Resid, w: torch.Tensor, eps: float, one_plus: bool = False):
+        self.resid, self.w, self.eps, self.one_plus = resid, w, eps, one_plus
+        self._t = None
+
+    @property
+    def shape(self):
+        return self.resid.x.shape
+
+    @property
+    def device(self):
+        return self.resid.x.device
+
+    @property
+    def is_cuda(self):
+        return True
+
+    @property
+    def dtype(self):
+        return torch.bfloat16
+
+    def norm_in(self) -> NormInC:
+        n = NormInC()
+        x = self.resid.x
+        n.res, n.ssq, n.w = x.data_ptr(), self.resid.ssq.data_ptr(), self.w.data_ptr()
+        n.nparts, n.ssq_ld, n.H, n.eps, n.one_plus = x.shape[1] // 128, SSQ_LD, x.shape[1], float(self.eps), int(self.one_plus)
+        return n
+
+    def tensor(self) -> torch.Tensor:
+        if self._t is None:
+            self._t = rmsnorm(self.resid.x, self.w, self.eps, self.one_plus)
+        return self._t
+
+
+class PendingMoe:
+    """Expert outputs of a decode round that have not been combined yet: y fp32 [R * slots, H] in pair order.  The
+    combine runs fused with the residual update (and leaves the partials for the next block's deferred norm)."""
+
+    def __init__(self, y, wts, ids, slots, R, H, shared=None, sg=None):
+        self.y, self.wts, self.ids, self.slots, self.R, self.H, self.shared, self.sg = y, wts, ids, slots, R, H, shared, sg
+
+    def tensor(self) -> torch.Tensor:
+        out = torch.empty(self.R, self.H, dtype=torch.float32, device=self.y.device)
+        rc = lib().spark_moe_combine_res(P(self.y), P(self.wts), P(self.ids), self.R, self.slots, self.H, None, P(out),
+                                         P(self.shared), P(self.sg), stream())
+        check(rc, "spark_moe_combine_res")
+        return out.to(torch.bfloat16)
+
+
+def _mat(x):
+    """Plain tensor of an activation that may still be a deferred norm."""
+    return x.tensor() if isinstance(x, LazyNorm) else x
+
+
+def fused_decode_rows(R: int, H: int) -> bool:
+    return FUSED_DECODE and R <= SSQ_LD and H % 128 == 0
+
+
+def can_fuse_residual(x, w) -> bool:
+    """Row-parallel / output projection of decode rows whose kernel can add into the residual stream itself."""
+    return (FUSED_DECODE and isinstance(w, Exl3Weight) and not w.experts and w.bits == 4 and x.shape[0] <= SSQ_LD)
+
+
 # ----------------------------------------------------------------------------- dense linear
 def _as_bf16(x):
     return x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
@@ -197,6 +303,12 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out_f32: bool = False, fmt: int 
 
 def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0, out_f32=False,
               expert_stride=0, n=None, k=None, out=None, ldx=None):
+    norm = None
+    if isinstance(x, LazyNorm):
+        if act == 0 and x.resid.valid:
+            norm, x = x.norm_in(), x.resid.x          # rows rebuilt in the kernel's prologue
+        else:
+            x = x.tensor()
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     n = n if n is not None else w.shape[-2]
     k = k if k is not None else w.shape[-1]
@@ -208,7 +320,7 @@ def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None
         out_f32 = out.dtype == torch.float32
     rc = lib().spark_gemv_bf16(P(x), ldx if ldx is not None else x.stride(0), P(w), expert_stride, w.stride(-2), P(y), ldy,
                                items, rows_per_item, n, k, P(pair_expert), P(pair_row), act, float(limit), int(out_f32),
-                               stream())
+                               stream(), C.addressof(norm) if norm is not None else None)
     check(rc, "spark_gemv_bf16")
     return y
 
@@ -223,10 +335,12 @@ def gemv_bf16_items(x, ldx, x_item_stride, w, expert_stride, ldw, y, ldy, y_item
     return y
 
 
-def dense_linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
-    x = _as_bf16(x)
+def dense_linear(x, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
     if w.dtype != torch.bfloat16:
         raise TypeError("dense weights must be bf16 on the device")
+    if isinstance(x, LazyNorm):
+        return gemv_bf16(x, w, out_f32=out_f32)
+    x = _as_bf16(x)
     R = x.shape[0]
     if R <= 16:
         return gemv_bf16(x.contiguous(), w, out_f32=out_f32)
@@ -234,11 +348,12 @@ def dense_linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> tor
 
 
 # ----------------------------------------------------------------------------- EXL3
-def _pick_slices(K: int) -> int:
+def _pick_slices(K: int, items: int = 1) -> int:
     """K-slices per 128-column strip = CTAs of one cluster (<= 8): aim at 256-deep slices so that one
-    batch of loads per warp covers the whole slice."""
+    batch of loads per warp covers the whole slice.  SPARK_EXL3_S / SPARK_EXL3_S_PAIRS force the count for
+    single-matrix / per-pair launches."""
     blocks = K // 128
-    forced = int(os.environ.get("SPARK_EXL3_S", "0"))
+    forced = int(os.environ.get("SPARK_EXL3_S_PAIRS" if items > 1 else "SPARK_EXL3_S", "0"))
     if forced and blocks % forced == 0:
         return forced
     best = 1
@@ -251,19 +366,34 @@ def _pick_slices(K: int) -> int:
 
 
 def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0,
-              out_f32=False):
+              out_f32=False, res_out: Optional[Resid] = None, pairs_early: bool = False):
+    """`x` may be a LazyNorm (rows normalised in the prologue).  With `res_out` the product is added into that
+    residual stream in place (strip partials updated) and nothing is returned."""
     assert w.bits == 4, "the GEMV kernel handles 4 bpw"
+    norm = None
+    if isinstance(x, LazyNorm):
+        if act == 0 and x.resid.valid:
+            norm, x = x.norm_in(), x.resid.x
+        else:
+            x = x.tensor()
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     K, N = w.k, w.n
-    S = _pick_slices(K)
+    S = _pick_slices(K, items)
     dev = x.device
-    y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+    y = None
+    if res_out is None:
+        y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
     tw = (K // 16) * (N // 16) * 32
     es = (tw, K, N) if w.experts else (0, 0, 0)
+    ro = res_out.res_out() if res_out is not None else None
     rc = lib().spark_exl3_gemv(P(x), x.stride(0), P(w.trellis), P(w.suh), P(w.svh), es[0], es[1], es[2], P(y), N,
                                int(out_f32), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
-                               act, float(limit), 0 if w.kind == "mul1" else 1, stream(), None)
+                               act, float(limit), 0 if w.kind == "mul1" else 1, stream(), None,
+                               C.addressof(norm) if norm is not None else None,
+                               C.addressof(ro) if ro is not None else None, int(pairs_early))
     check(rc, "spark_exl3_gemv")
+    if res_out is not None:
+        res_out.valid = True
     return y
 
 
@@ -313,6 +443,8 @@ def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False, rows_p
 
 
 def exl3_linear(x, w: Exl3Weight):
+    if isinstance(x, LazyNorm):
+        return exl3_gemv(x, w)
     x = _as_bf16(x).contiguous()
     if x.shape[0] <= 16:
         return exl3_gemv(x, w)
@@ -326,11 +458,53 @@ def quant_linear(x, w: QuantWeight):
     if isinstance(w, Exl3Weight):
         return exl3_linear(x, w)
     from . import mx
-    return mx.quant_linear(x, w)
+    return mx.quant_linear(_mat(x), w)
 
 
 # ----------------------------------------------------------------------------- elementwise
+def _delta_tensor(delta):
+    """Plain tensor of a deferred block output (a row-parallel product or an uncombined MoE)."""
+    if delta is None or isinstance(delta, torch.Tensor):
+        return delta
+    if isinstance(delta, PendingMoe):
+        return delta.tensor()
+    return linear_any(delta.x, delta.w)            # ops.Partial
+
+
+def _add_norm_resid(delta, rs: Resid, w, eps, one_plus):
+    """Residual update of a decode round.  Producers with a residual epilogue (EXL3 output projection, MoE combine)
+    add in place and leave the strip partials; the normalised rows stay deferred."""
+    R, H = rs.x.shape
+    if delta is None:
+        pass
+    elif isinstance(delta, PendingMoe):
+        ro = rs.res_out()
+        rc = lib().spark_moe_combine_res(P(delta.y), P(delta.wts), P(delta.ids), R, delta.slots, H, C.addressof(ro), None,
+                                         P(delta.shared), P(delta.sg), stream())
+        check(rc, "spark_moe_combine_res")
+        rs.valid = True
+    elif (not isinstance(delta, torch.Tensor) and isinstance(delta.w, Exl3Weight) and not delta.w.experts
+          and delta.w.n == H and delta.w.bits == 4):
+        x = delta.x
+        exl3_gemv(x if isinstance(x, LazyNorm) else _as_bf16(x).contiguous(), delta.w, res_out=rs)
+    else:
+        d = _delta_tensor(delta).contiguous()
+        out = torch.empty(R, H, dtype=torch.bfloat16, device=rs.x.device)
+        lib().spark_add_rmsnorm(P(d), int(d.dtype == torch.float32), P(rs.x), P(w), P(out), R, H, float(eps), int(one_plus),
+                                stream())
+        rs.valid = False
+        ln = LazyNorm(rs, w, eps, one_plus)
+        ln._t = out
+        return ln, rs
+    if not rs.valid:
+        row_ssq(rs)
+    return LazyNorm(rs, w, eps, one_plus), rs
+
+
 def add_rmsnorm(delta, res, w, eps, one_plus=False):
+    if isinstance(res, Resid):
+        return _add_norm_resid(delta, res, w, eps, one_plus)
+    delta = _delta_tensor(delta)
     R, H = res.shape
     assert res.dtype == torch.float32 and res.is_contiguous()
     out = torch.empty(R, H, dtype=torch.bfloat16, device=res.device)
@@ -352,11 +526,25 @@ def rmsnorm(x, w, eps, one_plus=False):
     return out
 
 
-def embed(table, ids32):
+def embed(table, ids32, resid: bool = False):
+    """fp32 embedding rows; with `resid` a decode-round residual stream (strip partials filled in)."""
     R, H = ids32.shape[0], table.shape[1]
     out = torch.empty(R, H, dtype=torch.float32, device=table.device)
-    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)))
+    rs = Resid(out) if resid and fused_decode_rows(R, H) else None
+    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)),
+                      P(rs.ssq) if rs is not None else None, SSQ_LD)
+    if rs is not None:
+        rs.valid = True
+        return rs
     return out
+
+
+def row_ssq(rs: Resid) -> Resid:
+    """Refill the strip partials of a residual stream that was updated by a kernel that does not leave them."""
+    R, H = rs.x.shape
+    check(lib().spark_row_ssq(P(rs.x), R, H, P(rs.ssq), SSQ_LD, stream()), "spark_row_ssq")
+    rs.valid = True
+    return rs
 
 
 def swiglu(gu, limit=0.0):
@@ -406,13 +594,13 @@ def moe_route(h, w, c, e_lo=0, e_hi=None):
     return wts, ids, prow, sg
 
 
-def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32):
+def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32, pairs_early=False):
     if isinstance(w, Exl3Weight):
         return exl3_gemv(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act,
-                         limit=limit, out_f32=out_f32)
+                         limit=limit, out_f32=out_f32, pairs_early=pairs_early)
     if isinstance(w, QuantWeight):
         from . import mx
-        return mx.expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32)
+        return mx.expert_gemv(_mat(x), w, pairs, pair_expert, pair_row, act, limit, out_f32)
     E, N, K = w.shape
     return gemv_bf16(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act,
                      limit=limit, out_f32=out_f32, expert_stride=N * K, n=N, k=K)
@@ -458,11 +646,78 @@ def _side_stream(device) -> torch.cuda.Stream:
     return _side[key]
 
 
-def moe(h, w, c):
-    """Routed + shared experts; returns the bf16 block output [R, H].  Under expert parallelism (`w["ep"]` =
-    (first local expert, end)) only the local experts' pairs are computed and the result is this rank's partial
-    sum; the shared expert is added by the rank that holds it."""
-    h = _as_bf16(h).contiguous()
+def _shared_expert_decode(h, w, c):
+    """The shared expert's two GEMVs for decode rows (when it is not a pair of the stack)."""
+    sgu = w["s_gu"]
+    if isinstance(sgu, Exl3Weight):
+        return exl3_gemv(exl3_gemv(h, sgu), w["s_down"], act=1, limit=c.swiglu_limit)
+    if isinstance(sgu, QuantWeight):
+        return quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
+    return gemv_bf16(gemv_bf16(h, sgu), w["s_down"], act=1, limit=c.swiglu_limit, k=w["s_down"].shape[1])
+
+
+def _moe_decode(h, w, c, defer: bool):
+    """Decode rows (<= 16): ONE router launch (GEMV + top-k + pair tables), gate/up GEMV and SwiGLU + down GEMV
+    over the (row, expert) pairs, then the slot-order combine (deferred into the residual update when `defer`).
+    The shared expert is one more pair when it lives in the expert stack (`w["shared_in_stack"]`)."""
+    lazy = isinstance(h, LazyNorm) and h.resid.valid
+    if isinstance(h, LazyNorm) and not lazy:
+        h = h.tensor()
+    if not lazy:
+        h = _as_bf16(h).contiguous()
+    R, H = h.shape
+    dev = h.device
+    ep = w.get("ep")
+    e_lo, e_hi = ep if ep else (0, c.n_experts)
+    rank, world = w.get("tp_rank", (0, 1))
+    stacked = bool(w.get("shared_in_stack"))
+    slots = c.top_k + (1 if stacked else 0)
+    gate = w["gate"]
+    NE = c.n_experts + (1 if c.shared_gate else 0)
+    ld = (NE + 7) // 8 * 8
+    logits = scratch("router_logits", SSQ_LD * ld, torch.float32, dev)
+    counter = scratch("router_counter", 4, torch.int32, dev, zero=True)
+    wts = torch.empty(R, slots, dtype=torch.float32, device=dev)
+    ids = torch.empty(R, slots, dtype=torch.int32, device=dev)
+    prow = torch.empty(R, slots, dtype=torch.int32, device=dev)
+    shared_sep = "s_gu" in w and not stacked
+    sg = torch.empty(R, dtype=torch.float32, device=dev) if (c.shared_gate and shared_sep) else None
+    norm = h.norm_in() if lazy else None
+    x = h.resid.x if lazy else h
+    rc = lib().spark_moe_router_topk(None if lazy else P(x), 0 if lazy else x.stride(0),
+                                     C.addressof(norm) if norm is not None else None, P(gate), gate.stride(0), P(logits), ld,
+                                     R, H, c.n_experts, c.top_k, ROUTER_KIND[c.router], P(w.get("bias")), float(c.route_scale),
+                                     int(c.shared_gate), slots, e_hi - e_lo, e_lo, e_hi, rank, world, P(wts), P(ids), P(prow),
+                                     P(sg), P(counter), stream())
+    check(rc, "spark_moe_router_topk")
+    shared = None
+    side = None
+    if shared_sep:
+        hm = _mat(h)
+        main = torch.cuda.current_stream()
+        side = _side_stream(dev) if SIDE_STREAMS else None
+        if side is not None:
+            side.wait_stream(main)
+        with torch.cuda.stream(side if side is not None else main):
+            shared = _shared_expert_decode(hm, w, c)
+    Pn = R * slots
+    pe, pr = ids.view(-1), prow.view(-1)
+    gu = _expert_gemv(h, w["w_gu"], Pn, pe, pr, 0, 0.0, False)                      # [P, 2F] bf16
+    y = _expert_gemv(gu, w["w_down"], Pn, pe, None, 1, c.swiglu_limit, True, pairs_early=True)   # [P, H] fp32
+    if side is not None:
+        torch.cuda.current_stream().wait_stream(side)
+    pm = PendingMoe(y, wts, ids, slots, R, H, shared, sg)
+    return pm if defer else pm.tensor()
+
+
+def moe(h, w, c, defer: bool = False):
+    """Routed + shared experts; returns the bf16 block output [R, H] (or, with `defer`, the uncombined expert
+    outputs of a decode round).  Under expert parallelism (`w["ep"]` = (first local expert, end)) only the local
+    experts' pairs are computed and the result is this rank's partial sum; the shared expert is added by the rank
+    that holds it."""
+    if h.shape[0] * c.top_k <= DECODE_PAIRS_MAX and h.shape[0] <= SSQ_LD and FUSED_DECODE:
+        return _moe_decode(h, w, c, defer)
+    h = _as_bf16(_mat(h)).contiguous()
     R, H = h.shape
     dev = h.device
     ep = w.get("ep")
@@ -489,6 +744,14 @@ def moe(h, w, c):
                 else:
                     gu_s = gemv_bf16(h, sgu)
                     shared = gemv_bf16(gu_s, w["s_down"], act=1, limit=c.swiglu_limit, k=w["s_down"].shape[1])
+        elif w.get("shared_in_stack") and w.get("tp_rank", (0, 1))[1] > 1:
+            # every rank holds the shared expert: rank r computes it for rows r, r + world, ... (the all-reduce of
+            # the block output puts the rows together)
+            rk, wd_ = w["tp_rank"]
+            rows = torch.arange(rk, R, wd_, device=dev)
+            shared = torch.zeros(R, H, dtype=torch.bfloat16, device=dev)
+            if rows.numel():
+                shared[rows] = linear_any(swiglu(linear_any(h[rows].contiguous(), w["s_gu"]), c.swiglu_limit), w["s_down"])
         else:
             shared = linear_any(swiglu(linear_any(h, w["s_gu"]), c.swiglu_limit), w["s_down"])
     out = torch.empty(R, H, dtype=torch.bfloat16, device=dev)

@@ -238,7 +238,7 @@ class FusedAllReduce:
         S = cu._pick_slices(w.k)
         rc = cu.lib().spark_exl3_gemv(cu.P(x), x.stride(0), cu.P(w.trellis), cu.P(w.suh), cu.P(w.svh), 0, 0, 0, None,
                                       self.N, 0, None, None, 1, R, w.k, w.n, S, act, float(limit),
-                                      0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar))
+                                      0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar), None, None, 0)
         cu.check(rc, "spark_exl3_gemv(fused all-reduce)")
         self._keep = ar
         return out

@@ -178,6 +178,27 @@ class CpuTP(TPBase):
         return L.rms(res.float(), w.float(), eps).to(res.dtype), res
 
 
+class NcclTP(TPBase):
+    """Library baseline on the device: NCCL all-reduce through torch.distributed + ATen ops for the residual add
+    and the norm (what a plain PyTorch tensor-parallel implementation does); used by `bench.py --impl aten`."""
+
+    def __init__(self, group=None):
+        super().__init__(dist.get_rank(group), dist.get_world_size(group))
+        self.group = group
+
+    def allreduce(self, x):
+        y = x.float().contiguous()
+        dist.all_reduce(y, group=self.group)
+        return y.to(x.dtype)
+
+    def add_rmsnorm(self, delta, res, w, eps):
+        if isinstance(delta, ops.Partial):
+            delta = ops.linear(delta.x, delta.w)
+        res = res + self.allreduce(ops.to_tensor(delta).float()).to(res.dtype)
+        from ..oracle import layers as L
+        return L.rms(res.float(), w.float(), eps).to(torch.bfloat16), res
+
+
 class DeviceTP(TPBase):
     """Peer-memory tensor parallelism on the GPUs of one box (fused all-reduce kernels)."""
 

@@ -62,6 +62,7 @@ class _DecodeGraph:
             d["ngram_rows"] = torch.zeros(R, engine.cfg.ngram_heads, dtype=torch.int64, device=dev)
         self.plan.dev = d
         self.graph = None
+        self.graph_fed = None          # the same round followed by the device-side feedback of the sampled ids
         self.out_ids = None
         self.logits = None
         self.hidden = None
@@ -117,6 +118,27 @@ class _DecodeGraph:
         from ..ops import cuda as cu
         self.graph.replay()
         cu.add_launches(self.launches)
+
+    def replay_fed(self):
+        """Replay the round and feed its sampled ids back on the device: ids <- sampled, every position + 1.  The next
+        replay is then the next decode step without any host work in between (one row per sequence, no hashed
+        n-gram layers: their row ids come from the host)."""
+        from ..ops import cuda as cu
+        assert self.k == 1 and self.ng_host is None
+        if self.graph_fed is None:
+            if self.graph is None:
+                raise RuntimeError("run() the round once before device-fed replays")
+            m = self.engine.model
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body(True)
+                cu.check(cu.lib().spark_decode_advance(cu.P(self.dev), cu.P(self.out_ids), len(self.slots), cu.stream()),
+                         "spark_decode_advance")
+            cu.add_launches(-(self.launches + 1))
+            self.graph_fed = g
+        self.graph_fed.replay()
+        cu.add_launches(self.launches + 1)
 
     def _body(self, commit: bool):
         m = self.engine.model
@@ -202,6 +224,44 @@ class LLMEngine:
             if p + rows_per_seq > cap:
                 raise RuntimeError(f"sequence in slot {s} is at {p} tokens: {rows_per_seq} more row(s) exceed its "
                                    f"KV region of {cap} tokens")
+
+    @torch.no_grad()
+    def decode_steps(self, slots: Sequence[int], ids: Sequence[int], steps: int) -> List[List[int]]:
+        """`steps` greedy tokens for each listed sequence with the sampled ids fed back on the device: one staging
+        copy, `steps` graph replays, one read-back per step queued behind them (no host round trip between steps).
+        Returns [steps][len(slots)] token ids.  Falls back to `decode_round` per step where rounds are not captured."""
+        m = self.model
+        pos0 = [m.seqs[s].length for s in slots]
+        self._check_capacity(slots, pos0, steps)
+        if not self.use_graphs or self.cfg.ngram_layers:
+            out, cur = [], list(ids)
+            for _ in range(steps):
+                cur = self.decode_round(slots, cur)
+                out.append(cur)
+            return out
+        key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + steps))
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _DecodeGraph(self, slots, 1, key[2])
+        g.stage([[t] for t in ids], pos0)
+        ring = torch.empty(steps, len(slots), dtype=torch.int32).pin_memory()
+        first = 0
+        if g.graph is None:                      # first use of this layout: capture with one ordinary round
+            g.run(commit=True)
+            ring[0].copy_(g.out_ids, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            g.stage([[int(t)] for t in ring[0].tolist()], [p + 1 for p in pos0])
+            first = 1
+        for i in range(first, steps):
+            g.replay_fed()
+            ring[i].copy_(g.out_ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        for s, p in zip(slots, pos0):
+            m.seqs[s].length = p + steps
+        self._rounds_since_check += steps
+        if self._rounds_since_check >= 64:
+            self.check_device_status()
+        return ring.tolist()
 
     def check_device_status(self):
         """Fail-stop on a device-side error: a bounded wait that ran out (a peer that never arrived, a stalled
