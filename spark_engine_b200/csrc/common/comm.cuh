@@ -63,7 +63,47 @@ struct ArRows {
   void* out; int out_f32;                // sum (no norm) or normed rows; bf16 or fp32 [R, N]
   uint32_t* seq_ptr;                     // optional device-side sequence counter (CUDA-graph replay): the kernel
                                          // uses *seq_ptr + 1 and the last CTA stores it back
+  // optional producer of the local rows: the slot-order combine of a decode-round MoE (in == nullptr):
+  //   row r = sum_k moe_w[r, k] * moe_y[r * slots + k, :]  (pairs with moe_ids < 0 belong to other ranks)
+  //           (+ moe_sg[r] * moe_shared[r, :])
+  const float* moe_y; const float* moe_w; const int* moe_ids; int moe_slots;
+  const __nv_bfloat16* moe_shared; const float* moe_sg;
 };
+
+// Four consecutive elements of this rank's partial row: from `in`, or combined from the expert outputs.
+__device__ __forceinline__ float4 ar_local4(const ArRows& a, int r, int i) {
+  if (a.in != nullptr) {
+    if (a.in_f32) return ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(r) * a.N + i);
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(r) * a.N + i);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+    return make_float4(f0.x, f0.y, f1.x, f1.y);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < a.moe_slots; k0 += 4) {            // four slots' loads in flight; summed in slot order
+    float4 v[4]; float w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int pi = r * a.moe_slots + k0 + u;
+      const bool live = (k0 + u) < a.moe_slots && a.moe_ids[pi] >= 0;
+      w[u] = live ? a.moe_w[pi] : 0.f;
+      v[u] = live ? ld_f4(a.moe_y + static_cast<size_t>(pi) * a.N + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      acc.x = fmaf(w[u], v[u].x, acc.x); acc.y = fmaf(w[u], v[u].y, acc.y);
+      acc.z = fmaf(w[u], v[u].z, acc.z); acc.w = fmaf(w[u], v[u].w, acc.w);
+    }
+  }
+  if (a.moe_shared != nullptr) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(a.moe_shared + static_cast<size_t>(r) * a.N + i);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+    const float g = a.moe_sg ? a.moe_sg[r] : 1.f;
+    acc.x += g * f0.x; acc.y += g * f0.y; acc.z += g * f1.x; acc.w += g * f1.y;
+  }
+  return acc;
+}
 
 // Sequence number of this launch: from the device counter when there is one (replayed graphs), else the
 // host-provided value.

@@ -3,9 +3,9 @@
 //                 kv_base[slot] + pos (bf16, or e4m3 with one fp32 scale per (token, head)); indexer
 //                 query norm+rope, raw indexer key append, and the mean-pooled (then normed + roped)
 //                 key of every 4-token block this row completes.
-//   attn_decode : split-KV (256 tokens per CTA): scores -> per-head softmax stats -> P.V, partials
-//                 (m, l, o) to scratch;  tokens are either the row's whole context or a selected list
-//                 (block-sparse top-k + tail).
+//   attn_decode : split-KV (64 tokens per CTA) on warp-level tensor-core MMAs: scores -> per-head softmax
+//                 stats -> P.V, partials (m, l, o) to scratch;  tokens are either the row's whole context or a
+//                 selected list (block-sparse top-k + tail); optional ancestor mask for tree verification.
 //   attn_merge  : fixed-order merge of the splits, sigmoid output gate, bf16 out.
 // All reductions have a fixed order (no float atomics): run-to-run bitwise equal, and a row's result is
 // independent of the other rows in the batch.
@@ -29,6 +29,7 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, AttnDims a,
                  const double* __restrict__ inv_freq,
                  const int* __restrict__ pos, const long long* __restrict__ row_kv,   // kv_base[slot] per row
                  const int* __restrict__ row_j,                                       // row index inside its segment
+                 const int* __restrict__ row_pos0,                                    // tree verify: first in-flight position
                  __nv_bfloat16* __restrict__ qbuf,                                    // [R, Hq, D]
                  void* __restrict__ kc, void* __restrict__ vc,                        // [tokens, Hkv, D]
                  float* __restrict__ ks, float* __restrict__ vs,                      // fp8 scales [tokens, Hkv]
@@ -42,7 +43,9 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, AttnDims a,
   const int qw = a.D * (a.gated ? 2 : 1);
   const int nq = a.Hq * qw, nkv = a.Hkv * a.D;
   const int p = pos[r];
-  const long long tok = row_kv[r] + p;
+  // KV row of this token: its position for chains; for tree rows (row_pos0 given) the in-flight slot pos0 + j, because
+  // sibling nodes share a position (the rotary angle still uses the position)
+  const long long tok = row_kv[r] + (row_pos0 ? row_pos0[r] + row_j[r] : p);
   const __nv_bfloat16* row = qkv + static_cast<size_t>(r) * ld;
   int kind, head, dim, off;            // kind 0 q, 1 k, 2 v, 3 indexer q, 4 indexer key
   if (job < a.Hq) { kind = 0; head = job; dim = a.D; off = head * qw; }
@@ -58,6 +61,7 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, AttnDims a,
   if (kind == 4) {
     // raw key of this row; pooled key only when this row completes a block
     for (int d = t; d < dim; d += 128) ik_raw[tok * dim + d] = __bfloat162float(row[off + d]);
+    if (row_pos0 != nullptr) return;          // tree rows: blocks are pooled when the accepted path is committed
     if ((p + 1) % a.block != 0) return;
     // mean of the block's raw keys BEFORE norm + rope at the block's first position
     for (int d = t; d < dim; d += 128) {
@@ -250,6 +254,204 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ qbuf, const void* __restric
   }
 }
 
+
+// ------------------------------------------------------------------------------------------ decode (tensor cores)
+// Split-KV decode / verify attention: grid (row, kv head, split of 64 tokens), 4 warps.  The split's K and V rows
+// (the row's context, or its selected-token list) are requested with cp.async in one go -- 64 KB in flight per CTA
+// for head_dim 256 -- so a split costs one memory round trip instead of one per group of tokens.  The q heads that
+// share the kv head are the M dimension of the warp-level MMA (<= 16), S = Q K^T and O = P V run on m16n8k16 bf16
+// with fp32 accumulation; V fragments come from ldmatrix.trans.  FP8 KV (e4m3 + one fp32 scale per token and head)
+// is converted to bf16 tiles in shared memory, the scales are folded into S and P.
+// Tree verification: `anc` holds, per row, the bitmask of segment-local rows it may attend to (itself and its
+// ancestors); tokens at or beyond the segment's first in-flight position (`row_pos0`) are kept only if their bit is
+// set, committed tokens are always visible.  Chains pass anc == nullptr (causal by the context length).
+// Splits are merged in ascending order by attn_merge_kernel: fixed order, a row never depends on its batch mates.
+// Replaces engine-rs/shim/qwen_qsa.cu:421-882 (attn_tc / attn_tcp / attn_combine) and the tree paths of
+// engine-rs/src/mla_latent.rs:472-773 for GQA layers.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_u32(smem)));
+}
+
+struct AttnDecodeArgs {
+  const __nv_bfloat16* qbuf; const void* kc; const void* vc; const float* ks; const float* vs;
+  const int* pos; const long long* row_kv; const int* sel; const int* sel_n; int sel_ld;
+  const int* row_pos0; const int* row_j; const uint32_t* anc;     // optional (tree verify / explicit in-flight index)
+  float* part_o; float* part_ml; int Hq, Hkv; float scale;
+};
+
+constexpr int ATT_ROWS = 16;       // q heads per kv head, padded to the MMA's M
+
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128)
+attn_decode_tc_kernel(const __grid_constant__ AttnDecodeArgs a) {
+  constexpr int LD = D + 8;                                   // bf16 elements per tile row (16-byte padded)
+  extern __shared__ __align__(16) uint8_t smem_att[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_att);                  // [16][LD]
+  __nv_bfloat16* Ks = Qs + ATT_ROWS * LD;                                           // [64][LD]
+  __nv_bfloat16* Vs = Ks + ATT_TS * LD;                                             // [64][LD]
+  float* Ss = reinterpret_cast<float*>(Vs + ATT_TS * LD);                           // [16][68]
+  __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + ATT_ROWS * 68);         // [16][72]
+  int* stok = reinterpret_cast<int*>(Ps + ATT_ROWS * 72);                           // [64]
+  float* ksc = reinterpret_cast<float*>(stok + ATT_TS);                             // [64]
+  float* vsc = ksc + ATT_TS;                                                        // [64]
+  uint8_t* stage = reinterpret_cast<uint8_t*>(vsc + ATT_TS);                        // FP8: [2][64][D] bytes
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
+  const int rep = a.Hq / a.Hkv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int pos0 = a.row_pos0 ? a.row_pos0[r] : 0;
+  const int n_ctx = a.sel ? a.sel_n[r] : (a.row_pos0 ? pos0 + a.row_j[r] + 1 : a.pos[r] + 1);
+  const int t0 = sp * ATT_TS;
+  const size_t pbase = (static_cast<size_t>(r) * a.Hq + hk * rep) * nsplit + sp;
+  if (t0 >= n_ctx) {                     // empty split: neutral partial
+    if (tid < rep) { a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2] = -INFINITY; a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2 + 1] = 0.f; }
+    return;
+  }
+  const int nt = min(ATT_TS, n_ctx - t0);
+  const long long base = a.row_kv[r];
+  const uint32_t anc = a.anc ? a.anc[r] : 0xffffffffu;
+  if (tid < ATT_TS) {
+    int tk = -1;
+    if (tid < nt) {
+      tk = a.sel ? a.sel[static_cast<size_t>(r) * a.sel_ld + t0 + tid] : t0 + tid;
+      if (a.anc && tk >= pos0 && !((anc >> min(tk - pos0, 31)) & 1u)) tk = -1;      // not an ancestor of this row
+    }
+    stok[tid] = tk;
+    if (FP8) {
+      ksc[tid] = tk >= 0 ? a.ks[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
+      vsc[tid] = tk >= 0 ? a.vs[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
+    }
+  }
+  __syncthreads();
+  // ---- request the whole split: K and V rows (16-byte pieces), zero rows for masked / missing tokens
+  constexpr int ROWB = FP8 ? D : D * 2;                       // bytes per token row in the cache
+  constexpr int CH = ROWB / 16;
+  for (int i = tid; i < ATT_TS * CH; i += 128) {
+    const int tok = i / CH, c = i - tok * CH;
+    const int tk = stok[tok];
+    uint8_t* dk = FP8 ? stage + tok * D + c * 16 : reinterpret_cast<uint8_t*>(Ks + tok * LD) + c * 16;
+    uint8_t* dv = FP8 ? stage + (ATT_TS + tok) * D + c * 16 : reinterpret_cast<uint8_t*>(Vs + tok * LD) + c * 16;
+    if (tk >= 0) {
+      const size_t off = (static_cast<size_t>(base + tk) * a.Hkv + hk) * ROWB + c * 16;
+      cp_async16(dk, reinterpret_cast<const uint8_t*>(a.kc) + off);
+      cp_async16(dv, reinterpret_cast<const uint8_t*>(a.vc) + off);
+    } else {
+      *reinterpret_cast<uint4*>(dk) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(dv) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  for (int i = tid; i < ATT_ROWS * (D / 8); i += 128) {       // queries of the heads that share this kv head
+    const int h = i / (D / 8), c = i - h * (D / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (h < rep) v = *reinterpret_cast<const uint4*>(a.qbuf + (static_cast<size_t>(r) * a.Hq + hk * rep + h) * D + c * 8);
+    *reinterpret_cast<uint4*>(Qs + h * LD + c * 8) = v;
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  if (FP8) {                                                  // e4m3 bytes -> bf16 tiles (scales applied to S and P)
+    for (int i = tid; i < ATT_TS * (D / 4); i += 128) {
+      const int tok = i / (D / 4), c = i - tok * (D / 4);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(stage + (which * ATT_TS + tok) * D + c * 4);
+        const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(static_cast<float>(f8[0]), static_cast<float>(f8[1]));
+        __nv_bfloat162 b1 = __floats2bfloat162_rn(static_cast<float>(f8[2]), static_cast<float>(f8[3]));
+        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+        *reinterpret_cast<uint2*>((which ? Vs : Ks) + tok * LD + c * 4) = o;
+      }
+    }
+    __syncthreads();
+  }
+  // ---- S = Q K^T: warp w owns tokens [16w, 16w + 16)
+  {
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* q_lo = Qs + g * LD + 2 * t;
+    const __nv_bfloat16* q_hi = Qs + (g + 8) * LD + 2 * t;
+    const __nv_bfloat16* k0 = Ks + (warp * 16 + g) * LD + 2 * t;
+    const __nv_bfloat16* k1 = Ks + (warp * 16 + 8 + g) * LD + 2 * t;
+#pragma unroll 4
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 8);
+      mma_bf16_16816(c0, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k0 + kk * 16), *reinterpret_cast<const uint32_t*>(k0 + kk * 16 + 8));
+      mma_bf16_16816(c1, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k1 + kk * 16), *reinterpret_cast<const uint32_t*>(k1 + kk * 16 + 8));
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float* c = j ? c1 : c0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g + (e >> 1) * 8, tok = warp * 16 + j * 8 + 2 * t + (e & 1);
+        float v = c[e] * a.scale;
+        if (FP8) v *= ksc[tok];
+        Ss[row * 68 + tok] = stok[tok] >= 0 ? v : -INFINITY;
+      }
+    }
+  }
+  __syncthreads();
+  // ---- softmax statistics of the split; P in bf16 (the row sum uses the same rounded values)
+  for (int row = warp * 4; row < warp * 4 + 4; ++row) {
+    const float s0 = Ss[row * 68 + lane], s1 = Ss[row * 68 + lane + 32];
+    const float m = warp_max(fmaxf(s0, s1));
+    float p0 = m == -INFINITY ? 0.f : __expf(s0 - m), p1 = m == -INFINITY ? 0.f : __expf(s1 - m);
+    p0 = __bfloat162float(__float2bfloat16(p0)); p1 = __bfloat162float(__float2bfloat16(p1));
+    const float l = warp_sum(p0 + p1);
+    Ps[row * 72 + lane] = __float2bfloat16(FP8 ? p0 * vsc[lane] : p0);
+    Ps[row * 72 + lane + 32] = __float2bfloat16(FP8 ? p1 * vsc[lane + 32] : p1);
+    if (lane == 0 && row < rep) {
+      a.part_ml[(pbase + static_cast<size_t>(row) * nsplit) * 2] = m;
+      a.part_ml[(pbase + static_cast<size_t>(row) * nsplit) * 2 + 1] = l;
+    }
+  }
+  __syncthreads();
+  // ---- O = P V: warp w owns dims [w D/4, (w+1) D/4)
+  {
+    constexpr int NT = D / 32;                                // 8-wide dim tiles per warp
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+    const __nv_bfloat16* p_lo = Ps + g * 72 + 2 * t;
+    const __nv_bfloat16* p_hi = Ps + (g + 8) * 72 + 2 * t;
+#pragma unroll
+    for (int kk = 0; kk < ATT_TS / 16; ++kk) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16 + 8);
+      const __nv_bfloat16* vrow = Vs + (kk * 16 + (lane & 15)) * LD + warp * (D / 4);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        uint32_t b0, b1;
+        ldmatrix_x2_trans(b0, b1, vrow + j * 8);
+        mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int d = warp * (D / 4) + j * 8 + 2 * t;
+      if (g < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g) * nsplit) * D + d) = make_float2(o[j][0], o[j][1]);
+      if (g + 8 < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g + 8) * nsplit) * D + d) = make_float2(o[j][2], o[j][3]);
+    }
+  }
+}
+
+template <int D, bool FP8>
+static size_t attn_decode_tc_smem() {
+  return static_cast<size_t>(ATT_ROWS + 2 * ATT_TS) * (D + 8) * 2 + ATT_ROWS * 68 * 4 + ATT_ROWS * 72 * 2 + ATT_TS * 12 +
+         (FP8 ? 2 * ATT_TS * D : 0);
+}
+
 // grid (R, Hq); D threads (<= 256).  Splits merged in ascending order.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nsplit,
                                   const __nv_bfloat16* __restrict__ qkv, int ld, int gated, int Hq, int D,
@@ -285,35 +487,75 @@ extern "C" int spark_attn_prep(const void* qkv, int ld, int R, int Hq, int Hkv, 
                                const float* q_norm, const float* k_norm, const float* iq_norm, const float* ik_norm,
                                const double* inv_freq, const int* pos, const long long* row_kv, const int* row_j,
                                void* qbuf, void* kc, void* vc, float* ks, float* vs, float* qi_buf, float* ik_raw,
-                               float* ik_pool, cudaStream_t s) {
+                               float* ik_pool, cudaStream_t s, const int* row_pos0) {
   if (R <= 0) return 0;
   if (D > 256 || idx_dim > 256) return -5;
   AttnDims a{Hq, Hkv, D, rope_dim, gated, qk_norm, idx_heads, idx_dim, block, fp8, eps};
   dim3 grid(R, Hq + 2 * Hkv + idx_heads + (idx_dim > 0 ? 1 : 0));
   const cudaError_t err = spark_launch_pdl(attn_prep_kernel, grid, dim3(128), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qkv, ld, a,
-                                           q_norm, k_norm, iq_norm, ik_norm, inv_freq, pos, row_kv, row_j, (__nv_bfloat16*)qbuf,
+                                           q_norm, k_norm, iq_norm, ik_norm, inv_freq, pos, row_kv, row_j, row_pos0, (__nv_bfloat16*)qbuf,
                                            kc, vc, ks, vs, qi_buf, ik_raw, ik_pool);
   return err == cudaSuccess ? 0 : -4;
 }
 
+// Launches split + merge for both entry points.  head_dim 64 / 128 / 256 with <= 16 q heads per kv head runs the
+// tensor-core kernel; anything else the scalar one (no tree mask there).
+template <int D, bool FP8>
+static cudaError_t launch_decode_tc(const AttnDecodeArgs& a, dim3 grid, cudaStream_t s, bool pdl) {
+  auto kern = attn_decode_tc_kernel<D, FP8>;
+  const size_t smem = attn_decode_tc_smem<D, FP8>();
+  static bool attr_set = false;
+  if (!attr_set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); attr_set = true; }
+  if (pdl) return spark_launch_pdl(kern, grid, dim3(128), smem, s, dim3(1, 1, 1), a);
+  kern<<<grid, 128, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+static int attn_decode_launch(const void* qbuf, const void* kc, const void* vc, const float* ks, const float* vs, int fp8,
+                              const int* pos, const long long* row_kv, const int* sel, const int* sel_n, int sel_ld,
+                              const int* row_pos0, const int* row_j, const uint32_t* anc, float* part_o, float* part_ml,
+                              int nsplit, const void* qkv, int ld, int gated, int R, int Hq, int Hkv, int D, float scale,
+                              void* out, cudaStream_t s, bool pdl) {
+  dim3 grid(R, Hkv, nsplit);
+  const int rep = Hq / Hkv;
+  cudaError_t err;
+  if ((D == 64 || D == 128 || D == 256) && rep <= ATT_ROWS && (row_pos0 == nullptr) == (row_j == nullptr)) {
+    AttnDecodeArgs a{(const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld, row_pos0, row_j, anc,
+                     part_o, part_ml, Hq, Hkv, scale};
+    if (D == 64) err = fp8 ? launch_decode_tc<64, true>(a, grid, s, pdl) : launch_decode_tc<64, false>(a, grid, s, pdl);
+    else if (D == 128) err = fp8 ? launch_decode_tc<128, true>(a, grid, s, pdl) : launch_decode_tc<128, false>(a, grid, s, pdl);
+    else err = fp8 ? launch_decode_tc<256, true>(a, grid, s, pdl) : launch_decode_tc<256, false>(a, grid, s, pdl);
+  } else {
+    if (D > 256 || rep > ATT_MAXREP || anc != nullptr) return -5;
+    if (fp8)
+      attn_decode_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
+                                                    part_o, part_ml, Hq, Hkv, D, scale);
+    else
+      attn_decode_kernel<false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
+                                                     part_o, part_ml, Hq, Hkv, D, scale);
+    err = cudaGetLastError();
+  }
+  if (err != cudaSuccess) return -4;
+  if (pdl)
+    err = spark_launch_pdl(attn_merge_kernel, dim3(R, Hq), dim3(D), 0, s, dim3(1, 1, 1), (const float*)part_o, (const float*)part_ml,
+                           nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D, (__nv_bfloat16*)out);
+  else {
+    attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D, (__nv_bfloat16*)out);
+    err = cudaGetLastError();
+  }
+  return err == cudaSuccess ? 0 : -4;
+}
+
+// row_pos0 / row_j (both or neither): first in-flight position of the row's segment and the row's index inside it (the
+// row's KV entry sits at row_pos0 + row_j); anc: optional per-row ancestor bitmask over segment rows (tree verify).
 extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* vc, const float* ks, const float* vs,
                                  int fp8, const int* pos, const long long* row_kv, const int* sel, const int* sel_n,
                                  int sel_ld, float* part_o, float* part_ml, int nsplit, const void* qkv, int ld,
-                                 int gated, int R, int Hq, int Hkv, int D, float scale, void* out, cudaStream_t s) {
+                                 int gated, int R, int Hq, int Hkv, int D, float scale, void* out, cudaStream_t s,
+                                 const int* row_pos0, const int* row_j, const unsigned* anc) {
   if (R <= 0) return 0;
-  if (D > 256 || Hq / Hkv > ATT_MAXREP) return -5;
-  dim3 grid(R, Hkv, nsplit);
-  cudaError_t err;
-  if (fp8)
-    err = spark_launch_pdl(attn_decode_kernel<true>, grid, dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qbuf, kc, vc, ks, vs,
-                           pos, row_kv, sel, sel_n, sel_ld, part_o, part_ml, Hq, Hkv, D, scale);
-  else
-    err = spark_launch_pdl(attn_decode_kernel<false>, grid, dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)qbuf, kc, vc, ks, vs,
-                           pos, row_kv, sel, sel_n, sel_ld, part_o, part_ml, Hq, Hkv, D, scale);
-  if (err != cudaSuccess) return -4;
-  err = spark_launch_pdl(attn_merge_kernel, dim3(R, Hq), dim3(D), 0, s, dim3(1, 1, 1), (const float*)part_o, (const float*)part_ml,
-                         nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D, (__nv_bfloat16*)out);
-  return err == cudaSuccess ? 0 : -4;
+  return attn_decode_launch(qbuf, kc, vc, ks, vs, fp8, pos, row_kv, sel, sel_n, sel_ld, row_pos0, row_j, anc, part_o, part_ml,
+                            nsplit, qkv, ld, gated, R, Hq, Hkv, D, scale, out, s, true);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -349,7 +591,7 @@ extern "C" int spark_attn_decode_noalloc(const void* qbuf, const void* kc, const
                                          int ld, int gated, int R, int Hq, int Hkv, int D, float scale, void* out,
                                          cudaStream_t s) {
   if (R <= 0) return 0;
-  if (D > 256 || Hq / Hkv > ATT_MAXREP || nsplit <= 0) return -5;
+  if (D > 256 || Hq / Hkv > ATT_ROWS || nsplit <= 0) return -5;
   const long long need = static_cast<long long>(R) * Hq * nsplit * (D + 2);
   if (need > SPARK_ATTN_NOALLOC_MAX_FLOATS) {
     fprintf(stderr, "spark_attn_decode_noalloc: rows*heads*splits*(head_dim+2) = %lld floats exceeds the built-in "
@@ -365,14 +607,6 @@ extern "C" int spark_attn_decode_noalloc(const void* qbuf, const void* kc, const
   }
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<size_t>(R) * Hq * nsplit * D;
-  dim3 grid(R, Hkv, nsplit);
-  if (fp8)
-    attn_decode_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
-                                                  part_o, part_ml, Hq, Hkv, D, scale);
-  else
-    attn_decode_kernel<false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
-                                                   part_o, part_ml, Hq, Hkv, D, scale);
-  attn_merge_kernel<<<dim3(R, Hq), D, 0, s>>>(part_o, part_ml, nsplit, (const __nv_bfloat16*)qkv, ld, gated, Hq, D,
-                                              (__nv_bfloat16*)out);
-  return spark_launch_rc(__func__);
+  return attn_decode_launch(qbuf, kc, vc, ks, vs, fp8, pos, row_kv, sel, sel_n, sel_ld, nullptr, nullptr, nullptr, part_o,
+                            part_ml, nsplit, qkv, ld, gated, R, Hq, Hkv, D, scale, out, s, false);
 }

@@ -14,6 +14,7 @@
 // engine-rs/shim/rdma_arn.cu:84-125,104-113).  Two slot sets alternate by sequence parity: a rank can only
 // reach sequence s+2 after every peer has finished reading set s.
 #include "../common/comm.cuh"
+#include "../common/decode.cuh"
 
 namespace spark {
 
@@ -34,6 +35,8 @@ __global__ void comm_barrier_kernel(CommCtx c, long long flag_off, uint32_t seq)
 // grid = R CTAs (one row each), 256 threads.  N % 4 == 0.
 __global__ void __launch_bounds__(256)
 allreduce_rows_kernel(ArRows a_in) {
+  pdl_wait();
+  pdl_trigger();
   ArRows a = a_in;
   a.seq = comm_seq(a.seq_ptr, a.seq);
   __shared__ float red[8];
@@ -41,14 +44,7 @@ allreduce_rows_kernel(ArRows a_in) {
   const int r = blockIdx.x, W = a.c.world;
   const size_t set = static_cast<size_t>(a.seq & 1) * W * a.rows_cap * a.N;
   for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
-    float4 v;
-    if (a.in_f32) v = ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(r) * a.N + i);
-    else {
-      const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(r) * a.N + i);
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
-      v = make_float4(f0.x, f0.y, f1.x, f1.y);
-    }
+    const float4 v = ar_local4(a, r, i);
     for (int p = 0; p < W; ++p) {
       float* dst = reinterpret_cast<float*>(a.c.peers[p] + a.slot_off) + set + (static_cast<size_t>(a.c.rank) * a.rows_cap + r) * a.N + i;
       st_f4(dst, v);
@@ -59,6 +55,95 @@ allreduce_rows_kernel(ArRows a_in) {
   __syncthreads();
   // every CTA finishes its own row once all flags are in
   ar_rows_tail(a, a.seq, r, gridDim.x, red);
+}
+
+// ------------------------------------------------------------------------------------------ vocabulary-parallel arg-max
+// Every rank scores its slice of the vocabulary; only (value, index) packets travel.  Stage 1 (many CTAs per row)
+// leaves per-chunk winners; stage 2 (one warp per row) picks the local winner, stores the packet {value, global id}
+// into slot [rank][row] of every peer, raises the flags once all rows are out, waits (bounded) for every rank's
+// flag and picks the global winner in rank order (ties -> lowest id), so all ranks agree bit for bit.
+// Reference: engine-rs/src/head_select.rs:42-67, shim/latent.cu:901-940 (gumbel_argmax_part / _packet).
+struct PkArgs {
+  CommCtx c;
+  long long slot_off;        // float2-sized packets [2][world][rows_cap]
+  long long flag_off;        // u32 [world]
+  uint32_t* seq_ptr;         // device-side sequence counter
+  int* counter;
+  int rows_cap, vocab_off;
+};
+
+__global__ void __launch_bounds__(256)
+tp_argmax_part_kernel(const float* __restrict__ logits, int V, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, c = blockIdx.y, nc = gridDim.y;
+  const int per = (V + nc - 1) / nc;
+  const int i0 = c * per, i1 = min(V, i0 + per);
+  const float* x = logits + static_cast<size_t>(r) * V;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = i0 + threadIdx.x; i < i1; i += 256) {
+    const float v = x[i];
+    if (v > best) { best = v; bi = i; }                   // ascending i per thread: first maximum kept
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) if (sv[i] > best || (sv[i] == best && si[i] < bi)) { best = sv[i]; bi = si[i]; }
+    pv[r * nc + c] = best; pi[r * nc + c] = bi;
+  }
+}
+
+// grid R (<= 64, all co-resident), 32 threads
+__global__ void tp_argmax_packets_kernel(PkArgs a, const float* __restrict__ pv, const int* __restrict__ pi, int nc,
+                                         int* __restrict__ out_id) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, lane = threadIdx.x, W = a.c.world;
+  const uint32_t seq = comm_seq(a.seq_ptr, 0);
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = lane; i < nc; i += 32) {
+    const float v = pv[r * nc + i]; const int ix = pi[r * nc + i];
+    if (v > best || (v == best && ix < bi)) { best = v; bi = ix; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const size_t set = static_cast<size_t>(seq & 1) * W * a.rows_cap;
+  if (lane < W) {
+    float2 pk; pk.x = best; pk.y = __int_as_float(bi + a.vocab_off);
+    *reinterpret_cast<float2*>(a.c.peers[lane] + a.slot_off + (set + static_cast<size_t>(a.c.rank) * a.rows_cap + r) * 8) = pk;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.counter = 0;
+      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, seq);
+      *a.seq_ptr = seq;
+    }
+  }
+  bool ok = true;
+  if (lane < W) ok = wait_flag(a.c, reinterpret_cast<const uint32_t*>(a.c.peers[a.c.rank] + a.flag_off) + lane, seq, lane);
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) { if (lane == 0) out_id[r] = 0; return; }
+  if (lane == 0) {
+    float gv = -INFINITY; int gi = 0x7fffffff;
+    for (int p = 0; p < W; ++p) {                          // rank order; ties -> lowest id
+      const float* q = reinterpret_cast<const float*>(a.c.peers[a.c.rank] + a.slot_off + (set + static_cast<size_t>(p) * a.rows_cap + r) * 8);
+      const float pvx = __ldcg(q);
+      const int ix = __float_as_int(__ldcg(q + 1));
+      if (pvx > gv || (pvx == gv && ix < gi)) { gv = pvx; gi = ix; }
+    }
+    out_id[r] = gi;
+  }
 }
 
 // ------------------------------------------------------------------------------------------ RS / AG by rows
@@ -260,14 +345,7 @@ ar_push_kernel(ArRows a_in) {
   const size_t set = static_cast<size_t>(a.seq & 1) * W * a.rows_cap * a.N;
   for (int r = blockIdx.x; r < a.R; r += gridDim.x) {
     for (int i = threadIdx.x * 4; i < a.N; i += blockDim.x * 4) {
-      float4 v;
-      if (a.in_f32) v = ld_f4(reinterpret_cast<const float*>(a.in) + static_cast<size_t>(r) * a.N + i);
-      else {
-        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.in) + static_cast<size_t>(r) * a.N + i);
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
-        v = make_float4(f0.x, f0.y, f1.x, f1.y);
-      }
+      const float4 v = ar_local4(a, r, i);
       for (int p = 0; p < W; ++p)
         st_f4(reinterpret_cast<float*>(a.c.peers[p] + a.slot_off) + set + (static_cast<size_t>(a.c.rank) * a.rows_cap + r) * a.N + i, v);
     }
@@ -289,20 +367,47 @@ ar_tail_kernel(ArRows a_in, int* tail_counter) {
   }
 }
 
+// CTAs of the one-kernel form that are certainly co-resident on an otherwise idle device (occupancy query).  A CTA
+// of that form waits for flags that every rank raises only after ALL of its CTAs have pushed; CTAs of this grid
+// that are not resident yet can still start later (no other grid depends on this one), so the wait always ends,
+// but the form is only used well below this number so that it normally ends at once.
+static int ar_coresident_limit() {
+  static int limit = 0;
+  if (limit == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_rows_kernel, 256, 0);
+    limit = sms * (per_sm > 0 ? per_sm : 1) / 4;
+    if (limit < 1) limit = 1;
+  }
+  return limit;
+}
+
+// moe: optional {y, wts, ids, slots, shared, sg} = the local rows are the slot-order combine of a decode MoE (in == null).
+struct ArMoe { const float* y; const float* w; const int* ids; int slots; const void* shared; const float* sg; };
+
 extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long long flag_off, unsigned seq, int rows_cap,
                                     int R, int N, const void* in, int in_f32, int* counter, float* res,
-                                    const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s, void* seq_ptr) {
+                                    const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s, void* seq_ptr,
+                                    const ArMoe* moe) {
   if (R <= 0) return 0;
   if (N % 4 || R > rows_cap) return -5;
+  if ((in == nullptr) == (moe == nullptr)) return -5;
   ArRows a;
   a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = seq; a.rows_cap = rows_cap; a.R = R; a.N = N;
   a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32; a.seq_ptr = (uint32_t*)seq_ptr;
-  if (R <= 64) {                 // all CTAs co-resident: one kernel pushes, signals, waits and reduces
-    allreduce_rows_kernel<<<R, 256, 0, s>>>(a);
-  } else {
-    ar_push_kernel<<<R < 592 ? R : 592, 256, 0, s>>>(a);
-    ar_tail_kernel<<<R < 296 ? R : 296, 256, 0, s>>>(a, counter + 1);
+  a.moe_y = nullptr; a.moe_w = nullptr; a.moe_ids = nullptr; a.moe_slots = 0; a.moe_shared = nullptr; a.moe_sg = nullptr;
+  if (moe) {
+    a.moe_y = moe->y; a.moe_w = moe->w; a.moe_ids = moe->ids; a.moe_slots = moe->slots;
+    a.moe_shared = (const __nv_bfloat16*)moe->shared; a.moe_sg = moe->sg;
   }
+  if (R <= 64 && R <= ar_coresident_limit()) {       // one kernel pushes, signals, waits and reduces
+    const cudaError_t e = spark_launch_pdl(allreduce_rows_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), a);
+    return e == cudaSuccess ? 0 : -4;
+  }
+  ar_push_kernel<<<R < 592 ? R : 592, 256, 0, s>>>(a);
+  ar_tail_kernel<<<R < 296 ? R : 296, 256, 0, s>>>(a, counter + 1);
   return spark_launch_rc(__func__);
 }
 
@@ -352,4 +457,21 @@ extern "C" int spark_wait_flags(const HostCtx* h, long long flag_off, unsigned s
 extern "C" int spark_wait_flags_dev(const HostCtx* h, long long flag_off, void* seq_ptr, int bump, cudaStream_t s) {
   wait_flags_kernel<<<1, 32, 0, s>>>(to_ctx(h), flag_off, 0, (uint32_t*)seq_ptr, bump);
   return spark_launch_rc(__func__);
+}
+
+// Vocabulary-parallel greedy sampling: logits fp32 [R, V_local] -> out_id [R] (global ids, identical on all ranks).
+// part_v / part_i: scratch of R * 64 entries each; seq_ptr: device sequence counter of this channel.
+extern "C" int spark_tp_argmax(const HostCtx* h, long long slot_off, long long flag_off, void* seq_ptr, int* counter,
+                               int rows_cap, const float* logits, int R, int V, int vocab_off, float* part_v, int* part_i,
+                               int* out_id, cudaStream_t s) {
+  if (R <= 0) return 0;
+  if (R > rows_cap || R > 64 || seq_ptr == nullptr) return -5;
+  const int nc = V >= 16384 ? 64 : (V >= 2048 ? 8 : 1);
+  cudaError_t e = spark_launch_pdl(tp_argmax_part_kernel, dim3(R, nc), dim3(256), 0, s, dim3(1, 1, 1), logits, V, part_v, part_i);
+  if (e != cudaSuccess) return -4;
+  PkArgs a;
+  a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq_ptr = (uint32_t*)seq_ptr; a.counter = counter;
+  a.rows_cap = rows_cap; a.vocab_off = vocab_off;
+  e = spark_launch_pdl(tp_argmax_packets_kernel, dim3(R), dim3(32), 0, s, dim3(1, 1, 1), a, (const float*)part_v, (const int*)part_i, nc, out_id);
+  return e == cudaSuccess ? 0 : -4;
 }

@@ -58,50 +58,19 @@ __global__ void rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ x, const f
 
 // A token id outside [0, V) never reaches memory: its row is zero and the status word records {ST_BOUNDS, row, id}
 // (ids come from clients; the host also validates them, this is the last line).
-// With `ssq` (H % 128 == 0) it also leaves the strip partial sums of squares of the row: the first block's deferred
-// RMSNorm reads them (decode.cuh).
 __global__ void embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int H, int V, int* __restrict__ status, float* __restrict__ ssq,
-                             int ssq_ld) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x;
   const int id = ids[r];
-  const bool bad = id < 0 || id >= V;
-  if (bad && threadIdx.x == 0 && status) set_status(status, ST_BOUNDS, r, id, V);
-  const __nv_bfloat16* src = table + static_cast<size_t>(bad ? 0 : id) * H;
-  if (ssq == nullptr) {
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-      out[static_cast<size_t>(r) * H + i] = bad ? 0.f : __bfloat162float(src[i]);
+  if (id < 0 || id >= V) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = 0.f;
+    if (threadIdx.x == 0 && status) set_status(status, ST_BOUNDS, r, id, V);
     return;
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int strip = warp; strip * 128 < H; strip += nw) {
-    const int col = strip * 128 + lane * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (!bad) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(src + col);
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
-      v = make_float4(f0.x, f0.y, f1.x, f1.y);
-    }
-    *reinterpret_cast<float4*>(out + static_cast<size_t>(r) * H + col) = v;
-    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-    if (lane == 0) ssq[static_cast<size_t>(strip) * ssq_ld + r] = ss;
-  }
-}
-
-// Strip partial sums of squares of existing fp32 rows (entry into the deferred-norm chain from a path that updated
-// the residual without leaving them).  grid R, one warp per strip.
-__global__ void row_ssq_kernel(const float* __restrict__ res, int H, float* __restrict__ ssq, int ssq_ld) {
-  pdl_wait();
-  pdl_trigger();
-  const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int strip = warp; strip * 128 < H; strip += nw) {
-    const float4 v = *reinterpret_cast<const float4*>(res + static_cast<size_t>(r) * H + strip * 128 + lane * 4);
-    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-    if (lane == 0) ssq[static_cast<size_t>(strip) * ssq_ld + r] = ss;
-  }
+  const __nv_bfloat16* src = table + static_cast<size_t>(id) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(r) * H + i] = __bfloat162float(src[i]);
 }
 
 // End of a device-fed decode round (one row per sequence): the sampled ids become the next round's input ids and
@@ -218,18 +187,9 @@ extern "C" void spark_rmsnorm_bf16(const void* x, const float* w, void* out, int
   if (R <= 0) return;
   rmsnorm_bf16_kernel<<<R, 256, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)out, H, eps, one_plus);
 }
-extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s, int V, int* status,
-                            float* ssq, int ssq_ld) {
+extern "C" void spark_embed(const void* table, const int* ids, float* out, int R, int H, cudaStream_t s, int V, int* status) {
   if (R <= 0) return;
-  if (H % 128) ssq = nullptr;
-  spark_launch_pdl(embed_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)table, ids, out, H, V, status,
-                   ssq, ssq_ld);
-}
-extern "C" int spark_row_ssq(const float* res, int R, int H, float* ssq, int ssq_ld, cudaStream_t s) {
-  if (R <= 0) return 0;
-  if (H % 128) return -5;
-  const cudaError_t e = spark_launch_pdl(row_ssq_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), res, H, ssq, ssq_ld);
-  return e == cudaSuccess ? 0 : -4;
+  spark_launch_pdl(embed_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)table, ids, out, H, V, status);
 }
 extern "C" int spark_decode_advance(int* dev, const int* out_ids, int n, cudaStream_t s) {
   if (n <= 0) return 0;

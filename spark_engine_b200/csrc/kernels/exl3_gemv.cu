@@ -30,8 +30,6 @@ struct Exl3GemvArgs {
   int R, K, N, S, act; float limit;
   int fuse_ar;                                  // 1: row-parallel layer under TP: the epilogue pushes the strip to every
   ArRows ar;                                    //    rank and the last CTA does all-reduce + residual + RMSNorm
-  NormIn nin;                                   // nin.res != nullptr: rows = rmsnorm(residual) rebuilt while staging
-  ResOut rout;                                  // rout.res != nullptr: residual += y, strip sums of squares (items == 1)
   int pairs_early;                              // pair tables were written at least two launches back: they may be read
 };                                              // (and the weight loads issued) before the dependency wait
 
@@ -96,7 +94,6 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
   }
 
   if (early) pdl_wait();
-  pdl_trigger();
   // ---- prologue: xh = had128(x * suh) / sqrt(128) for this K-slice; one warp per (row, 128-block)
   const __half* suh = a.suh + e * a.suh_stride + k_begin;
   const int nblk = Ks >> 7;
@@ -104,9 +101,7 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
     const int r = job / nblk, b = job - r * nblk;
     const __nv_bfloat16* xr = a.x + static_cast<size_t>(xr0 + r) * a.ldx + k_begin + b * 128 + lane * 4;
     float v[4];
-    if (a.nin.res != nullptr) {
-      norm_row4(a.nin, xr0 + r, k_begin + b * 128 + lane * 4, lane, v);
-    } else if (a.act == 1) {
+    if (a.act == 1) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float gg = __bfloat162float(xr[i]), uu = __bfloat162float(xr[a.K + i]);
@@ -165,6 +160,9 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
       for (int u = 0; u < 8; ++u) nxt[u] = __ldg(tw + (kb + 16 + u) * tstep);
     }
   }
+  // This CTA's weight stream is done: let the next kernel's CTAs start (they issue their own weight loads while this
+  // grid reduces and stores).  Triggering earlier only makes the two kernels' loads compete (measured: slower).
+  pdl_trigger();
   // ---- every CTA pushes its partial strip into the shared memory of cluster rank 0 (plain remote stores,
   //      no round trip), one cluster barrier, then rank 0 sums the slices in rank order:
   //      y = had128(sum) * svh.
@@ -204,16 +202,6 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
         st_f4(reinterpret_cast<float*>(a.ar.c.peers[p] + a.ar.slot_off) + so, make_float4(v[0], v[1], v[2], v[3]));
       continue;
     }
-    if (a.rout.res != nullptr) {
-      // residual update in place (this CTA owns the strip's columns) + the strip's share of the row's sum of squares
-      float* rp = a.rout.res + static_cast<size_t>(xr0 + r) * a.N + strip * 128 + lane * 4;
-      float4 o4 = *reinterpret_cast<const float4*>(rp);
-      o4.x += v[0]; o4.y += v[1]; o4.z += v[2]; o4.w += v[3];
-      *reinterpret_cast<float4*>(rp) = o4;
-      const float ss = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w);
-      if (lane == 0) a.rout.ssq[static_cast<size_t>(strip) * a.rout.ssq_ld + xr0 + r] = ss;
-      continue;
-    }
     const size_t o = static_cast<size_t>(item * R + r) * a.ldy + strip * 128 + lane * 4;
     if (a.out_f32) {
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + o) = make_float4(v[0], v[1], v[2], v[3]);
@@ -236,7 +224,7 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
                                long long t_stride_words, long long suh_stride, long long svh_stride, void* y, int ldy,
                                int out_f32, const int* pair_expert, const int* pair_row, int items, int rows_per_item,
                                int K, int N, int S, int act, float limit, int codebook, cudaStream_t s, const void* ar_args,
-                               const void* norm_in, const void* res_out, int pairs_early) {
+                               int pairs_early) {
   if (items <= 0 || rows_per_item <= 0) return 0;
   if (rows_per_item > 16 || (K & 127) || (N & 127) || S < 1 || S > 8 || ((K >> 7) % S) || K / S > EXL3_MAX_KS) return -5;
   if ((ldx & 3) || (ldy & 3)) return -5;
@@ -248,15 +236,7 @@ extern "C" int spark_exl3_gemv(const void* x, int ldx, const void* trellis, cons
   a.pair_expert = pair_expert; a.pair_row = pair_row;
   a.R = rows_per_item; a.K = K; a.N = N; a.S = S; a.act = act; a.limit = limit;
   a.fuse_ar = 0;
-  a.nin = NormIn{}; a.rout = ResOut{}; a.pairs_early = pairs_early;
-  if (norm_in) {
-    a.nin = *static_cast<const NormIn*>(norm_in);
-    if (act == 1 || a.nin.H != K) return -5;
-  }
-  if (res_out) {
-    if (items != 1 || ar_args) return -5;
-    a.rout = *static_cast<const ResOut*>(res_out);
-  }
+  a.pairs_early = pairs_early;
   if (ar_args) {
     if (items != 1) return -5;
     a.fuse_ar = 1;

@@ -25,13 +25,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                  long long expert_stride, int ldw, TO* __restrict__ y, int ldy, int rows_per_item, int N, int K,
                  const int* __restrict__ pair_expert, const int* __restrict__ pair_row, int act, float limit,
-                 long long x_item_stride, long long y_item_stride, const __grid_constant__ NormIn nin, int cpc) {
+                 long long x_item_stride, long long y_item_stride, int cpc) {
   extern __shared__ __align__(16) uint8_t smem_gemv[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [RB][K]
-  __shared__ float rstd_s[RB];
   const int item = blockIdx.y;
   pdl_wait();                                            // rows (and pair tables) come from earlier launches
-  pdl_trigger();
   if (pair_expert && pair_expert[item] < 0) return;      // pair of an expert that lives on another rank
   // strided items (either stride non-zero): item i reads rows x + i * x_item_stride + r * ldx and writes rows
   // y + i * y_item_stride + r * ldy, e.g. the per-head slices of a [rows, heads, dim] tensor
@@ -42,23 +40,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
   const __nv_bfloat16* Wb = W + (pair_expert ? static_cast<long long>(pair_expert[item]) * expert_stride : 0);
   const int R = rows_per_item;
   // stage activations (zero rows beyond R); plain rows are copied as 16-byte vectors
-  if (nin.res != nullptr) {
-    // rows = rmsnorm(residual) * w rebuilt from the strip partials (deferred norm), rounded to bf16
-    for (int r = threadIdx.x >> 5; r < RB; r += GEMV_WARPS) {
-      const float v = r < R ? norm_rstd(nin, xr0 + r, threadIdx.x & 31) : 0.f;
-      if ((threadIdx.x & 31) == 0) rstd_s[r] = v;
-    }
-    __syncthreads();
-    const int KV4 = K >> 2;
-    for (int i = threadIdx.x; i < RB * KV4; i += blockDim.x) {
-      const int r = i / KV4, kv = i - r * KV4;
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (r < R) norm_load4(nin, xr0 + r, kv * 4, rstd_s[r], v);
-      __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
-      uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
-      reinterpret_cast<uint2*>(xs)[i] = o;
-    }
-  } else if (act == 0) {
+  if (act == 0) {
     const int KV8 = K >> 3;
     for (int i = threadIdx.x; i < RB * KV8; i += blockDim.x) {
       const int r = i / KV8, kv = i - r * KV8;
@@ -119,6 +101,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
       }
     }
   }
+  if (cg == cpc - 1) pdl_trigger();                      // weight stream done: the next kernel may start its loads
 #pragma unroll
   for (int r = 0; r < RB; ++r) { acc0[r] = warp_sum(acc0[r]); acc1[r] = warp_sum(acc1[r]); }
   if (lane == 0) {
@@ -137,7 +120,7 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat
 template <int RB, typename TO>
 static int launch_gemv(const void* x, int ldx, const void* W, long long es, int ldw, void* y, int ldy, int items,
                        int rows, int N, int K, const int* pe, const int* pr, int act, float limit, cudaStream_t s,
-                       long long xis = 0, long long yis = 0, const NormIn* nin = nullptr) {
+                       long long xis = 0, long long yis = 0) {
   auto kern = gemv_bf16_kernel<RB, TO>;
   const int smem = RB * K * 2;
   if (smem > 48 * 1024) {
@@ -150,14 +133,9 @@ static int launch_gemv(const void* x, int ldx, const void* W, long long es, int 
   if (cpc < 1) cpc = 1;
   if (cpc > 8) cpc = 8;
   dim3 grid((groups + cpc - 1) / cpc, items);
-  NormIn n = {};
-  if (nin) {
-    n = *nin;
-    if (n.H != K || act != 0 || xis != 0 || yis != 0 || (K & 3)) return -5;
-  }
   const cudaError_t err = spark_launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, s, dim3(1, 1, 1),
                                            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, es, ldw, (TO*)y, ldy, rows, N, K,
-                                           pe, pr, act, limit, xis, yis, n, cpc);
+                                           pe, pr, act, limit, xis, yis, cpc);
   return err == cudaSuccess ? 0 : -4;
 }
 
@@ -168,16 +146,15 @@ using namespace spark;
 // items x rows_per_item rows; K % 8 == 0; out_f32 selects fp32 or bf16 output.
 extern "C" int spark_gemv_bf16(const void* x, int ldx, const void* W, long long expert_stride, int ldw, void* y, int ldy,
                                int items, int rows_per_item, int N, int K, const int* pair_expert, const int* pair_row,
-                               int act, float limit, int out_f32, cudaStream_t s, const void* norm_in) {
+                               int act, float limit, int out_f32, cudaStream_t s) {
   if (items <= 0 || rows_per_item <= 0) return 0;
   if (K % 8 || rows_per_item > 16) return -5;
-  const NormIn* nin = static_cast<const NormIn*>(norm_in);
 #define SPARK_GEMV_CASE(RB)                                                                                          \
   if (rows_per_item <= RB)                                                                                           \
     return out_f32 ? launch_gemv<RB, float>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N, K,       \
-                                            pair_expert, pair_row, act, limit, s, 0, 0, nin)                         \
+                                            pair_expert, pair_row, act, limit, s)                                    \
                    : launch_gemv<RB, __nv_bfloat16>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N,  \
-                                                    K, pair_expert, pair_row, act, limit, s, 0, 0, nin);
+                                                    K, pair_expert, pair_row, act, limit, s);
   SPARK_GEMV_CASE(1)
   SPARK_GEMV_CASE(2)
   SPARK_GEMV_CASE(4)

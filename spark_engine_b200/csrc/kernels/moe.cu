@@ -118,11 +118,9 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int E, int top_k, int
 // writes the pair tables the expert GEMVs read: ids / weights / source row for top_k routed slots plus an optional
 // shared-expert slot (the shared expert is stored as one more matrix of the expert stack, so it is just another
 // pair; under tensor parallelism row r's shared pair belongs to rank r % world).
-// Input rows are bf16, or the fp32 residual stream with the deferred RMSNorm (NormIn).
 // Replaces three launches (norm, GEMV, route); reference: engine-rs/shim/qwen_moe.cu:10-92, dataflow.cu:370-572.
 struct RouterArgs {
-  const __nv_bfloat16* x; int ldx;           // [R, K] (unused with nin.res)
-  NormIn nin;
+  const __nv_bfloat16* x; int ldx;           // [R, K]
   const __nv_bfloat16* Wg; int ldw;          // [E (+1), K]
   float* logits; int ld;                     // scratch [R, ld]
   int R, K, E, top_k, kind;                  // kind: 0 softmax, 1 sigmoid+bias, 2 sqrt(softplus)+bias
@@ -141,62 +139,40 @@ __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
   extern __shared__ __align__(16) uint8_t smem_router[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_router);     // [R][K]
-  __shared__ float rstd_s[ROUTER_RB];
   __shared__ int last_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int R = a.R, K = a.K;
   // the gate matrix depends on no earlier launch: its first batch of loads is in flight before the dependency wait
   const int NE = a.E + (a.shared_gate ? 1 : 0);
-  const int n0 = (blockIdx.x * 8 + warp) * 2;
-  const bool two = n0 + 1 < NE;
+  const int n0 = blockIdx.x * 8 + warp;                    // one gate column per warp
   const uint4* w0 = reinterpret_cast<const uint4*>(a.Wg + static_cast<size_t>(n0 < NE ? n0 : 0) * a.ldw);
-  const uint4* w1 = reinterpret_cast<const uint4*>(a.Wg + static_cast<size_t>(two ? n0 + 1 : (n0 < NE ? n0 : 0)) * a.ldw);
-  constexpr int BATCH = 8;                                 // weight loads in flight per lane and column
+  constexpr int BATCH = 8;                                 // weight loads in flight per lane
   const int KV = K >> 3;
-  uint4 wa[BATCH], wb[BATCH];
+  uint4 wa[BATCH];
 #pragma unroll
   for (int u = 0; u < BATCH; ++u) {
     const int kv = lane + 32 * u;
     wa[u] = kv < KV ? __ldg(w0 + kv) : make_uint4(0u, 0u, 0u, 0u);
-    wb[u] = kv < KV ? __ldg(w1 + kv) : make_uint4(0u, 0u, 0u, 0u);
   }
   pdl_wait();
   pdl_trigger();
-  if (a.nin.res != nullptr) {
-    for (int r = warp; r < R; r += 8) {
-      const float v = norm_rstd(a.nin, r, lane);
-      if (lane == 0) rstd_s[r] = v;
-    }
-    __syncthreads();
-    const int KV4 = K >> 2;
-    for (int i = tid; i < R * KV4; i += 256) {
-      const int r = i / KV4, kv = i - r * KV4;
-      float v[4];
-      norm_load4(a.nin, r, kv * 4, rstd_s[r], v);
-      __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
-      uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
-      reinterpret_cast<uint2*>(xs)[i] = o;
-    }
-  } else {
-    const int KV8 = K >> 3;
-    for (int i = tid; i < R * KV8; i += 256) {
-      const int r = i / KV8, kv = i - r * KV8;
-      reinterpret_cast<uint4*>(xs)[i] = *reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(r) * a.ldx + kv * 8);
-    }
+  const int KV8 = K >> 3;
+  for (int i = tid; i < R * KV8; i += 256) {
+    const int r = i / KV8, kv = i - r * KV8;
+    reinterpret_cast<uint4*>(xs)[i] = *reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(r) * a.ldx + kv * 8);
   }
   __syncthreads();
-  // ---- GEMV: this CTA's 16 gate columns (2 per warp), all rows; one warp per output => fixed reduction order
+  // ---- GEMV: this CTA's 8 gate columns (one per warp), all rows; one warp per output => fixed reduction order
   if (n0 < NE) {
-    float acc0[ROUTER_RB], acc1[ROUTER_RB];
+    float acc0[ROUTER_RB];
 #pragma unroll
-    for (int r = 0; r < ROUTER_RB; ++r) { acc0[r] = 0.f; acc1[r] = 0.f; }
+    for (int r = 0; r < ROUTER_RB; ++r) acc0[r] = 0.f;
     for (int kv0 = lane; kv0 < KV; kv0 += 32 * BATCH) {
       if (kv0 != lane) {
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
           const int kv = kv0 + 32 * u;
           wa[u] = kv < KV ? __ldg(w0 + kv) : make_uint4(0u, 0u, 0u, 0u);
-          wb[u] = kv < KV ? __ldg(w1 + kv) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
 #pragma unroll
@@ -204,12 +180,11 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
         const int kv = kv0 + 32 * u;
         if (kv >= KV) break;
         const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&wa[u]);
-        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&wb[u]);
-        float fa[8], fb[8];
+        float fa[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 t0 = __bfloat1622float2(pa[i]), t1 = __bfloat1622float2(pb[i]);
-          fa[2 * i] = t0.x; fa[2 * i + 1] = t0.y; fb[2 * i] = t1.x; fb[2 * i + 1] = t1.y;
+          const float2 t0 = __bfloat1622float2(pa[i]);
+          fa[2 * i] = t0.x; fa[2 * i + 1] = t0.y;
         }
 #pragma unroll
         for (int r = 0; r < ROUTER_RB; ++r) {
@@ -220,7 +195,6 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
             for (int i = 0; i < 4; ++i) {
               const float2 t = __bfloat1622float2(px[i]);
               acc0[r] = fmaf(fa[2 * i], t.x, acc0[r]); acc0[r] = fmaf(fa[2 * i + 1], t.y, acc0[r]);
-              acc1[r] = fmaf(fb[2 * i], t.x, acc1[r]); acc1[r] = fmaf(fb[2 * i + 1], t.y, acc1[r]);
             }
           }
         }
@@ -229,11 +203,8 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
 #pragma unroll
     for (int r = 0; r < ROUTER_RB; ++r) {
       if (r < R) {
-        const float s0 = warp_sum(acc0[r]), s1 = warp_sum(acc1[r]);
-        if (lane == 0) {
-          a.logits[static_cast<size_t>(r) * a.ld + n0] = s0;
-          if (two) a.logits[static_cast<size_t>(r) * a.ld + n0 + 1] = s1;
-        }
+        const float s0 = warp_sum(acc0[r]);
+        if (lane == 0) a.logits[static_cast<size_t>(r) * a.ld + n0] = s0;
       }
     }
   }
@@ -247,29 +218,24 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
   }
   __syncthreads();
   if (!last_s) return;
-  __threadfence();
+  // (the writers fenced before they arrived; the logits are read with L2 loads, so no reader-side fence)
   constexpr int EPL = 32;                                   // experts per lane (E <= 1024); loops stop at nj
   const int nj = (a.E + 31) >> 5;
   for (int r = warp; r < R; r += 8) {
     const float* lg = a.logits + static_cast<size_t>(r) * a.ld;
-    float p[EPL], s[EPL];
+    float p[EPL], s[EPL];                                   // p: what the weights are made of; s: selection score
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       const int e = lane + 32 * j;
       p[j] = (j < nj && e < a.E) ? __ldcg(lg + e) : -INFINITY;
-      s[j] = -INFINITY;
+      s[j] = p[j];
       mx = fmaxf(mx, p[j]);
     }
     if (a.kind == 0) {
+      // softmax -> top-k -> renormalise: the softmax denominator cancels, so experts are ranked by their logits and
+      // only the k winners are exponentiated
       mx = warp_max(mx);
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) if (j < nj) { p[j] = (lane + 32 * j) < a.E ? expf(p[j] - mx) : 0.f; sum += p[j]; }
-      sum = warp_sum(sum);
-      const float inv = 1.f / sum;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) if (j < nj) { p[j] = p[j] * inv; s[j] = (lane + 32 * j) < a.E ? p[j] : -INFINITY; }
     } else {
 #pragma unroll
       for (int j = 0; j < EPL; ++j) {
@@ -281,27 +247,30 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
         } else { p[j] = 0.f; s[j] = -INFINITY; }
       }
     }
-    float selp = 0.f; int seli = -1;                        // lane k keeps slot k's probability and expert
+    float selp = 0.f; int seli = -1;                        // lane k keeps slot k's weight numerator and expert
     float tot = 0.f;
+    // Every lane keeps the best of its own experts.  A round: warp maximum of the candidates' order-preserving integer
+    // keys (one redux), lowest expert id among the lanes that hold it (one redux), the winning lane takes its expert out
+    // and rescans its own.  Ties -> lowest expert id.
+    float best = -INFINITY; int bj = 0;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }
     for (int k = 0; k < a.top_k; ++k) {
-      float best = -INFINITY; int bj = 0;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }   // ascending e: first maximum kept
-      int bi = best == -INFINITY ? 0x7fffffff : lane + 32 * bj;
+      const uint32_t bits = __float_as_uint(best);
+      const uint32_t key = best == -INFINITY ? 0u : (bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
+      const uint32_t wmax = __reduce_max_sync(0xffffffffu, key);
+      const int cand = (key == wmax && key != 0u) ? lane + 32 * bj : 0x7fffffff;
+      const int wi = __reduce_min_sync(0xffffffffu, cand);
       float bp = 0.f;
+      if (wi == cand && wi != 0x7fffffff) {                 // this lane owns the winner
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) if (j == bj) bp = p[j];
-      float wv = best; int wi = bi; float wp = bp;
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-        const float op = __shfl_xor_sync(0xffffffffu, wp, o);
-        if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; wp = op; }
-      }
-      if (wi == bi && bi != 0x7fffffff) {
+        for (int j = 0; j < EPL; ++j) if (j == bj) { bp = p[j]; s[j] = -INFINITY; }
+        if (a.kind == 0) bp = __expf(bp - mx);
+        best = -INFINITY; bj = 0;
 #pragma unroll
-        for (int j = 0; j < EPL; ++j) if (j == bj) s[j] = -INFINITY;
+        for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }
       }
+      const float wp = __shfl_sync(0xffffffffu, bp, wi & 31);
       if (lane == k) { selp = wp; seli = wi; }
       tot += wp;                                            // slot order, identical on every lane
     }
@@ -313,7 +282,7 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
       if (a.pair_row) a.pair_row[o + lane] = r;
     }
     if (lane == 0) {
-      const float g = a.shared_gate ? 1.f / (1.f + expf(-__ldcg(lg + a.E))) : 1.f;
+      const float g = a.shared_gate ? 1.f / (1.f + __expf(-__ldcg(lg + a.E))) : 1.f;
       if (a.slots > a.top_k) {
         a.wts[o + a.top_k] = g;
         a.ids[o + a.top_k] = (r % a.world) == a.rank ? a.shared_expert : -1;
@@ -324,49 +293,68 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
   }
 }
 
-// Decode combine: residual += sum over slots (slot order) of weight * y[pair], plus the strip partial sums of
-// squares of the new residual (deferred RMSNorm of the next block).  One warp per 128-column strip of a row.
-__global__ void __launch_bounds__(128)
-moe_combine_res_kernel(const float* __restrict__ y, const float* __restrict__ wts, const int* __restrict__ ids, int slots,
-                       int H, ResOut rout, float* __restrict__ out_f32, const __nv_bfloat16* __restrict__ shared,
-                       const float* __restrict__ sg) {
+// Decode combine fused with the residual update and the next RMSNorm: one CTA per row.
+//   res[r] += sum over slots (slot order) of weight * y[pair] (+ gated shared);  h[r] = rmsnorm(res[r]) * w  (bf16)
+// Replaces combine + add_rmsnorm (two launches); reference: engine-rs/shim/moe_exl3.cuh:1381 finish_combine_kernel.
+__global__ void __launch_bounds__(1024)
+moe_combine_norm_kernel(const float* __restrict__ y, const float* __restrict__ wts, const int* __restrict__ ids, int slots,
+                        int H, float* __restrict__ res, const float* __restrict__ norm_w, float eps, int one_plus,
+                        __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ shared,
+                        const float* __restrict__ sg) {
+  __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int strip = blockIdx.x * 4 + warp;
-  if (strip * 128 >= H) return;
-  const int col = strip * 128 + lane * 4;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k0 = 0; k0 < slots; k0 += 4) {                  // four slots' loads in flight; summed in slot order
-    float4 v[4]; float w[4];
+  const int r = blockIdx.x;
+  float4 keep[2];                                          // H <= 2 * 4 * blockDim.x
+  float ss = 0.f;
+  int ki = 0;
+  for (int col = threadIdx.x * 4; col < H; col += blockDim.x * 4, ++ki) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < slots; k0 += 4) {                // four slots' loads in flight; summed in slot order
+      float4 v[4]; float w[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int pi = r * slots + k0 + u;
-      const bool live = (k0 + u) < slots && ids[pi] >= 0;   // -1: expert (or shared pair) of another rank
-      w[u] = live ? wts[pi] : 0.f;
-      v[u] = live ? __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(pi) * H + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+      for (int u = 0; u < 4; ++u) {
+        const int pi = r * slots + k0 + u;
+        const bool live = (k0 + u) < slots && ids[pi] >= 0;
+        w[u] = live ? wts[pi] : 0.f;
+        v[u] = live ? __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(pi) * H + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      acc.x = fmaf(w[u], v[u].x, acc.x); acc.y = fmaf(w[u], v[u].y, acc.y);
-      acc.z = fmaf(w[u], v[u].z, acc.z); acc.w = fmaf(w[u], v[u].w, acc.w);
+      for (int u = 0; u < 4; ++u) {
+        acc.x = fmaf(w[u], v[u].x, acc.x); acc.y = fmaf(w[u], v[u].y, acc.y);
+        acc.z = fmaf(w[u], v[u].z, acc.z); acc.w = fmaf(w[u], v[u].w, acc.w);
+      }
     }
-  }
-  if (shared) {                                            // shared expert computed outside the pair list
-    const uint2 raw = *reinterpret_cast<const uint2*>(shared + static_cast<size_t>(r) * H + col);
-    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
-    const float g = sg ? sg[r] : 1.f;
-    acc.x += g * f0.x; acc.y += g * f0.y; acc.z += g * f1.x; acc.w += g * f1.y;
-  }
-  if (out_f32) *reinterpret_cast<float4*>(out_f32 + static_cast<size_t>(r) * H + col) = acc;
-  if (rout.res) {
-    float* rp = rout.res + static_cast<size_t>(r) * H + col;
+    if (shared) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(shared + static_cast<size_t>(r) * H + col);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 f0 = __bfloat1622float2(p2[0]), f1 = __bfloat1622float2(p2[1]);
+      const float g = sg ? sg[r] : 1.f;
+      acc.x += g * f0.x; acc.y += g * f0.y; acc.z += g * f1.x; acc.w += g * f1.y;
+    }
+    float* rp = res + static_cast<size_t>(r) * H + col;
     float4 o4 = *reinterpret_cast<const float4*>(rp);
     o4.x += acc.x; o4.y += acc.y; o4.z += acc.z; o4.w += acc.w;
     *reinterpret_cast<float4*>(rp) = o4;
-    const float ss = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w);
-    if (lane == 0) rout.ssq[static_cast<size_t>(strip) * rout.ssq_ld + r] = ss;
+    ss += o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w;
+    if (ki < 2) keep[ki] = o4;
+  }
+  ss = warp_sum(ss);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < nw; ++w) tot += red[w];              // fixed order
+  const float rs = rsqrtf(tot / H + eps);
+  ki = 0;
+  for (int col = threadIdx.x * 4; col < H; col += blockDim.x * 4, ++ki) {
+    const float4 v = keep[ki < 2 ? ki : 1];
+    const float4 g = *reinterpret_cast<const float4*>(norm_w + col);
+    const float o = one_plus ? 1.f : 0.f;
+    __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x * rs * (g.x + o), v.y * rs * (g.y + o));
+    __nv_bfloat162 b1 = __floats2bfloat162_rn(v.z * rs * (g.z + o), v.w * rs * (g.w + o));
+    uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
+    *reinterpret_cast<uint2*>(h + static_cast<size_t>(r) * H + col) = ov;
   }
 }
 
@@ -519,8 +507,8 @@ extern "C" int spark_moe_combine(float* res, const void* y, int y_f32, const int
 }
 
 // Fused decode router: see moe_router_topk_kernel.  `logits` scratch [R, ld] fp32 (ld >= E + 1), `counter` one int
-// that is zero between launches.  norm_in: NormIn* or null (then x bf16 [R, K]).
-extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* norm_in, const void* Wg, int ldw, float* logits,
+// that is zero between launches.  x bf16 [R, K].
+extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* Wg, int ldw, float* logits,
                                      int ld, int R, int K, int E, int top_k, int kind, const float* bias, float scale,
                                      int shared_gate, int slots, int shared_expert, int e_lo, int e_hi, int rank, int world,
                                      float* wts, int* ids, int* pair_row, float* sg, int* counter, cudaStream_t s) {
@@ -529,8 +517,6 @@ extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* norm_in
     return -5;
   RouterArgs a;
   a.x = (const __nv_bfloat16*)x; a.ldx = ldx;
-  a.nin = NormIn{};
-  if (norm_in) { a.nin = *static_cast<const NormIn*>(norm_in); if (a.nin.H != K) return -5; }
   a.Wg = (const __nv_bfloat16*)Wg; a.ldw = ldw; a.logits = logits; a.ld = ld;
   a.R = R; a.K = K; a.E = E; a.top_k = top_k; a.kind = kind; a.bias = bias; a.scale = scale; a.shared_gate = shared_gate;
   a.slots = slots; a.shared_expert = shared_expert; a.e_lo = e_lo; a.e_hi = e_hi; a.rank = rank; a.world = world < 1 ? 1 : world;
@@ -540,19 +526,19 @@ extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* norm_in
   if (smem > 200 * 1024) return -6;
   static bool attr_set = false;
   if (!attr_set) { cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr_set = true; }
-  const cudaError_t err = spark_launch_pdl(moe_router_topk_kernel, dim3((NE + 15) / 16), dim3(256), smem, s, dim3(1, 1, 1), a);
+  const cudaError_t err = spark_launch_pdl(moe_router_topk_kernel, dim3((NE + 7) / 8), dim3(256), smem, s, dim3(1, 1, 1), a);
   return err == cudaSuccess ? 0 : -4;
 }
 
-// y fp32 [R * slots, H] in pair order.  res_out: ResOut* (residual += sum, strip sums of squares) and / or out_f32 [R, H].
-extern "C" int spark_moe_combine_res(const float* y, const float* wts, const int* ids, int R, int slots, int H,
-                                     const void* res_out, float* out_f32, const void* shared, const float* sg,
-                                     cudaStream_t s) {
+// res fp32 [R, H] (in/out), h bf16 [R, H] out; y fp32 [R * slots, H] in pair order.
+extern "C" int spark_moe_combine_norm(const float* y, const float* wts, const int* ids, int R, int slots, int H, float* res,
+                                      const float* norm_w, float eps, int one_plus, void* h, const void* shared,
+                                      const float* sg, cudaStream_t s) {
   if (R <= 0) return 0;
-  if (H % 128) return -5;
-  ResOut ro = {};
-  if (res_out) ro = *static_cast<const ResOut*>(res_out);
-  const cudaError_t err = spark_launch_pdl(moe_combine_res_kernel, dim3((H / 128 + 3) / 4, R), dim3(128), 0, s, dim3(1, 1, 1),
-                                           y, wts, ids, slots, H, ro, out_f32, (const __nv_bfloat16*)shared, sg);
+  int th = H / 4;
+  if (H % 128 || th > 2048) return -5;
+  if (th > 1024) th = 1024;
+  const cudaError_t err = spark_launch_pdl(moe_combine_norm_kernel, dim3(R), dim3(th), 0, s, dim3(1, 1, 1), y, wts, ids, slots, H,
+                                           res, norm_w, eps, one_plus, (__nv_bfloat16*)h, (const __nv_bfloat16*)shared, sg);
   return err == cudaSuccess ? 0 : -4;
 }

@@ -390,11 +390,26 @@ class AttnMixer:
         pass
 
     def compact(self, seqs, seg: Segment, rows: List[int]):
+        c = self.c
         base = seqs[seg.slot].kv_base + seg.pos0
+        tensors = (self.k, self.v) + ((self.ks, self.vs) if self.fp8 else ())
+        if c.sparse_topk_blocks:
+            tensors = tensors + (self.ik_raw,)
         for i, j in enumerate(rows):
             if i != j:
-                for t in (self.k, self.v) + ((self.ks, self.vs) if self.fp8 else ()):
+                for t in tensors:
                     t[base + i] = t[base + j]
+        if c.sparse_topk_blocks and ops.use_kernels(self.k):
+            # tree rows left their raw indexer keys at their in-flight slots without pooling: finish the blocks that the
+            # accepted path completes (mean of the raw keys, then norm + rope at the block's first position)
+            kvb, L0, n = seqs[seg.slot].kv_base, seg.pos0, len(rows)
+            b0, b1 = L0 // c.block, (L0 + n) // c.block
+            if b1 > b0:
+                raw = self.ik_raw[kvb + b0 * c.block: kvb + b1 * c.block].view(b1 - b0, c.block, c.idx_dim).mean(1)
+                p = torch.arange(b0, b1, device=raw.device) * c.block
+                kc = L.rope_neox(L.rms(raw, self.w["ik_norm"].float(), self.cfg.norm_eps, True), p,
+                                 min(c.rope_dim, c.idx_dim), c.rope_theta, self.inv)
+                self.ik_pool[kvb // c.block + b0: kvb // c.block + b1] = kc
 
     def state_tensors(self):
         d = {"k": self.k, "v": self.v}
@@ -546,8 +561,7 @@ class MoeBlock:
         c = self.c
         if self.dense:
             gu = ops.linear(h, self.w["dense_gu"])
-            a = ops.swiglu(gu, c.swiglu_limit)
-            return ops.row_parallel(a, self.w["dense_down"]) if defer else ops.linear(a, self.w["dense_down"])
+            return ops.linear(ops.swiglu(gu, c.swiglu_limit), self.w["dense_down"])
         return ops.moe(h, self.w, c, defer)
 
 
@@ -600,16 +614,14 @@ class Model:
         first RMSNorm happen in one fused op.  Returns (X, new pending output)."""
         cfg, tp = self.cfg, self.tp
         if cfg.hc_kind == "none":
-            deferred = not isinstance(X, torch.Tensor)      # decode round: residual-stream object, norms deferred
+            # decode rounds on the device: the MoE combine is deferred into the next residual update (one launch for
+            # combine + add + norm; under tensor parallelism the combine happens inside the all-reduce push)
+            deferred = plan.rows <= 16 and X.is_cuda and (tp is None or hasattr(tp, "argmax"))
             if "ngram" in lw:
                 if pend is not None:
                     _, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
                     pend = None
-                if deferred:
-                    X.x = ops.ngram_embed(self, X.x, plan, lw["ngram"])
-                    X.valid = False
-                else:
-                    X = ops.ngram_embed(self, X, plan, lw["ngram"])
+                X = ops.ngram_embed(self, X, plan, lw["ngram"])
             h, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
             a = mix.forward(h, plan, self.seqs, commit)
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
@@ -633,8 +645,6 @@ class Model:
         With commit=False no linear-attention state nor sequence length changes: call
         `commit(accepted)` afterwards."""
         cfg, W = self.cfg, self.W
-        # decode-size batches on the device keep the residual stream as an object whose RMSNorms stay deferred
-        resid = cfg.hc_kind == "none" and self.tp is None and plan.rows <= 16 and not plan.mm_rows
         if plan.mm_rows:
             # salted placeholder ids are outside the vocabulary: look up row 0 for them, then write the encoded media
             # rows over those positions (engine-rs/src/weights.rs:536-569)
@@ -644,7 +654,7 @@ class Model:
             X[salted.to(X.device)] = 0
             X = inject_rows(X, plan.ids, plan.mm_rows)
         else:
-            X = ops.embed(W["embed"], plan.ids, self.dtype, resid)
+            X = ops.embed(W["embed"], plan.ids, self.dtype)
         if cfg.hc_kind != "none":
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
         self._ids_for_ngram = plan
@@ -655,7 +665,7 @@ class Model:
         for li, (lw, mix, mlp) in enumerate(self.layers):
             X, pend = self._block(lw, mix, mlp, X, pend, plan, commit)
             if taps and li in taps:          # residual stream after layer li (feature taps of a drafter)
-                self.taps[li] = ops.to_tensor(X) if pend is None else ops.residual_add(ops.to_tensor(X).clone(), pend)
+                self.taps[li] = X if pend is None else ops.residual_add(X.clone(), pend)
         if cfg.hc_kind == "gated":
             _, X = ops.hc_gated_mix(X, W["hc_final"], cfg.norm_eps)
             hn = X
@@ -664,13 +674,13 @@ class Model:
             hn = ops.rmsnorm(X, W["final_norm"], cfg.norm_eps)
         else:
             hn, X = ops.add_rmsnorm(pend, X, W["final_norm"], cfg.norm_eps, self.tp)
-        self.hidden_out = ops.to_tensor(X)
+        self.hidden_out = X
         self._pending_plan = None if commit else plan
         if commit and not graph_mode:       # under a captured graph the engine tracks lengths itself
             for s in plan.segs:
                 self.seqs[s.slot].length = s.pos0 + s.n
         if plan.logit_rows.shape[0] != hn.shape[0]:
-            hn = ops.to_tensor(hn)[plan.logit_rows]
+            hn = hn[plan.logit_rows]
         return ops.lm_head(hn, W["lm_head"])
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:

@@ -41,24 +41,20 @@ def set_fallback(on: bool):
 
 
 # ----------------------------------------------------------------------------- basic ops
-def embed(table: torch.Tensor, ids: torch.Tensor, dtype, resid: bool = False):
-    """Token embedding rows.  On the device the residual stream is fp32 (activations bf16); with `resid` a decode
-    round gets the residual-stream object whose RMSNorms stay deferred (ops/cuda.py `Resid`)."""
+def embed(table: torch.Tensor, ids: torch.Tensor, dtype) -> torch.Tensor:
+    """Token embedding rows.  On the device the residual stream is fp32 (activations bf16)."""
     if use_kernels(table):
-        return cuda_ops().embed(table, ids.to(torch.int32), resid)
+        return cuda_ops().embed(table, ids.to(torch.int32))
     return table[ids].to(dtype)
 
 
 def to_tensor(x):
-    """Plain tensor of a value that may still be deferred (residual-stream object, lazy norm, uncombined MoE,
-    row-parallel product)."""
+    """Plain tensor of a block output that may still be deferred (uncombined MoE of a decode round, row-parallel
+    product)."""
     if x is None or isinstance(x, torch.Tensor):
         return x
     if isinstance(x, Partial):
         return linear(x.x, x.w)
-    c = cuda_ops()
-    if isinstance(x, c.Resid):
-        return x.x
     return x.tensor()
 
 
@@ -78,7 +74,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 def lm_head(h, w) -> torch.Tensor:
     """Logits in fp32."""
-    if (_is_lazy(h) or use_kernels(h)) and not isinstance(w, QuantWeight):
+    if use_kernels(h) and not isinstance(w, QuantWeight):
         return cuda_ops().dense_linear(h, w, out_f32=True)
     return linear(h, w).float()
 
@@ -86,22 +82,18 @@ def lm_head(h, w) -> torch.Tensor:
 def linear(x: torch.Tensor, w) -> torch.Tensor:
     """y = x @ W^T for a dense `[N,K]` tensor or a quantised weight object."""
     if isinstance(w, QuantWeight):
-        if _is_lazy(x) or use_kernels(x):
+        if use_kernels(x):
             return cuda_ops().quant_linear(x, w)
         return (x.float() @ w.dequant().to(x.device).t()).to(x.dtype)
-    if _is_lazy(x) or use_kernels(x):
+    if use_kernels(x):
         return cuda_ops().dense_linear(x, w)
     return x @ w.to(x.dtype).t()
-
-
-def _is_lazy(x) -> bool:
-    return not isinstance(x, torch.Tensor)
 
 
 def linear_pair(x, w_a, w_b):
     """Two independent projections of the same rows.  On the device, decode-size batches run the second one on a
     side stream next to the first (parallel branches of the captured graph)."""
-    if not _is_lazy(x) and use_kernels(x) and x.shape[0] <= 16 and cuda_ops().SIDE_STREAMS:
+    if use_kernels(x) and x.shape[0] <= 16 and cuda_ops().SIDE_STREAMS:
         c = cuda_ops()
         main = torch.cuda.current_stream()
         side = c._side_stream(x.device)
@@ -132,10 +124,8 @@ class Partial:
 def row_parallel(x, w, tp=None):
     """Output projection of a mixer.  Without tensor parallelism: the product.  With it: this rank's partial
     product, deferred when the fused GEMV + all-reduce kernel can take it (EXL3 weights, <= 16 rows)."""
-    if tp is not None:
-        return Partial(x, w) if tp.can_fuse_gemv(x, w) else linear(x, w)
-    if use_kernels(x) and cuda_ops().can_fuse_residual(x, w):
-        return Partial(x, w)          # decode rows: the product is added straight into the residual stream
+    if tp is not None and tp.can_fuse_gemv(x, w):
+        return Partial(x, w)
     return linear(x, w)
 
 
@@ -144,7 +134,7 @@ def add_rmsnorm(delta, res, w, eps, tp=None):
     rank's partial sum and is all-reduced first (one fused kernel on the device)."""
     if tp is not None and delta is not None:
         return tp.add_rmsnorm(delta, res, w, eps)
-    if _is_lazy(res) or use_kernels(res):
+    if use_kernels(res):
         return cuda_ops().add_rmsnorm(delta, res, w, eps)
     delta = to_tensor(delta)
     if delta is not None:
@@ -186,7 +176,7 @@ def route(h, w, c):
 def moe(h, w, c, defer: bool = False):
     """Routed experts (slot-order weighted sum) + shared expert.  `defer` (decode rounds on the device): the
     uncombined expert outputs are returned and the combine runs fused with the next residual update."""
-    if _is_lazy(h) or use_kernels(h):
+    if use_kernels(h):
         return cuda_ops().moe(h, w, c, defer)
     R = h.shape[0]
     wts, idx, sg = route(h, w, c)

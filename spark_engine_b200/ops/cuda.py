@@ -26,16 +26,15 @@ _SIGS = {
     "spark_gemm_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "spark_gemm_bf16_swiglu": [vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
     "spark_gemm_grouped_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, f32, i32, vp, vp],
-    "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp, vp],
+    "spark_gemv_bf16": [vp, i32, vp, i64, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, f32, i32, vp],
     "spark_gemv_bf16_items": [vp, i32, i64, vp, i64, i32, vp, i32, i64, i32, i32, i32, i32, vp, i32, vp],
     "spark_add_rmsnorm": [vp, i32, vp, vp, vp, i32, i32, f32, i32, vp],
     "spark_rmsnorm_bf16": [vp, vp, vp, i32, i32, f32, i32, vp],
-    "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp, vp, i32],
-    "spark_row_ssq": [vp, i32, i32, vp, i32, vp],
+    "spark_embed": [vp, vp, vp, i32, i32, vp, i32, vp],
     "spark_decode_advance": [vp, vp, i32, vp],
-    "spark_moe_router_topk": [vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, f32, i32, i32, i32, i32, i32, i32,
+    "spark_moe_router_topk": [vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, f32, i32, i32, i32, i32, i32, i32,
                               i32, vp, vp, vp, vp, vp, vp],
-    "spark_moe_combine_res": [vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp],
+    "spark_moe_combine_norm": [vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp],
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
     "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
@@ -54,14 +53,14 @@ _SIGS = {
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
                                 i32, f32, vp],
     "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
-                        vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
+                        vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     "spark_attn_decode": [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                          f32, vp, vp],
+                          f32, vp, vp, vp, vp, vp],
     "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp, i32, i32],
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp, vp],
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
-                        f32, i32, vp, vp, vp, vp, i32],
+                        f32, i32, vp, vp, i32],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
 }
@@ -183,105 +182,27 @@ def scratch_bytes() -> int:
     return sum(t.numel() * t.element_size() for t in _scratch.values())
 
 
-# ----------------------------------------------------------------------------- deferred norm (decode rounds)
-class NormInC(C.Structure):
-    _fields_ = [("res", vp), ("ssq", vp), ("w", vp), ("nparts", i32), ("ssq_ld", i32), ("H", i32), ("eps", f32),
-                ("one_plus", i32)]
-
-
-class ResOutC(C.Structure):
-    _fields_ = [("res", vp), ("ssq", vp), ("ssq_ld", i32)]
-
-
-SSQ_LD = 16          # rows per strip line of the partial sums of squares (decode rounds hold <= 16 rows)
+# ----------------------------------------------------------------------------- decode rounds
+DECODE_ROWS_MAX = 16
 FUSED_DECODE = os.environ.get("SPARK_FUSED_DECODE", "1") == "1"
-
-
-class Resid:
-    """fp32 residual stream of a decode round [R <= 16, H] with, per 128-column strip and row, the partial sum of
-    squares of the current rows (`ssq`, valid when `valid`).  Kernels that finish a residual update leave the
-    partials; the consumers of the normalised rows rebuild rstd from them (csrc/common/decode.cuh)."""
-
-    def __init__(self, x: torch.Tensor, ssq: Optional[torch.Tensor] = None, valid: bool = False):
-        self.x = x
-        H = x.shape[1]
-        self.ssq = ssq if ssq is not None else torch.empty(H // 128, SSQ_LD, dtype=torch.float32, device=x.device)
-        self.valid = valid
-
-    @property
-    def shape(self):
-        return self.x.shape
-
-    def res_out(self) -> ResOutC:
-        r = ResOutC()
-        r.res, r.ssq, r.ssq_ld = self.x.data_ptr(), self.ssq.data_ptr(), SSQ_LD
-        return r
-
-
-class LazyNorm:
-    """rmsnorm(residual) * w that has not been materialised: kernels with a norm prologue take it as it is,
-    everything else calls `tensor()` (one norm launch, cached)."""
-
-    def __init__(self, resid: Resid, w: torch.Tensor, eps: float, one_plus: bool = False):
-        self.resid, self.w, self.eps, self.one_plus = resid, w, eps, one_plus
-        self._t = None
-
-    @property
-    def shape(self):
-        return self.resid.x.shape
-
-    @property
-    def device(self):
-        return self.resid.x.device
-
-    @property
-    def is_cuda(self):
-        return True
-
-    @property
-    def dtype(self):
-        return torch.bfloat16
-
-    def norm_in(self) -> NormInC:
-        n = NormInC()
-        x = self.resid.x
-        n.res, n.ssq, n.w = x.data_ptr(), self.resid.ssq.data_ptr(), self.w.data_ptr()
-        n.nparts, n.ssq_ld, n.H, n.eps, n.one_plus = x.shape[1] // 128, SSQ_LD, x.shape[1], float(self.eps), int(self.one_plus)
-        return n
-
-    def tensor(self) -> torch.Tensor:
-        if self._t is None:
-            self._t = rmsnorm(self.resid.x, self.w, self.eps, self.one_plus)
-        return self._t
+SHARED_AS_PAIR = os.environ.get("SPARK_SHARED_PAIR", "0") == "1"
+FUSED_COMBINE = os.environ.get("SPARK_FUSED_COMBINE", "1") == "1"
 
 
 class PendingMoe:
     """Expert outputs of a decode round that have not been combined yet: y fp32 [R * slots, H] in pair order.  The
-    combine runs fused with the residual update (and leaves the partials for the next block's deferred norm)."""
+    slot-order combine runs fused with the residual update and the next RMSNorm (`add_rmsnorm`), or on its own
+    (`tensor()`)."""
 
     def __init__(self, y, wts, ids, slots, R, H, shared=None, sg=None):
         self.y, self.wts, self.ids, self.slots, self.R, self.H, self.shared, self.sg = y, wts, ids, slots, R, H, shared, sg
 
     def tensor(self) -> torch.Tensor:
-        out = torch.empty(self.R, self.H, dtype=torch.float32, device=self.y.device)
-        rc = lib().spark_moe_combine_res(P(self.y), P(self.wts), P(self.ids), self.R, self.slots, self.H, None, P(out),
-                                         P(self.shared), P(self.sg), stream())
-        check(rc, "spark_moe_combine_res")
-        return out.to(torch.bfloat16)
-
-
-def _mat(x):
-    """Plain tensor of an activation that may still be a deferred norm."""
-    return x.tensor() if isinstance(x, LazyNorm) else x
-
-
-def fused_decode_rows(R: int, H: int) -> bool:
-    return FUSED_DECODE and R <= SSQ_LD and H % 128 == 0
-
-
-def can_fuse_residual(x, w) -> bool:
-    """Row-parallel / output projection of decode rows whose kernel can add into the residual stream itself."""
-    return (FUSED_DECODE and isinstance(w, Exl3Weight) and not w.experts and w.bits == 4 and x.shape[0] <= SSQ_LD)
+        out = torch.empty(self.R, self.H, dtype=torch.bfloat16, device=self.y.device)
+        rc = lib().spark_moe_combine(None, P(self.y), 1, None, P(self.wts), self.R, self.slots, P(self.shared), P(self.sg),
+                                     self.H, P(out), stream(), P(self.ids))
+        check(rc, "spark_moe_combine")
+        return out
 
 
 # ----------------------------------------------------------------------------- dense linear
@@ -303,12 +224,6 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out_f32: bool = False, fmt: int 
 
 def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0, out_f32=False,
               expert_stride=0, n=None, k=None, out=None, ldx=None):
-    norm = None
-    if isinstance(x, LazyNorm):
-        if act == 0 and x.resid.valid:
-            norm, x = x.norm_in(), x.resid.x          # rows rebuilt in the kernel's prologue
-        else:
-            x = x.tensor()
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     n = n if n is not None else w.shape[-2]
     k = k if k is not None else w.shape[-1]
@@ -320,7 +235,7 @@ def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None
         out_f32 = out.dtype == torch.float32
     rc = lib().spark_gemv_bf16(P(x), ldx if ldx is not None else x.stride(0), P(w), expert_stride, w.stride(-2), P(y), ldy,
                                items, rows_per_item, n, k, P(pair_expert), P(pair_row), act, float(limit), int(out_f32),
-                               stream(), C.addressof(norm) if norm is not None else None)
+                               stream())
     check(rc, "spark_gemv_bf16")
     return y
 
@@ -335,11 +250,9 @@ def gemv_bf16_items(x, ldx, x_item_stride, w, expert_stride, ldw, y, ldy, y_item
     return y
 
 
-def dense_linear(x, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+def dense_linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
     if w.dtype != torch.bfloat16:
         raise TypeError("dense weights must be bf16 on the device")
-    if isinstance(x, LazyNorm):
-        return gemv_bf16(x, w, out_f32=out_f32)
     x = _as_bf16(x)
     R = x.shape[0]
     if R <= 16:
@@ -366,34 +279,21 @@ def _pick_slices(K: int, items: int = 1) -> int:
 
 
 def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, pair_row=None, act=0, limit=0.0,
-              out_f32=False, res_out: Optional[Resid] = None, pairs_early: bool = False):
-    """`x` may be a LazyNorm (rows normalised in the prologue).  With `res_out` the product is added into that
-    residual stream in place (strip partials updated) and nothing is returned."""
+              out_f32=False, pairs_early: bool = False):
+    """`pairs_early`: the pair tables were written at least two launches back, so the kernel may read them and issue
+    its weight loads before it waits for its predecessor (programmatic dependent launch)."""
     assert w.bits == 4, "the GEMV kernel handles 4 bpw"
-    norm = None
-    if isinstance(x, LazyNorm):
-        if act == 0 and x.resid.valid:
-            norm, x = x.norm_in(), x.resid.x
-        else:
-            x = x.tensor()
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     K, N = w.k, w.n
     S = _pick_slices(K, items)
     dev = x.device
-    y = None
-    if res_out is None:
-        y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+    y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
     tw = (K // 16) * (N // 16) * 32
     es = (tw, K, N) if w.experts else (0, 0, 0)
-    ro = res_out.res_out() if res_out is not None else None
     rc = lib().spark_exl3_gemv(P(x), x.stride(0), P(w.trellis), P(w.suh), P(w.svh), es[0], es[1], es[2], P(y), N,
                                int(out_f32), P(pair_expert), P(pair_row), items, rows_per_item, K, N, S,
-                               act, float(limit), 0 if w.kind == "mul1" else 1, stream(), None,
-                               C.addressof(norm) if norm is not None else None,
-                               C.addressof(ro) if ro is not None else None, int(pairs_early))
+                               act, float(limit), 0 if w.kind == "mul1" else 1, stream(), None, int(pairs_early))
     check(rc, "spark_exl3_gemv")
-    if res_out is not None:
-        res_out.valid = True
     return y
 
 
@@ -443,8 +343,6 @@ def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False, rows_p
 
 
 def exl3_linear(x, w: Exl3Weight):
-    if isinstance(x, LazyNorm):
-        return exl3_gemv(x, w)
     x = _as_bf16(x).contiguous()
     if x.shape[0] <= 16:
         return exl3_gemv(x, w)
@@ -458,7 +356,7 @@ def quant_linear(x, w: QuantWeight):
     if isinstance(w, Exl3Weight):
         return exl3_linear(x, w)
     from . import mx
-    return mx.quant_linear(_mat(x), w)
+    return mx.quant_linear(x, w)
 
 
 # ----------------------------------------------------------------------------- elementwise
@@ -471,43 +369,17 @@ def _delta_tensor(delta):
     return linear_any(delta.x, delta.w)            # ops.Partial
 
 
-def _add_norm_resid(delta, rs: Resid, w, eps, one_plus):
-    """Residual update of a decode round.  Producers with a residual epilogue (EXL3 output projection, MoE combine)
-    add in place and leave the strip partials; the normalised rows stay deferred."""
-    R, H = rs.x.shape
-    if delta is None:
-        pass
-    elif isinstance(delta, PendingMoe):
-        ro = rs.res_out()
-        rc = lib().spark_moe_combine_res(P(delta.y), P(delta.wts), P(delta.ids), R, delta.slots, H, C.addressof(ro), None,
-                                         P(delta.shared), P(delta.sg), stream())
-        check(rc, "spark_moe_combine_res")
-        rs.valid = True
-    elif (not isinstance(delta, torch.Tensor) and isinstance(delta.w, Exl3Weight) and not delta.w.experts
-          and delta.w.n == H and delta.w.bits == 4):
-        x = delta.x
-        exl3_gemv(x if isinstance(x, LazyNorm) else _as_bf16(x).contiguous(), delta.w, res_out=rs)
-    else:
-        d = _delta_tensor(delta).contiguous()
-        out = torch.empty(R, H, dtype=torch.bfloat16, device=rs.x.device)
-        lib().spark_add_rmsnorm(P(d), int(d.dtype == torch.float32), P(rs.x), P(w), P(out), R, H, float(eps), int(one_plus),
-                                stream())
-        rs.valid = False
-        ln = LazyNorm(rs, w, eps, one_plus)
-        ln._t = out
-        return ln, rs
-    if not rs.valid:
-        row_ssq(rs)
-    return LazyNorm(rs, w, eps, one_plus), rs
-
-
 def add_rmsnorm(delta, res, w, eps, one_plus=False):
-    if isinstance(res, Resid):
-        return _add_norm_resid(delta, res, w, eps, one_plus)
-    delta = _delta_tensor(delta)
     R, H = res.shape
     assert res.dtype == torch.float32 and res.is_contiguous()
     out = torch.empty(R, H, dtype=torch.bfloat16, device=res.device)
+    if isinstance(delta, PendingMoe) and H % 128 == 0 and H <= 8192 and FUSED_COMBINE:
+        # decode round: slot-order combine + residual add + RMSNorm in one launch
+        rc = lib().spark_moe_combine_norm(P(delta.y), P(delta.wts), P(delta.ids), R, delta.slots, H, P(res), P(w), float(eps),
+                                          int(one_plus), P(out), P(delta.shared), P(delta.sg), stream())
+        check(rc, "spark_moe_combine_norm")
+        return out, res
+    delta = _delta_tensor(delta)
     if delta is not None:
         delta = delta.contiguous()
     lib().spark_add_rmsnorm(P(delta), int(delta is not None and delta.dtype == torch.float32), P(res), P(w), P(out), R, H,
@@ -526,25 +398,11 @@ def rmsnorm(x, w, eps, one_plus=False):
     return out
 
 
-def embed(table, ids32, resid: bool = False):
-    """fp32 embedding rows; with `resid` a decode-round residual stream (strip partials filled in)."""
+def embed(table, ids32):
     R, H = ids32.shape[0], table.shape[1]
     out = torch.empty(R, H, dtype=torch.float32, device=table.device)
-    rs = Resid(out) if resid and fused_decode_rows(R, H) else None
-    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)),
-                      P(rs.ssq) if rs is not None else None, SSQ_LD)
-    if rs is not None:
-        rs.valid = True
-        return rs
+    lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)))
     return out
-
-
-def row_ssq(rs: Resid) -> Resid:
-    """Refill the strip partials of a residual stream that was updated by a kernel that does not leave them."""
-    R, H = rs.x.shape
-    check(lib().spark_row_ssq(P(rs.x), R, H, P(rs.ssq), SSQ_LD, stream()), "spark_row_ssq")
-    rs.valid = True
-    return rs
 
 
 def swiglu(gu, limit=0.0):
@@ -600,7 +458,7 @@ def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32, pairs_
                          limit=limit, out_f32=out_f32, pairs_early=pairs_early)
     if isinstance(w, QuantWeight):
         from . import mx
-        return mx.expert_gemv(_mat(x), w, pairs, pair_expert, pair_row, act, limit, out_f32)
+        return mx.expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32)
     E, N, K = w.shape
     return gemv_bf16(x, w, items=pairs, rows_per_item=1, pair_expert=pair_expert, pair_row=pair_row, act=act,
                      limit=limit, out_f32=out_f32, expert_stride=N * K, n=N, k=K)
@@ -660,32 +518,28 @@ def _moe_decode(h, w, c, defer: bool):
     """Decode rows (<= 16): ONE router launch (GEMV + top-k + pair tables), gate/up GEMV and SwiGLU + down GEMV
     over the (row, expert) pairs, then the slot-order combine (deferred into the residual update when `defer`).
     The shared expert is one more pair when it lives in the expert stack (`w["shared_in_stack"]`)."""
-    lazy = isinstance(h, LazyNorm) and h.resid.valid
-    if isinstance(h, LazyNorm) and not lazy:
-        h = h.tensor()
-    if not lazy:
-        h = _as_bf16(h).contiguous()
+    h = _as_bf16(h).contiguous()
     R, H = h.shape
     dev = h.device
     ep = w.get("ep")
     e_lo, e_hi = ep if ep else (0, c.n_experts)
     rank, world = w.get("tp_rank", (0, 1))
-    stacked = bool(w.get("shared_in_stack"))
+    # the shared expert as one more pair of the stack: always under tensor parallelism (row r's pair belongs to rank
+    # r % world); on one GPU it runs as two GEMVs on a side stream next to the router instead (SPARK_SHARED_PAIR=1
+    # forces the pair form)
+    stacked = bool(w.get("shared_in_stack")) and (world > 1 or SHARED_AS_PAIR or "s_gu" not in w)
     slots = c.top_k + (1 if stacked else 0)
     gate = w["gate"]
     NE = c.n_experts + (1 if c.shared_gate else 0)
     ld = (NE + 7) // 8 * 8
-    logits = scratch("router_logits", SSQ_LD * ld, torch.float32, dev)
+    logits = scratch("router_logits", DECODE_ROWS_MAX * ld, torch.float32, dev)
     counter = scratch("router_counter", 4, torch.int32, dev, zero=True)
     wts = torch.empty(R, slots, dtype=torch.float32, device=dev)
     ids = torch.empty(R, slots, dtype=torch.int32, device=dev)
     prow = torch.empty(R, slots, dtype=torch.int32, device=dev)
     shared_sep = "s_gu" in w and not stacked
     sg = torch.empty(R, dtype=torch.float32, device=dev) if (c.shared_gate and shared_sep) else None
-    norm = h.norm_in() if lazy else None
-    x = h.resid.x if lazy else h
-    rc = lib().spark_moe_router_topk(None if lazy else P(x), 0 if lazy else x.stride(0),
-                                     C.addressof(norm) if norm is not None else None, P(gate), gate.stride(0), P(logits), ld,
+    rc = lib().spark_moe_router_topk(P(h), h.stride(0), P(gate), gate.stride(0), P(logits), ld,
                                      R, H, c.n_experts, c.top_k, ROUTER_KIND[c.router], P(w.get("bias")), float(c.route_scale),
                                      int(c.shared_gate), slots, e_hi - e_lo, e_lo, e_hi, rank, world, P(wts), P(ids), P(prow),
                                      P(sg), P(counter), stream())
@@ -693,7 +547,7 @@ def _moe_decode(h, w, c, defer: bool):
     shared = None
     side = None
     if shared_sep:
-        hm = _mat(h)
+        hm = h
         main = torch.cuda.current_stream()
         side = _side_stream(dev) if SIDE_STREAMS else None
         if side is not None:
@@ -715,9 +569,9 @@ def moe(h, w, c, defer: bool = False):
     outputs of a decode round).  Under expert parallelism (`w["ep"]` = (first local expert, end)) only the local
     experts' pairs are computed and the result is this rank's partial sum; the shared expert is added by the rank
     that holds it."""
-    if h.shape[0] * c.top_k <= DECODE_PAIRS_MAX and h.shape[0] <= SSQ_LD and FUSED_DECODE:
+    if h.shape[0] * c.top_k <= DECODE_PAIRS_MAX and h.shape[0] <= DECODE_ROWS_MAX and FUSED_DECODE:
         return _moe_decode(h, w, c, defer)
-    h = _as_bf16(_mat(h)).contiguous()
+    h = _as_bf16(h).contiguous()
     R, H = h.shape
     dev = h.device
     ep = w.get("ep")
@@ -990,9 +844,23 @@ ATTN_PREFILL_KERNEL = os.environ.get("SPARK_ATTN_PREFILL", "1") == "1"
 ATTN_PREFILL_MIN_ROWS = 32
 
 
+def tree_ancestor_masks(plan, device) -> torch.Tensor:
+    """Per row, the bitmask of segment-local rows it may attend to (itself and its ancestors; chains: all earlier
+    rows of the segment)."""
+    import numpy as np
+    m = np.zeros(plan.rows, dtype=np.uint32)
+    for sg in plan.segs:
+        assert sg.n <= 32, "a verification tree holds at most 32 nodes per sequence"
+        for j in range(sg.n):
+            if sg.parents is None:
+                m[sg.r0 + j] = (1 << (j + 1)) - 1
+            else:
+                par = sg.parents[j]
+                m[sg.r0 + j] = (1 << j) | (int(m[sg.r0 + par]) if par >= 0 else 0)
+    return torch.from_numpy(m.view(np.int32)).to(device)
+
+
 def attn_mixer(mixer, qkv, plan, seqs):
-    if plan.is_tree:
-        return None          # ancestor-masked rows run the generic path
     c = mixer.c
     dev = qkv.device
     d = _plan_dev(plan, dev)
@@ -1003,8 +871,17 @@ def attn_mixer(mixer, qkv, plan, seqs):
         d["max_ctx"] = max(s.pos0 + s.n for s in plan.segs)
         for s in plan.segs:
             assert s.pos0 + s.n <= seqs[s.slot].kv_cap, "sequence capacity exceeded"
-    w = mixer.w
     sparse = c.sparse_topk_blocks > 0
+    tree = plan.is_tree
+    if tree:
+        # ancestor-masked rows run on the tensor-core decode kernel; a tree that also needs the block-sparse selection
+        # (context beyond the selection budget) or an unsupported head shape takes the generic path
+        if (c.head_dim not in (64, 128, 256) or c.n_q_heads // c.n_kv_heads > 16
+                or (sparse and d["max_ctx"] > c.sparse_topk_blocks * c.block)):
+            return None
+        if "anc" not in d:
+            d["anc"] = tree_ancestor_masks(plan, dev)
+    w = mixer.w
     qbuf = torch.empty(R, c.n_q_heads, c.head_dim, dtype=torch.bfloat16, device=dev)
     qi = torch.empty(R, c.idx_heads, c.idx_dim, dtype=torch.float32, device=dev) if sparse else None
     rc = lib().spark_attn_prep(P(qkv), qkv.stride(0), R, c.n_q_heads, c.n_kv_heads, c.head_dim, c.rope_dim, int(c.gated),
@@ -1013,7 +890,7 @@ def attn_mixer(mixer, qkv, plan, seqs):
                                P(w.get("iq_norm")), P(w.get("ik_norm")), P(mixer.inv), P(d["pos32"]), P(d["row_kv"]),
                                P(d["row_j"]), P(qbuf), P(mixer.k), P(mixer.v), P(getattr(mixer, "ks", None)),
                                P(getattr(mixer, "vs", None)), P(qi), P(getattr(mixer, "ik_raw", None)),
-                               P(getattr(mixer, "ik_pool", None)), stream())
+                               P(getattr(mixer, "ik_pool", None)), stream(), P(d["row_pos0"]) if tree else None)
     check(rc, "spark_attn_prep")
     sel = sel_n = None
     sel_ld = 0
@@ -1023,7 +900,7 @@ def attn_mixer(mixer, qkv, plan, seqs):
         sel, sel_n = sp.select_blocks(mixer, qi, plan, d)
         sel_ld = sel.shape[1]
         max_ctx = sel_ld
-    if (sel is None and not mixer.fp8 and ATTN_PREFILL_KERNEL and c.head_dim in (64, 128, 256)
+    if (sel is None and not tree and not mixer.fp8 and ATTN_PREFILL_KERNEL and c.head_dim in (64, 128, 256)
             and min(s.n for s in plan.segs) >= ATTN_PREFILL_MIN_ROWS):
         # whole segments, dense context: flash-style tensor-core kernel (one CTA per 64 rows of a head)
         out = torch.empty(R, c.n_q_heads * c.head_dim, dtype=torch.bfloat16, device=dev)
@@ -1039,6 +916,8 @@ def attn_mixer(mixer, qkv, plan, seqs):
     rc = lib().spark_attn_decode(P(qbuf), P(mixer.k), P(mixer.v), P(getattr(mixer, "ks", None)),
                                  P(getattr(mixer, "vs", None)), int(mixer.fp8), P(d["pos32"]), P(d["row_kv"]), P(sel),
                                  P(sel_n), sel_ld, P(part_o), P(part_ml), nsplit, P(qkv), qkv.stride(0), int(c.gated), R,
-                                 c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), P(out), stream())
+                                 c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), P(out), stream(),
+                                 P(d["row_pos0"]) if tree else None, P(d["row_j"]) if tree else None,
+                                 P(d["anc"]) if tree else None)
     check(rc, "spark_attn_decode")
     return out

@@ -30,7 +30,12 @@ class CommCtx(C.Structure):
 class ArRows(C.Structure):
     _fields_ = [("c", CommCtx), ("slot_off", i64), ("flag_off", i64), ("seq", u32), ("rows_cap", i32), ("R", i32),
                 ("N", i32), ("inp", vp), ("in_f32", i32), ("counter", vp), ("res", vp), ("norm_w", vp), ("eps", f32),
-                ("out", vp), ("out_f32", i32), ("seq_ptr", vp)]
+                ("out", vp), ("out_f32", i32), ("seq_ptr", vp),
+                ("moe_y", vp), ("moe_w", vp), ("moe_ids", vp), ("moe_slots", i32), ("moe_shared", vp), ("moe_sg", vp)]
+
+
+class ArMoe(C.Structure):
+    _fields_ = [("y", vp), ("w", vp), ("ids", vp), ("slots", i32), ("shared", vp), ("sg", vp)]
 
 
 class HostPush(C.Structure):
@@ -47,7 +52,8 @@ _SIGS = {
     "spark_arena_alloc": ([i64], vp), "spark_arena_free": ([vp], None),
     "spark_ipc_get_handle": ([vp, vp], i32), "spark_ipc_open_handle": ([vp], vp), "spark_ipc_close": ([vp], None),
     "spark_comm_barrier": ([vp, i64, u32, vp], i32),
-    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp], i32),
+    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp, vp], i32),
+    "spark_tp_argmax": ([vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp], i32),
     "spark_rs_ag_rows": ([vp, i64, i64, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp, vp], i32),
     "spark_ag_push": ([vp, vp, i32, i32, i64, i64, u32, vp, vp, vp], i32),
     "spark_seq_bump": ([vp, vp], i32),
@@ -214,15 +220,27 @@ class FusedAllReduce:
         ar.out, ar.out_f32 = cu.P(out), int(out.dtype == torch.float32)
         return ar
 
-    def __call__(self, x: torch.Tensor, res: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+    def __call__(self, x, res: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
                  eps: float = 1e-6, out_dtype=torch.bfloat16) -> torch.Tensor:
-        R, N = x.shape
+        """`x`: this rank's partial rows [R, N], or the uncombined expert outputs of a decode round (`cu.PendingMoe`):
+        the slot-order combine then happens inside the push."""
+        moe = None
+        if isinstance(x, cu.PendingMoe):
+            pm = x
+            R, N = pm.R, pm.H
+            moe = ArMoe()
+            moe.y, moe.w, moe.ids, moe.slots = cu.P(pm.y), cu.P(pm.wts), cu.P(pm.ids), pm.slots
+            moe.shared, moe.sg = cu.P(pm.shared), cu.P(pm.sg)
+            dev, x = pm.y.device, None
+        else:
+            R, N = x.shape
+            dev, x = x.device, x.contiguous()
         assert N == self.N and R <= self.rows_cap
-        out = torch.empty(R, N, dtype=out_dtype, device=x.device)
-        ar = self._args(R, x.contiguous(), res, norm_w, eps, out)
+        out = torch.empty(R, N, dtype=out_dtype, device=dev)
+        ar = self._args(R, x, res, norm_w, eps, out)
         rc = _lib()._dll.spark_allreduce_rows(C.byref(ar.c), ar.slot_off, ar.flag_off, ar.seq, ar.rows_cap, R, N, ar.inp,
                                               ar.in_f32, ar.counter, ar.res, ar.norm_w, ar.eps, ar.out, ar.out_f32,
-                                              cu.stream(), ar.seq_ptr)
+                                              cu.stream(), ar.seq_ptr, C.byref(moe) if moe is not None else None)
         cu.check(rc, "spark_allreduce_rows")
         return out
 
@@ -238,10 +256,34 @@ class FusedAllReduce:
         S = cu._pick_slices(w.k)
         rc = cu.lib().spark_exl3_gemv(cu.P(x), x.stride(0), cu.P(w.trellis), cu.P(w.suh), cu.P(w.svh), 0, 0, 0, None,
                                       self.N, 0, None, None, 1, R, w.k, w.n, S, act, float(limit),
-                                      0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar), None, None, 0)
+                                      0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar), 0)
         cu.check(rc, "spark_exl3_gemv(fused all-reduce)")
         self._keep = ar
         return out
+
+
+class PacketArgmax:
+    """Vocabulary-parallel greedy sampling: local two-stage arg-max, (value, global id) packets pushed to every rank,
+    winner picked in rank order (ties -> lowest id); two launches, no host work, replayable under CUDA graphs."""
+
+    def __init__(self, arena: Arena, name: str, rows_cap: int = 64):
+        self.a, self.rows_cap = arena, rows_cap
+        self.slot_off = arena.region(name + ".packets", 2 * arena.world * rows_cap * 8)
+        self.flag_off = arena.region(name + ".flags", 8 * 4)
+        self.counter = arena.counter()
+        self.seq = arena.seq_counter()
+
+    def __call__(self, logits: torch.Tensor, vocab_off: int) -> torch.Tensor:
+        R, V = logits.shape
+        assert R <= self.rows_cap and logits.dtype == torch.float32
+        logits = logits.contiguous()
+        ids = torch.empty(R, dtype=torch.int32, device=logits.device)
+        pv = cu.scratch("tp_argmax_v", R * 64, torch.float32, logits.device)
+        pi = cu.scratch("tp_argmax_i", R * 64, torch.int32, logits.device)
+        rc = _lib()._dll.spark_tp_argmax(C.byref(self.a.ctx), self.slot_off, self.flag_off, self.seq.data_ptr(), self.counter,
+                                         self.rows_cap, cu.P(logits), R, V, vocab_off, cu.P(pv), cu.P(pi), cu.P(ids), cu.stream())
+        cu.check(rc, "spark_tp_argmax")
+        return ids
 
 
 class RowParallelGemm:

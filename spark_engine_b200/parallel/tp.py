@@ -209,6 +209,12 @@ class DeviceTP(TPBase):
         self.rows_cap = rows_cap
         self.ar = symm.FusedAllReduce(arena, name + ".ar", rows_cap, hidden)
         self.pk = symm.FusedAllReduce(arena, name + ".packets", 64, 2 * 8)
+        self.argmax = symm.PacketArgmax(arena, name + ".argmax", 64)
+
+    def greedy(self, logits_local: torch.Tensor, vocab_local: int) -> torch.Tensor:
+        if logits_local.shape[0] <= 64:
+            return self.argmax(logits_local.float(), self.rank * vocab_local)
+        return super().greedy(logits_local, vocab_local)
 
     def can_fuse_gemv(self, x, w) -> bool:
         from ..quant.formats import Exl3Weight
@@ -224,6 +230,8 @@ class DeviceTP(TPBase):
         if isinstance(delta, ops.Partial):
             h = self.ar.gemv_fused(delta.x.contiguous(), delta.w, res=res, norm_w=w, eps=eps)
             return h, res
+        if not isinstance(delta, torch.Tensor):          # uncombined MoE of a decode round: combined inside the push
+            return self.ar(delta, res=res, norm_w=w, eps=eps), res
         R = delta.shape[0]
         if R <= self.rows_cap:
             return self.ar(delta, res=res, norm_w=w, eps=eps), res

@@ -25,55 +25,13 @@ def rel_err(a, b):
     return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
 
 
-def _resid(x):
-    c = cu()
-    return c.row_ssq(c.Resid(x.clone()))
-
-
-@pytest.mark.parametrize("R", [1, 4, 11])
-def test_exl3_gemv_norm_prologue_and_residual_epilogue(R):
-    g = torch.Generator(device=DEV).manual_seed(3)
-    H, N = 2048, 1024
-    res = torch.randn(R, H, device=DEV, generator=g)
-    wn = torch.rand(H, device=DEV, generator=g) + 0.5
-    w_in = Q.random_exl3(N, H, 4, 0, 0.05, 5, DEV)
-    w_out = Q.random_exl3(H, N, 4, 0, 0.05, 6, DEV)
-    c = cu()
-    rs = _resid(res)
-    # strip partials == sums of squares of each 128-column strip
-    ref_ssq = res.view(R, H // 128, 128).pow(2).sum(-1).t()
-    assert torch.allclose(rs.ssq[:, :R], ref_ssq, rtol=1e-5)
-    h_ref = res * torch.rsqrt(res.pow(2).mean(-1, keepdim=True) + 1e-6) * wn
-    y_ref = h_ref.bfloat16().float().cpu() @ w_in.dequant().t()
-    y = c.exl3_gemv(c.LazyNorm(rs, wn, 1e-6), w_in)
-    assert rel_err(y.cpu(), y_ref) < 1e-2
-    # the explicit path (norm kernel, then GEMV) gives the same rows up to the rounding of rstd
-    y2 = c.exl3_gemv(c.rmsnorm(res, wn, 1e-6), w_in)
-    assert rel_err(y, y2) < 4e-3
-    # residual epilogue: res += x @ W^T, partials of the new rows
-    x = torch.randn(R, N, device=DEV, generator=g).bfloat16()
-    add_ref = x.float().cpu() @ w_out.dequant().t()
-    before = rs.x.clone()
-    assert c.exl3_gemv(x, w_out, res_out=rs) is None and rs.valid
-    assert rel_err((rs.x - before).cpu(), add_ref) < 1e-2
-    assert torch.allclose(rs.ssq[:, :R], rs.x.view(R, H // 128, 128).pow(2).sum(-1).t(), rtol=1e-5)
-    torch.cuda.synchronize()
-    assert c.read_status(torch.device(DEV))[0] == 0
-
-
-def test_gemv_bf16_norm_prologue_and_wide_grid():
+def test_gemv_bf16_wide_grid():
     g = torch.Generator(device=DEV).manual_seed(4)
     R, H, N = 4, 1024, 40000                   # wide enough that a CTA loops over several column groups
-    res = torch.randn(R, H, device=DEV, generator=g)
-    wn = torch.rand(H, device=DEV, generator=g) + 0.5
+    x = torch.randn(R, H, device=DEV, generator=g).bfloat16()
     W = (torch.randn(N, H, device=DEV, generator=g) * 0.05).bfloat16()
-    c = cu()
-    h_ref = (res * torch.rsqrt(res.pow(2).mean(-1, keepdim=True) + 1e-6) * wn).bfloat16().float()
-    ref = h_ref @ W.float().t()
-    y = c.gemv_bf16(c.LazyNorm(_resid(res), wn, 1e-6), W, out_f32=True)
-    assert rel_err(y, ref) < 3e-3
-    y_plain = c.gemv_bf16(h_ref.bfloat16(), W, out_f32=True)
-    assert rel_err(y_plain, ref) < 1e-4
+    y = cu().gemv_bf16(x, W, out_f32=True)
+    assert rel_err(y, x.float() @ W.float().t()) < 1e-4
 
 
 @pytest.mark.parametrize("kind,E,k", [("softmax", 512, 10), ("sigmoid_bias", 288, 8), ("sqrt_softplus", 384, 6)])
@@ -95,7 +53,7 @@ def test_fused_router_matches_reference(kind, E, k):
         prow = torch.zeros(R, slots, dtype=torch.int32, device=DEV)
         sg = torch.zeros(R, device=DEV)
         for rep in range(2):               # the arrival counter must be back at zero after a launch
-            rc = lib.spark_moe_router_topk(h.data_ptr(), h.stride(0), None, gate.data_ptr(), gate.stride(0), logits.data_ptr(), ld,
+            rc = lib.spark_moe_router_topk(h.data_ptr(), h.stride(0), gate.data_ptr(), gate.stride(0), logits.data_ptr(), ld,
                                            R, H, E, k, cu().ROUTER_KIND[kind], bias.data_ptr(), float(c.route_scale),
                                            int(c.shared_gate), slots, e_hi - e_lo, e_lo, e_hi, rank, world, wts.data_ptr(),
                                            ids.data_ptr(), prow.data_ptr(), sg.data_ptr(), counter.data_ptr(),
@@ -153,17 +111,17 @@ def test_shared_expert_as_a_pair_and_deferred_combine():
           "s_gu": wp["s_gu"].dequant(), "s_down": wp["s_down"].dequant()}
     ref = ops.moe(h.float().cpu(), wc, c)
     assert rel_err(a.cpu(), ref) < 2e-2
-    # deferred: expert outputs combined inside the residual update, partials left for the next norm
+    # deferred: the expert outputs are combined inside the residual update + RMSNorm launch
     cm = cu()
     res = torch.randn(R, H, device=DEV, generator=g)
-    rs = _resid(res)
+    wn = torch.rand(H, device=DEV, generator=g) + 0.5
     pend = ops.moe(h, ws, c, defer=True)
-    wn = torch.ones(H, device=DEV)
-    ln, rs2 = cm.add_rmsnorm(pend, rs, wn, 1e-6)
-    assert rs2 is rs and rel_err((rs.x - res).cpu(), ref) < 2e-2
-    assert torch.allclose(rs.ssq[:, :R], rs.x.view(R, H // 128, 128).pow(2).sum(-1).t(), rtol=1e-5)
-    hn = ln.tensor().float()
-    assert rel_err(hn, rs.x * torch.rsqrt(rs.x.pow(2).mean(-1, keepdim=True) + 1e-6)) < 5e-3
+    hn, res2 = cm.add_rmsnorm(pend, res.clone(), wn, 1e-6)
+    assert rel_err((res2 - res).cpu(), ref) < 2e-2
+    want = res2 * torch.rsqrt(res2.pow(2).mean(-1, keepdim=True) + 1e-6) * wn
+    assert rel_err(hn, want) < 5e-3
+    # and on its own: same sum as the fused launch added
+    assert rel_err(pend.tensor().float(), (res2 - res)) < 1e-2
 
 
 def _small_model():
@@ -217,3 +175,81 @@ def test_device_fed_steps_equal_host_fed_rounds():
         assert [eng.model.seqs[s].length for s in (0, 1)] == [87, 87]
         outs.append(toks)
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,fp8", [(256, 16, 2, False), (128, 8, 8, False), (64, 4, 2, True), (256, 16, 2, True)])
+def test_decode_attention_tensor_core_kernel(D, Hq, Hkv, fp8):
+    """Split-KV decode attention (dense context, selected-token lists, tree ancestor masks, FP8 KV) against fp32 softmax
+    attention over the same cache contents."""
+    import math
+    g = torch.Generator(device=DEV).manual_seed(9)
+    c = cu()
+    lib = c.lib()
+    tokens, R = 700, 5
+    kv_base = torch.tensor([0, 0, 0, 300, 300], dtype=torch.int64, device=DEV)       # two sequences
+    pos0 = torch.tensor([200, 200, 200, 310, 310], dtype=torch.int32, device=DEV)     # first in-flight position
+    row_j = torch.tensor([0, 1, 2, 0, 1], dtype=torch.int32, device=DEV)
+    pos = pos0 + row_j
+    K = torch.randn(tokens, Hkv, D, device=DEV, generator=g)
+    V = torch.randn(tokens, Hkv, D, device=DEV, generator=g)
+    q = torch.randn(R, Hq, D, device=DEV, generator=g).bfloat16()
+    if fp8:
+        ks = K.abs().amax(-1).clamp_min(1e-8) / 448.0
+        vs = V.abs().amax(-1).clamp_min(1e-8) / 448.0
+        Kc, Vc = (K / ks.unsqueeze(-1)).to(torch.float8_e4m3fn), (V / vs.unsqueeze(-1)).to(torch.float8_e4m3fn)
+        Kd, Vd = Kc.float() * ks.unsqueeze(-1), Vc.float() * vs.unsqueeze(-1)
+    else:
+        ks = vs = None
+        Kc, Vc = K.bfloat16(), V.bfloat16()
+        Kd, Vd = Kc.float(), Vc.float()
+    rep = Hq // Hkv
+    scale = 1.0 / math.sqrt(D)
+    qkv = torch.zeros(R, 8, device=DEV).bfloat16()
+
+    def run(sel=None, sel_n=None, tree=False, anc=None, max_ctx=None):
+        nsplit = (max_ctx + 63) // 64
+        part_o = torch.empty(R * Hq * nsplit * D, device=DEV)
+        part_ml = torch.empty(R * Hq * nsplit * 2, device=DEV)
+        out = torch.empty(R, Hq * D, dtype=torch.bfloat16, device=DEV)
+        rc = lib.spark_attn_decode(q.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), c.P(ks), c.P(vs), int(fp8), pos.data_ptr(),
+                                   kv_base.data_ptr(), c.P(sel), c.P(sel_n), 0 if sel is None else sel.shape[1], part_o.data_ptr(),
+                                   part_ml.data_ptr(), nsplit, qkv.data_ptr(), qkv.stride(0), 0, R, Hq, Hkv, D, scale,
+                                   out.data_ptr(), c.stream(), pos0.data_ptr() if tree else None,
+                                   row_j.data_ptr() if tree else None, c.P(anc))
+        assert rc == 0
+        return out.float().view(R, Hq, D)
+
+    def ref(visible):                           # visible: list of token-index tensors per row
+        o = torch.empty(R, Hq, D, device=DEV)
+        for r in range(R):
+            idx = visible[r] + int(kv_base[r])
+            kk = Kd[idx].repeat_interleave(rep, 1)          # [n, Hq, D]
+            vv = Vd[idx].repeat_interleave(rep, 1)
+            sc = torch.einsum("hd,nhd->hn", q[r].float(), kk) * scale
+            o[r] = torch.einsum("hn,nhd->hd", torch.softmax(sc, -1), vv)
+        return o
+
+    # dense causal context
+    got = run(max_ctx=int(pos.max()) + 1)
+    want = ref([torch.arange(int(p) + 1, device=DEV) for p in pos])
+    assert rel_err(got, want) < 2e-2
+    # selected-token lists of different lengths
+    sel_n = torch.tensor([70, 129, 64, 5, 200], dtype=torch.int32, device=DEV)
+    sel = torch.zeros(R, 200, dtype=torch.int32, device=DEV)
+    vis = []
+    for r in range(R):
+        ch = torch.randperm(int(pos[r]) + 1, device=DEV, generator=g)[: int(sel_n[r])].sort().values
+        sel[r, : int(sel_n[r])] = ch.int()
+        vis.append(ch)
+    got = run(sel=sel, sel_n=sel_n, max_ctx=200)
+    assert rel_err(got, ref(vis)) < 2e-2
+    # tree rows: sequence 0 has three in-flight rows, row 2 is a sibling of row 1 (both children of row 0)
+    anc = torch.tensor([0b001, 0b011, 0b101, 0b01, 0b11], dtype=torch.int32, device=DEV)
+    got = run(tree=True, anc=anc, max_ctx=int((pos0 + row_j).max()) + 1)
+    vis = []
+    for r in range(R):
+        own = [j for j in range(3) if (int(anc[r]) >> j) & 1]
+        vis.append(torch.cat((torch.arange(int(pos0[r]), device=DEV), torch.tensor(own, device=DEV) + int(pos0[r]))))
+    assert rel_err(got, ref(vis)) < 2e-2
+    torch.cuda.synchronize()
+    assert c.read_status(torch.device(DEV))[0] == 0
