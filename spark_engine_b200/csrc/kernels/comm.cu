@@ -126,7 +126,7 @@ __global__ void tp_argmax_packets_kernel(PkArgs a, const float* __restrict__ pv,
     __threadfence_system();
     if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
       *a.counter = 0;
-      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, seq);
+      for (int p = 0; p < W; ++p) st_relaxed_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_off) + a.c.rank, seq);
       *a.seq_ptr = seq;
     }
   }
@@ -187,7 +187,7 @@ rs_push_kernel(RsAg a_in) {
     __threadfence_system();
     if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
       *a.counter = 0;
-      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_rs_off) + a.c.rank, a.seq);
+      for (int p = 0; p < W; ++p) st_relaxed_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_rs_off) + a.c.rank, a.seq);
     }
   }
 }
@@ -252,7 +252,7 @@ rs_finish_ag_push_kernel(RsAg a_in) {
     __threadfence_system();
     if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) {
       *a.counter = 0;
-      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_ag_off) + a.c.rank, a.seq);
+      for (int p = 0; p < W; ++p) st_relaxed_sys(reinterpret_cast<uint32_t*>(a.c.peers[p] + a.flag_ag_off) + a.c.rank, a.seq);
     }
   }
 }
@@ -288,7 +288,7 @@ ag_push_kernel(CommCtx c, const __nv_bfloat16* __restrict__ x, int rows, int K, 
     __threadfence_system();
     if (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1) {
       *counter = 0;
-      for (int p = 0; p < W; ++p) st_release_sys(reinterpret_cast<uint32_t*>(c.peers[p] + flag_off) + c.rank, seq);
+      for (int p = 0; p < W; ++p) st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peers[p] + flag_off) + c.rank, seq);
     }
   }
 }
@@ -357,6 +357,8 @@ ar_push_kernel(ArRows a_in) {
 __global__ void __launch_bounds__(256)
 ar_tail_kernel(ArRows a_in, int* tail_counter) {
   __shared__ float red[8];
+  pdl_wait();
+  pdl_trigger();
   ArRows a = a_in;
   a.seq = comm_seq(a.seq_ptr, a.seq);
   ar_rows_tail(a, a.seq, blockIdx.x, gridDim.x, red);
@@ -473,5 +475,22 @@ extern "C" int spark_tp_argmax(const HostCtx* h, long long slot_off, long long f
   a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq_ptr = (uint32_t*)seq_ptr; a.counter = counter;
   a.rows_cap = rows_cap; a.vocab_off = vocab_off;
   e = spark_launch_pdl(tp_argmax_packets_kernel, dim3(R), dim3(32), 0, s, dim3(1, 1, 1), a, (const float*)part_v, (const int*)part_i, nc, out_id);
+  return e == cudaSuccess ? 0 : -4;
+}
+
+// Second half of an all-reduce whose pushes were made by another kernel's epilogue (the row-parallel EXL3 GEMV):
+// one CTA per row waits (bounded) for every rank's flag, sums in rank order (+ residual)(+ RMSNorm), and the last CTA
+// closes the sequence.  `counter` + 1 is the tail's own arrival counter.
+extern "C" int spark_allreduce_tail(const HostCtx* h, long long slot_off, long long flag_off, int rows_cap, int R, int N,
+                                    int* counter, float* res, const float* norm_w, float eps, void* out, int out_f32,
+                                    cudaStream_t s, void* seq_ptr) {
+  if (R <= 0) return 0;
+  if (N % 4 || R > rows_cap || seq_ptr == nullptr) return -5;
+  ArRows a;
+  a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = 0; a.rows_cap = rows_cap; a.R = R; a.N = N;
+  a.in = nullptr; a.in_f32 = 0; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32;
+  a.seq_ptr = (uint32_t*)seq_ptr;
+  a.moe_y = nullptr; a.moe_w = nullptr; a.moe_ids = nullptr; a.moe_slots = 0; a.moe_shared = nullptr; a.moe_sg = nullptr;
+  const cudaError_t e = spark_launch_pdl(ar_tail_kernel, dim3(R < 296 ? R : 296), dim3(256), 0, s, dim3(1, 1, 1), a, counter + 1);
   return e == cudaSuccess ? 0 : -4;
 }

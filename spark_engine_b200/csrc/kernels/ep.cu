@@ -156,7 +156,7 @@ ep_dispatch_kernel(CommCtx c, EpLayout L, uint32_t seq, const __nv_bfloat16* __r
         send_count[d] = 0;
       }
       __threadfence_system();
-      for (int d = 0; d < c.world; ++d) st_release_sys(reinterpret_cast<uint32_t*>(c.peers[d] + L.flag_off) + c.rank, seq);
+      for (int d = 0; d < c.world; ++d) st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peers[d] + L.flag_off) + c.rank, seq);
     }
   }
 }
@@ -222,7 +222,7 @@ ep_combine_push_kernel(CommCtx c, EpLayout L, uint32_t seq, int H, int top_k, co
     __threadfence_system();
     if (atomicAdd(done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
       *done_counter = 0;
-      for (int d = 0; d < c.world; ++d) st_release_sys(reinterpret_cast<uint32_t*>(c.peers[d] + L.ret_flag_off) + c.rank, seq);
+      for (int d = 0; d < c.world; ++d) st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peers[d] + L.ret_flag_off) + c.rank, seq);
     }
   }
 }

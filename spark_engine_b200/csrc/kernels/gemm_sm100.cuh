@@ -341,7 +341,7 @@ struct EpiPushRS {
     if (atomicAdd(counter, 1) == n_ctas - 1) {
       *counter = 0;
       const uint32_t sq = comm_seq(seq_ptr, seq);
-      for (int p = 0; p < world; ++p) st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + flag_off) + rank, sq);
+      for (int p = 0; p < world; ++p) st_relaxed_sys(reinterpret_cast<uint32_t*>(peers[p] + flag_off) + rank, sq);
     }
   }
 };

@@ -216,10 +216,11 @@ def decode_step_bytes(W, cfg: ModelConfig, rows: int) -> int:
         else:
             stack = wg.packed.shape[0] if hasattr(wg, "packed") else cfg.moe.n_experts
         per_expert = (nbytes(m["w_gu"]) + nbytes(m["w_down"])) / max(stack, 1)
-        pairs = min(rows * cfg.moe.top_k, cfg.moe.n_experts)
+        world = m.get("tp_rank", (0, 1))[1]
+        pairs = min(rows * cfg.moe.top_k, cfg.moe.n_experts) / world       # this rank's share on average
         total += int(per_expert * pairs)
         if m.get("shared_in_stack"):
-            total += int(per_expert)
+            total += int(per_expert * min(1.0, rows / world))
         elif "s_gu" in m:
             total += nbytes(m["s_gu"]) + nbytes(m["s_down"])
     return int(total)

@@ -53,6 +53,7 @@ _SIGS = {
     "spark_ipc_get_handle": ([vp, vp], i32), "spark_ipc_open_handle": ([vp], vp), "spark_ipc_close": ([vp], None),
     "spark_comm_barrier": ([vp, i64, u32, vp], i32),
     "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp, vp], i32),
+    "spark_allreduce_tail": ([vp, i64, i64, i32, i32, i32, vp, vp, vp, f32, vp, i32, vp, vp], i32),
     "spark_tp_argmax": ([vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp], i32),
     "spark_rs_ag_rows": ([vp, i64, i64, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp, vp], i32),
     "spark_ag_push": ([vp, vp, i32, i32, i64, i64, u32, vp, vp, vp], i32),
@@ -246,8 +247,9 @@ class FusedAllReduce:
 
     def gemv_fused(self, x: torch.Tensor, w, res=None, norm_w=None, eps=1e-6, act=0, limit=0.0,
                    out_dtype=torch.bfloat16) -> torch.Tensor:
-        """y = allreduce(x @ W_shard^T) (+ res)(-> RMSNorm) in ONE kernel: the row-parallel EXL3 GEMV pushes its
-        strips into every rank's slots and its last CTA reduces."""
+        """y = allreduce(x @ W_shard^T) (+ res)(-> RMSNorm): the row-parallel EXL3 GEMV pushes its strips straight into
+        every rank's slots from its epilogue (no local round trip of the partial rows) and raises the flag; a tail
+        launch with one CTA per row reduces."""
         from ..quant.formats import Exl3Weight
         assert isinstance(w, Exl3Weight) and not w.experts and w.n == self.N
         R = x.shape[0]
@@ -258,6 +260,9 @@ class FusedAllReduce:
                                       self.N, 0, None, None, 1, R, w.k, w.n, S, act, float(limit),
                                       0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar), 0)
         cu.check(rc, "spark_exl3_gemv(fused all-reduce)")
+        rc = _lib()._dll.spark_allreduce_tail(C.byref(ar.c), ar.slot_off, ar.flag_off, ar.rows_cap, R, self.N, ar.counter, ar.res,
+                                              ar.norm_w, ar.eps, ar.out, ar.out_f32, cu.stream(), ar.seq_ptr)
+        cu.check(rc, "spark_allreduce_tail")
         self._keep = ar
         return out
 
