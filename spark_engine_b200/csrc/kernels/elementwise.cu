@@ -171,6 +171,32 @@ __global__ void gather_rows_bf16_kernel(const __nv_bfloat16* __restrict__ src, c
 
 using namespace spark;
 
+// Gumbel-max sampling noise, in place: x[r][v] = x[r][v] / T_r + g(seed_r, pos_r, off + v) for rows with T_r > 0
+// (rows with T_r <= 0 stay greedy).  g = -log(-log u), u a splitmix64 hash of (seed, position, global vocabulary id),
+// so every rank of a vocabulary-parallel head perturbs its slice with the noise of the global ids and the arg-max over
+// ranks is the token a single GPU would draw.  Double-precision logs keep it equal to the host oracle after rounding.
+// Reference: engine-rs/src/sampling.rs:20-170, shim/latent.cu:840-940.
+static __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+static __global__ void gumbel_perturb_kernel(float* __restrict__ x, int V, int ldx, const float* __restrict__ temp,
+                                      const long long* __restrict__ seed, const long long* __restrict__ pos, int off) {
+  const int r = blockIdx.y;
+  const float T = temp[r];
+  if (!(T > 0.f)) return;
+  const unsigned long long key = ((unsigned long long)seed[r] * 0x9E3779B97F4A7C15ull) ^
+                                 ((unsigned long long)(pos[r] + 1) * 0xBF58476D1CE4E5B9ull);
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x) {
+    const unsigned long long h = mix64((unsigned long long)(v + off) * 0x9E3779B97F4A7C15ull + key);
+    const double u = ((double)(h >> 11) + 0.5) * (1.0 / 9007199254740992.0);
+    const float g = (float)(-log(-log(u)));
+    float* p = x + (size_t)r * ldx + v;
+    *p = *p / T + g;
+  }
+}
+
 extern "C" void spark_add_rmsnorm(const void* delta, int delta_f32, float* res, const float* w, void* out, int R, int H,
                                   float eps, int one_plus, cudaStream_t s) {
   if (R <= 0) return;
@@ -209,6 +235,14 @@ extern "C" void spark_argmax(const float* logits, int R, int V, int* out_id, flo
   spark_launch_pdl(argmax_part_kernel, dim3(R, nc), dim3(256), 0, s, dim3(1, 1, 1), logits, V, part_v, part_i);
   spark_launch_pdl(argmax_final_kernel, dim3(R), dim3(32), 0, s, dim3(1, 1, 1), (const float*)part_v, (const int*)part_i, nc, out_id,
                    out_val);
+}
+extern "C" int spark_gumbel_perturb(float* x, int R, int V, int ldx, const float* temp, const long long* seed,
+                                    const long long* pos, int off, cudaStream_t s) {
+  if (R <= 0 || V <= 0) return 0;
+  if (R > 65535) return -5;
+  const int bx = V >= 65536 ? 32 : (V >= 4096 ? 8 : 1);
+  gumbel_perturb_kernel<<<dim3(bx, R), 256, 0, s>>>(x, V, ldx, temp, seed, pos, off);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 extern "C" void spark_add(const void* delta, int delta_f32, float* res, long n, cudaStream_t s) {
   if (n <= 0) return;

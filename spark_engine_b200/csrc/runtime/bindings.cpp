@@ -83,11 +83,13 @@ PYBIND11_MODULE(_runtime, m) {
       .def("on_admitted", &Scheduler::on_admitted).def("on_prefilled", &Scheduler::on_prefilled).def("on_tokens", &Scheduler::on_tokens)
       .def("on_finished", &Scheduler::on_finished).def("slot", &Scheduler::slot, py::return_value_policy::copy)
       .def("request", &Scheduler::request, py::return_value_policy::copy)
+      .def("has_work", &Scheduler::has_work)
       .def("stats", [](Scheduler& s) { auto t = s.stats(); return py::dict(py::arg("waiting") = t.waiting, py::arg("running") = t.running, py::arg("decoding") = t.decoding, py::arg("prefilling") = t.prefilling, py::arg("admitted") = t.admitted, py::arg("finished") = t.finished, py::arg("cancelled") = t.cancelled, py::arg("prefix_hit_tokens") = t.prefix_hit_tokens, py::arg("kv_budget") = t.kv_budget, py::arg("kv_active") = t.kv_active); })
       .def_static("common_prefix", &Scheduler::common_prefix);
 
   py::class_<OpLog>(m, "OpLog").def(py::init<const std::string&, bool, int, int>(), py::arg("name"), py::arg("create"), py::arg("n_followers") = 0, py::arg("follower_index") = -1)
       .def("append", &OpLog::append, py::arg("kind"), py::arg("payload"), py::arg("timeout_ms") = 5000, py::call_guard<py::gil_scoped_release>()).def("head", &OpLog::head)
+      .def("wait_acked", &OpLog::wait_acked, py::arg("seq"), py::arg("timeout_ms") = 2000, py::call_guard<py::gil_scoped_release>())
       .def("next", [](OpLog& o, uint64_t last, int timeout_ms) { int kind = 0; std::vector<int32_t> pl; bool ok; { py::gil_scoped_release rel; ok = o.next(last, timeout_ms, &kind, &pl); } return py::make_tuple(ok, kind, pl); })
       .def_static("unlink", &OpLog::unlink_name);
 
@@ -97,7 +99,9 @@ PYBIND11_MODULE(_runtime, m) {
       .def("names", &SafeTensors::names).def("info", &SafeTensors::info, py::return_value_policy::copy).def("has", &SafeTensors::has)
       .def("read_into", [](SafeTensors& s, const std::string& n, uintptr_t dst, int64_t cap) { py::gil_scoped_release rel; return s.read_into(n, reinterpret_cast<void*>(dst), cap); })
       .def("bytes", [](SafeTensors& s, const std::string& n) { auto& ti = s.info(n); return py::bytes(reinterpret_cast<const char*>(s.data(n)), ti.end - ti.begin); })
-      .def("prefetch", &SafeTensors::prefetch);
+      .def("prefetch", &SafeTensors::prefetch)
+      .def("data_offset", &SafeTensors::data_offset)
+      .def("path", &SafeTensors::path);
 
   m.def("mem_available_bytes", [](const std::string& p) { return mem_available_bytes(p.empty() ? nullptr : p.c_str()); }, py::arg("meminfo") = "");
   m.def("allocator_cap", [](int64_t r, int64_t mg, const std::string& p) { return allocator_cap(r, mg, p.empty() ? nullptr : p.c_str()); }, py::arg("reserved"), py::arg("margin"), py::arg("meminfo") = "");

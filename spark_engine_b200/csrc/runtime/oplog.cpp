@@ -49,6 +49,18 @@ uint64_t OpLog::append(int kind, const std::vector<int32_t>& payload, int timeou
   return seq;
 }
 
+int OpLog::wait_acked(uint64_t seq, int timeout_ms) const {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (int f = 0; f < n_followers_; ++f) {
+    int spins = 0;
+    while (sh_->acks[f].load(std::memory_order_acquire) < seq) {
+      if (std::chrono::steady_clock::now() > deadline) return f;
+      if (++spins < 200) std::this_thread::yield(); else std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+  return -1;
+}
+
 uint64_t OpLog::head() const { return sh_->head.load(std::memory_order_acquire); }
 
 bool OpLog::next(uint64_t last_seq, int timeout_ms, int* kind, std::vector<int32_t>* payload) {

@@ -33,6 +33,9 @@ class OpLog {
   // follower: waits up to timeout_ms for the record after `last_seq`; returns false on timeout (leader lost)
   bool next(uint64_t last_seq, int timeout_ms, int* kind, std::vector<int32_t>* payload);
   uint64_t head() const;
+  // leader: waits up to timeout_ms until every follower has read record `seq`; returns the index of the first follower
+  // that has not (a follower that stopped), or -1 when all have.  Called before a step whose collectives need every rank.
+  int wait_acked(uint64_t seq, int timeout_ms) const;
   static void unlink_name(const std::string& name);
 
  private:

@@ -22,6 +22,8 @@ class SafeTensors {
   int64_t read_into(const std::string& name, void* dst, int64_t cap) const;
   void prefetch(const std::string& name) const;                        // page-cache read-ahead hint
   bool has(const std::string& name) const { return tensors_.count(name) != 0; }
+  int64_t data_offset() const { return data_off_; }                    // file offset of the first tensor byte
+  const std::string& path() const { return path_; }
 
  private:
   std::string path_;

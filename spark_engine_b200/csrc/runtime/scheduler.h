@@ -76,6 +76,12 @@ class Scheduler {
   const SlotState& slot(int i) const { return slots_[i]; }
   const Request* request(int64_t id) const;
   SchedStats stats() const;
+  // anything queued or running (a step may still turn out idle, e.g. a queued request waiting for KV room)
+  bool has_work() const {
+    if (!queue_.empty()) return true;
+    for (auto& s : slots_) if (s.busy) return true;
+    return false;
+  }
   static int64_t common_prefix(const std::vector<int32_t>& a, const std::vector<int32_t>& b);
 
  private:

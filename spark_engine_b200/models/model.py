@@ -689,6 +689,38 @@ class Model:
             return self.tp.greedy(logits, logits.shape[1])
         return ops.argmax(logits)
 
+    def sample_rows(self, logits: torch.Tensor, temps, seeds, positions) -> List[int]:
+        """One token per logits row: Gumbel-max with noise keyed by (seed, position, global vocabulary id) where the
+        row's temperature is > 0, greedy otherwise.  Correct under vocabulary parallelism (every rank returns the
+        same global ids) and one device-to-host read for all rows.
+        Reference: engine-rs/src/sampling.rs:20-170, head_select.rs:1-101."""
+        if logits.dim() == 1:
+            logits = logits.unsqueeze(0)
+        off = self.tp.rank * logits.shape[1] if self.tp is not None else 0
+        x = ops.gumbel_perturb(logits, temps, seeds, positions, off, self.cfg.vocab)
+        return [int(t) for t in self.greedy(x).tolist()]
+
+    def sample(self, logits: torch.Tensor, temperature: float, seed: int, position: int) -> int:
+        return self.sample_rows(logits, [temperature], [seed], [position])[0]
+
+    def token_prob(self, logits_row: torch.Tensor, token: int) -> float:
+        """softmax(logits)[token] for one row; under vocabulary parallelism the maximum and the exponent sum are
+        combined over ranks, so every rank returns the same number."""
+        x = logits_row.float().reshape(-1)
+        if self.tp is None:
+            return float(torch.softmax(x, -1)[token])
+        tp, Vl = self.tp, x.shape[0]
+        pk = torch.full((1, tp.world), 0.0, dtype=torch.float32, device=x.device)
+        pk[0, tp.rank] = x.max()
+        mx = tp.allreduce(pk).max()                      # column r has one contributor (rank r): the sum gathers the maxima
+        own = tp.rank * Vl <= token < (tp.rank + 1) * Vl
+        pk2 = torch.zeros(1, 2, dtype=torch.float32, device=x.device)
+        pk2[0, 0] = torch.exp(x - mx).sum()
+        if own:
+            pk2[0, 1] = torch.exp(x[token - tp.rank * Vl] - mx)
+        out = tp.allreduce(pk2)
+        return float(out[0, 1] / out[0, 0])
+
     def commit(self, accepted: List[List[int]]):
         """accepted[i]: segment-local rows of segment i that become part of the sequence, a path
         from the segment's first row (always accepted: it is the last sampled token)."""

@@ -72,6 +72,27 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return torch.argmax(logits, -1).to(torch.int32)
 
 
+def gumbel_perturb(logits: torch.Tensor, temps, seeds, positions, offset: int, vocab: int) -> torch.Tensor:
+    """fp32 logits [R, V_local] of vocabulary ids [offset, offset + V_local): rows with temperature > 0 become
+    logits / T + g(seed, position, global id); greedy rows are returned unchanged.  The arg-max of the result (over
+    all ranks' slices) is the sampled token.  temps/seeds/positions are Python sequences of length R."""
+    if not any(t > 0 for t in temps):
+        return logits
+    x = logits.float() if logits.dtype != torch.float32 else logits.clone()
+    if use_kernels(x):
+        dev = x.device
+        t = torch.tensor(list(temps), dtype=torch.float32).to(dev, non_blocking=True)
+        sd = torch.tensor([int(v) for v in seeds], dtype=torch.int64).to(dev, non_blocking=True)
+        ps = torch.tensor([int(v) for v in positions], dtype=torch.int64).to(dev, non_blocking=True)
+        return cuda_ops().gumbel_perturb(x.contiguous(), t, sd, ps, offset)
+    from ..spec.sampling import gumbel_noise_ref
+    V = x.shape[1]
+    for r, T in enumerate(temps):
+        if T > 0:
+            x[r] = x[r] / T + gumbel_noise_ref(int(seeds[r]), int(positions[r]), vocab, x.device)[offset: offset + V]
+    return x
+
+
 def lm_head(h, w) -> torch.Tensor:
     """Logits in fp32."""
     if use_kernels(h) and not isinstance(w, QuantWeight):

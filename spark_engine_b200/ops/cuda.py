@@ -37,6 +37,7 @@ _SIGS = {
     "spark_moe_combine_norm": [vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, vp, vp, vp, vp],
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
     "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
+    "spark_gumbel_perturb": [vp, i32, i32, i32, vp, vp, vp, i32, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
@@ -424,6 +425,15 @@ def argmax(logits):
     pi = scratch("argmax_i", R * 64, torch.int32, logits.device)
     lib().spark_argmax(P(logits.contiguous()), R, V, P(ids), None, P(pv), P(pi), stream())
     return ids
+
+
+def gumbel_perturb(logits, temps, seeds, positions, offset):
+    """In place on fp32 logits [R, V]: rows with temperature > 0 become logits / T + Gumbel noise of the global ids."""
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    check(lib().spark_gumbel_perturb(P(logits), R, V, logits.stride(0), P(temps), P(seeds), P(positions), int(offset), stream()),
+          "gumbel_perturb")
+    return logits
 
 
 def gather_rows(src, idx32):

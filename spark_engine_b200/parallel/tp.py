@@ -38,18 +38,19 @@ def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
     return c
 
 
-def _rows(t, lo, hi):
-    return t[lo:hi].contiguous()
-
-
-def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
-    """This rank's shard of a dense (unquantised) weight dict laid out as in models/weights.py."""
+def shard_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
+    """This rank's shard of a full weight dict (dense tensors or packed EXL3 / MXFP4 / MXFP8 / FP8-block weights, cut
+    without decoding: quant/formats.py `take_out` / `take_in` / `take_experts`).  A shared expert that lives in the
+    expert stacks stays on every rank (decode serves row r's shared pair on rank r % world); a separate shared expert
+    stays on rank 0.  Reference: engine-rs/src/weights.rs:119-153,831-864, ds41/cfg.rs:86-113."""
+    from ..quant.formats import Exl3Weight, take_experts, take_in, take_out
+    ar = torch.arange
     out = {k: v for k, v in W.items() if k not in ("lm_head", "layers", "mtp")}      # replicated tensors and tables
-    out["layers"] = []
     V = cfg.vocab
     assert V % world == 0
-    out["lm_head"] = _rows(W["lm_head"], rank * V // world, (rank + 1) * V // world)
-    for lw in W["layers"]:
+    out["lm_head"] = take_out(W["lm_head"], ar(rank * V // world, (rank + 1) * V // world))
+
+    def layer(lw):
         kind, w = lw["type"], lw["mix"]
         nl = {"type": kind, "in_norm": lw["in_norm"], "post_norm": lw["post_norm"]}
         if kind == "gdn":
@@ -57,15 +58,15 @@ def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dic
             D, hk, hv = c.head_dim, c.n_k_heads // world, c.n_v_heads // world
             nq, nv = c.n_k_heads * D, c.n_v_heads * D
             q0, v0 = rank * hk * D, rank * hv * D
-            sel = torch.cat((torch.arange(q0, q0 + hk * D), nq + torch.arange(q0, q0 + hk * D),
-                             2 * nq + torch.arange(v0, v0 + hv * D)))
-            zsel = 2 * nq + nv + torch.arange(v0, v0 + hv * D)
-            hsel = torch.arange(rank * hv, (rank + 1) * hv)
-            nl["mix"] = {"in": w["in"][torch.cat((sel, zsel))].contiguous(),
-                         "ab": w["ab"][torch.cat((hsel, c.n_v_heads + hsel))].contiguous(),
-                         "conv": w["conv"][sel].contiguous(), "A_log": w["A_log"][hsel].contiguous(),
-                         "dt_bias": w["dt_bias"][hsel].contiguous(), "norm": w["norm"],
-                         "o": w["o"][:, v0: v0 + hv * D].contiguous()}
+            sel = torch.cat((ar(q0, q0 + hk * D), nq + ar(q0, q0 + hk * D), 2 * nq + ar(v0, v0 + hv * D)))
+            zsel = 2 * nq + nv + ar(v0, v0 + hv * D)
+            hsel = ar(rank * hv, (rank + 1) * hv)
+            nl["mix"] = {"in": take_out(w["in"], torch.cat((sel, zsel))),
+                         "ab": w["ab"][torch.cat((hsel, c.n_v_heads + hsel)).to(w["ab"].device)].contiguous(),
+                         "conv": w["conv"][sel.to(w["conv"].device)].contiguous(),
+                         "A_log": w["A_log"][hsel.to(w["A_log"].device)].contiguous(),
+                         "dt_bias": w["dt_bias"][hsel.to(w["dt_bias"].device)].contiguous(), "norm": w["norm"],
+                         "o": take_in(w["o"], v0, v0 + hv * D)}
         elif kind == "attn":
             c = cfg.attn
             D = c.head_dim
@@ -77,25 +78,24 @@ def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dic
                 kv0 = rank * hkv
             else:
                 hkv, kv0 = 1, rank * c.n_kv_heads // world
-            sel = torch.cat((torch.arange(rank * hq * qw, (rank + 1) * hq * qw),
-                             nq + torch.arange(kv0 * D, (kv0 + hkv) * D),
-                             nq + nkv + torch.arange(kv0 * D, (kv0 + hkv) * D),
-                             torch.arange(nq + 2 * nkv, w["qkv"].shape[0])))
+            sel = torch.cat((ar(rank * hq * qw, (rank + 1) * hq * qw), nq + ar(kv0 * D, (kv0 + hkv) * D),
+                             nq + nkv + ar(kv0 * D, (kv0 + hkv) * D), ar(nq + 2 * nkv, w["qkv"].shape[0])))
             nl["mix"] = dict(w)
-            nl["mix"]["qkv"] = w["qkv"][sel].contiguous()
-            nl["mix"]["o"] = w["o"][:, rank * hq * D: (rank + 1) * hq * D].contiguous()
+            nl["mix"]["qkv"] = take_out(w["qkv"], sel)
+            nl["mix"]["o"] = take_in(w["o"], rank * hq * D, (rank + 1) * hq * D)
         elif kind == "kda":
             c = cfg.kda
             D, hh = c.head_dim, c.n_heads // world
             n, r = c.n_heads * D, c.gate_rank
-            ch = torch.arange(rank * hh * D, (rank + 1) * hh * D)           # this rank's channels inside q, k or v
+            ch = ar(rank * hh * D, (rank + 1) * hh * D)                  # this rank's channels inside q, k or v
             sel = torch.cat((ch, n + ch, 2 * n + ch))
-            hsel = torch.arange(rank * hh, (rank + 1) * hh)
-            nl["mix"] = {"in": w["in"][sel].contiguous(), "conv": w["conv"][sel].contiguous(),
-                         "lr_a": torch.cat((w["lr_a"][: 2 * r], w["lr_a"][2 * r + hsel])).contiguous(),
-                         "f_b": w["f_b"][ch].contiguous(), "g_b": w["g_b"][ch].contiguous(),
-                         "A_log": w["A_log"][hsel].contiguous(), "dt_bias": w["dt_bias"][ch].contiguous(),
-                         "o_norm": w["o_norm"], "o": w["o"][:, ch].contiguous()}
+            hsel = ar(rank * hh, (rank + 1) * hh)
+            dv = w["conv"].device
+            nl["mix"] = {"in": take_out(w["in"], sel), "conv": w["conv"][sel.to(dv)].contiguous(),
+                         "lr_a": torch.cat((w["lr_a"][: 2 * r], w["lr_a"][(2 * r + hsel).to(w["lr_a"].device)])).contiguous(),
+                         "f_b": w["f_b"][ch.to(dv)].contiguous(), "g_b": w["g_b"][ch.to(dv)].contiguous(),
+                         "A_log": w["A_log"][hsel.to(dv)].contiguous(), "dt_bias": w["dt_bias"][ch.to(dv)].contiguous(),
+                         "o_norm": w["o_norm"], "o": take_in(w["o"], int(ch[0]), int(ch[-1]) + 1)}
         elif kind == "mla":
             c = cfg.mla
             hh = c.n_heads // world
@@ -104,7 +104,7 @@ def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dic
             nl["mix"] = dict(w)                                              # low-rank projections, norms, indexer: replicated
             nl["mix"]["q_b"] = torch.cat((w["q_b"][rank * hh * qw: (rank + 1) * hh * qw], w["q_b"][nq:])).contiguous()
             nl["mix"]["kv_b"] = w["kv_b"][rank * hh * 2 * c.head_dim: (rank + 1) * hh * 2 * c.head_dim].contiguous()
-            nl["mix"]["o"] = w["o"][:, rank * hh * c.head_dim: (rank + 1) * hh * c.head_dim].contiguous()
+            nl["mix"]["o"] = take_in(w["o"], rank * hh * c.head_dim, (rank + 1) * hh * c.head_dim)
             if "sink" in w:
                 nl["mix"]["sink"] = w["sink"][rank * hh: (rank + 1) * hh].contiguous()
         else:
@@ -116,20 +116,40 @@ def shard_dense_weights(W: dict, cfg: ModelConfig, rank: int, world: int) -> dic
         if "dense_gu" in m:
             F = cfg.moe.dense_ffn
             f0, f1 = rank * F // world, (rank + 1) * F // world
-            nl["mlp"] = {"dense_gu": torch.cat((m["dense_gu"][f0:f1], m["dense_gu"][F + f0: F + f1])).contiguous(),
-                         "dense_down": m["dense_down"][:, f0:f1].contiguous()}
+            nl["mlp"] = {"dense_gu": take_out(m["dense_gu"], torch.cat((ar(f0, f1), F + ar(f0, f1)))),
+                         "dense_down": take_in(m["dense_down"], f0, f1)}
         else:
             E = cfg.moe.n_experts
             e0, e1 = rank * E // world, (rank + 1) * E // world
-            nm = {"gate": m["gate"], "w_gu": m["w_gu"][e0:e1].contiguous(), "w_down": m["w_down"][e0:e1].contiguous(),
-                  "ep": (e0, e1)}
+            nm = {"gate": m["gate"], "ep": (e0, e1), "tp_rank": (rank, world)}
+            if m.get("shared_in_stack"):
+                # stack = E routed experts + the shared expert at index E: keep [e0, e1) and the shared one
+                def cut(w):
+                    a, b = take_experts(w, e0, e1), take_experts(w, E, E + 1)
+                    return Exl3Weight(torch.cat((a.trellis, b.trellis)), torch.cat((a.suh, b.suh)), torch.cat((a.svh, b.svh)),
+                                      a.bits, a.kind)
+                nm["w_gu"], nm["w_down"] = cut(m["w_gu"]), cut(m["w_down"])
+                nm["shared_in_stack"] = True
+                e_loc = e1 - e0
+                for name, st in (("s_gu", nm["w_gu"]), ("s_down", nm["w_down"])):
+                    nm[name] = Exl3Weight(st.trellis[e_loc], st.suh[e_loc], st.svh[e_loc], st.bits, st.kind)
+            else:
+                nm["w_gu"], nm["w_down"] = take_experts(m["w_gu"], e0, e1), take_experts(m["w_down"], e0, e1)
+                if "s_gu" in m and rank == 0:
+                    nm["s_gu"], nm["s_down"] = m["s_gu"], m["s_down"]
             if "bias" in m:
                 nm["bias"] = m["bias"]
-            if "s_gu" in m and rank == 0:
-                nm["s_gu"], nm["s_down"] = m["s_gu"], m["s_down"]
             nl["mlp"] = nm
-        out["layers"].append(nl)
+        return nl
+
+    out["layers"] = [layer(lw) for lw in W["layers"]]
+    if "mtp" in W:
+        out["mtp"] = dict(W["mtp"])
+        out["mtp"]["layers"] = [layer(lw) for lw in W["mtp"]["layers"]]
     return out
+
+
+shard_dense_weights = shard_weights      # older name: the same rules served dense tensors only
 
 
 class TPBase:

@@ -345,3 +345,101 @@ def random_mxfp8(n, k, std=0.02, seed=0, device="cpu") -> Mxfp8Weight:
     e = int(round(math.log2(std / 100))) + 127
     scales = torch.randint(e - 1, e + 1, (n, k // 32), dtype=torch.uint8, device=device, generator=g)
     return Mxfp8Weight(q, scales)
+
+
+# ----------------------------------------------------------------------------- slicing (tensor-parallel shards)
+# A shard of a quantised matrix is cut out of the packed tensors without decoding.  Output rows are taken in whole
+# 128-row blocks (the EXL3 output Hadamard and the FP8 block scales mix 128 rows; the MX formats scale along K only,
+# but every shard rule cuts at multiples of the head size, so one rule serves all), input columns in whole 128-column
+# blocks, experts by index range.  Dense tensors take the same three cuts with plain indexing.
+def _blocks_of(idx: torch.Tensor, block: int) -> torch.Tensor:
+    if idx.numel() % block:
+        raise ValueError(f"output rows of a quantised matrix must be selected in whole aligned blocks of {block}")
+    idx = idx.reshape(-1, block)
+    first = idx[:, 0]
+    if (first % block).any() or not torch.equal(idx, first.unsqueeze(1) + torch.arange(block)):
+        raise ValueError(f"output rows of a quantised matrix must be selected in whole aligned blocks of {block}")
+    return first // block
+
+
+def take_out(w, idx: torch.Tensor):
+    """Rows `idx` (output features) of a [.., N, K] weight."""
+    idx = idx.cpu()
+    if isinstance(w, torch.Tensor):
+        return w.index_select(-2, idx.to(w.device)).contiguous()
+    if isinstance(w, Exl3Weight):
+        tiles = (_blocks_of(idx, 128).unsqueeze(1) * 8 + torch.arange(8)).flatten().to(w.trellis.device)
+        return Exl3Weight(w.trellis.index_select(-2, tiles).contiguous(), w.suh,
+                          w.svh.index_select(-1, idx.to(w.svh.device)).contiguous(), w.bits, w.kind)
+    if isinstance(w, Mxfp4Weight):
+        i = idx.to(w.packed.device)
+        return Mxfp4Weight(w.packed.index_select(-2, i).contiguous(), w.scales.index_select(-2, i).contiguous())
+    if isinstance(w, Mxfp8Weight):
+        i = idx.to(w.q.device)
+        return Mxfp8Weight(w.q.index_select(-2, i).contiguous(), w.scales.index_select(-2, i).contiguous())
+    if isinstance(w, Fp8BlockWeight):
+        blk = _blocks_of(idx, w.bn).to(w.q.device)
+        return Fp8BlockWeight(w.q.index_select(-2, idx.to(w.q.device)).contiguous(),
+                              w.scales.index_select(-2, blk).contiguous(), w.bn, w.bk)
+    raise TypeError(type(w))
+
+
+def take_in(w, lo: int, hi: int):
+    """Columns [lo, hi) (input features) of a [.., N, K] weight; lo and hi multiples of 128 for quantised formats."""
+    if isinstance(w, torch.Tensor):
+        return w[..., lo:hi].contiguous()
+    if lo % 128 or hi % 128:
+        raise ValueError("input columns of a quantised matrix are cut at multiples of 128")
+    if isinstance(w, Exl3Weight):
+        return Exl3Weight(w.trellis[..., lo // 16: hi // 16, :, :].contiguous(), w.suh[..., lo:hi].contiguous(), w.svh,
+                          w.bits, w.kind)
+    if isinstance(w, Mxfp4Weight):
+        return Mxfp4Weight(w.packed[..., lo // 2: hi // 2].contiguous(), w.scales[..., lo // 32: hi // 32].contiguous())
+    if isinstance(w, Mxfp8Weight):
+        return Mxfp8Weight(w.q[..., lo:hi].contiguous(), w.scales[..., lo // 32: hi // 32].contiguous())
+    if isinstance(w, Fp8BlockWeight):
+        return Fp8BlockWeight(w.q[..., lo:hi].contiguous(), w.scales[..., lo // w.bk: hi // w.bk].contiguous(), w.bn, w.bk)
+    raise TypeError(type(w))
+
+
+def take_experts(w, lo: int, hi: int):
+    """Experts [lo, hi) of a stacked [E, N, K] weight."""
+    if isinstance(w, torch.Tensor):
+        return w[lo:hi].contiguous()
+    if isinstance(w, Exl3Weight):
+        return Exl3Weight(w.trellis[lo:hi].contiguous(), w.suh[lo:hi].contiguous(), w.svh[lo:hi].contiguous(), w.bits, w.kind)
+    if isinstance(w, Mxfp4Weight):
+        return Mxfp4Weight(w.packed[lo:hi].contiguous(), w.scales[lo:hi].contiguous())
+    if isinstance(w, Fp8BlockWeight):
+        return Fp8BlockWeight(w.q[lo:hi].contiguous(), w.scales[lo:hi].contiguous(), w.bn, w.bk)
+    raise TypeError(type(w))
+
+
+def weight_tensors(w) -> dict:
+    """The packed tensors of a weight by field name (what a checkpoint stores)."""
+    if isinstance(w, torch.Tensor):
+        return {"weight": w}
+    if isinstance(w, Exl3Weight):
+        return {"trellis": w.trellis, "suh": w.suh, "svh": w.svh}
+    if isinstance(w, Mxfp4Weight):
+        return {"packed": w.packed, "scales": w.scales}
+    if isinstance(w, Mxfp8Weight):
+        return {"q8": w.q, "scales8": w.scales}
+    if isinstance(w, Fp8BlockWeight):
+        return {"q": w.q, "block_scales": w.scales}
+    raise TypeError(type(w))
+
+
+def weight_from_tensors(t: dict, meta: dict):
+    """Inverse of `weight_tensors`; `meta` carries the format attributes that are not tensors."""
+    if "weight" in t:
+        return t["weight"]
+    if "trellis" in t:
+        return Exl3Weight(t["trellis"], t["suh"], t["svh"], t["trellis"].shape[-1] // 16, meta.get("kind", "mul1"))
+    if "packed" in t:
+        return Mxfp4Weight(t["packed"], t["scales"])
+    if "q8" in t:
+        return Mxfp8Weight(t["q8"], t["scales8"])
+    if "q" in t:
+        return Fp8BlockWeight(t["q"], t["block_scales"], int(meta.get("bn", 128)), int(meta.get("bk", 128)))
+    raise ValueError(sorted(t))

@@ -21,7 +21,6 @@ from ..config import EngineConfig, ModelConfig
 from ..models.model import Model
 from ..models.plan import make_plan
 from ..runtime import rt
-from ..spec import sampling
 from ..spec.decoder import SeqSpec, SpecDecoder
 from ..spec.lookup import LookupIndex
 from ..utils.profile import Profiler
@@ -42,8 +41,11 @@ class _Live:
 
 
 class EngineServer:
-    def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cpu", tp=None):
+    def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cpu", tp=None,
+                 leader=None):
+        """`leader`: a `serving.replica.Leader` when other ranks replay this server's inputs and steps."""
         self.cfg, self.ecfg = cfg, ecfg or EngineConfig()
+        self.leader = leader
         e = self.ecfg
         dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
         per = max(256, e.kv_tokens // e.max_seqs // 256 * 256)
@@ -72,8 +74,12 @@ class EngineServer:
             self.watchdog = StepWatchdog(e.step_deadline_s)
 
     # ------------------------------------------------------------------------------------------ requests
-    def submit(self, msg: dict):
-        now = time.time()
+    def submit(self, msg: dict, replay: bool = False):
+        if self.leader is not None and not replay and not msg.get("stats"):
+            msg = dict(msg)
+            msg.setdefault("_t_arrive", time.time())        # followers schedule with the leader's arrival time
+            self.leader.message(msg)
+        now = float(msg.get("_t_arrive", time.time()))
         if "cancel" in msg:
             self.sched.cancel(int(msg["cancel"]))
             return
@@ -105,10 +111,15 @@ class EngineServer:
         return d
 
     # ------------------------------------------------------------------------------------------ steps
-    def step(self) -> bool:
-        """Run one unit of work.  Returns False when idle."""
+    def step(self, replay: bool = False) -> bool:
+        """Run one unit of work.  Returns False when idle.  With a leader attached the step is first marked in the op
+        log and only runs once every follower has picked the mark up (its collectives need all ranks)."""
         K = rt().Step.Kind
         disk_tokens = 0
+        if self.leader is not None and not replay:
+            if not self.sched.has_work():
+                return False
+            self.leader.step()
         st = self.sched.next(disk_tokens)
         if st.kind == K.Idle:
             return False
@@ -194,7 +205,7 @@ class EngineServer:
         self.sched.on_prefilled(slot, c1)
         if c1 == len(prompt):
             s = lv.seq
-            first = sampling.sample(logits, s.temperature, s.seed, len(prompt))
+            first = m.sample(logits, s.temperature, s.seed, len(prompt))
             s.last_token, s.hidden = first, hid[-1].clone()
             s.pending_mtp = [(hid[-1].clone(), first)]
             s.generated = [first]
@@ -337,8 +348,12 @@ class EngineServer:
                     continue
                 if not buf:
                     outbuf.pop(c, None)
+            if self.leader is not None:
+                self.leader.heartbeat()
             if not busy and not outbuf:
                 time.sleep(idle_sleep)
+        if self.leader is not None:
+            self.leader.shutdown()
         for c in conns:
             c.close()
         srv.close()

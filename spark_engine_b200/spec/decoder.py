@@ -17,7 +17,6 @@ import torch
 
 from ..models.plan import make_plan
 from . import policy as P
-from . import sampling
 from .lookup import LookupIndex
 from .tree import Node, accept, chain, parents_of
 
@@ -63,13 +62,9 @@ class MtpDrafter:
         drafts, confs = [], []
         h = m.mtp_hidden[-1]
         for i in range(depth):
-            pr = torch.softmax(lg.float(), -1)
-            if seq.temperature > 0:
-                tok = sampling.sample(lg, seq.temperature, seq.seed, L + 1 + i)
-            else:
-                tok = int(torch.argmax(lg))
+            tok = m.sample(lg, seq.temperature, seq.seed, L + 1 + i)
             drafts.append(tok)
-            confs.append(float(pr[tok]))
+            confs.append(m.token_prob(lg, tok))
             if i + 1 == depth:
                 break
             plan = make_plan([(seq.slot, [tok], L + i)], device=dev)
@@ -106,7 +101,7 @@ class SpecDecoder:
                 mp = make_plan([(slot, nxt, c0)], device=m.device, all_logits=False) if nxt else None
                 if mp is not None:
                     m.mtp_forward(mp, hid[: len(nxt)])
-        first = sampling.sample(last, temperature, seed, len(prompt))
+        first = m.sample(last, temperature, seed, len(prompt))
         seq = SeqSpec(slot, first, hid[-1].clone(), temperature=temperature, seed=seed)
         seq.pending_mtp = [(hid[-1].clone(), first)]
         seq.lookup = LookupIndex(self.lookup_n)
@@ -155,12 +150,13 @@ class SpecDecoder:
         logits = m.forward(plan, commit=False)
         hidden = m.hidden_out
         emitted, accepted_rows = [], []
+        rows_of = [(s, seg.pos0 + 1 + j) for s, seg in zip(seqs, plan.segs) for j in range(seg.n)]
+        all_preds = m.sample_rows(logits, [s.temperature for s, _ in rows_of], [s.seed for s, _ in rows_of],
+                                  [p for _, p in rows_of])
         for i, (s, d) in enumerate(zip(seqs, drafts)):
             seg = plan.segs[i]
             L = seg.pos0
-            preds = []
-            for j in range(seg.n):
-                preds.append(sampling.sample(logits[seg.r0 + j], s.temperature, s.seed, L + 1 + j))
+            preds = all_preds[seg.r0: seg.r0 + seg.n]
             budget = budgets[i] if budgets is not None else None
             path, out, stopped = accept(chain(d), preds[0], preds[1:], budget=budget, stop=stop)
             n = len(path)
@@ -213,12 +209,18 @@ class SpecDecoder:
         logits = m.forward(plan, commit=False)
         hidden = m.hidden_out
         emitted, accepted_rows = [], []
-        for i, (s, nodes) in enumerate(zip(seqs, trees)):
-            seg = plan.segs[i]
+        temps, seeds, poss = [], [], []
+        for s, seg in zip(seqs, plan.segs):
             depth = [0] * seg.n
             for j in range(1, seg.n):
                 depth[j] = depth[seg.parents[j]] + 1
-            preds = [sampling.sample(logits[seg.r0 + j], s.temperature, s.seed, seg.pos0 + 1 + depth[j]) for j in range(seg.n)]
+            temps += [s.temperature] * seg.n
+            seeds += [s.seed] * seg.n
+            poss += [seg.pos0 + 1 + d for d in depth]
+        all_preds = m.sample_rows(logits, temps, seeds, poss)
+        for i, (s, nodes) in enumerate(zip(seqs, trees)):
+            seg = plan.segs[i]
+            preds = all_preds[seg.r0: seg.r0 + seg.n]
             budget = budgets[i] if budgets is not None else None
             path, out, _ = accept(nodes, preds[0], preds[1:], budget=budget, stop=stop)
             rows = [0] + [n + 1 for n in path]

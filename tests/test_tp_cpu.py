@@ -42,13 +42,16 @@ def _worker(rank, world, port, q, name="tiny"):
     ids = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
     lg = m.forward(make_plan([(0, ids[:32], 0)]))
     toks = m.greedy(lg)
+    R = lg.shape[0]
+    sampled = m.sample_rows(lg, [0.0 if r % 3 == 0 else 0.9 for r in range(R)], [7] * R, list(range(R)))
+    prob = m.token_prob(lg[0], sampled[0])
     lg2 = m.forward(make_plan([(0, ids[32:33], 32)]))          # one decode row on top of the prefill state
     parts = [torch.empty_like(lg) for _ in range(world)]
     dist.all_gather(parts, lg)
     parts2 = [torch.empty_like(lg2) for _ in range(world)]
     dist.all_gather(parts2, lg2)
     if rank == 0:
-        q.put((torch.cat(parts, 1), toks, torch.cat(parts2, 1)))
+        q.put((torch.cat(parts, 1), toks, torch.cat(parts2, 1), sampled, prob))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -67,7 +70,7 @@ def test_tp2_logits_match_unsharded(name):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q, name)) for r in range(2)]
     for p in procs:
         p.start()
-    logits, toks, logits2 = q.get(timeout=120)
+    logits, toks, logits2, sampled, prob = q.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
@@ -81,3 +84,8 @@ def test_tp2_logits_match_unsharded(name):
     assert (logits - ref).abs().max() < 1e-4
     assert (logits2 - ref2).abs().max() < 1e-4
     assert toks.tolist() == ref.argmax(-1).tolist()
+    # Gumbel-max sampling keyed by the GLOBAL vocabulary id: the sharded head draws the single-GPU token
+    R = ref.shape[0]
+    want = ref_m.sample_rows(ref, [0.0 if r % 3 == 0 else 0.9 for r in range(R)], [7] * R, list(range(R)))
+    assert sampled == want
+    assert abs(prob - float(torch.softmax(ref[0], -1)[want[0]])) < 1e-5
