@@ -239,6 +239,8 @@ class EngineConfig:
     step_deadline_s: float = 0.0         # > 0: a watchdog aborts the process when one engine step runs longer
     pcache_dir: Optional[str] = None
     pcache_bytes: int = 64 << 30
+    host_mem_floor_gb: float = 2.0       # > 0: below this much available host memory the server sheds load
+    meminfo_path: str = ""               # where the memory guard reads MemAvailable ("" = /proc/meminfo)
     socket: str = "/tmp/spark-b200.sock"
     host: str = "127.0.0.1"
     port: int = 8000

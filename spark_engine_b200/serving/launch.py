@@ -1,9 +1,13 @@
-"""Launcher: `python -m spark_engine_b200.serving.launch serve --model <preset|config.json> [--gpus N] ...`
+"""Launcher: `python -m spark_engine_b200.serving.launch serve --model <preset> | --checkpoint DIR [--gpus N] ...`
 
-Starts one engine process per GPU (rank 0 owns the Unix socket) and the HTTP front end, waits for
-"[serve] rank0 ready" with a liveness check and a timeout, polls /health, and tears everything down on exit.
+`serve` starts one engine process per GPU and the HTTP front end.  Rank 0 owns the Unix socket and the scheduler; with
+`--gpus N > 1` the model is sharded (tensor + expert parallel) and ranks 1..N-1 replay rank 0's inputs and steps from the
+shared-memory op log (`serving/replica.py`).  The launcher waits for "[serve] rank0 ready" with a liveness check of every
+rank and a timeout, polls /health, and tears all ranks down when any of them exits (fail-stop).  Environment profiles are
+layered: built-in defaults < each `--env-file` (KEY=VALUE lines, later files win) < the caller's environment.
 `status` and `stop` act on the pid file.  Reference: engine-rs/serve/start.sh, start-glm.sh:13-33 (ready wait with
-liveness + 1200 s timeout), common.sh, glm-rank.sh (env layering) -- without ssh: all ranks live on one box.
+liveness + 1200 s timeout), common.sh, glm-rank.sh (env layering, one process per rank) -- without ssh: all ranks live
+on one box.
 """
 from __future__ import annotations
 
@@ -11,39 +15,120 @@ import argparse
 import json
 import os
 import signal
+import socket
 import subprocess
 import sys
 import time
 import urllib.request
 
+_DEFAULT_ENV = {"NCCL_NVLS_ENABLE": "0", "CUDA_DEVICE_MAX_CONNECTIONS": "8", "OMP_NUM_THREADS": "8"}
+
+
+def layered_env(files, base=None) -> dict:
+    """defaults < env files in order < `base` (the caller's environment)."""
+    env = dict(_DEFAULT_ENV)
+    for path in files or []:
+        with open(path) as f:
+            for line in f:
+                line = line.strip()
+                if not line or line.startswith("#") or "=" not in line:
+                    continue
+                k, v = line.split("=", 1)
+                env[k.strip().removeprefix("export ").strip()] = v.strip().strip('"').strip("'")
+    env.update(os.environ if base is None else base)
+    return env
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
 
 def _engine_main(a):
+    """One rank.  RANK / LOCAL_RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT / SPARK_OPLOG come from the launcher."""
     import torch
     from ..config import EngineConfig, get_model_config
     from ..models.build import build_random_model
     from ..models.weights import init_weights, to_device
     from .worker import EngineServer
-    cfg = get_model_config(a.model)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = a.device
+    if a.checkpoint:
+        from ..models.checkpoint import load_config
+        cfg = load_config(a.checkpoint)
+    else:
+        cfg = get_model_config(a.model)
     if a.layers:
         cfg.n_layers = a.layers
         cfg.layer_types = cfg.layer_types[: a.layers]
     ecfg = EngineConfig.from_env(max_seqs=a.max_seqs, kv_tokens=a.kv_tokens, prefill_chunk=a.prefill_chunk, spec=a.spec,
-                                 spec_depth=a.spec_depth, pcache_dir=a.pcache_dir, socket=a.socket, profile=a.profile)
-    dev = a.device
-    if dev == "cpu":
+                                 spec_depth=a.spec_depth, pcache_dir=a.pcache_dir, socket=a.socket, profile=a.profile,
+                                 tp=world)
+    tp = None
+    if dev != "cpu":
+        torch.cuda.set_device(local)
+        dev = f"cuda:{local}"
+    if world > 1:
+        import torch.distributed as dist
+        from datetime import timedelta
+        if dev == "cpu":
+            from ..parallel.tp import CpuTP
+            dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=120))
+            tp = CpuTP()
+        else:
+            from ..parallel import symm
+            from ..parallel.tp import DeviceTP
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev),
+                                    timeout=timedelta(seconds=120))
+            tp = DeviceTP(symm.Arena(1 << 30, wait_ms=ecfg.comm_wait_ms), cfg.hidden, rows_cap=1024)
+    if a.checkpoint:
+        from ..models.checkpoint import load_checkpoint
+        _, W = load_checkpoint(a.checkpoint, dev, tp=(rank, world), cfg=cfg)
+    elif dev == "cpu":
         W = init_weights(cfg, seed=a.seed)
+        if world > 1:
+            from ..parallel.tp import shard_weights
+            W = shard_weights(W, cfg, rank, world)
+    elif cfg.weight_format != "dense" or cfg.hidden > 1024:
+        W = build_random_model(cfg, dev, seed=a.seed, tp=(rank, world))
     else:
-        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-        W = build_random_model(cfg, dev, seed=a.seed) if cfg.weight_format != "dense" or cfg.hidden > 1024 \
-            else to_device(init_weights(cfg, seed=a.seed), dev)
-    EngineServer(cfg, W, ecfg, device=dev).serve_forever(a.socket)
+        W = init_weights(cfg, seed=a.seed)
+        if world > 1:
+            from ..parallel.tp import shard_weights
+            W = shard_weights(W, cfg, rank, world)
+        W = to_device(W, dev)
+    oplog = os.environ.get("SPARK_OPLOG", f"/spark_b200_oplog_{os.getppid()}")
+    if world == 1:
+        EngineServer(cfg, W, ecfg, device=dev).serve_forever(a.socket)
+        return 0
+    import torch.distributed as dist
+    from .replica import Follower, Leader, LeaderLost
+    if rank == 0:
+        leader = Leader(oplog, world - 1, ack_timeout_ms=a.ack_timeout_ms)
+        dist.barrier()
+        EngineServer(cfg, W, ecfg, device=dev, tp=tp, leader=leader).serve_forever(a.socket)
+        return 0
+    dist.barrier()
+    srv = EngineServer(cfg, W, ecfg, device=dev, tp=tp)
+    print(f"[serve] rank{rank} ready", flush=True)
+    try:
+        Follower(oplog, rank - 1, world - 1, deadline_ms=a.ack_timeout_ms).run(srv)
+    except LeaderLost as e:
+        print(f"[serve] rank{rank}: {e}", flush=True)
+        return 3
+    return 0
 
 
-def _wait_ready(proc, log_path, timeout):
+def _wait_ready(procs, log_path, timeout):
     t0 = time.time()
     while time.time() - t0 < timeout:
-        if proc.poll() is not None:
-            raise RuntimeError(f"engine exited with {proc.returncode} before it was ready; see {log_path}")
+        for i, p in enumerate(procs):
+            if p.poll() is not None:
+                raise RuntimeError(f"engine rank {i} exited with {p.returncode} before the server was ready; see {log_path}")
         try:
             if "[serve] rank0 ready" in open(log_path).read():
                 return
@@ -53,29 +138,45 @@ def _wait_ready(proc, log_path, timeout):
     raise TimeoutError("engine did not become ready in time")
 
 
+def spawn_ranks(a, env):
+    """One engine process per rank; returns (processes, rank-0 log path)."""
+    n = max(1, a.gpus)
+    port, oplog = _free_port(), f"/spark_b200_oplog_{os.getpid()}"
+    procs = []
+    for r in range(n):
+        e = dict(env)
+        e.update(RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(n), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                 SPARK_OPLOG=oplog)
+        log = os.path.join(a.log_dir, f"spark-b200-rank{r}.log")
+        procs.append(subprocess.Popen([sys.executable, "-m", "spark_engine_b200.serving.launch", "engine"] + a.passthrough,
+                                      stdout=open(log, "w"), stderr=subprocess.STDOUT, env=e))
+    return procs, os.path.join(a.log_dir, "spark-b200-rank0.log")
+
+
 def cmd_serve(a):
-    log = f"/tmp/spark-b200-rank0.log"
-    env = dict(os.environ)
-    eng = subprocess.Popen([sys.executable, "-m", "spark_engine_b200.serving.launch", "engine"] + a.passthrough,
-                           stdout=open(log, "w"), stderr=subprocess.STDOUT, env=env)
+    env = layered_env(a.env_file)
+    procs, log = spawn_ranks(a, env)
+    front = None
     try:
-        _wait_ready(eng, log, a.ready_timeout)
+        _wait_ready(procs, log, a.ready_timeout)
         front = subprocess.Popen([sys.executable, "-m", "spark_engine_b200.serving.openai_server", "--socket", a.socket,
-                                  "--host", a.host, "--port", str(a.port), "--model-name", a.model])
+                                  "--host", a.host, "--port", str(a.port), "--model-name", a.checkpoint or a.model], env=env)
         with open(a.pidfile, "w") as f:
-            json.dump({"engine": eng.pid, "front": front.pid}, f)
+            json.dump({**{f"engine{i}": p.pid for i, p in enumerate(procs)}, "front": front.pid}, f)
         for _ in range(100):
             try:
                 if urllib.request.urlopen(f"http://{a.host}:{a.port}/health", timeout=1).status == 200:
                     break
             except Exception:
                 time.sleep(0.2)
-        print(f"serving {a.model} on http://{a.host}:{a.port}", flush=True)
-        front.wait()
+        print(f"serving {a.checkpoint or a.model} on http://{a.host}:{a.port} with {len(procs)} rank(s)", flush=True)
+        while front.poll() is None and all(p.poll() is None for p in procs):   # any rank gone = the whole server stops
+            time.sleep(0.5)
+        return 0 if front.poll() is not None else 1
     finally:
-        for p in (eng,):
+        for p in procs + ([front] if front else []):
             if p.poll() is None:
-                p.send_signal(signal.SIGTERM)
+                p.send_signal(signal.SIGTERM)          # exact children only
 
 
 def cmd_status(a):
@@ -107,6 +208,11 @@ def main():
     ap = argparse.ArgumentParser(prog="spark-b200")
     ap.add_argument("cmd", choices=["serve", "engine", "status", "stop"])
     ap.add_argument("--model", default="tiny-hybrid")
+    ap.add_argument("--checkpoint", default=None, help="directory written by models.checkpoint.save_checkpoint")
+    ap.add_argument("--gpus", type=int, default=1, help="ranks of one box; the model is sharded over them")
+    ap.add_argument("--env-file", action="append", default=[], help="KEY=VALUE profile; repeatable, later files win")
+    ap.add_argument("--log-dir", default="/tmp")
+    ap.add_argument("--ack-timeout-ms", type=int, default=30000, help="op-log deadline between leader and followers")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--socket", default="/tmp/spark-b200.sock")

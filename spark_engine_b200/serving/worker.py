@@ -69,12 +69,36 @@ class EngineServer:
         self.out: List[dict] = []
         self.shutdown = False
         self.watchdog = None
+        # host memory guard (native watch thread): while available host memory is below the floor new requests are
+        # refused, the host checkpoint library is halved and malloc arenas are trimmed, so the process sheds load
+        # before the kernel's OOM killer picks it.  Reference: engine-rs/src/ds41/mem.rs:48-163, host_memory.rs:22-104.
+        self.memwatch, self._mem_fired, self.mem_low_until = None, 0, 0.0
+        if e.host_mem_floor_gb > 0:
+            self.memwatch = rt().MemWatch(int(e.host_mem_floor_gb * (1 << 30)), 250, None, e.meminfo_path)
+            self.totals["host_mem_low_events"] = 0
         if e.step_deadline_s > 0:                 # fail-stop on a stuck step: the process is aborted, never the device
             from ..parallel.faults import StepWatchdog
             self.watchdog = StepWatchdog(e.step_deadline_s)
 
     # ------------------------------------------------------------------------------------------ requests
+    def _host_memory_low(self) -> bool:
+        """Polls the guard: a new firing sheds host memory once and opens a 2 s window in which requests are refused."""
+        if self.memwatch is None:
+            return False
+        f = self.memwatch.fired()
+        if f != self._mem_fired:
+            self._mem_fired = f
+            self.mem_low_until = time.monotonic() + 2.0
+            self.totals["host_mem_low_events"] += 1
+            while len(self.library.items) > max(1, self.library.max // 2):
+                self.library.items.popitem(last=False)
+            rt().trim_host_memory()
+        return time.monotonic() < self.mem_low_until
+
     def submit(self, msg: dict, replay: bool = False):
+        if not replay and "prompt_ids" in msg and self._host_memory_low():
+            msg = dict(msg)
+            msg["_refuse"] = "host memory is low; retry later"   # the leader decides, followers replay the decision
         if self.leader is not None and not replay and not msg.get("stats"):
             msg = dict(msg)
             msg.setdefault("_t_arrive", time.time())        # followers schedule with the leader's arrival time
@@ -89,7 +113,7 @@ class EngineServer:
         if msg.get("stats"):
             self.out.append({"id": msg.get("id"), "stats": self.stats()})
             return
-        err = proto.validate_request(msg, self.cfg.vocab, self.slot_tokens)
+        err = msg.get("_refuse") or proto.validate_request(msg, self.cfg.vocab, self.slot_tokens)
         if err:
             self.out.append({"id": msg.get("id"), "error": err})
             return
@@ -307,7 +331,7 @@ class EngineServer:
                 if not data:                          # front end gone: cancel everything it owns
                     for rid, c in list(owner.items()):
                         if c is s:
-                            self.sched.cancel(rid)
+                            self.submit({"cancel": rid})      # through submit: followers replay the cancellation
                             owner.pop(rid, None)
                     conns.pop(s, None)
                     s.close()
