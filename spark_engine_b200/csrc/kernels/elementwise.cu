@@ -197,6 +197,53 @@ static __global__ void gumbel_perturb_kernel(float* __restrict__ x, int V, int l
   }
 }
 
+// softmax(logits)[token] for one row from vocabulary slices: every rank reduces its slice to (max, sum exp(l - max)) and
+// the slice that holds the token contributes its logit; `final` combines the per-rank pairs.  Used for the drafter's
+// confidence (the draft-length policies read it), so all ranks must get the same number: the per-rank pairs travel
+// through the rank-ordered all-reduce.  ms: [R, ld] with rank r's pair at columns 2r, 2r+1; lt: [R] (zero unless owned).
+// Reference: engine-rs/src/sampling.rs:120-170 (confidence of the sampled draft), shim/draft_selector.cu:14.
+static __global__ void token_prob_part_kernel(const float* __restrict__ logits, int V, int ldx, const int* __restrict__ ids,
+                                              int off, int rank, float* __restrict__ ms, int ld, float* __restrict__ lt) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, t = threadIdx.x;
+  const float* x = logits + (size_t)r * ldx;
+  __shared__ float red[32];
+  float m = -INFINITY;
+  for (int v = t; v < V; v += blockDim.x) m = fmaxf(m, x[v]);
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
+  if ((t & 31) == 0) red[t >> 5] = m;
+  __syncthreads();
+  m = red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+  __syncthreads();
+  float s = 0.f;
+  for (int v = t; v < V; v += blockDim.x) s += __expf(x[v] - m);
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(~0u, s, o);
+  if ((t & 31) == 0) red[t >> 5] = s;
+  __syncthreads();
+  if (t == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+    ms[(size_t)r * ld + 2 * rank] = m;
+    ms[(size_t)r * ld + 2 * rank + 1] = tot;
+    const int id = ids[r] - off;
+    lt[r] = (id >= 0 && id < V) ? x[id] : 0.f;
+  }
+}
+static __global__ void token_prob_final_kernel(const float* __restrict__ ms, int ld, int world, const float* __restrict__ lt,
+                                               float* __restrict__ out, int R) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  float M = -INFINITY;
+  for (int k = 0; k < world; ++k) M = fmaxf(M, ms[(size_t)r * ld + 2 * k]);
+  float S = 0.f;
+  for (int k = 0; k < world; ++k) S += ms[(size_t)r * ld + 2 * k + 1] * __expf(ms[(size_t)r * ld + 2 * k] - M);
+  out[r] = __expf(lt[r] - M) / S;
+}
+
 extern "C" void spark_add_rmsnorm(const void* delta, int delta_f32, float* res, const float* w, void* out, int R, int H,
                                   float eps, int one_plus, cudaStream_t s) {
   if (R <= 0) return;
@@ -243,6 +290,19 @@ extern "C" int spark_gumbel_perturb(float* x, int R, int V, int ldx, const float
   const int bx = V >= 65536 ? 32 : (V >= 4096 ? 8 : 1);
   gumbel_perturb_kernel<<<dim3(bx, R), 256, 0, s>>>(x, V, ldx, temp, seed, pos, off);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+extern "C" int spark_token_prob_part(const float* logits, int R, int V, int ldx, const int* ids, int off, int rank, float* ms,
+                                     int ld, float* lt, cudaStream_t s) {
+  if (R <= 0) return 0;
+  const cudaError_t e = spark_launch_pdl(token_prob_part_kernel, dim3(R), dim3(1024), 0, s, dim3(1, 1, 1), logits, V, ldx, ids, off,
+                                         rank, ms, ld, lt);
+  return e == cudaSuccess ? 0 : -4;
+}
+extern "C" int spark_token_prob_final(const float* ms, int ld, int world, const float* lt, float* out, int R, cudaStream_t s) {
+  if (R <= 0) return 0;
+  const cudaError_t e = spark_launch_pdl(token_prob_final_kernel, dim3((R + 63) / 64), dim3(64), 0, s, dim3(1, 1, 1), ms, ld, world,
+                                         lt, out, R);
+  return e == cudaSuccess ? 0 : -4;
 }
 extern "C" void spark_add(const void* delta, int delta_f32, float* res, long n, cudaStream_t s) {
   if (n <= 0) return;

@@ -739,18 +739,27 @@ class Model:
     @torch.no_grad()
     def mtp_forward(self, plan: Plan, hidden: torch.Tensor):
         """Draft logits: row i combines embed(plan.ids[i]) (the NEXT token) with `hidden[i]` (target
-        hidden of the previous position).  plan positions index the drafter's own KV cache."""
-        cfg, M = self.cfg, self.W["mtp"]
+        hidden of the previous position).  plan positions index the drafter's own KV cache.  Blocks run like the
+        target's: the residual stream stays fp32 on the device and every residual update is one fused
+        (all-reduce +) add + RMSNorm."""
+        cfg, M, tp = self.cfg, self.W["mtp"], self.tp
         e = ops.rmsnorm(ops.embed(self.W["embed"], plan.ids, self.dtype), M["norm_e"], cfg.norm_eps)
-        hh = ops.rmsnorm(hidden.to(self.dtype), M["norm_h"], cfg.norm_eps)
+        hh = ops.rmsnorm(hidden if hidden.is_cuda else hidden.to(self.dtype), M["norm_h"], cfg.norm_eps)
         X = ops.linear(torch.cat((e, hh), -1), M["fc"])
+        if X.is_cuda:
+            X = X.float()
+        deferred = plan.rows <= 16 and X.is_cuda and (tp is None or hasattr(tp, "argmax"))
+        pend = None
         for lw, mix, mlp in self.mtp_layers:
-            h, X = ops.add_rmsnorm(None, X, lw["in_norm"], cfg.norm_eps)
+            h, X = ops.add_rmsnorm(pend, X, lw["in_norm"], cfg.norm_eps, tp)
             a = mix.forward(h, plan, self.mtp_seqs(), True)
-            h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps)
-            X = ops.residual_add(X, mlp.forward(h))
+            h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
+            pend = mlp.forward(h, defer=deferred)
+        hn, X = ops.add_rmsnorm(pend, X, M["final_norm"], cfg.norm_eps, tp)
         self.mtp_hidden = X
-        return ops.lm_head(ops.rmsnorm(X, M["final_norm"], cfg.norm_eps)[plan.logit_rows], self.W["lm_head"])
+        if plan.logit_rows.shape[0] != hn.shape[0] or getattr(plan, "gather_logit_rows", False):
+            hn = hn[plan.logit_rows]
+        return ops.lm_head(hn, self.W["lm_head"])
 
     def mtp_seqs(self):
         return self.seqs

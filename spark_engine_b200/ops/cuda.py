@@ -38,6 +38,8 @@ _SIGS = {
     "spark_swiglu": [vp, vp, i32, i32, f32, vp],
     "spark_argmax": [vp, i32, i32, vp, vp, vp, vp, vp],
     "spark_gumbel_perturb": [vp, i32, i32, i32, vp, vp, vp, i32, vp],
+    "spark_token_prob_part": [vp, i32, i32, i32, vp, i32, i32, vp, i32, vp, vp],
+    "spark_token_prob_final": [vp, i32, i32, vp, vp, i32, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
@@ -434,6 +436,25 @@ def gumbel_perturb(logits, temps, seeds, positions, offset):
     check(lib().spark_gumbel_perturb(P(logits), R, V, logits.stride(0), P(temps), P(seeds), P(positions), int(offset), stream()),
           "gumbel_perturb")
     return logits
+
+
+def token_prob(logits, ids32, tp=None):
+    """softmax(logits)[ids] per row -> fp32 [R]; `logits` is this rank's vocabulary slice under `tp` (the per-rank
+    (max, sum) pairs and the owner's logit go through the rank-ordered all-reduce, so every rank gets the same bits)."""
+    R, V = logits.shape
+    rank, world = (tp.rank, tp.world) if tp is not None else (0, 1)
+    assert world <= 8 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    ms = torch.zeros(R, 16, dtype=torch.float32, device=logits.device)
+    lt = torch.empty(R, dtype=torch.float32, device=logits.device)
+    check(lib().spark_token_prob_part(P(logits), R, V, logits.stride(0), P(ids32), rank * V, rank, P(ms), 16, P(lt), stream()),
+          "token_prob_part")
+    lt1 = lt
+    if world > 1:
+        ms = tp.allreduce(ms).clone()          # the packet channel's output buffer is reused by the next call
+        lt1 = tp.allreduce(lt.view(R, 1))[:, 0].contiguous()
+    out = torch.empty(R, dtype=torch.float32, device=logits.device)
+    check(lib().spark_token_prob_final(P(ms), ms.stride(0), world, P(lt1), P(out), R, stream()), "token_prob_final")
+    return out
 
 
 def gather_rows(src, idx32):

@@ -18,7 +18,8 @@ import torch
 from .. import ops
 from ..config import EngineConfig, ModelConfig
 from ..models.model import Model
-from ..models.plan import Plan, Segment, make_plan, plan_device_arrays
+from ..models.plan import make_plan
+from .graphs import RoundGraph, ctx_bucket
 
 
 @dataclass
@@ -31,124 +32,6 @@ class GenStats:
     accepted_drafts: int = 0
 
 
-class _DecodeGraph:
-    """Captured forward over a fixed row layout; refreshed through a packed int32 staging buffer."""
-
-    def __init__(self, engine: "LLMEngine", slots: Sequence[int], rows_per_seq: int, ctx_bucket: int):
-        self.engine, self.slots, self.k = engine, list(slots), rows_per_seq
-        m = engine.model
-        dev = m.device
-        n = len(slots)
-        R = n * rows_per_seq
-        self.R = R
-        # packed host staging: ids[R] pos[R] row_pos0[R] seg[n*4]  + row_kv handled as int64 separately
-        self.host = torch.zeros(3 * R + 4 * n, dtype=torch.int32).pin_memory()
-        self.dev = torch.zeros(3 * R + 4 * n, dtype=torch.int32, device=dev)
-        self.row_kv = torch.zeros(R, dtype=torch.int64, device=dev)
-        self.out_host = torch.zeros(R, dtype=torch.int32).pin_memory()
-        segs = [Segment(s, i * rows_per_seq, rows_per_seq, 0) for i, s in enumerate(self.slots)]
-        self.plan = Plan(ids=torch.zeros(R, dtype=torch.long, device=dev), pos=torch.zeros(R, dtype=torch.long, device=dev),
-                         segs=segs, logit_rows=torch.arange(R, device=dev))
-        d = {"ids32": self.dev[:R], "pos32": self.dev[R:2 * R], "row_pos0": self.dev[2 * R:3 * R],
-             "seg": self.dev[3 * R:].view(n, 4), "row_kv": self.row_kv, "max_ctx": ctx_bucket,
-             "row_slot": torch.tensor([s for s in self.slots for _ in range(rows_per_seq)], dtype=torch.int32, device=dev),
-             "row_j": torch.tensor(list(range(rows_per_seq)) * n, dtype=torch.int32, device=dev),
-             "row_r0": torch.tensor([i * rows_per_seq for i in range(n) for _ in range(rows_per_seq)], dtype=torch.int32,
-                                    device=dev)}
-        # hashed n-gram layers: the row ids of each position come from the token history, which lives on the host
-        self.ng_host = None
-        if engine.cfg.ngram_layers:
-            self.ng_host = torch.zeros(R, engine.cfg.ngram_heads, dtype=torch.int64).pin_memory()
-            d["ngram_rows"] = torch.zeros(R, engine.cfg.ngram_heads, dtype=torch.int64, device=dev)
-        self.plan.dev = d
-        self.graph = None
-        self.graph_fed = None          # the same round followed by the device-side feedback of the sampled ids
-        self.out_ids = None
-        self.logits = None
-        self.hidden = None
-
-    def stage(self, ids: List[List[int]], pos0: List[int]):
-        R, n, k = self.R, len(self.slots), self.k
-        h = self.host
-        m = self.engine.model
-        for i, s in enumerate(self.slots):
-            for j in range(k):
-                r = i * k + j
-                h[r] = ids[i][j]
-                h[R + r] = pos0[i] + j
-                h[2 * R + r] = pos0[i]
-            h[3 * R + 4 * i + 0] = s
-            h[3 * R + 4 * i + 1] = i * k
-            h[3 * R + 4 * i + 2] = k
-            h[3 * R + 4 * i + 3] = pos0[i]
-            self.plan.segs[i].pos0 = pos0[i]
-        self.dev.copy_(h, non_blocking=True)
-        if self.ng_host is not None:
-            from ..models.ngram import chain_row_ids
-            for i, s in enumerate(self.slots):
-                self.ng_host[i * k:(i + 1) * k] = torch.tensor(chain_row_ids(m, s, pos0[i], ids[i]), dtype=torch.int64)
-            self.plan.dev["ngram_rows"].copy_(self.ng_host, non_blocking=True)
-
-    def set_kv(self):
-        m = self.engine.model
-        kv = torch.tensor([m.seqs[s].kv_base for s in self.slots for _ in range(self.k)], dtype=torch.int64)
-        self.row_kv.copy_(kv)
-
-    def run(self, commit: bool):
-        m = self.engine.model
-        if self.graph is None:
-            self.set_kv()
-            # eager warm-up sizes every persistent scratch buffer, then capture
-            from ..ops import cuda as cu
-            # (warm-up runs without commit: linear-attention state is written exactly once, by the replay)
-            n0 = cu.launch_count()
-            self._body(False)
-            self.launches = cu.launch_count() - n0
-            m._pending_plan = None
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._body(commit)
-            cu.add_launches(-self.launches)       # the capture pass launched nothing
-            self.graph = g
-        self.replay()
-        self.out_host.copy_(self.out_ids, non_blocking=True)
-
-    def replay(self):
-        from ..ops import cuda as cu
-        self.graph.replay()
-        cu.add_launches(self.launches)
-
-    def replay_fed(self):
-        """Replay the round and feed its sampled ids back on the device: ids <- sampled, every position + 1.  The next
-        replay is then the next decode step without any host work in between (one row per sequence, no hashed
-        n-gram layers: their row ids come from the host)."""
-        from ..ops import cuda as cu
-        assert self.k == 1 and self.ng_host is None
-        if self.graph_fed is None:
-            if self.graph is None:
-                raise RuntimeError("run() the round once before device-fed replays")
-            m = self.engine.model
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._body(True)
-                cu.check(cu.lib().spark_decode_advance(cu.P(self.dev), cu.P(self.out_ids), len(self.slots), cu.stream()),
-                         "spark_decode_advance")
-            cu.add_launches(-(self.launches + 1))
-            self.graph_fed = g
-        self.graph_fed.replay()
-        cu.add_launches(self.launches + 1)
-
-    def _body(self, commit: bool):
-        m = self.engine.model
-        self.plan.ids = self.plan.dev["ids32"]
-        logits = m.forward(self.plan, commit=commit, graph_mode=True)
-        self.logits = logits
-        self.hidden = m.hidden_out
-        self.out_ids = m.greedy(logits)
-
-
 class LLMEngine:
     def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cuda",
                  max_seqs: int = 4, kv_tokens_per_seq: int = 4096, tp=None):
@@ -157,7 +40,7 @@ class LLMEngine:
         self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=max_seqs,
                            kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
-        self.graphs: Dict[tuple, _DecodeGraph] = {}
+        self.graphs: Dict[tuple, RoundGraph] = {}
         # decode rounds are captured when every layer runs on capturable kernels: hashed n-gram layers qualify when
         # their table is resident on the device (row ids are staged by the host, the gather is captured); a
         # host-streamed table goes through host-side gathers and runs eagerly
@@ -186,10 +69,7 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ decode
     def _ctx_bucket(self, max_ctx: int) -> int:
-        b = 256
-        while b < max_ctx:
-            b *= 2
-        return b
+        return ctx_bucket(max_ctx)
 
     @torch.no_grad()
     def decode_round(self, slots: Sequence[int], ids: Sequence[int]) -> List[int]:
@@ -204,7 +84,7 @@ class LLMEngine:
         key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + 1))
         g = self.graphs.get(key)
         if g is None:
-            g = self.graphs[key] = _DecodeGraph(self, slots, 1, key[2])
+            g = self.graphs[key] = RoundGraph(self.model, slots, 1, key[2])
         g.stage([[t] for t in ids], pos0)
         g.run(commit=True)
         torch.cuda.current_stream().synchronize()
@@ -242,7 +122,7 @@ class LLMEngine:
         key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + steps))
         g = self.graphs.get(key)
         if g is None:
-            g = self.graphs[key] = _DecodeGraph(self, slots, 1, key[2])
+            g = self.graphs[key] = RoundGraph(self.model, slots, 1, key[2])
         g.stage([[t] for t in ids], pos0)
         ring = torch.empty(steps, len(slots), dtype=torch.int32).pin_memory()
         first = 0

@@ -58,7 +58,8 @@ class EngineServer:
         if e.spec == "lookup":
             drafter = "lookup"
         self.spec = SpecDecoder(self.model, drafter, depth=e.spec_depth if e.spec != "none" else 0,
-                                policy={"theta": "theta", "tau": "tau", "rate": "rate"}.get(e.spec_policy, "all"))
+                                policy={"theta": "theta", "tau": "tau", "rate": "rate"}.get(e.spec_policy, "all"),
+                                graphs=e.cuda_graphs)
         self.library = CheckpointLibrary(8)
         self.disk = DiskPrefixCache(e.pcache_dir, [cfg.name, cfg.to_json(), e.numerics], e.pcache_bytes) if e.pcache_dir else None
         self.live: Dict[int, _Live] = {}

@@ -75,8 +75,16 @@ class MtpDrafter:
 
 class SpecDecoder:
     def __init__(self, model, drafter="mtp", depth: int = 3, policy: str = "all", theta: float = 0.3, tau: float = 0.3,
-                 cost: Optional[P.CostModel] = None, max_rows: int = 64, lookup_n: int = 3):
+                 cost: Optional[P.CostModel] = None, max_rows: int = 64, lookup_n: int = 3, graphs: bool = False):
+        """`graphs`: replay captured CUDA graphs for the drafter chain, the verify forward and the commit (chain
+        rounds on the device); tree rounds and host-side drafters' proposals stay eager."""
         self.m = model
+        self.graphs = None
+        if graphs and model.device.type == "cuda":
+            capturable = not model.cfg.ngram_layers or model.W["ngram_table"].device.type == "cuda"
+            if capturable and model.cfg.hc_kind == "none":
+                from ..serving.graphs import SpecGraphs
+                self.graphs = SpecGraphs(model)
         self.depth, self.policy, self.theta, self.tau = depth, policy, theta, tau
         self.cost = cost or P.CostModel()
         self.max_rows = max_rows
@@ -132,31 +140,67 @@ class SpecDecoder:
         return min(len(confs), self.depth)
 
     # ---------------------------------------------------------------------------------------------
+    def _propose_graph(self, seqs: List[SeqSpec], L: List[int]):
+        """All sequences' MTP chains in one captured replay; same proposals as `_draft` one by one."""
+        m, k = self.m, 1 + self.depth
+        g = self.graphs.mtp_graph([s.slot for s in seqs], k, self.depth, max(L) + self.depth + 1)
+        g.stage([[t for _, t in s.pending_mtp] for s in seqs], [[h for h, _ in s.pending_mtp] for s in seqs], L,
+                [s.temperature for s in seqs], [s.seed for s in seqs])
+        g.run()
+        torch.cuda.current_stream().synchronize()
+        drafts, confs = g.result()
+        out = []
+        for s, d, c in zip(seqs, drafts, confs):
+            s.pending_mtp = []
+            copy = s.lookup.propose(self.depth) if s.lookup is not None else []
+            out.append((copy, [0.9] * len(copy)) if len(copy) > len(d) else (d, c))
+        return out
+
     @torch.no_grad()
     def round(self, seqs: List[SeqSpec], budgets: Optional[List[int]] = None, stop: Sequence[int] = ()) -> List[List[int]]:
         """One speculative round over all given sequences.  Returns the tokens emitted per sequence."""
         m = self.m
+        L = [m.seqs[s.slot].length for s in seqs]
+        k_graph = 1 + self.depth
+        use_g = (self.graphs is not None and len(seqs) * k_graph <= 16
+                 and all(l + k_graph + 1 <= m.seqs[s.slot].kv_cap for s, l in zip(seqs, L)))
+        if use_g and self.depth > 0 and isinstance(self.drafter, MtpDrafter) and \
+                all(1 <= len(s.pending_mtp) <= k_graph for s in seqs):
+            proposals = self._propose_graph(seqs, L)
+        else:
+            proposals = [self._draft(s, self.depth) for s in seqs]
         drafts, draft_confs = [], []
-        for s in seqs:
-            d, c = self._draft(s, self.depth)
+        for s, (d, c) in zip(seqs, proposals):
             k = self._choose(s, c, len(seqs), sum(1 + len(x) for x in drafts))
-            drafts.append(d[:k])
+            drafts.append(list(d[:k]))
             draft_confs.append(list(c[:k]))
-        items = []
-        for s, d in zip(seqs, drafts):
-            L = m.seqs[s.slot].length
-            items.append((s.slot, [s.last_token] + d, L))
-        plan = make_plan(items, device=m.device)
-        logits = m.forward(plan, commit=False)
-        hidden = m.hidden_out
+        toks = [[s.last_token] + d for s, d in zip(seqs, drafts)]
+        temps, seeds = [s.temperature for s in seqs], [s.seed for s in seqs]
+        if use_g and max(len(t) for t in toks) <= k_graph:
+            # captured verify: every sequence padded to the layout's rows; the commit replays device-side counts
+            k = k_graph if any(drafts) else 1
+            vg = self.graphs.round_graph([s.slot for s in seqs], k, max(L) + k)
+            vg.stage(toks, L, temps, seeds)
+            vg.run(commit=(k == 1))
+            torch.cuda.current_stream().synchronize()
+            flat = vg.out_host.tolist()
+            all_preds = [flat[i * k: i * k + len(t)] for i, t in enumerate(toks)]
+            hidden = vg.hidden.clone()                   # the next replay overwrites the graph's buffer
+            row0 = [i * k for i in range(len(seqs))]
+            plan = None
+        else:
+            vg = None
+            plan = make_plan([(s.slot, t, l) for s, t, l in zip(seqs, toks, L)], device=m.device)
+            logits = m.forward(plan, commit=False)
+            hidden = m.hidden_out
+            rows_of = [(s, seg.pos0 + 1 + j) for s, seg in zip(seqs, plan.segs) for j in range(seg.n)]
+            flat = m.sample_rows(logits, [s.temperature for s, _ in rows_of], [s.seed for s, _ in rows_of],
+                                 [p for _, p in rows_of])
+            all_preds = [flat[seg.r0: seg.r0 + seg.n] for seg in plan.segs]
+            row0 = [seg.r0 for seg in plan.segs]
         emitted, accepted_rows = [], []
-        rows_of = [(s, seg.pos0 + 1 + j) for s, seg in zip(seqs, plan.segs) for j in range(seg.n)]
-        all_preds = m.sample_rows(logits, [s.temperature for s, _ in rows_of], [s.seed for s, _ in rows_of],
-                                  [p for _, p in rows_of])
         for i, (s, d) in enumerate(zip(seqs, drafts)):
-            seg = plan.segs[i]
-            L = seg.pos0
-            preds = all_preds[seg.r0: seg.r0 + seg.n]
+            preds = all_preds[i]
             budget = budgets[i] if budgets is not None else None
             path, out, stopped = accept(chain(d), preds[0], preds[1:], budget=budget, stop=stop)
             n = len(path)
@@ -172,19 +216,24 @@ class SpecDecoder:
             s.drafted += len(d)
             s.accepted += n
             emitted.append(out)
-        m.commit(accepted_rows)
+        if vg is None:
+            m.commit(accepted_rows)
+        else:
+            if vg.k > 1:
+                vg.commit_rows([len(r) for r in accepted_rows])
+            for s, l, rows in zip(seqs, L, accepted_rows):
+                m.seqs[s.slot].length = l + len(rows)
         for i, (s, out) in enumerate(zip(seqs, emitted)):
-            seg, rows = plan.segs[i], accepted_rows[i]
-            toks_in = [s.last_token] + drafts[i]
+            r0, rows = row0[i], accepted_rows[i]
             # MTP catch-up inputs: (hidden of committed row j, the token that follows it)
             new_pairs = []
             for j in rows:
                 nxt = out[j] if j < len(out) else None
                 if nxt is not None:
-                    new_pairs.append((hidden[seg.r0 + j].clone(), nxt))
+                    new_pairs.append((hidden[r0 + j] if vg is not None else hidden[r0 + j].clone(), nxt))
             s.pending_mtp = new_pairs
             s.last_token = out[-1]
-            s.hidden = hidden[seg.r0 + rows[-1]].clone()
+            s.hidden = hidden[r0 + rows[-1]] if vg is not None else hidden[r0 + rows[-1]].clone()
             s.generated.extend(out)
             if s.lookup is not None:
                 s.lookup.extend(out)

@@ -1,0 +1,79 @@
+"""Speculative rounds through captured CUDA graphs on the device: the drafter chain, the padded verify forward and the
+commit with device-side accepted counts must emit exactly the tokens of the eager rounds and of plain greedy decoding."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from spark_engine_b200.config import tiny_hybrid
+from spark_engine_b200.models.model import Model
+from spark_engine_b200.models.weights import init_weights, to_device
+from spark_engine_b200.spec.decoder import SpecDecoder
+
+
+def _model(n_slots=2):
+    cfg = tiny_hybrid()
+    cfg.mtp_layers, cfg.mtp_depth = 1, 3
+    W = to_device(init_weights(cfg, seed=0), "cuda")
+    return cfg, W, Model(cfg, W, device="cuda", dtype=torch.bfloat16, n_slots=n_slots, kv_tokens=512 * n_slots)
+
+
+def _greedy(cfg, W, prompts, n):
+    m = Model(cfg, W, device="cuda", dtype=torch.bfloat16, n_slots=len(prompts), kv_tokens=512 * len(prompts))
+    return SpecDecoder(m, lambda s, d: ([], []), depth=0).generate(prompts, n)
+
+
+def test_mtp_chain_graphs_equal_eager_and_greedy():
+    cfg, W, m = _model()
+    g = torch.Generator().manual_seed(3)
+    prompts = torch.randint(0, cfg.vocab, (2, 24), generator=g).tolist()
+    ref = _greedy(cfg, W, prompts, 14)
+    eager = SpecDecoder(m, "mtp", depth=3).generate(prompts, 14)
+    cfg2, W2, m2 = _model()
+    sd = SpecDecoder(m2, "mtp", depth=3, graphs=True)
+    got = sd.generate(prompts, 14)
+    assert sd.graphs is not None and sd.graphs.rounds and sd.graphs.mtp     # the captured path actually ran
+    assert got == eager == ref
+
+
+@pytest.mark.parametrize("mode", ["perfect", "half", "wrong"])
+def test_verify_and_commit_graphs_with_known_drafts(mode):
+    """Drafts with a known acceptance pattern: all accepted (the commit advances 4 rows), one accepted, none."""
+    cfg, W, m = _model(1)
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    ref = _greedy(cfg, W, [prompt], 16)[0]
+
+    def drafter(seq, depth):
+        n = len(seq.generated)
+        d = ref[n: n + depth]
+        if mode == "wrong":
+            d = [(t + 1) % cfg.vocab for t in d]
+        if mode == "half" and len(d) > 1:
+            d = d[:1] + [(t + 1) % cfg.vocab for t in d[1:]]
+        return d, [0.9] * len(d)
+    sd = SpecDecoder(m, drafter, depth=3, graphs=True)
+    assert sd.generate([prompt], 16)[0] == ref
+    assert sd.graphs.rounds
+    if mode == "perfect":
+        assert sd.rounds <= 5
+
+
+def test_sampled_graph_rounds_equal_eager_sampling():
+    cfg, W, m = _model(1)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (16,), generator=g).tolist()
+    eager = SpecDecoder(m, "mtp", depth=3).generate([prompt], 10, temperature=1.0, seed=42)[0]
+    cfg2, W2, m2 = _model(1)
+    graph = SpecDecoder(m2, "mtp", depth=3, graphs=True).generate([prompt], 10, temperature=1.0, seed=42)[0]
+    assert graph == eager
+
+
+def test_token_prob_kernel():
+    from spark_engine_b200.ops import cuda as cu
+    torch.manual_seed(1)
+    lg = torch.randn(5, 3001, device="cuda") * 4
+    ids = torch.tensor([0, 17, 3000, 1500, 2], dtype=torch.int32, device="cuda")
+    got = cu.token_prob(lg, ids)
+    want = torch.softmax(lg, -1)[torch.arange(5), ids.long()]
+    assert (got - want).abs().max().item() < 1e-5
