@@ -153,6 +153,7 @@ def main():
     ap.add_argument("--format", default=None, help="dense | exl3 | mx (default: the config's)")
     ap.add_argument("--kv", default=None, help="bf16 | fp8 (default: the config's)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--hc", default=None, help="gated | mhc: run the model with 4 hyper-connection residual streams")
     ap.add_argument("--spec", default="none", help="mtp: also time speculative rounds (MTP chain of 3 drafts, 4 rows per "
                                                    "sequence verified) through the captured draft / verify / commit graphs")
     ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
@@ -187,6 +188,8 @@ def main():
     cfg = get_model_config(args.model, **kw)
     if args.kv:
         cfg.kv_dtype = args.kv
+    if args.hc:
+        cfg.hc_kind, cfg.hc_streams, cfg.hc_rank = args.hc, 4, 32
     aten = args.impl == "aten"
     if aten and cfg.weight_format != "dense":
         # the ATen path has no kernels for the packed formats: it would dequantise every matrix on the host per call
@@ -288,7 +291,7 @@ def main():
     replicas = 1 if use_tp else world
     value = replicas * S * 1e3 / dev_ms
     e2e = replicas * S * 1e3 / e2e_ms
-    full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS
+    full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS and not args.hc
             and cfg.weight_format == DEFAULT_FORMAT[args.model])
     # what a step streams: the weights a round of S rows touches on this rank (not the whole model)
     step_bytes = decode_step_bytes(W, cfg, S)
@@ -311,7 +314,7 @@ def main():
         "config": {"model": cfg.name, "layers": cfg.n_layers, "hidden": cfg.hidden, "experts": cfg.moe.n_experts,
                    "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
                    "kv": kv_label, "global_batch": replicas * S, "seq_len": args.prompt, "streams_per_gpu": S,
-                   "parallelism": (f"tp{world}+ep{world}" if use_tp else f"dp{world}") if world > 1 else "single", "speculation": "none (greedy)",
+                   "parallelism": (f"tp{world}+ep{world}" if use_tp else f"dp{world}") if world > 1 else "single", "speculation": "none (greedy)", "hyper_connections": cfg.hc_kind,
                    "cache": "inputs larger than L2: a step streams %.2f GB of weights per GPU (of %.1f GB resident)"
                             % (step_bytes / 1e9, weight_bytes(W) / 1e9),
                    "full_config": full},

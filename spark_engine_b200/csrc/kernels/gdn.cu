@@ -25,7 +25,10 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
                const int* __restrict__ seg,                          // [nseg, 4] slot, r0, n, pos0
                const int* __restrict__ n_rows,                       // optional [nseg]: rows to process
                __nv_bfloat16* __restrict__ out, int ldo,             // [R, Hv*D]
-               int Hk, int Hv, float eps, int commit) {
+               int Hk, int Hv, float eps, int commit,
+               const int* __restrict__ path, int path_ld) {          // optional [nseg, path_ld]: the rows a segment walks
+  // With `path` a segment is one root-to-node walk of a verification tree: step t reads batch row path[sg][t] (n_rows[sg]
+  // of them) from the committed state, and only the last step's output is kept unless the walk is being committed.
   const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x;
   // The segment table, the state and the conv history were last written at least two launches back (plan staging,
   // this layer's launch of the previous round): they are fetched before the dependency wait, so the 64 KB state of
@@ -67,7 +70,8 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
   const int warp = i >> 5, lane = i & 31;
 
   for (int t = 0; t < n; ++t) {
-    const __nv_bfloat16* pr = proj + static_cast<size_t>(r0 + t) * ldp;
+    const int row = path != nullptr ? path[sg * path_ld + t] : r0 + t;
+    const __nv_bfloat16* pr = proj + static_cast<size_t>(row) * ldp;
     const float xq = __bfloat162float(pr[cq]), xk = __bfloat162float(pr[ck]), xv = __bfloat162float(pr[cv]);
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
     float k = hk_[0] * wk[0] + hk_[1] * wk[1] + hk_[2] * wk[2] + xk * wk[3];
@@ -86,8 +90,8 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
     sq[i] = q * rsqrtf(q2 + eps) * qscale;
     sk[i] = k * rsqrtf(k2 + eps);
     __syncthreads();
-    const float bl = __bfloat162float(ab[static_cast<size_t>(r0 + t) * ldab + h]);
-    const float al = __bfloat162float(ab[static_cast<size_t>(r0 + t) * ldab + Hv + h]);
+    const float bl = __bfloat162float(ab[static_cast<size_t>(row) * ldab + h]);
+    const float al = __bfloat162float(ab[static_cast<size_t>(row) * ldab + Hv + h]);
     const float beta = 1.f / (1.f + __expf(-bl));
     const float xa = al + dtb;
     const float sp = xa > 20.f ? xa : log1pf(__expf(xa));          // softplus
@@ -108,7 +112,7 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
     for (int w = 0; w < D / 32; ++w) o2 += sred[w];
     const float z = __bfloat162float(pr[zc]);
     const float res = o * rsqrtf(o2 / D + eps) * nw / (1.f + __expf(-z));
-    out[static_cast<size_t>(r0 + t) * ldo + h * D + i] = __float2bfloat16(res);
+    if (path == nullptr || commit || t == n - 1) out[static_cast<size_t>(row) * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();     // sq/sk/red reused by the next row
   }
   if (commit) {
@@ -129,19 +133,19 @@ using namespace spark;
 extern "C" int spark_gdn_seq(const void* proj, int ldp, const void* ab, int ldab, const float* conv_w,
                              const float* A_log, const float* dt_bias, const float* norm_w, float* S, float* tail,
                              const int* seg, const int* n_rows, int nseg, void* out, int ldo, int Hk, int Hv, int D,
-                             float eps, int commit, cudaStream_t s) {
+                             float eps, int commit, cudaStream_t s, const int* path, int path_ld) {
   if (nseg <= 0) return 0;
   dim3 grid(Hv, nseg);
   cudaError_t e = cudaSuccess;
   if (D == 128)
     e = spark_launch_pdl(gdn_seq_kernel<128>, grid, dim3(128), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                             dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+                                             dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
   else if (D == 64)
     e = spark_launch_pdl(gdn_seq_kernel<64>, grid, dim3(64), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
   else if (D == 32)
     e = spark_launch_pdl(gdn_seq_kernel<32>, grid, dim3(32), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit);
+                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
   else
     return -5;
   return e == cudaSuccess ? 0 : -4;

@@ -23,7 +23,10 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
                float* __restrict__ S,                                    // [slots, H, D, D]
                float* __restrict__ tail,                                 // [slots, 3, 3*H*D]
                const int* __restrict__ seg, const int* __restrict__ n_rows,
-               __nv_bfloat16* __restrict__ out, int ldo, int H, int commit) {
+               __nv_bfloat16* __restrict__ out, int ldo, int H, int commit,
+               const int* __restrict__ path, int path_ld) {             // optional [nseg, path_ld]: the rows a segment walks
+  // With `path` a segment is one root-to-node walk of a verification tree (see gdn.cu): step t reads batch row
+  // path[sg][t]; only the last step's output is kept unless the walk is being committed.
   constexpr int DS = D / SPLIT, NW = D * SPLIT / 32;
   const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x / SPLIT, part = threadIdx.x % SPLIT;
   const int slot = seg[sg * 4 + 0], r0 = seg[sg * 4 + 1];
@@ -57,7 +60,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
   const float* pd = sdec + part * DS;
 
   for (int t = 0; t < n; ++t) {
-    const size_t r = static_cast<size_t>(r0 + t);
+    const size_t r = static_cast<size_t>(path != nullptr ? path[sg * path_ld + t] : r0 + t);
     const __nv_bfloat16* pr = pre + r * ldp;
     const float xq = __bfloat162float(pr[cq]), xk = __bfloat162float(pr[ck]), xv = __bfloat162float(pr[cv]);
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
@@ -99,7 +102,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
     o2 *= 1.f / SPLIT;
     const float gate = g2[r * ldg + h * D + i];
     const float res = nw * (o * rsqrtf(o2 / D + 1e-5f)) / (1.f + __expf(-gate));
-    if (part == 0) out[r * ldo + h * D + i] = __float2bfloat16(res);
+    if (part == 0 && (path == nullptr || commit || t == n - 1)) out[r * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();
   }
   if (commit) {
@@ -119,13 +122,13 @@ using namespace spark;
 extern "C" int spark_kda_seq(const void* pre, int ldp, const float* g1, const float* g2, int ldg, const void* lr, int ldl,
                              int beta_off, const float* conv_w, const float* A_log, const float* dt_bias,
                              const float* o_norm, float* S, float* tail, const int* seg, const int* n_rows, int nseg,
-                             void* out, int ldo, int H, int D, int commit, cudaStream_t s) {
+                             void* out, int ldo, int H, int D, int commit, cudaStream_t s, const int* path, int path_ld) {
   if (nseg <= 0) return 0;
   dim3 grid(H, nseg);
 #define SPARK_KDA(DD, SP)                                                                                              \
   kda_seq_kernel<DD, SP><<<grid, DD * SP, 0, s>>>((const __nv_bfloat16*)pre, ldp, g1, g2, ldg, (const __nv_bfloat16*)lr, ldl,  \
                                          beta_off, conv_w, A_log, dt_bias, o_norm, S, tail, seg, n_rows,             \
-                                         (__nv_bfloat16*)out, ldo, H, commit)
+                                         (__nv_bfloat16*)out, ldo, H, commit, path, path_ld)
   if (D == 128) SPARK_KDA(128, 2);
   else if (D == 64) SPARK_KDA(64, 1);
   else if (D == 32) SPARK_KDA(32, 1);

@@ -139,9 +139,25 @@ def _mlp(cfg: ModelConfig, it: _DevInit, dense: bool, tp=(0, 1)) -> dict:
     return w
 
 
+def _hc(cfg: ModelConfig, it: _DevInit, inject: bool = True) -> dict:
+    """Hyper-connection site weights (replicated on every rank: they act on the full hidden width)."""
+    S, H, r = cfg.hc_streams, cfg.hidden, cfg.hc_rank
+    if cfg.hc_kind == "gated":
+        w = {"norm": it.mat_common(S, H).float(), "down": it.mat_common(r, S * H), "up": it.mat_common(S * H, r)}
+        if inject:
+            w["inject"] = it.mat_common(S, S * H)
+        return w
+    n = 2 * S + S * S
+    return {"fn": it.mat_common(n, S * H), "scale": torch.rand(3, device=it.device, generator=it.gc) + 0.5,
+            "base": it.mat_common(n).float(), "norm": it.f32(H, val=1.0)}
+
+
 def _layer(cfg: ModelConfig, lcfg: ModelConfig, it: _DevInit, i: int, kind: str, tp=(0, 1)) -> dict:
-    return {"type": kind, "in_norm": it.f32(cfg.hidden, val=1.0), "post_norm": it.f32(cfg.hidden, val=1.0),
-            "mix": _mix(lcfg, it, kind), "mlp": _mlp(cfg, it, i < cfg.moe.dense_layers, tp)}
+    w = {"type": kind, "in_norm": it.f32(cfg.hidden, val=1.0), "post_norm": it.f32(cfg.hidden, val=1.0),
+         "mix": _mix(lcfg, it, kind), "mlp": _mlp(cfg, it, i < cfg.moe.dense_layers, tp)}
+    if cfg.hc_kind != "none":
+        w["hc_mix"], w["hc_mlp"] = _hc(cfg, it), _hc(cfg, it)
+    return w
 
 
 def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0, tp=(0, 1)) -> dict:
@@ -157,14 +173,16 @@ def build_random_model(cfg: ModelConfig, device="cuda", seed: int = 0, tp=(0, 1)
          "layers": [_layer(cfg, lcfg, it, i, cfg.layer_types[i], tp) for i in range(cfg.n_layers)]}
     if cfg.mtp_layers:
         kind = "attn" if cfg.family == "hybrid" else "mla"
-        W["mtp"] = {"fc": it.mat(cfg.hidden, 2 * cfg.hidden), "norm_e": it.f32(cfg.hidden, val=1.0),
+        W["mtp"] = {"fc": it.mat_common(cfg.hidden, 2 * cfg.hidden), "norm_e": it.f32(cfg.hidden, val=1.0),
                     "norm_h": it.f32(cfg.hidden, val=1.0), "final_norm": it.f32(cfg.hidden, val=1.0),
                     "layers": [_layer(cfg, lcfg, it, cfg.n_layers, kind, tp) for _ in range(cfg.mtp_layers)]}
+    if cfg.hc_kind == "gated":
+        W["hc_final"] = _hc(cfg, it, inject=False)
     if cfg.ngram_layers:
-        W["ngram_table"] = it.mat(cfg.ngram_rows, cfg.ngram_dim)
+        W["ngram_table"] = it.mat_common(cfg.ngram_rows, cfg.ngram_dim)
         D = cfg.ngram_dim * cfg.ngram_heads
         for i in (j for j in cfg.ngram_layers if j < cfg.n_layers):
-            W["layers"][i]["ngram"] = {"key": it.mat(cfg.hidden, D), "value": it.mat(cfg.hidden, D),
+            W["layers"][i]["ngram"] = {"key": it.mat_common(cfg.hidden, D), "value": it.mat_common(cfg.hidden, D),
                                        "norm_k": it.f32(cfg.hidden, val=1.0), "norm_q": it.f32(cfg.hidden, val=1.0)}
     return W
 

@@ -626,18 +626,17 @@ class Model:
             a = mix.forward(h, plan, self.seqs, commit)
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
             return X, mlp.forward(h, defer=deferred)
-        assert tp is None, "hyper-connection models run without tensor parallelism"
-        if pend is not None:
-            X = X + ops.to_tensor(pend)
+        # hyper-connections: `pend` carries the previous block's output with its write-back coefficients; every site
+        # applies it and forms its own mixed row in one pass over the streams
         if cfg.hc_kind == "gated":
-            post, h = ops.hc_gated_mix(X, lw["hc_mix"], cfg.norm_eps)
-            X = X + post.unsqueeze(-1).to(X.dtype) * ops.to_tensor(mix.forward(h, plan, self.seqs, commit)).unsqueeze(1)
-            post, h = ops.hc_gated_mix(X, lw["hc_mlp"], cfg.norm_eps)
-            return X + post.unsqueeze(-1).to(X.dtype) * mlp.forward(h).unsqueeze(1), None
-        h, post, comb = ops.mhc_pre(X, lw["hc_mix"], cfg.sinkhorn_iters, cfg.norm_eps)
-        X = ops.mhc_post(X, ops.to_tensor(mix.forward(h, plan, self.seqs, commit)), post, comb)
-        h, post, comb = ops.mhc_pre(X, lw["hc_mlp"], cfg.sinkhorn_iters, cfg.norm_eps)
-        return ops.mhc_post(X, mlp.forward(h), post, comb), None
+            X, h, _, post = ops.hc_gated_site(X, pend, lw["hc_mix"], cfg.norm_eps, tp)
+            a = mix.forward(h, plan, self.seqs, commit)
+            X, h, _, post2 = ops.hc_gated_site(X, (a, post), lw["hc_mlp"], cfg.norm_eps, tp)
+            return X, (mlp.forward(h), post2)
+        X, h, post, comb = ops.mhc_site(X, pend, lw["hc_mix"], cfg.sinkhorn_iters, cfg.norm_eps, tp)
+        a = mix.forward(h, plan, self.seqs, commit)
+        X, h, post2, comb2 = ops.mhc_site(X, (a, post, comb), lw["hc_mlp"], cfg.sinkhorn_iters, cfg.norm_eps, tp)
+        return X, (mlp.forward(h), post2, comb2)
 
     @torch.no_grad()
     def forward(self, plan: Plan, commit: bool = True, want_hidden: bool = False, graph_mode: bool = False):
@@ -656,7 +655,7 @@ class Model:
         else:
             X = ops.embed(W["embed"], plan.ids, self.dtype)
         if cfg.hc_kind != "none":
-            X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1)
+            X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1).contiguous()
         self._ids_for_ngram = plan
         pend = None
         taps = getattr(self, "tap_layers", None)
@@ -665,13 +664,12 @@ class Model:
         for li, (lw, mix, mlp) in enumerate(self.layers):
             X, pend = self._block(lw, mix, mlp, X, pend, plan, commit)
             if taps and li in taps:          # residual stream after layer li (feature taps of a drafter)
-                self.taps[li] = X if pend is None else ops.residual_add(X.clone(), pend)
+                self.taps[li] = X if (pend is None or cfg.hc_kind != "none") else ops.residual_add(X.clone(), pend)
         if cfg.hc_kind == "gated":
-            _, X = ops.hc_gated_mix(X, W["hc_final"], cfg.norm_eps)
-            hn = X
+            _, hn, hf, _ = ops.hc_gated_site(X, pend, W["hc_final"], cfg.norm_eps, self.tp)
+            X = hf if hf is not None else hn
         elif cfg.hc_kind == "mhc":
-            X = X.mean(1)
-            hn = ops.rmsnorm(X, W["final_norm"], cfg.norm_eps)
+            X, hn = ops.mhc_final(X, pend, W["final_norm"], cfg.norm_eps, self.tp)
         else:
             hn, X = ops.add_rmsnorm(pend, X, W["final_norm"], cfg.norm_eps, self.tp)
         self.hidden_out = X

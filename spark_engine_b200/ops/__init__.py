@@ -235,7 +235,7 @@ def gdn_mixer(mixer, proj, ab, plan, commit) -> Optional[torch.Tensor]:
 
 
 def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
-    if use_kernels(proj) and not plan.is_tree:
+    if use_kernels(proj):
         return cuda_ops().gdn_commit(mixer, proj, ab, plan, accepted)
     return False
 
@@ -247,7 +247,7 @@ def kda_mixer(mixer, pre, lr, plan, commit) -> Optional[torch.Tensor]:
 
 
 def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
-    if use_kernels(pre) and not plan.is_tree:
+    if use_kernels(pre):
         return cuda_ops().kda_commit(mixer, pre, lr, plan, accepted)
     return False
 
@@ -265,18 +265,53 @@ def attn_mixer(mixer, qkv, plan, seqs) -> Optional[torch.Tensor]:
 
 
 # ----------------------------------------------------------------------------- hyper-connections
-def hc_gated_mix(X, w, eps):
-    post, mixed = L.hc_gated_mix(X.float(), {k: v.float() for k, v in w.items()}, eps)
-    return (None if post is None else post), mixed.to(X.dtype)
+def _reduced(x, tp):
+    """Block output as a plain tensor; under tensor parallelism this rank's partial sum is all-reduced first."""
+    if x is None:
+        return None
+    if tp is not None:
+        return tp.reduce(x)
+    return to_tensor(x)
 
 
-def mhc_pre(X, w, iters, eps):
-    h, post, comb = L.mhc_pre(X.float(), {k: v.float() for k, v in w.items()}, iters, eps)
-    return h.to(X.dtype), post, comb
+def hc_gated_site(X, pend, w, eps, tp=None):
+    """Gated hyper-connection site.  `pend` = (block output, post) of the previous site, applied to the streams first:
+    X[:, s] += post[:, s] * x.  Returns (X, mixed row h, hidden copy in fp32 or None, post for this site's block)."""
+    if pend is not None:
+        pend = (_reduced(pend[0], tp), pend[1])
+    if use_kernels(X) and X.shape[1] == 4 and w["down"].shape[0] == 32 and X.dtype == torch.float32:
+        h, hf, post = cuda_ops().hc_gated_site(X, pend, w, eps)
+        return X, h, hf, post
+    if pend is not None:
+        X = X + pend[1].unsqueeze(-1).to(X.dtype) * pend[0].to(X.dtype).unsqueeze(1)
+    post, mixed = L.hc_gated_mix(X.float(), {k: v.float() for k, v in w.items() if torch.is_tensor(v)}, eps)
+    return X, mixed.to(X.dtype), None, post
 
 
-def mhc_post(X, x, post, comb):
-    return L.mhc_post(X.float(), x.float(), post, comb).to(X.dtype)
+def mhc_site(X, pend, w, iters, eps, tp=None):
+    """mHC site.  `pend` = (block output, post, comb) of the previous site, applied first.  Returns (X, h, post, comb)."""
+    if pend is not None:
+        pend = (_reduced(pend[0], tp),) + tuple(pend[1:])
+    if use_kernels(X) and X.shape[1] == 4 and X.dtype == torch.float32:
+        h, post, comb = cuda_ops().mhc_site(X, pend, w, iters, eps)
+        return X, h, post, comb
+    if pend is not None:
+        X = L.mhc_post(X.float(), pend[0].float(), pend[1], pend[2]).to(X.dtype)
+    h, post, comb = L.mhc_pre(X.float(), {k: v.float() for k, v in w.items() if torch.is_tensor(v)}, iters, eps)
+    return X, h.to(X.dtype), post, comb
+
+
+def mhc_final(X, pend, norm_w, eps, tp=None):
+    """Last update, then the mean over streams and its RMSNorm.  Returns (hidden fp32-or-input dtype [T,D], normed row)."""
+    if pend is not None:
+        pend = (_reduced(pend[0], tp),) + tuple(pend[1:])
+    if use_kernels(X) and X.shape[1] == 4 and X.dtype == torch.float32:
+        h, mean = cuda_ops().mhc_site(X, pend, None, 0, eps, mode=2, norm=norm_w)
+        return mean, h
+    if pend is not None:
+        X = L.mhc_post(X.float(), pend[0].float(), pend[1], pend[2]).to(X.dtype)
+    m = X.mean(1)
+    return m, rmsnorm(m, norm_w, eps)
 
 
 def ngram_embed(model, X, plan, w):
@@ -286,11 +321,14 @@ def ngram_embed(model, X, plan, w):
     emb = ngram_rows_for_plan(model, plan)                   # [R, heads*dim] fp32 on X.device
     if use_kernels(X):                                       # the two projections on the GEMV / tcgen05 GEMM kernels
         eb = emb.to(torch.bfloat16)
-        key = L.rms(linear(eb, w["key"]).float(), w["norm_k"].float(), cfg.norm_eps)
+        key_raw = linear(eb, w["key"]).float()
         val = linear(eb, w["value"]).float()
     else:
-        key = L.rms(emb @ w["key"].float().t(), w["norm_k"].float(), cfg.norm_eps)
+        key_raw = emb @ w["key"].float().t()
         val = emb @ w["value"].float().t()
+    if use_kernels(X) and X.dtype == torch.float32 and X.dim() == 2:
+        return cuda_ops().ngram_gate(X.contiguous(), key_raw, val, w["norm_k"], w["norm_q"], cfg.norm_eps)
+    key = L.rms(key_raw, w["norm_k"].float(), cfg.norm_eps)
     d = (key * L.rms(X.float(), w["norm_q"].float(), cfg.norm_eps)).sum(-1, keepdim=True) / math.sqrt(X.shape[-1])
     gate = torch.sigmoid(torch.sign(d) * torch.sqrt(d.abs().clamp_min(cfg.norm_eps)))
     return (X.float() + gate * val).to(X.dtype)

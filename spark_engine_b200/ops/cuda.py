@@ -40,17 +40,22 @@ _SIGS = {
     "spark_gumbel_perturb": [vp, i32, i32, i32, vp, vp, vp, i32, vp],
     "spark_token_prob_part": [vp, i32, i32, i32, vp, i32, i32, vp, i32, vp, vp],
     "spark_token_prob_final": [vp, i32, i32, vp, vp, i32, vp],
+    "spark_mhc_site": [vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp],
+    "spark_hc_gated_site": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, vp],
+    "spark_ngram_gate": [vp, vp, vp, vp, vp, i32, i32, f32, vp],
+    "spark_draft_topk": [vp, i32, i32, i32, vp, vp, vp],
+    "spark_draft_path": [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp],
     "spark_add": [vp, i32, vp, C.c_long, vp],
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
-    "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp],
+    "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp, i32],
     "spark_mla_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                        vp, vp],
     "spark_mla_qrope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp],
     "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp],
     "spark_kda_chunk_prefill": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                 i32, i32, vp],
-    "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp],
+    "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
@@ -70,7 +75,7 @@ _SIGS = {
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-_KERNELS_PER_CALL = {"spark_attn_decode": 2, "spark_moe_sort": 3, "spark_argmax": 2}
+_KERNELS_PER_CALL = {"spark_attn_decode": 2, "spark_moe_sort": 3, "spark_argmax": 2, "spark_hc_gated_site": 2}
 _launches = 0
 
 
@@ -457,6 +462,111 @@ def token_prob(logits, ids32, tp=None):
     return out
 
 
+# ----------------------------------------------------------------------------- hyper-connections
+def _hc_scratch(T, D, gated, dev):
+    dll = lib()._dll
+    fn = dll.spark_hc_partial_floats
+    fn.restype, fn.argtypes = i32, [i32, i32, i32]
+    return (scratch("hc_partial", fn(T, D, int(gated)), torch.float32, dev),
+            scratch("hc_counter", max(T, 1024), torch.int32, dev, zero=True))
+
+
+def _hc_weights(w):
+    """bf16 copies of the matrices, fp32 vectors (cached on the dict)."""
+    c = w.get("_dev")
+    if c is None:
+        c = {k: (v.to(torch.bfloat16).contiguous() if (torch.is_tensor(v) and v.dim() == 2 and k != "norm") else
+                 (v.float().contiguous() if torch.is_tensor(v) else v)) for k, v in w.items() if k != "_dev"}
+        w["_dev"] = c
+    return c
+
+
+def mhc_site(X, pend, w, iters, eps, mode=1, norm=None):
+    """One launch: apply the previous block's update `pend` = (x, post, comb) to the streams X [T,S,D] in place, then
+    (mode 1) the next block's mixed row with its post / comb, or (mode 2) the stream mean and its RMSNorm (`norm`).
+    Returns (h bf16 [T,D], post, comb) or (h, mean fp32)."""
+    T, S, D = X.shape
+    assert X.dtype == torch.float32 and X.is_contiguous()
+    dev = X.device
+    x, post_in, comb_in = pend if pend is not None else (None, None, None)
+    if x is not None:
+        x = x.contiguous()
+        assert x.dtype in (torch.float32, torch.bfloat16)
+    h = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    partial, counter = _hc_scratch(T, D, False, dev)
+    if mode == 1:
+        c = _hc_weights(w)
+        post = torch.empty(T, S, dtype=torch.float32, device=dev)
+        comb = torch.empty(T, S, S, dtype=torch.float32, device=dev)
+        rc = lib().spark_mhc_site(P(X), T, S, D, P(x), int(x is not None and x.dtype == torch.float32), P(post_in), P(comb_in),
+                                  P(c["fn"]), P(c["scale"]), P(c["base"]), P(c["norm"]), P(h), None, P(post), P(comb),
+                                  P(partial), P(counter), int(iters), float(eps), 1, stream())
+        check(rc, "spark_mhc_site")
+        return h, post, comb
+    mean = torch.empty(T, D, dtype=torch.float32, device=dev)
+    rc = lib().spark_mhc_site(P(X), T, S, D, P(x), int(x is not None and x.dtype == torch.float32), P(post_in), P(comb_in),
+                              None, None, None, P(norm.float().contiguous()), P(h), P(mean), None, None, P(partial),
+                              P(counter), int(iters), float(eps), 2, stream())
+    check(rc, "spark_mhc_site")
+    return h, mean
+
+
+def hc_gated_site(X, pend, w, eps):
+    """Two launches: apply `pend` = (x, post) to the streams in place, logits of the gate (and the next post), then the
+    mixed row.  Returns (h bf16, h fp32, post or None)."""
+    T, S, D = X.shape
+    assert X.dtype == torch.float32 and X.is_contiguous()
+    dev = X.device
+    c = _hc_weights(w)
+    if "norm_f" not in c:
+        c["norm_f"] = w["norm"].float().contiguous()
+    x, post_in = pend if pend is not None else (None, None)
+    if x is not None:
+        x = x.contiguous()
+    r = c["down"].shape[0]
+    h = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
+    hf = torch.empty(T, D, dtype=torch.float32, device=dev)
+    tvec = torch.empty(T, r + S, dtype=torch.float32, device=dev)
+    post = torch.empty(T, S, dtype=torch.float32, device=dev) if "inject" in c else None
+    partial, counter = _hc_scratch(T, D, True, dev)
+    rc = lib().spark_hc_gated_site(P(X), T, S, D, r, P(x), int(x is not None and x.dtype == torch.float32), P(post_in),
+                                   P(c["norm_f"]), P(c["down"]), P(c.get("inject")), P(c["up"]), P(tvec), P(post), P(h), P(hf),
+                                   P(partial), P(counter), float(eps), stream())
+    check(rc, "spark_hc_gated_site")
+    return h, hf, post
+
+
+def ngram_gate(X, key, val, nk, nq, eps):
+    """X (fp32, in place) += sigmoid(sign(d) sqrt|d|) * val with d the scaled dot of the normalised key and hidden rows."""
+    R, H = X.shape
+    check(lib().spark_ngram_gate(P(X), P(key.contiguous()), P(val.contiguous()), P(nk), P(nq), R, H, float(eps), stream()),
+          "spark_ngram_gate")
+    return X
+
+
+def draft_topk(logits, K):
+    """[J, V] fp32 logits -> (ids int32 [J, K], log-probabilities [J, K]) sorted descending, ties -> lowest id."""
+    J, V = logits.shape
+    ids = torch.empty(J, K, dtype=torch.int32, device=logits.device)
+    unary = torch.empty(J, K, dtype=torch.float32, device=logits.device)
+    check(lib().spark_draft_topk(P(logits), J, V, K, P(ids), P(unary), stream()), "spark_draft_topk")
+    return ids, unary
+
+
+def draft_path(unary, ids, eu, ev):
+    """Edge scores <eu[j, a], ev[j+1, b]> and the greedy path through (unary + edge): (edges, path, tokens, conf)."""
+    J, K = unary.shape
+    r = eu.shape[-1]
+    dev = unary.device
+    edges = torch.empty(max(J - 1, 0), K, K, dtype=torch.float32, device=dev)
+    path = torch.empty(J, dtype=torch.int32, device=dev)
+    tok = torch.empty(J, dtype=torch.int32, device=dev)
+    conf = torch.empty(J, dtype=torch.float32, device=dev)
+    check(lib().spark_draft_path(P(unary), P(ids), P(eu), P(ev), J, K, r, P(edges), P(path), P(tok), P(conf), stream()),
+          "spark_draft_path")
+    return edges, path, tok, conf
+
+
 def gather_rows(src, idx32):
     R, H = idx32.shape[0], src.shape[1]
     out = torch.empty(R, H, dtype=torch.bfloat16, device=src.device)
@@ -709,26 +819,73 @@ def _gdn_chunk_prefill(mixer, proj, ab, plan, d, out):
     return out
 
 
-def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None):
-    if plan.is_tree:
-        return None          # tree rows: per-node states through the generic path (every node forks its parent's state)
+def _tree_walks(plan, dev, accepted=None):
+    """Virtual segments for linear-attention kernels on a verification tree: one root-to-node walk per node (verify) or
+    the accepted walk per sequence (commit).  Returns (seg [n,4], walk lengths [n], rows [n, ld], n, ld)."""
+    key = "tree_walks" if accepted is None else None
+    d = plan.dev
+    if key and key in d:
+        return d[key]
+    segs, lens, rows = [], [], []
+    for i, sg in enumerate(plan.segs):
+        par = sg.parents if sg.parents is not None else [j - 1 for j in range(sg.n)]
+        if accepted is not None:
+            walks = [list(accepted[i])] if accepted[i] else []
+        else:
+            walks = []
+            for j in range(sg.n):
+                w, k = [], j
+                while k >= 0:
+                    w.append(k)
+                    k = par[k]
+                walks.append(w[::-1])
+        for w in walks:
+            segs.append([sg.slot, sg.r0, 0, sg.pos0])
+            lens.append(len(w))
+            rows.append([sg.r0 + k for k in w])
+    ld = max([len(r) for r in rows] + [1])
+    for s_, l in zip(segs, lens):
+        s_[2] = ld
+    tab = torch.tensor([r + [0] * (ld - len(r)) for r in rows] or [[0]], dtype=torch.int32).to(dev)
+    out = (torch.tensor(segs or [[0, 0, 0, 0]], dtype=torch.int32).to(dev), torch.tensor(lens or [0], dtype=torch.int32).to(dev),
+           tab, len(segs), ld)
+    if key:
+        d[key] = out
+    return out
+
+
+def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None, accepted=None):
     c = mixer.c
     d = _plan_dev(plan, proj.device)
     R = proj.shape[0]
     out = torch.empty(R, c.n_v_heads * c.head_dim, dtype=torch.bfloat16, device=proj.device)
     w = mixer.w
+    if plan.is_tree:
+        # every node forks its parent's state: one walk from the committed state per node (verify), or the accepted
+        # walk per sequence (commit); a tree round never commits directly
+        assert not commit or accepted is not None
+        seg, lens, tab, nw, ld = _tree_walks(plan, proj.device, accepted)
+        rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
+                                 P(w["norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), out.stride(0),
+                                 c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit), stream(),
+                                 P(tab), ld)
+        check(rc, "spark_gdn_seq")
+        return out
     if (commit and n_rows is None and c.head_dim == 128 and GDN_CHUNKED
             and min(s.n for s in plan.segs) >= GDN_CHUNK_MIN_ROWS):
         return _gdn_chunk_prefill(mixer, proj, ab, plan, d, out)
     rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
                              P(w["norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows), len(plan.segs), P(out),
                              out.stride(0), c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit),
-                             stream())
+                             stream(), None, 0)
     check(rc, "spark_gdn_seq")
     return out
 
 
 def gdn_commit(mixer, proj, ab, plan, accepted) -> bool:
+    if plan.is_tree:
+        gdn_mixer(mixer, proj, ab, plan, True, accepted=accepted)
+        return True
     n_rows = torch.tensor([len(a) for a in accepted], dtype=torch.int32, device=proj.device)
     gdn_mixer(mixer, proj, ab, plan, True, n_rows)
     return True
@@ -738,11 +895,10 @@ KDA_CHUNKED = os.environ.get("SPARK_KDA_CHUNKED", "1") == "1"
 _KERNELS_PER_CALL["spark_kda_chunk_prefill"] = 3
 
 
-def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
+def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None, accepted=None):
     """KDA layer core on the device: the low-rank gate expansions run on the GEMV/GEMM kernels, conv + norms +
-    per-channel-decay delta rule + gated RMS output in one launch (sequential over the rows of a segment)."""
-    if plan.is_tree:
-        return None
+    per-channel-decay delta rule + gated RMS output in one launch (sequential over the rows of a segment; on a
+    verification tree one root-to-node walk per node, see `_tree_walks`)."""
     c, w = mixer.c, mixer.w
     dev = pre.device
     d = _plan_dev(plan, dev)
@@ -755,6 +911,14 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
     g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
     R = pre.shape[0]
     out = torch.empty(R, n, dtype=torch.bfloat16, device=dev)
+    if plan.is_tree:
+        assert not commit or accepted is not None
+        seg, lens, tab, nw, ld = _tree_walks(plan, dev, accepted)
+        rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
+                                 P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), n,
+                                 c.n_heads, c.head_dim, int(commit), stream(), P(tab), ld)
+        check(rc, "spark_kda_seq")
+        return out
     if (commit and n_rows is None and c.head_dim == 128 and KDA_CHUNKED
             and min(s.n for s in plan.segs) >= GDN_CHUNK_MIN_ROWS):
         # committed segments of >= 64 rows: chunked form on tensor cores (16-row chunks, per-channel decay)
@@ -780,12 +944,15 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None):
         return out
     rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
                              P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows),
-                             len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream())
+                             len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream(), None, 0)
     check(rc, "spark_kda_seq")
     return out
 
 
 def kda_commit(mixer, pre, lr, plan, accepted) -> bool:
+    if plan.is_tree:
+        kda_mixer(mixer, pre, lr, plan, True, accepted=accepted)
+        return True
     n_rows = torch.tensor([len(a) for a in accepted], dtype=torch.int32, device=pre.device)
     kda_mixer(mixer, pre, lr, plan, True, n_rows)
     return True

@@ -162,6 +162,11 @@ class TPBase:
     def can_fuse_gemv(self, x, w) -> bool:
         return False
 
+    def reduce(self, delta) -> torch.Tensor:
+        """All-reduced rows of a block output that is still this rank's partial sum (tensor, deferred product or
+        uncombined expert outputs)."""
+        return self.allreduce(ops.to_tensor(delta).float())
+
     def greedy(self, logits_local: torch.Tensor, vocab_local: int) -> torch.Tensor:
         """Global arg-max from vocabulary-parallel logits: (value, index) packets, ties -> lowest id."""
         val, idx = logits_local.max(-1)
@@ -239,6 +244,16 @@ class DeviceTP(TPBase):
     def can_fuse_gemv(self, x, w) -> bool:
         from ..quant.formats import Exl3Weight
         return isinstance(w, Exl3Weight) and not w.experts and x.shape[0] <= 16 and x.is_cuda
+
+    def reduce(self, delta) -> torch.Tensor:
+        if isinstance(delta, ops.Partial):
+            if self.can_fuse_gemv(delta.x, delta.w):
+                return self.ar.gemv_fused(delta.x.contiguous(), delta.w, out_dtype=torch.float32)
+            delta = ops.linear(delta.x, delta.w)
+        if isinstance(delta, torch.Tensor) and delta.shape[0] > self.rows_cap:
+            return torch.cat([self.ar(delta[r0: r0 + self.rows_cap], out_dtype=torch.float32)
+                              for r0 in range(0, delta.shape[0], self.rows_cap)])
+        return self.ar(delta, out_dtype=torch.float32)
 
     def allreduce(self, x):
         assert x.shape[0] <= 64 and x.shape[1] <= 16

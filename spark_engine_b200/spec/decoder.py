@@ -82,7 +82,7 @@ class SpecDecoder:
         self.graphs = None
         if graphs and model.device.type == "cuda":
             capturable = not model.cfg.ngram_layers or model.W["ngram_table"].device.type == "cuda"
-            if capturable and model.cfg.hc_kind == "none":
+            if capturable:
                 from ..serving.graphs import SpecGraphs
                 self.graphs = SpecGraphs(model)
         self.depth, self.policy, self.theta, self.tau = depth, policy, theta, tau

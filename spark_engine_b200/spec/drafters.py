@@ -94,10 +94,39 @@ def _rms(x, w, eps=1e-6):
     return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
 
 
+def _to(W, device):
+    if isinstance(W, dict):
+        return {k: _to(v, device) for k, v in W.items()}
+    if isinstance(W, list):
+        return [_to(v, device) for v in W]
+    return W.to(device)
+
+
+def select_candidates(logits: torch.Tensor, embed: torch.Tensor, edge_u: torch.Tensor, edge_v: torch.Tensor, K: int):
+    """logits [depth, sub_vocab] -> (ids, unary, edges, path, conf): sorted top-K log-probabilities per position,
+    low-rank pairwise scores and the greedy path.  On the device: two kernels (`draft.cu`) around two small matmuls."""
+    if logits.is_cuda:
+        from ..ops import cuda as cu
+        ids, unary = cu.draft_topk(logits.float().contiguous(), K)
+        e = embed[ids.long()]
+        edges, path, _, conf = cu.draft_path(unary, ids, (e @ edge_u.t()).float().contiguous(),
+                                             (e @ edge_v.t()).float().contiguous())
+        return ids.long(), unary, edges, path.tolist(), conf.tolist()
+    logp = torch.log_softmax(logits, -1)
+    unary, ids = torch.sort(logp, dim=-1, descending=True, stable=True)
+    unary, ids = unary[:, :K], ids[:, :K]
+    e = embed[ids]                                                                    # [depth, K, d_model]
+    edges = torch.einsum("jar,jbr->jab", e[:-1] @ edge_u.t(), e[1:] @ edge_v.t())
+    path = greedy_path(unary, edges)
+    return ids, unary, edges, path, [float(torch.exp(unary[j, a])) for j, a in enumerate(path)]
+
+
 class FeatureDrafter:
-    def __init__(self, model, cfg: FeatureDrafterConfig, W: Optional[dict] = None, seed: int = 0):
+    def __init__(self, model, cfg: FeatureDrafterConfig, W: Optional[dict] = None, seed: int = 0, device="cpu"):
+        """`device`: where the drafter's weights and windows live; on a GPU the candidate selection runs on kernels."""
         self.m, self.c = model, cfg
-        self.W = W or init_feature_drafter(cfg, seed)
+        self.device = torch.device(device)
+        self.W = _to(W or init_feature_drafter(cfg, seed), self.device)
         model.tap_layers = set(cfg.taps)
         self.slabs = {}                   # slot -> [n_layers] list of (k, v, conv history) windows
         self.last: Optional[Candidates] = None
@@ -105,7 +134,7 @@ class FeatureDrafter:
     def _features(self, seq) -> torch.Tensor:
         """Concatenated taps of the row that produced seq.last_token (the target ran it in the previous round)."""
         taps = getattr(self.m, "taps", {})
-        rows = [taps[i][-1].float().flatten().cpu() for i in self.c.taps]
+        rows = [taps[i][-1].float().flatten().to(self.device) for i in self.c.taps]
         return torch.cat(rows)
 
     def _step(self, slot: int, x: torch.Tensor) -> torch.Tensor:
@@ -116,9 +145,9 @@ class FeatureDrafter:
             h = _rms(x, lw["n1"])
             s["h"] = (s["h"] + [h])[-c.conv_k:]
             hist = torch.stack([torch.zeros_like(h)] * (c.conv_k - len(s["h"])) + s["h"], 1)      # [d_model, conv_k]
-            gsz = c.d_model // c.conv_groups
-            conv = torch.stack([(lw["conv"][o] * hist[(o // gsz) * gsz: (o // gsz + 1) * gsz]).sum()
-                                for o in range(c.d_model)])
+            gsz = c.d_model // c.conv_groups                  # grouped causal conv: output o reads its group's channels
+            conv = torch.einsum("goik,gik->go", lw["conv"].view(c.conv_groups, gsz, gsz, c.conv_k),
+                                hist.view(c.conv_groups, gsz, c.conv_k)).reshape(c.d_model)
             h = F.silu(conv)
             qkv = lw["qkv"] @ h
             q = qkv[: c.n_q * c.head_dim].view(c.n_q, c.head_dim)
@@ -139,13 +168,7 @@ class FeatureDrafter:
         h = _rms(self._step(seq.slot, x), W["norm"])
         q = torch.einsum("jde,e->jd", W["pos_q"], h)                                  # one query per future position
         logits = q @ W["head"].t()                                                    # [depth, sub_vocab]
-        logp = torch.log_softmax(logits, -1)
-        unary, ids = torch.sort(logp, dim=-1, descending=True, stable=True)
-        unary, ids = unary[:, : c.cand_k], ids[:, : c.cand_k]
-        e = W["embed"][ids]                                                           # [depth, K, d_model]
-        edges = torch.einsum("jar,jbr->jab", e[:-1] @ W["edge_u"].t(), e[1:] @ W["edge_v"].t())
-        path = greedy_path(unary, edges)
-        conf = [float(torch.exp(unary[j, a])) for j, a in enumerate(path)]
+        ids, unary, edges, path, conf = select_candidates(logits, W["embed"], W["edge_u"], W["edge_v"], c.cand_k)
         self.last = Candidates(ids, unary, edges, path, conf)
         return self.last
 

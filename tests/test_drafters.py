@@ -1,5 +1,6 @@
 """Feature-conditioned (DFlash2-style) and staged (DSpark-style) drafters: candidate paths, trees, and exactness of
 speculative decoding with them (drafts only change speed, never the tokens)."""
+import pytest
 import torch
 
 from spark_engine_b200.config import tiny_hybrid
@@ -94,3 +95,19 @@ def test_tree_verification_rounds_are_exact():
         out += emitted
         rnd += 1
     assert out == ref
+
+
+@pytest.mark.gpu
+def test_candidate_selection_kernels_match_the_host_selection():
+    """Sorted top-K log-probabilities, pairwise edges and the greedy path on the device equal the host formulas,
+    including ties (equal logits resolve to the lowest id)."""
+    g = torch.Generator().manual_seed(0)
+    J, V, K, d, r = 4, 512, 16, 64, 32
+    logits = torch.randn(J, V, generator=g) * 2
+    logits[1, 7] = logits[1, 300] = logits[1].max() + 1.0          # a tie for the best candidate
+    embed, eu, ev = torch.randn(V, d, generator=g), torch.randn(r, d, generator=g), torch.randn(r, d, generator=g)
+    ids, unary, edges, path, conf = D.select_candidates(logits, embed, eu, ev, K)
+    gi, gu, ge, gp, gc = D.select_candidates(logits.cuda(), embed.cuda(), eu.cuda(), ev.cuda(), K)
+    assert torch.equal(gi.cpu(), ids) and ids[1, 0] == 7 and ids[1, 1] == 300
+    assert (gu.cpu() - unary).abs().max() < 1e-5 and (ge.cpu() - edges).abs().max() < 1e-3
+    assert gp == path and max(abs(a - b) for a, b in zip(gc, conf)) < 1e-5

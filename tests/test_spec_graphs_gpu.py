@@ -77,3 +77,39 @@ def test_token_prob_kernel():
     got = cu.token_prob(lg, ids)
     want = torch.softmax(lg, -1)[torch.arange(5), ids.long()]
     assert (got - want).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("family", ["hybrid", "glm"])
+def test_tree_rounds_on_the_device_equal_greedy(family):
+    """Tree verification (width 4, depth 5) through the kernels: ancestor-masked attention, one root-to-node walk per
+    node for the linear-attention layers, commit of the accepted walk; the emitted text is plain greedy decoding."""
+    from spark_engine_b200.spec.tree import Node
+    if family == "hybrid":
+        cfg, W, m = _model(1)
+    else:
+        from spark_engine_b200.config import get_model_config, scaled_down
+        cfg = scaled_down(get_model_config("glm-style"))
+        cfg.mtp_layers = 0
+        W = to_device(init_weights(cfg, seed=0), "cuda")
+        m = Model(cfg, W, device="cuda", dtype=torch.bfloat16, n_slots=1, kv_tokens=512)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    ref = _greedy(cfg, W, [prompt], 18)[0]
+    sd = SpecDecoder(m, lambda s, d: ([], []), depth=0)
+    seq = sd.start(0, prompt)
+    while len(seq.generated) < 18:
+        n = len(seq.generated)
+        want = ref[n: n + 5]
+        nodes, parent = [], -1
+        for j, tok in enumerate(want):
+            good = tok if j < 3 else (tok + 1) % cfg.vocab           # the spine is right for three levels
+            sibs = [(tok + 2 + q) % cfg.vocab for q in range(3)]
+            order = sibs[:1] + [good] + sibs[1:] if j == 1 else [good] + sibs     # level 1: the right child is not the first
+            first = len(nodes)
+            for t in order:
+                nodes.append(Node(parent, t))
+            parent = first + (1 if j == 1 else 0)
+        out = sd.round_tree([seq], [nodes], budgets=[18 - n])[0]
+        assert len(out) >= 1
+    assert seq.generated[:18] == ref
+    assert seq.accepted > 0

@@ -20,6 +20,10 @@ def _config(name):
     from spark_engine_b200.config import get_model_config, scaled_down, tiny_hybrid
     if name == "tiny":
         return tiny_hybrid()
+    if name in ("tiny-mhc", "tiny-gated"):
+        cfg = tiny_hybrid()
+        cfg.hc_kind, cfg.hc_streams, cfg.hc_rank, cfg.mtp_layers = name.split("-")[1], 4, 32, 0
+        return cfg
     cfg = scaled_down(get_model_config(name))
     cfg.mtp_layers = 0
     return cfg
@@ -59,7 +63,7 @@ def _worker(rank, world, port, q, name="tiny"):
 import pytest
 
 
-@pytest.mark.parametrize("name", ["tiny", "glm-style", "ds4-style"])
+@pytest.mark.parametrize("name", ["tiny", "glm-style", "ds4-style", "tiny-mhc", "tiny-gated"])
 def test_tp2_logits_match_unsharded(name):
     from spark_engine_b200.models.model import Model
     from spark_engine_b200.models.plan import make_plan
