@@ -10,10 +10,11 @@
 //                      g = sigmoid(t . up^T); layer_in = mean_s(g n); after the block: res'[s] = res[s] + post[s] x
 //
 // One kernel per site does [apply the previous site's update] -> [this site's logits] in a single pass over the
-// streams: grid (row, chunk of D); a CTA updates its chunk of all S streams in place, accumulates its share of the
-// logits, and the LAST CTA of a row to arrive (ticket counter, no CTA ever waits on another) sums the partials in
-// chunk order (deterministic), runs the tiny S x S part on one thread and produces the mixed row.  The gated site
-// needs the logits before it can form g, so its mixed row is a second launch.
+// streams: grid (row, chunk of D, group of logits); a CTA forms its chunk of the updated streams in registers (one
+// CTA of the chunk stores them, out of place), accumulates its share of the logits, and the LAST CTA of a row to
+// arrive (ticket counter, no CTA ever waits on another) sums the partials in chunk order (deterministic), runs the
+// S x S Sinkhorn on 16 lanes and produces the mixed row.  The gated site needs the logits before it can form g, so
+// its mixed row is a second launch.
 // Reference: shim/mhc.cu:27-517 (pre/post, Sinkhorn(20)), qwen_hc.cu:23-477, ds41_hc.cu:27-355, glm53/mhc.py:31-60,
 // qwen38/model.py:65-82.
 #include "../common/decode.cuh"
@@ -22,8 +23,10 @@ namespace spark {
 
 constexpr int HC_S = 4;                 // streams
 constexpr int HC_NL = 2 * HC_S + HC_S * HC_S;
-constexpr int HC_THREADS = 128;
+constexpr int HC_THREADS = 256;
 constexpr int HC_DC = HC_THREADS * 4;   // columns of D per CTA
+constexpr int HC_ZG = 3;                // CTAs that share one chunk of a row, each owning HC_NL / HC_ZG logits
+constexpr int HC_LG = HC_NL / HC_ZG;    // logits per CTA
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
@@ -60,7 +63,7 @@ __device__ __forceinline__ float4 ld_w4(const __nv_bfloat16* w, size_t i) { retu
 // ------------------------------------------------------------------------------------------------ mHC
 // mode: 0 = update only (no next site), 1 = full pre (logits, Sinkhorn, contraction, RMSNorm), 2 = stream mean + RMSNorm
 struct MhcArgs {
-  float* res;                 // [T, S, D] updated in place when x != nullptr
+  const float* res;           // [T, S, D] streams before the pending update
   const void* x;              // [T, D] block output of the previous site (nullptr: no update)
   int x_f32;
   const float* post_in;       // [T, S]
@@ -75,19 +78,23 @@ struct MhcArgs {
   float* comb_out;            // [T, S, S]
   float* partial;             // [T, NS, NL + 1]
   int* counter;               // [T], zero; the last CTA resets it
+  float* res_out;             // [T, S, D] updated streams (written when x != nullptr; several CTAs read one chunk of
+                              // `res`, so the update is never in place)
   int D, iters, mode;
   float eps;
 };
 
 __global__ void __launch_bounds__(HC_THREADS) mhc_site_kernel(MhcArgs a) {
   extern __shared__ float sm[];                       // [D] mixed row of the finishing CTA
-  __shared__ float red[(HC_THREADS / 32) * (HC_NL + 1)];
+  __shared__ float red[(HC_THREADS / 32) * (HC_LG + 1)];
+  __shared__ float msum[HC_NL + 1];
   __shared__ float pre_s[HC_S];
   __shared__ int last_s;
-  const int row = blockIdx.x, c = blockIdx.y, NS = gridDim.y, D = a.D, t = threadIdx.x;
+  // grid (row, chunk of D, logit group): the groups of a chunk all form the updated streams in registers, group 0 stores them
+  const int row = blockIdx.x, c = blockIdx.y, zg = blockIdx.z, NS = gridDim.y, NZ = gridDim.z, D = a.D, t = threadIdx.x;
   pdl_wait();
   pdl_trigger();
-  float* R = a.res + static_cast<size_t>(row) * HC_S * D;
+  const float* R = a.res + static_cast<size_t>(row) * HC_S * D;
   float comb[HC_S][HC_S], post[HC_S];
   if (a.x != nullptr) {
 #pragma unroll
@@ -97,9 +104,9 @@ __global__ void __launch_bounds__(HC_THREADS) mhc_site_kernel(MhcArgs a) {
       for (int j = 0; j < HC_S; ++j) comb[i][j] = a.comb_in[(row * HC_S + i) * HC_S + j];
     }
   }
-  float acc[HC_NL + 1];
+  float acc[HC_LG + 1];
 #pragma unroll
-  for (int l = 0; l <= HC_NL; ++l) acc[l] = 0.f;
+  for (int l = 0; l <= HC_LG; ++l) acc[l] = 0.f;
   const int d = c * HC_DC + t * 4;
   if (d < D) {
     float4 v[HC_S];
@@ -118,90 +125,92 @@ __global__ void __launch_bounds__(HC_THREADS) mhc_site_kernel(MhcArgs a) {
         }
       }
 #pragma unroll
-      for (int s = 0; s < HC_S; ++s) {
-        v[s] = n[s];
-        *reinterpret_cast<float4*>(R + static_cast<size_t>(s) * D + d) = n[s];
-      }
+      for (int s = 0; s < HC_S; ++s) v[s] = n[s];
     }
     if (a.mode == 1) {
+      float4 w[HC_S][HC_LG];                            // all of this thread's weight loads in flight together
+#pragma unroll
+      for (int s = 0; s < HC_S; ++s)
+#pragma unroll
+        for (int l = 0; l < HC_LG; ++l) w[s][l] = ld_w4(a.fn, (static_cast<size_t>(zg * HC_LG + l) * HC_S + s) * D + d);
 #pragma unroll
       for (int s = 0; s < HC_S; ++s) {
-        acc[HC_NL] += v[s].x * v[s].x + v[s].y * v[s].y + v[s].z * v[s].z + v[s].w * v[s].w;
+        acc[HC_LG] += v[s].x * v[s].x + v[s].y * v[s].y + v[s].z * v[s].z + v[s].w * v[s].w;
 #pragma unroll
-        for (int l = 0; l < HC_NL; ++l) {
-          const float4 w = ld_w4(a.fn, (static_cast<size_t>(l) * HC_S + s) * D + d);
-          acc[l] += v[s].x * w.x + v[s].y * w.y + v[s].z * w.z + v[s].w * w.w;
-        }
+        for (int l = 0; l < HC_LG; ++l) acc[l] += v[s].x * w[s][l].x + v[s].y * w[s][l].y + v[s].z * w[s][l].z + v[s].w * w[s][l].w;
       }
+    }
+    if (a.x != nullptr && zg == 0) {
+      float* W = a.res_out + static_cast<size_t>(row) * HC_S * D;
+#pragma unroll
+      for (int s = 0; s < HC_S; ++s) *reinterpret_cast<float4*>(W + static_cast<size_t>(s) * D + d) = v[s];
     }
   }
   if (a.mode == 0) return;
   if (a.mode == 1) {
-    block_sum<HC_NL + 1>(acc, red);
-    if (t <= HC_NL) a.partial[(static_cast<size_t>(row) * NS + c) * (HC_NL + 1) + t] = red[t];
+    block_sum<HC_LG + 1>(acc, red);
+    float* P = a.partial + (static_cast<size_t>(row) * NS + c) * (HC_NL + 1);
+    if (t < HC_LG) P[zg * HC_LG + t] = red[t];
+    if (t == HC_LG && zg == 0) P[HC_NL] = red[HC_LG];
   }
   __threadfence();
   __syncthreads();
-  if (t == 0) last_s = (atomicAdd(a.counter + row, 1) == NS - 1);
+  if (t == 0) last_s = (atomicAdd(a.counter + row, 1) == NS * NZ - 1);
   __syncthreads();
   if (!last_s) return;
   __threadfence();
-  if (t == 0) {
-    a.counter[row] = 0;
-    if (a.mode == 1) {
-      float m[HC_NL + 1];
-      for (int l = 0; l <= HC_NL; ++l) {
-        float s = 0.f;
-        for (int k = 0; k < NS; ++k) s += __ldcg(a.partial + (static_cast<size_t>(row) * NS + k) * (HC_NL + 1) + l);
-        m[l] = s;
-      }
-      const float inv = rsqrtf(m[HC_NL] / static_cast<float>(HC_S * D) + a.eps);
-      for (int s = 0; s < HC_S; ++s) {
-        pre_s[s] = sigmoidf_(m[s] * inv * a.scale[0] + a.base[s]) + 1e-6f;
-        a.post_out[row * HC_S + s] = 2.f * sigmoidf_(m[HC_S + s] * inv * a.scale[1] + a.base[HC_S + s]);
-      }
-      float cb[HC_S][HC_S];
-      for (int i = 0; i < HC_S; ++i) {
-        float mx = -INFINITY, z[HC_S], sum = 0.f;
-        for (int j = 0; j < HC_S; ++j) {
-          z[j] = m[2 * HC_S + i * HC_S + j] * inv * a.scale[2] + a.base[2 * HC_S + i * HC_S + j];
-          mx = fmaxf(mx, z[j]);
-        }
-        for (int j = 0; j < HC_S; ++j) { z[j] = expf(z[j] - mx); sum += z[j]; }
-        for (int j = 0; j < HC_S; ++j) cb[i][j] = z[j] / sum + 1e-6f;
-      }
-      for (int j = 0; j < HC_S; ++j) {                 // column normalisation (sum over i)
-        float s = 0.f;
-        for (int i = 0; i < HC_S; ++i) s += cb[i][j];
-        for (int i = 0; i < HC_S; ++i) cb[i][j] /= (s + 1e-6f);
-      }
-      for (int it = 1; it < a.iters; ++it) {
-        for (int i = 0; i < HC_S; ++i) {
-          float s = 0.f;
-          for (int j = 0; j < HC_S; ++j) s += cb[i][j];
-          for (int j = 0; j < HC_S; ++j) cb[i][j] /= (s + 1e-6f);
-        }
-        for (int j = 0; j < HC_S; ++j) {
-          float s = 0.f;
-          for (int i = 0; i < HC_S; ++i) s += cb[i][j];
-          for (int i = 0; i < HC_S; ++i) cb[i][j] /= (s + 1e-6f);
-        }
-      }
-      for (int i = 0; i < HC_S; ++i)
-        for (int j = 0; j < HC_S; ++j) a.comb_out[(row * HC_S + i) * HC_S + j] = cb[i][j];
-    } else {
-      for (int s = 0; s < HC_S; ++s) pre_s[s] = 1.f / HC_S;
+  const float* Rn = a.x != nullptr ? a.res_out + static_cast<size_t>(row) * HC_S * D : R;
+  if (t == 0) a.counter[row] = 0;
+  if (a.mode == 1) {
+    if (t <= HC_NL) {
+      float s = 0.f;
+      for (int k = 0; k < NS; ++k) s += __ldcg(a.partial + (static_cast<size_t>(row) * NS + k) * (HC_NL + 1) + t);
+      msum[t] = s;
     }
+    __syncthreads();
+    const float inv = rsqrtf(msum[HC_NL] / static_cast<float>(HC_S * D) + a.eps);
+    if (t < HC_S) {
+      pre_s[t] = sigmoidf_(msum[t] * inv * a.scale[0] + a.base[t]) + 1e-6f;
+      a.post_out[row * HC_S + t] = 2.f * sigmoidf_(msum[HC_S + t] * inv * a.scale[1] + a.base[HC_S + t]);
+    }
+    if (t < 32) {
+      // Sinkhorn on 16 lanes: lane = i * S + j holds comb[i][j]; row sums run over j (xor 1, 2), column sums over i (xor 4, 8)
+      const int e = t & 15;
+      float z = msum[2 * HC_S + e] * inv * a.scale[2] + a.base[2 * HC_S + e];
+      float mx = fmaxf(z, __shfl_xor_sync(~0u, z, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(~0u, mx, 2));
+      float p = expf(z - mx);
+      float sum = p + __shfl_xor_sync(~0u, p, 1);
+      sum += __shfl_xor_sync(~0u, sum, 2);
+      float cb = p / sum + 1e-6f;
+      float cs = cb + __shfl_xor_sync(~0u, cb, 4);
+      cs += __shfl_xor_sync(~0u, cs, 8);
+      cb /= (cs + 1e-6f);
+      for (int it = 1; it < a.iters; ++it) {
+        float rs = cb + __shfl_xor_sync(~0u, cb, 1);
+        rs += __shfl_xor_sync(~0u, rs, 2);
+        cb /= (rs + 1e-6f);
+        cs = cb + __shfl_xor_sync(~0u, cb, 4);
+        cs += __shfl_xor_sync(~0u, cs, 8);
+        cb /= (cs + 1e-6f);
+      }
+      if (t < 16) a.comb_out[row * HC_S * HC_S + e] = cb;
+    }
+  } else if (t < HC_S) {
+    pre_s[t] = 1.f / HC_S;
   }
   __syncthreads();
-  // mixed row: sum_s pre[s] res[s] (the other CTAs' chunks are read through L2), then RMSNorm
+  // the mixed row: sum_s pre[s] res'[s] (the other CTAs' chunks come through L2), then RMSNorm
   float ss[1] = {0.f};
-  for (int i = t; i < D; i += HC_THREADS) {
-    float v = 0.f;
+  for (int i = t * 4; i < D; i += HC_THREADS * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int s = 0; s < HC_S; ++s) v += pre_s[s] * __ldcg(R + static_cast<size_t>(s) * D + i);
-    sm[i] = v;
-    ss[0] += v * v;
+    for (int s = 0; s < HC_S; ++s) {
+      const float4 x = __ldcg(reinterpret_cast<const float4*>(Rn + static_cast<size_t>(s) * D + i));
+      v.x += pre_s[s] * x.x; v.y += pre_s[s] * x.y; v.z += pre_s[s] * x.z; v.w += pre_s[s] * x.w;
+    }
+    *reinterpret_cast<float4*>(sm + i) = v;
+    ss[0] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   block_sum<1>(ss, red);
   const float r = rsqrtf(red[0] / static_cast<float>(D) + a.eps);
@@ -215,8 +224,12 @@ __global__ void __launch_bounds__(HC_THREADS) mhc_site_kernel(MhcArgs a) {
 constexpr int GH_R = 32;                // rank of the gate's bottleneck
 constexpr int GH_NL = GH_R + HC_S;      // down rows + inject rows
 
+constexpr int GH_ZG = 4;                // CTAs that share one chunk of a row
+constexpr int GH_LG = GH_NL / GH_ZG;    // gate / inject rows per CTA
+
 struct GatedArgs {
-  float* res;                 // [T, S, D]
+  const float* res;           // [T, S, D] streams before the pending update
+  float* res_out;             // [T, S, D] updated streams (written when x != nullptr, never in place)
   const void* x;              // [T, D] previous block output (nullptr: no update)
   int x_f32;
   const float* post_in;       // [T, S]
@@ -236,52 +249,60 @@ struct GatedArgs {
 
 // pass 1: update, per-stream square sums and per-stream partial dots; the last CTA folds the rms factors in
 __global__ void __launch_bounds__(HC_THREADS) hc_gated_logits_kernel(GatedArgs a) {
-  constexpr int NA = GH_NL * HC_S + HC_S;
-  __shared__ float red[(HC_THREADS / 32) * NA];
+  constexpr int NA = GH_NL * HC_S + HC_S;          // a row's partial record: [row l][stream s] dots, then S square sums
+  constexpr int NC = GH_LG * HC_S + HC_S;          // what one CTA accumulates
+  __shared__ float red[(HC_THREADS / 32) * NC];
+  __shared__ float tot[NA];
   __shared__ int last_s;
-  const int row = blockIdx.x, c = blockIdx.y, NS = gridDim.y, D = a.D, t = threadIdx.x;
+  const int row = blockIdx.x, c = blockIdx.y, zg = blockIdx.z, NS = gridDim.y, D = a.D, t = threadIdx.x;
   pdl_wait();
   pdl_trigger();
-  float* R = a.res + static_cast<size_t>(row) * HC_S * D;
-  float acc[NA];
+  const float* R = a.res + static_cast<size_t>(row) * HC_S * D;
+  float acc[NC];
 #pragma unroll
-  for (int l = 0; l < NA; ++l) acc[l] = 0.f;
+  for (int l = 0; l < NC; ++l) acc[l] = 0.f;
   const int d = c * HC_DC + t * 4;
   const int nl = a.inject != nullptr ? GH_NL : GH_R;
   if (d < D) {
     float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (a.x != nullptr) xv = ld_x4(a.x, a.x_f32, static_cast<size_t>(row) * D + d);
+    float4 w[GH_LG];
 #pragma unroll
     for (int s = 0; s < HC_S; ++s) {
+#pragma unroll
+      for (int q = 0; q < GH_LG; ++q) {
+        const int l = zg * GH_LG + q;
+        if (l < nl) {
+          const __nv_bfloat16* wrow = l < GH_R ? a.down + (static_cast<size_t>(l) * HC_S + s) * D
+                                               : a.inject + (static_cast<size_t>(l - GH_R) * HC_S + s) * D;
+          w[q] = ld_w4(wrow, d);
+        } else {
+          w[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
       float4 v = *reinterpret_cast<const float4*>(R + static_cast<size_t>(s) * D + d);
       if (a.x != nullptr) {
         const float p = a.post_in[row * HC_S + s];
         v.x += p * xv.x; v.y += p * xv.y; v.z += p * xv.z; v.w += p * xv.w;
-        *reinterpret_cast<float4*>(R + static_cast<size_t>(s) * D + d) = v;
+        if (zg == 0) *reinterpret_cast<float4*>(a.res_out + (static_cast<size_t>(row) * HC_S + s) * D + d) = v;
       }
-      acc[GH_NL * HC_S + s] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      acc[GH_LG * HC_S + s] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
       const float4 g = *reinterpret_cast<const float4*>(a.norm + static_cast<size_t>(s) * D + d);
       v.x *= 1.f + g.x; v.y *= 1.f + g.y; v.z *= 1.f + g.z; v.w *= 1.f + g.w;
 #pragma unroll
-      for (int l = 0; l < GH_NL; ++l) {
-        if (l < nl) {
-          const __nv_bfloat16* wrow = l < GH_R ? a.down + (static_cast<size_t>(l) * HC_S + s) * D
-                                               : a.inject + (static_cast<size_t>(l - GH_R) * HC_S + s) * D;
-          const float4 w = ld_w4(wrow, d);
-          acc[l * HC_S + s] += v.x * w.x + v.y * w.y + v.z * w.z + v.w * w.w;
-        }
-      }
+      for (int q = 0; q < GH_LG; ++q) acc[q * HC_S + s] += v.x * w[q].x + v.y * w[q].y + v.z * w[q].z + v.w * w[q].w;
     }
   }
-  block_sum<NA>(acc, red);
-  for (int i = t; i < NA; i += HC_THREADS) a.partial[(static_cast<size_t>(row) * NS + c) * NA + i] = red[i];
+  block_sum<NC>(acc, red);
+  float* P = a.partial + (static_cast<size_t>(row) * NS + c) * NA;
+  if (t < GH_LG * HC_S) P[zg * GH_LG * HC_S + t] = red[t];
+  if (zg == 0 && t >= GH_LG * HC_S && t < NC) P[GH_NL * HC_S + (t - GH_LG * HC_S)] = red[t];
   __threadfence();
   __syncthreads();
-  if (t == 0) last_s = (atomicAdd(a.counter + row, 1) == NS - 1);
+  if (t == 0) last_s = (atomicAdd(a.counter + row, 1) == NS * static_cast<int>(gridDim.z) - 1);
   __syncthreads();
   if (!last_s) return;
   __threadfence();
-  __shared__ float tot[NA];
   for (int i = t; i < NA; i += HC_THREADS) {
     float s = 0.f;
     for (int k = 0; k < NS; ++k) s += __ldcg(a.partial + (static_cast<size_t>(row) * NS + k) * NA + i);
@@ -308,7 +329,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_gated_mix_kernel(GatedArgs a) {
   pdl_trigger();
   if (t < GH_R + HC_S) tv[t] = a.tvec[row * (GH_R + HC_S) + t];
   __syncthreads();
-  const float* R = a.res + static_cast<size_t>(row) * HC_S * D;
+  const float* R = (a.x != nullptr ? a.res_out : a.res) + static_cast<size_t>(row) * HC_S * D;
   const int d = blockIdx.y * HC_DC + t * 4;
   if (d >= D) return;
   float out[4] = {0.f, 0.f, 0.f, 0.f};
@@ -381,30 +402,34 @@ extern "C" int spark_hc_partial_floats(int T, int D, int gated) {
 }
 
 // mHC site.  mode 0 = apply the update only, 1 = update (if x) + pre for the next block, 2 = update + stream mean + RMSNorm.
-extern "C" int spark_mhc_site(float* res, int T, int S, int D, const void* x, int x_f32, const float* post_in,
+// The updated streams go to `res_out` (a different buffer than `res`); without an update `res` is only read.
+extern "C" int spark_mhc_site(const float* res, int T, int S, int D, const void* x, int x_f32, const float* post_in,
                               const float* comb_in, const void* fn, const float* scale, const float* base, const float* norm,
                               void* h, float* mean_out, float* post_out, float* comb_out, float* partial, int* counter,
-                              int iters, float eps, int mode, cudaStream_t s) {
+                              int iters, float eps, int mode, cudaStream_t s, float* res_out) {
   if (T <= 0) return 0;
   if (S != HC_S || D % 4 != 0 || D > 16384) return -5;
   MhcArgs a{res, x, x_f32, post_in, comb_in, static_cast<const __nv_bfloat16*>(fn), scale, base, norm,
-            static_cast<__nv_bfloat16*>(h), mean_out, post_out, comb_out, partial, counter, D, iters, mode, eps};
+            static_cast<__nv_bfloat16*>(h), mean_out, post_out, comb_out, partial, counter, res_out, D, iters, mode, eps};
+  if (x != nullptr && (res_out == nullptr || res_out == res)) return -5;
+  const int nz = mode == 1 ? HC_ZG : 1;
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   if (smem > 48 * 1024) cudaFuncSetAttribute(mhc_site_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  const cudaError_t e = spark_launch_pdl(mhc_site_kernel, dim3(T, spark_hc_chunks(D)), dim3(HC_THREADS), smem, s, dim3(1, 1, 1), a);
+  const cudaError_t e = spark_launch_pdl(mhc_site_kernel, dim3(T, spark_hc_chunks(D), nz), dim3(HC_THREADS), smem, s, dim3(1, 1, 1), a);
   return e == cudaSuccess ? 0 : -4;
 }
 
 // Gated site: two launches (logits, then the mixed row).  `inject` == nullptr: no post (the final site).
-extern "C" int spark_hc_gated_site(float* res, int T, int S, int D, int rank, const void* x, int x_f32, const float* post_in,
+extern "C" int spark_hc_gated_site(const float* res, int T, int S, int D, int rank, const void* x, int x_f32, const float* post_in,
                                    const float* norm, const void* down, const void* inject, const void* up, float* tvec,
                                    float* post_out, void* h, float* h_f32, float* partial, int* counter, float eps,
-                                   cudaStream_t s) {
+                                   cudaStream_t s, float* res_out) {
   if (T <= 0) return 0;
   if (S != HC_S || rank != GH_R || D % 4 != 0) return -5;
-  GatedArgs a{res, x, x_f32, post_in, norm, static_cast<const __nv_bfloat16*>(down), static_cast<const __nv_bfloat16*>(inject),
+  if (x != nullptr && (res_out == nullptr || res_out == res)) return -5;
+  GatedArgs a{res, res_out, x, x_f32, post_in, norm, static_cast<const __nv_bfloat16*>(down), static_cast<const __nv_bfloat16*>(inject),
               static_cast<const __nv_bfloat16*>(up), tvec, post_out, static_cast<__nv_bfloat16*>(h), h_f32, partial, counter, D, eps};
-  cudaError_t e = spark_launch_pdl(hc_gated_logits_kernel, dim3(T, spark_hc_chunks(D)), dim3(HC_THREADS), 0, s, dim3(1, 1, 1), a);
+  cudaError_t e = spark_launch_pdl(hc_gated_logits_kernel, dim3(T, spark_hc_chunks(D), GH_ZG), dim3(HC_THREADS), 0, s, dim3(1, 1, 1), a);
   if (e != cudaSuccess) return -4;
   e = spark_launch_pdl(hc_gated_mix_kernel, dim3(T, spark_hc_chunks(D)), dim3(HC_THREADS), 0, s, dim3(1, 1, 1), a);
   return e == cudaSuccess ? 0 : -4;

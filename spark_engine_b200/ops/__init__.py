@@ -280,8 +280,7 @@ def hc_gated_site(X, pend, w, eps, tp=None):
     if pend is not None:
         pend = (_reduced(pend[0], tp), pend[1])
     if use_kernels(X) and X.shape[1] == 4 and w["down"].shape[0] == 32 and X.dtype == torch.float32:
-        h, hf, post = cuda_ops().hc_gated_site(X, pend, w, eps)
-        return X, h, hf, post
+        return cuda_ops().hc_gated_site(X, pend, w, eps)
     if pend is not None:
         X = X + pend[1].unsqueeze(-1).to(X.dtype) * pend[0].to(X.dtype).unsqueeze(1)
     post, mixed = L.hc_gated_mix(X.float(), {k: v.float() for k, v in w.items() if torch.is_tensor(v)}, eps)
@@ -293,8 +292,7 @@ def mhc_site(X, pend, w, iters, eps, tp=None):
     if pend is not None:
         pend = (_reduced(pend[0], tp),) + tuple(pend[1:])
     if use_kernels(X) and X.shape[1] == 4 and X.dtype == torch.float32:
-        h, post, comb = cuda_ops().mhc_site(X, pend, w, iters, eps)
-        return X, h, post, comb
+        return cuda_ops().mhc_site(X, pend, w, iters, eps)
     if pend is not None:
         X = L.mhc_post(X.float(), pend[0].float(), pend[1], pend[2]).to(X.dtype)
     h, post, comb = L.mhc_pre(X.float(), {k: v.float() for k, v in w.items() if torch.is_tensor(v)}, iters, eps)
@@ -306,7 +304,7 @@ def mhc_final(X, pend, norm_w, eps, tp=None):
     if pend is not None:
         pend = (_reduced(pend[0], tp),) + tuple(pend[1:])
     if use_kernels(X) and X.shape[1] == 4 and X.dtype == torch.float32:
-        h, mean = cuda_ops().mhc_site(X, pend, None, 0, eps, mode=2, norm=norm_w)
+        _, h, mean = cuda_ops().mhc_site(X, pend, None, 0, eps, mode=2, norm=norm_w)
         return mean, h
     if pend is not None:
         X = L.mhc_post(X.float(), pend[0].float(), pend[1], pend[2]).to(X.dtype)

@@ -40,8 +40,8 @@ _SIGS = {
     "spark_gumbel_perturb": [vp, i32, i32, i32, vp, vp, vp, i32, vp],
     "spark_token_prob_part": [vp, i32, i32, i32, vp, i32, i32, vp, i32, vp, vp],
     "spark_token_prob_final": [vp, i32, i32, vp, vp, i32, vp],
-    "spark_mhc_site": [vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp],
-    "spark_hc_gated_site": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, vp],
+    "spark_mhc_site": [vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp, vp],
+    "spark_hc_gated_site": [vp, i32, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, vp, vp],
     "spark_ngram_gate": [vp, vp, vp, vp, vp, i32, i32, f32, vp],
     "spark_draft_topk": [vp, i32, i32, i32, vp, vp, vp],
     "spark_draft_path": [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp],
@@ -482,47 +482,50 @@ def _hc_weights(w):
 
 
 def mhc_site(X, pend, w, iters, eps, mode=1, norm=None):
-    """One launch: apply the previous block's update `pend` = (x, post, comb) to the streams X [T,S,D] in place, then
-    (mode 1) the next block's mixed row with its post / comb, or (mode 2) the stream mean and its RMSNorm (`norm`).
-    Returns (h bf16 [T,D], post, comb) or (h, mean fp32)."""
+    """One launch: apply the previous block's update `pend` = (x, post, comb) to the streams X [T,S,D] (out of place: the
+    updated streams are returned), then (mode 1) the next block's mixed row with its post / comb, or (mode 2) the
+    stream mean and its RMSNorm (`norm`).  Returns (X', h bf16 [T,D], post, comb) or (X', h, mean fp32)."""
     T, S, D = X.shape
     assert X.dtype == torch.float32 and X.is_contiguous()
     dev = X.device
     x, post_in, comb_in = pend if pend is not None else (None, None, None)
+    Xn = X
     if x is not None:
         x = x.contiguous()
         assert x.dtype in (torch.float32, torch.bfloat16)
+        Xn = torch.empty_like(X)
     h = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
     partial, counter = _hc_scratch(T, D, False, dev)
+    xf = int(x is not None and x.dtype == torch.float32)
     if mode == 1:
         c = _hc_weights(w)
         post = torch.empty(T, S, dtype=torch.float32, device=dev)
         comb = torch.empty(T, S, S, dtype=torch.float32, device=dev)
-        rc = lib().spark_mhc_site(P(X), T, S, D, P(x), int(x is not None and x.dtype == torch.float32), P(post_in), P(comb_in),
-                                  P(c["fn"]), P(c["scale"]), P(c["base"]), P(c["norm"]), P(h), None, P(post), P(comb),
-                                  P(partial), P(counter), int(iters), float(eps), 1, stream())
+        rc = lib().spark_mhc_site(P(X), T, S, D, P(x), xf, P(post_in), P(comb_in), P(c["fn"]), P(c["scale"]), P(c["base"]),
+                                  P(c["norm"]), P(h), None, P(post), P(comb), P(partial), P(counter), int(iters), float(eps), 1,
+                                  stream(), P(Xn) if x is not None else None)
         check(rc, "spark_mhc_site")
-        return h, post, comb
+        return Xn, h, post, comb
     mean = torch.empty(T, D, dtype=torch.float32, device=dev)
-    rc = lib().spark_mhc_site(P(X), T, S, D, P(x), int(x is not None and x.dtype == torch.float32), P(post_in), P(comb_in),
-                              None, None, None, P(norm.float().contiguous()), P(h), P(mean), None, None, P(partial),
-                              P(counter), int(iters), float(eps), 2, stream())
+    rc = lib().spark_mhc_site(P(X), T, S, D, P(x), xf, P(post_in), P(comb_in), None, None, None, P(norm.float().contiguous()),
+                              P(h), P(mean), None, None, P(partial), P(counter), int(iters), float(eps), 2, stream(),
+                              P(Xn) if x is not None else None)
     check(rc, "spark_mhc_site")
-    return h, mean
+    return Xn, h, mean
 
 
 def hc_gated_site(X, pend, w, eps):
-    """Two launches: apply `pend` = (x, post) to the streams in place, logits of the gate (and the next post), then the
-    mixed row.  Returns (h bf16, h fp32, post or None)."""
+    """Two launches: apply `pend` = (x, post) to the streams (out of place), logits of the gate (and the next post), then
+    the mixed row.  Returns (X', h bf16, h fp32, post or None)."""
     T, S, D = X.shape
     assert X.dtype == torch.float32 and X.is_contiguous()
     dev = X.device
     c = _hc_weights(w)
-    if "norm_f" not in c:
-        c["norm_f"] = w["norm"].float().contiguous()
     x, post_in = pend if pend is not None else (None, None)
+    Xn = X
     if x is not None:
         x = x.contiguous()
+        Xn = torch.empty_like(X)
     r = c["down"].shape[0]
     h = torch.empty(T, D, dtype=torch.bfloat16, device=dev)
     hf = torch.empty(T, D, dtype=torch.float32, device=dev)
@@ -530,10 +533,10 @@ def hc_gated_site(X, pend, w, eps):
     post = torch.empty(T, S, dtype=torch.float32, device=dev) if "inject" in c else None
     partial, counter = _hc_scratch(T, D, True, dev)
     rc = lib().spark_hc_gated_site(P(X), T, S, D, r, P(x), int(x is not None and x.dtype == torch.float32), P(post_in),
-                                   P(c["norm_f"]), P(c["down"]), P(c.get("inject")), P(c["up"]), P(tvec), P(post), P(h), P(hf),
-                                   P(partial), P(counter), float(eps), stream())
+                                   P(c["norm"]), P(c["down"]), P(c.get("inject")), P(c["up"]), P(tvec), P(post), P(h), P(hf),
+                                   P(partial), P(counter), float(eps), stream(), P(Xn) if x is not None else None)
     check(rc, "spark_hc_gated_site")
-    return h, hf, post
+    return Xn, h, hf, post
 
 
 def ngram_gate(X, key, val, nk, nq, eps):
