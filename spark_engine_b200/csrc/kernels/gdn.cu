@@ -69,10 +69,24 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
   const float qscale = rsqrtf(static_cast<float>(D));
   const int warp = i >> 5, lane = i & 31;
 
+  // the inputs of row t + 1 are fetched while row t is computed (nothing in them depends on the recurrence)
+  struct RowIn { float xq, xk, xv, bl, al, z; int row; };
+  auto fetch = [&](int t) {
+    RowIn r;
+    r.row = path != nullptr ? path[sg * path_ld + t] : r0 + t;
+    const __nv_bfloat16* pr = proj + static_cast<size_t>(r.row) * ldp;
+    r.xq = __bfloat162float(pr[cq]); r.xk = __bfloat162float(pr[ck]); r.xv = __bfloat162float(pr[cv]);
+    r.z = __bfloat162float(pr[zc]);
+    r.bl = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + h]);
+    r.al = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + Hv + h]);
+    return r;
+  };
+  RowIn nxt = fetch(0);
   for (int t = 0; t < n; ++t) {
-    const int row = path != nullptr ? path[sg * path_ld + t] : r0 + t;
-    const __nv_bfloat16* pr = proj + static_cast<size_t>(row) * ldp;
-    const float xq = __bfloat162float(pr[cq]), xk = __bfloat162float(pr[ck]), xv = __bfloat162float(pr[cv]);
+    const RowIn cur = nxt;
+    if (t + 1 < n) nxt = fetch(t + 1);
+    const int row = cur.row;
+    const float xq = cur.xq, xk = cur.xk, xv = cur.xv;
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
     float k = hk_[0] * wk[0] + hk_[1] * wk[1] + hk_[2] * wk[2] + xk * wk[3];
     float v = hv[0] * wv[0] + hv[1] * wv[1] + hv[2] * wv[2] + xv * wv[3];
@@ -90,10 +104,8 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
     sq[i] = q * rsqrtf(q2 + eps) * qscale;
     sk[i] = k * rsqrtf(k2 + eps);
     __syncthreads();
-    const float bl = __bfloat162float(ab[static_cast<size_t>(row) * ldab + h]);
-    const float al = __bfloat162float(ab[static_cast<size_t>(row) * ldab + Hv + h]);
-    const float beta = 1.f / (1.f + __expf(-bl));
-    const float xa = al + dtb;
+    const float beta = 1.f / (1.f + __expf(-cur.bl));
+    const float xa = cur.al + dtb;
     const float sp = xa > 20.f ? xa : log1pf(__expf(xa));          // softplus
     const float dec = __expf(a_neg * sp);
     float dot = 0.f;
@@ -110,8 +122,7 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
     o2 = 0.f;
 #pragma unroll
     for (int w = 0; w < D / 32; ++w) o2 += sred[w];
-    const float z = __bfloat162float(pr[zc]);
-    const float res = o * rsqrtf(o2 / D + eps) * nw / (1.f + __expf(-z));
+    const float res = o * rsqrtf(o2 / D + eps) * nw / (1.f + __expf(-cur.z));
     if (path == nullptr || commit || t == n - 1) out[static_cast<size_t>(row) * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();     // sq/sk/red reused by the next row
   }

@@ -59,10 +59,24 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
   const float* pk = sk + part * DS;
   const float* pd = sdec + part * DS;
 
+  // the inputs of row t + 1 are fetched while row t is computed (nothing in them depends on the recurrence)
+  struct RowIn { float xq, xk, xv, g1, g2, bl; size_t r; };
+  auto fetch = [&](int t) {
+    RowIn in;
+    in.r = static_cast<size_t>(path != nullptr ? path[sg * path_ld + t] : r0 + t);
+    const __nv_bfloat16* pr = pre + in.r * ldp;
+    in.xq = __bfloat162float(pr[cq]); in.xk = __bfloat162float(pr[ck]); in.xv = __bfloat162float(pr[cv]);
+    in.g1 = g1[in.r * ldg + h * D + i];
+    in.g2 = g2[in.r * ldg + h * D + i];
+    in.bl = __bfloat162float(lr[in.r * ldl + beta_off + h]);
+    return in;
+  };
+  RowIn nxt = fetch(0);
   for (int t = 0; t < n; ++t) {
-    const size_t r = static_cast<size_t>(path != nullptr ? path[sg * path_ld + t] : r0 + t);
-    const __nv_bfloat16* pr = pre + r * ldp;
-    const float xq = __bfloat162float(pr[cq]), xk = __bfloat162float(pr[ck]), xv = __bfloat162float(pr[cv]);
+    const RowIn cur = nxt;
+    if (t + 1 < n) nxt = fetch(t + 1);
+    const size_t r = cur.r;
+    const float xq = cur.xq, xk = cur.xk, xv = cur.xv;
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
     float k = hk_[0] * wk[0] + hk_[1] * wk[1] + hk_[2] * wk[2] + xk * wk[3];
     float v = hv[0] * wv[0] + hv[1] * wv[1] + hv[2] * wv[2] + xv * wv[3];
@@ -73,7 +87,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
     float q2 = warp_sum(q * q), k2 = warp_sum(k * k);
     if (lane == 0) { red[0][warp] = q2; red[1][warp] = k2; }
     // decay of key channel i for this row
-    const float lam = -5.f / (1.f + __expf(-a_exp * (g1[r * ldg + h * D + i] + dtb)));
+    const float lam = -5.f / (1.f + __expf(-a_exp * (cur.g1 + dtb)));
     sdec[i] = __expf(lam);
     __syncthreads();
     q2 = 0.f; k2 = 0.f;
@@ -83,7 +97,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
     sq[i] = q * rsqrtf(q2 + 1e-6f) * qscale;
     sk[i] = k * rsqrtf(k2 + 1e-6f);
     __syncthreads();
-    const float beta = 1.f / (1.f + __expf(-__bfloat162float(lr[r * ldl + beta_off + h])));
+    const float beta = 1.f / (1.f + __expf(-cur.bl));
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < DS; ++j) { s[j] *= pd[j]; dot = fmaf(s[j], pk[j], dot); }
@@ -100,7 +114,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
 #pragma unroll
     for (int w = 0; w < NW; ++w) o2 += sred[w];
     o2 *= 1.f / SPLIT;
-    const float gate = g2[r * ldg + h * D + i];
+    const float gate = cur.g2;
     const float res = nw * (o * rsqrtf(o2 / D + 1e-5f)) / (1.f + __expf(-gate));
     if (part == 0 && (path == nullptr || commit || t == n - 1)) out[r * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();

@@ -56,6 +56,9 @@ def _worker(rank, world, port):
         cfg3 = scaled_down(get_model_config(name))
         cfg3.mtp_layers = 0
         W3 = init_weights(cfg3, seed=1)
+        for lw in W3["layers"]:                      # wide router margins: a bf16 rounding difference must not flip an expert,
+            if "gate" in lw["mlp"]:                  # so the comparison measures arithmetic, not routing luck
+                lw["mlp"]["gate"] = lw["mlp"]["gate"] * 8.0
         tp3 = DeviceTP(arena, cfg3.hidden, rows_cap=64, name=f"tp3{k}")
         ref3 = Model(cfg3, to_device(W3, dev), device=dev, dtype=torch.bfloat16, n_slots=1, kv_tokens=128)
         m3 = Model(cfg3, to_device(shard_dense_weights(W3, cfg3, rank, world), dev), device=dev, dtype=torch.bfloat16,
@@ -67,7 +70,7 @@ def _worker(rank, world, port):
             parts3 = [torch.empty_like(lt3) for _ in range(world)]
             dist.all_gather(parts3, lt3.contiguous())
             err3 = ((torch.cat(parts3, 1) - lr3).norm() / lr3.norm()).item()
-            assert err3 < 8e-2, (name, err3)      # bf16 + top-k router flips on random weights: 0.01..0.06 measured
+            assert err3 < 3e-2, (name, err3)
     # ---- EXL3 model, graphs on: GEMV-fused all-reduce in the decode graph; all ranks emit the same tokens
     cfg2 = qwen3next_style(n_layers=4)
     cfg2.moe.n_experts = 32
@@ -83,6 +86,44 @@ def _worker(rank, world, port):
     assert all(torch.equal(a, allt[0]) for a in allt), "ranks diverged"
     eng2 = LLMEngine(cfg2, W2, EngineConfig(cuda_graphs=False, prefill_chunk=64), device=dev, max_seqs=2, kv_tokens_per_seq=512, tp=tp2)
     assert eng2.generate(prompts, 10) == outs, "graph replay differs from eager under TP"
+    # ---- the SAME quantised weights on one GPU and sharded: every rank generates the full EXL3 model from one seed, takes
+    # its shard of the packed tensors (no decode / re-encode), and the sharded logits must match the unsharded ones
+    from spark_engine_b200.parallel.tp import shard_weights
+    cfg4 = qwen3next_style(n_layers=4)
+    cfg4.moe.n_experts, cfg4.vocab, cfg4.mtp_layers = 32, 4096, 1
+    Wfull = build_random_model(cfg4, dev, seed=3, tp=(0, 1))
+    for lw in Wfull["layers"]:
+        if "gate" in lw["mlp"]:
+            lw["mlp"]["gate"] = (lw["mlp"]["gate"].float() * 8.0).to(lw["mlp"]["gate"].dtype)
+    one = Model(cfg4, Wfull, device=dev, dtype=torch.bfloat16, n_slots=2, kv_tokens=1024)
+    tp4 = DeviceTP(arena, cfg4.hidden, rows_cap=64, name="tp4")
+    shard = Model(cfg4, shard_weights(Wfull, cfg4, rank, world), device=dev, dtype=torch.bfloat16, n_slots=2, kv_tokens=1024, tp=tp4)
+    ids4 = torch.randint(0, cfg4.vocab, (2, 40), generator=g).tolist()
+    for items in ([(0, ids4[0][:32], 0), (1, ids4[1][:32], 0)], [(0, ids4[0][32:33], 32), (1, ids4[1][32:33], 32)],
+                  [(0, ids4[0][33:37], 33), (1, ids4[1][33:37], 33)]):
+        l1 = one.forward(make_plan(items, device=dev))
+        lt4 = shard.forward(make_plan(items, device=dev))
+        parts4 = [torch.empty_like(lt4) for _ in range(world)]
+        dist.all_gather(parts4, lt4.contiguous())
+        err4 = ((torch.cat(parts4, 1) - l1).norm() / l1.norm()).item()
+        assert err4 < 3e-2, ("same EXL3 weights, sharded vs one GPU", err4)
+        if lt4.shape[0] >= 32:                           # random weights give near-flat logits: judge the arg-max on many rows
+            assert (shard.greedy(lt4).long() == l1.argmax(-1)).float().mean() > 0.8
+    # ---- speculative rounds under tensor parallelism: captured MTP chain / verify / commit graphs == eager rounds, all ranks agree
+    from spark_engine_b200.spec.decoder import SpecDecoder
+    outs_sd = []
+    for graphs in (False, True):
+        msd = Model(cfg4, shard_weights(Wfull, cfg4, rank, world), device=dev, dtype=torch.bfloat16, n_slots=2, kv_tokens=1024,
+                    tp=tp4)
+        sd = SpecDecoder(msd, "mtp", depth=3, graphs=graphs)
+        outs_sd.append(sd.generate([ids4[0][:24], ids4[1][:24]], 12, temperature=0.7, seed=9))
+        if graphs:
+            assert sd.graphs is not None and sd.graphs.rounds and sd.graphs.mtp
+    assert outs_sd[0] == outs_sd[1], "speculative graphs differ from eager rounds under TP"
+    t = torch.tensor(outs_sd[1], device=dev)
+    allt = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(allt, t)
+    assert all(torch.equal(a, allt[0]) for a in allt), "ranks diverged in sampled speculative decoding"
     torch.cuda.synchronize()
     assert arena.status()[0] == 0, arena.status()
     arena.close()
