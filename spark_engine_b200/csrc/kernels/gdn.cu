@@ -1,7 +1,7 @@
 // Gated-DeltaNet decode / verify / sequential-prefill kernel (one launch per layer):
 //   depthwise causal conv (k=4) + SiLU on q,k,v  ->  L2-norm q,k (q scaled D^-0.5)  ->  per row
 //   S <- e^g S;  v' = beta (v - S k);  S <- S + v' k^T;  o = S q   ->  RMSNorm(o) * w * sigmoid(z).
-// Grid (value head, segment); 128 threads; thread i owns state row S[h, i, :] (D floats) in registers
+// Grid (value head, segment); D * SPLIT threads; the SPLIT lanes of row i own state row S[h, i, :] in registers
 // for the whole segment, so decode touches the state once.  Rows of a segment run in order with the
 // oracle's operation order; `commit` = 0 leaves state and conv tails untouched (speculative verify),
 // a later launch with the accepted row counts replays and commits (device-side counts `n_rows`).
@@ -12,10 +12,11 @@
 
 namespace spark {
 
-constexpr int GDN_CONV_K = 4;
-
-template <int D>
-__global__ void __launch_bounds__(D)
+// SPLIT lanes share one state row: lane `part` keeps columns [part * D/SPLIT, (part + 1) * D/SPLIT) in registers.  With
+// D = 128 a whole row per thread (128 floats + temporaries) does not fit the register file and the compiler parks the
+// state in local memory (ptxas: 32 registers, 2.6 KB of spills per thread); two lanes per row keep it in registers.
+template <int D, int SPLIT, bool PF>
+__global__ void __launch_bounds__(D * SPLIT)
 gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk*D + 2*Hv*D]  q | k | v | z
                const __nv_bfloat16* __restrict__ ab, int ldab,       // [R, 2*Hv]  b | a
                const float* __restrict__ conv_w,                     // [2*Hk*D + Hv*D, 4]
@@ -29,7 +30,8 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
                const int* __restrict__ path, int path_ld) {          // optional [nseg, path_ld]: the rows a segment walks
   // With `path` a segment is one root-to-node walk of a verification tree: step t reads batch row path[sg][t] (n_rows[sg]
   // of them) from the committed state, and only the last step's output is kept unless the walk is being committed.
-  const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x;
+  constexpr int DS = D / SPLIT, NW = D * SPLIT / 32;
+  const int h = blockIdx.x, sg = blockIdx.y, i = threadIdx.x / SPLIT, part = threadIdx.x % SPLIT;
   // The segment table, the state and the conv history were last written at least two launches back (plan staging,
   // this layer's launch of the previous round): they are fetched before the dependency wait, so the 64 KB state of
   // the head streams in while the input projection that precedes this kernel drains.
@@ -38,13 +40,13 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
   const int hk = h / (Hv / Hk);
   const int cq = hk * D + i, ck = Hk * D + hk * D + i, cv = 2 * Hk * D + h * D + i;   // conv channels
   const int zc = 2 * Hk * D + Hv * D + h * D + i;                                       // z column
-  __shared__ float sq[D], sk[D], red[2][D / 32];
-  __shared__ float sred[D / 32];
+  __shared__ float sq[D], sk[D], red[2][NW];
+  __shared__ float sred[NW];
 
-  float s[D];
-  float* Srow = S + ((static_cast<size_t>(slot) * Hv + h) * D + i) * D;
+  float s[DS];
+  float* Srow = S + ((static_cast<size_t>(slot) * Hv + h) * D + i) * D + part * DS;
 #pragma unroll
-  for (int j = 0; j < D; j += 4) {
+  for (int j = 0; j < DS; j += 4) {
     float4 t = *reinterpret_cast<const float4*>(Srow + j);
     s[j] = t.x; s[j + 1] = t.y; s[j + 2] = t.z; s[j + 3] = t.w;
   }
@@ -67,24 +69,30 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
   const float dtb = dt_bias[h];
   const float nw = norm_w[i];
   const float qscale = rsqrtf(static_cast<float>(D));
-  const int warp = i >> 5, lane = i & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* pq = sq + part * DS;
+  const float* pk = sk + part * DS;
 
-  // the inputs of row t + 1 are fetched while row t is computed (nothing in them depends on the recurrence)
+  // PF (launches with several rows per segment): the inputs of row t + 1 are fetched while row t is computed (nothing in
+  // them depends on the recurrence).  Single-row decode launches keep each load next to its use.
   struct RowIn { float xq, xk, xv, bl, al, z; int row; };
   auto fetch = [&](int t) {
     RowIn r;
     r.row = path != nullptr ? path[sg * path_ld + t] : r0 + t;
     const __nv_bfloat16* pr = proj + static_cast<size_t>(r.row) * ldp;
     r.xq = __bfloat162float(pr[cq]); r.xk = __bfloat162float(pr[ck]); r.xv = __bfloat162float(pr[cv]);
-    r.z = __bfloat162float(pr[zc]);
-    r.bl = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + h]);
-    r.al = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + Hv + h]);
+    if (PF) {
+      r.z = __bfloat162float(pr[zc]);
+      r.bl = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + h]);
+      r.al = __bfloat162float(ab[static_cast<size_t>(r.row) * ldab + Hv + h]);
+    }
     return r;
   };
   RowIn nxt = fetch(0);
   for (int t = 0; t < n; ++t) {
-    const RowIn cur = nxt;
-    if (t + 1 < n) nxt = fetch(t + 1);
+    RowIn cur = nxt;
+    if (PF && t + 1 < n) nxt = fetch(t + 1);
+    if (!PF && t > 0) cur = fetch(t);
     const int row = cur.row;
     const float xq = cur.xq, xk = cur.xk, xv = cur.xv;
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
@@ -94,45 +102,57 @@ gdn_seq_kernel(const __nv_bfloat16* __restrict__ proj, int ldp,      // [R, 2*Hk
     hk_[0] = hk_[1]; hk_[1] = hk_[2]; hk_[2] = xk;
     hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = xv;
     q = q / (1.f + __expf(-q)); k = k / (1.f + __expf(-k)); v = v / (1.f + __expf(-v));
-    // L2 norms of q and k over the D channels of this head
+    // L2 norms of q and k over the D channels of this head (every channel is counted by its SPLIT lanes)
     float q2 = warp_sum(q * q), k2 = warp_sum(k * k);
     if (lane == 0) { red[0][warp] = q2; red[1][warp] = k2; }
     __syncthreads();
     q2 = 0.f; k2 = 0.f;
 #pragma unroll
-    for (int w = 0; w < D / 32; ++w) { q2 += red[0][w]; k2 += red[1][w]; }
+    for (int w = 0; w < NW; ++w) { q2 += red[0][w]; k2 += red[1][w]; }
+    q2 *= 1.f / SPLIT; k2 *= 1.f / SPLIT;
     sq[i] = q * rsqrtf(q2 + eps) * qscale;
     sk[i] = k * rsqrtf(k2 + eps);
     __syncthreads();
+    if (!PF) {
+      cur.bl = __bfloat162float(ab[static_cast<size_t>(row) * ldab + h]);
+      cur.al = __bfloat162float(ab[static_cast<size_t>(row) * ldab + Hv + h]);
+    }
     const float beta = 1.f / (1.f + __expf(-cur.bl));
     const float xa = cur.al + dtb;
     const float sp = xa > 20.f ? xa : log1pf(__expf(xa));          // softplus
     const float dec = __expf(a_neg * sp);
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < D; ++j) { s[j] *= dec; dot = fmaf(s[j], sk[j], dot); }
+    for (int j = 0; j < DS; ++j) { s[j] *= dec; dot = fmaf(s[j], pk[j], dot); }
+    if (SPLIT == 2) dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     const float vp = beta * (v - dot);
     float o = 0.f;
 #pragma unroll
-    for (int j = 0; j < D; ++j) { s[j] = fmaf(vp, sk[j], s[j]); o = fmaf(s[j], sq[j], o); }
+    for (int j = 0; j < DS; ++j) { s[j] = fmaf(vp, pk[j], s[j]); o = fmaf(s[j], pq[j], o); }
+    if (SPLIT == 2) o += __shfl_xor_sync(0xffffffffu, o, 1);
     // RMSNorm over the head's D outputs, gate with sigmoid(z)
     float o2 = warp_sum(o * o);
     if (lane == 0) sred[warp] = o2;
     __syncthreads();
     o2 = 0.f;
 #pragma unroll
-    for (int w = 0; w < D / 32; ++w) o2 += sred[w];
+    for (int w = 0; w < NW; ++w) o2 += sred[w];
+    o2 *= 1.f / SPLIT;
+    if (!PF) cur.z = __bfloat162float(proj[static_cast<size_t>(row) * ldp + zc]);
     const float res = o * rsqrtf(o2 / D + eps) * nw / (1.f + __expf(-cur.z));
-    if (path == nullptr || commit || t == n - 1) out[static_cast<size_t>(row) * ldo + h * D + i] = __float2bfloat16(res);
+    if (part == 0 && (path == nullptr || commit || t == n - 1))
+      out[static_cast<size_t>(row) * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();     // sq/sk/red reused by the next row
   }
   if (commit) {
 #pragma unroll
-    for (int j = 0; j < D; j += 4) *reinterpret_cast<float4*>(Srow + j) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
+    for (int j = 0; j < DS; j += 4) *reinterpret_cast<float4*>(Srow + j) = make_float4(s[j], s[j + 1], s[j + 2], s[j + 3]);
+    if (part == 0) {
 #pragma unroll
-    for (int j = 0; j < 3; ++j) {
-      float* t = tl + static_cast<size_t>(j) * Hv * 3 * D;
-      t[i] = hq[j]; t[D + i] = hk_[j]; t[2 * D + i] = hv[j];
+      for (int j = 0; j < 3; ++j) {
+        float* t = tl + static_cast<size_t>(j) * Hv * 3 * D;
+        t[i] = hq[j]; t[D + i] = hk_[j]; t[2 * D + i] = hv[j];
+      }
     }
   }
 }
@@ -144,19 +164,19 @@ using namespace spark;
 extern "C" int spark_gdn_seq(const void* proj, int ldp, const void* ab, int ldab, const float* conv_w,
                              const float* A_log, const float* dt_bias, const float* norm_w, float* S, float* tail,
                              const int* seg, const int* n_rows, int nseg, void* out, int ldo, int Hk, int Hv, int D,
-                             float eps, int commit, cudaStream_t s, const int* path, int path_ld) {
+                             float eps, int commit, cudaStream_t s, const int* path, int path_ld, int multi_row) {
   if (nseg <= 0) return 0;
   dim3 grid(Hv, nseg);
   cudaError_t e = cudaSuccess;
-  if (D == 128)
-    e = spark_launch_pdl(gdn_seq_kernel<128>, grid, dim3(128), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                             dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
-  else if (D == 64)
-    e = spark_launch_pdl(gdn_seq_kernel<64>, grid, dim3(64), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
-  else if (D == 32)
-    e = spark_launch_pdl(gdn_seq_kernel<32>, grid, dim3(32), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, (const __nv_bfloat16*)ab, ldab, conv_w, A_log,
-                                           dt_bias, norm_w, S, tail, seg, n_rows, (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld);
+#define SPARK_GDN(DD, SP, PFV)                                                                                          \
+  e = spark_launch_pdl(gdn_seq_kernel<DD, SP, PFV>, grid, dim3(DD * SP), 0, s, dim3(1, 1, 1), (const __nv_bfloat16*)proj, ldp, \
+                       (const __nv_bfloat16*)ab, ldab, conv_w, A_log, dt_bias, norm_w, S, tail, seg, n_rows,             \
+                       (__nv_bfloat16*)out, ldo, Hk, Hv, eps, commit, path, path_ld)
+  const bool pf = multi_row != 0;
+  if (D == 128) { if (pf) SPARK_GDN(128, 2, true); else SPARK_GDN(128, 2, false); }
+  else if (D == 64) { if (pf) SPARK_GDN(64, 1, true); else SPARK_GDN(64, 1, false); }
+  else if (D == 32) { if (pf) SPARK_GDN(32, 1, true); else SPARK_GDN(32, 1, false); }
+#undef SPARK_GDN
   else
     return -5;
   return e == cudaSuccess ? 0 : -4;

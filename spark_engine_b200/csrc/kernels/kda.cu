@@ -13,7 +13,7 @@
 
 namespace spark {
 
-template <int D, int SPLIT>
+template <int D, int SPLIT, bool PF>
 __global__ void __launch_bounds__(D * SPLIT)
 kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3*H*D]  q | k | v before the conv
                const float* __restrict__ g1, const float* __restrict__ g2, int ldg,   // [R, H*D] each
@@ -59,7 +59,8 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
   const float* pk = sk + part * DS;
   const float* pd = sdec + part * DS;
 
-  // the inputs of row t + 1 are fetched while row t is computed (nothing in them depends on the recurrence)
+  // PF (several rows per segment): the inputs of row t + 1 are fetched while row t is computed (nothing in them depends
+  // on the recurrence); single-row decode launches keep each load next to its use (see gdn.cu).
   struct RowIn { float xq, xk, xv, g1, g2, bl; size_t r; };
   auto fetch = [&](int t) {
     RowIn in;
@@ -67,14 +68,17 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
     const __nv_bfloat16* pr = pre + in.r * ldp;
     in.xq = __bfloat162float(pr[cq]); in.xk = __bfloat162float(pr[ck]); in.xv = __bfloat162float(pr[cv]);
     in.g1 = g1[in.r * ldg + h * D + i];
-    in.g2 = g2[in.r * ldg + h * D + i];
-    in.bl = __bfloat162float(lr[in.r * ldl + beta_off + h]);
+    if (PF) {
+      in.g2 = g2[in.r * ldg + h * D + i];
+      in.bl = __bfloat162float(lr[in.r * ldl + beta_off + h]);
+    }
     return in;
   };
   RowIn nxt = fetch(0);
   for (int t = 0; t < n; ++t) {
-    const RowIn cur = nxt;
-    if (t + 1 < n) nxt = fetch(t + 1);
+    RowIn cur = nxt;
+    if (PF && t + 1 < n) nxt = fetch(t + 1);
+    if (!PF && t > 0) cur = fetch(t);
     const size_t r = cur.r;
     const float xq = cur.xq, xk = cur.xk, xv = cur.xv;
     float q = hq[0] * wq[0] + hq[1] * wq[1] + hq[2] * wq[2] + xq * wq[3];
@@ -97,6 +101,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
     sq[i] = q * rsqrtf(q2 + 1e-6f) * qscale;
     sk[i] = k * rsqrtf(k2 + 1e-6f);
     __syncthreads();
+    if (!PF) cur.bl = __bfloat162float(lr[r * ldl + beta_off + h]);
     const float beta = 1.f / (1.f + __expf(-cur.bl));
     float dot = 0.f;
 #pragma unroll
@@ -114,7 +119,7 @@ kda_seq_kernel(const __nv_bfloat16* __restrict__ pre, int ldp,          // [R, 3
 #pragma unroll
     for (int w = 0; w < NW; ++w) o2 += sred[w];
     o2 *= 1.f / SPLIT;
-    const float gate = cur.g2;
+    const float gate = PF ? cur.g2 : g2[r * ldg + h * D + i];
     const float res = nw * (o * rsqrtf(o2 / D + 1e-5f)) / (1.f + __expf(-gate));
     if (part == 0 && (path == nullptr || commit || t == n - 1)) out[r * ldo + h * D + i] = __float2bfloat16(res);
     __syncthreads();
@@ -136,16 +141,16 @@ using namespace spark;
 extern "C" int spark_kda_seq(const void* pre, int ldp, const float* g1, const float* g2, int ldg, const void* lr, int ldl,
                              int beta_off, const float* conv_w, const float* A_log, const float* dt_bias,
                              const float* o_norm, float* S, float* tail, const int* seg, const int* n_rows, int nseg,
-                             void* out, int ldo, int H, int D, int commit, cudaStream_t s, const int* path, int path_ld) {
+                             void* out, int ldo, int H, int D, int commit, cudaStream_t s, const int* path, int path_ld, int multi_row) {
   if (nseg <= 0) return 0;
   dim3 grid(H, nseg);
-#define SPARK_KDA(DD, SP)                                                                                              \
-  kda_seq_kernel<DD, SP><<<grid, DD * SP, 0, s>>>((const __nv_bfloat16*)pre, ldp, g1, g2, ldg, (const __nv_bfloat16*)lr, ldl,  \
+#define SPARK_KDA(DD, SP, PFV)                                                                                            \
+  kda_seq_kernel<DD, SP, PFV><<<grid, DD * SP, 0, s>>>((const __nv_bfloat16*)pre, ldp, g1, g2, ldg, (const __nv_bfloat16*)lr, ldl,  \
                                          beta_off, conv_w, A_log, dt_bias, o_norm, S, tail, seg, n_rows,             \
                                          (__nv_bfloat16*)out, ldo, H, commit, path, path_ld)
-  if (D == 128) SPARK_KDA(128, 2);
-  else if (D == 64) SPARK_KDA(64, 1);
-  else if (D == 32) SPARK_KDA(32, 1);
+  if (D == 128) { if (multi_row) SPARK_KDA(128, 2, true); else SPARK_KDA(128, 2, false); }
+  else if (D == 64) { if (multi_row) SPARK_KDA(64, 1, true); else SPARK_KDA(64, 1, false); }
+  else if (D == 32) { if (multi_row) SPARK_KDA(32, 1, true); else SPARK_KDA(32, 1, false); }
   else return -5;
 #undef SPARK_KDA
   return spark_launch_rc(__func__);

@@ -579,6 +579,8 @@ class Model:
         self.layers = self._build_layers(W["layers"])
         self.mtp_layers = self._build_layers(W["mtp"]["layers"]) if "mtp" in W else []
         self.hidden_out = None
+        if tp is not None and hasattr(tp, "sp_min_rows") and (cfg.ngram_layers or cfg.hc_kind != "none"):
+            tp.sp_min_rows = 0           # these blocks read the whole residual between updates: keep it replicated
 
     def _build_layers(self, lws):
         out = []
@@ -672,6 +674,8 @@ class Model:
             X, hn = ops.mhc_final(X, pend, W["final_norm"], cfg.norm_eps, self.tp)
         else:
             hn, X = ops.add_rmsnorm(pend, X, W["final_norm"], cfg.norm_eps, self.tp)
+        if self.tp is not None and getattr(self.tp, "rows_sharded", False):
+            X = self.tp.gather_rows(X)       # sequence-parallel prefill kept the residual row-sharded until here
         self.hidden_out = X
         self._pending_plan = None if commit else plan
         if commit and not graph_mode:       # under a captured graph the engine tracks lengths itself
@@ -754,6 +758,8 @@ class Model:
             h, X = ops.add_rmsnorm(a, X, lw["post_norm"], cfg.norm_eps, tp)
             pend = mlp.forward(h, defer=deferred)
         hn, X = ops.add_rmsnorm(pend, X, M["final_norm"], cfg.norm_eps, tp)
+        if tp is not None and getattr(tp, "rows_sharded", False):
+            X = tp.gather_rows(X)
         self.mtp_hidden = X
         if plan.logit_rows.shape[0] != hn.shape[0] or getattr(plan, "gather_logit_rows", False):
             hn = hn[plan.logit_rows]

@@ -48,14 +48,14 @@ _SIGS = {
     "spark_add": [vp, i32, vp, C.c_long, vp],
     "spark_f32_to_bf16": [vp, vp, C.c_long, vp],
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
-    "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp, i32],
+    "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp, i32, i32],
     "spark_mla_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                        vp, vp],
     "spark_mla_qrope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp],
     "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp],
     "spark_kda_chunk_prefill": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                 i32, i32, vp],
-    "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32],
+    "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32, i32],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
@@ -871,7 +871,7 @@ def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None, accepted=None):
         rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
                                  P(w["norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), out.stride(0),
                                  c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit), stream(),
-                                 P(tab), ld)
+                                 P(tab), ld, int(ld > 1))
         check(rc, "spark_gdn_seq")
         return out
     if (commit and n_rows is None and c.head_dim == 128 and GDN_CHUNKED
@@ -880,7 +880,7 @@ def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None, accepted=None):
     rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
                              P(w["norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows), len(plan.segs), P(out),
                              out.stride(0), c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit),
-                             stream(), None, 0)
+                             stream(), None, 0, int(max(sg.n for sg in plan.segs) > 1))
     check(rc, "spark_gdn_seq")
     return out
 
@@ -919,7 +919,7 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None, accepted=None):
         seg, lens, tab, nw, ld = _tree_walks(plan, dev, accepted)
         rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
                                  P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), n,
-                                 c.n_heads, c.head_dim, int(commit), stream(), P(tab), ld)
+                                 c.n_heads, c.head_dim, int(commit), stream(), P(tab), ld, int(ld > 1))
         check(rc, "spark_kda_seq")
         return out
     if (commit and n_rows is None and c.head_dim == 128 and KDA_CHUNKED
@@ -947,7 +947,8 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None, accepted=None):
         return out
     rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
                              P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(d["seg"]), P(n_rows),
-                             len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream(), None, 0)
+                             len(plan.segs), P(out), n, c.n_heads, c.head_dim, int(commit), stream(), None, 0,
+                             int(max(sg.n for sg in plan.segs) > 1))
     check(rc, "spark_kda_seq")
     return out
 

@@ -329,14 +329,30 @@ class RowParallelGemm:
             push_only = 2
             inp = None
         else:
-            part = cu.gemm_bf16(x, w, out_f32=True)
-            if Mp != M:
-                part = torch.cat((part, part.new_zeros(Mp - M, self.N)))
-            push_only = 0
-            inp = part
+            return self.rows(cu.gemm_bf16(x, w, out_f32=True), res_owned, norm_w, eps)
         rc = lib.spark_rs_ag_rows(C.byref(a.ctx), self.slot_off, self.out_off, self.flag_rs, self.flag_ag, seq, Mp,
                                   self.N, rpr, cu.P(inp), 1, self.counters[1:].data_ptr(), cu.P(res_owned), cu.P(norm_w),
                                   float(eps), push_only, cu.stream(), self.seq.data_ptr())
+        cu.check(rc, "spark_rs_ag_rows")
+        return a.view(self.out_off, Mp * self.N * 2, torch.bfloat16).view(Mp, self.N)[:M]
+
+    def rows(self, part: torch.Tensor, res_owned=None, norm_w=None, eps=1e-6) -> torch.Tensor:
+        """Reduce-scatter + (residual + RMSNorm on the owned row block) + all-gather of precomputed partial rows
+        `part` [M, N] (fp32 or bf16): every rank ends with all M result rows in bf16 (a view into the arena, valid
+        until the next call) and `res_owned` (this rank's block of the residual stream) updated in place."""
+        a = self.a
+        W = a.world
+        M = part.shape[0]
+        rpr = (M + W - 1) // W
+        assert rpr <= self.rpr_cap and part.shape[1] == self.N
+        Mp = rpr * W
+        part = part.contiguous()
+        if Mp != M:
+            part = torch.cat((part, part.new_zeros(Mp - M, self.N)))
+        rc = _lib()._dll.spark_rs_ag_rows(C.byref(a.ctx), self.slot_off, self.out_off, self.flag_rs, self.flag_ag, 0, Mp,
+                                          self.N, rpr, cu.P(part), int(part.dtype == torch.float32),
+                                          self.counters[1:].data_ptr(), cu.P(res_owned), cu.P(norm_w), float(eps), 0,
+                                          cu.stream(), self.seq.data_ptr())
         cu.check(rc, "spark_rs_ag_rows")
         return a.view(self.out_off, Mp * self.N * 2, torch.bfloat16).view(Mp, self.N)[:M]
 

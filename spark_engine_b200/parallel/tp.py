@@ -13,6 +13,8 @@ is fused with the residual add and the following RMSNorm, and for EXL3 decode ro
 """
 from __future__ import annotations
 
+import os
+
 import dataclasses
 from typing import Optional
 
@@ -235,6 +237,14 @@ class DeviceTP(TPBase):
         self.ar = symm.FusedAllReduce(arena, name + ".ar", rows_cap, hidden)
         self.pk = symm.FusedAllReduce(arena, name + ".packets", 64, 2 * 8)
         self.argmax = symm.PacketArgmax(arena, name + ".argmax", 64)
+        # sequence-parallel prefill: the residual stream of a large chunk lives row-sharded (each rank owns a block of
+        # rows); a block output is reduce-scattered to the owners, who add it to their rows, normalise them and
+        # all-gather the bf16 result.  Against the all-reduce of full rows this moves (W - 1) / W of one fp32 copy plus
+        # one bf16 copy instead of (W - 1) fp32 copies per rank, and the norm runs once per row instead of W times.
+        # Reference: engine-rs/src/forward.rs:578-871 (sequence-parallel prefill), shim/mhc.cu:128-181.
+        self.sp_min_rows = int(os.environ.get("SPARK_SP_MIN_ROWS", "128"))
+        self.rp = symm.RowParallelGemm(arena, name + ".sp", rows_cap, hidden) if hidden <= 4096 and hidden % 4 == 0 else None
+        self.rows_sharded = False            # True while the residual of the forward in flight is valid on owned rows only
 
     def greedy(self, logits_local: torch.Tensor, vocab_local: int) -> torch.Tensor:
         if logits_local.shape[0] <= 64:
@@ -261,13 +271,36 @@ class DeviceTP(TPBase):
         pad[:, : x.shape[1]] = x
         return self.pk(pad, out_dtype=torch.float32)[:, : x.shape[1]]
 
+    def _sp(self, R: int) -> bool:
+        return (self.rp is not None and self.sp_min_rows <= R <= self.rows_cap and R % self.world == 0
+                and self.sp_min_rows > 0)
+
+    def _sp_rows(self, part, res, w, eps):
+        rpr = part.shape[0] // self.world
+        self.rows_sharded = True
+        return self.rp.rows(part, res[self.rank * rpr: (self.rank + 1) * rpr], w, eps)
+
+    def gather_rows(self, X: torch.Tensor) -> torch.Tensor:
+        """Make a row-sharded residual whole again (every rank contributes its owned block)."""
+        if not self.rows_sharded:
+            return X
+        self.rows_sharded = False
+        rpr = X.shape[0] // self.world
+        out = torch.empty_like(X)
+        dist.all_gather_into_tensor(out, X[self.rank * rpr: (self.rank + 1) * rpr].contiguous())
+        return out
+
     def add_rmsnorm(self, delta, res, w, eps):
         if isinstance(delta, ops.Partial):
+            if self._sp(delta.x.shape[0]):
+                return self._sp_rows(ops.linear(delta.x, delta.w), res, w, eps), res
             h = self.ar.gemv_fused(delta.x.contiguous(), delta.w, res=res, norm_w=w, eps=eps)
             return h, res
         if not isinstance(delta, torch.Tensor):          # uncombined MoE of a decode round: combined inside the push
             return self.ar(delta, res=res, norm_w=w, eps=eps), res
         R = delta.shape[0]
+        if self._sp(R):
+            return self._sp_rows(delta, res, w, eps), res
         if R <= self.rows_cap:
             return self.ar(delta, res=res, norm_w=w, eps=eps), res
         outs = []

@@ -96,9 +96,22 @@ def _worker(rank, world, port):
         if "gate" in lw["mlp"]:
             lw["mlp"]["gate"] = (lw["mlp"]["gate"].float() * 8.0).to(lw["mlp"]["gate"].dtype)
     one = Model(cfg4, Wfull, device=dev, dtype=torch.bfloat16, n_slots=2, kv_tokens=1024)
-    tp4 = DeviceTP(arena, cfg4.hidden, rows_cap=64, name="tp4")
+    tp4 = DeviceTP(arena, cfg4.hidden, rows_cap=512, name="tp4")
     shard = Model(cfg4, shard_weights(Wfull, cfg4, rank, world), device=dev, dtype=torch.bfloat16, n_slots=2, kv_tokens=1024, tp=tp4)
     ids4 = torch.randint(0, cfg4.vocab, (2, 40), generator=g).tolist()
+    # a 256-row prefill chunk takes the sequence-parallel path (reduce-scatter + owner-side norm + all-gather)
+    long_ids = torch.randint(0, cfg4.vocab, (256,), generator=g).tolist()
+    l_one = one.forward(make_plan([(1, long_ids, 0)], device=dev))
+    h_one = one.hidden_out.clone()
+    l_sp = shard.forward(make_plan([(1, long_ids, 0)], device=dev))
+    assert tp4.rp is not None and not tp4.rows_sharded      # the residual was gathered back at the end of the forward
+    parts_sp = [torch.empty_like(l_sp) for _ in range(world)]
+    dist.all_gather(parts_sp, l_sp.contiguous())
+    err_sp = ((torch.cat(parts_sp, 1) - l_one).norm() / l_one.norm()).item()
+    assert err_sp < 3e-2, ("sequence-parallel prefill vs one GPU", err_sp)
+    assert ((shard.hidden_out - h_one).norm() / h_one.norm()).item() < 3e-2
+    one.reset_slot(1)
+    shard.reset_slot(1)
     for items in ([(0, ids4[0][:32], 0), (1, ids4[1][:32], 0)], [(0, ids4[0][32:33], 32), (1, ids4[1][32:33], 32)],
                   [(0, ids4[0][33:37], 33), (1, ids4[1][33:37], 33)]):
         l1 = one.forward(make_plan(items, device=dev))
