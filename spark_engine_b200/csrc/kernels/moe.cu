@@ -135,6 +135,7 @@ struct RouterArgs {
 
 constexpr int ROUTER_RB = 16;
 
+template <int EPL>
 __global__ void __launch_bounds__(256)
 moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
   extern __shared__ __align__(16) uint8_t smem_router[];
@@ -219,8 +220,25 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
   __syncthreads();
   if (!last_s) return;
   // (the writers fenced before they arrived; the logits are read with L2 loads, so no reader-side fence)
-  constexpr int EPL = 32;                                   // experts per lane (E <= 1024); loops stop at nj
+  // EPL experts per lane (E <= 32 * EPL).  The k selection rounds are a serial chain, so each round is kept short: the
+  // lane's best candidate comes from a max TREE over its EPL scores and a bit mask of the positions that hold it
+  // (lowest position = lowest expert id), not from a serial compare chain (timed inside the kernel: the serial form spent 5.8 us per group of rows).
   const int nj = (a.E + 31) >> 5;
+  auto lane_best = [&](const float (&s)[EPL], float& best, int& bj) {
+    float m[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) m[j] = s[j];
+#pragma unroll
+    for (int w = EPL / 2; w >= 1; w >>= 1)
+#pragma unroll
+      for (int j = 0; j < w; ++j) m[j] = fmaxf(m[j], m[j + w]);
+    best = m[0];
+    unsigned mask = 0u;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) mask |= (s[j] == best ? 1u : 0u) << j;
+    bj = __ffs(mask) - 1;
+    if (bj < 0) bj = 0;
+  };
   for (int r = warp; r < R; r += 8) {
     const float* lg = a.logits + static_cast<size_t>(r) * a.ld;
     float p[EPL], s[EPL];                                   // p: what the weights are made of; s: selection score
@@ -249,12 +267,10 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
     }
     float selp = 0.f; int seli = -1;                        // lane k keeps slot k's weight numerator and expert
     float tot = 0.f;
-    // Every lane keeps the best of its own experts.  A round: warp maximum of the candidates' order-preserving integer
-    // keys (one redux), lowest expert id among the lanes that hold it (one redux), the winning lane takes its expert out
-    // and rescans its own.  Ties -> lowest expert id.
-    float best = -INFINITY; int bj = 0;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }
+    // A round: warp maximum of the candidates' order-preserving integer keys (one redux), lowest expert id among the
+    // lanes that hold it (one redux), the winning lane takes its expert out and finds its next best.
+    float best; int bj;
+    lane_best(s, best, bj);
     for (int k = 0; k < a.top_k; ++k) {
       const uint32_t bits = __float_as_uint(best);
       const uint32_t key = best == -INFINITY ? 0u : (bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
@@ -266,9 +282,7 @@ moe_router_topk_kernel(const __grid_constant__ RouterArgs a) {
 #pragma unroll
         for (int j = 0; j < EPL; ++j) if (j == bj) { bp = p[j]; s[j] = -INFINITY; }
         if (a.kind == 0) bp = __expf(bp - mx);
-        best = -INFINITY; bj = 0;
-#pragma unroll
-        for (int j = 0; j < EPL; ++j) if (j < nj && s[j] > best) { best = s[j]; bj = j; }
+        lane_best(s, best, bj);
       }
       const float wp = __shfl_sync(0xffffffffu, bp, wi & 31);
       if (lane == k) { selp = wp; seli = wi; }
@@ -525,8 +539,14 @@ extern "C" int spark_moe_router_topk(const void* x, int ldx, const void* Wg, int
   const size_t smem = static_cast<size_t>(R) * K * 2;
   if (smem > 200 * 1024) return -6;
   static bool attr_set = false;
-  if (!attr_set) { cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr_set = true; }
-  const cudaError_t err = spark_launch_pdl(moe_router_topk_kernel, dim3((NE + 7) / 8), dim3(256), smem, s, dim3(1, 1, 1), a);
+  if (!attr_set) {
+    cudaFuncSetAttribute(moe_router_topk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(moe_router_topk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_set = true;
+  }
+  const cudaError_t err = E <= 512
+      ? spark_launch_pdl(moe_router_topk_kernel<16>, dim3((NE + 7) / 8), dim3(256), smem, s, dim3(1, 1, 1), a)
+      : spark_launch_pdl(moe_router_topk_kernel<32>, dim3((NE + 7) / 8), dim3(256), smem, s, dim3(1, 1, 1), a);
   return err == cudaSuccess ? 0 : -4;
 }
 
