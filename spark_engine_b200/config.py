@@ -230,6 +230,7 @@ class EngineConfig:
     prefill_chunk: int = 4096
     kv_tokens: int = 1 << 20             # KV budget in tokens
     kv_granule: int = 16384
+    kv_backing: str = "dense"            # dense (one allocation of the whole budget) | vmm (address space reserved, backed on demand)
     cuda_graphs: bool = True
     spec: str = "mtp"                    # none | mtp | tree | lookup
     spec_depth: int = 3

@@ -260,22 +260,24 @@ class KdaMixer:
 class AttnMixer:
     """Softmax GQA with optional q/k norm, output gate and block-sparse selection."""
 
-    def __init__(self, cfg: ModelConfig, w: dict, kv_tokens: int, device, dtype):
+    def __init__(self, cfg: ModelConfig, w: dict, kv_tokens: int, device, dtype, alloc=None):
+        """`alloc(rows, row_shape, dtype, rows_of)`: allocator of the per-token tensors (growable backing), default dense."""
         c = cfg.attn
         self.cfg, self.c, self.w = cfg, c, w
         self.nq = c.n_q_heads * c.head_dim * (2 if c.gated else 1)
         self.nkv = c.n_kv_heads * c.head_dim
         self.fp8 = cfg.kv_dtype == "fp8" and str(device) != "cpu"
         kvd = torch.float8_e4m3fn if self.fp8 else dtype
-        self.k = torch.zeros(kv_tokens, c.n_kv_heads, c.head_dim, device=device, dtype=kvd)
-        self.v = torch.zeros(kv_tokens, c.n_kv_heads, c.head_dim, device=device, dtype=kvd)
+        alloc = alloc or (lambda rows, shape, dt, rows_of=None: torch.zeros(rows, *shape, device=device, dtype=dt))
+        self.k = alloc(kv_tokens, (c.n_kv_heads, c.head_dim), kvd, lambda t: t)
+        self.v = alloc(kv_tokens, (c.n_kv_heads, c.head_dim), kvd, lambda t: t)
         if self.fp8:   # per-(token, head) fp32 scale (reference: qwen_qsa.cu:69-177)
-            self.ks = torch.zeros(kv_tokens, c.n_kv_heads, device=device, dtype=torch.float32)
-            self.vs = torch.zeros(kv_tokens, c.n_kv_heads, device=device, dtype=torch.float32)
+            self.ks = alloc(kv_tokens, (c.n_kv_heads,), torch.float32, lambda t: t)
+            self.vs = alloc(kv_tokens, (c.n_kv_heads,), torch.float32, lambda t: t)
         if c.sparse_topk_blocks:
-            self.ik_raw = torch.zeros(kv_tokens, c.idx_dim, device=device, dtype=torch.float32)
-            self.ik_pool = torch.zeros((kv_tokens + c.block - 1) // c.block + 1, c.idx_dim, device=device,
-                                       dtype=torch.float32)
+            self.ik_raw = alloc(kv_tokens, (c.idx_dim,), torch.float32, lambda t: t)
+            self.ik_pool = alloc((kv_tokens + c.block - 1) // c.block + 1, (c.idx_dim,), torch.float32,
+                                 lambda t, b=c.block: (t + b - 1) // b + 1)
         self.inv = L.yarn_inv_freq(c.rope_dim, c.rope_theta, c.yarn_factor, c.yarn_orig_len).to(device)
         self.pending = None
 
@@ -426,14 +428,15 @@ class MlaMixer:
     sliding window and attention sink.  Reference: engine-rs/src/mla_latent.rs:196-248,406-470;
     dsa.rs:127-230; shim/ds41_attn.cu:90-424."""
 
-    def __init__(self, cfg: ModelConfig, w: dict, kv_tokens: int, device, dtype):
+    def __init__(self, cfg: ModelConfig, w: dict, kv_tokens: int, device, dtype, alloc=None):
         c = cfg.mla
         self.cfg, self.c, self.w = cfg, c, w
         self.fp8 = cfg.kv_dtype == "fp8" and str(device) != "cpu"
-        self.lat = torch.zeros(kv_tokens, c.kv_lora + c.rope_dim, device=device, dtype=torch.float32 if str(device) == "cpu" else dtype)
-        self.ik = torch.zeros(kv_tokens, c.idx_dim, device=device, dtype=torch.float32)       # LayerNorm'ed keys
-        self.ig = torch.zeros(kv_tokens, c.idx_dim, device=device, dtype=torch.float32)       # pool gates
-        self.pool = torch.zeros(kv_tokens // c.pool + 2, c.idx_dim, device=device, dtype=torch.float32)
+        alloc = alloc or (lambda rows, shape, dt, rows_of=None: torch.zeros(rows, *shape, device=device, dtype=dt))
+        self.lat = alloc(kv_tokens, (c.kv_lora + c.rope_dim,), torch.float32 if str(device) == "cpu" else dtype, lambda t: t)
+        self.ik = alloc(kv_tokens, (c.idx_dim,), torch.float32, lambda t: t)       # LayerNorm'ed keys
+        self.ig = alloc(kv_tokens, (c.idx_dim,), torch.float32, lambda t: t)       # pool gates
+        self.pool = alloc(kv_tokens // c.pool + 2, (c.idx_dim,), torch.float32, lambda t, b=c.pool: t // b + 2)
         # absorbed projections: q_nope . W_uk  and  o_lat . W_uv
         kvb = w["kv_b"].float().view(c.n_heads, 2 * c.head_dim, c.kv_lora)
         self.w_uk = kvb[:, : c.head_dim].contiguous()       # [H, D, kv_lora]
@@ -568,14 +571,18 @@ class MoeBlock:
 # ============================================================================= the model
 class Model:
     def __init__(self, cfg: ModelConfig, W: dict, device="cpu", dtype=torch.float32, n_slots: int = 4,
-                 kv_tokens: int = 4096, slot_tokens: Optional[int] = None, tp=None):
-        """`tp`: tensor/expert-parallel context (spark_engine_b200.parallel.tp); `W` then holds this rank's shard."""
+                 kv_tokens: int = 4096, slot_tokens: Optional[int] = None, tp=None, kv_backing=None):
+        """`tp`: tensor/expert-parallel context (spark_engine_b200.parallel.tp); `W` then holds this rank's shard.
+        `kv_backing`: a `cache.kv.KvBacking`; the per-token cache tensors then reserve address space for `kv_tokens`
+        and are backed on demand (a `KvManager` backs a region before it leases it)."""
         self.cfg, self.W, self.device, self.dtype = cfg, W, torch.device(device), dtype
         self.tp = tp
+        self.kv_backing = kv_backing
         self.lcfg = tp.local_config(cfg) if tp is not None else cfg      # per-rank head counts
         self.n_slots, self.kv_tokens = n_slots, kv_tokens
         per = slot_tokens or kv_tokens // n_slots
-        self.seqs = [SeqInfo(i * per, per) for i in range(n_slots)]
+        # with a growable backing no region exists until a KvManager leases (and backs) one
+        self.seqs = [SeqInfo(i * per, per) if kv_backing is None else SeqInfo(0, 0) for i in range(n_slots)]
         self.layers = self._build_layers(W["layers"])
         self.mtp_layers = self._build_layers(W["mtp"]["layers"]) if "mtp" in W else []
         self.hidden_out = None
@@ -591,9 +598,11 @@ class Model:
             elif kind == "kda":
                 mix = KdaMixer(self.lcfg, lw["mix"], self.n_slots, self.device, self.dtype)
             elif kind == "attn":
-                mix = AttnMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
+                mix = AttnMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype,
+                                self.kv_backing.alloc if self.kv_backing is not None else None)
             elif kind == "mla":
-                mix = MlaMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype)
+                mix = MlaMixer(self.lcfg, lw["mix"], self.kv_tokens, self.device, self.dtype,
+                               self.kv_backing.alloc if self.kv_backing is not None else None)
             else:
                 raise ValueError(kind)
             mix.tp = self.tp
@@ -646,6 +655,11 @@ class Model:
         With commit=False no linear-attention state nor sequence length changes: call
         `commit(accepted)` afterwards."""
         cfg, W = self.cfg, self.W
+        if not graph_mode:                   # a captured round carries fixed KV bases: the engine checks before it stages
+            for sg in plan.segs:
+                if sg.pos0 + sg.n > self.seqs[sg.slot].kv_cap:
+                    raise RuntimeError(f"slot {sg.slot}: rows up to position {sg.pos0 + sg.n} exceed its KV region of "
+                                       f"{self.seqs[sg.slot].kv_cap} tokens")
         if plan.mm_rows:
             # salted placeholder ids are outside the vocabulary: look up row 0 for them, then write the encoded media
             # rows over those positions (engine-rs/src/weights.rs:536-569)

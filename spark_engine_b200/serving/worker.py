@@ -49,8 +49,12 @@ class EngineServer:
         e = self.ecfg
         dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
         per = max(256, e.kv_tokens // e.max_seqs // 256 * 256)
+        backing = None
+        if e.kv_backing == "vmm":
+            from ..cache.kv import KvBacking
+            backing = KvBacking(device)
         self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=e.max_seqs, kv_tokens=per * e.max_seqs,
-                           slot_tokens=per, tp=tp)
+                           slot_tokens=per, tp=tp, kv_backing=backing)
         self.slot_tokens = per
         self.kv = KvManager(self.model, granule=256)
         self.sched = rt().Scheduler(e.max_seqs, per * e.max_seqs, per, e.prefill_chunk, e.max_seqs)

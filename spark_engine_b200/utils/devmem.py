@@ -31,6 +31,15 @@ class GrowableDeviceBuffer:
     def resize(self, nbytes: int) -> int:
         return self.region.resize(nbytes)
 
+    def view_unchecked(self, nbytes: int) -> torch.Tensor:
+        """uint8 tensor over the first `nbytes` of the RESERVED range, backed or not: the caller guarantees that nothing
+        touches bytes past `size` (they are unmapped).  For tensors that must keep one address while the backing grows."""
+        if self.fake:
+            import ctypes
+            import numpy as np
+            return torch.from_numpy(np.ctypeslib.as_array((ctypes.c_uint8 * nbytes).from_address(self.region.ptr)))
+        return torch.as_tensor(_CudaView(self.region.ptr, nbytes, self.region), device=f"cuda:{self.device}")
+
     def view(self, offset: int, shape, dtype) -> torch.Tensor:
         n = int(torch.tensor(shape).prod()) * torch.empty((), dtype=dtype).element_size()
         if offset + n > self.region.size:

@@ -69,3 +69,61 @@ def test_vmm_region_and_loader_on_device(tmp_path):
     assert torch.equal(dst.cpu(), data) and st.bytes == data.numel()
     pb = rt.rt().PinnedBuffer(1 << 20, True, False)
     assert pb.registered
+
+
+def _kv_backed_generation(device, fake):
+    """Tiny hybrid model whose KV tensors grow on demand: leases back their rows first, tokens equal the dense model's,
+    the backing follows the highest live lease up and down."""
+    import torch
+    from spark_engine_b200.cache.kv import KvBacking, KvManager
+    from spark_engine_b200.config import tiny_hybrid
+    from spark_engine_b200.models.model import Model
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.models.weights import init_weights, to_device
+    cfg = tiny_hybrid()
+    cfg.mtp_layers = 0
+    W = init_weights(cfg, seed=0)
+    dt = torch.float32 if device == "cpu" else torch.bfloat16
+    if device != "cpu":
+        W = to_device(W, device)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (2, 40), generator=g).tolist()
+    dense = Model(cfg, W, device=device, dtype=dt, n_slots=2, kv_tokens=1 << 16, slot_tokens=1 << 15)
+    backing = KvBacking(device, fake=fake)
+    m = Model(cfg, W, device=device, dtype=dt, n_slots=2, kv_tokens=1 << 16, kv_backing=backing)
+    kv = KvManager(m, granule=256)
+    import pytest
+    with pytest.raises(RuntimeError):                   # no lease, no region: refused on the host, nothing is touched
+        m.forward(make_plan([(0, ids[0][:8], 0)], device=device))
+    assert kv.assign(0, 512) and kv.assign(1, 40000)
+    b1 = backing.backed_bytes()
+    assert backing.tokens >= 40512 - 512 and b1 > 0
+    for s in (0, 1):
+        a = dense.forward(make_plan([(s, ids[s][:32], 0)], device=device))
+        b = m.forward(make_plan([(s, ids[s][:32], 0)], device=device))
+        assert torch.equal(a, b)
+        for t in range(32, 40):
+            a = dense.forward(make_plan([(s, [ids[s][t]], t)], device=device))
+            b = m.forward(make_plan([(s, [ids[s][t]], t)], device=device))
+            assert torch.equal(a, b)
+    kv.release(1)                                        # the high lease goes away: the backing shrinks under it
+    assert backing.backed_bytes() < b1 and backing.tokens <= 2048
+    assert kv.grow(0, 1024) and backing.tokens >= 1024   # in place, now that the neighbour is gone
+    b = m.forward(make_plan([(0, [ids[0][0]], 40)], device=device))      # slot 0 still works after the shrink
+    a = dense.forward(make_plan([(0, [ids[0][0]], 40)], device=device))
+    assert torch.equal(a, b)
+    assert "kv_backed_bytes" in kv.stats()
+
+
+def test_kv_tensors_grow_on_demand_fake_driver():
+    _kv_backed_generation("cpu", True)
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_kv_tensors_grow_on_demand_on_the_device():
+    """The same through the CUDA virtual-memory calls: a few MB mapped, grown and unmapped; no row outside a backed
+    lease is ever addressed."""
+    _kv_backed_generation("cuda", False)
