@@ -586,6 +586,12 @@ class Model:
         self.layers = self._build_layers(W["layers"])
         self.mtp_layers = self._build_layers(W["mtp"]["layers"]) if "mtp" in W else []
         self.hidden_out = None
+        # a hashed n-gram table that stays on the host is read through asynchronous gathers into a pinned ring
+        self.engram = None
+        if cfg.ngram_layers and self.device.type == "cuda" and W["ngram_table"].device.type == "cpu":
+            from ..cache.engram import EngramTable
+            self.engram = EngramTable(W["ngram_table"], device=self.device, ring_slots=3,
+                                      max_rows=4096 * cfg.ngram_heads)
         if tp is not None and hasattr(tp, "sp_min_rows") and (cfg.ngram_layers or cfg.hc_kind != "none"):
             tp.sp_min_rows = 0           # these blocks read the whole residual between updates: keep it replicated
 
@@ -673,6 +679,9 @@ class Model:
         if cfg.hc_kind != "none":
             X = X.unsqueeze(1).repeat(1, cfg.hc_streams, 1).contiguous()
         self._ids_for_ngram = plan
+        if cfg.ngram_layers and self.engram is not None:
+            from .ngram import prefetch_for_plan
+            prefetch_for_plan(self, plan)        # the gather and the upload overlap the layers before the first n-gram layer
         pend = None
         taps = getattr(self, "tap_layers", None)
         if taps:

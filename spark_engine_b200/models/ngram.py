@@ -38,13 +38,11 @@ def chain_row_ids(model, slot: int, pos0: int, new_ids) -> list:
     return out
 
 
-def ngram_rows_for_plan(model, plan) -> torch.Tensor:
+def row_ids_for_plan(model, plan) -> torch.Tensor:
+    """Table row ids [R, heads] (int64, on the host) of every row of the plan; updates the per-slot id history."""
     cfg = model.cfg
     table = model.W["ngram_table"]
     head_rows = table.shape[0] // cfg.ngram_heads
-    staged = (getattr(plan, "dev", None) or {}).get("ngram_rows")
-    if staged is not None:             # captured decode: the host staged the row ids, the gather runs on the device
-        return table[staged].flatten(1).float()
     hist = getattr(model, "id_history", None)
     if hist is None:
         hist = model.id_history = {}
@@ -52,7 +50,7 @@ def ngram_rows_for_plan(model, plan) -> torch.Tensor:
     ids_cpu = plan.ids.cpu()
     for s in plan.segs:
         past = hist.get(s.slot, torch.empty(0, dtype=torch.long))[: s.pos0]
-        seg_ids = ids_cpu[s.r0: s.r0 + s.n]
+        seg_ids = ids_cpu[s.r0: s.r0 + s.n].long()
         if s.parents is None:
             full = torch.cat((past, seg_ids))
             rows = L.ngram_ids(full, cfg.ngram_heads, head_rows)[s.pos0:]
@@ -67,5 +65,42 @@ def ngram_rows_for_plan(model, plan) -> torch.Tensor:
                 full = torch.cat((past, torch.tensor(chain[::-1], dtype=torch.long)))
                 rows.append(L.ngram_ids(full, cfg.ngram_heads, head_rows)[-1])
             rows = torch.stack(rows)
-        out.append(table[rows.to(table.device)].flatten(1).float())
-    return torch.cat(out, 0).to(plan.ids.device)
+        out.append(rows)
+    return torch.cat(out, 0)
+
+
+def prefetch_for_plan(model, plan):
+    """Start the host gather + upload of this forward's table rows (a host-resident table behind an `EngramTable`), so
+    that they travel while the layers before the first n-gram layer compute.  No-op for device tables and for
+    captured rounds (their rows are staged with the plan)."""
+    eng = getattr(model, "engram", None)
+    d = plan.dev
+    if eng is None or d.get("ngram_emb") is not None or d.get("ngram_rows") is not None or "ngram_fut" in d:
+        return
+    d["ngram_fut"] = eng.prefetch(row_ids_for_plan(model, plan))
+
+
+def ngram_rows_for_plan(model, plan) -> torch.Tensor:
+    """fp32 [R, heads * dim] concatenated table rows of the plan's positions; computed once per forward (all n-gram
+    layers read the same rows through their own projections)."""
+    cfg = model.cfg
+    table = model.W["ngram_table"]
+    d = plan.dev
+    if d.get("ngram_emb") is not None:     # captured round, host-resident table: the rows themselves were staged
+        return d["ngram_emb"].flatten(1).float()
+    staged = d.get("ngram_rows")
+    if staged is not None:                 # captured round, device table: the row ids were staged, gather on the device
+        return table[staged].flatten(1).float()
+    if d.get("ngram_cache") is not None:
+        return d["ngram_cache"]
+    eng = getattr(model, "engram", None)
+    if eng is not None:
+        from ..cache.engram import EngramTable
+        if "ngram_fut" not in d:
+            prefetch_for_plan(model, plan)
+        emb = EngramTable.take(d.pop("ngram_fut")).view(plan.rows, -1).float()
+    else:
+        rows = row_ids_for_plan(model, plan)
+        emb = table[rows.to(table.device)].flatten(1).float().to(plan.ids.device)
+    d["ngram_cache"] = emb
+    return emb

@@ -41,11 +41,9 @@ class LLMEngine:
                            kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
         self.graphs: Dict[tuple, RoundGraph] = {}
-        # decode rounds are captured when every layer runs on capturable kernels: hashed n-gram layers qualify when
-        # their table is resident on the device (row ids are staged by the host, the gather is captured); a
-        # host-streamed table goes through host-side gathers and runs eagerly
-        capturable = not cfg.ngram_layers or self.model.W["ngram_table"].device.type == "cuda"
-        self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda" and capturable
+        # every family captures: hashed n-gram layers get their table rows staged with the plan (row ids for a device
+        # table, the gathered rows themselves for a host-resident one)
+        self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda"
         self.stats = GenStats()
         self._rounds_since_check = 0
 

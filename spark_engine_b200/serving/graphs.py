@@ -69,7 +69,11 @@ class RoundGraph:
         self.ng_host = None
         if m.cfg.ngram_layers:
             self.ng_host = torch.zeros(R, m.cfg.ngram_heads, dtype=torch.int64).pin_memory()
-            d["ngram_rows"] = torch.zeros(R, m.cfg.ngram_heads, dtype=torch.int64, device=dev)
+            table = m.W["ngram_table"]
+            if table.device.type == "cuda":
+                d["ngram_rows"] = torch.zeros(R, m.cfg.ngram_heads, dtype=torch.int64, device=dev)
+            else:      # host-resident table: the rows themselves are gathered on the host and staged like the ids
+                d["ngram_emb"] = torch.zeros(R, m.cfg.ngram_heads, table.shape[1], dtype=table.dtype, device=dev)
         self.plan.dev = d
         self.graph = None
         self.graph_fed = None          # the same round followed by the device-side feedback of the sampled ids
@@ -108,7 +112,12 @@ class RoundGraph:
             for i, s in enumerate(self.slots):
                 row = list(ids[i]) + [ids[i][-1]] * (k - len(ids[i]))
                 self.ng_host[i * k:(i + 1) * k] = torch.tensor(chain_row_ids(m, s, pos0[i], row), dtype=torch.int64)
-            self.plan.dev["ngram_rows"].copy_(self.ng_host, non_blocking=True)
+            if "ngram_rows" in self.plan.dev:
+                self.plan.dev["ngram_rows"].copy_(self.ng_host, non_blocking=True)
+            else:
+                from ..cache.engram import EngramTable
+                emb = EngramTable.take(m.engram.prefetch(self.ng_host))
+                self.plan.dev["ngram_emb"].copy_(emb.view_as(self.plan.dev["ngram_emb"]))
 
     def set_kv(self):
         m = self.m

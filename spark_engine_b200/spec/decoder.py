@@ -81,10 +81,8 @@ class SpecDecoder:
         self.m = model
         self.graphs = None
         if graphs and model.device.type == "cuda":
-            capturable = not model.cfg.ngram_layers or model.W["ngram_table"].device.type == "cuda"
-            if capturable:
-                from ..serving.graphs import SpecGraphs
-                self.graphs = SpecGraphs(model)
+            from ..serving.graphs import SpecGraphs
+            self.graphs = SpecGraphs(model)
         self.depth, self.policy, self.theta, self.tau = depth, policy, theta, tau
         self.cost = cost or P.CostModel()
         self.max_rows = max_rows

@@ -60,3 +60,27 @@ def test_integer_chain_row_ids_equal_the_tensor_hash():
     again = chain_row_ids(m, 0, 12, ids[12:15].tolist())
     assert torch.equal(torch.tensor(again), ref[12:15])
     assert m.id_history[0].tolist() == ids[:15].tolist()
+
+
+@pytest.mark.gpu
+def test_host_resident_table_feeds_the_model_eager_and_under_graphs():
+    """DS-style model with its hashed n-gram table left on the host: rows come through the asynchronous gather ring
+    (prefetched at the start of a forward, staged with the plan for captured rounds) and the tokens equal those of the
+    same model with the table on the device."""
+    from spark_engine_b200.config import EngineConfig, get_model_config, scaled_down
+    from spark_engine_b200.models.weights import init_weights, to_device
+    from spark_engine_b200.serving.engine import LLMEngine
+    cfg = scaled_down(get_model_config("ds4-style"))
+    cfg.mtp_layers = 0
+    assert cfg.ngram_layers
+    W = to_device(init_weights(cfg, seed=0), "cuda")
+    Wh = dict(W)
+    Wh["ngram_table"] = W["ngram_table"].cpu()
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (2, 40), generator=g).tolist()
+    ref = LLMEngine(cfg, W, EngineConfig(cuda_graphs=True, prefill_chunk=16), max_seqs=2, kv_tokens_per_seq=256).generate(prompts, 8)
+    for graphs in (False, True):
+        eng = LLMEngine(cfg, Wh, EngineConfig(cuda_graphs=graphs, prefill_chunk=16), max_seqs=2, kv_tokens_per_seq=256)
+        assert eng.model.engram is not None and eng.use_graphs == graphs
+        assert eng.generate(prompts, 8) == ref, f"graphs={graphs}"
+        assert eng.model.engram.stats["requests"] > 0
