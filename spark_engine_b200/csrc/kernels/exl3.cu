@@ -33,27 +33,71 @@ __global__ void exl3_reconstruct_kernel(const uint32_t* __restrict__ trellis, __
 }
 
 // y[r, :] = had128(x[r, :] * scale[:]) (pre) or had128(x[r, :]) * scale[:] (post); 128-blocks along the row.
+// One warp per 128-block: a lane keeps 4 consecutive elements (one 8- or 16-byte load), the strides 1 and 2 of the
+// butterfly run in registers and the strides 4..64 through five shuffles -- the same additions in the same order as a
+// shared-memory butterfly, without its 14 barriers per block (this pass was 0.76 TB/s as one block per CTA).
+template <typename T> __device__ __forceinline__ void ld4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void ld4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void ld4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
+}
+__device__ __forceinline__ void st4(__half* p, const float (&v)[4]) {
+  const __half2 a = __floats2half2_rn(v[0], v[1]), c = __floats2half2_rn(v[2], v[3]);
+  uint2 o; o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&c);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), c = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 o; o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&c);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
 template <typename TI, typename TOUT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 exl3_had_rows_kernel(const TI* __restrict__ x, int ldx, const __half* __restrict__ scale, TOUT* __restrict__ y, int ldy,
-                     int post, const int* __restrict__ row_expert, long long expert_stride) {
-  __shared__ float b[128];
-  const int r = blockIdx.x, blk = blockIdx.y, t = threadIdx.x;
-  float v = static_cast<float>(x[static_cast<size_t>(r) * ldx + blk * 128 + t]);
+                     int post, const int* __restrict__ row_expert, long long expert_stride, int nblk, long long total) {
+  const int lane = threadIdx.x & 31;
+  const long long w = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);      // (row, 128-block) of this warp
+  if (w >= total) return;
+  const int r = static_cast<int>(w / nblk), blk = static_cast<int>(w - static_cast<long long>(r) * nblk);
+  const int c0 = blk * 128 + lane * 4;
+  float v[4];
+  ld4(x + static_cast<size_t>(r) * ldx + c0, v);
   const __half* srow = scale + (row_expert ? row_expert[r] * expert_stride : 0);
-  const float sc = __half2float(srow[blk * 128 + t]);
-  if (!post) v *= sc;
-  b[t] = v;
-  __syncthreads();
-  for (int st = 1; st < 128; st <<= 1) {
-    const float me = b[t], other = b[t ^ st];
-    __syncthreads();
-    b[t] = (t & st) ? other - me : me + other;
-    __syncthreads();
+  const uint2 sraw = *reinterpret_cast<const uint2*>(srow + c0);
+  const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw.x));
+  const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw.y));
+  const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
+  if (!post) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] *= sc[i];
   }
-  v = b[t] * 0.08838834764831845f;
-  if (post) v *= sc;
-  y[static_cast<size_t>(r) * ldy + blk * 128 + t] = static_cast<TOUT>(v);
+  // strides 1, 2: inside the lane (element i pairs with i ^ stride; the upper one takes lower - upper)
+  {
+    const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+    v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+  }
+  // strides 4 .. 64: lane ^ 1 .. lane ^ 16
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], m);
+      v[i] = (lane & m) ? other - v[i] : v[i] + other;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[i] *= 0.08838834764831845f;
+    if (post) v[i] *= sc[i];
+  }
+  st4(y + static_cast<size_t>(r) * ldy + c0, v);
 }
 
 }  // namespace spark
@@ -75,8 +119,11 @@ extern "C" int spark_exl3_had_rows(const void* x, int ldx, const void* scale, vo
                                    const int* row_expert, cudaStream_t s, long long expert_stride) {
   if (R <= 0) return 0;
   if (C & 127) return -5;
-  dim3 grid(R, C / 128);
-  if (!post) exl3_had_rows_kernel<__nv_bfloat16, __half><<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ldx, (const __half*)scale, (__half*)y, ldy, 0, row_expert, expert_stride);
-  else exl3_had_rows_kernel<float, __nv_bfloat16><<<grid, 128, 0, s>>>((const float*)x, ldx, (const __half*)scale, (__nv_bfloat16*)y, ldy, 1, row_expert, expert_stride);
+  if ((ldx & 3) || (ldy & 3)) return -5;               // 8- / 16-byte vector accesses along the rows
+  const int nblk = C / 128;
+  const long long total = static_cast<long long>(R) * nblk;
+  const unsigned grid = static_cast<unsigned>((total + 7) / 8);
+  if (!post) exl3_had_rows_kernel<__nv_bfloat16, __half><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, (const __half*)scale, (__half*)y, ldy, 0, row_expert, expert_stride, nblk, total);
+  else exl3_had_rows_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>((const float*)x, ldx, (const __half*)scale, (__nv_bfloat16*)y, ldy, 1, row_expert, expert_stride, nblk, total);
   return spark_launch_rc(__func__);
 }

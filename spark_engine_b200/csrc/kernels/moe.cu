@@ -416,25 +416,36 @@ __global__ void moe_hist_kernel(const int* __restrict__ ids, int P, int E, int* 
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) block_hist[static_cast<size_t>(blockIdx.x) * E + e] = sh[e];
 }
-// one CTA: exclusive scan over blocks per expert, expert offsets, tile list
+// one CTA: exclusive scan over blocks per expert, expert offsets, tile list.  Every step is parallel over the experts
+// (two block-wide scans: rows per expert -> offsets, tiles per expert -> first tile), each expert's thread writes its
+// own tiles; a single thread walking the 512 experts took 72 us per layer of a prefill chunk.
 __global__ void __launch_bounds__(1024)
 moe_scan_kernel(int* __restrict__ block_hist, int nblocks, int E, int* __restrict__ offsets,
                 int4* __restrict__ tile_list, int* __restrict__ tile_count) {
-  extern __shared__ int tot[];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+  extern __shared__ int tot[];                         // [E]
+  __shared__ int sa[1024], sb[1024];
+  const int e = threadIdx.x;
+  int mine = 0;
+  if (e < E) {
     int acc = 0;
     for (int b = 0; b < nblocks; ++b) { int c = block_hist[static_cast<size_t>(b) * E + e]; block_hist[static_cast<size_t>(b) * E + e] = acc; acc += c; }
     tot[e] = acc;
+    mine = acc;
   }
+  const int my_tiles = (mine + 127) / 128;
+  sa[e] = mine; sb[e] = my_tiles;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      offsets[e] = acc;
-      for (int r0 = 0; r0 < tot[e]; r0 += 128) tile_list[nt++] = make_int4(acc + r0, acc + tot[e], e, 0);
-      acc += tot[e];
-    }
-    offsets[E] = acc; *tile_count = nt;
+  for (int st = 1; st < 1024; st <<= 1) {               // inclusive scans of rows and of tiles
+    const int a = e >= st ? sa[e - st] : 0, b = e >= st ? sb[e - st] : 0;
+    __syncthreads();
+    sa[e] += a; sb[e] += b;
+    __syncthreads();
+  }
+  if (e < E) {
+    const int off = sa[e] - mine, t0 = sb[e] - my_tiles;
+    offsets[e] = off;
+    for (int i = 0; i < my_tiles; ++i) tile_list[t0 + i] = make_int4(off + i * 128, off + mine, e, 0);
+    if (e == E - 1) { offsets[E] = sa[e]; *tile_count = sb[e]; }
   }
 }
 __global__ void moe_place_kernel(const int* __restrict__ ids, int P, int E, const int* __restrict__ block_hist,
@@ -496,6 +507,7 @@ extern "C" int spark_moe_route(const float* logits, int ld, int R, int E, int to
 extern "C" int spark_moe_sort(const int* ids, int P, int E, int* perm, int* inv_perm, int* offsets, void* tile_list,
                               int* tile_count, int* block_hist, cudaStream_t s) {
   if (P <= 0) return 0;
+  if (E > 1024) return -5;                     // one thread per expert in the scan
   if (P <= 2048) {
     moe_sort_kernel<<<1, 1024, (2 * E + 1) * sizeof(int), s>>>(ids, P, E, perm, inv_perm, offsets, (int4*)tile_list, tile_count);
   } else {

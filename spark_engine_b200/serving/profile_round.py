@@ -3,7 +3,7 @@
     ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv --log-file launches.csv \\
         python -m spark_engine_b200.serving.profile_round --layers 4 --streams 4
 
-(one pass per launch: nothing is saved or restored).  `--summary launches.csv` prints the per-kernel table of the last
+(one pass per launch: nothing is saved or restored).  `--prefill 1024` profiles two prefill chunks instead.  `--summary launches.csv` prints the per-kernel table of the last
 round of such a capture.  Eager on purpose: every kernel of a round is its own launch with its own duration.
 """
 from __future__ import annotations
@@ -26,6 +26,15 @@ def run(a):
     prompts = torch.randint(0, cfg.vocab, (a.streams, a.prompt), generator=g).tolist()
     cur = [int(torch.argmax(eng.prefill(s, prompts[s]))) for s in range(a.streams)]
     slots = list(range(a.streams))
+    if a.prefill:                      # one more prefill chunk of the first prompt, profiled
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStart()
+        for _ in range(2):
+            eng.prefill(0, prompts[0][: a.prefill], chunk=a.prefill)
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
+        print("done prefill")
+        return
     for _ in range(3):
         cur = eng.decode_round(slots, cur)
     torch.cuda.synchronize()
@@ -61,6 +70,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--streams", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--prefill", type=int, default=0, help="profile two prefill chunks of this many tokens instead of decode rounds")
     ap.add_argument("--summary", default="")
     a = ap.parse_args()
     if a.summary:
