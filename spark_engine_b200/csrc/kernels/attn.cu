@@ -288,6 +288,7 @@ struct AttnDecodeArgs {
   const int* pos; const long long* row_kv; const int* sel; const int* sel_n; int sel_ld;
   const int* row_pos0; const int* row_j; const uint32_t* anc;     // optional (tree verify / explicit in-flight index)
   float* part_o; float* part_ml; int Hq, Hkv; float scale;
+  int chunks;                        // 64-token tiles per split (>= 1)
 };
 
 constexpr int ATT_ROWS = 16;       // q heads per kv head, padded to the MMA's M
@@ -296,6 +297,7 @@ template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
 attn_decode_tc_kernel(const __grid_constant__ AttnDecodeArgs a) {
   constexpr int LD = D + 8;                                   // bf16 elements per tile row (16-byte padded)
+  constexpr int NT = D / 32;                                  // 8-wide dim tiles per warp
   extern __shared__ __align__(16) uint8_t smem_att[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_att);                  // [16][LD]
   __nv_bfloat16* Ks = Qs + ATT_ROWS * LD;                                           // [64][LD]
@@ -306,6 +308,7 @@ attn_decode_tc_kernel(const __grid_constant__ AttnDecodeArgs a) {
   float* ksc = reinterpret_cast<float*>(stok + ATT_TS);                             // [64]
   float* vsc = ksc + ATT_TS;                                                        // [64]
   uint8_t* stage = reinterpret_cast<uint8_t*>(vsc + ATT_TS);                        // FP8: [2][64][D] bytes
+  __shared__ float m_run[ATT_ROWS], l_run[ATT_ROWS], alpha[ATT_ROWS];
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
@@ -313,136 +316,155 @@ attn_decode_tc_kernel(const __grid_constant__ AttnDecodeArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int pos0 = a.row_pos0 ? a.row_pos0[r] : 0;
   const int n_ctx = a.sel ? a.sel_n[r] : (a.row_pos0 ? pos0 + a.row_j[r] + 1 : a.pos[r] + 1);
-  const int t0 = sp * ATT_TS;
+  // a split is `chunks` tiles of 64 tokens walked in order with a running (max, sum): decode rounds use one tile per
+  // split (parallelism over splits), prefill-size batches walk the whole row in one CTA (no partials to merge)
+  const int span = a.chunks * ATT_TS;
+  const int s0 = sp * span;
   const size_t pbase = (static_cast<size_t>(r) * a.Hq + hk * rep) * nsplit + sp;
-  if (t0 >= n_ctx) {                     // empty split: neutral partial
+  if (s0 >= n_ctx) {                     // empty split: neutral partial
     if (tid < rep) { a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2] = -INFINITY; a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2 + 1] = 0.f; }
     return;
   }
-  const int nt = min(ATT_TS, n_ctx - t0);
+  const int s1 = min(n_ctx, s0 + span);
   const long long base = a.row_kv[r];
   const uint32_t anc = a.anc ? a.anc[r] : 0xffffffffu;
-  if (tid < ATT_TS) {
-    int tk = -1;
-    if (tid < nt) {
-      tk = a.sel ? a.sel[static_cast<size_t>(r) * a.sel_ld + t0 + tid] : t0 + tid;
-      if (a.anc && tk >= pos0 && !((anc >> min(tk - pos0, 31)) & 1u)) tk = -1;      // not an ancestor of this row
-    }
-    stok[tid] = tk;
-    if (FP8) {
-      ksc[tid] = tk >= 0 ? a.ks[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
-      vsc[tid] = tk >= 0 ? a.vs[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
-    }
-  }
-  __syncthreads();
-  // ---- request the whole split: K and V rows (16-byte pieces), zero rows for masked / missing tokens
-  constexpr int ROWB = FP8 ? D : D * 2;                       // bytes per token row in the cache
-  constexpr int CH = ROWB / 16;
-  for (int i = tid; i < ATT_TS * CH; i += 128) {
-    const int tok = i / CH, c = i - tok * CH;
-    const int tk = stok[tok];
-    uint8_t* dk = FP8 ? stage + tok * D + c * 16 : reinterpret_cast<uint8_t*>(Ks + tok * LD) + c * 16;
-    uint8_t* dv = FP8 ? stage + (ATT_TS + tok) * D + c * 16 : reinterpret_cast<uint8_t*>(Vs + tok * LD) + c * 16;
-    if (tk >= 0) {
-      const size_t off = (static_cast<size_t>(base + tk) * a.Hkv + hk) * ROWB + c * 16;
-      cp_async16(dk, reinterpret_cast<const uint8_t*>(a.kc) + off);
-      cp_async16(dv, reinterpret_cast<const uint8_t*>(a.vc) + off);
-    } else {
-      *reinterpret_cast<uint4*>(dk) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(dv) = make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
+  if (tid < ATT_ROWS) { m_run[tid] = -INFINITY; l_run[tid] = 0.f; alpha[tid] = 1.f; }
   for (int i = tid; i < ATT_ROWS * (D / 8); i += 128) {       // queries of the heads that share this kv head
     const int h = i / (D / 8), c = i - h * (D / 8);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (h < rep) v = *reinterpret_cast<const uint4*>(a.qbuf + (static_cast<size_t>(r) * a.Hq + hk * rep + h) * D + c * 8);
     *reinterpret_cast<uint4*>(Qs + h * LD + c * 8) = v;
   }
-  cp_async_wait_all();
-  __syncthreads();
-  if (FP8) {                                                  // e4m3 bytes -> bf16 tiles (scales applied to S and P)
-    for (int i = tid; i < ATT_TS * (D / 4); i += 128) {
-      const int tok = i / (D / 4), c = i - tok * (D / 4);
+  float o[NT][4];
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(stage + (which * ATT_TS + tok) * D + c * 4);
-        const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
-        __nv_bfloat162 b0 = __floats2bfloat162_rn(static_cast<float>(f8[0]), static_cast<float>(f8[1]));
-        __nv_bfloat162 b1 = __floats2bfloat162_rn(static_cast<float>(f8[2]), static_cast<float>(f8[3]));
-        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
-        *reinterpret_cast<uint2*>((which ? Vs : Ks) + tok * LD + c * 4) = o;
+  for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+
+  for (int t0 = s0; t0 < s1; t0 += ATT_TS) {
+    const int nt = min(ATT_TS, s1 - t0);
+    if (tid < ATT_TS) {
+      int tk = -1;
+      if (tid < nt) {
+        tk = a.sel ? a.sel[static_cast<size_t>(r) * a.sel_ld + t0 + tid] : t0 + tid;
+        if (a.anc && tk >= pos0 && !((anc >> min(tk - pos0, 31)) & 1u)) tk = -1;      // not an ancestor of this row
+      }
+      stok[tid] = tk;
+      if (FP8) {
+        ksc[tid] = tk >= 0 ? a.ks[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
+        vsc[tid] = tk >= 0 ? a.vs[static_cast<size_t>(base + tk) * a.Hkv + hk] : 0.f;
       }
     }
     __syncthreads();
-  }
-  // ---- S = Q K^T: warp w owns tokens [16w, 16w + 16)
-  {
-    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-    const __nv_bfloat16* q_lo = Qs + g * LD + 2 * t;
-    const __nv_bfloat16* q_hi = Qs + (g + 8) * LD + 2 * t;
-    const __nv_bfloat16* k0 = Ks + (warp * 16 + g) * LD + 2 * t;
-    const __nv_bfloat16* k1 = Ks + (warp * 16 + 8 + g) * LD + 2 * t;
+    // ---- request the whole tile: K and V rows (16-byte pieces), zero rows for masked / missing tokens
+    constexpr int ROWB = FP8 ? D : D * 2;                       // bytes per token row in the cache
+    constexpr int CH = ROWB / 16;
+    for (int i = tid; i < ATT_TS * CH; i += 128) {
+      const int tok = i / CH, c = i - tok * CH;
+      const int tk = stok[tok];
+      uint8_t* dk = FP8 ? stage + tok * D + c * 16 : reinterpret_cast<uint8_t*>(Ks + tok * LD) + c * 16;
+      uint8_t* dv = FP8 ? stage + (ATT_TS + tok) * D + c * 16 : reinterpret_cast<uint8_t*>(Vs + tok * LD) + c * 16;
+      if (tk >= 0) {
+        const size_t off = (static_cast<size_t>(base + tk) * a.Hkv + hk) * ROWB + c * 16;
+        cp_async16(dk, reinterpret_cast<const uint8_t*>(a.kc) + off);
+        cp_async16(dv, reinterpret_cast<const uint8_t*>(a.vc) + off);
+      } else {
+        *reinterpret_cast<uint4*>(dk) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dv) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    if (FP8) {                                                  // e4m3 bytes -> bf16 tiles (scales applied to S and P)
+      for (int i = tid; i < ATT_TS * (D / 4); i += 128) {
+        const int tok = i / (D / 4), c = i - tok * (D / 4);
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t raw = *reinterpret_cast<const uint32_t*>(stage + (which * ATT_TS + tok) * D + c * 4);
+          const __nv_fp8_e4m3* f8 = reinterpret_cast<const __nv_fp8_e4m3*>(&raw);
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(static_cast<float>(f8[0]), static_cast<float>(f8[1]));
+          __nv_bfloat162 b1 = __floats2bfloat162_rn(static_cast<float>(f8[2]), static_cast<float>(f8[3]));
+          uint2 ov; ov.x = *reinterpret_cast<uint32_t*>(&b0); ov.y = *reinterpret_cast<uint32_t*>(&b1);
+          *reinterpret_cast<uint2*>((which ? Vs : Ks) + tok * LD + c * 4) = ov;
+        }
+      }
+      __syncthreads();
+    }
+    // ---- S = Q K^T: warp w owns tokens [16w, 16w + 16)
+    {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* q_lo = Qs + g * LD + 2 * t;
+      const __nv_bfloat16* q_hi = Qs + (g + 8) * LD + 2 * t;
+      const __nv_bfloat16* k0 = Ks + (warp * 16 + g) * LD + 2 * t;
+      const __nv_bfloat16* k1 = Ks + (warp * 16 + 8 + g) * LD + 2 * t;
 #pragma unroll 4
-    for (int kk = 0; kk < D / 16; ++kk) {
-      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16);
-      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 8);
-      mma_bf16_16816(c0, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k0 + kk * 16), *reinterpret_cast<const uint32_t*>(k0 + kk * 16 + 8));
-      mma_bf16_16816(c1, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k1 + kk * 16), *reinterpret_cast<const uint32_t*>(k1 + kk * 16 + 8));
-    }
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(q_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(q_hi + kk * 16 + 8);
+        mma_bf16_16816(c0, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k0 + kk * 16), *reinterpret_cast<const uint32_t*>(k0 + kk * 16 + 8));
+        mma_bf16_16816(c1, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(k1 + kk * 16), *reinterpret_cast<const uint32_t*>(k1 + kk * 16 + 8));
+      }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const float* c = j ? c1 : c0;
+      for (int j = 0; j < 2; ++j) {
+        const float* c = j ? c1 : c0;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = g + (e >> 1) * 8, tok = warp * 16 + j * 8 + 2 * t + (e & 1);
-        float v = c[e] * a.scale;
-        if (FP8) v *= ksc[tok];
-        Ss[row * 68 + tok] = stok[tok] >= 0 ? v : -INFINITY;
+        for (int e = 0; e < 4; ++e) {
+          const int row = g + (e >> 1) * 8, tok = warp * 16 + j * 8 + 2 * t + (e & 1);
+          float v = c[e] * a.scale;
+          if (FP8) v *= ksc[tok];
+          Ss[row * 68 + tok] = stok[tok] >= 0 ? v : -INFINITY;
+        }
       }
     }
-  }
-  __syncthreads();
-  // ---- softmax statistics of the split; P in bf16 (the row sum uses the same rounded values)
-  for (int row = warp * 4; row < warp * 4 + 4; ++row) {
-    const float s0 = Ss[row * 68 + lane], s1 = Ss[row * 68 + lane + 32];
-    const float m = warp_max(fmaxf(s0, s1));
-    float p0 = m == -INFINITY ? 0.f : __expf(s0 - m), p1 = m == -INFINITY ? 0.f : __expf(s1 - m);
-    p0 = __bfloat162float(__float2bfloat16(p0)); p1 = __bfloat162float(__float2bfloat16(p1));
-    const float l = warp_sum(p0 + p1);
-    Ps[row * 72 + lane] = __float2bfloat16(FP8 ? p0 * vsc[lane] : p0);
-    Ps[row * 72 + lane + 32] = __float2bfloat16(FP8 ? p1 * vsc[lane + 32] : p1);
-    if (lane == 0 && row < rep) {
-      a.part_ml[(pbase + static_cast<size_t>(row) * nsplit) * 2] = m;
-      a.part_ml[(pbase + static_cast<size_t>(row) * nsplit) * 2 + 1] = l;
-    }
-  }
-  __syncthreads();
-  // ---- O = P V: warp w owns dims [w D/4, (w+1) D/4)
-  {
-    constexpr int NT = D / 32;                                // 8-wide dim tiles per warp
-    float o[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
-    const __nv_bfloat16* p_lo = Ps + g * 72 + 2 * t;
-    const __nv_bfloat16* p_hi = Ps + (g + 8) * 72 + 2 * t;
-#pragma unroll
-    for (int kk = 0; kk < ATT_TS / 16; ++kk) {
-      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16);
-      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16 + 8);
-      const __nv_bfloat16* vrow = Vs + (kk * 16 + (lane & 15)) * LD + warp * (D / 4);
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        uint32_t b0, b1;
-        ldmatrix_x2_trans(b0, b1, vrow + j * 8);
-        mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+    __syncthreads();
+    // ---- running softmax statistics; P in bf16 relative to the new running maximum (the row sum uses the same
+    //      rounded values); alpha rescales what was accumulated under the old maximum
+    for (int row = warp * 4; row < warp * 4 + 4; ++row) {
+      const float s0v = Ss[row * 68 + lane], s1v = Ss[row * 68 + lane + 32];
+      const float mo = m_run[row];
+      const float m = fmaxf(mo, warp_max(fmaxf(s0v, s1v)));
+      float p0 = m == -INFINITY ? 0.f : __expf(s0v - m), p1 = m == -INFINITY ? 0.f : __expf(s1v - m);
+      p0 = __bfloat162float(__float2bfloat16(p0)); p1 = __bfloat162float(__float2bfloat16(p1));
+      const float l = warp_sum(p0 + p1);
+      Ps[row * 72 + lane] = __float2bfloat16(FP8 ? p0 * vsc[lane] : p0);
+      Ps[row * 72 + lane + 32] = __float2bfloat16(FP8 ? p1 * vsc[lane + 32] : p1);
+      if (lane == 0) {
+        const float al = (mo == -INFINITY) ? 0.f : __expf(mo - m);
+        alpha[row] = al;
+        l_run[row] = l_run[row] * al + l;
+        m_run[row] = m;
       }
     }
+    __syncthreads();
+    // ---- O = alpha O + P V: warp w owns dims [w D/4, (w+1) D/4)
+    {
+      const float al_lo = alpha[g], al_hi = alpha[g + 8];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      const int d = warp * (D / 4) + j * 8 + 2 * t;
-      if (g < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g) * nsplit) * D + d) = make_float2(o[j][0], o[j][1]);
-      if (g + 8 < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g + 8) * nsplit) * D + d) = make_float2(o[j][2], o[j][3]);
+      for (int j = 0; j < NT; ++j) { o[j][0] *= al_lo; o[j][1] *= al_lo; o[j][2] *= al_hi; o[j][3] *= al_hi; }
+      const __nv_bfloat16* p_lo = Ps + g * 72 + 2 * t;
+      const __nv_bfloat16* p_hi = Ps + (g + 8) * 72 + 2 * t;
+#pragma unroll
+      for (int kk = 0; kk < ATT_TS / 16; ++kk) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16), a1 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(p_lo + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t*>(p_hi + kk * 16 + 8);
+        const __nv_bfloat16* vrow = Vs + (kk * 16 + (lane & 15)) * LD + warp * (D / 4);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          uint32_t b0, b1;
+          ldmatrix_x2_trans(b0, b1, vrow + j * 8);
+          mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+        }
+      }
     }
+    __syncthreads();                     // the next tile overwrites K, V, P and the token list
+  }
+  if (tid < rep) {
+    a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2] = m_run[tid];
+    a.part_ml[(pbase + static_cast<size_t>(tid) * nsplit) * 2 + 1] = l_run[tid];
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int d = warp * (D / 4) + j * 8 + 2 * t;
+    if (g < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g) * nsplit) * D + d) = make_float2(o[j][0], o[j][1]);
+    if (g + 8 < rep) *reinterpret_cast<float2*>(a.part_o + (pbase + static_cast<size_t>(g + 8) * nsplit) * D + d) = make_float2(o[j][2], o[j][3]);
   }
 }
 
@@ -515,18 +537,18 @@ static int attn_decode_launch(const void* qbuf, const void* kc, const void* vc, 
                               const int* pos, const long long* row_kv, const int* sel, const int* sel_n, int sel_ld,
                               const int* row_pos0, const int* row_j, const uint32_t* anc, float* part_o, float* part_ml,
                               int nsplit, const void* qkv, int ld, int gated, int R, int Hq, int Hkv, int D, float scale,
-                              void* out, cudaStream_t s, bool pdl) {
+                              void* out, cudaStream_t s, bool pdl, int chunks = 1) {
   dim3 grid(R, Hkv, nsplit);
   const int rep = Hq / Hkv;
   cudaError_t err;
   if ((D == 64 || D == 128 || D == 256) && rep <= ATT_ROWS && (row_pos0 == nullptr) == (row_j == nullptr)) {
     AttnDecodeArgs a{(const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld, row_pos0, row_j, anc,
-                     part_o, part_ml, Hq, Hkv, scale};
+                     part_o, part_ml, Hq, Hkv, scale, chunks < 1 ? 1 : chunks};
     if (D == 64) err = fp8 ? launch_decode_tc<64, true>(a, grid, s, pdl) : launch_decode_tc<64, false>(a, grid, s, pdl);
     else if (D == 128) err = fp8 ? launch_decode_tc<128, true>(a, grid, s, pdl) : launch_decode_tc<128, false>(a, grid, s, pdl);
     else err = fp8 ? launch_decode_tc<256, true>(a, grid, s, pdl) : launch_decode_tc<256, false>(a, grid, s, pdl);
   } else {
-    if (D > 256 || rep > ATT_MAXREP || anc != nullptr) return -5;
+    if (D > 256 || rep > ATT_MAXREP || anc != nullptr || chunks > 1) return -5;
     if (fp8)
       attn_decode_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)qbuf, kc, vc, ks, vs, pos, row_kv, sel, sel_n, sel_ld,
                                                     part_o, part_ml, Hq, Hkv, D, scale);
@@ -552,10 +574,10 @@ extern "C" int spark_attn_decode(const void* qbuf, const void* kc, const void* v
                                  int fp8, const int* pos, const long long* row_kv, const int* sel, const int* sel_n,
                                  int sel_ld, float* part_o, float* part_ml, int nsplit, const void* qkv, int ld,
                                  int gated, int R, int Hq, int Hkv, int D, float scale, void* out, cudaStream_t s,
-                                 const int* row_pos0, const int* row_j, const unsigned* anc) {
+                                 const int* row_pos0, const int* row_j, const unsigned* anc, int chunks) {
   if (R <= 0) return 0;
   return attn_decode_launch(qbuf, kc, vc, ks, vs, fp8, pos, row_kv, sel, sel_n, sel_ld, row_pos0, row_j, anc, part_o, part_ml,
-                            nsplit, qkv, ld, gated, R, Hq, Hkv, D, scale, out, s, true);
+                            nsplit, qkv, ld, gated, R, Hq, Hkv, D, scale, out, s, true, chunks);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -63,7 +63,7 @@ _SIGS = {
     "spark_attn_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
                         vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     "spark_attn_decode": [vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                          f32, vp, vp, vp, vp, vp],
+                          f32, vp, vp, vp, vp, vp, i32],
     "spark_moe_route": [vp, i32, i32, i32, i32, i32, vp, f32, i32, vp, vp, vp, vp, vp, i32, i32],
     "spark_moe_sort": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp],
     "spark_moe_combine": [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, vp, vp, vp],
@@ -1111,7 +1111,11 @@ def attn_mixer(mixer, qkv, plan, seqs):
                                       c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), stream())
         check(rc, "spark_attn_prefill")
         return out
-    nsplit = (max_ctx + ATT_TS - 1) // ATT_TS
+    nsplit, chunks = (max_ctx + ATT_TS - 1) // ATT_TS, 1
+    if R >= 64 and c.head_dim in (64, 128, 256) and c.n_q_heads // c.n_kv_heads <= 16:
+        # prefill-size batches have rows enough to fill the GPU: one CTA walks a row's whole context with a running
+        # softmax, so no per-split partials are written and merged (2.2 GB of them for a 4096-row chunk at 2K tokens each)
+        nsplit, chunks = 1, nsplit
     part_o = scratch("attn_part_o", R * c.n_q_heads * nsplit * c.head_dim, torch.float32, dev)
     part_ml = scratch("attn_part_ml", R * c.n_q_heads * nsplit * 2, torch.float32, dev)
     out = torch.empty(R, c.n_q_heads * c.head_dim, dtype=torch.bfloat16, device=dev)
@@ -1120,6 +1124,6 @@ def attn_mixer(mixer, qkv, plan, seqs):
                                  P(sel_n), sel_ld, P(part_o), P(part_ml), nsplit, P(qkv), qkv.stride(0), int(c.gated), R,
                                  c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), P(out), stream(),
                                  P(d["row_pos0"]) if tree else None, P(d["row_j"]) if tree else None,
-                                 P(d["anc"]) if tree else None)
+                                 P(d["anc"]) if tree else None, chunks)
     check(rc, "spark_attn_decode")
     return out

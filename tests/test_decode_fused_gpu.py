@@ -206,8 +206,8 @@ def test_decode_attention_tensor_core_kernel(D, Hq, Hkv, fp8):
     scale = 1.0 / math.sqrt(D)
     qkv = torch.zeros(R, 8, device=DEV).bfloat16()
 
-    def run(sel=None, sel_n=None, tree=False, anc=None, max_ctx=None):
-        nsplit = (max_ctx + 63) // 64
+    def run(sel=None, sel_n=None, tree=False, anc=None, max_ctx=None, chunks=1):
+        nsplit = ((max_ctx + 63) // 64 + chunks - 1) // chunks
         part_o = torch.empty(R * Hq * nsplit * D, device=DEV)
         part_ml = torch.empty(R * Hq * nsplit * 2, device=DEV)
         out = torch.empty(R, Hq * D, dtype=torch.bfloat16, device=DEV)
@@ -215,7 +215,7 @@ def test_decode_attention_tensor_core_kernel(D, Hq, Hkv, fp8):
                                    kv_base.data_ptr(), c.P(sel), c.P(sel_n), 0 if sel is None else sel.shape[1], part_o.data_ptr(),
                                    part_ml.data_ptr(), nsplit, qkv.data_ptr(), qkv.stride(0), 0, R, Hq, Hkv, D, scale,
                                    out.data_ptr(), c.stream(), pos0.data_ptr() if tree else None,
-                                   row_j.data_ptr() if tree else None, c.P(anc))
+                                   row_j.data_ptr() if tree else None, c.P(anc), chunks)
         assert rc == 0
         return out.float().view(R, Hq, D)
 
@@ -243,6 +243,13 @@ def test_decode_attention_tensor_core_kernel(D, Hq, Hkv, fp8):
         vis.append(ch)
     got = run(sel=sel, sel_n=sel_n, max_ctx=200)
     assert rel_err(got, ref(vis)) < 2e-2
+    # several 64-token tiles per split with a running softmax (what prefill-size batches use): 2 tiles per split, and
+    # the whole row in one split
+    for chunks in (2, 4):
+        got = run(sel=sel, sel_n=sel_n, max_ctx=200, chunks=chunks)
+        assert rel_err(got, ref(vis)) < 2e-2, chunks
+    got = run(max_ctx=int(pos.max()) + 1, chunks=(int(pos.max()) + 64) // 64)
+    assert rel_err(got, want) < 2e-2
     # tree rows: sequence 0 has three in-flight rows, row 2 is a sibling of row 1 (both children of row 0)
     anc = torch.tensor([0b001, 0b011, 0b101, 0b01, 0b11], dtype=torch.int32, device=DEV)
     got = run(tree=True, anc=anc, max_ctx=int((pos0 + row_j).max()) + 1)

@@ -43,7 +43,7 @@ def test_noalloc_entry_point_matches_regular_one_twice():
         rc = cu.lib().spark_attn_decode(qbuf.data_ptr(), kc.data_ptr(), vc.data_ptr(), None, None, 0, pos.data_ptr(),
                                         row_kv.data_ptr(), None, None, 0, part_o.data_ptr(), part_ml.data_ptr(), nsplit,
                                         qkv.data_ptr(), qkv.stride(0), 1, R, Hq, Hkv, D, scale, ref.data_ptr(), cu.stream(),
-                                        None, None, None)
+                                        None, None, None, 1)
         assert rc == 0
         rc = fn(qbuf.data_ptr(), kc.data_ptr(), vc.data_ptr(), None, None, 0, pos.data_ptr(), row_kv.data_ptr(), None, None,
                 0, nsplit, qkv.data_ptr(), qkv.stride(0), 1, R, Hq, Hkv, D, scale, out.data_ptr(), cu.stream())
