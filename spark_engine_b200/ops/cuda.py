@@ -910,8 +910,13 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None, accepted=None):
         mixer._gate_w = (w["f_b"].to(torch.bfloat16).contiguous(), w["g_b"].to(torch.bfloat16).contiguous())
     pre = _as_bf16(pre)
     lr = _as_bf16(lr)
-    g1 = dense_linear(lr[:, :r].contiguous(), mixer._gate_w[0], out_f32=True)
-    g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
+    if pre.shape[0] <= 16 and lr.stride(0) % 8 == 0 and r % 8 == 0 and lr.data_ptr() % 16 == 0:
+        # decode rows: the GEMV reads the two low-rank halves in place (row stride of `lr`; 16-byte aligned rows)
+        g1 = gemv_bf16(lr[:, :r], mixer._gate_w[0], out_f32=True, ldx=lr.stride(0))
+        g2 = gemv_bf16(lr[:, r: 2 * r], mixer._gate_w[1], out_f32=True, ldx=lr.stride(0))
+    else:
+        g1 = dense_linear(lr[:, :r].contiguous(), mixer._gate_w[0], out_f32=True)
+        g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
     R = pre.shape[0]
     out = torch.empty(R, n, dtype=torch.bfloat16, device=dev)
     if plan.is_tree:
