@@ -153,6 +153,7 @@ def main():
     ap.add_argument("--format", default=None, help="dense | exl3 | mx (default: the config's)")
     ap.add_argument("--kv", default=None, help="bf16 | fp8 (default: the config's)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--chunk", type=int, default=0, help="prefill chunk in tokens (default 8192 on one GPU, 4096 under tp)")
     ap.add_argument("--hc", default=None, help="gated | mhc: run the model with 4 hyper-connection residual streams")
     ap.add_argument("--spec", default="none", help="mtp: also time speculative rounds (MTP chain of 3 drafts, 4 rows per "
                                                    "sequence verified) through the captured draft / verify / commit graphs")
@@ -210,7 +211,7 @@ def main():
             from spark_engine_b200.parallel import symm
             from spark_engine_b200.parallel.tp import DeviceTP
             arena = symm.Arena(1 << 30, wait_ms=4000.0)
-            tp = DeviceTP(arena, cfg.hidden, rows_cap=1024)
+            tp = DeviceTP(arena, cfg.hidden, rows_cap=max(1024, args.chunk or 4096))
     W = build_random_model(cfg, dev, seed=0, tp=(rank, world) if use_tp else (0, 1))
     torch.cuda.synchronize()
     build_s = time.time() - t0
@@ -219,7 +220,7 @@ def main():
     if aten:
         ops.set_fallback(True)
     S = args.streams
-    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not (args.no_graphs or aten), prefill_chunk=1024 if use_tp else 4096),
+    eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=not (args.no_graphs or aten), prefill_chunk=args.chunk or (4096 if use_tp else 8192)),
                     device=dev, max_seqs=S, kv_tokens_per_seq=max(4096, 2 * args.prompt), tp=tp)
     g = torch.Generator().manual_seed(1234 + (0 if use_tp else rank))
     prompts = torch.randint(0, cfg.vocab, (S, args.prompt), generator=g)

@@ -227,7 +227,7 @@ class EngineConfig:
     ep: int = 1
     max_seqs: int = 8
     max_rows: int = 64                   # rows per decode/verify forward
-    prefill_chunk: int = 4096
+    prefill_chunk: int = 8192            # larger chunks amortise the one-off expert reconstruction (16K prompt: 14.7k tok/s at 4096, 17.1k at 8192)
     kv_tokens: int = 1 << 20             # KV budget in tokens
     kv_granule: int = 16384
     kv_backing: str = "dense"            # dense (one allocation of the whole budget) | vmm (address space reserved, backed on demand)

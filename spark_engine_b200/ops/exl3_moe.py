@@ -19,7 +19,8 @@ from . import cuda as cu
 
 EXL3_MOE_FUSED = os.environ.get("SPARK_EXL3_MOE_FUSED", "1") == "1"
 SMALL_ITEM_ROWS_PER_EXPERT = int(os.environ.get("SPARK_MG_SMALL", "24"))   # average rows per expert up to which 32-row items win
-FUSED_MAX_ROWS_PER_EXPERT = 512      # beyond this the one-off reconstruction is cheaper than decoding once per 64 rows
+FUSED_MAX_ROWS_PER_EXPERT = int(os.environ.get("SPARK_MG_FUSED_MAX", "48"))   # average rows per expert beyond which the
+                                     # one-off reconstruction + tcgen05 grouped GEMM beats decoding once per 64 rows
 
 
 def exl3_grouped_experts(a, wgu, wd, ids, perm, tiles, ntile, max_tiles, c):

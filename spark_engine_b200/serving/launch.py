@@ -84,7 +84,8 @@ def _engine_main(a):
             from ..parallel.tp import DeviceTP
             dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev),
                                     timeout=timedelta(seconds=120))
-            tp = DeviceTP(symm.Arena(1 << 30, wait_ms=ecfg.comm_wait_ms), cfg.hidden, rows_cap=1024)
+            tp = DeviceTP(symm.Arena(1 << 30, wait_ms=ecfg.comm_wait_ms), cfg.hidden,
+                          rows_cap=max(1024, min(a.prefill_chunk, 4096)))
     if a.checkpoint:
         from ..models.checkpoint import load_checkpoint
         _, W = load_checkpoint(a.checkpoint, dev, tp=(rank, world), cfg=cfg)
