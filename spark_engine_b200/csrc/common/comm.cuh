@@ -74,7 +74,31 @@ struct ArRows {
   //           (+ moe_sg[r] * moe_shared[r, :])
   const float* moe_y; const float* moe_w; const int* moe_ids; int moe_slots;
   const __nv_bfloat16* moe_shared; const float* moe_sg;
+  long long ll_off;                      // >= 0: decode rounds travel as {value, sequence} words in this region (see below)
 };
+
+// Low-latency wire format of the decode all-reduce (R <= AR_LL_ROWS rows): every element travels as an 8-byte
+// {value, sequence} word, so a receiver knows a value has arrived by looking at the value itself -- no fence, no arrival
+// counter, no flag fan-out and no flag poll between the pushes and the sum.  A 16-byte store carries two such words;
+// its 8-byte halves are single-copy atomic and the reader checks both sequence fields.  Region: u64 [2][world][16 * N],
+// the set alternates with the parity of the sequence number (a rank can only push number k + 2 after it finished k + 1,
+// which needed every rank's k + 1 pushes, which every rank issued after finishing k).
+// Reference: engine-rs/shim/rdma_arn.cu:129-164 (flag-in-data wire format of the decode all-reduce).
+constexpr int AR_LL_ROWS = 16;
+__device__ __forceinline__ void st_ll(uint4* p, float a, float b, uint32_t seq) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(a)), "r"(seq),
+               "r"(__float_as_uint(b)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// 16-byte slot that holds elements [i, i + 2) of row r as pushed by rank `src`, in the arena that `base` points at
+__device__ __forceinline__ uint4* ll_slot(uint8_t* base, long long ll_off, uint32_t seq, int world, int src, int r, int N, int i) {
+  const size_t set = static_cast<size_t>(seq & 1) * world * AR_LL_ROWS * N;
+  return reinterpret_cast<uint4*>(base + ll_off) + (set + (static_cast<size_t>(src) * AR_LL_ROWS + r) * N + i) / 2;
+}
 
 // Four consecutive elements of this rank's partial row: from `in`, or combined from the expert outputs.
 __device__ __forceinline__ float4 ar_local4(const ArRows& a, int r, int i) {

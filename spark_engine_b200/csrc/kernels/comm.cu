@@ -57,6 +57,90 @@ allreduce_rows_kernel(ArRows a_in) {
   ar_rows_tail(a, a.seq, r, gridDim.x, red);
 }
 
+// Low-latency all-reduce (wire format: comm.cuh).  grid = R CTAs (one row each), 256 threads, N <= 8192, N % 4 == 0.
+// PUSH = false: the rows were pushed by another kernel's epilogue (the row-parallel EXL3 GEMV); this launch only sums.
+template <bool PUSH>
+__global__ void __launch_bounds__(256)
+allreduce_rows_ll_kernel(ArRows a_in) {
+  const long long ll_off = a_in.ll_off;
+  pdl_wait();
+  pdl_trigger();
+  ArRows a = a_in;
+  const uint32_t seq = comm_seq(a.seq_ptr, a.seq);
+  __shared__ float red[8];
+  const int r = blockIdx.x, W = a.c.world, N = a.N;
+  constexpr int KEEP = 8;                                                         // float4 per thread: N <= 256 * 4 * KEEP
+  float4 keep[KEEP];
+#pragma unroll
+  for (int ki = 0; ki < KEEP; ++ki) {
+    const int i = threadIdx.x * 4 + ki * 1024;
+    if (i >= N) break;
+    if (!PUSH) break;
+    const float4 v = ar_local4(a, r, i);
+    for (int p = 0; p < W; ++p) {
+      uint4* dst = ll_slot(a.c.peers[p], ll_off, seq, W, a.c.rank, r, N, i);
+      st_ll(dst, v.x, v.y, seq);
+      st_ll(dst + 1, v.z, v.w, seq);
+    }
+  }
+  // rank-ordered sum of the row: every word is polled until it carries this launch's sequence number (bounded)
+  const unsigned long long t0 = globaltimer_ns();
+  float ss = 0.f;
+#pragma unroll
+  for (int ki = 0; ki < KEEP; ++ki) {
+    const int i = threadIdx.x * 4 + ki * 1024;
+    if (i >= N) break;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < W; ++p) {
+      const uint4* src = ll_slot(a.c.peers[a.c.rank], ll_off, seq, W, p, r, N, i);
+      uint4 w0 = ld_ll(src), w1 = ld_ll(src + 1);
+      while (w0.y != seq || w0.w != seq || w1.y != seq || w1.w != seq) {
+        if (globaltimer_ns() - t0 > a.c.wait_ns) {
+          set_status(a.c.status, ST_TIMEOUT_PEER_FLAG, p, static_cast<int>(seq), static_cast<int>(w0.y));
+          break;
+        }
+        w0 = ld_ll(src); w1 = ld_ll(src + 1);
+      }
+      acc.x += __uint_as_float(w0.x); acc.y += __uint_as_float(w0.z);
+      acc.z += __uint_as_float(w1.x); acc.w += __uint_as_float(w1.z);
+    }
+    if (a.res) {
+      const float4 rv = ld_f4(a.res + static_cast<size_t>(r) * N + i);
+      acc.x += rv.x; acc.y += rv.y; acc.z += rv.z; acc.w += rv.w;
+      st_f4(a.res + static_cast<size_t>(r) * N + i, acc);
+    }
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    keep[ki] = acc;
+  }
+  float rs = 1.f;
+  if (a.norm_w) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    rs = rsqrtf(tot / N + a.eps);
+  }
+#pragma unroll
+  for (int ki = 0; ki < KEEP; ++ki) {
+    const int i = threadIdx.x * 4 + ki * 1024;
+    if (i >= N) break;
+    float4 v = keep[ki];
+    if (a.norm_w) { const float4 g = ld_f4(a.norm_w + i); v.x *= rs * g.x; v.y *= rs * g.y; v.z *= rs * g.z; v.w *= rs * g.w; }
+    if (a.out_f32) st_f4(reinterpret_cast<float*>(a.out) + static_cast<size_t>(r) * N + i, v);
+    else {
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+      uint2 o; o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + static_cast<size_t>(r) * N + i) = o;
+    }
+  }
+  // the last CTA to finish publishes the sequence number for the next launch (every CTA read it at entry)
+  __syncthreads();
+  if (threadIdx.x == 0 && a.seq_ptr) {
+    if (atomicAdd(a.counter, 1) == static_cast<int>(gridDim.x) - 1) { *a.counter = 0; *a.seq_ptr = seq; }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ vocabulary-parallel arg-max
 // Every rank scores its slice of the vocabulary; only (value, index) packets travel.  Stage 1 (many CTAs per row)
 // leaves per-chunk winners; stage 2 (one warp per row) picks the local winner, stores the packet {value, global id}
@@ -392,7 +476,7 @@ struct ArMoe { const float* y; const float* w; const int* ids; int slots; const 
 extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long long flag_off, unsigned seq, int rows_cap,
                                     int R, int N, const void* in, int in_f32, int* counter, float* res,
                                     const float* norm_w, float eps, void* out, int out_f32, cudaStream_t s, void* seq_ptr,
-                                    const ArMoe* moe) {
+                                    const ArMoe* moe, long long ll_off) {
   if (R <= 0) return 0;
   if (N % 4 || R > rows_cap) return -5;
   if ((in == nullptr) == (moe == nullptr)) return -5;
@@ -400,9 +484,14 @@ extern "C" int spark_allreduce_rows(const HostCtx* h, long long slot_off, long l
   a.c = to_ctx(h); a.slot_off = slot_off; a.flag_off = flag_off; a.seq = seq; a.rows_cap = rows_cap; a.R = R; a.N = N;
   a.in = in; a.in_f32 = in_f32; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32; a.seq_ptr = (uint32_t*)seq_ptr;
   a.moe_y = nullptr; a.moe_w = nullptr; a.moe_ids = nullptr; a.moe_slots = 0; a.moe_shared = nullptr; a.moe_sg = nullptr;
+  a.ll_off = ll_off;
   if (moe) {
     a.moe_y = moe->y; a.moe_w = moe->w; a.moe_ids = moe->ids; a.moe_slots = moe->slots;
     a.moe_shared = (const __nv_bfloat16*)moe->shared; a.moe_sg = moe->sg;
+  }
+  if (ll_off >= 0 && R <= AR_LL_ROWS && N <= 8192 && seq_ptr != nullptr && R <= ar_coresident_limit()) {
+    const cudaError_t e = spark_launch_pdl(allreduce_rows_ll_kernel<true>, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), a);
+    return e == cudaSuccess ? 0 : -4;
   }
   if (R <= 64 && R <= ar_coresident_limit()) {       // one kernel pushes, signals, waits and reduces
     const cudaError_t e = spark_launch_pdl(allreduce_rows_kernel, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), a);
@@ -483,7 +572,7 @@ extern "C" int spark_tp_argmax(const HostCtx* h, long long slot_off, long long f
 // closes the sequence.  `counter` + 1 is the tail's own arrival counter.
 extern "C" int spark_allreduce_tail(const HostCtx* h, long long slot_off, long long flag_off, int rows_cap, int R, int N,
                                     int* counter, float* res, const float* norm_w, float eps, void* out, int out_f32,
-                                    cudaStream_t s, void* seq_ptr) {
+                                    cudaStream_t s, void* seq_ptr, long long ll_off) {
   if (R <= 0) return 0;
   if (N % 4 || R > rows_cap || seq_ptr == nullptr) return -5;
   ArRows a;
@@ -491,6 +580,11 @@ extern "C" int spark_allreduce_tail(const HostCtx* h, long long slot_off, long l
   a.in = nullptr; a.in_f32 = 0; a.counter = counter; a.res = res; a.norm_w = norm_w; a.eps = eps; a.out = out; a.out_f32 = out_f32;
   a.seq_ptr = (uint32_t*)seq_ptr;
   a.moe_y = nullptr; a.moe_w = nullptr; a.moe_ids = nullptr; a.moe_slots = 0; a.moe_shared = nullptr; a.moe_sg = nullptr;
+  a.ll_off = ll_off;
+  if (ll_off >= 0 && R <= AR_LL_ROWS && N <= 8192) {       // the pushing kernel used the low-latency wire format too
+    const cudaError_t e = spark_launch_pdl(allreduce_rows_ll_kernel<false>, dim3(R), dim3(256), 0, s, dim3(1, 1, 1), a);
+    return e == cudaSuccess ? 0 : -4;
+  }
   const cudaError_t e = spark_launch_pdl(ar_tail_kernel, dim3(R < 296 ? R : 296), dim3(256), 0, s, dim3(1, 1, 1), a, counter + 1);
   return e == cudaSuccess ? 0 : -4;
 }

@@ -197,6 +197,14 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
     if (a.fuse_ar) {
       // fused all-reduce: this rank's partial strip goes straight into slot[rank] of every peer's arena
       const uint32_t ar_seq = comm_seq(a.ar.seq_ptr, a.ar.seq);
+      if (a.ar.ll_off >= 0) {                     // decode rows: {value, sequence} words, the tail polls the data itself
+        for (int p = 0; p < a.ar.c.world; ++p) {
+          uint4* dst = ll_slot(a.ar.c.peers[p], a.ar.ll_off, ar_seq, a.ar.c.world, a.ar.c.rank, r, a.ar.N, strip * 128 + lane * 4);
+          st_ll(dst, v[0], v[1], ar_seq);
+          st_ll(dst + 1, v[2], v[3], ar_seq);
+        }
+        continue;
+      }
       const size_t so = static_cast<size_t>(ar_seq & 1) * a.ar.c.world * a.ar.rows_cap * a.ar.N +
                         (static_cast<size_t>(a.ar.c.rank) * a.ar.rows_cap + r) * a.ar.N + strip * 128 + lane * 4;
       for (int p = 0; p < a.ar.c.world; ++p)
@@ -212,7 +220,7 @@ exl3_gemv_kernel(const __grid_constant__ Exl3GemvArgs a) {
       *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.y) + o) = ov;
     }
   }
-  if (a.fuse_ar) exl3_fused_ar_arrive(a);
+  if (a.fuse_ar && a.ar.ll_off < 0) exl3_fused_ar_arrive(a);
 }
 
 }  // namespace spark

@@ -13,6 +13,7 @@ code (links, GIDs, proxy threads) has no counterpart on an NVSwitch box.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional
 
 import torch
@@ -31,7 +32,8 @@ class ArRows(C.Structure):
     _fields_ = [("c", CommCtx), ("slot_off", i64), ("flag_off", i64), ("seq", u32), ("rows_cap", i32), ("R", i32),
                 ("N", i32), ("inp", vp), ("in_f32", i32), ("counter", vp), ("res", vp), ("norm_w", vp), ("eps", f32),
                 ("out", vp), ("out_f32", i32), ("seq_ptr", vp),
-                ("moe_y", vp), ("moe_w", vp), ("moe_ids", vp), ("moe_slots", i32), ("moe_shared", vp), ("moe_sg", vp)]
+                ("moe_y", vp), ("moe_w", vp), ("moe_ids", vp), ("moe_slots", i32), ("moe_shared", vp), ("moe_sg", vp),
+                ("ll_off", i64)]
 
 
 class ArMoe(C.Structure):
@@ -52,8 +54,8 @@ _SIGS = {
     "spark_arena_alloc": ([i64], vp), "spark_arena_free": ([vp], None),
     "spark_ipc_get_handle": ([vp, vp], i32), "spark_ipc_open_handle": ([vp], vp), "spark_ipc_close": ([vp], None),
     "spark_comm_barrier": ([vp, i64, u32, vp], i32),
-    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp, vp], i32),
-    "spark_allreduce_tail": ([vp, i64, i64, i32, i32, i32, vp, vp, vp, f32, vp, i32, vp, vp], i32),
+    "spark_allreduce_rows": ([vp, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, vp, i32, vp, vp, vp, i64], i32),
+    "spark_allreduce_tail": ([vp, i64, i64, i32, i32, i32, vp, vp, vp, f32, vp, i32, vp, vp, i64], i32),
     "spark_tp_argmax": ([vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp], i32),
     "spark_rs_ag_rows": ([vp, i64, i64, i64, i64, u32, i32, i32, i32, vp, i32, vp, vp, vp, f32, i32, vp, vp], i32),
     "spark_ag_push": ([vp, vp, i32, i32, i64, i64, u32, vp, vp, vp], i32),
@@ -207,6 +209,11 @@ class FusedAllReduce:
         self.flag_off = arena.region(name + ".flags", 8 * 4)
         self.counter = arena.counter()
         self.seq = arena.seq_counter()
+        # decode rounds (<= 16 rows): 8-byte {value, sequence} words, no flags (comm.cu `allreduce_rows_ll_kernel`)
+        self.ll_off = -1
+        if os.environ.get("SPARK_AR_LL", "1") == "1" and N <= 8192:
+            nb = 2 * W * 16 * N * 8
+            self.ll_off = arena.region(name + ".ll", nb)     # (the arena is zero-filled: below every live sequence number)
 
     def _args(self, R, inp, res, norm_w, eps, out) -> ArRows:
         ar = ArRows()
@@ -219,6 +226,7 @@ class FusedAllReduce:
         ar.counter = self.counter
         ar.res, ar.norm_w, ar.eps = cu.P(res), cu.P(norm_w), float(eps)
         ar.out, ar.out_f32 = cu.P(out), int(out.dtype == torch.float32)
+        ar.ll_off = self.ll_off if R <= 16 else -1
         return ar
 
     def __call__(self, x, res: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
@@ -241,7 +249,8 @@ class FusedAllReduce:
         ar = self._args(R, x, res, norm_w, eps, out)
         rc = _lib()._dll.spark_allreduce_rows(C.byref(ar.c), ar.slot_off, ar.flag_off, ar.seq, ar.rows_cap, R, N, ar.inp,
                                               ar.in_f32, ar.counter, ar.res, ar.norm_w, ar.eps, ar.out, ar.out_f32,
-                                              cu.stream(), ar.seq_ptr, C.byref(moe) if moe is not None else None)
+                                              cu.stream(), ar.seq_ptr, C.byref(moe) if moe is not None else None,
+                                              C.c_longlong(ar.ll_off))
         cu.check(rc, "spark_allreduce_rows")
         return out
 
@@ -261,7 +270,8 @@ class FusedAllReduce:
                                       0 if w.kind == "mul1" else 1, cu.stream(), C.addressof(ar), 0)
         cu.check(rc, "spark_exl3_gemv(fused all-reduce)")
         rc = _lib()._dll.spark_allreduce_tail(C.byref(ar.c), ar.slot_off, ar.flag_off, ar.rows_cap, R, self.N, ar.counter, ar.res,
-                                              ar.norm_w, ar.eps, ar.out, ar.out_f32, cu.stream(), ar.seq_ptr)
+                                              ar.norm_w, ar.eps, ar.out, ar.out_f32, cu.stream(), ar.seq_ptr,
+                                              C.c_longlong(ar.ll_off))
         cu.check(rc, "spark_allreduce_tail")
         self._keep = ar
         return out
