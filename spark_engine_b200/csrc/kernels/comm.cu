@@ -90,19 +90,41 @@ allreduce_rows_ll_kernel(ArRows a_in) {
   for (int ki = 0; ki < KEEP; ++ki) {
     const int i = threadIdx.x * 4 + ki * 1024;
     if (i >= N) break;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < W; ++p) {
-      const uint4* src = ll_slot(a.c.peers[a.c.rank], ll_off, seq, W, p, r, N, i);
-      uint4 w0 = ld_ll(src), w1 = ld_ll(src + 1);
-      while (w0.y != seq || w0.w != seq || w1.y != seq || w1.w != seq) {
-        if (globaltimer_ns() - t0 > a.c.wait_ns) {
-          set_status(a.c.status, ST_TIMEOUT_PEER_FLAG, p, static_cast<int>(seq), static_cast<int>(w0.y));
-          break;
-        }
-        w0 = ld_ll(src); w1 = ld_ll(src + 1);
+    // every peer's words are requested together (one memory latency for the whole set, not one per peer); words that
+    // do not carry this launch's sequence number yet are asked for again
+    uint4 w0[COMM_MAX_RANKS], w1[COMM_MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p) {
+      if (p < W) {
+        const uint4* src = ll_slot(a.c.peers[a.c.rank], ll_off, seq, W, p, r, N, i);
+        w0[p] = ld_ll(src); w1[p] = ld_ll(src + 1);
       }
-      acc.x += __uint_as_float(w0.x); acc.y += __uint_as_float(w0.z);
-      acc.z += __uint_as_float(w1.x); acc.w += __uint_as_float(w1.z);
+    }
+    for (;;) {
+      bool ready = true;
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p)
+        if (p < W && (w0[p].y != seq || w0[p].w != seq || w1[p].y != seq || w1[p].w != seq)) ready = false;
+      if (ready) break;
+      if (globaltimer_ns() - t0 > a.c.wait_ns) {
+        set_status(a.c.status, ST_TIMEOUT_PEER_FLAG, -1, static_cast<int>(seq), static_cast<int>(w0[0].y));
+        break;
+      }
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p) {
+        if (p < W && (w0[p].y != seq || w0[p].w != seq || w1[p].y != seq || w1[p].w != seq)) {
+          const uint4* src = ll_slot(a.c.peers[a.c.rank], ll_off, seq, W, p, r, N, i);
+          w0[p] = ld_ll(src); w1[p] = ld_ll(src + 1);
+        }
+      }
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p) {               // fixed rank order
+      if (p < W) {
+        acc.x += __uint_as_float(w0[p].x); acc.y += __uint_as_float(w0[p].z);
+        acc.z += __uint_as_float(w1[p].x); acc.w += __uint_as_float(w1[p].z);
+      }
     }
     if (a.res) {
       const float4 rv = ld_f4(a.res + static_cast<size_t>(r) * N + i);
