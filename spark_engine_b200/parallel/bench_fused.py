@@ -6,6 +6,12 @@
     all-reduce + residual add + RMSNorm;
 (b) MoE expert-parallel dispatch + combine, T in {1,16,256,4096} tokens per rank, hidden 4096, 256 experts
     top-8, uniform-random router logits, FP8 e4m3 payload with 1x128 scales.
+(c) all-gather fused into a column-parallel GEMM: x row-sharded [M/tp, 4096], W [4096/tp, 4096];
+(d) sequence-parallel residual update: reduce-scatter of fp32 partial rows [M, 2048] to the row owners + residual +
+    RMSNorm + bf16 all-gather, against the full-row all-reduce kernel and NCCL;
+(e) decode-round collectives inside a captured CUDA graph (32 back-to-back launches per replay): all-reduce + residual
+    + RMSNorm of 1 / 4 / 16 rows x 2048 in the low-latency wire format and in the flag format, the row-parallel EXL3
+    GEMV with the all-reduce in its epilogue, the packet arg-max; NCCL + ATen beside them.
 All inputs N(0,1) bf16, seed 0.  Device-timed with CUDA events, max over ranks; every case also reports its
 roofline: the slower of FLOPs / measured GEMM peak and NVLink bytes / measured link bandwidth.
 """
@@ -36,7 +42,7 @@ def main():
             peaks["bf16_tflops"] = json.load(f)["bf16_tflops"]
     except Exception:
         pass
-    arena = symm.Arena(1 << 30)
+    arena = symm.Arena(2 << 30)
     iters, warm = 20, 5
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -136,6 +142,111 @@ def main():
         results.append({"case": "ep_dispatch_combine", "T": T, "H": H, "E": E, "top_k": k, "ep": world,
                         "ours_us": round(t_ours, 2), "nccl_torch_us": round(t_base, 2), "speedup": round(t_base / t_ours, 2),
                         "roofline_us": round(roof_us, 3), "frac_of_roofline": round(roof_us / t_ours, 3) if t_ours else None})
+    # ------------------------------------------------------------------ (c) all-gather + column-parallel GEMM
+    Kc, Nc = 4096, 4096 // world
+    wc = torch.randn(Nc, Kc, device=dev, generator=g).bfloat16()
+    agg = symm.AllGatherGemm(arena, "bench_ag", 4096, Kc)
+    for M in (64 * world, 512, 4096):
+        rows = M // world
+        xl = torch.randn(rows, Kc, device=dev, generator=g).bfloat16()
+
+        def ours_ag():
+            return agg(xl, wc)
+
+        def base_ag():
+            full = torch.empty(M, Kc, dtype=torch.bfloat16, device=dev)
+            dist.all_gather_into_tensor(full, xl)
+            return torch.matmul(full, wc.t())
+
+        t_ours, t_base = timed(ours_ag), timed(base_ag)
+        flops = 2.0 * M * Nc * Kc
+        nv_bytes = (world - 1) * rows * Kc * 2
+        roof_us = max(flops / (peaks["bf16_tflops"] * 1e12), nv_bytes / (peaks["link_gbs"] * 1e9)) * 1e6
+        results.append({"case": "allgather_colpar_gemm", "M": M, "K": Kc, "N_shard": Nc, "tp": world, "ours_us": round(t_ours, 2),
+                        "nccl_cublas_us": round(t_base, 2), "speedup": round(t_base / t_ours, 2),
+                        "roofline_us": round(roof_us, 3), "frac_of_roofline": round(roof_us / t_ours, 3)})
+    # ------------------------------------------------------------------ (d) sequence-parallel residual update of prefill rows
+    Hs = 2048
+    nws = torch.ones(Hs, device=dev)
+    sp = symm.RowParallelGemm(arena, "bench_sp", 4096, Hs)
+    far_big = symm.FusedAllReduce(arena, "bench_ar_big", 1024, Hs)
+    for M in (1024, 4096):
+        part = torch.randn(M, Hs, device=dev, generator=g)
+        resf = torch.zeros(M, Hs, device=dev)
+        rpr = M // world
+
+        def ours_sp():
+            return sp.rows(part, resf[rank * rpr:(rank + 1) * rpr], nws, 1e-6)
+
+        def ours_ar():
+            return far_big(part, res=resf, norm_w=nws)
+
+        def base_sp():
+            y = part.clone()
+            dist.all_reduce(y)
+            r = resf + y
+            return (r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + 1e-6) * nws).bfloat16()
+
+        t_sp, t_base = timed(ours_sp), timed(base_sp)
+        t_ar = timed(ours_ar) if M <= 1024 else float("nan")
+        nv_bytes = (world - 1) / world * M * Hs * (4 + 2)
+        roof_us = nv_bytes / (peaks["link_gbs"] * 1e9) * 1e6
+        results.append({"case": "seqpar_rs_norm_ag_rows", "M": M, "N": Hs, "tp": world, "ours_us": round(t_sp, 2),
+                        "full_row_allreduce_kernel_us": round(t_ar, 2) if t_ar == t_ar else None, "nccl_aten_us": round(t_base, 2),
+                        "speedup": round(t_base / t_sp, 2), "roofline_us": round(roof_us, 3),
+                        "frac_of_roofline": round(roof_us / t_sp, 3)})
+    # ------------------------------------------------------------------ (e) decode-round collectives inside a CUDA graph
+    from spark_engine_b200.quant import formats as Q
+
+    def gtimed(fn, n=32, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(n):
+                fn()
+        gr.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (reps * n) * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    for R in (1, 4, 16):
+        far_ll = symm.FusedAllReduce(arena, f"bench_ll{R}", 64, Hs)
+        far_fl = symm.FusedAllReduce(arena, f"bench_fl{R}", 64, Hs)
+        far_fl.ll_off = -1                                   # the flag format (push, fence, arrival counter, flags, poll)
+        xr = torch.randn(R, Hs, device=dev, generator=g).bfloat16()
+        rr = torch.zeros(R, Hs, device=dev)
+        wq = Q.random_exl3(Hs, 4096 // world, 4, 0, 0.02, 3, dev)
+        xo = torch.randn(R, 4096 // world, device=dev, generator=g).bfloat16()
+
+        def nccl_ar():
+            y = xr.float()
+            dist.all_reduce(y)
+            r = rr + y
+            return (r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + 1e-6) * nws).bfloat16()
+
+        results.append({"case": "graph_decode_allreduce_residual_norm", "rows": R, "N": Hs, "tp": world,
+                        "low_latency_us": round(gtimed(lambda: far_ll(xr, res=rr, norm_w=nws)), 2),
+                        "flags_us": round(gtimed(lambda: far_fl(xr, res=rr, norm_w=nws)), 2),
+                        "nccl_aten_us": round(gtimed(nccl_ar), 2),
+                        "exl3_gemv_fused_low_latency_us": round(gtimed(lambda: far_ll.gemv_fused(xo, wq, res=rr, norm_w=nws)), 2),
+                        "exl3_gemv_fused_flags_us": round(gtimed(lambda: far_fl.gemv_fused(xo, wq, res=rr, norm_w=nws)), 2),
+                        "exl3_gemv_alone_us": round(gtimed(lambda: cu.exl3_gemv(xo, wq)), 2)})
+    pk = symm.PacketArgmax(arena, "bench_pk", 64)
+    lg = torch.randn(4, 151936 // world, device=dev, generator=g)
+    results.append({"case": "graph_decode_packet_argmax", "rows": 4, "vocab": 151936, "tp": world,
+                    "ours_us": round(gtimed(lambda: pk(lg, rank * lg.shape[1])), 2),
+                    "local_argmax_us": round(gtimed(lambda: cu.argmax(lg)), 2)})
     st = arena.status()
     if rank == 0:
         for r in results:
