@@ -232,7 +232,7 @@ class EngineConfig:
     kv_granule: int = 16384
     kv_backing: str = "dense"            # dense (one allocation of the whole budget) | vmm (address space reserved, backed on demand)
     cuda_graphs: bool = True
-    spec: str = "mtp"                    # none | mtp | tree | lookup
+    spec: str = "mtp"                    # none | mtp | lookup | feature (tap-conditioned drafter) | stage (staged drafter)
     spec_depth: int = 3
     spec_policy: str = "theta"           # tau | theta | rate | cost
     comm: str = "fused"                  # fused (peer-memory kernels) | nccl (baseline)

@@ -19,7 +19,7 @@ from .. import ops
 from ..config import EngineConfig, ModelConfig
 from ..models.model import Model
 from ..models.plan import make_plan
-from .graphs import RoundGraph, ctx_bucket
+from .graphs import GraphCache, RoundGraph, ctx_bucket, runtime_signature
 
 
 @dataclass
@@ -40,7 +40,7 @@ class LLMEngine:
         self.model = Model(cfg, W, device=device, dtype=dtype, n_slots=max_seqs,
                            kv_tokens=max_seqs * kv_tokens_per_seq, slot_tokens=kv_tokens_per_seq, tp=tp)
         self.device = self.model.device
-        self.graphs: Dict[tuple, RoundGraph] = {}
+        self.graphs = GraphCache(runtime_signature(self.ecfg) if self.device.type == "cuda" else "")
         # every family captures: hashed n-gram layers get their table rows staged with the plan (row ids for a device
         # table, the gathered rows themselves for a host-resident one)
         self.use_graphs = self.ecfg.cuda_graphs and self.device.type == "cuda"
@@ -80,9 +80,7 @@ class LLMEngine:
             logits = m.forward(plan)
             return m.greedy(logits).tolist()
         key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + 1))
-        g = self.graphs.get(key)
-        if g is None:
-            g = self.graphs[key] = RoundGraph(self.model, slots, 1, key[2])
+        g = self.graphs.get(key, lambda: RoundGraph(self.model, slots, 1, key[2], pool=self.graphs.pool))
         g.stage([[t] for t in ids], pos0)
         g.run(commit=True)
         torch.cuda.current_stream().synchronize()
@@ -118,9 +116,7 @@ class LLMEngine:
                 out.append(cur)
             return out
         key = (tuple(slots), 1, self._ctx_bucket(max(pos0) + steps))
-        g = self.graphs.get(key)
-        if g is None:
-            g = self.graphs[key] = RoundGraph(self.model, slots, 1, key[2])
+        g = self.graphs.get(key, lambda: RoundGraph(self.model, slots, 1, key[2], pool=self.graphs.pool))
         g.stage([[t] for t in ids], pos0)
         ring = torch.empty(steps, len(slots), dtype=torch.int32).pin_memory()
         first = 0
@@ -132,7 +128,7 @@ class LLMEngine:
             first = 1
         for i in range(first, steps):
             g.replay_fed()
-            ring[i].copy_(g.out_ids, non_blocking=True)
+            ring[i].copy_(g.fed_out_ids, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         for s, p in zip(slots, pos0):
             m.seqs[s].length = p + steps

@@ -19,6 +19,58 @@ import torch
 from ..models.plan import Plan, Segment
 
 
+class GraphCache:
+    """Captured graphs of one engine: least-recently-used eviction, keys prefixed by the flag signature (a changed switch
+    can never replay a graph captured under the old setting), one memory pool shared by every capture (graphs of one
+    engine replay one at a time on one stream, so they can share their intermediate buffers; what a graph hands out --
+    logits, hidden rows, sampled ids -- stays allocated for as long as the graph object lives).
+    Reference: engine-rs/src/spec_probe.rs:316-327 (flag signature), qwen/graph.rs:538-845 (graph sets per store set)."""
+
+    def __init__(self, signature: str = "", max_entries: int = 64):
+        from collections import OrderedDict
+        self.signature, self.max_entries = signature, max_entries
+        self.d = OrderedDict()
+        self._pool = None
+        self.evicted = 0
+
+    @property
+    def pool(self):
+        if self._pool is None and torch.cuda.is_available():
+            self._pool = torch.cuda.graph_pool_handle()
+        return self._pool
+
+    def get(self, key: tuple, make):
+        full = (self.signature,) + tuple(key)
+        g = self.d.get(full)
+        if g is not None:
+            self.d.move_to_end(full)
+            return g
+        g = make()
+        self.d[full] = g
+        while len(self.d) > self.max_entries:
+            self.d.popitem(last=False)
+            self.evicted += 1
+        return g
+
+    def __len__(self):
+        return len(self.d)
+
+    def values(self):
+        return self.d.values()
+
+    def __bool__(self):
+        return len(self.d) > 0
+
+
+def runtime_signature(ecfg=None) -> str:
+    """What a captured graph depends on besides its layout: the engine's flag signature and the kernel-level switches."""
+    from ..ops import cuda as cu
+    parts = [ecfg.signature() if ecfg is not None else ""]
+    for name in ("FUSED_DECODE", "SHARED_AS_PAIR", "FUSED_COMBINE", "SIDE_STREAMS"):
+        parts.append(f"{name}={getattr(cu, name, None)}")
+    return ";".join(parts)
+
+
 def ctx_bucket(max_ctx: int) -> int:
     b = 256
     while b < max_ctx:
@@ -36,8 +88,9 @@ def _layout_arrays(slots, k, dev):
 class RoundGraph:
     """Captured target forward over a fixed row layout (rows_per_seq rows for each listed slot)."""
 
-    def __init__(self, model, slots: Sequence[int], rows_per_seq: int, bucket: int, sample: bool = False):
+    def __init__(self, model, slots: Sequence[int], rows_per_seq: int, bucket: int, sample: bool = False, pool=None):
         self.m, self.slots, self.k, self.sample = model, list(slots), rows_per_seq, sample
+        self.pool = pool
         m = model
         dev = m.device
         n = len(self.slots)
@@ -150,7 +203,7 @@ class RoundGraph:
             m._pending_plan = None
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, pool=self.pool):
                 self._body(commit)
             cu.add_launches(-self.launches)       # the capture pass launched nothing
             m._pending_plan = None
@@ -175,13 +228,16 @@ class RoundGraph:
             if self.graph is None:
                 raise RuntimeError("run() the round once before device-fed replays")
             torch.cuda.synchronize()
+            keep = (self.logits, self.hidden, self.out_ids)      # the plain round's outputs stay its own
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, pool=self.pool):
                 self._body(True)
                 cu.check(cu.lib().spark_decode_advance(cu.P(self.plan_ints), cu.P(self.out_ids), self.n, cu.stream()),
                          "spark_decode_advance")
             cu.add_launches(-(self.launches + 1))
             self.graph_fed = g
+            self.fed_out_ids = self.out_ids
+            self.logits, self.hidden, self.out_ids = keep
         self.graph_fed.replay()
         cu.add_launches(self.launches + 1)
 
@@ -200,7 +256,7 @@ class RoundGraph:
             n0 = cu.launch_count()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, pool=self.pool):
                 self._commit_body()
             self.commit_launches = cu.launch_count() - n0
             cu.add_launches(-self.commit_launches)
@@ -222,8 +278,9 @@ class MtpGraph:
     sequence, then `depth` chained draft steps with the sampled draft fed back on the device.  Returns the drafts and
     the drafter's confidence in each (softmax probability of the drafted token) with one read."""
 
-    def __init__(self, model, slots: Sequence[int], k: int, depth: int, bucket: int):
+    def __init__(self, model, slots: Sequence[int], k: int, depth: int, bucket: int, pool=None):
         self.m, self.slots, self.k, self.depth = model, list(slots), k, depth
+        self.pool = pool
         m, dev = model, model.device
         n = len(self.slots)
         R = n * k
@@ -335,7 +392,7 @@ class MtpGraph:
             self.dev.copy_(keep)                  # the warm-up advanced the chain rows: restore the staged plan
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, pool=self.pool):
                 self._body()
             cu.add_launches(-self.launches)
             self.graph = g
@@ -351,22 +408,18 @@ class MtpGraph:
 
 
 class SpecGraphs:
-    """The captured rounds a speculative decoder replays, keyed by layout."""
+    """The captured rounds a speculative decoder replays, keyed by layout (LRU, shared pool: `GraphCache`)."""
 
-    def __init__(self, model):
+    def __init__(self, model, signature: str = "", max_entries: int = 64):
         self.m = model
-        self.rounds, self.mtp = {}, {}
+        self.rounds = GraphCache(signature, max_entries)
+        self.mtp = GraphCache(signature, max_entries)
+        self.mtp._pool = None
 
     def round_graph(self, slots, k: int, max_ctx: int) -> RoundGraph:
         key = (tuple(slots), k, ctx_bucket(max_ctx))
-        g = self.rounds.get(key)
-        if g is None:
-            g = self.rounds[key] = RoundGraph(self.m, slots, k, key[2], sample=True)
-        return g
+        return self.rounds.get(key, lambda: RoundGraph(self.m, slots, k, key[2], sample=True, pool=self.rounds.pool))
 
     def mtp_graph(self, slots, k: int, depth: int, max_ctx: int) -> MtpGraph:
         key = (tuple(slots), k, depth, ctx_bucket(max_ctx))
-        g = self.mtp.get(key)
-        if g is None:
-            g = self.mtp[key] = MtpGraph(self.m, slots, k, depth, key[3])
-        return g
+        return self.mtp.get(key, lambda: MtpGraph(self.m, slots, k, depth, key[3], pool=self.rounds.pool))

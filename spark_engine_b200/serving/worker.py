@@ -61,6 +61,18 @@ class EngineServer:
         drafter = "mtp" if (e.spec == "mtp" and self.model.mtp_layers) else (lambda s, d: ([], []))
         if e.spec == "lookup":
             drafter = "lookup"
+        elif e.spec in ("feature", "stage"):
+            # model-conditioned drafters beside the MTP head (randomly initialised unless the checkpoint carries them:
+            # W["drafter"]); both are callables (seq, depth) -> (tokens, confidences)
+            from ..spec import drafters as D
+            if e.spec == "feature":
+                dc = D.FeatureDrafterConfig(target_hidden=cfg.hidden, taps=(0, max(0, cfg.n_layers - 1)), vocab=cfg.vocab,
+                                            sub_vocab=min(512, cfg.vocab), depth=max(1, e.spec_depth))
+                drafter = D.FeatureDrafter(self.model, dc, W.get("drafter"), seed=e.seed,
+                                           device=device if str(device) != "cpu" else "cpu")
+            else:
+                drafter = D.StageDrafter(D.StageDrafterConfig(hidden=cfg.hidden, vocab=cfg.vocab, block=max(1, e.spec_depth)),
+                                         W.get("drafter"), seed=e.seed)
         self.spec = SpecDecoder(self.model, drafter, depth=e.spec_depth if e.spec != "none" else 0,
                                 policy={"theta": "theta", "tau": "tau", "rate": "rate"}.get(e.spec_policy, "all"),
                                 graphs=e.cuda_graphs)

@@ -168,11 +168,15 @@ def test_device_fed_steps_equal_host_fed_rounds():
         if fed:
             first = eng.decode_steps([0, 1], cur, 3)            # captures the round, then replays with device feedback
             toks = first + eng.decode_steps([0, 1], first[-1], 4)
-        else:
-            for _ in range(7):
+            cur = toks[-1]
+            for _ in range(2):                                  # plain rounds after fed replays read their own outputs
                 cur = eng.decode_round([0, 1], cur)
                 toks.append(cur)
-        assert [eng.model.seqs[s].length for s in (0, 1)] == [87, 87]
+        else:
+            for _ in range(9):
+                cur = eng.decode_round([0, 1], cur)
+                toks.append(cur)
+        assert [eng.model.seqs[s].length for s in (0, 1)] == [89, 89]
         outs.append(toks)
     assert outs[0] == outs[1]
 

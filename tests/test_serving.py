@@ -163,3 +163,23 @@ def test_http_bench_script_against_a_live_front_end(tmp_path):
     srv.shutdown()
     es.shutdown = True
     th.join(10)
+
+
+import pytest
+
+
+@pytest.mark.parametrize("spec", ["feature", "stage", "lookup"])
+def test_server_with_the_other_drafters_still_serves_greedy_text(tmp_path, spec):
+    """The tap-conditioned and the staged drafter (randomly initialised here) and prompt lookup as the server's drafter:
+    whatever they propose, verification keeps the served text equal to plain greedy decoding."""
+    cfg, W, es, sock, th = _start(tmp_path, spec=spec)
+    g = torch.Generator().manual_seed(2)
+    p1 = torch.randint(0, cfg.vocab, (30,), generator=g).tolist()
+    ref = oracle.greedy_generate(cfg, W, torch.tensor(p1), 8)[0].tolist()
+    c, buf = _client(sock)
+    c.sendall(proto.encode({"id": 1, "prompt_ids": p1, "max_new": 8}))
+    done, _ = _collect(c, buf, [1])
+    assert done[1]["token_ids"] == ref
+    assert done[1]["drafted_tokens"] >= 0
+    c.sendall(proto.encode({"shutdown": True}))
+    th.join(10)
