@@ -235,6 +235,7 @@ class EngineConfig:
     spec: str = "mtp"                    # none | mtp | lookup | feature (tap-conditioned drafter) | stage (staged drafter)
     spec_depth: int = 3
     spec_policy: str = "theta"           # tau | theta | rate | cost
+    spec_tree_widths: str = ""           # e.g. "3,2,1": verify a tree (widths per depth) built from the feature drafter's candidates
     comm: str = "fused"                  # fused (peer-memory kernels) | nccl (baseline)
     comm_wait_ms: float = 1000.0         # bound of every device-side wait
     step_deadline_s: float = 0.0         # > 0: a watchdog aborts the process when one engine step runs longer

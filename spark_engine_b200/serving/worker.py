@@ -278,7 +278,15 @@ class EngineServer:
         for lv in lvs:
             stops.update(lv.msg.get("stop_token_ids", []))
         with self.prof.section("spec.round"):
-            outs = self.spec.round([lv.seq for lv in lvs], budgets, stop=tuple(stops))
+            widths = [int(x) for x in self.ecfg.spec_tree_widths.split(",") if x.strip()]
+            drafter = self.spec.drafter
+            if widths and hasattr(drafter, "candidates"):
+                # tree verification: the drafter's top candidates per depth hang off the greedy spine as siblings
+                from ..spec.drafters import to_tree
+                trees = [to_tree(drafter.candidates(lv.seq), widths) for lv in lvs]
+                outs = self.spec.round_tree([lv.seq for lv in lvs], trees, budgets, stop=tuple(stops))
+            else:
+                outs = self.spec.round([lv.seq for lv in lvs], budgets, stop=tuple(stops))
         dt = (time.time() - t0) * 1e3
         self.totals["spec_rounds"] += 1
         for lv, out in zip(lvs, outs):

@@ -17,13 +17,13 @@ from spark_engine_b200.serving.openai_server import ReasoningSplit, StopStrings,
 from spark_engine_b200.serving.worker import EngineServer
 
 
-def _start(tmp_path, spec="mtp", pcache=None):
+def _start(tmp_path, spec="mtp", pcache=None, tree=""):
     cfg = tiny_hybrid()
     cfg.mtp_layers = 1
     W = init_weights(cfg, seed=0)
     sock = str(tmp_path / "e.sock")
     es = EngineServer(cfg, W, EngineConfig(max_seqs=2, kv_tokens=2048, prefill_chunk=32, spec=spec, spec_depth=2,
-                                           pcache_dir=pcache, pcache_bytes=64 << 20, profile=True))
+                                           spec_tree_widths=tree, pcache_dir=pcache, pcache_bytes=64 << 20, profile=True))
     ready = threading.Event()
     th = threading.Thread(target=es.serve_forever, args=(sock,), kwargs={"ready_cb": ready.set}, daemon=True)
     th.start()
@@ -168,11 +168,11 @@ def test_http_bench_script_against_a_live_front_end(tmp_path):
 import pytest
 
 
-@pytest.mark.parametrize("spec", ["feature", "stage", "lookup"])
+@pytest.mark.parametrize("spec", ["feature", "stage", "lookup", "feature-tree"])
 def test_server_with_the_other_drafters_still_serves_greedy_text(tmp_path, spec):
     """The tap-conditioned and the staged drafter (randomly initialised here) and prompt lookup as the server's drafter:
     whatever they propose, verification keeps the served text equal to plain greedy decoding."""
-    cfg, W, es, sock, th = _start(tmp_path, spec=spec)
+    cfg, W, es, sock, th = _start(tmp_path, spec=spec.split("-")[0], tree="3,2" if spec.endswith("tree") else "")
     g = torch.Generator().manual_seed(2)
     p1 = torch.randint(0, cfg.vocab, (30,), generator=g).tolist()
     ref = oracle.greedy_generate(cfg, W, torch.tensor(p1), 8)[0].tolist()
