@@ -139,6 +139,116 @@ static int launch_gemv(const void* x, int ldx, const void* W, long long es, int 
   return err == cudaSuccess ? 0 : -4;
 }
 
+// Wide projections (lm_head: N >= 2048 columns, every column read once) with the rows as the N side of
+// mma.sync m16n8k16: a warp owns 16 weight rows, lane (g, t) loads 16 contiguous bytes of rows g and g + 8 per
+// 32 k and uses them as the A fragments of two MMAs; the same permutation of k is applied to the activation
+// fragment (one 16-byte shared-memory load per lane), which leaves every dot product unchanged.  No unpacking,
+// no cross-lane reduction: about 8 warp-instructions per KB of weights instead of about 30 x rows.  Which kernel
+// runs depends on (N, K) only, never on the number of rows, and every output element is one fixed chain of
+// MMAs over k, so a row's logits do not depend on the batch it is in.
+constexpr int GEMV_MMA_PAD = 8;   // bf16 of padding per staged activation row: spreads rows over the banks
+
+__device__ __forceinline__ void gemv_mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, typename TO>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw,
+                     TO* __restrict__ y, int ldy, int R, int N, int K, int cpc) {
+  extern __shared__ __align__(16) uint8_t smem_gemv[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [NT * 8][K + GEMV_MMA_PAD]
+  const int lds = K + GEMV_MMA_PAD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int KC = K >> 5;                                 // 32-wide k chunks
+  constexpr int BATCH = 8;                               // chunks in flight per lane and weight row
+  uint4 ra[BATCH], rb[BATCH];
+  auto rows_of = [&](int cg, const uint4*& w0, const uint4*& w1) -> int {
+    const int n0 = ((blockIdx.x * cpc + cg) * GEMV_WARPS + warp) * 16;
+    w0 = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(n0 + g, N - 1)) * ldw) + t;
+    w1 = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(n0 + g + 8, N - 1)) * ldw) + t;
+    return n0;
+  };
+  auto load = [&](const uint4* w0, const uint4* w1, int kc0) {
+#pragma unroll
+    for (int u = 0; u < BATCH; ++u) {
+      const bool in = kc0 + u < KC;
+      ra[u] = in ? __ldg(w0 + (kc0 + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+      rb[u] = in ? __ldg(w1 + (kc0 + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  const uint4 *w0, *w1;
+  int n0 = rows_of(0, w0, w1);
+  pdl_wait();
+  if (n0 < N) load(w0, w1, 0);                           // in flight while the rows are staged
+  const int KV8 = K >> 3;
+  for (int i = threadIdx.x; i < NT * 8 * KV8; i += blockDim.x) {
+    const int r = i / KV8, kv = i - r * KV8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < R) v = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ldx + kv * 8);
+    *reinterpret_cast<uint4*>(xs + r * lds + kv * 8) = v;
+  }
+  __syncthreads();
+  for (int cg = 0; cg < cpc; ++cg) {
+    if (cg) { n0 = rows_of(cg, w0, w1); if (n0 < N) load(w0, w1, 0); }
+    if (n0 >= N) break;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    for (int kc0 = 0; kc0 < KC; kc0 += BATCH) {
+      if (kc0) load(w0, w1, kc0);
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        if (kc0 + u < KC) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 xb = *reinterpret_cast<const uint4*>(xs + (nt * 8 + g) * lds + (kc0 + u) * 32 + t * 8);
+            gemv_mma16816(acc[nt], ra[u].x, rb[u].x, ra[u].y, rb[u].y, xb.x, xb.y);
+            gemv_mma16816(acc[nt], ra[u].z, rb[u].z, ra[u].w, rb[u].w, xb.z, xb.w);
+          }
+        }
+      }
+    }
+    // accumulator (g, t): weight rows n0 + g and n0 + g + 8, activation rows nt * 8 + 2t and + 1
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = nt * 8 + 2 * t + (j & 1), n = n0 + g + (j >> 1) * 8;
+        if (r < R && n < N) y[static_cast<size_t>(r) * ldy + n] = static_cast<TO>(acc[nt][j]);
+      }
+    }
+  }
+  pdl_trigger();
+}
+
+template <int NT, typename TO>
+static int launch_gemv_wide(const void* x, int ldx, const void* W, int ldw, void* y, int ldy, int rows, int N, int K,
+                            cudaStream_t s) {
+  auto kern = gemv_wide_mma_kernel<NT, TO>;
+  const int smem = NT * 8 * (K + GEMV_MMA_PAD) * 2;
+  if (smem > 200 * 1024) return -6;
+  if (smem > 48 * 1024) {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+  }
+  const int groups = (N + GEMV_WARPS * 16 - 1) / (GEMV_WARPS * 16);
+  int cpc = (groups + 2367) / 2368;                  // short CTAs: the tail of the last wave stays small
+  if (cpc < 1) cpc = 1;
+  dim3 grid((groups + cpc - 1) / cpc);
+  const cudaError_t err = spark_launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, s, dim3(1, 1, 1),
+                                           (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)y, ldy, rows, N, K, cpc);
+  return err == cudaSuccess ? 0 : -4;
+}
+
+// Shapes the wide kernel takes: one item, no activation, no expert tables, K a multiple of 32.
+static bool gemv_wide_ok(int ldx, int ldw, int items, int N, int K, const int* pe, const int* pr, int act) {
+  return items == 1 && !pe && !pr && act == 0 && N >= 2048 && (K & 31) == 0 && (ldx & 7) == 0 && (ldw & 7) == 0;
+}
+
 }  // namespace spark
 
 using namespace spark;
@@ -149,6 +259,14 @@ extern "C" int spark_gemv_bf16(const void* x, int ldx, const void* W, long long 
                                int act, float limit, int out_f32, cudaStream_t s) {
   if (items <= 0 || rows_per_item <= 0) return 0;
   if (K % 8 || rows_per_item > 16) return -5;
+  if (gemv_wide_ok(ldx, ldw, items, N, K, pair_expert, pair_row, act) &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) == 0) {
+    if (rows_per_item <= 8)
+      return out_f32 ? launch_gemv_wide<1, float>(x, ldx, W, ldw, y, ldy, rows_per_item, N, K, s)
+                     : launch_gemv_wide<1, __nv_bfloat16>(x, ldx, W, ldw, y, ldy, rows_per_item, N, K, s);
+    return out_f32 ? launch_gemv_wide<2, float>(x, ldx, W, ldw, y, ldy, rows_per_item, N, K, s)
+                   : launch_gemv_wide<2, __nv_bfloat16>(x, ldx, W, ldw, y, ldy, rows_per_item, N, K, s);
+  }
 #define SPARK_GEMV_CASE(RB)                                                                                          \
   if (rows_per_item <= RB)                                                                                           \
     return out_f32 ? launch_gemv<RB, float>(x, ldx, W, expert_stride, ldw, y, ldy, items, rows_per_item, N, K,       \

@@ -46,7 +46,7 @@ if which in ("all", "moe"):
 if which in ("all", "gemv"):
     V = 151936
     lm = [torch.randn(V, H, device=dev).bfloat16() for _ in range(2)]
-    for R in (1, 4):
+    for R in (1, 4, 8, 16):
         x = torch.randn(R, H, device=dev).bfloat16()
         t = gtime([(lambda w=w: cu.gemv_bf16(x, w, out_f32=True)) for w in lm])
         out.append((f"lm_head gemv R={R}", t, V * H * 2 / t / 1e6))

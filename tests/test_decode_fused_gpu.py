@@ -27,11 +27,17 @@ def rel_err(a, b):
 
 def test_gemv_bf16_wide_grid():
     g = torch.Generator(device=DEV).manual_seed(4)
-    R, H, N = 4, 1024, 40000                   # wide enough that a CTA loops over several column groups
-    x = torch.randn(R, H, device=DEV, generator=g).bfloat16()
+    H, N = 1024, 40003                         # wide, and not a multiple of the 16 weight rows a warp owns
     W = (torch.randn(N, H, device=DEV, generator=g) * 0.05).bfloat16()
-    y = cu().gemv_bf16(x, W, out_f32=True)
-    assert rel_err(y, x.float() @ W.float().t()) < 1e-4
+    x = torch.randn(13, H, device=DEV, generator=g).bfloat16()
+    outs = {}
+    for R in (1, 4, 9, 13):
+        outs[R] = y = cu().gemv_bf16(x[:R].contiguous(), W, out_f32=True)
+        assert rel_err(y, x[:R].float() @ W.float().t()) < 1e-4
+        assert torch.isfinite(y).all()
+        assert torch.equal(y[0], outs[1][0])                    # a row's logits do not depend on the batch
+    yb = cu().gemv_bf16(x[:4].contiguous(), W, out_f32=False)
+    assert rel_err(yb, x[:4].float() @ W.float().t()) < 8e-3
 
 
 @pytest.mark.parametrize("kind,E,k", [("softmax", 512, 10), ("sigmoid_bias", 288, 8), ("sqrt_softplus", 384, 6)])
