@@ -304,7 +304,7 @@ def main():
         pass
     hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
     kv_t = next((mix.k if hasattr(mix, "k") else mix.lat for _, mix, _ in eng.model.layers if hasattr(mix, "k") or hasattr(mix, "lat")), None)
-    kv_label = {torch.bfloat16: "bf16", torch.float8_e4m3fn: "fp8", torch.float32: "fp32"}.get(kv_t.dtype, str(kv_t.dtype)) \
+    kv_label = {torch.bfloat16: "bf16", torch.float8_e4m3fn: "fp8", torch.uint8: "fp8 (packed latent rows)", torch.float32: "fp32"}.get(kv_t.dtype, str(kv_t.dtype)) \
         if kv_t is not None else "none"
     out = {
         "metric": "aggregate decode tok/s at 4 streams" if S == 4 else f"aggregate decode tok/s at {S} streams",

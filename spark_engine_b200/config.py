@@ -110,6 +110,7 @@ class ModelConfig:
     weight_format: str = "dense"  # dense | exl3 | mx (MXFP4 experts + FP8 dense)
     exl3_bits: int = 4
     kv_dtype: str = "bf16"        # bf16 | fp8
+    kv_quant_on_cpu: bool = False  # the CPU runner keeps fp32 caches; set to model the packed FP8 latent rows there too
 
     def to_json(self) -> str:
         return json.dumps(dataclasses.asdict(self), indent=1)

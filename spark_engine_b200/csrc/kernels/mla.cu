@@ -9,9 +9,13 @@
 //                     row, which is both key and value), so the latent tile is fetched once per split and used by
 //                     64 heads.  mma.sync m16n8k16 bf16, ldmatrix-fed; token gather by cp.async from the selection.
 //   mla_merge_kernel  ordered merge of the splits (+ attention sink in the denominator), bf16 latent-space output.
+// FP8 cache rows (lat_fp8): [kv_lora e4m3 | 4 fp32 tile scales (tiles of kv_lora / max(1, kv_lora / 128)) | rope bf16],
+// 656 bytes instead of 1152 for 512 + 64; the decode kernel copies the packed row into the tail of its bf16 tile row and
+// a warp expands it in place.
 // The visible tokens of a row come from the top-k pool selection (sparse_select.cu) or are 0..pos.
 // Reference: engine-rs/shim/latent.cu (sparse_latent*, latent_tc16*, merge_latent), ds41_attn.cu:90-424,
-// engine-rs/src/mla_latent.rs:196-248, dsa.rs:127-230.
+// engine-rs/src/mla_latent.rs:36-38,196-248, dsa.rs:127-230; FP8 rows: latent.cu:25-47.
+#include <cuda_fp8.h>
 #include "../common/ptx.cuh"
 
 namespace spark {
@@ -49,12 +53,16 @@ mla_prep_kernel(const __nv_bfloat16* __restrict__ a, int lda, MlaDims dm, const 
                 const float* __restrict__ ape, const double* __restrict__ inv_freq, const int* __restrict__ pos,
                 const long long* __restrict__ row_kv, const int* __restrict__ row_j,
                 __nv_bfloat16* __restrict__ cq, __nv_bfloat16* __restrict__ lat, float* __restrict__ ik,
-                float* __restrict__ ig, float* __restrict__ pool, float* __restrict__ hw) {
+                float* __restrict__ ig, float* __restrict__ pool, float* __restrict__ hw,
+                const int* __restrict__ row_pos0, int lat_fp8) {
   __shared__ float red[4];
+  __shared__ int tmax[4];
   const int r = blockIdx.x, t = threadIdx.x;
   const __nv_bfloat16* ar = a + static_cast<size_t>(r) * lda;
   const int p = pos[r];
-  const long long tok = row_kv[r] + p;
+  // rows of a verification tree (row_pos0 given) are rotated at their depth position p but stored at the slot of
+  // their node, first in-flight slot + node index; their pools are finished when the accepted path is compacted
+  const long long tok = row_kv[r] + (row_pos0 ? row_pos0[r] + row_j[r] : p);
   const int KW = dm.kv_lora + dm.rope;
   // q low-rank activation
   float ss = 0.f;
@@ -68,7 +76,27 @@ mla_prep_kernel(const __nv_bfloat16* __restrict__ a, int lda, MlaDims dm, const 
   for (int i = t; i < dm.kv_lora; i += 128) { const float x = __bfloat162float(akv[i]); ss = fmaf(x, x, ss); }
   rs = rsqrtf(block_sum_128(ss, red) / dm.kv_lora + dm.eps);
   __nv_bfloat16* lrow = lat + tok * KW;
-  for (int i = t; i < dm.kv_lora; i += 128) lrow[i] = __float2bfloat16(__bfloat162float(akv[i]) * rs * kv_norm[i]);
+  if (lat_fp8) {
+    const int nt8 = max(1, dm.kv_lora >> 7), tw = dm.kv_lora / nt8;
+    uint8_t* brow = reinterpret_cast<uint8_t*>(lat) + tok * (dm.kv_lora + 16 + 2 * dm.rope);
+    if (t < 4) tmax[t] = 0;
+    __syncthreads();
+    for (int i = t; i < dm.kv_lora; i += 128)
+      atomicMax(&tmax[i / tw], __float_as_int(fabsf(__bfloat162float(akv[i]) * rs * kv_norm[i])));   // non-negative floats order as ints
+    __syncthreads();
+    for (int i = t; i < dm.kv_lora; i += 128) {
+      const float amax = __int_as_float(tmax[i / tw]);
+      const float sc = amax > 0.f ? amax / 448.f : 1.f;
+      brow[i] = __nv_cvt_float_to_fp8(__bfloat162float(akv[i]) * rs * kv_norm[i] / sc, __NV_SATFINITE, __NV_E4M3);
+    }
+    if (t < 4) {
+      const float amax = __int_as_float(tmax[t]);
+      reinterpret_cast<float*>(brow + dm.kv_lora)[t] = t < nt8 ? (amax > 0.f ? amax / 448.f : 1.f) : 0.f;
+    }
+    lrow = reinterpret_cast<__nv_bfloat16*>(brow + dm.kv_lora + 16) - dm.kv_lora;     // rope tail written below
+  } else {
+    for (int i = t; i < dm.kv_lora; i += 128) lrow[i] = __float2bfloat16(__bfloat162float(akv[i]) * rs * kv_norm[i]);
+  }
   const int half = dm.rope >> 1;
   for (int i = t; i < half; i += 128) {
     const float x1 = __bfloat162float(akv[dm.kv_lora + i]), x2 = __bfloat162float(akv[dm.kv_lora + half + i]);
@@ -84,7 +112,7 @@ mla_prep_kernel(const __nv_bfloat16* __restrict__ a, int lda, MlaDims dm, const 
   idx_key_gate(ar, o1, Dm, ln_w, ln_b, red, key, gate);
   if (t < Dm) { ik[tok * Dm + t] = key; ig[tok * Dm + t] = gate; }
   if (t < dm.idx_heads) hw[static_cast<size_t>(r) * dm.idx_heads + t] = __bfloat162float(ar[o1 + 2 * Dm + t]) * rsqrtf(static_cast<float>(dm.idx_heads));
-  if ((p + 1) % dm.pool == 0) {
+  if (!row_pos0 && (p + 1) % dm.pool == 0) {
     // this row closes a pool: gates/keys of the earlier tokens come from this launch's rows when they belong to
     // the same segment (their cache entries may not be written yet), else from the cache
     float gmax = gate + ape[(dm.pool - 1) * Dm + (t < Dm ? t : 0)];
@@ -154,7 +182,9 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
                   const int* __restrict__ pos, const long long* __restrict__ row_kv, const int* __restrict__ sel,
                   const int* __restrict__ sel_n, int sel_ld, float* __restrict__ part_o,   // [R, H, nsplit, L]
                   float* __restrict__ part_ml,                   // [R, H, nsplit, 2]
-                  int H, int KW, int L, float scale, int nsplit, int spc) {
+                  int H, int KW, int L, float scale, int nsplit, int spc,
+                  const int* __restrict__ row_pos0, const int* __restrict__ row_j, const int* __restrict__ anc,
+                  int lat_fp8) {
   extern __shared__ __align__(16) uint8_t smem_mla[];
   const int LDK = KW + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_mla);          // [HM*16][LDK]
@@ -164,7 +194,12 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   __shared__ int stok[MLA_TS];
   const int r = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int n_ctx = sel ? sel_n[r] : pos[r] + 1;
+  // tree rows (anc given, no selection): the committed context [0, first in-flight slot) plus the in-flight slots
+  // of the row's ancestors and its own, bit j of anc[r] = node j of the sequence is visible
+  const bool tree = anc != nullptr;
+  const int tp0 = tree ? row_pos0[r] : 0;
+  const unsigned amask = tree ? static_cast<unsigned>(anc[r]) : 0u;
+  const int n_ctx = sel ? sel_n[r] : (tree ? tp0 + row_j[r] + 1 : pos[r] + 1);
   const long long base = row_kv[r];
   const int VPR = KW >> 3;
   // the row's queries (all heads) are staged once and serve every split this CTA walks through
@@ -187,13 +222,59 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   __syncthreads();                                             // the previous split's tiles are no longer read
   if (tid < MLA_TS) stok[tid] = tid < nt ? (sel ? sel[static_cast<size_t>(r) * sel_ld + t0 + tid] : t0 + tid) : -1;
   __syncthreads();
-  for (int i = tid; i < MLA_TS * VPR; i += 256) {
-    const int k = i / VPR, v = i - k * VPR;
-    if (stok[k] >= 0) mla_cp16(Ls + k * LDK + v * 8, lat + (base + stok[k]) * KW + v * 8);
-    else *reinterpret_cast<uint4*>(Ls + k * LDK + v * 8) = make_uint4(0u, 0u, 0u, 0u);
+  if (!lat_fp8) {
+    for (int i = tid; i < MLA_TS * VPR; i += 256) {
+      const int k = i / VPR, v = i - k * VPR;
+      if (stok[k] >= 0) mla_cp16(Ls + k * LDK + v * 8, lat + (base + stok[k]) * KW + v * 8);
+      else *reinterpret_cast<uint4*>(Ls + k * LDK + v * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+  } else {
+    // packed rows land at byte L of their tile row (the row is 2 KW + 16 bytes, the packed row L + 16 + 2 rope), then
+    // one warp per row expands them in place: every lane reads its 16 codes, its scale and its piece of the rope
+    // tail into registers before any lane writes
+    const int RB = L + 16 + 2 * (KW - L), CH = RB >> 4;
+    const uint8_t* lat8 = reinterpret_cast<const uint8_t*>(lat);
+    for (int i = tid; i < MLA_TS * CH; i += 256) {
+      const int k = i / CH, v = i - k * CH;
+      if (stok[k] >= 0) mla_cp16(reinterpret_cast<uint8_t*>(Ls + k * LDK) + L + v * 16, lat8 + (base + stok[k]) * RB + v * 16);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    const int nt8 = max(1, L >> 7), tw = L / nt8, rch = (KW - L) >> 3;
+    for (int k = warp; k < MLA_TS; k += 8) {
+      uint8_t* rowb = reinterpret_cast<uint8_t*>(Ls + k * LDK);
+      if (stok[k] < 0) {
+        for (int v = lane; v < VPR; v += 32) *reinterpret_cast<uint4*>(rowb + v * 16) = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
+      const bool mine = lane < (L >> 4);
+      uint4 q = make_uint4(0u, 0u, 0u, 0u), rp = q;
+      float sc = 0.f;
+      if (mine) {
+        q = *reinterpret_cast<const uint4*>(rowb + L + lane * 16);
+        sc = *reinterpret_cast<const float*>(rowb + 2 * L + (lane * 16 / tw) * 4);
+      }
+      if (lane < rch) rp = *reinterpret_cast<const uint4*>(rowb + 2 * L + 16 + lane * 16);
+      __syncwarp();
+      if (mine) {
+        const uint16_t* q2 = reinterpret_cast<const uint16_t*>(&q);
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(q2[j], __NV_E4M3);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+          const __nv_bfloat162 b = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+          o[j] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(rowb + lane * 32) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(rowb + lane * 32 + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      if (lane < rch) *reinterpret_cast<uint4*>(rowb + 2 * L + lane * 16) = rp;
+    }
+    __syncthreads();
   }
-  asm volatile("cp.async.wait_all;" ::: "memory");
-  __syncthreads();
   // ---- phase 1: S[h][tok] for this warp's 8 tokens, all head tiles
   {
     float s[HM][4];
@@ -225,10 +306,16 @@ mla_decode_kernel(const __nv_bfloat16* __restrict__ q_full,      // [R, H, KW]
   __syncthreads();
   // ---- phase 2: per-head softmax statistics over the split; P (bf16) for the second product
   for (int h = warp; h < HM * 16; h += 8) {
-    const float s0 = lane < nt ? Ss[h * 65 + lane] : -INFINITY;
-    const float s1 = lane + 32 < nt ? Ss[h * 65 + lane + 32] : -INFINITY;
-    const float m = warp_max(fmaxf(s0, s1));
-    const float e0 = lane < nt ? __expf(s0 - m) : 0.f, e1 = lane + 32 < nt ? __expf(s1 - m) : 0.f;
+    bool v0 = lane < nt, v1 = lane + 32 < nt;
+    if (tree) {
+      const int k0 = t0 + lane - tp0, k1 = k0 + 32;
+      v0 = v0 && (k0 < 0 || (k0 < 32 && ((amask >> k0) & 1u)));
+      v1 = v1 && (k1 < 0 || (k1 < 32 && ((amask >> k1) & 1u)));
+    }
+    const float s0 = v0 ? Ss[h * 65 + lane] : -INFINITY;
+    const float s1 = v1 ? Ss[h * 65 + lane + 32] : -INFINITY;
+    const float m = warp_max(fmaxf(s0, s1));                     // -inf when the split holds no visible token
+    const float e0 = v0 ? __expf(s0 - m) : 0.f, e1 = v1 ? __expf(s1 - m) : 0.f;
     const float l = warp_sum(e0 + e1);
     Ps[h * 72 + lane] = __float2bfloat16(e0);
     Ps[h * 72 + lane + 32] = __float2bfloat16(e1);
@@ -323,16 +410,23 @@ mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ par
 
 using namespace spark;
 
+// Shapes the packed FP8 rows cover: at most four scale tiles, 16 codes per lane of one warp, 16-byte pieces.
+static bool mla_fp8_ok(int kv_lora, int rope) {
+  const int nt8 = kv_lora >= 128 ? kv_lora / 128 : 1;
+  return kv_lora <= 512 && kv_lora % 16 == 0 && kv_lora % nt8 == 0 && (kv_lora / nt8) % 16 == 0 && rope % 8 == 0 && rope <= 256;
+}
+
 extern "C" int spark_mla_prep(const void* a, int lda, int R, int q_lora, int kv_lora, int rope, int idx_dim, int idx_heads,
                               int pool_sz, float eps, const float* q_norm, const float* kv_norm, const float* ln_w,
                               const float* ln_b, const float* ape, const double* inv_freq, const int* pos,
                               const long long* row_kv, const int* row_j, void* cq, void* lat, float* ik, float* ig,
-                              float* pool, float* hw, cudaStream_t s) {
+                              float* pool, float* hw, cudaStream_t s, const int* row_pos0, int lat_fp8) {
   if (R <= 0) return 0;
   if (idx_dim > 128 || idx_heads > 128 || pool_sz > 8 || pool_sz < 1 || (rope & 1)) return -5;
+  if (lat_fp8 && !mla_fp8_ok(kv_lora, rope)) return -5;
   MlaDims dm{q_lora, kv_lora, rope, idx_dim, idx_heads, pool_sz, eps};
   mla_prep_kernel<<<R, 128, 0, s>>>((const __nv_bfloat16*)a, lda, dm, q_norm, kv_norm, ln_w, ln_b, ape, inv_freq, pos, row_kv,
-                                    row_j, (__nv_bfloat16*)cq, (__nv_bfloat16*)lat, ik, ig, pool, hw);
+                                    row_j, (__nv_bfloat16*)cq, (__nv_bfloat16*)lat, ik, ig, pool, hw, row_pos0, lat_fp8);
   return spark_launch_rc(__func__);
 }
 
@@ -348,22 +442,26 @@ extern "C" int spark_mla_qrope(const void* qb, int ldq, int R, int H, int D, int
 // part_o: fp32 [R, H, nsplit, L]; part_ml: fp32 [R, H, nsplit, 2]; out: bf16 [R, H, L].
 extern "C" int spark_mla_attn(const void* q_full, const void* lat, const int* pos, const long long* row_kv, const int* sel,
                               const int* sel_n, int sel_ld, float* part_o, float* part_ml, int nsplit, const float* sink,
-                              int R, int H, int kv_lora, int rope, float scale, void* out, cudaStream_t s) {
+                              int R, int H, int kv_lora, int rope, float scale, void* out, cudaStream_t s,
+                              const int* row_pos0, const int* row_j, const int* anc, int lat_fp8) {
   if (R <= 0) return 0;
   const int KW = kv_lora + rope;
+  if (lat_fp8 && !mla_fp8_ok(kv_lora, rope)) return -5;
   if (H > 64 || (KW & 15) || (kv_lora & 15) || nsplit <= 0) return -5;
+  if (anc && (sel || !row_pos0 || !row_j)) return -5;          // tree rows read a dense context
   const int HM = H <= 16 ? 1 : (H <= 32 ? 2 : 4);
   const int smem = (HM * 16 + MLA_TS) * (KW + 8) * 2 + HM * 16 * 65 * 4 + HM * 16 * 72 * 2;
   if (smem > 200 * 1024) return -6;
   void (*kern)(const __nv_bfloat16*, const __nv_bfloat16*, const int*, const long long*, const int*, const int*, int, float*,
-               float*, int, int, int, float, int, int) = HM == 1 ? mla_decode_kernel<1> : (HM == 2 ? mla_decode_kernel<2> : mla_decode_kernel<4>);
+               float*, int, int, int, float, int, int, const int*, const int*, const int*, int) = HM == 1 ? mla_decode_kernel<1> : (HM == 2 ? mla_decode_kernel<2> : mla_decode_kernel<4>);
   static bool done[3] = {false, false, false};
   const int id = HM == 1 ? 0 : (HM == 2 ? 1 : 2);
   if (!done[id]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); done[id] = true; }
   // few rows (decode): one split per CTA for parallelism; many rows (prefill): a CTA per row walks all its splits
   const int spc = R >= 128 ? nsplit : (R >= 32 ? 4 : 1);
   kern<<<dim3(R, (nsplit + spc - 1) / spc), 256, smem, s>>>((const __nv_bfloat16*)q_full, (const __nv_bfloat16*)lat, pos, row_kv,
-                                                            sel, sel_n, sel_ld, part_o, part_ml, H, KW, kv_lora, scale, nsplit, spc);
+                                                            sel, sel_n, sel_ld, part_o, part_ml, H, KW, kv_lora, scale, nsplit, spc,
+                                                            row_pos0, row_j, anc, lat_fp8);
   if (H * nsplit * 4 > 48 * 1024) return -6;
   int hpc = H;                                          // heads per merge CTA: enough CTAs for two per SM when rows are few
   while (hpc > 1 && R * ((H + hpc - 1) / hpc) < 296) hpc = (hpc + 1) / 2;

@@ -148,6 +148,204 @@ topk_select_kernel(const float* __restrict__ score, int ld, const int* __restric
   if (t == 0) sel_n[r] = cnt + (p - lo + 1);
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Multi-CTA form of the same exact selection for very long contexts (>= 128K candidates per row, where one CTA per row
+// leaves a decode round of a few rows on a handful of SMs): C CTAs per row, each owning one slice of the candidates.
+//   mc_hist   x3  pass 2, 1, 0 over key digits of 11 / 11 / 10 bits: every CTA first resolves the passes already
+//                 finished from the row's global histograms (a block-wide suffix scan of 2048 bins), then adds its
+//                 slice's digits of the current pass to the global histogram through a shared-memory one.
+//   mc_count      per slice: keys above the threshold in fully selectable blocks, keys equal to it, and those of
+//                 them in fully selectable blocks.
+//   mc_emit       a CTA sums the counts of the slices before it (ties go to the lowest indices, so the equal keys a
+//                 slice may take are what earlier slices left), emits its slice in ascending block order; the last
+//                 CTA adds the straddling block, the always-visible range and the count.
+// Launches depend on one another only through stream order: no CTA waits for another.  Output identical to
+// topk_select_kernel.  Reference: engine-rs/shim/ds41_attn.cu:825-942 (multi-CTA radix select).
+constexpr int MC_BINS = 2048;
+
+__device__ __forceinline__ int mc_digit(uint32_t key, int pass) {
+  return pass == 2 ? static_cast<int>(key >> 21) : (pass == 1 ? static_cast<int>((key >> 10) & 2047u) : static_cast<int>(key & 1023u));
+}
+__device__ __forceinline__ uint32_t mc_place(int d, int pass) {
+  return pass == 2 ? static_cast<uint32_t>(d) << 21 : (pass == 1 ? static_cast<uint32_t>(d) << 10 : static_cast<uint32_t>(d));
+}
+__device__ __forceinline__ uint32_t mc_mask(int pass) {       // bits decided once passes > `pass`... down to `pass` are done
+  return pass == 2 ? 0xFFE00000u : (pass == 1 ? 0xFFFFFC00u : 0xFFFFFFFFu);
+}
+
+// Resolves passes 2 .. last (inclusive) from the row's global histograms; all 1024 threads call it.
+__device__ void mc_resolve(const int* __restrict__ gh, int last, int k, int* warp_tot, int* s_pair, uint32_t& prefix, int& need) {
+  prefix = 0u;
+  need = k;
+  for (int pass = 2; pass >= last; --pass) {
+    const int* h = gh + pass * MC_BINS;
+    // thread t owns bins 2047 - 2t and 2046 - 2t: an exclusive scan in thread order counts the keys with larger digits
+    const int h0 = h[MC_BINS - 1 - 2 * threadIdx.x], h1 = h[MC_BINS - 2 - 2 * threadIdx.x];
+    int tot;
+    const int before = block_excl_scan(h0 + h1, warp_tot, tot);
+    if (before < need && before + h0 >= need) { s_pair[0] = MC_BINS - 1 - 2 * threadIdx.x; s_pair[1] = need - before; }
+    else if (before + h0 < need && before + h0 + h1 >= need) { s_pair[0] = MC_BINS - 2 - 2 * threadIdx.x; s_pair[1] = need - before - h0; }
+    __syncthreads();
+    prefix |= mc_place(s_pair[0], pass);
+    need = s_pair[1];
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void mc_slice(int vis, int C, int c, int& i0, int& i1) {
+  const int chunk = ((vis + C - 1) / C + 31) & ~31;
+  i0 = min(vis, c * chunk);
+  i1 = min(vis, i0 + chunk);
+}
+
+// grid (C, R), 1024 threads.  ghist [R, 3, 2048] zeroed before pass 2.
+__global__ void __launch_bounds__(1024)
+mc_hist_kernel(const float* __restrict__ score, int ld, const int* __restrict__ pos, int block, int k, int pass,
+               int* __restrict__ ghist) {
+  __shared__ int hist[MC_BINS];
+  __shared__ int warp_tot[32];
+  __shared__ int s_pair[2];
+  const int r = blockIdx.y, t = threadIdx.x;
+  const int vis = (pos[r] + 1) / block;
+  if (vis <= k) return;
+  int* gh = ghist + static_cast<size_t>(r) * 3 * MC_BINS;
+  uint32_t prefix = 0u;
+  int need = k;
+  if (pass < 2) mc_resolve(gh, pass + 1, k, warp_tot, s_pair, prefix, need);
+  const uint32_t mask = pass < 2 ? mc_mask(pass + 1) : 0u;
+  hist[t] = 0; hist[t + 1024] = 0;
+  __syncthreads();
+  int i0, i1;
+  mc_slice(vis, gridDim.x, blockIdx.x, i0, i1);
+  const uint32_t* s = reinterpret_cast<const uint32_t*>(score + static_cast<size_t>(r) * ld);
+  for (int i = i0 + t; i < i1; i += 1024) {
+    const uint32_t key = order_key(s[i]);
+    if ((key & mask) == prefix) atomicAdd(&hist[mc_digit(key, pass)], 1);
+  }
+  __syncthreads();
+  for (int b = t; b < MC_BINS; b += 1024)
+    if (hist[b]) atomicAdd(&gh[pass * MC_BINS + b], hist[b]);
+}
+
+__device__ __forceinline__ int mc_lo(int p, int vis, int block, int window) {
+  const int tail0 = vis * block;
+  return window > 0 ? min(max(0, p + 1 - window), tail0) : tail0;
+}
+
+// grid (C, R), 1024 threads.  counts [R, C, 3] = {above threshold and full, equal, equal and full}
+__global__ void __launch_bounds__(1024)
+mc_count_kernel(const float* __restrict__ score, int ld, const int* __restrict__ pos, int block, int k, int window,
+                const int* __restrict__ ghist, int* __restrict__ counts) {
+  __shared__ int warp_tot[32];
+  __shared__ int s_pair[2];
+  __shared__ int s_cnt[3];
+  const int r = blockIdx.y, t = threadIdx.x, p = pos[r];
+  const int vis = (p + 1) / block;
+  if (vis <= k) return;
+  uint32_t thr;
+  int need;
+  mc_resolve(ghist + static_cast<size_t>(r) * 3 * MC_BINS, 0, k, warp_tot, s_pair, thr, need);
+  if (t < 3) s_cnt[t] = 0;
+  __syncthreads();
+  const int nfull = mc_lo(p, vis, block, window) / block;        // blocks 0 .. nfull-1 lie below the always-visible range
+  int i0, i1;
+  mc_slice(vis, gridDim.x, blockIdx.x, i0, i1);
+  const uint32_t* s = reinterpret_cast<const uint32_t*>(score + static_cast<size_t>(r) * ld);
+  int gt_full = 0, eq = 0, eq_full = 0;
+  for (int i = i0 + t; i < i1; i += 1024) {
+    const uint32_t key = order_key(s[i]);
+    gt_full += key > thr && i < nfull;
+    eq += key == thr;
+    eq_full += key == thr && i < nfull;
+  }
+  gt_full = __reduce_add_sync(0xffffffffu, gt_full); eq = __reduce_add_sync(0xffffffffu, eq);
+  eq_full = __reduce_add_sync(0xffffffffu, eq_full);
+  if ((t & 31) == 0) { atomicAdd(&s_cnt[0], gt_full); atomicAdd(&s_cnt[1], eq); atomicAdd(&s_cnt[2], eq_full); }
+  __syncthreads();
+  if (t < 3) counts[(static_cast<size_t>(r) * gridDim.x + blockIdx.x) * 3 + t] = s_cnt[t];
+}
+
+// grid (C, R), 1024 threads.
+__global__ void __launch_bounds__(1024)
+mc_emit_kernel(const float* __restrict__ score, int ld, const int* __restrict__ pos, int block, int k, int window,
+               const int* __restrict__ ghist, const int* __restrict__ counts, int* __restrict__ sel, int sel_ld,
+               int* __restrict__ sel_n) {
+  __shared__ int warp_tot[32];
+  __shared__ int s_pair[2];
+  __shared__ int s_before[2];
+  const int r = blockIdx.y, t = threadIdx.x, p = pos[r], C = gridDim.x, c = blockIdx.x;
+  const int vis = (p + 1) / block;
+  int* out = sel + static_cast<size_t>(r) * sel_ld;
+  if (vis <= k) {                                  // every token is visible
+    for (int i = c * 1024 + t; i <= p; i += C * 1024) out[i] = i;
+    if (c == 0 && t == 0) sel_n[r] = p + 1;
+    return;
+  }
+  uint32_t thr;
+  int need;
+  mc_resolve(ghist + static_cast<size_t>(r) * 3 * MC_BINS, 0, k, warp_tot, s_pair, thr, need);
+  const int lo = mc_lo(p, vis, block, window);
+  const int nfull = lo / block;
+  const int* cn = counts + static_cast<size_t>(r) * C * 3;
+  if (t == 0) {
+    int eq_before = 0, full_before = 0;
+    for (int q = 0; q < c; ++q) {
+      full_before += cn[q * 3] + min(cn[q * 3 + 2], max(0, need - eq_before));
+      eq_before += cn[q * 3 + 1];
+    }
+    s_before[0] = eq_before; s_before[1] = full_before;
+  }
+  __syncthreads();
+  int eq_taken = s_before[0], n_out = s_before[1];
+  int i0, i1;
+  mc_slice(vis, C, c, i0, i1);
+  const uint32_t* s = reinterpret_cast<const uint32_t*>(score + static_cast<size_t>(r) * ld);
+  for (int base = i0; base < i1; base += 1024) {
+    const int i = base + t;
+    const uint32_t key = i < i1 ? order_key(s[i]) : 0u;
+    const int is_eq = (i < i1 && key == thr) ? 1 : 0;
+    int tot_eq;
+    const int eq_rank = block_excl_scan(is_eq, warp_tot, tot_eq);
+    const int take = (i < i1) && (key > thr || (is_eq && eq_taken + eq_rank < need));
+    const int full = take && i < nfull;
+    int tot_take;
+    const int o = block_excl_scan(full ? 1 : 0, warp_tot, tot_take);
+    if (full) {
+      const int dst = (n_out + o) * block;
+      for (int j = 0; j < block; ++j) out[dst + j] = i * block + j;
+    }
+    n_out += tot_take;
+    eq_taken += tot_eq;
+  }
+  if (c != C - 1) return;
+  // ---- last CTA: n_out is the row's total; the block that straddles lo, then the always-visible range
+  int cnt = n_out * block;
+  const int sb = nfull;
+  if (lo > sb * block && sb < vis) {               // lo inside block sb: is sb selected?
+    const uint32_t ksb = order_key(s[sb]);
+    int taken = ksb > thr;
+    if (ksb == thr) {
+      // rank of sb among the equal keys = equal keys of the slices before sb's + those before sb inside its slice
+      const int chunk = ((vis + C - 1) / C + 31) & ~31;
+      const int cs = sb / chunk;
+      int part = 0;
+      for (int i = cs * chunk + t; i < sb; i += 1024) part += order_key(s[i]) == thr;
+      int tot;
+      block_excl_scan(part, warp_tot, tot);
+      int eq_b = tot;
+      for (int q = 0; q < cs; ++q) eq_b += cn[q * 3 + 1];
+      taken = eq_b < need;
+    }
+    if (taken) {
+      const int m = lo - sb * block;
+      if (t < m) out[cnt + t] = sb * block + t;
+      cnt += m;
+    }
+  }
+  for (int i = t; i <= p - lo; i += 1024) out[cnt + i] = lo + i;
+  if (t == 0) sel_n[r] = cnt + (p - lo + 1);
+}
+
 }  // namespace spark
 
 using namespace spark;
@@ -166,5 +364,20 @@ extern "C" int spark_topk_select(const float* score, int ld, const int* pos, int
   if (R <= 0) return 0;
   if (sel_ld < k * block + block + window || window < 0) return -5;
   topk_select_kernel<<<R, 1024, 0, s>>>(score, ld, pos, block, k, window, sel, sel_ld, sel_n);
+  return spark_launch_rc(__func__);
+}
+
+// Multi-CTA exact selection: `ctas` CTAs per row (<= 64); work: int32 [R * (3 * 2048 + 3 * ctas)] scratch.
+extern "C" int spark_topk_select_mc(const float* score, int ld, const int* pos, int R, int block, int k, int* sel,
+                                    int sel_ld, int* sel_n, cudaStream_t s, int window, int ctas, int* work) {
+  if (R <= 0) return 0;
+  if (sel_ld < k * block + block + window || window < 0 || ctas < 1 || ctas > 64 || !work) return -5;
+  int* ghist = work;
+  int* counts = work + static_cast<size_t>(R) * 3 * MC_BINS;
+  if (cudaMemsetAsync(ghist, 0, static_cast<size_t>(R) * 3 * MC_BINS * sizeof(int), s) != cudaSuccess) return -4;
+  const dim3 grid(ctas, R);
+  for (int pass = 2; pass >= 0; --pass) mc_hist_kernel<<<grid, 1024, 0, s>>>(score, ld, pos, block, k, pass, ghist);
+  mc_count_kernel<<<grid, 1024, 0, s>>>(score, ld, pos, block, k, window, ghist, counts);
+  mc_emit_kernel<<<grid, 1024, 0, s>>>(score, ld, pos, block, k, window, ghist, counts, sel, sel_ld, sel_n);
   return spark_launch_rc(__func__);
 }

@@ -422,6 +422,37 @@ class AttnMixer:
         return d
 
 
+def _latent_tiles(kv_lora: int):
+    nt = kv_lora // 128 if kv_lora >= 128 else 1
+    return nt, kv_lora // nt
+
+
+def pack_latent_fp8(rows: torch.Tensor, kv_lora: int) -> torch.Tensor:
+    """[n, kv_lora + rope] fp32 -> packed uint8 rows [n, kv_lora + 16 + 2 rope]: e4m3 codes with one fp32 scale per
+    tile (amax / 448), four scale slots, the rope dims in bf16."""
+    n = rows.shape[0]
+    nt, tw = _latent_tiles(kv_lora)
+    tiles = rows[:, :kv_lora].reshape(n, nt, tw)
+    amax = tiles.abs().amax(-1, keepdim=True)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    codes = (tiles / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).reshape(n, kv_lora)
+    sc = torch.zeros(n, 4, dtype=torch.float32, device=rows.device)
+    sc[:, :nt] = scale[..., 0]
+    rope = rows[:, kv_lora:].to(torch.bfloat16).contiguous().view(torch.uint8).reshape(n, -1)
+    return torch.cat((codes, sc.view(torch.uint8).reshape(n, 16), rope), 1)
+
+
+def unpack_latent_fp8(packed: torch.Tensor, kv_lora: int) -> torch.Tensor:
+    n = packed.shape[0]
+    nt, tw = _latent_tiles(kv_lora)
+    codes = packed[:, :kv_lora].contiguous().view(torch.float8_e4m3fn).float().reshape(n, nt, tw)
+    sc = packed[:, kv_lora: kv_lora + 16].contiguous().view(torch.float32)[:, :nt]
+    # through bf16, as the kernels expand the codes into bf16 tiles
+    lat = (codes * sc.unsqueeze(-1)).reshape(n, kv_lora).to(torch.bfloat16).float()
+    rope = packed[:, kv_lora + 16:].contiguous().view(torch.bfloat16).float()
+    return torch.cat((lat, rope), 1)
+
+
 class MlaMixer:
     """Multi-head latent attention in the absorbed form over a latent KV cache (kv_lora + rope dims
     per token), with the DSA indexer (softmax-gated 4-token pools, top-k pools + tail), optional
@@ -431,9 +462,14 @@ class MlaMixer:
     def __init__(self, cfg: ModelConfig, w: dict, kv_tokens: int, device, dtype, alloc=None):
         c = cfg.mla
         self.cfg, self.c, self.w = cfg, c, w
-        self.fp8 = cfg.kv_dtype == "fp8" and str(device) != "cpu"
+        self.fp8 = cfg.kv_dtype == "fp8" and (str(device) != "cpu" or cfg.kv_quant_on_cpu)
         alloc = alloc or (lambda rows, shape, dt, rows_of=None: torch.zeros(rows, *shape, device=device, dtype=dt))
-        self.lat = alloc(kv_tokens, (c.kv_lora + c.rope_dim,), torch.float32 if str(device) == "cpu" else dtype, lambda t: t)
+        if self.fp8:
+            # packed rows: kv_lora e4m3 codes | 4 fp32 tile scales | rope dims in bf16 (656 bytes for 512 + 64 against
+            # 1152 in bf16; reference: shim/latent.cu:25-47, 528-byte rows without a separate rope part)
+            self.lat = alloc(kv_tokens, (c.kv_lora + 16 + 2 * c.rope_dim,), torch.uint8, lambda t: t)
+        else:
+            self.lat = alloc(kv_tokens, (c.kv_lora + c.rope_dim,), torch.float32 if str(device) == "cpu" else dtype, lambda t: t)
         self.ik = alloc(kv_tokens, (c.idx_dim,), torch.float32, lambda t: t)       # LayerNorm'ed keys
         self.ig = alloc(kv_tokens, (c.idx_dim,), torch.float32, lambda t: t)       # pool gates
         self.pool = alloc(kv_tokens // c.pool + 2, (c.idx_dim,), torch.float32, lambda t, b=c.pool: t // b + 2)
@@ -479,15 +515,19 @@ class MlaMixer:
             base, L0 = si.kv_base, s.pos0
             assert L0 + s.n <= si.kv_cap, "sequence capacity exceeded"
             sl = slice(s.r0, s.r0 + s.n)
-            self.lat[base + L0: base + L0 + s.n] = row[sl].to(self.lat.dtype)
+            self._lat_store(base + L0, row[sl])
             if s.parents is None:
                 self._append_index(base, L0, ik[sl], ig[sl])
                 mask = self._mask(base, L0, s.n, qi[sl], hw[sl]).to(h.device)
             else:
+                # tree rows keep their raw indexer keys and gates at their in-flight slots; pools are finished when
+                # the accepted path is compacted
+                self.ik[base + L0: base + L0 + s.n] = ik[sl]
+                self.ig[base + L0: base + L0 + s.n] = ig[sl]
                 mask = torch.zeros(s.n, L0 + s.n, dtype=torch.bool, device=h.device)
                 mask[:, :L0] = True
                 mask[:, L0:] = _anc_mask(s).to(h.device)
-            lat = self.lat[base: base + L0 + s.n].float()
+            lat = self._lat_load(base, base + L0 + s.n)
             sc = torch.einsum("thl,sl->hts", q_full[sl], lat) * scale
             sc = sc.masked_fill(~mask.unsqueeze(0), float("-inf"))
             if c.sink:
@@ -500,6 +540,17 @@ class MlaMixer:
             out[sl] = torch.einsum("hts,sl->thl", p, lat[:, : c.kv_lora])
         o = torch.einsum("thl,hdl->thd", out, self.w_uv)                                 # expand W_uv
         return ops.linear(o.reshape(R, c.n_heads * c.head_dim).to(h.dtype), self.w["o"])
+
+    def _lat_store(self, lo: int, rows):
+        if not self.fp8:
+            self.lat[lo: lo + rows.shape[0]] = rows.to(self.lat.dtype)
+            return
+        self.lat[lo: lo + rows.shape[0]] = pack_latent_fp8(rows.float(), self.c.kv_lora)
+
+    def _lat_load(self, lo: int, hi: int):
+        if not self.fp8:
+            return self.lat[lo:hi].float()
+        return unpack_latent_fp8(self.lat[lo:hi], self.c.kv_lora)
 
     def _append_index(self, base, L0, ik, ig):
         c = self.c
@@ -545,10 +596,20 @@ class MlaMixer:
         pass
 
     def compact(self, seqs, seg: Segment, rows: List[int]):
-        base = seqs[seg.slot].kv_base + seg.pos0
+        c = self.c
+        kvb, L0, n = seqs[seg.slot].kv_base, seg.pos0, len(rows)
+        base = kvb + L0
         for i, j in enumerate(rows):
             if i != j:
-                self.lat[base + i] = self.lat[base + j]
+                for t in (self.lat, self.ik, self.ig):
+                    t[base + i] = t[base + j]
+        # the pools that the accepted path completes (tree rows never pool at verification time)
+        b0, b1 = L0 // c.pool, (L0 + n) // c.pool
+        if b1 > b0:
+            kb = self.ik[kvb + b0 * c.pool: kvb + b1 * c.pool].view(b1 - b0, c.pool, c.idx_dim)
+            gb = self.ig[kvb + b0 * c.pool: kvb + b1 * c.pool].view(b1 - b0, c.pool, c.idx_dim) \
+                + self.w["ape"].float().view(1, c.pool, c.idx_dim).to(kb.device)
+            self.pool[kvb // c.pool + b0: kvb // c.pool + b1] = (torch.softmax(gb, 1) * kb).sum(1)
 
     def state_tensors(self):
         return {"lat": self.lat, "ik": self.ik, "ig": self.ig, "pool": self.pool}

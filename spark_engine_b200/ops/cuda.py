@@ -50,9 +50,9 @@ _SIGS = {
     "spark_gather_rows_bf16": [vp, vp, vp, i32, i32, vp],
     "spark_gdn_seq": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, i32, vp, vp, i32, i32],
     "spark_mla_prep": [vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
-                       vp, vp],
+                       vp, vp, vp, i32],
     "spark_mla_qrope": [vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp],
-    "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp],
+    "spark_mla_attn": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, i32],
     "spark_kda_chunk_prefill": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32,
                                 i32, i32, vp],
     "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32, i32],
@@ -972,12 +972,22 @@ MLA_KERNELS = os.environ.get("SPARK_MLA_KERNELS", "1") == "1"
 _KERNELS_PER_CALL["spark_mla_attn"] = 2
 
 
+def mla_fp8_shape_ok(kv_lora: int, rope: int) -> bool:
+    """Latent shapes the packed FP8 rows of the kernels cover (<= 4 scale tiles, 16 codes per lane of one warp)."""
+    nt = kv_lora // 128 if kv_lora >= 128 else 1
+    return kv_lora <= 512 and kv_lora % 16 == 0 and kv_lora % nt == 0 and (kv_lora // nt) % 16 == 0 \
+        and rope % 8 == 0 and rope <= 256
+
+
 def mla_mixer(mixer, h, plan, seqs):
-    """Latent attention on the device: returns the per-head outputs [R, H*D] (before the output projection), or None
-    (tree plans run the generic path)."""
-    if plan.is_tree or not MLA_KERNELS:
+    """Latent attention on the device: returns the per-head outputs [R, H*D] (before the output projection), or None.
+    Rows of a verification tree read the committed context densely plus their ancestors' in-flight slots (bit-masks
+    in the decode kernel); a tree on a context long enough to need the pool selection runs the generic path."""
+    if not MLA_KERNELS:
         return None
     c, w, cfg = mixer.c, mixer.w, mixer.cfg
+    if mixer.fp8 and not mla_fp8_shape_ok(c.kv_lora, c.rope_dim):
+        return None
     dev = h.device
     d = _plan_dev(plan, dev)
     R = h.shape[0]
@@ -986,6 +996,12 @@ def mla_mixer(mixer, h, plan, seqs):
         d["max_ctx"] = max(s.pos0 + s.n for s in plan.segs)
         for s in plan.segs:
             assert s.pos0 + s.n <= seqs[s.slot].kv_cap, "sequence capacity exceeded"
+    tree = plan.is_tree
+    if tree:
+        if d["max_ctx"] // c.pool > c.topk_pools:
+            return None
+        if "anc" not in d:
+            d["anc"] = tree_ancestor_masks(plan, dev)
     H, D, L, Rr = c.n_heads, c.head_dim, c.kv_lora, c.rope_dim
     KW = L + Rr
     if not hasattr(mixer, "_dev"):
@@ -1001,7 +1017,8 @@ def mla_mixer(mixer, h, plan, seqs):
     rc = lib().spark_mla_prep(P(a), a.stride(0), R, c.q_lora, L, Rr, c.idx_dim, c.idx_heads, c.pool, float(cfg.norm_eps),
                               P(w["q_a_norm"]), P(w["kv_a_norm"]), P(w["k_ln_w"]), P(w["k_ln_b"]), P(md["ape"]), P(md["inv"]),
                               P(d["pos32"]), P(d["row_kv"]), P(d["row_j"]), P(cq), P(mixer.lat), P(mixer.ik), P(mixer.ig),
-                              P(mixer.pool), P(hw), stream())
+                              P(mixer.pool), P(hw), stream(), P(d["row_pos0"]) if tree else None,
+                              int(mixer.fp8))
     check(rc, "spark_mla_prep")
     qb = _as_bf16(linear_any(cq, w["q_b"]))
     nq = H * (D + Rr)
@@ -1036,7 +1053,8 @@ def mla_mixer(mixer, h, plan, seqs):
     out_lat = torch.empty(R, H, L, dtype=torch.bfloat16, device=dev)
     rc = lib().spark_mla_attn(P(q_full), P(mixer.lat), P(d["pos32"]), P(d["row_kv"]), P(sel), P(sel_n), sel_ld, P(part_o),
                               P(part_ml), nsplit, P(w.get("sink")) if c.sink else None, R, H, L, Rr,
-                              1.0 / math.sqrt(D + Rr), P(out_lat), stream())
+                              1.0 / math.sqrt(D + Rr), P(out_lat), stream(), P(d["row_pos0"]) if tree else None,
+                              P(d["row_j"]) if tree else None, P(d["anc"]) if tree else None, int(mixer.fp8))
     check(rc, "spark_mla_attn")
     if decode:
         out = torch.empty(R, H * D, dtype=torch.bfloat16, device=dev)

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 
 import torch
 
@@ -20,6 +21,8 @@ def _dll():
         dll.spark_idx_score.restype = i32
         dll.spark_topk_select.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, vp, vp, i32]
         dll.spark_topk_select.restype = i32
+        dll.spark_topk_select_mc.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, vp, vp, i32, i32, vp]
+        dll.spark_topk_select_mc.restype = i32
         _bound = True
     return dll
 
@@ -37,9 +40,31 @@ def select_tokens(qi, pool, row_kv, pos32, block, topk, max_ctx, head_w=None, sc
                                 float(scale if scale is not None else 1.0 / math.sqrt(Dm)), cu.P(score), nb_max, nb_max,
                                 cu.stream())
     cu.check(rc, "spark_idx_score")
+    sel, sel_n = topk_select(score, nb_max, pos32, block, topk, window)
+    return sel, sel_n
+
+
+MC_MIN_CANDIDATES = int(os.environ.get("SPARK_TOPK_MC_MIN", "32768"))
+
+
+def topk_select(score, nb_max, pos32, block, topk, window=0, ctas=None):
+    """Exact top-k blocks per row (ties -> lowest index), expanded to token indices + the always-visible tail.  Rows
+    of >= MC_MIN_CANDIDATES candidates with few rows in the batch use the multi-CTA select (`ctas` CTAs per row, 4096
+    candidates each, at most 64); the result is identical."""
+    R = pos32.shape[0]
+    dev = score.device
     sel_ld = topk * block + block + window
     sel = torch.empty(R, sel_ld, dtype=torch.int32, device=dev)
     sel_n = torch.empty(R, dtype=torch.int32, device=dev)
+    if ctas is None:
+        ctas = min(64, (nb_max + 4095) // 4096) if (nb_max >= MC_MIN_CANDIDATES and R <= 64) else 1
+    if ctas > 1:
+        work = cu.scratch("topk_mc_work", R * (3 * 2048 + 3 * ctas), torch.int32, dev)
+        cu.add_launches(4)                       # 5 launches instead of 1
+        rc = _dll().spark_topk_select_mc(cu.P(score), nb_max, cu.P(pos32), R, block, topk, cu.P(sel), sel_ld, cu.P(sel_n),
+                                         cu.stream(), window, ctas, cu.P(work))
+        cu.check(rc, "spark_topk_select_mc")
+        return sel, sel_n
     rc = _dll().spark_topk_select(cu.P(score), nb_max, cu.P(pos32), R, block, topk, cu.P(sel), sel_ld, cu.P(sel_n),
                                   cu.stream(), window)
     cu.check(rc, "spark_topk_select")

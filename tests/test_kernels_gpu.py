@@ -329,3 +329,84 @@ def test_embedding_rejects_out_of_range_ids():
     st = cu().read_status(torch.device(DEV))
     assert st[0] == 8 and st[1] in (1, 3)
     cu().reset_status(torch.device(DEV))
+
+
+def test_mla_fp8_latent_rows_kernels_equal_generic_path():
+    """FP8 latent cache rows (e4m3 codes + tile scales + bf16 rope): the prep kernel writes the same packed bytes as the
+    torch packer, and decode over packed rows matches the masked-softmax path on the dequantised cache."""
+    import dataclasses
+    from spark_engine_b200.config import get_model_config, scaled_down
+    from spark_engine_b200.models.model import Model, pack_latent_fp8, unpack_latent_fp8
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.models.weights import init_weights, to_device
+    from spark_engine_b200.ops import cuda as cuo
+    x = torch.randn(5, 256 + 64, device=DEV) * 3
+    back = unpack_latent_fp8(pack_latent_fp8(x, 256), 256)
+    assert rel_err(back[:, :256], x[:, :256]) < 4e-2 and rel_err(back[:, 256:], x[:, 256:]) < 4e-3
+    cfg = scaled_down(get_model_config("glm-style"))
+    cfg.mtp_layers = 0
+    cfg.kv_dtype = "fp8"
+    cfg.mla = dataclasses.replace(cfg.mla, kv_lora=256, rope_dim=32)
+    W = to_device(init_weights(cfg, seed=0), DEV)
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab, (150,), generator=g).tolist()
+    outs, lats = [], []
+    for kernels in (True, False):
+        m = Model(cfg, W, device=DEV, dtype=torch.bfloat16, n_slots=1, kv_tokens=512)
+        old = cuo.MLA_KERNELS
+        cuo.MLA_KERNELS = kernels
+        try:
+            lg = [m.forward(make_plan([(0, prompt[:140], 0)], device=DEV, all_logits=False), commit=True).float()]
+            lg.append(m.forward(make_plan([(0, prompt[140:144], 140)], device=DEV), commit=True).float())     # verify-style rows
+            lg.append(m.forward(make_plan([(0, prompt[144:145], 144)], device=DEV), commit=True).float())
+        finally:
+            cuo.MLA_KERNELS = old
+        outs.append(torch.cat(lg))
+        mla = [mix for _, mix, _ in m.layers if hasattr(mix, "lat")]
+        assert mla and mla[0].lat.dtype == torch.uint8 and mla[0].fp8
+        lats.append(mla[0].lat[:145].clone())
+    # the first latent layer sees identical inputs on both paths: packed bytes agree except for rounding ties
+    same = (lats[0] == lats[1]).float().mean().item()
+    assert same > 0.9, same
+    assert rel_err(outs[0], outs[1]) < 4e-2
+
+
+def _topk_reference(score, p, block, k, window):
+    vis = (p + 1) // block
+    if vis <= k:
+        return list(range(p + 1))
+    order = torch.sort(score[:vis].cpu(), descending=True, stable=True).indices[:k]
+    taken = sorted(order.tolist())
+    tail0 = vis * block
+    lo = min(max(0, p + 1 - window), tail0) if window > 0 else tail0
+    out = []
+    for b in taken:
+        out += [t for t in range(b * block, (b + 1) * block) if t < lo]
+    return out + list(range(lo, p + 1))
+
+
+@pytest.mark.parametrize("window", [0, 130])
+def test_topk_select_multi_cta_equals_single_cta_and_reference(window):
+    """Exact top-k over 70K candidates per row: one CTA per row, 18 CTAs per row (three digit passes over global
+    histograms, per-slice counts, ordered emission) and a stable sort agree element for element, ties included."""
+    from spark_engine_b200.ops import sparse as sp
+    g = torch.Generator(device=DEV).manual_seed(21)
+    block, k, nb = 4, 512, 70000
+    pos = torch.tensor([nb * block - 1, 250001, 1999, 279998], dtype=torch.int32, device=DEV)
+    R = pos.shape[0]
+    score = torch.randn(R, nb, device=DEV, generator=g)
+    score[0] = torch.randint(0, 40, (nb,), device=DEV, generator=g).float() / 8          # heavy ties, also at the threshold
+    score[3] = torch.relu(score[3])                                                       # half the keys are +0
+    score[3, ::3] = -0.0
+    one, one_n = sp.topk_select(score, nb, pos, block, k, window, ctas=1)
+    many, many_n = sp.topk_select(score, nb, pos, block, k, window, ctas=18)
+    auto, auto_n = sp.topk_select(score, nb, pos, block, k, window)
+    torch.cuda.synchronize()
+    assert torch.equal(one_n, many_n) and torch.equal(one_n, auto_n)
+    for r in range(R):
+        n = int(one_n[r])
+        ref = _topk_reference(score[r], int(pos[r]), block, k, window)
+        assert n == len(ref), (r, n, len(ref))
+        assert one[r, :n].tolist() == ref, r
+        assert many[r, :n].tolist() == ref, r
+        assert auto[r, :n].tolist() == ref, r

@@ -136,13 +136,15 @@ def test_other_families_on_device_match_cpu_runner(preset):
     """KDA + MLA/DSA + mHC (GLM-style) and compressed sparse MLA + n-gram tables (DS-style), scaled down: device prefill
     and decode rows against the CPU fp32 runner on the same (bf16-rounded) weights."""
     from spark_engine_b200.config import get_model_config, scaled_down
+    import dataclasses
     cfg = scaled_down(get_model_config(preset))
     cfg.mtp_layers = 0
     W = init_weights(cfg, seed=2)
     Wr = map_weights(W, lambda t: t.bfloat16().float() if t.dim() >= 2 else t)
     g = torch.Generator().manual_seed(4)
     ids = torch.randint(0, cfg.vocab, (48,), generator=g).tolist()
-    ref = Model(cfg, Wr, n_slots=1, kv_tokens=128).forward(make_plan([(0, ids, 0)]))
+    # the DS-style preset keeps packed FP8 latent rows: the CPU runner models the same rows
+    ref = Model(dataclasses.replace(cfg, kv_quant_on_cpu=True), Wr, n_slots=1, kv_tokens=128).forward(make_plan([(0, ids, 0)]))
     m = Model(cfg, to_device(W, "cuda"), device="cuda", dtype=torch.bfloat16, n_slots=1, kv_tokens=128)
     lg = m.forward(make_plan([(0, ids[:40], 0)], device="cuda")).float().cpu()
     rows = [m.forward(make_plan([(0, [ids[t]], t)], device="cuda")).float().cpu()[0] for t in range(40, 48)]

@@ -90,3 +90,19 @@ def test_other_codings_run_on_device(kind):
     y = ops.linear(x, cw).float().cpu()
     ref = x.float().cpu() @ cw.dequant().bfloat16().float().t()
     assert ((y - ref).norm() / ref.norm()) < 1e-2
+
+
+def test_latent_fp8_rows_round_trip():
+    """Packed FP8 latent cache rows: e4m3 codes with a scale per tile of 128, four scale slots, rope dims in bf16."""
+    import torch
+    from spark_engine_b200.models.model import pack_latent_fp8, unpack_latent_fp8
+    g = torch.Generator().manual_seed(0)
+    for L, r in ((512, 64), (256, 32), (32, 16)):
+        x = torch.randn(7, L + r, generator=g) * 3
+        x[3, :L] = 0                                            # an all-zero tile keeps scale 1
+        p = pack_latent_fp8(x, L)
+        assert p.dtype == torch.uint8 and p.shape == (7, L + 16 + 2 * r)
+        b = unpack_latent_fp8(p, L)
+        assert ((b - x).norm() / x.norm()).item() < 3e-2
+        assert torch.equal(b[3, :L], torch.zeros(L))
+        assert (b[:, L:] - x[:, L:]).abs().max().item() < 2e-2 * x.abs().max().item()

@@ -113,3 +113,39 @@ def test_tree_rounds_on_the_device_equal_greedy(family):
         assert len(out) >= 1
     assert seq.generated[:18] == ref
     assert seq.accepted > 0
+
+
+def test_latent_attention_tree_rows_kernel_equals_generic_path():
+    """Tree rows of latent attention through the kernels (node slots, ancestor bit-masks) against the per-segment
+    masked-softmax path, and the indexer pools that the accepted path completes at compaction."""
+    from spark_engine_b200.config import get_model_config, scaled_down
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.ops import cuda as cu
+    cfg = scaled_down(get_model_config("glm-style"))
+    cfg.mtp_layers = 0
+    W = to_device(init_weights(cfg, seed=0), "cuda")
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, cfg.vocab, (2, 70), generator=g).tolist()       # trees start at 70: the kernel's second split
+    toks = torch.randint(0, cfg.vocab, (2, 9), generator=g).tolist()
+    parents = [[-1, 0, 0, 1, 1, 2, 3, 3, 6], [-1, 0, 1, 2, 0, 4, 4, 5, 7]]
+    outs, pools = [], []
+    for kernels in (True, False):
+        m = Model(cfg, W, device="cuda", dtype=torch.bfloat16, n_slots=2, kv_tokens=512)
+        m.forward(make_plan([(0, prompt[0], 0), (1, prompt[1], 0)], device="cuda", all_logits=False), commit=True)
+        old = cu.MLA_KERNELS
+        cu.MLA_KERNELS = kernels
+        try:
+            plan = make_plan([(0, toks[0], 70), (1, toks[1], 70)], device="cuda", parents=parents)
+            outs.append(m.forward(plan, commit=False).float())
+            mla = [mix for _, mix, _ in m.layers if hasattr(mix, "lat")]
+            assert mla
+            for seg, rows in zip(plan.segs, ([0, 1, 3, 6, 8], [0, 4, 5, 7])):
+                for mx in mla:
+                    mx.compact(m.seqs, seg, rows)
+            pools.append(torch.stack([mx.pool.float().clone() for mx in mla]))
+        finally:
+            cu.MLA_KERNELS = old
+    assert torch.isfinite(outs[0]).all()
+    err = (outs[0] - outs[1]).abs().max().item() / outs[1].abs().max().item()
+    assert err < 3e-2, err
+    assert (pools[0] - pools[1]).abs().max().item() < 3e-2 * pools[1].abs().max().item()
