@@ -71,6 +71,20 @@ def build_runtime(force=False) -> str:
     return out
 
 
+def build_race_stress(sanitizer: str = "thread", force=False) -> str:
+    """The host runtime's concurrency stress driver (csrc/runtime/stress/race_stress.cpp) linked against the runtime
+    sources with -fsanitize=<sanitizer> ("thread", or "address,undefined"); returns the executable's path.  It needs
+    no GPU: device memory is the fake driver's host memory."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    out = os.path.join(LIBDIR, "race_stress_" + sanitizer.replace(",", "_"))
+    rt = os.path.join(CSRC, "runtime")
+    srcs = [os.path.join(rt, "stress", "race_stress.cpp")] + [os.path.join(rt, f) for f in
+                                                              ("pcache.cpp", "oplog.cpp", "memguard.cpp", "devmem.cpp")]
+    if force or _newer(srcs + glob.glob(os.path.join(rt, "*.h")), out):
+        _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", "-fsanitize=" + sanitizer] + srcs + ["-o", out, "-lrt", "-ldl"])
+    return out
+
+
 def build_all(force=False, verbose=False):
     return build_kernels(force, verbose), build_runtime(force)
 

@@ -114,6 +114,8 @@ def reset_launch_count():
     _launches = 0
 
 
+from ..utils import debug as dbg
+
 def lib():
     global _LIB
     if _LIB is None:
@@ -183,6 +185,8 @@ def scratch(name: str, numel: int, dtype, device, zero: bool = False) -> torch.T
             _retired.append(t)      # captured graphs may still point at the old buffer: keep it alive
         t = (torch.zeros if zero else torch.empty)(max(numel, 1), dtype=dtype, device=device)
         _scratch[key] = t
+    if dbg.POISON and not zero:
+        dbg.poison(t[:max(numel, 1)])
     return t
 
 
@@ -241,6 +245,9 @@ def gemv_bf16(x, w, items=1, rows_per_item=None, pair_expert=None, pair_row=None
     else:
         y, ldy = out, out.stride(0)
         out_f32 = out.dtype == torch.float32
+    if dbg.CHECK:
+        dbg.check_index("gemv_bf16 pair_expert", pair_expert, 0, w.shape[0] if w.dim() == 3 else 1, allow=-1, count=items)
+        dbg.check_index("gemv_bf16 pair_row", pair_row, 0, x.shape[0], count=items)
     rc = lib().spark_gemv_bf16(P(x), ldx if ldx is not None else x.stride(0), P(w), expert_stride, w.stride(-2), P(y), ldy,
                                items, rows_per_item, n, k, P(pair_expert), P(pair_row), act, float(limit), int(out_f32),
                                stream())
@@ -252,6 +259,8 @@ def gemv_bf16_items(x, ldx, x_item_stride, w, expert_stride, ldw, y, ldy, y_item
                     pair_expert):
     """Per-item GEMV over strided slices: item i multiplies rows x[i * x_item_stride + r * ldx] (r < rows_per_item) by
     matrix pair_expert[i] of `w` and writes y[i * y_item_stride + r * ldy].  Strides in elements."""
+    if dbg.CHECK:
+        dbg.check_index("gemv_bf16_items pair_expert", pair_expert, 0, w.shape[0], count=items)
     rc = lib().spark_gemv_bf16_items(P(x), ldx, x_item_stride, P(w), expert_stride, ldw, P(y), ldy, y_item_stride, items,
                                      rows_per_item, n, k, P(pair_expert), int(y.dtype == torch.float32), stream())
     check(rc, "spark_gemv_bf16_items")
@@ -293,6 +302,9 @@ def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, p
     assert w.bits == 4, "the GEMV kernel handles 4 bpw"
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     K, N = w.k, w.n
+    if dbg.CHECK:
+        dbg.check_index("exl3_gemv pair_expert", pair_expert, 0, max(w.experts, 1), allow=-1, count=items)
+        dbg.check_index("exl3_gemv pair_row", pair_row, 0, x.shape[0], count=items)
     S = _pick_slices(K, items)
     dev = x.device
     y = torch.empty(items * rows_per_item, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
@@ -408,6 +420,7 @@ def rmsnorm(x, w, eps, one_plus=False):
 
 def embed(table, ids32):
     R, H = ids32.shape[0], table.shape[1]
+    dbg.check_index("embed token ids", ids32, 0, table.shape[0])
     out = torch.empty(R, H, dtype=torch.float32, device=table.device)
     lib().spark_embed(P(table), P(ids32), P(out), R, H, stream(), table.shape[0], P(status_word(table.device)))
     return out
@@ -572,6 +585,7 @@ def draft_path(unary, ids, eu, ev):
 
 def gather_rows(src, idx32):
     R, H = idx32.shape[0], src.shape[1]
+    dbg.check_index("gather_rows indices", idx32, 0, src.shape[0])
     out = torch.empty(R, H, dtype=torch.bfloat16, device=src.device)
     lib().spark_gather_rows_bf16(P(src), P(idx32), P(out), R, H, stream())
     return out
@@ -611,6 +625,7 @@ def _expert_gemv(x, w, pairs, pair_expert, pair_row, act, limit, out_f32, pairs_
 def moe_sort(ids, E):
     Pn = ids.numel()
     dev = ids.device
+    dbg.check_index("moe_sort expert ids", ids, 0, E, allow=-1)
     perm = torch.zeros(Pn, dtype=torch.int32, device=dev)      # entries past the local pairs stay valid indices
     inv = torch.empty(Pn, dtype=torch.int32, device=dev)
     offs = torch.empty(E + 1, dtype=torch.int32, device=dev)
@@ -792,6 +807,18 @@ def _plan_dev(plan, device):
     return plan.dev
 
 
+def _check_cache_rows(what, d, tree, cache_rows):
+    """SPARK_CHECK: every row's cache slot (sequence base + position, or + node slot for tree rows) is inside the cache."""
+    slot = d["row_kv"] + ((d["row_pos0"] + d["row_j"]) if tree else d["pos32"]).long()
+    dbg.check_index(what + " cache slot", slot, 0, cache_rows)
+
+
+def _check_slots(what, plan, n_slots):
+    bad = [s.slot for s in plan.segs if not 0 <= s.slot < n_slots]
+    if bad:
+        raise dbg.IndexTableError(f"{what}: sequence slots {bad} outside [0, {n_slots})")
+
+
 GDN_CHUNKED = os.environ.get("SPARK_GDN_CHUNKED", "1") == "1"
 GDN_CHUNK_MIN_ROWS = 64
 _KERNELS_PER_CALL["spark_gdn_chunk_prefill"] = 3
@@ -863,11 +890,14 @@ def gdn_mixer(mixer, proj, ab, plan, commit, n_rows=None, accepted=None):
     R = proj.shape[0]
     out = torch.empty(R, c.n_v_heads * c.head_dim, dtype=torch.bfloat16, device=proj.device)
     w = mixer.w
+    if dbg.CHECK:
+        _check_slots("gdn_mixer", plan, mixer.S.shape[0])
     if plan.is_tree:
         # every node forks its parent's state: one walk from the committed state per node (verify), or the accepted
         # walk per sequence (commit); a tree round never commits directly
         assert not commit or accepted is not None
         seg, lens, tab, nw, ld = _tree_walks(plan, proj.device, accepted)
+        dbg.check_index("gdn_mixer walk table", tab, 0, R, allow=-1)
         rc = lib().spark_gdn_seq(P(proj), proj.stride(0), P(ab), ab.stride(0), P(w["conv"]), P(w["A_log"]), P(w["dt_bias"]),
                                  P(w["norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), out.stride(0),
                                  c.n_k_heads, c.n_v_heads, c.head_dim, float(mixer.cfg.norm_eps), int(commit), stream(),
@@ -919,9 +949,12 @@ def kda_mixer(mixer, pre, lr, plan, commit, n_rows=None, accepted=None):
         g2 = dense_linear(lr[:, r: 2 * r].contiguous(), mixer._gate_w[1], out_f32=True)
     R = pre.shape[0]
     out = torch.empty(R, n, dtype=torch.bfloat16, device=dev)
+    if dbg.CHECK:
+        _check_slots("kda_mixer", plan, mixer.S.shape[0])
     if plan.is_tree:
         assert not commit or accepted is not None
         seg, lens, tab, nw, ld = _tree_walks(plan, dev, accepted)
+        dbg.check_index("kda_mixer walk table", tab, 0, R, allow=-1)
         rc = lib().spark_kda_seq(P(pre), pre.stride(0), P(g1), P(g2), n, P(lr), lr.stride(0), 2 * r, P(w["conv"]), P(w["A_log"]),
                                  P(w["dt_bias"]), P(w["o_norm"]), P(mixer.S), P(mixer.tail), P(seg), P(lens), nw, P(out), n,
                                  c.n_heads, c.head_dim, int(commit), stream(), P(tab), ld, int(ld > 1))
@@ -1011,6 +1044,8 @@ def mla_mixer(mixer, h, plan, seqs):
                       "w_uv": mixer.w_uv.contiguous().to(torch.bfloat16),
                       "ape": w["ape"].float().contiguous()}
     md = mixer._dev
+    if dbg.CHECK:
+        _check_cache_rows("mla_mixer", d, tree, mixer.lat.shape[0])
     a = _as_bf16(linear_any(h, w["a"])).contiguous()
     cq = torch.empty(R, c.q_lora, dtype=torch.bfloat16, device=dev)
     hw = torch.empty(R, c.idx_heads, dtype=torch.float32, device=dev)
@@ -1107,6 +1142,8 @@ def attn_mixer(mixer, qkv, plan, seqs):
         if "anc" not in d:
             d["anc"] = tree_ancestor_masks(plan, dev)
     w = mixer.w
+    if dbg.CHECK:
+        _check_cache_rows("attn_mixer", d, tree, mixer.k.shape[0])
     qbuf = torch.empty(R, c.n_q_heads, c.head_dim, dtype=torch.bfloat16, device=dev)
     qi = torch.empty(R, c.idx_heads, c.idx_dim, dtype=torch.float32, device=dev) if sparse else None
     rc = lib().spark_attn_prep(P(qkv), qkv.stride(0), R, c.n_q_heads, c.n_kv_heads, c.head_dim, c.rope_dim, int(c.gated),

@@ -289,3 +289,50 @@ def test_gumbel_perturb_kernel_matches_the_host_oracle():
     assert torch.equal(got[1], lg[1]) and torch.equal(got[3], lg[3])
     assert (got - want).abs().max().item() < 1e-4
     assert ops.argmax(got).tolist() == want.argmax(-1).tolist()
+
+
+def test_checked_mode_rejects_bad_tables_before_launch(monkeypatch):
+    """SPARK_CHECK: an expert id or a token id outside its table raises in Python and nothing is launched (the device
+    status word stays clear and the context stays usable); valid tables pass; poisoned scratch does not leak into
+    results."""
+    from spark_engine_b200.utils import debug as dbg
+    monkeypatch.setattr(dbg, "CHECK", True)
+    monkeypatch.setattr(dbg, "POISON", True)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    E, N, K = 4, 64, 128
+    # views of larger allocations: should a check ever miss, the launch would still read memory that exists
+    w = (torch.randn(E + 2, N, K, device=DEV, generator=g) * 0.05).bfloat16()[:E]
+    x = torch.randn(4, K, device=DEV, generator=g).bfloat16()[:2]
+    rows = torch.tensor([0, 1, 1], dtype=torch.int32, device=DEV)
+    good = torch.tensor([3, 0, -1], dtype=torch.int32, device=DEV)
+    y = cu().gemv_bf16(x, w, items=3, rows_per_item=1, pair_expert=good, pair_row=rows, out_f32=True, expert_stride=N * K, n=N, k=K)
+    assert rel_err(y[0], x[0].float() @ w[3].float().t()) < 1e-4
+    bad = torch.tensor([3, 4, 0], dtype=torch.int32, device=DEV)
+    with pytest.raises(dbg.IndexTableError):
+        cu().gemv_bf16(x, w, items=3, rows_per_item=1, pair_expert=bad, pair_row=rows, out_f32=True, expert_stride=N * K, n=N, k=K)
+    with pytest.raises(dbg.IndexTableError):
+        cu().gemv_bf16(x, w, items=3, rows_per_item=1, pair_expert=good, pair_row=rows + 1, out_f32=True, expert_stride=N * K, n=N, k=K)
+    table = torch.randn(52, 64, device=DEV).bfloat16()[:50]
+    with pytest.raises(dbg.IndexTableError):
+        cu().embed(table, torch.tensor([1, 50], dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    assert cu().read_status(torch.device(DEV))[0] == 0
+    # a whole model step under both modes: finite logits, same tokens as the plain run
+    from spark_engine_b200.config import tiny_hybrid
+    from spark_engine_b200.models.model import Model
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.models.weights import init_weights, to_device
+    cfg = tiny_hybrid()
+    W = to_device(init_weights(cfg, seed=0), DEV)
+    ids = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    outs = []
+    for on in (True, False):
+        monkeypatch.setattr(dbg, "CHECK", on)
+        monkeypatch.setattr(dbg, "POISON", on)
+        m = Model(cfg, W, device=DEV, dtype=torch.bfloat16, n_slots=1, kv_tokens=256)
+        a = m.forward(make_plan([(0, ids[:36], 0)], device=DEV, all_logits=False), commit=True)
+        b = m.forward(make_plan([(0, ids[36:40], 36)], device=DEV), commit=True)
+        outs.append(torch.cat((a, b)).float())
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])
+    assert dbg.stats["checked"] > 0 and dbg.stats["poisoned"] > 0

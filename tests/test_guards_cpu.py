@@ -80,3 +80,25 @@ def test_online_calibration_reaches_the_cells_the_rate_policy_reads():
         dec.round([s])
     after = [s.table.prob(j, conf) for j in range(3)]
     assert all(a < b for a, b in zip(after, before)), (before, after)
+
+
+def test_index_table_check_and_poison_fill(monkeypatch):
+    """Debug modes: a table with an out-of-range entry raises before anything would be launched; poison fills floats with
+    NaN and integers with 0x7f bytes.  Both are no-ops unless switched on."""
+    import pytest
+    import torch
+    from spark_engine_b200.utils import debug as dbg
+    t = torch.tensor([0, 3, -1, 7], dtype=torch.int32)
+    dbg.check_index("off", t, 0, 4)                                   # switched off: nothing happens
+    monkeypatch.setattr(dbg, "CHECK", True)
+    dbg.check_index("pairs", t, 0, 8, allow=-1)
+    dbg.check_index("pairs", t, 0, 4, allow=-1, count=2)              # only the first two entries count
+    with pytest.raises(dbg.IndexTableError, match=r"\[-1, 7\]"):
+        dbg.check_index("pairs", t, 0, 8)
+    with pytest.raises(dbg.IndexTableError, match="valid range"):
+        dbg.check_index("pairs", t, 0, 7, allow=-1)
+    x, i = torch.zeros(4), torch.zeros(4, dtype=torch.int32)
+    assert dbg.poison(x).eq(0).all()                                  # switched off
+    monkeypatch.setattr(dbg, "POISON", True)
+    assert torch.isnan(dbg.poison(x)).all()
+    assert dbg.poison(i).eq(0x7F7F7F7F).all()

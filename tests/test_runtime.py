@@ -1,5 +1,6 @@
 """C++ host runtime on CPU: KV pool, NVMe prefix cache (crash safety, checksums, LRU budget, reconciliation),
 scheduler admission / round planning, replicated op log with a lost leader, safetensors, memory guard."""
+import pytest
 import os
 import threading
 import time
@@ -178,3 +179,20 @@ def test_safetensors_roundtrip_and_memguard(tmp_path):
     del w
     assert fired and fired[0] == 2048 * 1024
     assert R.sha256_hex(b"abc") == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+
+
+@pytest.mark.parametrize("sanitizer", ["thread", "address,undefined"])
+def test_runtime_concurrency_under_sanitizers(sanitizer, tmp_path):
+    """The threaded parts of the host runtime (prefix-cache writer and evictor, op-log ring with two followers, memory
+    watch thread, multi-threaded staged file load) run their stress driver under ThreadSanitizer and under
+    Address/UB sanitizers: exit code 0 and no report."""
+    import os
+    import subprocess
+    from spark_engine_b200 import build
+    exe = build.build_race_stress(sanitizer)
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66", ASAN_OPTIONS="detect_leaks=1 exitcode=67",
+               UBSAN_OPTIONS="halt_on_error=1 print_stacktrace=1")
+    r = subprocess.run([exe, str(tmp_path)], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "race_stress ok" in r.stdout
+    assert "Sanitizer" not in r.stderr, r.stderr[-3000:]
