@@ -303,7 +303,7 @@ def exl3_gemv(x, w: Exl3Weight, items=1, rows_per_item=None, pair_expert=None, p
     rows_per_item = rows_per_item if rows_per_item is not None else x.shape[0]
     K, N = w.k, w.n
     if dbg.CHECK:
-        dbg.check_index("exl3_gemv pair_expert", pair_expert, 0, max(w.experts, 1), allow=-1, count=items)
+        dbg.check_index("exl3_gemv pair_expert", pair_expert, 0, w.trellis.shape[0] if w.experts else 1, allow=-1, count=items)
         dbg.check_index("exl3_gemv pair_row", pair_row, 0, x.shape[0], count=items)
     S = _pick_slices(K, items)
     dev = x.device
