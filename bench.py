@@ -155,6 +155,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--chunk", type=int, default=0, help="prefill chunk in tokens (default 8192 on one GPU, 4096 under tp)")
     ap.add_argument("--hc", default=None, help="gated | mhc: run the model with 4 hyper-connection residual streams")
+    ap.add_argument("--ple", action="store_true",
+                    help="add hashed n-gram embedding layers (bi/tri-gram ids, 16 heads, a 4M-row table) to the model")
     ap.add_argument("--spec", default="none", help="mtp: also time speculative rounds (MTP chain of 3 drafts, 4 rows per "
                                                    "sequence verified) through the captured draft / verify / commit graphs")
     ap.add_argument("--sweep", action="store_true", help="also time 1,2,3 streams")
@@ -191,6 +193,8 @@ def main():
         cfg.kv_dtype = args.kv
     if args.hc:
         cfg.hc_kind, cfg.hc_streams, cfg.hc_rank = args.hc, 4, 32
+    if args.ple and not cfg.ngram_layers:
+        cfg.ngram_layers, cfg.ngram_rows, cfg.ngram_dim = [1, cfg.n_layers // 2], 1 << 22, 1024
     aten = args.impl == "aten"
     if aten and cfg.weight_format != "dense":
         # the ATen path has no kernels for the packed formats: it would dequantise every matrix on the host per call
@@ -292,7 +296,7 @@ def main():
     replicas = 1 if use_tp else world
     value = replicas * S * 1e3 / dev_ms
     e2e = replicas * S * 1e3 / e2e_ms
-    full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS and not args.hc
+    full = (args.layers == 0 and args.model in BASELINE_DECODE_4STREAMS and not args.hc and not args.ple
             and cfg.weight_format == DEFAULT_FORMAT[args.model])
     # what a step streams: the weights a round of S rows touches on this rank (not the whole model)
     step_bytes = decode_step_bytes(W, cfg, S)
@@ -316,6 +320,7 @@ def main():
                    "top_k": cfg.moe.top_k, "vocab": cfg.vocab, "weights": cfg.weight_format + ("-4bpw" if cfg.weight_format == "exl3" else ""),
                    "kv": kv_label, "global_batch": replicas * S, "seq_len": args.prompt, "streams_per_gpu": S,
                    "parallelism": (f"tp{world}+ep{world}" if use_tp else f"dp{world}") if world > 1 else "single", "speculation": "none (greedy)", "hyper_connections": cfg.hc_kind,
+                   "ngram_layers": list(cfg.ngram_layers),
                    "cache": "inputs larger than L2: a step streams %.2f GB of weights per GPU (of %.1f GB resident)"
                             % (step_bytes / 1e9, weight_bytes(W) / 1e9),
                    "full_config": full},

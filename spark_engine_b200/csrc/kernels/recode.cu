@@ -1,11 +1,14 @@
-// GEMV over the load-time re-codings of dense weights (<= 16 rows): Q8 (int8 + fp32 scale per row and 128 k) and
-// Q4 (4-bit codes + fp32 (scale, minimum) per row and 64 k, w = code * scale + minimum).
+// GEMV over the load-time re-codings of dense weights (<= 16 rows): Q8 (int8 + fp32 scale per row and 128 k),
+// Q4 (4-bit codes + fp32 (scale, minimum) per row and 64 k, w = code * scale + minimum) and FP8 per row (e4m3 codes
+// + one fp32 scale per row; the codes convert to fp16 exactly and share the Q8 data path, the scale is applied to
+// each group's partial dot product).
 // Same scheme as the micro-scaled GEMV: 16-byte (Q8) or 8-byte (Q4) pieces of a weight row go straight into
 // `mma.sync.m16n8k16` B fragments as exact fp16 integers, one warp iteration covers exactly one scale group, the
 // group's integer dot products are scaled in fp32 (Q4 adds minimum * sum of the activations of the group), the 8 warps
 // of a CTA split K in a fixed pattern and are summed in warp order.  Run-to-run bitwise equal, rows independent.
 // Reference: engine-rs/shim/q8.cuh, q4d.cuh, qwen_q8.cu (int8 / int4 skinny GEMMs).
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "../common/ptx.cuh"
 
@@ -18,6 +21,10 @@ __device__ __forceinline__ uint32_t rc_s8x2_to_h2(uint32_t v16) {      // two in
   const uint32_t u = (v16 & 0xFFFFu) ^ 0x8080u;
   const uint32_t packed = __byte_perm(u, 0x64646464u, 0x7170);          // bytes {b0, 0x64, b1, 0x64}
   const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&packed), __float2half2_rn(1152.f));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t rc_e4m3x2_to_h2(uint32_t v16) {    // two e4m3 codes -> half2, exact
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v16 & 0xFFFFu), __NV_E4M3);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 __device__ __forceinline__ uint32_t rc_u4x2_to_h2(uint32_t v8) {       // two 4-bit codes (low nibble first) -> half2
@@ -33,7 +40,8 @@ __device__ __forceinline__ void rc_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
 
 // Q4 = false: W int8 [N,K], sc fp32 [N, K/128].  Q4 = true: W nibbles [N, K/2], sc fp32 [N, K/64, 2].
 // One warp iteration = 64 k (Q8: 4 lanes x 16 bytes; Q4: 4 lanes x 8 bytes).
-template <bool Q4, int RB, typename TO>
+// F8 (with Q4 = false): W e4m3 [N,K], sc fp32 [N].
+template <bool Q4, int RB, typename TO, bool F8 = false>
 __global__ void __launch_bounds__(RCV_WARPS * 32)
 coded_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* __restrict__ W, const float* __restrict__ sc,
                   TO* __restrict__ y, int ldy, int R, int N, int K) {
@@ -106,6 +114,9 @@ coded_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* _
           const uint32_t vl = pl[s >> 1] >> ((s & 1) * 16), vh = ph[s >> 1] >> ((s & 1) * 16);
           b0l = rc_u4x2_to_h2(vl & 0xFFu); b1l = rc_u4x2_to_h2((vl >> 8) & 0xFFu);
           b0h = rc_u4x2_to_h2(vh & 0xFFu); b1h = rc_u4x2_to_h2((vh >> 8) & 0xFFu);
+        } else if (F8) {
+          b0l = rc_e4m3x2_to_h2(pl[s]); b1l = rc_e4m3x2_to_h2(pl[s] >> 16);
+          b0h = rc_e4m3x2_to_h2(ph[s]); b1h = rc_e4m3x2_to_h2(ph[s] >> 16);
         } else {
           b0l = rc_s8x2_to_h2(pl[s]); b1l = rc_s8x2_to_h2(pl[s] >> 16);
           b0h = rc_s8x2_to_h2(ph[s]); b1h = rc_s8x2_to_h2(ph[s] >> 16);
@@ -124,7 +135,7 @@ coded_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* _
         acc[1][0] += s10.x * c[1][0] + s10.y * xa_s; acc[1][1] += s11.x * c[1][1] + s11.y * xa_s;
         acc[1][2] += s10.x * c[1][2] + s10.y * xb_s; acc[1][3] += s11.x * c[1][3] + s11.y * xb_s;
       } else {
-        const int gq = it >> 1, G128 = K >> 7;
+        const int gq = F8 ? 0 : it >> 1, G128 = F8 ? 1 : K >> 7;
         const float s00 = __ldg(sc + static_cast<size_t>(c00) * G128 + gq), s01 = __ldg(sc + static_cast<size_t>(c01) * G128 + gq);
         const float s10 = __ldg(sc + static_cast<size_t>(c10) * G128 + gq), s11 = __ldg(sc + static_cast<size_t>(c11) * G128 + gq);
         acc[0][0] = fmaf(s00, c[0][0], acc[0][0]); acc[0][1] = fmaf(s01, c[0][1], acc[0][1]);
@@ -152,10 +163,10 @@ coded_gemv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const uint8_t* _
   }
 }
 
-template <bool Q4, int RB, typename TO>
+template <bool Q4, int RB, typename TO, bool F8 = false>
 static int launch_coded(const void* x, int ldx, const void* W, const float* sc, void* y, int ldy, int R, int N, int K,
                         cudaStream_t s) {
-  auto kern = coded_gemv_kernel<Q4, RB, TO>;
+  auto kern = coded_gemv_kernel<Q4, RB, TO, F8>;
   const int smem = RB * (K + 8) * 2 + RCV_WARPS * 256 * 4 + (Q4 ? RB * (K / 64) * 4 : 0);
   if (smem > 200 * 1024) return -6;
   static bool done = false;
@@ -168,15 +179,21 @@ static int launch_coded(const void* x, int ldx, const void* W, const float* sc, 
 
 using namespace spark;
 
-// fmt 2 = Q8, 3 = Q4.  R <= 16 rows of bf16 activations; K % 128 == 0, N % 16 == 0.
+// fmt 2 = Q8, 3 = Q4, 4 = FP8 per row.  R <= 16 rows of bf16 activations; K % 128 == 0, N % 16 == 0.
 extern "C" int spark_coded_gemv(const void* x, int ldx, const void* W, const float* scales, int fmt, void* y, int ldy, int R,
                                 int N, int K, int out_f32, cudaStream_t s) {
   if (R <= 0) return 0;
-  if (R > 16 || N % 16 || K % 128 || (fmt != 2 && fmt != 3)) return -5;
+  if (R > 16 || N % 16 || K % 128 || (fmt != 2 && fmt != 3 && fmt != 4)) return -5;
 #define SPARK_RC(Q, RB)                                                                              \
   (out_f32 ? launch_coded<Q, RB, float>(x, ldx, W, scales, y, ldy, R, N, K, s)                      \
            : launch_coded<Q, RB, __nv_bfloat16>(x, ldx, W, scales, y, ldy, R, N, K, s))
   if (fmt == 2) return R <= 4 ? SPARK_RC(false, 4) : SPARK_RC(false, 16);
+  if (fmt == 4) {
+    if (R <= 4) return out_f32 ? launch_coded<false, 4, float, true>(x, ldx, W, scales, y, ldy, R, N, K, s)
+                               : launch_coded<false, 4, __nv_bfloat16, true>(x, ldx, W, scales, y, ldy, R, N, K, s);
+    return out_f32 ? launch_coded<false, 16, float, true>(x, ldx, W, scales, y, ldy, R, N, K, s)
+                   : launch_coded<false, 16, __nv_bfloat16, true>(x, ldx, W, scales, y, ldy, R, N, K, s);
+  }
   return R <= 4 ? SPARK_RC(true, 4) : SPARK_RC(true, 16);
 #undef SPARK_RC
 }

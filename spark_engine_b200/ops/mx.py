@@ -15,7 +15,7 @@ import os
 import torch
 
 from ..quant.formats import Fp8BlockWeight, Mxfp4Weight, Mxfp8Weight, QuantWeight
-from ..quant.recode import Q4Weight, Q8Weight
+from ..quant.recode import Fp8RowWeight, Q4Weight, Q8Weight
 from . import cuda as cu
 
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
@@ -104,13 +104,13 @@ def act_quant(x, block=128, pow2=False, act=0, limit=0.0):
 
 
 def coded_gemv(x, w, out_f32=False):
-    """<= 16 rows through the int8 / int4 re-coded copy of a dense weight."""
+    """<= 16 rows through the int8 / int4 / FP8-per-row re-coded copy of a dense weight."""
     x = cu._as_bf16(x).contiguous()
-    q4 = isinstance(w, Q4Weight)
-    assert (w.group == 64) if q4 else (w.group == 128)
+    q4, f8 = isinstance(w, Q4Weight), isinstance(w, Fp8RowWeight)
+    assert f8 or ((w.group == 64) if q4 else (w.group == 128))
     y = torch.empty(x.shape[0], w.n, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
-    rc = _lib().spark_coded_gemv(cu.P(x), x.stride(0), cu.P(w.q), cu.P(w.sm if q4 else w.scales), 3 if q4 else 2, cu.P(y),
-                                 w.n, x.shape[0], w.n, w.k, int(out_f32), cu.stream())
+    rc = _lib().spark_coded_gemv(cu.P(x), x.stride(0), cu.P(w.q), cu.P(w.sm if q4 else w.scales), 4 if f8 else (3 if q4 else 2),
+                                 cu.P(y), w.n, x.shape[0], w.n, w.k, int(out_f32), cu.stream())
     cu.check(rc, "spark_coded_gemv")
     return y
 
@@ -191,7 +191,7 @@ def quant_linear(x, w: QuantWeight):
             return gemv(x, w)
         wt = dequant_bf16(w, cu.scratch("mx_deq", w.n * w.k, torch.bfloat16, x.device))
         return cu.gemm_bf16(x, wt)
-    if isinstance(w, (Q8Weight, Q4Weight)) and x.shape[0] <= 16 and w.n % 16 == 0:
+    if isinstance(w, (Q8Weight, Q4Weight, Fp8RowWeight)) and x.shape[0] <= 16 and w.n % 16 == 0 and w.k % 128 == 0:
         return coded_gemv(x, w)
     return cu.dense_linear(x, _resident_bf16(w, x.device))
 

@@ -63,7 +63,7 @@ def test_recode_dense_replaces_only_large_projections():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("kind", ["q8", "q4"])
+@pytest.mark.parametrize("kind", ["q8", "q4", "fp8"])
 @pytest.mark.parametrize("R", [1, 4, 11, 16])
 def test_coded_gemv_on_device(kind, R):
     from spark_engine_b200 import ops
