@@ -244,9 +244,12 @@ static int launch_gemv_wide(const void* x, int ldx, const void* W, int ldw, void
   return err == cudaSuccess ? 0 : -4;
 }
 
-// Shapes the wide kernel takes: one item, no activation, no expert tables, K a multiple of 32.
+// Shapes the wide kernel takes: one item, no activation, no expert tables, K a multiple of 32 and small enough that
+// 16 staged rows fit in shared memory (the choice must not depend on the number of rows: a row's result may not
+// change with the batch it is in).
 static bool gemv_wide_ok(int ldx, int ldw, int items, int N, int K, const int* pe, const int* pr, int act) {
-  return items == 1 && !pe && !pr && act == 0 && N >= 2048 && (K & 31) == 0 && (ldx & 7) == 0 && (ldw & 7) == 0;
+  return items == 1 && !pe && !pr && act == 0 && N >= 2048 && (K & 31) == 0 && (ldx & 7) == 0 && (ldw & 7) == 0 &&
+         16 * (K + GEMV_MMA_PAD) * 2 <= 200 * 1024;
 }
 
 }  // namespace spark
