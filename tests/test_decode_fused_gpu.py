@@ -38,6 +38,12 @@ def test_gemv_bf16_wide_grid():
         assert torch.equal(y[0], outs[1][0])                    # a row's logits do not depend on the batch
     yb = cu().gemv_bf16(x[:4].contiguous(), W, out_f32=False)
     assert rel_err(yb, x[:4].float() @ W.float().t()) < 8e-3
+    # a reduction too long for 16 staged rows (the n-gram value projection: 16 heads x 1024) stays on the streaming kernel
+    W2 = (torch.randn(2048, 16384, device=DEV, generator=g) * 0.02).bfloat16()
+    x2 = torch.randn(4, 16384, device=DEV, generator=g).bfloat16()
+    y2 = cu().gemv_bf16(x2, W2, out_f32=True)
+    assert rel_err(y2, x2.float() @ W2.float().t()) < 1e-4
+    assert torch.equal(cu().gemv_bf16(x2[:1].contiguous(), W2, out_f32=True)[0], y2[0])
 
 
 @pytest.mark.parametrize("kind,E,k", [("softmax", 512, 10), ("sigmoid_bias", 288, 8), ("sqrt_softplus", 384, 6)])
