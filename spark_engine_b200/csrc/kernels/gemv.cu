@@ -155,19 +155,25 @@ __device__ __forceinline__ void gemv_mma16816(float (&c)[4], uint32_t a0, uint32
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, typename TO>
+// KS = false: a warp owns 16 weight rows over the whole of K (heads of >= 150K rows).  KS = true: a CTA owns 16 weight
+// rows, its 8 warps split K and their partial tiles are summed in warp order through shared memory (projections of
+// a few thousand rows, where one warp per 16 rows would leave most SMs idle).
+template <int NT, typename TO, bool KS>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw,
                      TO* __restrict__ y, int ldy, int R, int N, int K, int cpc) {
   extern __shared__ __align__(16) uint8_t smem_gemv[];
+  __shared__ float red[KS ? GEMV_WARPS : 1][NT * 4][32];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_gemv);     // [NT * 8][K + GEMV_MMA_PAD]
   const int lds = K + GEMV_MMA_PAD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int KC = K >> 5;                                 // 32-wide k chunks
+  const int per = (KC + GEMV_WARPS - 1) / GEMV_WARPS;
+  const int kb = KS ? min(KC, warp * per) : 0, ke = KS ? min(KC, kb + per) : KC;    // this warp's chunks
   constexpr int BATCH = 8;                               // chunks in flight per lane and weight row
   uint4 ra[BATCH], rb[BATCH];
   auto rows_of = [&](int cg, const uint4*& w0, const uint4*& w1) -> int {
-    const int n0 = ((blockIdx.x * cpc + cg) * GEMV_WARPS + warp) * 16;
+    const int n0 = KS ? blockIdx.x * 16 : ((blockIdx.x * cpc + cg) * GEMV_WARPS + warp) * 16;
     w0 = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(n0 + g, N - 1)) * ldw) + t;
     w1 = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(n0 + g + 8, N - 1)) * ldw) + t;
     return n0;
@@ -175,7 +181,7 @@ gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bf
   auto load = [&](const uint4* w0, const uint4* w1, int kc0) {
 #pragma unroll
     for (int u = 0; u < BATCH; ++u) {
-      const bool in = kc0 + u < KC;
+      const bool in = kc0 + u < ke;
       ra[u] = in ? __ldg(w0 + (kc0 + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
       rb[u] = in ? __ldg(w1 + (kc0 + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
     }
@@ -183,7 +189,7 @@ gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bf
   const uint4 *w0, *w1;
   int n0 = rows_of(0, w0, w1);
   pdl_wait();
-  if (n0 < N) load(w0, w1, 0);                           // in flight while the rows are staged
+  if (n0 < N) load(w0, w1, kb);                          // in flight while the rows are staged
   const int KV8 = K >> 3;
   for (int i = threadIdx.x; i < NT * 8 * KV8; i += blockDim.x) {
     const int r = i / KV8, kv = i - r * KV8;
@@ -192,17 +198,17 @@ gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bf
     *reinterpret_cast<uint4*>(xs + r * lds + kv * 8) = v;
   }
   __syncthreads();
-  for (int cg = 0; cg < cpc; ++cg) {
-    if (cg) { n0 = rows_of(cg, w0, w1); if (n0 < N) load(w0, w1, 0); }
+  for (int cg = 0; cg < (KS ? 1 : cpc); ++cg) {
+    if (cg) { n0 = rows_of(cg, w0, w1); if (n0 < N) load(w0, w1, kb); }
     if (n0 >= N) break;
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
-    for (int kc0 = 0; kc0 < KC; kc0 += BATCH) {
-      if (kc0) load(w0, w1, kc0);
+    for (int kc0 = kb; kc0 < ke; kc0 += BATCH) {
+      if (kc0 != kb) load(w0, w1, kc0);
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        if (kc0 + u < KC) {
+        if (kc0 + u < ke) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint4 xb = *reinterpret_cast<const uint4*>(xs + (nt * 8 + g) * lds + (kc0 + u) * 32 + t * 8);
@@ -212,36 +218,62 @@ gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bf
         }
       }
     }
-    // accumulator (g, t): weight rows n0 + g and n0 + g + 8, activation rows nt * 8 + 2t and + 1
+    if (KS) {
+      // the CTA's 16 weight rows: partial tiles of the 8 warps, summed in warp order
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = nt * 8 + 2 * t + (j & 1), n = n0 + g + (j >> 1) * 8;
-        if (r < R && n < N) y[static_cast<size_t>(r) * ldy + n] = static_cast<TO>(acc[nt][j]);
+        for (int j = 0; j < 4; ++j) red[warp][nt * 4 + j][lane] = acc[nt][j];
+      __syncthreads();
+      for (int i = threadIdx.x; i < NT * 4 * 32; i += blockDim.x) {
+        const int slot = i >> 5, ln = i & 31, nt = slot >> 2, j = slot & 3;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_WARPS; ++w) v += red[w][slot][ln];
+        const int r = nt * 8 + 2 * (ln & 3) + (j & 1), n = n0 + (ln >> 2) + (j >> 1) * 8;
+        if (r < R && n < N) y[static_cast<size_t>(r) * ldy + n] = static_cast<TO>(v);
+      }
+    } else {
+      // accumulator (g, t): weight rows n0 + g and n0 + g + 8, activation rows nt * 8 + 2t and + 1
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = nt * 8 + 2 * t + (j & 1), n = n0 + g + (j >> 1) * 8;
+          if (r < R && n < N) y[static_cast<size_t>(r) * ldy + n] = static_cast<TO>(acc[nt][j]);
+        }
       }
     }
   }
   pdl_trigger();
 }
 
-template <int NT, typename TO>
-static int launch_gemv_wide(const void* x, int ldx, const void* W, int ldw, void* y, int ldy, int rows, int N, int K,
-                            cudaStream_t s) {
-  auto kern = gemv_wide_mma_kernel<NT, TO>;
+template <int NT, typename TO, bool KS>
+static int launch_gemv_wide_as(const void* x, int ldx, const void* W, int ldw, void* y, int ldy, int rows, int N, int K,
+                               cudaStream_t s) {
+  auto kern = gemv_wide_mma_kernel<NT, TO, KS>;
   const int smem = NT * 8 * (K + GEMV_MMA_PAD) * 2;
   if (smem > 200 * 1024) return -6;
   if (smem > 48 * 1024) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
   }
-  const int groups = (N + GEMV_WARPS * 16 - 1) / (GEMV_WARPS * 16);
-  int cpc = (groups + 2367) / 2368;                  // short CTAs: the tail of the last wave stays small
+  const int groups = KS ? (N + 15) / 16 : (N + GEMV_WARPS * 16 - 1) / (GEMV_WARPS * 16);
+  int cpc = KS ? 1 : (groups + 2367) / 2368;         // short CTAs: the tail of the last wave stays small
   if (cpc < 1) cpc = 1;
   dim3 grid((groups + cpc - 1) / cpc);
   const cudaError_t err = spark_launch_pdl(kern, grid, dim3(GEMV_WARPS * 32), smem, s, dim3(1, 1, 1),
                                            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)y, ldy, rows, N, K, cpc);
   return err == cudaSuccess ? 0 : -4;
+}
+
+// Fewer than 8 x 148 tiles of 16 weight rows: split K over the warps of a CTA instead of giving every warp its own tile
+// (depends on N only, so a row's result does not change with the batch it is in).
+template <int NT, typename TO>
+static int launch_gemv_wide(const void* x, int ldx, const void* W, int ldw, void* y, int ldy, int rows, int N, int K,
+                            cudaStream_t s) {
+  return (N + 15) / 16 < 8 * 148 ? launch_gemv_wide_as<NT, TO, true>(x, ldx, W, ldw, y, ldy, rows, N, K, s)
+                                 : launch_gemv_wide_as<NT, TO, false>(x, ldx, W, ldw, y, ldy, rows, N, K, s);
 }
 
 // Shapes the wide kernel takes: one item, no activation, no expert tables, K a multiple of 32 and small enough that
