@@ -65,6 +65,33 @@ class LLMEngine:
             last = m.forward(plan)
         return last[0]
 
+    @torch.no_grad()
+    def prefill_many(self, slots: Sequence[int], ids_list: Sequence[Sequence[int]], chunk: Optional[int] = None) -> torch.Tensor:
+        """Prefill of several fresh sequences in shared forwards: every forward takes up to `chunk` rows in total, one
+        segment per sequence that still has prompt tokens left, so the weights of a layer (and the trellis decode of
+        the experts) are paid once for all of them.  Returns the last-token logits [len(slots), vocab]."""
+        chunk = chunk or self.ecfg.prefill_chunk
+        m = self.model
+        vocab = self.cfg.vocab
+        for ids in ids_list:
+            for t in ids:
+                if not 0 <= t < vocab and not (1 << 20) <= t < (1 << 24):
+                    raise ValueError(f"token id {t} is outside the vocabulary of {vocab} entries")
+        for s in slots:
+            m.reset_slot(s)
+        done = [0] * len(slots)
+        last: List[Optional[torch.Tensor]] = [None] * len(slots)
+        while any(d < len(ids) for d, ids in zip(done, ids_list)):
+            live = [i for i, ids in enumerate(ids_list) if done[i] < len(ids)]
+            share = max(1, chunk // len(live))
+            items = [(slots[i], list(ids_list[i][done[i]: done[i] + share]), done[i]) for i in live]
+            out = m.forward(make_plan(items, device=self.device, all_logits=False))
+            for row, (i, it) in enumerate(zip(live, items)):
+                done[i] += len(it[1])
+                if done[i] >= len(ids_list[i]):
+                    last[i] = out[row]
+        return torch.stack(last)
+
     # ------------------------------------------------------------------ decode
     def _ctx_bucket(self, max_ctx: int) -> int:
         return ctx_bucket(max_ctx)

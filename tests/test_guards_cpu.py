@@ -102,3 +102,24 @@ def test_index_table_check_and_poison_fill(monkeypatch):
     monkeypatch.setattr(dbg, "POISON", True)
     assert torch.isnan(dbg.poison(x)).all()
     assert dbg.poison(i).eq(0x7F7F7F7F).all()
+
+
+def test_batched_prefill_equals_per_sequence_prefill():
+    """Several prompts of different lengths prefilled in shared forwards (one segment each, a row budget per forward) end
+    with the same last-token logits and the same cache state as one prefill per sequence."""
+    import torch
+    from spark_engine_b200.config import EngineConfig, tiny_hybrid
+    from spark_engine_b200.models.weights import init_weights
+    from spark_engine_b200.serving.engine import LLMEngine
+    cfg = tiny_hybrid()
+    W = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (37, 9, 64)]
+    one = LLMEngine(cfg, W, EngineConfig(cuda_graphs=False, prefill_chunk=16), device="cpu", max_seqs=3, kv_tokens_per_seq=128)
+    ref = torch.stack([one.prefill(s, p) for s, p in enumerate(prompts)])
+    many = LLMEngine(cfg, W, EngineConfig(cuda_graphs=False, prefill_chunk=48), device="cpu", max_seqs=3, kv_tokens_per_seq=128)
+    got = many.prefill_many([0, 1, 2], prompts)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-4)
+    assert [many.model.seqs[s].length for s in range(3)] == [37, 9, 64]
+    nxt = ref.argmax(-1).tolist()
+    assert many.decode_round([0, 1, 2], nxt) == one.decode_round([0, 1, 2], nxt)
