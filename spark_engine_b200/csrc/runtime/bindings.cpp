@@ -72,11 +72,14 @@ PYBIND11_MODULE(_runtime, m) {
   py::class_<SlotState>(m, "SlotState").def_readonly("busy", &SlotState::busy).def_readonly("request_id", &SlotState::request_id)
       .def_readonly("tokens", &SlotState::tokens).def_readonly("prefilled", &SlotState::prefilled).def_readonly("prompt_len", &SlotState::prompt_len)
       .def_readonly("generated", &SlotState::generated).def_readonly("max_new", &SlotState::max_new).def_readonly("cancelled", &SlotState::cancelled);
+  py::class_<PrefillPart>(m, "PrefillPart").def_readonly("slot", &PrefillPart::slot).def_readonly("begin", &PrefillPart::begin)
+      .def_readonly("end", &PrefillPart::end);
   py::class_<Step> step(m, "Step");
   py::enum_<Step::Kind>(step, "Kind").value("Idle", Step::Idle).value("Admit", Step::Admit).value("Prefill", Step::Prefill)
       .value("Decode", Step::Decode).value("Cancel", Step::Cancel);
   step.def_readonly("kind", &Step::kind).def_readonly("admit", &Step::admit).def_readonly("slot", &Step::slot)
-      .def_readonly("chunk_begin", &Step::chunk_begin).def_readonly("chunk_end", &Step::chunk_end).def_readonly("decode_slots", &Step::decode_slots);
+      .def_readonly("chunk_begin", &Step::chunk_begin).def_readonly("chunk_end", &Step::chunk_end).def_readonly("decode_slots", &Step::decode_slots)
+      .def_readonly("parts", &Step::parts);
   py::class_<Scheduler>(m, "Scheduler").def(py::init<int, int64_t, int64_t, int, int>())
       .def("submit", &Scheduler::submit).def("cancel", &Scheduler::cancel).def("set_checkpoint", &Scheduler::set_checkpoint)
       .def("drop_checkpoint", &Scheduler::drop_checkpoint).def("next", &Scheduler::next, py::arg("disk_prefix_tokens") = 0)

@@ -100,10 +100,18 @@ Step Scheduler::next(int64_t disk_prefix_tokens) {
   // alternate one prefill chunk with one batched decode round so that running streams keep their cadence
   const bool do_prefill = !pre.empty() && (dec.empty() || !last_was_prefill_);
   if (do_prefill) {
-    const int i = pre[rr_++ % pre.size()];
-    s.kind = Step::Prefill; s.slot = i;
-    s.chunk_begin = slots_[i].prefilled;
-    s.chunk_end = std::min<int64_t>(slots_[i].prompt_len, s.chunk_begin + chunk_);
+    const int n = static_cast<int>(pre.size()), first = rr_++ % n;
+    const int64_t share = std::max<int64_t>(1, chunk_ / n);
+    s.kind = Step::Prefill;
+    for (int k = 0; k < n; ++k) {
+      const int i = pre[(first + k) % n];
+      PrefillPart p;
+      p.slot = i;
+      p.begin = slots_[i].prefilled;
+      p.end = std::min<int64_t>(slots_[i].prompt_len, p.begin + share);
+      s.parts.push_back(p);
+    }
+    s.slot = s.parts[0].slot; s.chunk_begin = s.parts[0].begin; s.chunk_end = s.parts[0].end;
     last_was_prefill_ = true;
     return s;
   }

@@ -46,11 +46,16 @@ struct SlotState {
   uint64_t last_use = 0;
 };
 
+struct PrefillPart { int slot = -1; int64_t begin = 0, end = 0; };
+
 struct Step {
   enum Kind : int { Idle = 0, Admit = 1, Prefill = 2, Decode = 3, Cancel = 4 } kind = Idle;
   AdmitPlan admit;
-  int slot = -1;                       // Prefill / Cancel
+  int slot = -1;                       // Prefill (first part) / Cancel
   int64_t chunk_begin = 0, chunk_end = 0;
+  // Prefill: every sequence that still has prompt tokens gets a share of the chunk budget in the same forward (one
+  // segment each), so a layer's weights are read once for all of them; parts[0] repeats slot / chunk_begin / chunk_end
+  std::vector<PrefillPart> parts;
   std::vector<int> decode_slots;       // Decode: sequences batched into this round
 };
 

@@ -82,7 +82,8 @@ class EngineServer:
         self.by_slot: Dict[int, _Live] = {}
         self.prof = Profiler(e.profile)
         self.totals = {"prompt_tokens": 0, "generation_tokens": 0, "requests": 0, "spec_rounds": 0, "drafted_tokens": 0,
-                       "accepted_drafts": 0, "prefix_hit_tokens": 0, "disk_restores": 0}
+                       "accepted_drafts": 0, "prefix_hit_tokens": 0, "disk_restores": 0, "prefill_steps": 0,
+                       "prefill_shared_steps": 0}
         self.out: List[dict] = []
         self.shutdown = False
         self.watchdog = None
@@ -175,7 +176,7 @@ class EngineServer:
         if st.kind == K.Admit:
             self._admit(st.admit)
         elif st.kind == K.Prefill:
-            self._prefill(st.slot, st.chunk_begin, st.chunk_end)
+            self._prefill([(p.slot, p.begin, p.end) for p in st.parts])
         elif st.kind == K.Decode:
             self._decode(list(st.decode_slots))
         elif st.kind == K.Cancel:
@@ -229,34 +230,49 @@ class EngineServer:
         lv.seq.lookup = LookupIndex(self.spec.lookup_n)
         lv.seq.lookup.extend(prompt[:reuse])
 
-    def _prefill(self, slot: int, c0: int, c1: int):
-        lv, m = self.by_slot[slot], self.model
-        prompt = lv.msg["prompt_ids"]
+    def _prefill(self, parts):
+        """One forward over a prefill chunk of every listed sequence: parts = [(slot, first token, end)], one segment
+        each (the scheduler shares its chunk budget among the sequences that still have prompt tokens)."""
+        m = self.model
         t0 = time.time()
+        lives = [self.by_slot[slot] for slot, _, _ in parts]
         with self.prof.section("prefill"):
-            toks = prompt[c0:c1]
-            logits = m.forward(make_plan([(slot, toks, c0)], device=m.device, all_logits=False))[0]
+            items = [(slot, lv.msg["prompt_ids"][c0:c1], c0) for (slot, c0, c1), lv in zip(parts, lives)]
+            plan = make_plan(items, device=m.device, all_logits=False)
+            logits = m.forward(plan)
             hid = m.hidden_out
             if m.mtp_layers:
-                nxt = prompt[c0 + 1: c1 + 1]
-                if nxt:
-                    m.mtp_forward(make_plan([(slot, nxt, c0)], device=m.device, all_logits=False), hid[: len(nxt)])
-        lv.seq.lookup.extend(toks)
-        lv.prefill_ms += (time.time() - t0) * 1e3
-        self.sched.on_prefilled(slot, c1)
-        if c1 == len(prompt):
-            s = lv.seq
-            first = m.sample(logits, s.temperature, s.seed, len(prompt))
-            s.last_token, s.hidden = first, hid[-1].clone()
-            s.pending_mtp = [(hid[-1].clone(), first)]
-            s.generated = [first]
-            s.lookup.extend([first])
-            lv.t_first = time.time()
-            self.totals["prompt_tokens"] += len(prompt)
-            boundary = len(prompt) // 256 * 256
-            if self.disk is not None and boundary and boundary == len(prompt):
-                self.disk.save(prompt, m.snapshot(slot))
-            self._emit(lv, [first])
+                mtp_items, rows = [], []
+                for (slot, c0, c1), lv, seg in zip(parts, lives, plan.segs):
+                    nxt = lv.msg["prompt_ids"][c0 + 1: c1 + 1]
+                    if nxt:
+                        mtp_items.append((slot, nxt, c0))
+                        rows.append(hid[seg.r0: seg.r0 + len(nxt)])
+                if mtp_items:
+                    m.mtp_forward(make_plan(mtp_items, device=m.device, all_logits=False),
+                                  rows[0] if len(rows) == 1 else torch.cat(rows))
+        dt = (time.time() - t0) * 1e3
+        self.totals["prefill_steps"] += 1
+        self.totals["prefill_shared_steps"] += len(parts) > 1
+        for k, ((slot, c0, c1), lv, seg) in enumerate(zip(parts, lives, plan.segs)):
+            prompt = lv.msg["prompt_ids"]
+            lv.seq.lookup.extend(prompt[c0:c1])
+            lv.prefill_ms += dt / len(parts)
+            self.sched.on_prefilled(slot, c1)
+            if c1 == len(prompt):
+                s = lv.seq
+                h_last = hid[seg.r0 + seg.n - 1].clone()
+                first = m.sample(logits[k], s.temperature, s.seed, len(prompt))
+                s.last_token, s.hidden = first, h_last
+                s.pending_mtp = [(h_last.clone(), first)]
+                s.generated = [first]
+                s.lookup.extend([first])
+                lv.t_first = time.time()
+                self.totals["prompt_tokens"] += len(prompt)
+                boundary = len(prompt) // 256 * 256
+                if self.disk is not None and boundary and boundary == len(prompt):
+                    self.disk.save(prompt, m.snapshot(slot))
+                self._emit(lv, [first])
 
     def _emit(self, lv: _Live, toks: List[int]):
         msg = lv.msg

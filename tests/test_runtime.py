@@ -85,15 +85,18 @@ def test_scheduler_admission_prefix_reuse_and_round_robin():
     assert st.kind == R.Step.Kind.Admit and st.admit.slot == 1
     s.on_admitted(st.admit)
     trace = []
-    for _ in range(6):                           # prefill chunks alternate with decode rounds of the running streams
+    for _ in range(6):              # sequences that still have prompt tokens share the chunk budget of one forward
         st = s.next()
-        trace.append((st.kind, st.slot, list(st.decode_slots)))
+        trace.append((st.kind, [(p.slot, p.begin, p.end) for p in st.parts], list(st.decode_slots)))
         if st.kind == R.Step.Kind.Prefill:
-            s.on_prefilled(st.slot, st.chunk_end)
+            assert (st.slot, st.chunk_begin, st.chunk_end) == (st.parts[0].slot, st.parts[0].begin, st.parts[0].end)
+            for p in st.parts:
+                s.on_prefilled(p.slot, p.end)
         if st.kind == R.Step.Kind.Decode and st.decode_slots == [0, 1]:
             break
-    assert trace[0][:2] == (R.Step.Kind.Prefill, 1) and trace[1] == (R.Step.Kind.Decode, -1, [1])
-    assert trace[2][:2] == (R.Step.Kind.Prefill, 0) and st.decode_slots == [0, 1]
+    assert trace[0][0] == R.Step.Kind.Prefill and sorted(trace[0][1]) == [(0, 64, 96), (1, 0, 32)]
+    assert trace[1][0] == R.Step.Kind.Prefill and sorted(trace[1][1]) == [(0, 96, 100), (1, 32, 50)]
+    assert trace[2] == (R.Step.Kind.Decode, [], [0, 1])
     s.on_tokens(0, [7], False)
     s.on_tokens(1, [8], True)
     assert s.cancel(1)
@@ -117,7 +120,8 @@ def test_scheduler_admission_prefix_reuse_and_round_robin():
         if st.kind == R.Step.Kind.Admit:
             break
         if st.kind == R.Step.Kind.Prefill:
-            s.on_prefilled(st.slot, st.chunk_end)
+            for p in st.parts:
+                s.on_prefilled(p.slot, p.end)
         elif st.kind == R.Step.Kind.Decode:
             for sl in st.decode_slots:
                 s.on_tokens(sl, [1], True)

@@ -61,6 +61,7 @@ def test_socket_protocol_matches_greedy_and_reuses_prefix(tmp_path):
     done, deltas = _collect(c, buf, [1, 2])
     assert done[1]["token_ids"] == ref1 == deltas[1] and done[2]["token_ids"] == ref2
     assert done[1]["finish_reason"] == "length" and done[1]["rounds"] >= 1 and done[1]["prefill_ms"] > 0
+    assert es.totals["prefill_shared_steps"] > 0        # the two prompts shared prefill forwards (one segment each)
     # follow-up turn: the finished store is continued, only the new tokens are prefilled
     p3 = p1 + ref1 + [5, 6, 7]
     ref3 = oracle.greedy_generate(cfg, W, torch.tensor(p3), 4)[0].tolist()
