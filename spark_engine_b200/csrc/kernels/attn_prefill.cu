@@ -36,14 +36,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// grid (row tiles, Hq, segments); 128 threads
-template <int D>
+// grid (row tiles, Hq, segments); 128 threads.  MASK: rows also carry a bit per 4-token key block (bmask [R, mw] words,
+// bit b of a row = block b may be attended): block-sparse selections of a few thousand tokens run through the dense
+// tiles with the unselected blocks masked, which beats one gathering CTA per row while the context is short enough.
+template <int D, bool MASK>
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
                     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,   // [tokens, Hkv, D]
                     const long long* __restrict__ row_kv, const int* __restrict__ seg,
                     const __nv_bfloat16* __restrict__ qkv, int ld, int gated,
-                    __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2) {
+                    __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2,
+                    const uint32_t* __restrict__ bmask, int mw) {
   constexpr int LDS = D + 8;                                // smem row stride (elements): 16 bytes past a 128-byte multiple
   extern __shared__ __align__(16) uint8_t smem_pf[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_pf);        // [64][LDS]
@@ -92,6 +95,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
   // query positions of this thread's two rows (padded rows: the last valid row's)
   const int p_lo = pos0 + qt * PF_BM + min(warp * 16 + g, rows_valid - 1);
   const int p_hi = pos0 + qt * PF_BM + min(warp * 16 + g + 8, rows_valid - 1);
+  const uint32_t* bm_lo = MASK ? bmask + static_cast<size_t>(r0 + p_lo - pos0) * mw : nullptr;
+  const uint32_t* bm_hi = MASK ? bmask + static_cast<size_t>(r0 + p_hi - pos0) * mw : nullptr;
 
   for (int j = 0; j < ntiles; ++j) {
     const int buf = j & 1;
@@ -119,6 +124,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
     // ---- scale, causal mask, streaming softmax
     const int k0 = j * PF_BN;
     const bool need_mask = k0 + PF_BN - 1 > pos0 + qt * PF_BM;
+    // 16 block bits of this 64-key tile for the thread's two rows (a word covers two tiles)
+    const uint32_t sel_lo = MASK ? (__ldg(bm_lo + (j >> 1)) >> ((j & 1) * 16)) : 0u;
+    const uint32_t sel_hi = MASK ? (__ldg(bm_hi + (j >> 1)) >> ((j & 1) * 16)) : 0u;
     float mx_lo = m_lo, mx_hi = m_hi;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -129,6 +137,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
           const int key = k0 + i * 8 + 2 * t + (e & 1);
           if (key > ((e >> 1) ? p_hi : p_lo)) v = -INFINITY;
         }
+        if (MASK && !((((e >> 1) ? sel_hi : sel_lo) >> (i * 2 + (t >> 1))) & 1u)) v = -INFINITY;
         s[i][e] = v;
       }
       mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
@@ -136,13 +145,16 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
     }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-    const float c_lo = exp2f(m_lo - mx_lo), c_hi = exp2f(m_hi - mx_hi);      // key 0 is visible to every row: mx is finite
+    // dense: key 0 is visible to every row, so mx is finite.  Masked: a row may have seen no key yet (mx = -inf):
+    // exponentials are then taken against 0, every term is exp2(-inf) = 0 and the running sums stay 0.
+    const float f_lo = (MASK && mx_lo == -INFINITY) ? 0.f : mx_lo, f_hi = (MASK && mx_hi == -INFINITY) ? 0.f : mx_hi;
+    const float c_lo = exp2f(m_lo - f_lo), c_hi = exp2f(m_hi - f_hi);
     m_lo = mx_lo; m_hi = mx_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      s[i][0] = exp2f(s[i][0] - mx_lo); s[i][1] = exp2f(s[i][1] - mx_lo);
-      s[i][2] = exp2f(s[i][2] - mx_hi); s[i][3] = exp2f(s[i][3] - mx_hi);
+      s[i][0] = exp2f(s[i][0] - f_lo); s[i][1] = exp2f(s[i][1] - f_lo);
+      s[i][2] = exp2f(s[i][2] - f_hi); s[i][3] = exp2f(s[i][3] - f_hi);
       sum_lo += s[i][0] + s[i][1]; sum_hi += s[i][2] + s[i][3];
     }
     l_lo = l_lo * c_lo + sum_lo; l_hi = l_hi * c_hi + sum_hi;
@@ -186,19 +198,38 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ qbuf,        // [R, Hq, D]
   }
 }
 
-template <int D>
+template <int D, bool MASK>
 static int launch_prefill(const void* qbuf, const void* kc, const void* vc, const long long* row_kv, const int* seg, int nseg,
                           int max_rows, const void* qkv, int ld, int gated, void* out, int Hq, int Hkv, float scale,
-                          cudaStream_t s) {
-  auto kern = attn_prefill_kernel<D>;
+                          cudaStream_t s, const uint32_t* bmask = nullptr, int mw = 0) {
+  auto kern = attn_prefill_kernel<D, MASK>;
   constexpr int smem = (PF_BM + 4 * PF_BN) * (D + 8) * 2;
   static bool done = false;
   if (!done) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
   dim3 grid((max_rows + PF_BM - 1) / PF_BM, Hq, nseg);
   kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qbuf, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, row_kv, seg,
                                (const __nv_bfloat16*)qkv, ld, gated, (__nv_bfloat16*)out, Hq, Hkv,
-                               scale * 1.4426950408889634f);
+                               scale * 1.4426950408889634f, bmask, mw);
   return spark_launch_rc(__func__);
+}
+
+// grid R, 256 threads: the row's selected token list -> one bit per 4-token block (the always-visible tail is part of
+// the list, so its blocks are set as well; keys past the row's position are cut by the causal test).
+__global__ void __launch_bounds__(256)
+sel_blockmask_kernel(const int* __restrict__ sel, const int* __restrict__ sel_n, int sel_ld, uint32_t* __restrict__ bmask,
+                     int mw) {
+  extern __shared__ uint32_t bits[];
+  const int r = blockIdx.x;
+  for (int i = threadIdx.x; i < mw; i += blockDim.x) bits[i] = 0u;
+  __syncthreads();
+  const int n = sel_n[r];
+  const int* row = sel + static_cast<size_t>(r) * sel_ld;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int b = row[i] >> 2;
+    if ((b >> 5) < mw) atomicOr(&bits[b >> 5], 1u << (b & 31));
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < mw; i += blockDim.x) bmask[static_cast<size_t>(r) * mw + i] = bits[i];
 }
 
 }  // namespace spark
@@ -212,8 +243,23 @@ extern "C" int spark_attn_prefill(const void* qbuf, const void* kc, const void* 
                                   int D, float scale, cudaStream_t s) {
   if (nseg <= 0 || max_rows <= 0) return 0;
   if (Hq % Hkv) return -5;
-  if (D == 256) return launch_prefill<256>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
-  if (D == 128) return launch_prefill<128>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
-  if (D == 64) return launch_prefill<64>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
+  if (D == 256) return launch_prefill<256, false>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
+  if (D == 128) return launch_prefill<128, false>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
+  if (D == 64) return launch_prefill<64, false>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s);
+  return -5;
+}
+
+// The same tiles for rows with a block-sparse selection (4-token blocks): sel / sel_n are the per-row token lists of the
+// selection kernels (R rows, plan order), bmask a scratch of R * mw words with mw >= ceil(max context / 128).
+extern "C" int spark_attn_prefill_masked(const void* qbuf, const void* kc, const void* vc, const long long* row_kv,
+                                         const int* seg, int nseg, int max_rows, const void* qkv, int ld, int gated, void* out,
+                                         int Hq, int Hkv, int D, float scale, const int* sel, const int* sel_n, int sel_ld,
+                                         int R, unsigned* bmask, int mw, cudaStream_t s) {
+  if (nseg <= 0 || max_rows <= 0 || R <= 0) return 0;
+  if (Hq % Hkv || mw <= 0 || mw > 8192 || !sel || !sel_n || !bmask) return -5;
+  sel_blockmask_kernel<<<R, 256, mw * 4, s>>>(sel, sel_n, sel_ld, bmask, mw);
+  if (D == 256) return launch_prefill<256, true>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s, bmask, mw);
+  if (D == 128) return launch_prefill<128, true>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s, bmask, mw);
+  if (D == 64) return launch_prefill<64, true>(qbuf, kc, vc, row_kv, seg, nseg, max_rows, qkv, ld, gated, out, Hq, Hkv, scale, s, bmask, mw);
   return -5;
 }

@@ -57,6 +57,8 @@ _SIGS = {
                                 i32, i32, vp],
     "spark_kda_seq": [vp, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, vp, vp, i32, i32],
     "spark_attn_prefill": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp],
+    "spark_attn_prefill_masked": [vp, vp, vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, f32, vp, vp, i32, i32, vp,
+                                  i32, vp],
     "spark_exl3_mgemm": [vp, i32, vp, vp, i64, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "spark_gdn_chunk_prefill": [vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32,
                                 i32, f32, vp],
@@ -1102,6 +1104,8 @@ ATT_TS = 64
 
 ATTN_PREFILL_KERNEL = os.environ.get("SPARK_ATTN_PREFILL", "1") == "1"
 ATTN_PREFILL_MIN_ROWS = 32
+# block-sparse prefill rows take the masked dense tiles while a segment's average causal context is at most this
+ATTN_MASKED_MAX_KEYS = int(os.environ.get("SPARK_ATTN_MASKED_MAX_KEYS", "6144"))
 
 
 def tree_ancestor_masks(plan, device) -> torch.Tensor:
@@ -1170,6 +1174,21 @@ def attn_mixer(mixer, qkv, plan, seqs):
                                       max(s.n for s in plan.segs), P(qkv), qkv.stride(0), int(c.gated), P(out),
                                       c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), stream())
         check(rc, "spark_attn_prefill")
+        return out
+    if (sel is not None and not tree and not mixer.fp8 and ATTN_PREFILL_KERNEL and c.block == 4
+            and c.head_dim in (64, 128, 256) and min(s.n for s in plan.segs) >= ATTN_PREFILL_MIN_ROWS
+            and max(s.pos0 + s.n // 2 for s in plan.segs) <= ATTN_MASKED_MAX_KEYS):
+        # block-sparse rows on a context of a few thousand tokens: the dense tiles with the unselected blocks masked
+        # (64 rows share every key tile) beat one gathering CTA per row, which is bound by L2 bandwidth
+        mw = (d["max_ctx"] + 127) // 128
+        bmask = scratch("attn_block_mask", R * mw, torch.int32, dev)
+        out = torch.empty(R, c.n_q_heads * c.head_dim, dtype=torch.bfloat16, device=dev)
+        add_launches(1)
+        rc = lib().spark_attn_prefill_masked(P(qbuf), P(mixer.k), P(mixer.v), P(d["row_kv"]), P(d["seg"]), len(plan.segs),
+                                             max(s.n for s in plan.segs), P(qkv), qkv.stride(0), int(c.gated), P(out),
+                                             c.n_q_heads, c.n_kv_heads, c.head_dim, 1.0 / math.sqrt(c.head_dim), P(sel),
+                                             P(sel_n), sel_ld, R, P(bmask), mw, stream())
+        check(rc, "spark_attn_prefill_masked")
         return out
     nsplit, chunks = (max_ctx + ATT_TS - 1) // ATT_TS, 1
     if R >= 64 and c.head_dim in (64, 128, 256) and c.n_q_heads // c.n_kv_heads <= 16:

@@ -131,6 +131,42 @@ def test_prefill_attention_kernel_matches_per_row_kernel(head_dim):
     assert err < 2e-2, err      # probabilities are rounded to bf16 for the P V product
 
 
+@pytest.mark.parametrize("head_dim", [64, 256])
+def test_block_sparse_prefill_on_masked_dense_tiles_matches_per_row_kernel(head_dim):
+    """Prefill rows whose context exceeds the selection budget: the flash tiles with unselected 4-token blocks masked
+    against the per-row gathering kernel (same selection lists), ragged segments, a continuation chunk, rows whose first
+    key tiles hold no selected block at all.  One attention layer: both paths then work from the same selection (with
+    a second layer, rounding differences of the first flip near-tied blocks and the comparison measures that)."""
+    import dataclasses
+    from spark_engine_b200 import ops
+    cfg = tiny_hybrid()
+    cfg.layer_types = ["attn"]
+    cfg.n_layers = 1
+    cfg.attn = dataclasses.replace(cfg.attn, head_dim=head_dim, rope_dim=32, sparse_topk_blocks=8, block=4, idx_heads=2,
+                                   idx_dim=32)
+    W = init_weights(cfg, seed=3)
+    Wd = to_device(W, "cuda")
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, cfg.vocab, (2, 420), generator=g)
+    cu = ops.cuda_ops()
+    outs = []
+    for masked in (True, False):
+        old = cu.ATTN_MASKED_MAX_KEYS
+        cu.ATTN_MASKED_MAX_KEYS = old if masked else -1
+        n0 = cu.launch_count()
+        try:
+            m = Model(cfg, Wd, device="cuda", dtype=torch.bfloat16, n_slots=2, kv_tokens=1024)
+            a = m.forward(make_plan([(0, ids[0, :230].tolist(), 0), (1, ids[1, :97].tolist(), 0)], device="cuda")).float()
+            b = m.forward(make_plan([(0, ids[0, 230:420].tolist(), 230), (1, ids[1, 97:200].tolist(), 97)],
+                                    device="cuda")).float()
+            outs.append(torch.cat((a, b)))
+        finally:
+            cu.ATTN_MASKED_MAX_KEYS = old
+    assert torch.isfinite(outs[0]).all()
+    err = (outs[0] - outs[1]).norm() / outs[1].norm()
+    assert err < 2e-2, err
+
+
 @pytest.mark.parametrize("preset", ["glm-style", "ds4-style"])
 def test_other_families_on_device_match_cpu_runner(preset):
     """KDA + MLA/DSA + mHC (GLM-style) and compressed sparse MLA + n-gram tables (DS-style), scaled down: device prefill
