@@ -39,6 +39,114 @@ idx_score_kernel(const float* __restrict__ qi, int H, int Dm, const float* __res
   if (lane == 0) score[static_cast<size_t>(r) * ld + b] = acc;
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The same scores for prefill rows on tensor cores.  The M side of the MMA tiles is (row, head): 64 consecutive
+// [row][head] query vectors of one segment (64 / H rows) are staged once, pooled-key tiles of 64 blocks are streamed
+// with cp.async (double buffered), S = Q K^T runs as 3xTF32 (every operand split into a TF32 head and a TF32 remainder,
+// three m16n8k8 MMAs per product: fp32-grade scores, so a row selects the same blocks whether it is scored here or by
+// the decode kernel), then relu x scale x head weight goes through shared memory where the H heads of a row are summed
+// in head order.  Blocks beyond a row's visible range get values nobody reads.
+// Reference: engine-rs/shim/ds41_attn.cu:447-824, dataflow.cu:159-336 (tensor-core indexer scoring for prefill rows).
+constexpr int IS_M = 64, IS_N = 64;
+
+__device__ __forceinline__ void is_cp16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc));
+}
+__device__ __forceinline__ void is_split(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+}
+__device__ __forceinline__ void is_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid (ceil(max segment rows / (64 / H)), segments); 128 threads.  H in {1, 2, 4, ..., 64}, Dm % 8 == 0, Dm <= 128.
+// seg: int [nseg][4] = slot, first row, rows, first position.
+__global__ void __launch_bounds__(128)
+idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* __restrict__ pool,
+                     const long long* __restrict__ row_kv, const int* __restrict__ seg, int block,
+                     const float* __restrict__ head_w, float scale, float* __restrict__ score, int ld) {
+  extern __shared__ __align__(16) uint8_t smem_is[];
+  const int LQ = Dm + 4;                                             // row stride in floats: rows fall on different banks
+  float* Qs = reinterpret_cast<float*>(smem_is);                     // [64][LQ]
+  float* Ks = Qs + IS_M * LQ;                                        // [2][64][LQ]
+  float* Ss = Ks + 2 * IS_N * LQ;                                    // [64][65]
+  const int sg = blockIdx.y, rpc = IS_M / H;
+  const int r0 = seg[sg * 4 + 1], n = seg[sg * 4 + 2], pos0 = seg[sg * 4 + 3];
+  const int q0 = blockIdx.x * rpc;                                   // first row of this CTA inside the segment
+  if (q0 >= n) return;
+  const int rows_valid = min(rpc, n - q0);
+  const int nb = (pos0 + q0 + rows_valid) / block;                   // blocks visible to the CTA's last row
+  if (nb <= 0) return;
+  const int ntiles = (nb + IS_N - 1) / IS_N;
+  const float* kbase = pool + (row_kv[r0] / block) * Dm;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int VPR = Dm >> 2;                                           // 16-byte vectors per row
+  for (int i = tid; i < IS_M * VPR; i += 128) {
+    const int m = i / VPR, v = i - m * VPR;
+    const int mm = min(m, rows_valid * H - 1);                       // padded (row, head) pairs repeat the last valid one
+    is_cp16(Qs + m * LQ + v * 4, qi + (static_cast<size_t>(r0 + q0) * H + mm) * Dm + v * 4);
+  }
+  auto load_k = [&](int j, int buf) {
+    float* kd = Ks + buf * IS_N * LQ;
+    for (int i = tid; i < IS_N * VPR; i += 128) {
+      const int r = i / VPR, v = i - r * VPR;
+      const int b = j * IS_N + r;
+      if (b < nb) is_cp16(kd + r * LQ + v * 4, kbase + static_cast<size_t>(b) * Dm + v * 4);
+      else *reinterpret_cast<float4*>(kd + r * LQ + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  load_k(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // weights of this thread's two (row, head) pairs: accumulator rows g and g + 8 of the warp's 16
+  const int m_lo = warp * 16 + g, m_hi = m_lo + 8;
+  const int mv_lo = min(m_lo, rows_valid * H - 1), mv_hi = min(m_hi, rows_valid * H - 1);
+  const float w_lo = scale * (head_w ? head_w[static_cast<size_t>(r0 + q0) * H + mv_lo] : 1.f);
+  const float w_hi = scale * (head_w ? head_w[static_cast<size_t>(r0 + q0) * H + mv_hi] : 1.f);
+  for (int j = 0; j < ntiles; ++j) {
+    const int buf = j & 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                                 // tile j landed; Ss of tile j-1 has been read
+    if (j + 1 < ntiles) { load_k(j + 1, buf ^ 1); asm volatile("cp.async.commit_group;" ::: "memory"); }
+    const float* kb = Ks + buf * IS_N * LQ;
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+    for (int ks = 0; ks < Dm / 8; ++ks) {
+      uint32_t ah[4], al[4];
+      is_split(Qs[m_lo * LQ + ks * 8 + t], ah[0], al[0]);
+      is_split(Qs[m_hi * LQ + ks * 8 + t], ah[1], al[1]);
+      is_split(Qs[m_lo * LQ + ks * 8 + t + 4], ah[2], al[2]);
+      is_split(Qs[m_hi * LQ + ks * 8 + t + 4], ah[3], al[3]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        uint32_t bh0, bl0, bh1, bl1;
+        is_split(kb[(nt * 8 + g) * LQ + ks * 8 + t], bh0, bl0);
+        is_split(kb[(nt * 8 + g) * LQ + ks * 8 + t + 4], bh1, bl1);
+        is_mma(s[nt], al, bh0, bh1);                                 // small terms first
+        is_mma(s[nt], ah, bl0, bl1);
+        is_mma(s[nt], ah, bh0, bh1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int c = nt * 8 + 2 * t;
+      Ss[m_lo * 65 + c] = fmaxf(s[nt][0], 0.f) * w_lo; Ss[m_lo * 65 + c + 1] = fmaxf(s[nt][1], 0.f) * w_lo;
+      Ss[m_hi * 65 + c] = fmaxf(s[nt][2], 0.f) * w_hi; Ss[m_hi * 65 + c + 1] = fmaxf(s[nt][3], 0.f) * w_hi;
+    }
+    __syncthreads();
+    for (int i = tid; i < rows_valid * IS_N; i += 128) {
+      const int rq = i >> 6, c = i & 63, b = j * IS_N + c;
+      if (b >= nb) continue;
+      float acc = 0.f;
+      for (int h = 0; h < H; ++h) acc += Ss[(rq * H + h) * 65 + c];
+      score[static_cast<size_t>(r0 + q0 + rq) * ld + b] = acc;
+    }
+  }
+}
+
 __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int& total) {
   // exclusive prefix sum over the 1024 threads of the CTA; `total` = sum over all threads
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -356,6 +464,21 @@ extern "C" int spark_idx_score(const float* qi, int R, int H, int Dm, const floa
   if (R <= 0 || nb_max <= 0) return 0;
   if (Dm > 128) return -5;
   idx_score_kernel<<<dim3((nb_max + 7) / 8, R), 256, 0, s>>>(qi, H, Dm, pool, row_kv, pos, block, head_w, scale, score, ld);
+  return spark_launch_rc(__func__);
+}
+
+// Prefill rows (whole segments): tensor-core scoring.  H a power of two <= 64, Dm % 8 == 0, Dm <= 128.
+extern "C" int spark_idx_score_mma(const float* qi, int H, int Dm, const float* pool, const long long* row_kv, const int* seg,
+                                   int nseg, int max_rows, int block, const float* head_w, float scale, float* score, int ld,
+                                   cudaStream_t s) {
+  if (nseg <= 0 || max_rows <= 0) return 0;
+  if (H < 1 || H > 64 || (H & (H - 1)) || (Dm & 7) || Dm > 128 || Dm < 8) return -5;
+  const int smem = (3 * 64 * (Dm + 4) + 64 * 65) * 4;
+  static bool done = false;
+  if (!done) { cudaFuncSetAttribute(idx_score_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); done = true; }
+  const int rpc = 64 / H;
+  idx_score_mma_kernel<<<dim3((max_rows + rpc - 1) / rpc, nseg), 128, smem, s>>>(qi, H, Dm, pool, row_kv, seg, block, head_w, scale,
+                                                                                score, ld);
   return spark_launch_rc(__func__);
 }
 

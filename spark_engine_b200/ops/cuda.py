@@ -1081,7 +1081,8 @@ def mla_mixer(mixer, h, plan, seqs):
         from . import sparse as sp
         qi = qb[:, nq:].float().view(R, c.idx_heads, c.idx_dim).contiguous()
         sel, sel_n = sp.select_tokens(qi, mixer.pool, d["row_kv"], d["pos32"], c.pool, c.topk_pools, max_ctx, head_w=hw,
-                                      scale=c.idx_dim ** -0.5, window=c.window)
+                                      scale=c.idx_dim ** -0.5, window=c.window,
+                                      segs=None if tree else (d["seg"], len(plan.segs), max(s.n for s in plan.segs)))
         sel_ld = sel.shape[1]
         max_ctx = sel_ld
     nsplit = (max_ctx + MLA_TS - 1) // MLA_TS

@@ -410,3 +410,37 @@ def test_topk_select_multi_cta_equals_single_cta_and_reference(window):
         assert one[r, :n].tolist() == ref, r
         assert many[r, :n].tolist() == ref, r
         assert auto[r, :n].tolist() == ref, r
+
+
+@pytest.mark.parametrize("H,Dm,weighted", [(4, 128, False), (32, 128, True), (2, 32, True), (16, 64, False)])
+def test_indexer_scores_on_tensor_cores_equal_the_per_row_kernel(H, Dm, weighted):
+    """Prefill rows scored as (row, head) x pooled-key tiles with 3xTF32 MMAs against the fp32 per-row kernel: two ragged
+    segments at different offsets of their sequences, with and without per-head weights; the selections agree."""
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.ops import sparse as sp
+    g = torch.Generator(device=DEV).manual_seed(31)
+    block, topk = 4, 16
+    n0, n1, p0, p1 = 150, 77, 260, 0
+    plan = make_plan([(0, [1] * n0, p0), (1, [1] * n1, p1)], device=DEV)
+    d = plan.dev
+    R = n0 + n1
+    cap = 1024                                                    # tokens per sequence
+    row_kv = torch.tensor([0] * n0 + [cap] * n1, dtype=torch.int64, device=DEV)
+    pool = torch.randn(2 * cap // block + 2, Dm, device=DEV, generator=g)
+    qi = torch.randn(R, H, Dm, device=DEV, generator=g)
+    hw = torch.rand(R, H, device=DEV, generator=g) if weighted else None
+    max_ctx = p0 + n0
+    outs = []
+    for segs in (None, (d["seg"], 2, max(n0, n1))):
+        sel, sel_n = sp.select_tokens(qi, pool, row_kv, d["pos32"], block, topk, max_ctx, head_w=hw, window=8, segs=segs)
+        nb_max = max_ctx // block
+        score = cu().scratch("idx_score", R * nb_max, torch.float32, torch.device(DEV))[: R * nb_max].view(R, nb_max).clone()
+        outs.append((sel.clone(), sel_n.clone(), score))
+    vis = ((d["pos32"] + 1) // block).long()
+    live = torch.arange(outs[0][2].shape[1], device=DEV).unsqueeze(0) < vis.unsqueeze(1)
+    a, b = outs[0][2][live], outs[1][2][live]
+    assert torch.isfinite(b).all()
+    assert (a - b).abs().max().item() <= 2e-5 * a.abs().max().item()
+    assert torch.equal(outs[0][1], outs[1][1])
+    same = sum(int(torch.equal(outs[0][0][r, : int(outs[0][1][r])], outs[1][0][r, : int(outs[1][1][r])])) for r in range(R))
+    assert same >= R - 2, same            # a near-tie at the threshold may pick the other block
