@@ -55,6 +55,7 @@ def _worker(rank, world, port):
     for k, name in enumerate(("glm-style", "ds4-style")):
         cfg3 = scaled_down(get_model_config(name))
         cfg3.mtp_layers = 0
+        cfg3.kv_dtype = "bf16"                       # sharding arithmetic only: e4m3 cache codes amplify last-bit differences
         W3 = init_weights(cfg3, seed=1)
         for lw in W3["layers"]:                      # wide router margins: a bf16 rounding difference must not flip an expert,
             if "gate" in lw["mlp"]:                  # so the comparison measures arithmetic, not routing luck
@@ -70,8 +71,7 @@ def _worker(rank, world, port):
             parts3 = [torch.empty_like(lt3) for _ in range(world)]
             dist.all_gather(parts3, lt3.contiguous())
             err3 = ((torch.cat(parts3, 1) - lr3).norm() / lr3.norm()).item()
-            # DS-style keeps packed FP8 latent rows: a last-bit difference in the reduced activations flips a few codes
-            assert err3 < (5e-2 if name == "ds4-style" else 3e-2), (name, err3)
+            assert err3 < 3e-2, (name, err3)
     # ---- EXL3 model, graphs on: GEMV-fused all-reduce in the decode graph; all ranks emit the same tokens
     cfg2 = qwen3next_style(n_layers=4)
     cfg2.moe.n_experts = 32
