@@ -829,7 +829,10 @@ class Model:
         target's: the residual stream stays fp32 on the device and every residual update is one fused
         (all-reduce +) add + RMSNorm."""
         cfg, M, tp = self.cfg, self.W["mtp"], self.tp
-        e = ops.rmsnorm(ops.embed(self.W["embed"], plan.ids, self.dtype), M["norm_e"], cfg.norm_eps)
+        ids = plan.ids
+        if plan.has_media:                       # salted media placeholders of a prompt: the drafter sees token 0 there
+            ids = torch.where(ids >= cfg.vocab, torch.zeros_like(ids), ids)
+        e = ops.rmsnorm(ops.embed(self.W["embed"], ids, self.dtype), M["norm_e"], cfg.norm_eps)
         hh = ops.rmsnorm(hidden if hidden.is_cuda else hidden.to(self.dtype), M["norm_h"], cfg.norm_eps)
         X = ops.linear(torch.cat((e, hh), -1), M["fc"])
         if X.is_cuda:

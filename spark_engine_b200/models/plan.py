@@ -31,6 +31,7 @@ class Plan:
     segs: List[Segment]
     logit_rows: torch.Tensor          # [L] int64 rows whose logits are wanted
     dev: dict = field(default_factory=dict)   # device-side int32 mirrors for the kernels
+    has_media: bool = False                   # some ids are salted media placeholders (outside the vocabulary)
     mm_rows: Optional[list] = None            # multimodal: [(first row, tensor [n, hidden])] written over the embedding
                                               # rows of salted placeholder ids (multimodal/canvas.py)
 

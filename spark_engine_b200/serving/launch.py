@@ -103,18 +103,19 @@ def _engine_main(a):
             W = shard_weights(W, cfg, rank, world)
         W = to_device(W, dev)
     oplog = os.environ.get("SPARK_OPLOG", f"/spark_b200_oplog_{os.getppid()}")
+    vision = _vision_tower(a, cfg)
     if world == 1:
-        EngineServer(cfg, W, ecfg, device=dev).serve_forever(a.socket)
+        EngineServer(cfg, W, ecfg, device=dev, vision=vision).serve_forever(a.socket)
         return 0
     import torch.distributed as dist
     from .replica import Follower, Leader, LeaderLost
     if rank == 0:
         leader = Leader(oplog, world - 1, ack_timeout_ms=a.ack_timeout_ms)
         dist.barrier()
-        EngineServer(cfg, W, ecfg, device=dev, tp=tp, leader=leader).serve_forever(a.socket)
+        EngineServer(cfg, W, ecfg, device=dev, tp=tp, leader=leader, vision=vision).serve_forever(a.socket)
         return 0
     dist.barrier()
-    srv = EngineServer(cfg, W, ecfg, device=dev, tp=tp)
+    srv = EngineServer(cfg, W, ecfg, device=dev, tp=tp, vision=vision)
     print(f"[serve] rank{rank} ready", flush=True)
     try:
         Follower(oplog, rank - 1, world - 1, deadline_ms=a.ack_timeout_ms).run(srv)
@@ -154,14 +155,46 @@ def spawn_ranks(a, env):
     return procs, os.path.join(a.log_dir, "spark-b200-rank0.log")
 
 
+def _vision_config(a, hidden: int):
+    """The vision tower the `--vision` flag names: "tiny" (tests) or "vit-l" (24 x 1024, patch 14), aligned to `hidden`."""
+    from ..multimodal.vision import VisionConfig
+    if not a.vision:
+        return None
+    if a.vision == "tiny":
+        return VisionConfig(depth=2, width=64, heads=4, mlp=128, patch=4, merge=2, out_hidden=hidden, max_side=64)
+    if a.vision == "vit-l":
+        return VisionConfig(out_hidden=hidden)
+    raise SystemExit(f"unknown --vision {a.vision!r} (tiny | vit-l)")
+
+
+def _vision_tower(a, cfg):
+    """(config, weights) of the vision tower: from `<checkpoint>/vision.safetensors` when the checkpoint has one, else
+    random weights of the named architecture (every rank draws the same seed, so all ranks encode identical rows)."""
+    vc = _vision_config(a, cfg.hidden)
+    if vc is None:
+        return None
+    from ..multimodal.vision import init_vision_weights
+    path = os.path.join(a.checkpoint, "vision.safetensors") if a.checkpoint else ""
+    if path and os.path.exists(path):
+        from ..utils.safetensors_io import load_safetensors
+        return vc, load_safetensors(path)
+    return vc, init_vision_weights(vc, seed=a.seed)
+
+
 def cmd_serve(a):
     env = layered_env(a.env_file)
     procs, log = spawn_ranks(a, env)
     front = None
     try:
         _wait_ready(procs, log, a.ready_timeout)
-        front = subprocess.Popen([sys.executable, "-m", "spark_engine_b200.serving.openai_server", "--socket", a.socket,
-                                  "--host", a.host, "--port", str(a.port), "--model-name", a.checkpoint or a.model], env=env)
+        front_cmd = [sys.executable, "-m", "spark_engine_b200.serving.openai_server", "--socket", a.socket,
+                     "--host", a.host, "--port", str(a.port), "--model-name", a.checkpoint or a.model]
+        if a.vision:
+            vc = _vision_config(a, 1)
+            front_cmd += ["--media-canvas", str(a.canvas), "--media-rows", str(vc.rows_for(a.canvas, a.canvas))]
+            if a.allow_media_fetch:
+                front_cmd.append("--allow-media-fetch")
+        front = subprocess.Popen(front_cmd, env=env)
         with open(a.pidfile, "w") as f:
             json.dump({**{f"engine{i}": p.pid for i, p in enumerate(procs)}, "front": front.pid}, f)
         for _ in range(100):
@@ -228,6 +261,9 @@ def main():
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pidfile", default="/tmp/spark-b200.pid")
+    ap.add_argument("--vision", default="", help="tiny | vit-l: serve image / video parts of chat requests through a vision tower")
+    ap.add_argument("--canvas", type=int, default=448, help="side of the square canvas every frame is fitted onto (pixels)")
+    ap.add_argument("--allow-media-fetch", action="store_true", help="let the front end download http(s) media URLs")
     ap.add_argument("--ready-timeout", type=float, default=1200.0)
     a = ap.parse_args()
     a.passthrough = [x for x in sys.argv[2:]]

@@ -68,13 +68,16 @@ class EngineClient:
         with self.lock:
             self.sock.sendall(proto.encode(msg))
 
-    def generate(self, prompt_ids: List[int], max_new: int, stop_ids: List[int], temperature: float, seed: int):
+    def generate(self, prompt_ids: List[int], max_new: int, stop_ids: List[int], temperature: float, seed: int, mm=None):
         with self.lock:
             rid = self.next_id
             self.next_id += 1
             q = self.queues[rid] = queue.Queue()
-        self._send({"id": rid, "prompt_ids": prompt_ids, "max_new": max_new, "stop_token_ids": stop_ids,
-                    "temperature": temperature, "seed": seed})
+        msg = {"id": rid, "prompt_ids": prompt_ids, "max_new": max_new, "stop_token_ids": stop_ids,
+               "temperature": temperature, "seed": seed}
+        if mm:
+            msg["mm"] = mm                      # canvas files + the prompt positions of their salted placeholder runs
+        self._send(msg)
         return rid, q
 
     def cancel(self, rid: int):
@@ -176,18 +179,42 @@ def parse_tool_calls(text: str):
 
 
 class App:
-    def __init__(self, engine: EngineClient, tokenizer, model_name: str, max_new_default: int = 256):
+    def __init__(self, engine: EngineClient, tokenizer, model_name: str, max_new_default: int = 256, media: Optional[dict] = None):
         self.engine, self.tok, self.model_name, self.max_new_default = engine, tokenizer, model_name, max_new_default
         self.metrics = Metrics(model_name)
+        # media: {"height", "width", "rows" (placeholder ids per frame), "dir", "allow_fetch", "video_frames"} when the
+        # engine has a vision tower; None = text only (media parts are refused)
+        self.media = media
 
-    def run(self, prompt_ids: List[int], body: dict, chat: bool, write_event=None, disconnected=None) -> dict:
+    def chat_prompt(self, body: dict):
+        """(prompt ids, mm items) of a chat request: media parts are decoded, fitted onto canvases and replaced by runs
+        of salted placeholder ids (multimodal/media.py, multimodal/canvas.py)."""
+        messages = body.get("messages", [])
+        if not any(isinstance(m.get("content"), list) and any(isinstance(p, dict) and p.get("type", "text") != "text"
+                                                              for p in m["content"]) for m in messages):
+            return self.tok.apply_chat_template(messages, True, body.get("tools")), None
+        from ..multimodal import media as M
+        from .tokenizer import IMAGE_PLACEHOLDER
+        if self.media is None:
+            raise ValueError("this server has no vision tower: media parts are not accepted")
+        tid = getattr(self.tok, "image_token_id", None)
+        if tid is None:
+            raise ValueError("the tokenizer has no media placeholder token")
+        flat, sources = M.split_chat_content(messages, getattr(self.tok, "image_token", IMAGE_PLACEHOLDER))
+        md = self.media
+        items = M.build_items(sources, md["height"], md["width"], md.get("dir", "/dev/shm"), md.get("allow_fetch", False),
+                              md.get("video_frames", 4))
+        ids = self.tok.apply_chat_template(flat, True, body.get("tools"))
+        return M.expand_prompt(list(ids), tid, items, lambda it: md["rows"]), items
+
+    def run(self, prompt_ids: List[int], body: dict, chat: bool, write_event=None, disconnected=None, mm=None) -> dict:
         max_new = int(body.get("max_tokens") or body.get("max_completion_tokens") or self.max_new_default)
         stops = body.get("stop") or []
         stops = [stops] if isinstance(stops, str) else list(stops)
         eos = getattr(self.tok, "eos_token_id", None)
         t0 = time.time()
         rid, q = self.engine.generate(prompt_ids, max_new, [eos] if eos is not None else [], float(body.get("temperature", 0.0) or 0.0),
-                                      int(body.get("seed", 0) or 0))
+                                      int(body.get("seed", 0) or 0), mm=mm)
         detok, ss, rs = IncrementalDetok(self.tok), StopStrings(stops), ReasoningSplit(chat)
         content, reasoning, itls, last_t, done, finish = "", "", [], None, None, "length"
         try:
@@ -279,8 +306,8 @@ def make_handler(app: App):
                 if self.path == "/detokenize":
                     return self._json(200, {"prompt": app.tok.decode(body.get("tokens", []))})
                 if self.path == "/v1/chat/completions":
-                    ids = app.tok.apply_chat_template(body.get("messages", []), True, body.get("tools"))
-                    return self._complete(ids, body, True)
+                    ids, mm = app.chat_prompt(body)
+                    return self._complete(ids, body, True, mm)
                 if self.path == "/v1/completions":
                     p = body.get("prompt", "")
                     ids = p if isinstance(p, list) and p and isinstance(p[0], int) else app.tok.encode(p if isinstance(p, str) else "".join(p))
@@ -294,12 +321,12 @@ def make_handler(app: App):
                 except Exception:
                     pass
 
-        def _complete(self, ids, body, chat):
+        def _complete(self, ids, body, chat, mm=None):
             cid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
             created = int(time.time())
             obj = "chat.completion" if chat else "text_completion"
             if not body.get("stream"):
-                r = app.run(ids, body, chat)
+                r = app.run(ids, body, chat, mm=mm)
                 if chat:
                     text, calls = parse_tool_calls(r["content"])
                     msg = {"role": "assistant", "content": text}
@@ -341,7 +368,7 @@ def make_handler(app: App):
             if chat:
                 chunk(json.dumps({"id": cid, "object": obj + ".chunk", "created": created, "model": app.model_name,
                                   "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}))
-            r = app.run(ids, body, chat, ev, lambda: gone["v"])
+            r = app.run(ids, body, chat, ev, lambda: gone["v"], mm=mm)
             last = {"index": 0, "finish_reason": r["finish"]}
             last["delta" if chat else "text"] = {} if chat else ""
             final = {"id": cid, "object": obj + ".chunk", "created": created, "model": app.model_name, "choices": [last]}
@@ -356,8 +383,9 @@ def make_handler(app: App):
     return H
 
 
-def serve(socket_path: str, host: str, port: int, model_name: str, tokenizer_path: Optional[str] = None):
-    app = App(EngineClient(socket_path), load_tokenizer(tokenizer_path), model_name)
+def serve(socket_path: str, host: str, port: int, model_name: str, tokenizer_path: Optional[str] = None,
+          media: Optional[dict] = None):
+    app = App(EngineClient(socket_path), load_tokenizer(tokenizer_path), model_name, media=media)
     srv = ThreadingHTTPServer((host, port), make_handler(app))
     srv.daemon_threads = True
     return srv, app
@@ -370,8 +398,16 @@ def main():
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--model-name", default="spark")
     ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--media-canvas", type=int, default=0, help="side of the canvas media frames are fitted onto (0 = text only)")
+    ap.add_argument("--media-rows", type=int, default=0, help="placeholder ids per frame (rows the vision tower returns)")
+    ap.add_argument("--media-dir", default="/dev/shm")
+    ap.add_argument("--allow-media-fetch", action="store_true")
     a = ap.parse_args()
-    srv, _ = serve(a.socket, a.host, a.port, a.model_name, a.tokenizer)
+    media = None
+    if a.media_canvas > 0 and a.media_rows > 0:
+        media = {"height": a.media_canvas, "width": a.media_canvas, "rows": a.media_rows, "dir": a.media_dir,
+                 "allow_fetch": a.allow_media_fetch}
+    srv, _ = serve(a.socket, a.host, a.port, a.model_name, a.tokenizer, media)
     print(f"[front] listening on {a.host}:{a.port}", flush=True)
     srv.serve_forever()
 

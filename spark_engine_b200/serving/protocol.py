@@ -42,7 +42,10 @@ def validate_request(msg: Dict[str, Any], vocab: int, max_ctx: int) -> str:
     ids = msg.get("prompt_ids")
     if not isinstance(ids, list) or not ids:
         return "prompt_ids must be a non-empty list"
-    if any((not isinstance(t, int)) or t < 0 or t >= vocab for t in ids):
+    # salted media placeholders (outside every vocabulary) are legal only with an "mm" array, which the engine checks
+    # position by position against its canvases
+    lo, hi = (1 << 20, 1 << 24) if msg.get("mm") else (0, 0)
+    if any((not isinstance(t, int)) or t < 0 or (t >= vocab and not lo <= t < hi) for t in ids):
         return "prompt_ids out of range"
     mn = msg.get("max_new", 256)
     if not isinstance(mn, int) or mn <= 0:

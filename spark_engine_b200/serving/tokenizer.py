@@ -6,9 +6,12 @@ from __future__ import annotations
 from typing import List, Optional
 
 
+IMAGE_PLACEHOLDER = "<|image|>"
+
+
 class ByteTokenizer:
-    bos_token_id, eos_token_id = 256, 257
-    vocab_size = 258
+    bos_token_id, eos_token_id, image_token_id = 256, 257, 258
+    vocab_size = 259
 
     def encode(self, text: str) -> List[int]:
         return list(text.encode("utf-8"))
@@ -28,7 +31,12 @@ class ByteTokenizer:
             parts.append(f"<|{m['role']}|>{c}\n")
         if add_generation_prompt:
             parts.append("<|assistant|>")
-        return [self.bos_token_id] + self.encode("".join(parts))
+        ids = [self.bos_token_id]
+        for k, piece in enumerate("".join(parts).split(IMAGE_PLACEHOLDER)):      # media placeholders become one id each
+            if k:
+                ids.append(self.image_token_id)
+            ids += self.encode(piece)
+        return ids
 
 
 class HfTokenizer:
@@ -37,6 +45,13 @@ class HfTokenizer:
         self.tk = AutoTokenizer.from_pretrained(path)
         self.eos_token_id = self.tk.eos_token_id
         self.vocab_size = len(self.tk)
+        # the placeholder a multimodal checkpoint reserves for media rows, when it has one
+        self.image_token_id = None
+        for name in ("<|image_pad|>", "<image>", "<|image|>", "<|IMAGE|>"):
+            t = self.tk.convert_tokens_to_ids(name)
+            if isinstance(t, int) and t >= 0 and t != self.tk.unk_token_id:
+                self.image_token_id, self.image_token = t, name
+                break
 
     def encode(self, text):
         return self.tk.encode(text, add_special_tokens=False)

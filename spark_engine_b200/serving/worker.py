@@ -38,14 +38,26 @@ class _Live:
         self.seq: Optional[SeqSpec] = None
         self.prefix_hit = 0
         self.sent = 0
+        self.mm: list = []              # parsed media items of the request (multimodal/canvas.py)
+        self.mm_rows: dict = {}         # (item index, frame) -> encoded rows, kept while the prompt is being prefilled
 
 
 class EngineServer:
     def __init__(self, cfg: ModelConfig, W: dict, ecfg: Optional[EngineConfig] = None, device="cpu", tp=None,
-                 leader=None):
-        """`leader`: a `serving.replica.Leader` when other ranks replay this server's inputs and steps."""
+                 leader=None, vision=None):
+        """`leader`: a `serving.replica.Leader` when other ranks replay this server's inputs and steps.
+        `vision`: (VisionConfig, weights) of the vision tower; requests may then carry media ("mm" items: canvas files
+        and the prompt positions of their salted placeholder runs), which are encoded while their chunks are prefilled
+        and written over the embedding rows of those positions.  Every rank encodes the same canvases with the same
+        weights, so followers need no extra traffic."""
         self.cfg, self.ecfg = cfg, ecfg or EngineConfig()
         self.leader = leader
+        self.tower = None
+        if vision is not None:
+            from ..multimodal.vision import VisionTower
+            vcfg, vW = vision
+            assert vcfg.out_hidden == cfg.hidden, "the aligner must project to the model's hidden size"
+            self.tower = VisionTower(vcfg, vW, device=device, dtype=torch.float32 if str(device) == "cpu" else torch.bfloat16)
         e = self.ecfg
         dtype = torch.float32 if str(device) == "cpu" else torch.bfloat16
         per = max(256, e.kv_tokens // e.max_seqs // 256 * 256)
@@ -135,11 +147,24 @@ class EngineServer:
         if err:
             self.out.append({"id": msg.get("id"), "error": err})
             return
+        items = []
+        if msg.get("mm"):
+            from ..multimodal import canvas as mmc
+            try:
+                if self.tower is None:
+                    raise ValueError("this engine has no vision tower")
+                tc = self.tower.c
+                items = mmc.parse_items(msg["mm"], lambda it: tc.rows_for(it.height, it.width))
+                mmc.validate(msg["prompt_ids"], self.cfg.vocab, items)
+            except (ValueError, KeyError, TypeError, OSError) as e:
+                self.out.append({"id": msg.get("id"), "error": f"media: {e}"})
+                return
         R = rt().Request()
         R.id, R.prompt, R.max_new = int(msg["id"]), list(msg["prompt_ids"]), int(msg.get("max_new", 256))
         R.stop = list(msg.get("stop_token_ids", []))
         R.temperature, R.seed, R.t_arrive = float(msg.get("temperature", 0.0)), int(msg.get("seed", 0)), now
         self.live[R.id] = _Live(msg, now)
+        self.live[R.id].mm = items
         self.sched.submit(R)
         self.out.append({"id": R.id, "queued": True})
 
@@ -239,6 +264,13 @@ class EngineServer:
         with self.prof.section("prefill"):
             items = [(slot, lv.msg["prompt_ids"][c0:c1], c0) for (slot, c0, c1), lv in zip(parts, lives)]
             plan = make_plan(items, device=m.device, all_logits=False)
+            for (slot, c0, c1), lv, seg in zip(parts, lives, plan.segs):
+                if lv.mm:
+                    from ..multimodal import canvas as mmc
+                    rows = mmc.chunk_rows(lv.mm, c0, c1 - c0, lambda it, f, lv=lv: self._encode_media(lv, it, f))
+                    plan.mm_rows = (plan.mm_rows or []) + [(seg.r0 + r, t) for r, t in rows]
+                    if c1 == len(lv.msg["prompt_ids"]):
+                        lv.mm_rows.clear()
             logits = m.forward(plan)
             hid = m.hidden_out
             if m.mtp_layers:
@@ -249,14 +281,15 @@ class EngineServer:
                         mtp_items.append((slot, nxt, c0))
                         rows.append(hid[seg.r0: seg.r0 + len(nxt)])
                 if mtp_items:
-                    m.mtp_forward(make_plan(mtp_items, device=m.device, all_logits=False),
-                                  rows[0] if len(rows) == 1 else torch.cat(rows))
+                    mplan = make_plan(mtp_items, device=m.device, all_logits=False)
+                    mplan.has_media = any(lv.mm for lv in lives)
+                    m.mtp_forward(mplan, rows[0] if len(rows) == 1 else torch.cat(rows))
         dt = (time.time() - t0) * 1e3
         self.totals["prefill_steps"] += 1
         self.totals["prefill_shared_steps"] += len(parts) > 1
         for k, ((slot, c0, c1), lv, seg) in enumerate(zip(parts, lives, plan.segs)):
             prompt = lv.msg["prompt_ids"]
-            lv.seq.lookup.extend(prompt[c0:c1])
+            lv.seq.lookup.extend([t for t in prompt[c0:c1] if t < self.cfg.vocab])    # media placeholders are never drafted
             lv.prefill_ms += dt / len(parts)
             self.sched.on_prefilled(slot, c1)
             if c1 == len(prompt):
@@ -273,6 +306,16 @@ class EngineServer:
                 if self.disk is not None and boundary and boundary == len(prompt):
                     self.disk.save(prompt, m.snapshot(slot))
                 self._emit(lv, [first])
+
+    def _encode_media(self, lv: _Live, item, frame: int) -> torch.Tensor:
+        """Rows of one canvas frame; a segment that straddles prefill chunks is encoded once."""
+        key = (id(item), frame)
+        if key not in lv.mm_rows:
+            from ..multimodal import canvas as mmc
+            with self.prof.section("vision"):
+                lv.mm_rows[key] = self.tower.encode(mmc.load_frame(item, frame))
+            self.totals["media_frames"] = self.totals.get("media_frames", 0) + 1
+        return lv.mm_rows[key]
 
     def _emit(self, lv: _Live, toks: List[int]):
         msg = lv.msg
