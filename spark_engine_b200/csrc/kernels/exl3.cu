@@ -32,6 +32,44 @@ __global__ void exl3_reconstruct_kernel(const uint32_t* __restrict__ trellis, __
   dst1[r0 >> 1] = w[2]; dst1[(r0 + 8) >> 1] = w[3];
 }
 
+// Any bit width (2..8 bits/weight: checkpoints mix 3 to 6 bits per tensor, heads often 6): a tile is 8 * bits words;
+// the state of stream position t is the 16 bits that start at bit ((t + 1) * bits - 16) of the tail-biting ring, read
+// MSB-first over little-endian 32-bit words.  Lane l still decodes positions 8l .. 8l+7, so the fragment assembly
+// and the store pattern are those of the 4-bit kernel; only the window extraction reads its two words per state
+// from memory (L1) instead of from the lane's own register.
+template <int CB>
+__global__ void exl3_reconstruct_bits_kernel(const uint32_t* __restrict__ trellis, __half* __restrict__ Wt, int K, int N,
+                                             int E, int bits) {
+  const int KT = K >> 4, NT = N >> 4;
+  const long long per = static_cast<long long>(KT) * NT;
+  long long tile = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (tile >= per * E) return;
+  const int lane = threadIdx.x & 31;
+  const int n_words = 8 * bits, n_bits = 256 * bits;
+  const uint32_t* tw = trellis + tile * n_words;
+  uint32_t st[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    int first = (8 * lane + j + 1) * bits - 16;
+    if (first < 0) first += n_bits;
+    const int wi = first >> 5, off = first & 31;
+    const uint32_t hi = __ldg(tw + wi), lo = __ldg(tw + (wi + 1 == n_words ? 0 : wi + 1));
+    st[j] = __funnelshift_l(lo, hi, off) >> 16;
+  }
+  const long long e = tile / per;
+  tile -= e * per;
+  Wt += e * static_cast<long long>(N) * K;
+  const int kt = static_cast<int>(tile / NT), nt = static_cast<int>(tile % NT);
+  uint32_t w[4];
+  w[0] = exl3_pair<CB>(st[0], st[1]); w[1] = exl3_pair<CB>(st[2], st[3]);
+  w[2] = exl3_pair<CB>(st[4], st[5]); w[3] = exl3_pair<CB>(st[6], st[7]);
+  const int r0 = (lane & 3) * 2, c0 = lane >> 2;
+  uint32_t* dst0 = reinterpret_cast<uint32_t*>(Wt + static_cast<size_t>(nt * 16 + c0) * K + kt * 16);
+  uint32_t* dst1 = reinterpret_cast<uint32_t*>(Wt + static_cast<size_t>(nt * 16 + c0 + 8) * K + kt * 16);
+  dst0[r0 >> 1] = w[0]; dst0[(r0 + 8) >> 1] = w[1];
+  dst1[r0 >> 1] = w[2]; dst1[(r0 + 8) >> 1] = w[3];
+}
+
 // y[r, :] = had128(x[r, :] * scale[:]) (pre) or had128(x[r, :]) * scale[:] (post); 128-blocks along the row.
 // One warp per 128-block: a lane keeps 4 consecutive elements (one 8- or 16-byte load), the strides 1 and 2 of the
 // butterfly run in registers and the strides 4..64 through five shuffles -- the same additions in the same order as a
@@ -110,6 +148,17 @@ extern "C" int spark_exl3_reconstruct(const void* trellis, void* Wt, int K, int 
   const unsigned blocks = (unsigned)((tiles * 32 + 255) / 256);
   if (codebook == 0) exl3_reconstruct_kernel<0><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
   else exl3_reconstruct_kernel<1><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E);
+  return spark_launch_rc(__func__);
+}
+
+// The same for any bit width 2..8 (trellis [E][K/16][N/16][8 * bits words]).
+extern "C" int spark_exl3_reconstruct_bits(const void* trellis, void* Wt, int K, int N, int codebook, cudaStream_t s, int E,
+                                           int bits) {
+  if (bits < 2 || bits > 8 || (K & 15) || (N & 15) || E < 1) return -5;
+  const long long tiles = (long long)(K >> 4) * (N >> 4) * E;
+  const unsigned blocks = (unsigned)((tiles * 32 + 255) / 256);
+  if (codebook == 0) exl3_reconstruct_bits_kernel<0><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E, bits);
+  else exl3_reconstruct_bits_kernel<1><<<blocks, 256, 0, s>>>((const uint32_t*)trellis, (__half*)Wt, K, N, E, bits);
   return spark_launch_rc(__func__);
 }
 

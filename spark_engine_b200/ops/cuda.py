@@ -72,6 +72,7 @@ _SIGS = {
     "spark_exl3_gemv": [vp, i32, vp, vp, vp, i64, i64, i64, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
                         f32, i32, vp, vp, i32],
     "spark_exl3_reconstruct": [vp, vp, i32, i32, i32, vp, i32],
+    "spark_exl3_reconstruct_bits": [vp, vp, i32, i32, i32, vp, i32, i32],
     "spark_exl3_had_rows": [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, i64],
 }
 
@@ -324,6 +325,10 @@ def exl3_reconstruct(w: Exl3Weight, out: Optional[torch.Tensor] = None) -> torch
     E = w.trellis.shape[0] if w.experts else 1
     if out is None:
         out = torch.empty((E, w.n, w.k) if w.experts else (w.n, w.k), dtype=torch.float16, device=w.trellis.device)
+    if w.bits != 4:
+        rc = lib().spark_exl3_reconstruct_bits(P(w.trellis), P(out), w.k, w.n, 0 if w.kind == "mul1" else 1, stream(), E, w.bits)
+        check(rc, "spark_exl3_reconstruct_bits")
+        return out
     rc = lib().spark_exl3_reconstruct(P(w.trellis), P(out), w.k, w.n, 0 if w.kind == "mul1" else 1, stream(), E)
     check(rc, "spark_exl3_reconstruct")
     return out
@@ -364,12 +369,33 @@ def exl3_mgemm(xh, w: Exl3Weight, tiles, ntile, max_tiles, out_f32=False, rows_p
     return y
 
 
+EXL3_RESIDENT_MAX_BYTES = int(os.environ.get("SPARK_EXL3_RESIDENT_MB", "4096")) << 20
+_exl3_resident_bytes = 0
+
+
+def _exl3_resident(w: Exl3Weight) -> Optional[torch.Tensor]:
+    """fp16 inner weights of a tensor whose bit width has no GEMV kernel (everything but 4 bpw), decoded once and kept
+    for decode rows, within a byte budget (a 6 bpw head of 152K x 2048 is 622 MB)."""
+    global _exl3_resident_bytes
+    t = getattr(w, "_inner_fp16", None)
+    if t is None:
+        need = w.n * w.k * 2
+        if _exl3_resident_bytes + need > EXL3_RESIDENT_MAX_BYTES:
+            return None
+        t = exl3_reconstruct(w)
+        w._inner_fp16 = t
+        _exl3_resident_bytes += need
+    return t
+
+
 def exl3_linear(x, w: Exl3Weight):
     x = _as_bf16(x).contiguous()
-    if x.shape[0] <= 16:
+    if x.shape[0] <= 16 and w.bits == 4:
         return exl3_gemv(x, w)
     xh = exl3_had_rows(x, w.suh, post=False)
-    wt = exl3_reconstruct(w, scratch("exl3_recon", w.n * w.k, torch.float16, x.device)[: w.n * w.k].view(w.n, w.k))
+    wt = _exl3_resident(w) if (x.shape[0] <= 16 and not w.experts) else None
+    if wt is None:
+        wt = exl3_reconstruct(w, scratch("exl3_recon", w.n * w.k, torch.float16, x.device)[: w.n * w.k].view(w.n, w.k))
     acc = gemm_bf16(xh, wt, out_f32=True, fmt=0)
     return exl3_had_rows(acc, w.svh, post=True)
 
@@ -669,6 +695,8 @@ def _shared_expert_decode(h, w, c):
     """The shared expert's two GEMVs for decode rows (when it is not a pair of the stack)."""
     sgu = w["s_gu"]
     if isinstance(sgu, Exl3Weight):
+        if sgu.bits != 4 or w["s_down"].bits != 4:       # bit widths without a GEMV kernel: resident fp16 inner weights
+            return exl3_linear(swiglu(exl3_linear(h, sgu), c.swiglu_limit), w["s_down"])
         return exl3_gemv(exl3_gemv(h, sgu), w["s_down"], act=1, limit=c.swiglu_limit)
     if isinstance(sgu, QuantWeight):
         return quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
@@ -752,8 +780,11 @@ def moe(h, w, c, defer: bool = False):
                 side.wait_stream(main)
             with torch.cuda.stream(side if side is not None else main):
                 if isinstance(sgu, Exl3Weight):
-                    gu_s = exl3_gemv(h, sgu)
-                    shared = exl3_gemv(gu_s, w["s_down"], act=1, limit=c.swiglu_limit)
+                    if sgu.bits != 4 or w["s_down"].bits != 4:
+                        shared = exl3_linear(swiglu(exl3_linear(h, sgu), c.swiglu_limit), w["s_down"])
+                    else:
+                        gu_s = exl3_gemv(h, sgu)
+                        shared = exl3_gemv(gu_s, w["s_down"], act=1, limit=c.swiglu_limit)
                 elif isinstance(sgu, QuantWeight):
                     shared = quant_linear(swiglu(quant_linear(h, sgu), c.swiglu_limit), w["s_down"])
                 else:

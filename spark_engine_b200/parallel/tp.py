@@ -253,7 +253,7 @@ class DeviceTP(TPBase):
 
     def can_fuse_gemv(self, x, w) -> bool:
         from ..quant.formats import Exl3Weight
-        return isinstance(w, Exl3Weight) and not w.experts and x.shape[0] <= 16 and x.is_cuda
+        return isinstance(w, Exl3Weight) and not w.experts and w.bits == 4 and x.shape[0] <= 16 and x.is_cuda
 
     def reduce(self, delta) -> torch.Tensor:
         if isinstance(delta, ops.Partial):

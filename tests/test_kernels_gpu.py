@@ -147,6 +147,36 @@ def test_exl3_reconstruct_is_bit_exact(kind):
     assert torch.equal(got, ref.t())
 
 
+@pytest.mark.parametrize("bits", [2, 3, 5, 6, 8])
+@pytest.mark.parametrize("kind", ["mul1", "mcg"])
+def test_exl3_reconstruct_other_bit_widths_is_bit_exact(bits, kind):
+    """Checkpoints mix 3 to 6 bits per tensor: the window extraction for any width against the codec, single tensors
+    and an expert stack."""
+    w = Q.random_exl3(256, 384, bits=bits, seed=3 + bits, kind=kind)
+    assert w.trellis.shape[-1] == 16 * bits
+    got = cu().exl3_reconstruct(w.to(DEV)).float().cpu()
+    assert torch.equal(got, Q.exl3_inner(w.trellis, kind).t())
+    we = Q.random_exl3(128, 256, bits=bits, experts=3, seed=bits, kind=kind)
+    gote = cu().exl3_reconstruct(we.to(DEV)).float().cpu()
+    for e in range(3):
+        assert torch.equal(gote[e], Q.exl3_inner(we.trellis[e], kind).t())
+
+
+@pytest.mark.parametrize("bits", [3, 6])
+@pytest.mark.parametrize("R", [2, 40])
+def test_exl3_linear_other_bit_widths(bits, R):
+    """Decode rows and prefill rows through a 3- and a 6-bit tensor (Hadamard rows, decoded inner weights, tcgen05 GEMM)."""
+    from spark_engine_b200 import ops
+    w = Q.random_exl3(512, 1024, bits=bits, seed=11, std=0.05)
+    g = torch.Generator(device=DEV).manual_seed(8)
+    x = torch.randn(R, 1024, device=DEV, generator=g).bfloat16()
+    wd = w.to(DEV)
+    y = ops.linear(x, wd).float().cpu()
+    ref = x.float().cpu() @ w.dequant().t()
+    assert rel_err(y, ref) < 6e-3
+    assert torch.equal(ops.linear(x, wd), ops.linear(x, wd))
+
+
 @pytest.mark.parametrize("R", [1, 4, 16])
 @pytest.mark.parametrize("N,K", [(256, 512), (1024, 2048), (2048, 512)])
 def test_exl3_gemv_matches_dequant_matmul(R, N, K):
