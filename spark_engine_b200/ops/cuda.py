@@ -127,6 +127,8 @@ def lib():
                 f"{LIB_PATH} is missing: run `python -m spark_engine_b200.build` (the CUDA kernels are required "
                 "on a GPU; there is no silent eager fallback)")
         dll = C.CDLL(LIB_PATH)
+        from ..utils import precision
+        precision.ensure()                  # library GEMMs that remain on the path: fp32 accumulation, TF32 only by flag
         _LIB = _Counting(dll)
         for name, sig in _SIGS.items():
             fn = getattr(dll, name, None)

@@ -84,3 +84,25 @@ def test_memory_guard_refuses_requests_while_host_memory_is_low(tmp_path):
     es.submit({"id": 3, "prompt_ids": [1, 2, 3], "max_new": 2})
     assert es.out[-1].get("queued")
     del es.memwatch
+
+
+def test_package_cli_dispatch_and_precision_flags():
+    """`python -m spark_engine_b200 <command>`: version, presets, an unknown command, a launcher command; library GEMMs are
+    set to fp32 accumulation without reduced-precision reductions."""
+    import json
+    import subprocess
+    import sys
+    import torch
+    from spark_engine_b200.utils import precision
+    run = lambda *a: subprocess.run([sys.executable, "-m", "spark_engine_b200", *a], capture_output=True, text=True, timeout=120)
+    assert run("version").stdout.strip()
+    cfgs = json.loads(run("configs").stdout)
+    assert {"qwen3next-style", "glm-style", "ds4-style"} <= set(cfgs) and cfgs["qwen3next-style"]["n_layers"] == 48
+    assert run("nope").returncode == 2
+    assert "not running" in run("status", "--pidfile", "/tmp/spark-b200-no-such.pid").stdout
+    flags = precision.set_fp32_accum(tf32=False)
+    assert flags == {"bf16_reduced_precision_reduction": False, "fp16_reduced_precision_reduction": False, "tf32": False}
+    assert torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction is False
+    assert torch.backends.cuda.matmul.allow_tf32 is False
+    assert precision.set_fp32_accum(tf32=True)["tf32"] and torch.backends.cuda.matmul.allow_tf32 is True
+    precision.set_fp32_accum(tf32=False)
