@@ -248,6 +248,7 @@ class EngineConfig:
     host: str = "127.0.0.1"
     port: int = 8000
     profile: bool = False
+    prewarm: bool = False         # run synthetic requests for 1..max_seqs streams before serving (captures the graphs)
     nvtx: bool = False
     log_rounds: bool = False
     seed: int = 0

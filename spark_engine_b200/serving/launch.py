@@ -67,7 +67,7 @@ def _engine_main(a):
         cfg.layer_types = cfg.layer_types[: a.layers]
     ecfg = EngineConfig.from_env(max_seqs=a.max_seqs, kv_tokens=a.kv_tokens, prefill_chunk=a.prefill_chunk, spec=a.spec,
                                  spec_depth=a.spec_depth, pcache_dir=a.pcache_dir, socket=a.socket, profile=a.profile,
-                                 tp=world)
+                                 tp=world, prewarm=a.prewarm)
     tp = None
     if dev != "cpu":
         torch.cuda.set_device(local)
@@ -116,6 +116,8 @@ def _engine_main(a):
         return 0
     dist.barrier()
     srv = EngineServer(cfg, W, ecfg, device=dev, tp=tp, vision=vision)
+    if ecfg.prewarm:
+        srv.prewarm()                          # the leader runs the same synthetic requests before it serves
     print(f"[serve] rank{rank} ready", flush=True)
     try:
         Follower(oplog, rank - 1, world - 1, deadline_ms=a.ack_timeout_ms).run(srv)
@@ -261,6 +263,7 @@ def main():
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--pidfile", default="/tmp/spark-b200.pid")
+    ap.add_argument("--prewarm", action="store_true", help="capture the graphs of 1..max-seqs streams before serving")
     ap.add_argument("--vision", default="", help="tiny | vit-l: serve image / video parts of chat requests through a vision tower")
     ap.add_argument("--canvas", type=int, default=448, help="side of the square canvas every frame is fitted onto (pixels)")
     ap.add_argument("--allow-media-fetch", action="store_true", help="let the front end download http(s) media URLs")

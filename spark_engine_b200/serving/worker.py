@@ -385,7 +385,39 @@ class EngineServer:
         self.live.pop(lv.id, None)
 
     # ------------------------------------------------------------------------------------------ socket loop
+    def prewarm(self, prompt_tokens: int = 24) -> int:
+        """Synthetic requests for 1 .. max_seqs concurrent streams through the normal admit / prefill / round path, so
+        that the decode, verify, drafter and commit graphs of those stream counts are captured (and every scratch buffer
+        sized) before the first client arrives.  Every rank calls this on its own before it serves: the requests are
+        deterministic, so the ranks of a sharded model run identical steps.  Outputs and counters are discarded.
+        Reference: engine-rs/src/spec_probe.rs:2215-2311 (graph prewarm, vision warm-up).  Returns the steps run."""
+        saved_totals, saved_leader, saved_disk = dict(self.totals), self.leader, self.disk
+        self.leader = self.disk = None          # nothing is replicated or written to the prefix cache
+        steps, rid = 0, -(1 << 30)
+        try:
+            for n in range(1, self.ecfg.max_seqs + 1):
+                for i in range(n):
+                    rid += 1
+                    prompt = [(17 * n + 5 * i + 3 * j + 1) % min(self.cfg.vocab, 30000) for j in range(prompt_tokens)]
+                    self.submit({"id": rid, "prompt_ids": prompt, "max_new": max(4, 2 * (self.ecfg.spec_depth + 1)),
+                                 "temperature": 0.0}, replay=True)
+                guard = 0
+                while self.sched.has_work() and guard < 10000:
+                    self.step(replay=True)
+                    steps += 1
+                    guard += 1
+                self.out = []
+        finally:
+            self.leader, self.disk = saved_leader, saved_disk
+            self.totals = saved_totals
+            self.out = []
+        return steps
+
     def serve_forever(self, path: str, idle_sleep: float = 0.002, ready_cb=None):
+        if self.ecfg.prewarm:
+            t0 = time.time()
+            n = self.prewarm()
+            print(f"[serve] prewarm: {n} steps in {time.time() - t0:.1f} s", flush=True)
         if os.path.exists(path):
             os.unlink(path)
         srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)

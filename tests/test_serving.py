@@ -17,13 +17,14 @@ from spark_engine_b200.serving.openai_server import ReasoningSplit, StopStrings,
 from spark_engine_b200.serving.worker import EngineServer
 
 
-def _start(tmp_path, spec="mtp", pcache=None, tree=""):
+def _start(tmp_path, spec="mtp", pcache=None, tree="", prewarm=False):
     cfg = tiny_hybrid()
     cfg.mtp_layers = 1
     W = init_weights(cfg, seed=0)
     sock = str(tmp_path / "e.sock")
     es = EngineServer(cfg, W, EngineConfig(max_seqs=2, kv_tokens=2048, prefill_chunk=32, spec=spec, spec_depth=2,
-                                           spec_tree_widths=tree, pcache_dir=pcache, pcache_bytes=64 << 20, profile=True))
+                                           spec_tree_widths=tree, pcache_dir=pcache, pcache_bytes=64 << 20, profile=True,
+                                           prewarm=prewarm))
     ready = threading.Event()
     th = threading.Thread(target=es.serve_forever, args=(sock,), kwargs={"ready_cb": ready.set}, daemon=True)
     th.start()
@@ -182,5 +183,26 @@ def test_server_with_the_other_drafters_still_serves_greedy_text(tmp_path, spec)
     done, _ = _collect(c, buf, [1])
     assert done[1]["token_ids"] == ref
     assert done[1]["drafted_tokens"] >= 0
+    c.sendall(proto.encode({"shutdown": True}))
+    th.join(10)
+
+
+def test_prewarmed_server_serves_the_same_tokens_and_starts_with_clean_counters(tmp_path):
+    """Prewarm runs synthetic requests for 1..max_seqs streams before the socket opens: afterwards the counters are
+    those of a fresh server, nothing was written to the prefix cache, and real requests get plain greedy text."""
+    cfg, W, es, sock, th = _start(tmp_path, prewarm=True, pcache=str(tmp_path / "pc"))
+    assert es.totals["requests"] == 0 and es.totals["prompt_tokens"] == 0 and es.totals["prefill_steps"] == 0
+    assert es.disk is not None and es.disk.stats().get("saves", 0) == 0
+    assert not es.sched.has_work() and es.out == []
+    g = torch.Generator().manual_seed(3)
+    p1 = torch.randint(0, cfg.vocab, (33,), generator=g).tolist()
+    p2 = torch.randint(0, cfg.vocab, (21,), generator=g).tolist()
+    ref1 = oracle.greedy_generate(cfg, W, torch.tensor(p1), 8)[0].tolist()
+    ref2 = oracle.greedy_generate(cfg, W, torch.tensor(p2), 5)[0].tolist()
+    c, buf = _client(sock)
+    c.sendall(proto.encode({"id": 1, "prompt_ids": p1, "max_new": 8}) + proto.encode({"id": 2, "prompt_ids": p2, "max_new": 5}))
+    done, _ = _collect(c, buf, [1, 2])
+    assert done[1]["token_ids"] == ref1 and done[2]["token_ids"] == ref2
+    assert es.totals["requests"] == 2
     c.sendall(proto.encode({"shutdown": True}))
     th.join(10)
