@@ -159,7 +159,7 @@ __device__ __forceinline__ void gemv_mma16816(float (&c)[4], uint32_t a0, uint32
 // rows, its 8 warps split K and their partial tiles are summed in warp order through shared memory (projections of
 // a few thousand rows, where one warp per 16 rows would leave most SMs idle).
 template <int NT, typename TO, bool KS>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+__global__ void __launch_bounds__(GEMV_WARPS * 32, NT == 1 ? 3 : 2)      // <= 85 registers: three CTAs of loads in flight per SM
 gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw,
                      TO* __restrict__ y, int ldy, int R, int N, int K, int cpc) {
   extern __shared__ __align__(16) uint8_t smem_gemv[];
@@ -170,7 +170,7 @@ gemv_wide_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bf
   const int KC = K >> 5;                                 // 32-wide k chunks
   const int per = (KC + GEMV_WARPS - 1) / GEMV_WARPS;
   const int kb = KS ? min(KC, warp * per) : 0, ke = KS ? min(KC, kb + per) : KC;    // this warp's chunks
-  constexpr int BATCH = 8;                               // chunks in flight per lane and weight row
+  constexpr int BATCH = NT == 1 ? 6 : 8;                 // chunks in flight per lane and weight row (fits the register budget)
   uint4 ra[BATCH], rb[BATCH];
   auto rows_of = [&](int cg, const uint4*& w0, const uint4*& w1) -> int {
     const int n0 = KS ? blockIdx.x * 16 : ((blockIdx.x * cpc + cg) * GEMV_WARPS + warp) * 16;
