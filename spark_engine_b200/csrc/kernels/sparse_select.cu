@@ -62,9 +62,11 @@ __device__ __forceinline__ void is_mma(float (&c)[4], const uint32_t (&a)[4], ui
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (ceil(max segment rows / (64 / H)), segments); 128 threads.  H in {1, 2, 4, ..., 64}, Dm % 8 == 0, Dm <= 128.
+// grid (ceil(max segment rows / (64 / H)), segments); 256 threads: warps w and w + 4 share the 16 (row, head) pairs of
+// M tile w & 3 and take four of the eight 8-block column tiles each (shared memory allows one CTA per SM, so the
+// second set of warps is what hides the fragment-load latency).  H in {1, 2, 4, ..., 64}, Dm % 8 == 0, Dm <= 128.
 // seg: int [nseg][4] = slot, first row, rows, first position.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* __restrict__ pool,
                      const long long* __restrict__ row_kv, const int* __restrict__ seg, int block,
                      const float* __restrict__ head_w, float scale, float* __restrict__ score, int ld) {
@@ -84,14 +86,14 @@ idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* _
   const float* kbase = pool + (row_kv[r0] / block) * Dm;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int VPR = Dm >> 2;                                           // 16-byte vectors per row
-  for (int i = tid; i < IS_M * VPR; i += 128) {
+  for (int i = tid; i < IS_M * VPR; i += 256) {
     const int m = i / VPR, v = i - m * VPR;
     const int mm = min(m, rows_valid * H - 1);                       // padded (row, head) pairs repeat the last valid one
     is_cp16(Qs + m * LQ + v * 4, qi + (static_cast<size_t>(r0 + q0) * H + mm) * Dm + v * 4);
   }
   auto load_k = [&](int j, int buf) {
     float* kd = Ks + buf * IS_N * LQ;
-    for (int i = tid; i < IS_N * VPR; i += 128) {
+    for (int i = tid; i < IS_N * VPR; i += 256) {
       const int r = i / VPR, v = i - r * VPR;
       const int b = j * IS_N + r;
       if (b < nb) is_cp16(kd + r * LQ + v * 4, kbase + static_cast<size_t>(b) * Dm + v * 4);
@@ -101,7 +103,7 @@ idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* _
   load_k(0, 0);
   asm volatile("cp.async.commit_group;" ::: "memory");
   // weights of this thread's two (row, head) pairs: accumulator rows g and g + 8 of the warp's 16
-  const int m_lo = warp * 16 + g, m_hi = m_lo + 8;
+  const int m_lo = (warp & 3) * 16 + g, m_hi = m_lo + 8, nt0 = (warp >> 2) * 4;
   const int mv_lo = min(m_lo, rows_valid * H - 1), mv_hi = min(m_hi, rows_valid * H - 1);
   const float w_lo = scale * (head_w ? head_w[static_cast<size_t>(r0 + q0) * H + mv_lo] : 1.f);
   const float w_hi = scale * (head_w ? head_w[static_cast<size_t>(r0 + q0) * H + mv_hi] : 1.f);
@@ -111,9 +113,9 @@ idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* _
     __syncthreads();                                                 // tile j landed; Ss of tile j-1 has been read
     if (j + 1 < ntiles) { load_k(j + 1, buf ^ 1); asm volatile("cp.async.commit_group;" ::: "memory"); }
     const float* kb = Ks + buf * IS_N * LQ;
-    float s[8][4];
+    float s[4][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+    for (int i = 0; i < 4; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
     for (int ks = 0; ks < Dm / 8; ++ks) {
       uint32_t ah[4], al[4];
       is_split(Qs[m_lo * LQ + ks * 8 + t], ah[0], al[0]);
@@ -121,23 +123,23 @@ idx_score_mma_kernel(const float* __restrict__ qi, int H, int Dm, const float* _
       is_split(Qs[m_lo * LQ + ks * 8 + t + 4], ah[2], al[2]);
       is_split(Qs[m_hi * LQ + ks * 8 + t + 4], ah[3], al[3]);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
         uint32_t bh0, bl0, bh1, bl1;
-        is_split(kb[(nt * 8 + g) * LQ + ks * 8 + t], bh0, bl0);
-        is_split(kb[(nt * 8 + g) * LQ + ks * 8 + t + 4], bh1, bl1);
+        is_split(kb[((nt0 + nt) * 8 + g) * LQ + ks * 8 + t], bh0, bl0);
+        is_split(kb[((nt0 + nt) * 8 + g) * LQ + ks * 8 + t + 4], bh1, bl1);
         is_mma(s[nt], al, bh0, bh1);                                 // small terms first
         is_mma(s[nt], ah, bl0, bl1);
         is_mma(s[nt], ah, bh0, bh1);
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int c = nt * 8 + 2 * t;
+    for (int nt = 0; nt < 4; ++nt) {
+      const int c = (nt0 + nt) * 8 + 2 * t;
       Ss[m_lo * 65 + c] = fmaxf(s[nt][0], 0.f) * w_lo; Ss[m_lo * 65 + c + 1] = fmaxf(s[nt][1], 0.f) * w_lo;
       Ss[m_hi * 65 + c] = fmaxf(s[nt][2], 0.f) * w_hi; Ss[m_hi * 65 + c + 1] = fmaxf(s[nt][3], 0.f) * w_hi;
     }
     __syncthreads();
-    for (int i = tid; i < rows_valid * IS_N; i += 128) {
+    for (int i = tid; i < rows_valid * IS_N; i += 256) {
       const int rq = i >> 6, c = i & 63, b = j * IS_N + c;
       if (b >= nb) continue;
       float acc = 0.f;
@@ -477,7 +479,7 @@ extern "C" int spark_idx_score_mma(const float* qi, int H, int Dm, const float* 
   static bool done = false;
   if (!done) { cudaFuncSetAttribute(idx_score_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); done = true; }
   const int rpc = 64 / H;
-  idx_score_mma_kernel<<<dim3((max_rows + rpc - 1) / rpc, nseg), 128, smem, s>>>(qi, H, Dm, pool, row_kv, seg, block, head_w, scale,
+  idx_score_mma_kernel<<<dim3((max_rows + rpc - 1) / rpc, nseg), 256, smem, s>>>(qi, H, Dm, pool, row_kv, seg, block, head_w, scale,
                                                                                 score, ld);
   return spark_launch_rc(__func__);
 }
