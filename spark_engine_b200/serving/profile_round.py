@@ -20,6 +20,8 @@ def run(a):
     from ..models.build import build_random_model
     from .engine import LLMEngine
     cfg = get_model_config(a.model, n_layers=a.layers)
+    if a.hc:
+        cfg.hc_kind, cfg.hc_streams, cfg.hc_rank = a.hc, 4, 32
     W = build_random_model(cfg, "cuda", 0)
     eng = LLMEngine(cfg, W, EngineConfig(cuda_graphs=False), max_seqs=a.streams, kv_tokens_per_seq=max(4096, 2 * a.prompt))
     g = torch.Generator().manual_seed(0)
@@ -71,6 +73,7 @@ def main():
     ap.add_argument("--streams", type=int, default=4)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--prefill", type=int, default=0, help="profile two prefill chunks of this many tokens instead of decode rounds")
+    ap.add_argument("--hc", default="", help="gated | mhc: 4 hyper-connection residual streams")
     ap.add_argument("--summary", default="")
     a = ap.parse_args()
     if a.summary:
