@@ -23,7 +23,7 @@ namespace spark {
 
 constexpr int HC_S = 4;                 // streams
 constexpr int HC_NL = 2 * HC_S + HC_S * HC_S;
-constexpr int HC_THREADS = 256;
+constexpr int HC_THREADS = 128;
 constexpr int HC_DC = HC_THREADS * 4;   // columns of D per CTA
 constexpr int HC_ZG = 3;                // CTAs that share one chunk of a row, each owning HC_NL / HC_ZG logits
 constexpr int HC_LG = HC_NL / HC_ZG;    // logits per CTA
