@@ -82,7 +82,9 @@ class VisionTower:
         self.W = to_device(W, device, dtype) if str(device) != "cpu" else W
 
     def _lin(self, x, w, b=None):
-        y = ops.linear(x.to(self.dtype), w).to(self.dtype)
+        # plain library GEMMs, as the reference's towers (vision.rs: libtorch ops): patch and merge widths (3 * 14 * 14 =
+        # 588, ...) do not meet the alignment rules of the language model's kernels, and a tower runs once per frame
+        y = F.linear(x.to(self.dtype), w.to(self.dtype))
         return y if b is None else y + b.to(y.dtype)
 
     @torch.no_grad()
