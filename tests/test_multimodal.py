@@ -269,3 +269,35 @@ def test_chat_request_with_an_image_is_served_through_the_vision_tower(tmp_path)
         srv.shutdown()
         es.shutdown = True
         th.join(10)
+
+
+@pytest.mark.gpu
+def test_vision_tower_and_row_injection_on_the_device(tmp_path):
+    """The tower in bf16 on the GPU (patch 4 and patch 14: widths that are not multiples of 8) against the fp32 CPU tower,
+    and a prompt with injected media rows through the device model against the CPU runner."""
+    from spark_engine_b200.config import tiny_hybrid
+    from spark_engine_b200.models.model import Model
+    from spark_engine_b200.models.plan import make_plan
+    from spark_engine_b200.models.weights import init_weights, to_device
+    cfg = tiny_hybrid()
+    W = init_weights(cfg, seed=0)
+    for vc in (VisionConfig(depth=1, width=32, heads=2, mlp=64, patch=4, merge=2, out_hidden=cfg.hidden, max_side=16),
+               VisionConfig(depth=2, width=64, heads=4, mlp=128, patch=14, merge=2, out_hidden=cfg.hidden, max_side=16)):
+        vW = init_vision_weights(vc, 3)
+        side = vc.patch * vc.merge * 4
+        item = C.parse_items([dict(C.write_canvas([_img(side, side, 1)], side, side, str(tmp_path)),
+                                   segments=[[3, vc.rows_for(side, side), 0]])], lambda it: vc.rows_for(it.height, it.width))[0]
+        rc = VisionTower(vc, vW).encode(C.load_frame(item, 0))
+        rg = VisionTower(vc, vW, device="cuda", dtype=torch.bfloat16).encode(C.load_frame(item, 0)).float().cpu()
+        assert rg.shape == rc.shape and ((rg - rc).norm() / rc.norm()).item() < 3e-2
+    n = rc.shape[0]
+    ids = [1, 2, 3] + C.salted_ids(b"x", n) + [4, 5]
+    outs = []
+    for dev in ("cpu", "cuda"):
+        m = Model(cfg, W if dev == "cpu" else to_device(W, dev), device=dev,
+                  dtype=torch.float32 if dev == "cpu" else torch.bfloat16, n_slots=1, kv_tokens=256)
+        plan = make_plan([(0, ids, 0)], device=dev)
+        plan.mm_rows = [(3, rc)]
+        outs.append(m.forward(plan).float().cpu())
+    assert torch.isfinite(outs[1]).all()
+    assert ((outs[1] - outs[0]).norm() / outs[0].norm()).item() < 5e-2
