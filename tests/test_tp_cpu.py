@@ -93,3 +93,52 @@ def test_tp2_logits_match_unsharded(name):
     want = ref_m.sample_rows(ref, [0.0 if r % 3 == 0 else 0.9 for r in range(R)], [7] * R, list(range(R)))
     assert sampled == want
     assert abs(prob - float(torch.softmax(ref[0], -1)[want[0]])) < 1e-5
+
+
+def _worker_many(rank, world, port, q, name):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from spark_engine_b200.config import EngineConfig
+    from spark_engine_b200.models.weights import init_weights
+    from spark_engine_b200.parallel.tp import CpuTP, shard_dense_weights
+    from spark_engine_b200.serving.engine import LLMEngine
+    cfg = _config(name)
+    W = init_weights(cfg, seed=0)
+    eng = LLMEngine(cfg, shard_dense_weights(W, cfg, rank, world), EngineConfig(cuda_graphs=False, prefill_chunk=24),
+                    device="cpu", max_seqs=3, kv_tokens_per_seq=128, tp=CpuTP())
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (29, 7, 40)]
+    lg = eng.prefill_many([0, 1, 2], prompts)
+    toks = eng.model.greedy(lg).tolist()
+    nxt = eng.decode_round([0, 1, 2], toks)
+    if rank == 0:
+        q.put((toks, nxt))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["tiny", "glm-style"])
+def test_tp2_shared_prefill_of_several_sequences_matches_unsharded(name):
+    """Several ragged prompts prefilled in shared forwards on a model sharded over two ranks (one segment per sequence,
+    a row budget per forward) give the tokens of per-sequence prefill on the unsharded model, and so does the next round."""
+    from spark_engine_b200.config import EngineConfig
+    from spark_engine_b200.models.weights import init_weights
+    from spark_engine_b200.serving.engine import LLMEngine
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_many, args=(r, 2, port, q, name)) for r in range(2)]
+    for p in procs:
+        p.start()
+    toks, nxt = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    cfg = _config(name)
+    W = init_weights(cfg, seed=0)
+    ref = LLMEngine(cfg, W, EngineConfig(cuda_graphs=False, prefill_chunk=16), device="cpu", max_seqs=3, kv_tokens_per_seq=128)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (29, 7, 40)]
+    want = [int(ref.prefill(s, p).argmax()) for s, p in enumerate(prompts)]
+    assert toks == want
+    assert nxt == ref.decode_round([0, 1, 2], want)
