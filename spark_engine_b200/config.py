@@ -249,6 +249,8 @@ class EngineConfig:
     port: int = 8000
     profile: bool = False
     prewarm: bool = False         # run synthetic requests for 1..max_seqs streams before serving (captures the graphs)
+    serve_log: bool = False       # one stderr line per admission / prefill forward / round ([serve-admit], [serve-round] ...)
+    draft_trace: str = ""         # file ("-" = stderr) that gets one JSON line per speculative round
     nvtx: bool = False
     log_rounds: bool = False
     seed: int = 0

@@ -253,7 +253,9 @@ class EngineServer:
         self.by_slot[plan.slot] = lv
         lv.seq = SeqSpec(plan.slot, -1, temperature=float(msg.get("temperature", 0.0)), seed=int(msg.get("seed", 0)))
         lv.seq.lookup = LookupIndex(self.spec.lookup_n)
-        lv.seq.lookup.extend(prompt[:reuse])
+        lv.seq.lookup.extend([t for t in prompt[:reuse] if t < self.cfg.vocab])
+        self._log("admit", id=lv.id, slot=plan.slot, kind=str(plan.kind).split(".")[-1], reuse=reuse, prompt=len(prompt),
+                  queue_ms=round((lv.t_admit - lv.t_arrive) * 1e3, 2))
 
     def _prefill(self, parts):
         """One forward over a prefill chunk of every listed sequence: parts = [(slot, first token, end)], one segment
@@ -285,6 +287,8 @@ class EngineServer:
                     mplan.has_media = any(lv.mm for lv in lives)
                     m.mtp_forward(mplan, rows[0] if len(rows) == 1 else torch.cat(rows))
         dt = (time.time() - t0) * 1e3
+        self._log("prefill", parts=[(slot, c0, c1) for slot, c0, c1 in parts], rows=sum(c1 - c0 for _, c0, c1 in parts),
+                  ms=round(dt, 2))
         self.totals["prefill_steps"] += 1
         self.totals["prefill_shared_steps"] += len(parts) > 1
         for k, ((slot, c0, c1), lv, seg) in enumerate(zip(parts, lives, plan.segs)):
@@ -306,6 +310,27 @@ class EngineServer:
                 if self.disk is not None and boundary and boundary == len(prompt):
                     self.disk.save(prompt, m.snapshot(slot))
                 self._emit(lv, [first])
+
+    def _log(self, tag: str, **kv):
+        """`[serve-<tag>] key=value ...` on stderr when EngineConfig.serve_log is set (reference: GLM53_SERVE_LOG lines
+        `[serve-round] rows .. accepted .. round_ms`, `[serve-admit]`, spec_probe.rs:1795,1838,2570)."""
+        if self.ecfg.serve_log:
+            import sys
+            print(f"[serve-{tag}] " + " ".join(f"{k}={v}" for k, v in kv.items()), file=sys.stderr, flush=True)
+
+    def _trace_round(self, rec: dict):
+        """One JSON line per speculative round (EngineConfig.draft_trace; reference: GLM53_DRAFT_TRACE, spec_probe.rs:1818-1827)."""
+        path = self.ecfg.draft_trace
+        if not path:
+            return
+        import json
+        import sys
+        line = json.dumps(rec, separators=(",", ":"))
+        if path == "-":
+            print(line, file=sys.stderr, flush=True)
+        else:
+            with open(path, "a") as f:
+                f.write(line + "\n")
 
     def _encode_media(self, lv: _Live, item, frame: int) -> torch.Tensor:
         """Rows of one canvas frame; a segment that straddles prefill chunks is encoded once."""
@@ -333,6 +358,7 @@ class EngineServer:
         lvs = [self.by_slot[s] for s in slots]
         t0 = time.time()
         budgets = [int(lv.msg.get("max_new", 256)) - lv.sent for lv in lvs]
+        before = [(lv.seq.drafted, lv.seq.accepted) for lv in lvs]
         stops = set()
         for lv in lvs:
             stops.update(lv.msg.get("stop_token_ids", []))
@@ -348,6 +374,14 @@ class EngineServer:
                 outs = self.spec.round([lv.seq for lv in lvs], budgets, stop=tuple(stops))
         dt = (time.time() - t0) * 1e3
         self.totals["spec_rounds"] += 1
+        if self.ecfg.serve_log or self.ecfg.draft_trace:
+            drafted = [lv.seq.drafted - b[0] for lv, b in zip(lvs, before)]
+            accepted = [lv.seq.accepted - b[1] for lv, b in zip(lvs, before)]
+            self._log("round", streams=len(lvs), rows=len(lvs) + sum(drafted), drafted=drafted, accepted=accepted,
+                      emitted=[len(o) for o in outs], round_ms=round(dt, 2))
+            self._trace_round({"round": self.totals["spec_rounds"], "ms": round(dt, 3),
+                               "seqs": [{"id": lv.id, "slot": s, "pos": self.model.seqs[s].length, "drafted": d, "accepted": a,
+                                         "emitted": list(o)} for lv, s, d, a, o in zip(lvs, slots, drafted, accepted, outs)]})
         for lv, out in zip(lvs, outs):
             lv.decode_ms += dt
             lv.rounds += 1

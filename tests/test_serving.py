@@ -206,3 +206,32 @@ def test_prewarmed_server_serves_the_same_tokens_and_starts_with_clean_counters(
     assert es.totals["requests"] == 2
     c.sendall(proto.encode({"shutdown": True}))
     th.join(10)
+
+
+def test_serve_log_lines_and_round_trace(tmp_path, capfd):
+    """EngineConfig.serve_log prints one line per admission, prefill forward and round; draft_trace appends one JSON line
+    per speculative round whose accepted / emitted counts add up to the served tokens."""
+    import json as js
+    from spark_engine_b200.serving.worker import EngineServer as ES
+    cfg = tiny_hybrid()
+    cfg.mtp_layers = 1
+    W = init_weights(cfg, seed=0)
+    trace = tmp_path / "trace.jsonl"
+    es = ES(cfg, W, EngineConfig(max_seqs=2, kv_tokens=2048, prefill_chunk=32, spec="mtp", spec_depth=2, serve_log=True,
+                                 draft_trace=str(trace)))
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    es.submit({"id": 7, "prompt_ids": prompt, "max_new": 9})
+    for _ in range(200):
+        if not es.step():
+            break
+    done = [m for m in es.out if m.get("done")]
+    assert done and len(done[0]["token_ids"]) == 9
+    err = capfd.readouterr().err
+    assert "[serve-admit] id=7 slot=0 kind=Cold reuse=0 prompt=40" in err
+    assert "[serve-prefill] parts=[(0, 0, 32)] rows=32" in err and "[serve-round] streams=1" in err
+    recs = [js.loads(l) for l in trace.read_text().splitlines()]
+    assert recs and all(r["seqs"][0]["id"] == 7 for r in recs)
+    assert sum(len(r["seqs"][0]["emitted"]) for r in recs) >= 8               # the first token comes from the prefill
+    assert sum(r["seqs"][0]["accepted"] for r in recs) == done[0]["accepted_drafts"]
+    assert [r["round"] for r in recs] == list(range(1, len(recs) + 1))
