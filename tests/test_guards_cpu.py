@@ -123,3 +123,32 @@ def test_batched_prefill_equals_per_sequence_prefill():
     assert [many.model.seqs[s].length for s in range(3)] == [37, 9, 64]
     nxt = ref.argmax(-1).tolist()
     assert many.decode_round([0, 1, 2], nxt) == one.decode_round([0, 1, 2], nxt)
+
+
+def test_row_invariance_probe_finds_the_first_layer_that_depends_on_the_batch():
+    """The probe reports nothing on the CPU runner (rows are independent) and names the layer once one layer's output is
+    made to depend on the number of rows in the forward."""
+    import torch
+    from spark_engine_b200.config import tiny_hybrid
+    from spark_engine_b200.models.model import Model
+    from spark_engine_b200.models.weights import init_weights
+    from spark_engine_b200.utils.invariance import first_divergent_layer
+    cfg = tiny_hybrid()
+    W = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (12, 9, 15)]
+    make = lambda: Model(cfg, W, n_slots=3, kv_tokens=192)
+    assert first_divergent_layer(make, prompts, probe=1, rows=2, atol=1e-5) is None
+
+    def make_bad():
+        m = Model(cfg, W, n_slots=3, kv_tokens=192)
+        lw, mix, mlp = m.layers[2]
+        real = mlp.forward
+
+        def leaky(h, defer=False):                      # a "kernel" whose result depends on how many rows it was given
+            out = real(h, defer)
+            return out + 1e-3 * (h.shape[0] > 2) if isinstance(out, torch.Tensor) else out
+        mlp.forward = leaky
+        return m
+    hit = first_divergent_layer(make_bad, prompts, probe=1, rows=2, atol=1e-5)
+    assert hit is not None and hit[0] == 2 and hit[1] > 5e-4
