@@ -345,6 +345,18 @@ def exl3_had_rows(x, scale, post: bool, row_expert=None, expert_stride=0):
     return y
 
 
+def exl3_fold(w: Exl3Weight) -> torch.Tensor:
+    """The dense bf16 weight [N, K] of an EXL3 tensor, made on the device: inner codebook values (any bit width), then
+    the input-side Hadamard + sign/scale along K and the output-side ones along N folded in, so that y = x @ W^T needs no
+    Hadamard passes at run time.  For tensors that are cheaper to keep dense than to decode on every call (a sub-vocabulary
+    head, a drafter's head).  Reference: engine-rs/shim/qwen_exl3.cuh:661 `fold_kernel`."""
+    assert not w.experts
+    wt = exl3_reconstruct(w).float()                                          # inner^T [N, K]
+    a = exl3_had_rows(wt, w.suh, post=True)                                   # rows n: had128 along K, x suh[k]
+    b = exl3_had_rows(a.t().float().contiguous(), w.svh, post=True)           # rows k: had128 along N, x svh[n]
+    return b.t().contiguous()
+
+
 def _pick_mg_slices(K: int, target: int) -> int:
     """K-slices (cluster size) of the grouped EXL3 GEMM: the smallest of 1/2/4/8 that brings the slice to <= target."""
     blocks = K // 128

@@ -177,6 +177,16 @@ def test_exl3_linear_other_bit_widths(bits, R):
     assert torch.equal(ops.linear(x, wd), ops.linear(x, wd))
 
 
+@pytest.mark.parametrize("bits", [4, 6])
+def test_exl3_fold_to_dense_matches_the_codec(bits):
+    """Inner weights + both Hadamard / scale sides folded into one dense bf16 matrix on the device."""
+    w = Q.random_exl3(384, 256, bits=bits, seed=21, std=0.05)
+    got = cu().exl3_fold(w.to(DEV)).float().cpu()            # [N, K]
+    ref = w.dequant()                                         # [N, K]
+    assert got.shape == ref.shape == (384, 256)
+    assert rel_err(got, ref) < 8e-3                           # two bf16 roundings
+
+
 @pytest.mark.parametrize("R", [1, 4, 16])
 @pytest.mark.parametrize("N,K", [(256, 512), (1024, 2048), (2048, 512)])
 def test_exl3_gemv_matches_dequant_matmul(R, N, K):
