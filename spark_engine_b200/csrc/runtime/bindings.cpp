@@ -129,12 +129,13 @@ PYBIND11_MODULE(_runtime, m) {
       .def_property_readonly("ptr", [](const PinnedBuffer& b) { return reinterpret_cast<uint64_t>(b.data()); })
       .def_buffer([](PinnedBuffer& b) { return py::buffer_info(b.data(), 1, py::format_descriptor<uint8_t>::format(), 1, {b.size()}, {1}); });
   py::class_<LoadStats>(m, "LoadStats").def_readonly("bytes", &LoadStats::bytes).def_readonly("reads", &LoadStats::reads)
-      .def_readonly("copies", &LoadStats::copies).def_readonly("read_s", &LoadStats::read_s).def_readonly("total_s", &LoadStats::total_s);
+      .def_readonly("copies", &LoadStats::copies).def_readonly("read_s", &LoadStats::read_s).def_readonly("total_s", &LoadStats::total_s).def_readonly("direct", &LoadStats::direct);
   m.def("fast_load", [pick](const std::string& path, int64_t offset, int64_t size, uint64_t dst, uint64_t stream, size_t chunk,
-                            int n_buffers, int n_threads, bool fake) {
+                            int n_buffers, int n_threads, bool fake, bool direct) {
           py::gil_scoped_release rel;
-          return fast_load(pick(fake), path, offset, size, dst, stream, chunk, n_buffers, n_threads);
+          return fast_load(pick(fake), path, offset, size, dst, stream, chunk, n_buffers, n_threads, direct);
         }, py::arg("path"), py::arg("offset"), py::arg("size"), py::arg("dst"), py::arg("stream") = 0,
-        py::arg("chunk") = 64 << 20, py::arg("n_buffers") = 3, py::arg("n_threads") = 2, py::arg("fake") = false);
+        py::arg("chunk") = 64 << 20, py::arg("n_buffers") = 3, py::arg("n_threads") = 2, py::arg("fake") = false,
+        py::arg("direct") = false);
   m.def("sha256_hex", [](py::bytes b) { std::string s = b; Sha256 h; h.update(s.data(), s.size()); return h.hex(); });
 }

@@ -218,17 +218,24 @@ PinnedBuffer::~PinnedBuffer() {
 
 // ------------------------------------------------------------------------------------------------ fast_load
 LoadStats fast_load(const DriverApi* api, const std::string& path, int64_t offset, int64_t size, uint64_t dst, uint64_t stream,
-                    size_t chunk, int n_buffers, int n_threads) {
+                    size_t chunk, int n_buffers, int n_threads, bool direct) {
   if (!api) throw std::runtime_error("no CUDA driver on this host");
   LoadStats st;
   const auto t0 = std::chrono::steady_clock::now();
-  const int fd = open(path.c_str(), O_RDONLY);
+  constexpr int64_t kAlign = 4096;
+  int fd = -1;
+  if (direct) fd = open(path.c_str(), O_RDONLY | O_DIRECT);
+  st.direct = fd >= 0;
+  if (fd < 0) fd = open(path.c_str(), O_RDONLY);
   if (fd < 0) throw std::runtime_error("fast_load: cannot open " + path);
-  posix_fadvise(fd, offset, size, POSIX_FADV_SEQUENTIAL);
+  if (!st.direct) posix_fadvise(fd, offset, size, POSIX_FADV_SEQUENTIAL);
   n_buffers = std::max(2, n_buffers);
   n_threads = std::max(1, n_threads);
   std::vector<std::unique_ptr<PinnedBuffer>> bufs;
-  for (int i = 0; i < n_buffers; ++i) bufs.emplace_back(new PinnedBuffer(api, chunk, chunk >= (2u << 20)));
+  // direct reads start and end on 4 KiB boundaries of the file: room for the widened head and tail
+  const size_t buf_bytes = chunk + (st.direct ? 2 * static_cast<size_t>(kAlign) : 0);
+  for (int i = 0; i < n_buffers; ++i) bufs.emplace_back(new PinnedBuffer(api, buf_bytes, buf_bytes >= (2u << 20)));
+  std::vector<size_t> head(n_buffers, 0);             // where a chunk's first byte sits inside its buffer
   const int64_t n_chunks = (size + static_cast<int64_t>(chunk) - 1) / static_cast<int64_t>(chunk);
   // chunk c uses buffer c % n_buffers; a buffer is free again once the copy of chunk c - n_buffers was synchronised
   std::mutex mu;
@@ -251,12 +258,18 @@ LoadStats fast_load(const DriverApi* api, const std::string& path, int64_t offse
       const int64_t off = c * static_cast<int64_t>(chunk);
       const size_t n = static_cast<size_t>(std::min<int64_t>(chunk, size - off));
       const auto r0 = std::chrono::steady_clock::now();
+      const int64_t fo = offset + off;                                      // file position of the chunk
+      const int64_t a0 = st.direct ? fo / kAlign * kAlign : fo;             // where the read starts
+      const size_t h = static_cast<size_t>(fo - a0);
+      const size_t want = st.direct ? (h + n + kAlign - 1) / kAlign * kAlign : n;   // may reach past the end of the file
       size_t got = 0;
-      while (got < n) {
-        const ssize_t k = pread(fd, static_cast<char*>(bufs[b]->data()) + got, n - got, offset + off + static_cast<int64_t>(got));
+      while (got < h + n) {
+        const ssize_t k = pread(fd, static_cast<char*>(bufs[b]->data()) + got, want - got, a0 + static_cast<int64_t>(got));
         if (k <= 0) { failed = true; cv.notify_all(); return; }
         got += static_cast<size_t>(k);
+        if (st.direct && (got % kAlign) != 0 && got < h + n) { failed = true; cv.notify_all(); return; }   // short, unaligned, not at the end
       }
+      head[b] = h;
       read_ns += std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - r0).count();
       {
         std::lock_guard<std::mutex> lk(mu);
@@ -276,7 +289,8 @@ LoadStats fast_load(const DriverApi* api, const std::string& path, int64_t offse
     }
     const int64_t off = c * static_cast<int64_t>(chunk);
     const size_t n = static_cast<size_t>(std::min<int64_t>(chunk, size - off));
-    if (api->memcpy_htod_async(dst + static_cast<uint64_t>(off), bufs[b]->data(), n, stream) != 0 || api->stream_sync(stream) != 0) {
+    if (api->memcpy_htod_async(dst + static_cast<uint64_t>(off), static_cast<char*>(bufs[b]->data()) + head[b], n, stream) != 0 ||
+        api->stream_sync(stream) != 0) {
       failed = true;
     }
     {

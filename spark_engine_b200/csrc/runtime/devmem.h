@@ -71,9 +71,12 @@ class PinnedBuffer {
   bool registered_ = false;
 };
 
-struct LoadStats { int64_t bytes = 0, reads = 0, copies = 0; double read_s = 0, total_s = 0; };
+struct LoadStats { int64_t bytes = 0, reads = 0, copies = 0; double read_s = 0, total_s = 0; bool direct = false; };
 
 // Copy file[offset, offset+size) to device memory at dst through `n_buffers` pinned staging buffers of `chunk` bytes,
 // `n_threads` reader threads.  Blocks until every copy has been issued and the stream is synchronised.
+// `direct`: read with O_DIRECT (no page cache: a checkpoint larger than host memory does not evict everything else and
+// is not copied twice); reads are widened to 4 KiB boundaries inside the staging buffer.  Falls back to buffered reads
+// when the file system refuses the flag (LoadStats::direct tells which).
 LoadStats fast_load(const DriverApi* api, const std::string& path, int64_t offset, int64_t size, uint64_t dst, uint64_t stream,
-                    size_t chunk, int n_buffers, int n_threads);
+                    size_t chunk, int n_buffers, int n_threads, bool direct = false);

@@ -122,6 +122,11 @@ static void stress_fast_load(const std::string& root) {
   const LoadStats st = fast_load(api, path, 0, static_cast<int64_t>(n), reinterpret_cast<uint64_t>(dst.data()), 0, 256 << 10, 3, 3);
   EXPECT(st.bytes == static_cast<int64_t>(n));
   EXPECT(std::memcmp(src.data(), dst.data(), n) == 0);
+  // the same through O_DIRECT reads at an unaligned offset (falls back to buffered reads where the flag is refused)
+  std::vector<unsigned char> dst2(n - 4099, 0);
+  const LoadStats st2 = fast_load(api, path, 4099, static_cast<int64_t>(n - 4099), reinterpret_cast<uint64_t>(dst2.data()), 0, 300001, 2, 3, true);
+  EXPECT(st2.bytes == static_cast<int64_t>(n - 4099));
+  EXPECT(std::memcmp(src.data() + 4099, dst2.data(), n - 4099) == 0);
 }
 
 int main(int argc, char** argv) {

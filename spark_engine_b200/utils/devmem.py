@@ -3,6 +3,9 @@ staging buffers and the threaded file -> device loader.  Reference: engine-rs/sr
 shim/vmm.cpp, shim/host_pin.cuh, weights.rs:194-283."""
 from __future__ import annotations
 
+import os
+from typing import Optional
+
 import torch
 
 from .. import runtime as rt
@@ -54,13 +57,16 @@ class GrowableDeviceBuffer:
 
 
 def load_file_range_to(t: torch.Tensor, path: str, offset: int, chunk: int = 64 << 20, n_buffers: int = 3,
-                       n_threads: int = 2):
+                       n_threads: int = 2, direct: Optional[bool] = None):
     """Fill the contiguous device tensor `t` with file bytes [offset, offset + t.nbytes) through pinned staging buffers
-    (reader threads overlap the disk reads with the host-to-device copies)."""
+    (reader threads overlap the disk reads with the host-to-device copies).  `direct` (default: SPARK_LOAD_DIRECT=1)
+    reads with O_DIRECT, bypassing the page cache; the returned stats say whether the file system took the flag."""
     assert t.is_contiguous()
+    if direct is None:
+        direct = os.environ.get("SPARK_LOAD_DIRECT", "0") == "1"
     n = t.numel() * t.element_size()
     if t.is_cuda:
         with torch.cuda.device(t.device):
             return rt.rt().fast_load(path, offset, n, t.data_ptr(), torch.cuda.current_stream().cuda_stream, chunk,
-                                      n_buffers, n_threads, False)
-    return rt.rt().fast_load(path, offset, n, t.data_ptr(), 0, chunk, n_buffers, n_threads, True)
+                                      n_buffers, n_threads, False, bool(direct))
+    return rt.rt().fast_load(path, offset, n, t.data_ptr(), 0, chunk, n_buffers, n_threads, True, bool(direct))

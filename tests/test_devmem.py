@@ -42,6 +42,14 @@ def test_fast_load_through_staging_ring_fake(tmp_path):
         load_file_range_to(torch.zeros(10, dtype=torch.uint8), str(tmp_path / "missing"), 0)
     pb = rt.rt().PinnedBuffer(100000, False, True)
     assert pb.size >= 100000 and memoryview(pb).nbytes == pb.size
+    # O_DIRECT reads: unaligned offset and size, chunks that are not multiples of 4 KiB, the tail past the last aligned
+    # block of the file; the bytes are the same whether or not the file system takes the flag
+    for off, n, chunk in ((4, data.numel(), 1 << 20), (4099, 777777, 300001), (8192, 4096, 1 << 16), (1, data.numel() + 3, 999983)):
+        dst2 = torch.zeros(n, dtype=torch.uint8)
+        raw = (b"HEAD" + data.numpy().tobytes())[off: off + n]
+        st2 = load_file_range_to(dst2, str(p), off, chunk=chunk, n_buffers=2, n_threads=2, direct=True)
+        assert bytes(dst2.numpy().tobytes()) == raw and st2.bytes == n
+        assert isinstance(st2.direct, bool)
 
 
 @pytest.mark.gpu
