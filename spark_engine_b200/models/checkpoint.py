@@ -180,20 +180,43 @@ def _to_device(x, device, pinned: bool):
     return x
 
 
+def _streamed_tensor(st, name: str, device) -> torch.Tensor:
+    """A tensor read from its byte range of the file straight to `device` by the threaded loader (reader threads fill
+    pinned staging buffers, copies are issued as they land; O_DIRECT with SPARK_LOAD_DIRECT=1): no mapping of the file,
+    no second host copy.  Reference: engine-rs/src/weights.rs:194-283 (pread -> pinned staging -> device)."""
+    from ..utils.devmem import load_file_range_to
+    info = st.info(name)
+    dt = _RDT[info.dtype]
+    t = torch.empty(*info.shape, dtype=dt, device=device)
+    if info.end > info.begin:
+        load_file_range_to(t, st.path(), st.data_offset() + info.begin, chunk=32 << 20)
+    return t
+
+
 def load_checkpoint(directory: str, device="cpu", tp: Tuple[int, int] = (0, 1), pinned: bool = True,
-                    cfg: Optional[ModelConfig] = None):
-    """-> (cfg, W) with W this rank's shard on `device`."""
+                    cfg: Optional[ModelConfig] = None, stream: Optional[bool] = None):
+    """-> (cfg, W) with W this rank's shard on `device`.  `stream` (default: SPARK_LOAD_STREAM=1): an unsharded load (one
+    rank, or a directory written by `write_rank_shards`) reads every tensor straight to the device through the threaded
+    loader instead of mapping the files."""
     cfg = cfg or load_config(directory)
     with open(os.path.join(directory, INDEX)) as f:
         idx = json.load(f)
+    rank, world = tp
+    if stream is None:
+        stream = os.environ.get("SPARK_LOAD_STREAM", "0") == "1"
+    stream = bool(stream) and world == 1
     files = {}
     tensors = {}
     for name, fn in idx["weight_map"].items():
         if fn not in files:
             files[fn] = rt().SafeTensors(os.path.join(directory, fn))        # validates the header and every offset
-        tensors[name] = _mapped_tensor(files[fn], name)
+        tensors[name] = _streamed_tensor(files[fn], name, device) if stream else _mapped_tensor(files[fn], name)
     W = unflatten(tensors, idx["weights"], idx["structure"])
-    rank, world = tp
+    if stream:
+        _rebuild_shared_views(W)
+        if str(device) != "cpu":
+            torch.cuda.synchronize()
+        return cfg, W
     if world > 1:
         from ..parallel.tp import shard_weights
         W = shard_weights(W, cfg, rank, world)

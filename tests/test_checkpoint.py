@@ -43,6 +43,14 @@ def test_round_trip_and_shards(tmp_path, fmt):
     cfg2, W2 = load_checkpoint(d, "cpu")
     assert cfg2.to_json() == cfg.to_json()
     _same(W, W2)
+    # the streamed load (reader threads -> staging buffers -> destination, with and without O_DIRECT) gives the same bytes
+    for direct in ("0", "1"):
+        os.environ["SPARK_LOAD_DIRECT"] = direct
+        try:
+            _, W3 = load_checkpoint(d, "cpu", stream=True)
+        finally:
+            os.environ.pop("SPARK_LOAD_DIRECT", None)
+        _same(W, W3)
     # a rank's shard loaded from disk == the shard cut from the in-memory model
     for rank in range(2):
         _, Wr = load_checkpoint(d, "cpu", tp=(rank, 2))
