@@ -101,14 +101,30 @@ Step Scheduler::next(int64_t disk_prefix_tokens) {
   const bool do_prefill = !pre.empty() && (dec.empty() || !last_was_prefill_);
   if (do_prefill) {
     const int n = static_cast<int>(pre.size()), first = rr_++ % n;
-    const int64_t share = std::max<int64_t>(1, chunk_ / n);
     s.kind = Step::Prefill;
+    // equal shares of the chunk budget; what a sequence with few tokens left does not use goes to the others (two passes:
+    // sequences that fit their share first, then the rest split what remains)
+    std::vector<int64_t> want(n), give(n, 0);
+    int64_t budget = chunk_;
+    int open = n;
+    for (int k = 0; k < n; ++k) { const int i = pre[(first + k) % n]; want[k] = slots_[i].prompt_len - slots_[i].prefilled; }
+    for (int pass = 0; pass < 2 && open > 0; ++pass) {
+      const int64_t share = std::max<int64_t>(1, budget / open);
+      for (int k = 0; k < n; ++k) {
+        if (give[k] > 0) continue;
+        if (pass == 0 && want[k] > share) continue;             // the long ones wait for the second pass
+        give[k] = std::min(want[k], std::max<int64_t>(share, 1));
+        budget -= give[k];
+        --open;
+      }
+      if (budget < open) budget = open;                            // every sequence advances by at least one token
+    }
     for (int k = 0; k < n; ++k) {
       const int i = pre[(first + k) % n];
       PrefillPart p;
       p.slot = i;
       p.begin = slots_[i].prefilled;
-      p.end = std::min<int64_t>(slots_[i].prompt_len, p.begin + share);
+      p.end = p.begin + give[k];
       s.parts.push_back(p);
     }
     s.slot = s.parts[0].slot; s.chunk_begin = s.parts[0].begin; s.chunk_end = s.parts[0].end;

@@ -65,6 +65,28 @@ def test_pcache_roundtrip_corruption_eviction_and_restart(tmp_path):
     assert [e.key for e in pc2.entries()] == [k1]
 
 
+def test_scheduler_prefill_shares_are_redistributed():
+    """Sequences with few prompt tokens left take what they need; the long ones split the rest of the chunk budget."""
+    R = rt()
+    s = R.Scheduler(4, 1 << 20, 1 << 18, 64, 4)
+    for i, n in enumerate((500, 5, 300, 11)):
+        r = R.Request()
+        r.id, r.prompt, r.max_new = i + 1, list(range(n)), 4
+        s.submit(r)
+        st = s.next()
+        assert st.kind == R.Step.Kind.Admit
+        s.on_admitted(st.admit)
+    st = s.next()
+    parts = sorted((p.slot, p.begin, p.end) for p in st.parts)
+    assert st.kind == R.Step.Kind.Prefill and parts == [(0, 0, 24), (1, 0, 5), (2, 0, 24), (3, 0, 11)]
+    for p in st.parts:
+        s.on_prefilled(p.slot, p.end)
+    st = s.next()                                   # slots 1 and 3 are done prefilling: a decode round comes first
+    assert st.kind == R.Step.Kind.Decode and list(st.decode_slots) == [1, 3]
+    st = s.next()
+    assert sorted((p.slot, p.begin, p.end) for p in st.parts) == [(0, 24, 56), (2, 24, 56)]
+
+
 def test_scheduler_admission_prefix_reuse_and_round_robin():
     R = rt()
     s = R.Scheduler(2, 4096, 2048, 64, 4)
