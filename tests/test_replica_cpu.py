@@ -56,7 +56,7 @@ def _worker(rank, world, port, name, mode, q):
     else:
         f = Follower(name, rank - 1, world - 1, deadline_ms=5000)
         if mode == "follower_stops":
-            f.run(srv, max_ops=12)                       # leaves between steps, nothing in flight
+            f.run(srv, max_ops=7)                        # leaves between steps, nothing in flight
             q.put(("follower_left", f.seq))
         else:
             f.run(srv)
