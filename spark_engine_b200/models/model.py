@@ -823,6 +823,22 @@ class Model:
 
     # -- MTP drafter ------------------------------------------------------------------------
     @torch.no_grad()
+    def sparse_ctx_limit(self) -> Optional[int]:
+        """Context length up to which every sparse-attention layer still selects all of it (block-sparse GQA: top-k blocks x
+        block; latent attention: top-k pools x pool), or None when no layer selects.  Up to here dense visibility of the
+        committed context (what tree-verification rows use) equals what a decode row sees."""
+        lim = None
+        for _, mix, _ in self.layers:
+            c = getattr(mix, "c", None)
+            if isinstance(mix, AttnMixer) and c.sparse_topk_blocks:
+                v = c.sparse_topk_blocks * c.block
+            elif isinstance(mix, MlaMixer):
+                v = c.topk_pools * c.pool
+            else:
+                continue
+            lim = v if lim is None else min(lim, v)
+        return lim
+
     def mtp_forward(self, plan: Plan, hidden: torch.Tensor):
         """Draft logits: row i combines embed(plan.ids[i]) (the NEXT token) with `hidden[i]` (target
         hidden of the previous position).  plan positions index the drafter's own KV cache.  Blocks run like the

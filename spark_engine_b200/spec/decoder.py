@@ -155,21 +155,26 @@ class SpecDecoder:
         return out
 
     @torch.no_grad()
-    def round(self, seqs: List[SeqSpec], budgets: Optional[List[int]] = None, stop: Sequence[int] = ()) -> List[List[int]]:
-        """One speculative round over all given sequences.  Returns the tokens emitted per sequence."""
+    def round(self, seqs: List[SeqSpec], budgets: Optional[List[int]] = None, stop: Sequence[int] = (),
+              proposals: Optional[List[tuple]] = None) -> List[List[int]]:
+        """One speculative round over all given sequences.  Returns the tokens emitted per sequence.  `proposals`:
+        (draft tokens, confidences) per sequence from the caller instead of the drafter."""
         m = self.m
         L = [m.seqs[s.slot].length for s in seqs]
         k_graph = 1 + self.depth
         use_g = (self.graphs is not None and len(seqs) * k_graph <= 16
                  and all(l + k_graph + 1 <= m.seqs[s.slot].kv_cap for s, l in zip(seqs, L)))
-        if use_g and self.depth > 0 and isinstance(self.drafter, MtpDrafter) and \
+        given = proposals is not None
+        if given:
+            pass
+        elif use_g and self.depth > 0 and isinstance(self.drafter, MtpDrafter) and \
                 all(1 <= len(s.pending_mtp) <= k_graph for s in seqs):
             proposals = self._propose_graph(seqs, L)
         else:
             proposals = [self._draft(s, self.depth) for s in seqs]
         drafts, draft_confs = [], []
         for s, (d, c) in zip(seqs, proposals):
-            k = self._choose(s, c, len(seqs), sum(1 + len(x) for x in drafts))
+            k = len(d) if given else self._choose(s, c, len(seqs), sum(1 + len(x) for x in drafts))
             drafts.append(list(d[:k]))
             draft_confs.append(list(c[:k]))
         toks = [[s.last_token] + d for s, d in zip(seqs, drafts)]
@@ -244,9 +249,25 @@ class SpecDecoder:
         """One speculative round with a verification TREE per sequence (nodes in topological order, parent -1 = the
         last sampled token): every node is one extra row that sees the committed context plus its own ancestors; the
         accept walk follows the target's samples through the tree and the accepted root-to-leaf path is committed
-        (linear-attention states replayed along the path, KV rows compacted).  Reference: engine-rs/src/speculative.rs,
+        (linear-attention states replayed along the path, KV rows compacted).  Tree rows read the committed context
+        densely, which equals sequential decoding only while the sparse-attention layers still select everything; past
+        that context the tree's first-child spine is verified as a chain (whose rows go through the selection like
+        decode rows), so the round stays lossless.  Reference: engine-rs/src/speculative.rs,
         spec_probe.rs:254-460 (tree topologies), mla_latent.rs:472-773."""
         m = self.m
+        limit = m.sparse_ctx_limit()
+        if limit is not None and any(m.seqs[s.slot].length + 1 + len(nodes) > limit for s, nodes in zip(seqs, trees)):
+            props = []
+            for nodes in trees:
+                spine, cur = [], -1
+                while True:
+                    nxt = next((i for i, nd in enumerate(nodes) if nd.parent == cur), None)
+                    if nxt is None:
+                        break
+                    spine.append(nodes[nxt].token)
+                    cur = nxt
+                props.append((spine, [0.5] * len(spine)))
+            return self.round(seqs, budgets, stop, proposals=props)
         items, parents = [], []
         for s, nodes in zip(seqs, trees):
             L = m.seqs[s.slot].length

@@ -1,5 +1,6 @@
 """Speculative decoding: acceptance walk unit tests (in the spirit of engine-rs/src/speculative.rs:40-80) and
 end-to-end exactness: speculative output == plain greedy output, token for token."""
+import pytest
 import torch
 
 from spark_engine_b200.config import tiny_hybrid
@@ -117,3 +118,41 @@ def test_sampled_speculation_is_a_function_of_the_seed():
         m = Model(cfg, W, n_slots=1, kv_tokens=128)
         outs.append(SpecDecoder(m, drafter, depth=3).generate([prompt], 10, temperature=1.0, seed=42)[0])
     assert outs[0] == outs[1]          # with and without drafts: same text for the same seed
+
+
+@pytest.mark.parametrize("family", ["hybrid", "glm"])
+def test_tree_rounds_stay_lossless_past_the_dense_context(family):
+    """Tree rows read the committed context densely; once the sparse-attention layers select (context beyond top-k
+    blocks x block) that is no longer what a decode row sees, so the round verifies the tree's spine as a chain: the
+    text is still plain greedy decoding and the right drafts are still accepted."""
+    import dataclasses
+    from spark_engine_b200.config import get_model_config, scaled_down, tiny_hybrid
+    from spark_engine_b200.models.model import Model
+    from spark_engine_b200.models.weights import init_weights
+    from spark_engine_b200.spec.decoder import SpecDecoder
+    if family == "hybrid":
+        cfg = tiny_hybrid()
+        cfg.layer_types = ["gdn", "attn", "gdn", "attn"]
+        cfg.attn = dataclasses.replace(cfg.attn, sparse_topk_blocks=4, block=4, idx_heads=2, idx_dim=32, rope_dim=32)
+    else:
+        cfg = scaled_down(get_model_config("glm-style"))
+        cfg.mtp_layers = 0
+    W = init_weights(cfg, seed=1)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab, (60,), generator=g).tolist()
+    ref = SpecDecoder(Model(cfg, W, n_slots=1, kv_tokens=256), lambda s, d: ([], []), depth=0).generate([prompt], 14)[0]
+    m = Model(cfg, W, n_slots=1, kv_tokens=256)
+    assert m.sparse_ctx_limit() is not None and m.sparse_ctx_limit() < len(prompt)
+    sd = SpecDecoder(m, lambda s, d: ([], []), depth=0)
+    seq = sd.start(0, prompt)
+    while len(seq.generated) < 14:
+        n = len(seq.generated)
+        nodes, parent = [], -1
+        for tok in ref[n: n + 3]:
+            first = len(nodes)
+            nodes.append(Node(parent, tok))
+            nodes.append(Node(parent, (tok + 1) % cfg.vocab))
+            parent = first
+        sd.round_tree([seq], [nodes], budgets=[14 - n])
+    assert seq.generated[:14] == ref
+    assert seq.accepted >= 8
